@@ -1,0 +1,111 @@
+"""ctypes binding of libcssm_b200.so.  There is no fallback: if the library is missing the
+import of anything that computes raises, telling the user to build it."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcssm_b200.so")
+
+ROPE_MODES = {"none": 0, "spatiotemporal": 1, "temporal": 2, "spatial_only": 3, "mrope": 4}
+GATE_TYPES = {"dense": 0, "factored": 1}
+GATE_ACTS = {"softplus": 0, "sigmoid": 1, "exp": 2}
+
+
+class CssmError(RuntimeError):
+    pass
+
+
+class GatedDesc(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("W", C.c_int32),
+                ("C", C.c_int32), ("kernel_size", C.c_int32), ("rope_mode", C.c_int32),
+                ("rope_base", C.c_float), ("spectral_rho", C.c_float),
+                ("gate_activation", C.c_int32), ("short_conv_size", C.c_int32),
+                ("short_conv_spatial_size", C.c_int32), ("gate_type", C.c_int32)]
+
+
+class GatedWeights(C.Structure):
+    _fields_ = [("in_proj_kernel", C.c_void_p), ("in_proj_bias", C.c_void_p),
+                ("conv_sp_kernel", C.c_void_p), ("conv_sp_bias", C.c_void_p),
+                ("conv_t_kernel", C.c_void_p), ("conv_t_bias", C.c_void_p),
+                ("kernel", C.c_void_p),
+                ("gate_kernel", C.c_void_p * 6), ("gate_bias", C.c_void_p * 6),
+                ("out_proj_kernel", C.c_void_p), ("out_proj_bias", C.c_void_p)]
+
+
+class GatedWsLayout(C.Structure):
+    _fields_ = [("xz_planar", C.c_size_t), ("ctx_sum", C.c_size_t),
+                ("gate_maps", C.c_size_t), ("total", C.c_size_t)]
+
+
+class GdnDesc(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("W", C.c_int32),
+                ("C", C.c_int32), ("delta_key_dim", C.c_int32), ("kernel_size", C.c_int32),
+                ("rope_mode", C.c_int32), ("rope_base", C.c_float), ("spectral_rho", C.c_float),
+                ("gate_type", C.c_int32), ("short_conv_size", C.c_int32),
+                ("output_norm", C.c_int32), ("use_input_gates", C.c_int32),
+                ("output_gate_act", C.c_int32), ("use_spectral_l2_norm", C.c_int32),
+                ("qkv_conv_size", C.c_int32), ("no_spectral_clamp", C.c_int32)]
+
+
+class GdnWeights(C.Structure):
+    _fields_ = [("kernel", C.c_void_p),
+                ("qkv_dw_kernel", C.c_void_p), ("qkv_dw_bias", C.c_void_p),
+                ("qkv_proj_kernel", C.c_void_p), ("qkv_proj_bias", C.c_void_p),
+                ("conv_t_kernel", C.c_void_p * 3), ("conv_t_bias", C.c_void_p * 3),
+                ("gate_kernel", C.c_void_p * 8), ("gate_bias", C.c_void_p * 8),
+                ("gate_proj_kernel", C.c_void_p), ("gate_proj_bias", C.c_void_p),
+                ("rms_scale", C.c_void_p),
+                ("output_proj_kernel", C.c_void_p), ("output_proj_bias", C.c_void_p)]
+
+
+# name -> (restype, argtypes); every symbol include/cssm_b200.h declares
+_P = C.c_void_p
+SIGNATURES = {
+    "cssm_strerror": (C.c_char_p, [C.c_int]),
+    "cssm_last_cuda_error": (C.c_char_p, []),
+    "cssm_version": (C.c_char_p, []),
+    "cssm_gated_plan_bytes": (C.c_size_t, [C.POINTER(GatedDesc)]),
+    "cssm_gated_workspace_bytes": (C.c_size_t, [C.POINTER(GatedDesc)]),
+    "cssm_gated_plan_init": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P,
+                                       C.c_size_t, _P]),
+    "cssm_gated_forward": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P,
+                                     _P, C.c_size_t, _P]),
+    "cssm_gated_host_workspace_bytes": (C.c_size_t, [C.POINTER(GatedDesc), C.c_int32]),
+    "cssm_gated_forward_host": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
+                                          _P, C.c_int32, _P, C.c_size_t, _P]),
+    "cssm_gated_in_proj": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P, _P]),
+    "cssm_gated_short_conv": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P]),
+    "cssm_gated_gates": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P]),
+    "cssm_gated_spectral": (C.c_int, [C.POINTER(GatedDesc), _P, _P, _P, _P]),
+    "cssm_gated_out_proj": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P]),
+    "cssm_gated_workspace_layout": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWsLayout)]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises CssmError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise CssmError(
+                f"{LIB_PATH} is missing: build it with `python -m cssm_b200.build` "
+                "(needs nvcc).  cssm_b200 has no CPU or PyTorch fallback.")
+        h = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(h, name)          # AttributeError here = header/library mismatch
+            fn.restype = res
+            fn.argtypes = args
+        _lib = h
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        L = lib()
+        msg = L.cssm_strerror(status).decode()
+        extra = L.cssm_last_cuda_error().decode() if status == 6 else ""
+        raise CssmError(f"{what}: {msg} (status {status}) {extra}".strip())

@@ -1,0 +1,54 @@
+// Shared helpers for the cssm_b200 CUDA sources (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+#include "../../include/cssm_b200.h"
+
+namespace cssm {
+
+struct __align__(8) cf {
+  float x, y;
+};
+
+__device__ __forceinline__ cf mk(float x, float y) { cf r; r.x = x; r.y = y; return r; }
+__device__ __forceinline__ cf operator+(cf a, cf b) { return mk(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ cf operator-(cf a, cf b) { return mk(a.x - b.x, a.y - b.y); }
+__device__ __forceinline__ cf cmul(cf a, cf b) {
+  return mk(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
+}
+// a * conj(b)
+__device__ __forceinline__ cf cmulc(cf a, cf b) {
+  return mk(a.x * b.x + a.y * b.y, a.y * b.x - a.x * b.y);
+}
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + __expf(-v)); }
+
+// Host-side record of the last CUDA error seen on this thread.
+void set_cuda_error(cudaError_t e);
+int check_launch();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- plan layouts (device memory prepared by *_plan_init) ----
+struct GatedPlan {
+  size_t khat;     // cf [C][H*Wf] in the bin order of the spectral kernel in use
+  size_t rope_t;   // float2 [T][C/2]  (cos, sin)
+  size_t rope_h;   // float2 [H][C/2]
+  size_t rope_w;   // float2 [W][C/2]
+  size_t total;
+};
+GatedPlan gated_plan_layout(const cssm_gated_desc& d);
+
+// Which spectral kernel handles an (H, W) plane.
+enum SpectralPath { PATH_GENERIC = 0, PATH_R64 = 1 };
+SpectralPath spectral_path(int H, int W);
+
+// Position of frequency bin (kh, kw) inside a per-(b,t) gate map / per-channel K_hat.
+__host__ __device__ inline int bin_index(int path, int kh, int kw, int H, int Wf) {
+  if (path == PATH_R64) return (((kh >> 3) * 33 + kw) << 3) + (kh & 7);
+  return kh * Wf + kw;
+}
+
+}  // namespace cssm

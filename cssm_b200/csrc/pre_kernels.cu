@@ -1,0 +1,302 @@
+// Weight-only precompute (kernel spectrum, RoPE tables), the per-plane short-conv stencil
+// with its plane sums, and the gate-map kernels.
+#include "kernels.cuh"
+
+namespace cssm {
+
+// ------------------------------------------------------------ kernel spectrum ----
+// K[c][kh][kw] = rfft2(centre-padded k[c]) squashed to |K| < rho, floored at 1e-7.
+// One thread per bin; double precision (runs once per weight set).
+__global__ void khat_kernel(const float* __restrict__ k, cf* __restrict__ out, int nch, int ks,
+                            int H, int W, float rho, int squash, int floor_eps, int path) {
+  const int Wf = W / 2 + 1, NB = H * Wf;
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= nch * NB) return;
+  const int c = o / NB, bin = o % NB, kh = bin / Wf, kw = bin % Wf;
+  // crop (ks > H or W) or centre-pad, exactly as the reference slices / pads
+  int i0 = 0, i1 = ks, j0 = 0, j1 = ks, offh, offw;
+  if (ks > H || ks > W) {
+    const int sh = (ks - H) / 2, sw = (ks - W) / 2;
+    i0 = sh; i1 = sh + H; j0 = sw; j1 = sw + W; offh = -sh; offw = -sw;
+    if (i0 < 0) { i0 = 0; }
+    if (j0 < 0) { j0 = 0; }
+    if (i1 > ks) i1 = ks;
+    if (j1 > ks) j1 = ks;
+  } else {
+    offh = (H - ks) / 2; offw = (W - ks) / 2;
+  }
+  double re = 0.0, im = 0.0;
+  for (int i = i0; i < i1; ++i) {
+    const int ph = i + offh;
+    if (ph < 0 || ph >= H) continue;
+    for (int j = j0; j < j1; ++j) {
+      const int pw = j + offw;
+      if (pw < 0 || pw >= W) continue;
+      const double ang = -2.0 * ((double)((kh * ph) % H) / H + (double)((kw * pw) % W) / W);
+      double s, co;
+      sincospi(ang, &s, &co);
+      const double v = k[((size_t)c * ks + i) * ks + j];
+      re += v * co; im += v * s;
+    }
+  }
+  if (squash) {
+    const double mag = sqrt(re * re + im * im);
+    const double sc = (double)rho / (1.0 + mag);
+    re *= sc; im *= sc;
+  }
+  if (floor_eps && sqrt(re * re + im * im) < 1e-7) { re = 1e-7; im = 0.0; }
+  out[(size_t)c * NB + bin_index(path, kh, kw, H, Wf)] = mk((float)re, (float)im);
+}
+
+int launch_khat(const float* k, cf* out, int nch, int ks, int H, int W, float rho, int squash,
+                int floor_eps, int path, cudaStream_t st) {
+  const int n = nch * H * (W / 2 + 1);
+  khat_kernel<<<(n + 127) / 128, 128, 0, st>>>(k, out, nch, ks, H, W, rho, squash, floor_eps, path);
+  return check_launch();
+}
+
+// ---------------------------------------------------------------- RoPE tables ----
+// (cos, sin)(pos * f_axis[i]) for the three axes; f_axis comes from the mode exactly as
+// apply_rope slices and right-pads inv_freq (cssm.py:125-244).
+__device__ double rope_freq(int axis, int i, int n, int mode, double base, int C) {
+  auto inv = [&](int q) { return 1.0 / pow(base, (double)(2 * q) / (double)C); };
+  if (mode == CSSM_ROPE_TEMPORAL) return axis == 0 ? inv(i) : 0.0;
+  if (mode == CSSM_ROPE_SPATIAL_ONLY) {
+    if (axis == 1) { const int q = 2 * i; return q < n ? inv(q) : 0.0; }
+    if (axis == 2) { const int q = 2 * i + 1; return q < n ? inv(q) : 0.0; }
+    return 0.0;
+  }
+  if (mode == CSSM_ROPE_SPATIOTEMPORAL) {
+    const int nt = n / 3;
+    if (axis == 0) return i < nt ? inv(i) : 0.0;
+    if (axis == 1) { const int q = nt + 2 * i; return q < n ? inv(q) : 0.0; }
+    const int q = nt + 1 + 2 * i; return q < n ? inv(q) : 0.0;
+  }
+  if (mode == CSSM_ROPE_MROPE) {
+    const int nt = n / 3;
+    if (i < 3 * nt) {
+      const int r = i % 3, q = i / 3;
+      if (r != axis) return 0.0;
+      return inv(axis * nt + q);
+    }
+    // left-over width frequencies
+    return axis == 2 ? inv(2 * nt + nt + (i - 3 * nt)) : 0.0;
+  }
+  return 0.0;
+}
+
+__global__ void rope_table_kernel(float2* tt, float2* th, float2* tw, int T, int H, int W, int C,
+                                  int mode, float base) {
+  const int n = C / 2;
+  const int total = (T + H + W) * n;
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= total) return;
+  int pos = o / n, i = o % n, axis = 0;
+  float2* dst = tt;
+  if (pos >= T + H) { axis = 2; pos -= T + H; dst = tw; }
+  else if (pos >= T) { axis = 1; pos -= T; dst = th; }
+  const double ang = (double)pos * rope_freq(axis, i, n, mode, (double)base, C);
+  dst[pos * n + i] = make_float2((float)cos(ang), (float)sin(ang));
+}
+
+int launch_rope_tables(float2* tt, float2* th, float2* tw, int T, int H, int W, int C, int mode,
+                       float base, cudaStream_t st) {
+  const int total = (T + H + W) * (C / 2);
+  rope_table_kernel<<<(total + 127) / 128, 128, 0, st>>>(tt, th, tw, T, H, W, C, mode, base);
+  return check_launch();
+}
+
+// interleaved (sin, cos) temporal code added to the GDN gate context (cssm.py:353-383)
+__global__ void tcode_kernel(float* out, int T, int C, float base) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= T * C) return;
+  const int t = o / C, ch = o % C, i = ch >> 1;
+  const double f = 1.0 / pow((double)base, (double)(2 * i) / (double)C);
+  const double ang = (double)t * f;
+  out[o] = (float)((ch & 1) ? cos(ang) : sin(ang));
+}
+
+int launch_tcode(float* out, int T, int C, float base, cudaStream_t st) {
+  tcode_kernel<<<(T * C + 127) / 128, 128, 0, st>>>(out, T, C, base);
+  return check_launch();
+}
+
+// ------------------------------------------------------------- plane stencil ----
+// One CTA per (b, channel) walks t = 0..T-1 over planes of a planar tensor, in place:
+//   s_t  = dwconv_kxk(raw_t) + b_sp                (if ksp > 0, zero 'SAME' padding)
+//   o_t  = b_t + sum_j w_t[j] * s_{t-(kt-1)+j}     (if kt > 0; frames before 0 are zero)
+//   o_t  = silu(o_t) (if act); o_t *= post[b,t,pixel] (if post)
+// and writes sum over the plane of o_t to sums[(b*T+t)*C + c] (if sums).
+constexpr int ST_THREADS = 256;
+
+
+// KSP / KT >= 0 fix the tap counts at compile time (taps stay in registers); -1 = run time.
+template <int KSP, int KT>
+__global__ void __launch_bounds__(ST_THREADS) plane_stencil_kernel(const StencilArgs s) {
+  extern __shared__ __align__(16) float sm[];
+  const int HW = s.H * s.W;
+  float* raw = sm;                       // [HW]
+  float* hist = sm + HW;                 // [(kt-1)][HW] ring of earlier s planes
+  __shared__ float red[ST_THREADS / 32];
+  const int tid = threadIdx.x;
+  const int b = blockIdx.x / s.C, c = blockIdx.x % s.C;
+  const int ksp = KSP >= 0 ? KSP : s.ksp;
+  const int kt = KT >= 0 ? KT : s.kt;
+  const int nh = kt > 0 ? kt - 1 : 0;
+
+  float wsp[KSP >= 0 ? (KSP * KSP > 0 ? KSP * KSP : 1) : 49];
+  if (ksp > 0) {
+#pragma unroll
+    for (int i = 0; i < ksp * ksp; ++i) wsp[i] = s.wsp[(size_t)i * s.C + c];
+  }
+  const float bsp = ksp > 0 ? s.bsp[c] : 0.f;
+  float wt[KT >= 0 ? (KT > 0 ? KT : 1) : 8];
+  if (kt > 0) {
+#pragma unroll
+    for (int j = 0; j < kt; ++j) wt[j] = s.wt[(size_t)j * s.C + c];
+  }
+  const float btv = kt > 0 ? s.bt[c] : 0.f;
+  const int lo = (ksp - 1) / 2;
+
+  for (int t = 0; t < s.T; ++t) {
+    const size_t frame = (size_t)(b * s.T + t);
+    float* p = s.buf + (frame * s.planes_per_frame + s.plane0 + c) * HW;
+    __syncthreads();
+    for (int i = tid; i < HW; i += ST_THREADS) raw[i] = p[i];
+    __syncthreads();
+    float lsum = 0.f;
+    for (int i = tid; i < HW; i += ST_THREADS) {
+      float v;
+      if (ksp > 0) {
+        const int h = i / s.W, w = i % s.W;
+        v = bsp;
+#pragma unroll
+        for (int di = 0; di < ksp; ++di) {
+          const int hh = h + di - lo;
+          if (hh < 0 || hh >= s.H) continue;
+#pragma unroll
+          for (int dj = 0; dj < ksp; ++dj) {
+            const int ww = w + dj - lo;
+            if (ww < 0 || ww >= s.W) continue;
+            v = fmaf(wsp[di * ksp + dj], raw[hh * s.W + ww], v);
+          }
+        }
+      } else {
+        v = raw[i];
+      }
+      float o = v;
+      if (kt > 0) {
+        o = btv + wt[kt - 1] * v;
+        // tap j reads s_{t-(kt-1)+j}; ring slot of frame f is f % nh
+#pragma unroll
+        for (int j = 0; j < kt - 1; ++j) {
+          const int f = t - (kt - 1) + j;
+          if (f >= 0) o = fmaf(wt[j], hist[(f % nh) * HW + i], o);
+        }
+      }
+      // each thread owns pixel i in every pass, so the ring can be updated in place:
+      // slot t % nh holds s_{t-nh}, which tap 0 has just consumed
+      if (nh > 0) hist[(t % nh) * HW + i] = v;
+      if (s.act) o = silu_f(o);
+      if (s.post) o *= s.post[frame * HW + i];
+      p[i] = o;
+      lsum += o;
+    }
+    if (s.sums) {
+      for (int off = 16; off > 0; off >>= 1) lsum += __shfl_down_sync(0xffffffffu, lsum, off);
+      if ((tid & 31) == 0) red[tid >> 5] = lsum;
+      __syncthreads();
+      if (tid == 0) {
+        float tot = 0.f;
+        for (int i = 0; i < ST_THREADS / 32; ++i) tot += red[i];
+        s.sums[frame * s.C + c] = tot;
+      }
+    }
+  }
+}
+
+int launch_plane_stencil(const StencilArgs& s, cudaStream_t st) {
+  if (s.ksp > 7 || s.kt > 8) return CSSM_ERR_UNSUPPORTED;
+  const int nh = s.kt > 0 ? s.kt - 1 : 0;
+  const size_t smem = (size_t)(1 + nh) * s.H * s.W * sizeof(float);
+  if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
+  auto go = [&](auto kern) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+    kern<<<s.B * s.C, ST_THREADS, smem, st>>>(s);
+    return check_launch();
+  };
+  if (s.ksp == 3 && s.kt == 4) return go(plane_stencil_kernel<3, 4>);
+  if (s.ksp == 0 && s.kt == 4) return go(plane_stencil_kernel<0, 4>);
+  if (s.ksp == 3 && s.kt == 0) return go(plane_stencil_kernel<3, 0>);
+  if (s.ksp == 0 && s.kt == 0) return go(plane_stencil_kernel<0, 0>);
+  return go(plane_stencil_kernel<-1, -1>);
+}
+
+// ----------------------------------------------------------- gated gate maps ----
+// One CTA per (b,t).  ctx = ctx_sum / (H*W).  Writes, per bin, the float4
+// {exp(-D), (D+1e-8)*Bg, Cg/(H*W), 1e-7*(D+1e-8)} at bin_index(path, kh, kw).
+
+__device__ __forceinline__ float gate_act(float x, int act) {
+  if (act == CSSM_ACT_SIGMOID2) return 2.0f / (1.0f + expf(-x));
+  if (act == CSSM_ACT_EXP_CLIP) return expf(fminf(fmaxf(x, -4.f), 2.f));
+  return x > 20.f ? x : log1pf(expf(x));
+}
+
+__global__ void __launch_bounds__(256) gated_gates_kernel(const GatedGateArgs g) {
+  extern __shared__ float sh[];
+  const int Wf = g.W / 2 + 1, NB = g.H * Wf;
+  float* ctx = sh;                 // [C]
+  float* vec = sh + g.C;           // factored: 3 x (H + Wf)
+  const int bt = blockIdx.x, tid = threadIdx.x;
+  const float inv = 1.0f / (float)(g.H * g.W);
+  for (int i = tid; i < g.C; i += blockDim.x) ctx[i] = g.ctx_sum[(size_t)bt * g.C + i] * inv;
+  __syncthreads();
+  if (g.gate_type == CSSM_GATE_FACTORED) {
+    const int per = g.H + Wf;
+    for (int o = tid; o < 3 * per; o += blockDim.x) {
+      const int gi = o / per, r = o % per;
+      const bool isw = r >= g.H;
+      const int col = isw ? r - g.H : r, ncol = isw ? Wf : g.H;
+      const float* kk = g.gk[2 * gi + (isw ? 1 : 0)];
+      float acc = g.gb[2 * gi + (isw ? 1 : 0)][col];
+      for (int c = 0; c < g.C; ++c) acc = fmaf(ctx[c], kk[(size_t)c * ncol + col], acc);
+      vec[o] = acc;
+    }
+    __syncthreads();
+  }
+  for (int bin = tid; bin < NB; bin += blockDim.x) {
+    const int kh = bin / Wf, kw = bin % Wf;
+    float r[3];
+    if (g.gate_type == CSSM_GATE_FACTORED) {
+      const int per = g.H + Wf;
+#pragma unroll
+      for (int gi = 0; gi < 3; ++gi) r[gi] = vec[gi * per + kh] * vec[gi * per + g.H + kw];
+    } else {
+#pragma unroll
+      for (int gi = 0; gi < 3; ++gi) {
+        float acc = g.gb[gi][bin];
+        const float* kk = g.gk[gi];
+        for (int c = 0; c < g.C; ++c) acc = fmaf(ctx[c], kk[(size_t)c * NB + bin], acc);
+        r[gi] = acc;
+      }
+    }
+    const float D = gate_act(r[0], g.act);
+    float4 o;
+    o.x = expf(-D);
+    o.y = (D + 1e-8f) * r[1];
+    o.z = r[2] * inv;
+    o.w = 1e-7f * (D + 1e-8f);
+    g.maps[(size_t)bt * NB + bin_index(g.path, kh, kw, g.H, Wf)] = o;
+  }
+}
+
+int launch_gated_gates(const GatedGateArgs& g, cudaStream_t st) {
+  const int Wf = g.W / 2 + 1;
+  const size_t smem = (size_t)(g.C + 3 * (g.H + Wf)) * sizeof(float);
+  gated_gates_kernel<<<g.BT, 256, smem, st>>>(g);
+  return check_launch();
+}
+
+}  // namespace cssm

@@ -1,0 +1,164 @@
+/*
+ * cssm_b200 — C ABI of the B200 (sm_100a) forward pass of CSSM's spectral SSM blocks.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as
+ * void* so the header needs no CUDA include).  Ownership: the caller allocates every
+ * input, output, plan and workspace buffer; the library never allocates, frees or keeps
+ * a pointer after the call returns.  All work is enqueued on the caller's stream; no
+ * call synchronises the device.  Every function returns a cssm_status (0 = ok) and never
+ * throws, aborts or traps.  Activations and weights are float32.
+ *
+ * The reference interface each entry point stands in for is cited by file:line of
+ * drewlinsley/CSSM (src/models/cssm.py unless another file is named).
+ */
+#ifndef CSSM_B200_H_
+#define CSSM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum cssm_status {
+  CSSM_OK = 0,
+  CSSM_ERR_NULL = 1,        /* a required pointer is NULL                               */
+  CSSM_ERR_DIMS = 2,        /* a dimension is zero, negative or inconsistent            */
+  CSSM_ERR_UNSUPPORTED = 3, /* a field combination this build has no kernel for         */
+  CSSM_ERR_ALIGN = 4,       /* a pointer is not 16-byte aligned                         */
+  CSSM_ERR_WORKSPACE = 5,   /* plan or workspace buffer too small                       */
+  CSSM_ERR_CUDA = 6,        /* a CUDA runtime call or launch failed (see cssm_last_cuda_error) */
+  CSSM_ERR_SIZE_LIMIT = 7   /* size beyond a documented fixed maximum                   */
+} cssm_status;
+
+typedef enum cssm_rope_mode {      /* apply_rope modes, cssm.py:94-262 */
+  CSSM_ROPE_NONE = 0,
+  CSSM_ROPE_SPATIOTEMPORAL = 1,
+  CSSM_ROPE_TEMPORAL = 2,
+  CSSM_ROPE_SPATIAL_ONLY = 3,
+  CSSM_ROPE_MROPE = 4
+} cssm_rope_mode;
+
+typedef enum cssm_gate_type { CSSM_GATE_DENSE = 0, CSSM_GATE_FACTORED = 1 } cssm_gate_type;
+
+typedef enum cssm_gate_act {       /* GatedCSSM._compute_gate, cssm.py:432-441 */
+  CSSM_ACT_SOFTPLUS = 0,
+  CSSM_ACT_SIGMOID2 = 1,
+  CSSM_ACT_EXP_CLIP = 2
+} cssm_gate_act;
+
+const char* cssm_strerror(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* cssm_last_cuda_error(void);
+/* "cssm_b200 <version> sm_100a" */
+const char* cssm_version(void);
+
+/* ------------------------------------------------------------------ GatedCSSM --- */
+/* Fields of the Flax dataclass GatedCSSM (cssm.py:416-430) that the depthwise path
+ * reads, plus the call-time shape of x (cssm.py:455-456). */
+typedef struct cssm_gated_desc {
+  int32_t B, T, H, W, C;
+  int32_t kernel_size;              /* spectral kernel is (C, ks, ks)                   */
+  int32_t rope_mode;                /* cssm_rope_mode                                   */
+  float   rope_base;
+  float   spectral_rho;
+  int32_t gate_activation;          /* cssm_gate_act                                    */
+  int32_t short_conv_size;          /* temporal causal taps, 0 = layer absent           */
+  int32_t short_conv_spatial_size;  /* spatial depthwise k, 0 = layer absent            */
+  int32_t gate_type;                /* cssm_gate_type                                   */
+} cssm_gated_desc;
+
+/* Parameter tree of GatedCSSM in Flax layout (cssm.py:481-584): Dense kernels are
+ * (in, out) row-major, conv kernels HWIO.  gate_* order: delta_proj, B_proj, C_proj;
+ * for factored gates index 2*g is "<name>_h" (C,H) and 2*g+1 is "<name>_w" (C,W/2+1),
+ * for dense gates index g is "<name>" (C, H*(W/2+1)) and entries 3..5 are ignored. */
+typedef struct cssm_gated_weights {
+  const float* in_proj_kernel;   /* (C, 2C)   */
+  const float* in_proj_bias;     /* (2C)      */
+  const float* conv_sp_kernel;   /* (k,k,1,C) or NULL when short_conv_spatial_size==0 */
+  const float* conv_sp_bias;     /* (C)       */
+  const float* conv_t_kernel;    /* (k,1,C)   or NULL when short_conv_size==0         */
+  const float* conv_t_bias;      /* (C)       */
+  const float* kernel;           /* (C,ks,ks) */
+  const float* gate_kernel[6];
+  const float* gate_bias[6];
+  const float* out_proj_kernel;  /* (C, C)    */
+  const float* out_proj_bias;    /* (C)       */
+} cssm_gated_weights;
+
+/* Bytes of the weight-derived plan (squashed kernel spectrum K_hat, RoPE tables) and of
+ * the per-call workspace.  Both return 0 for a descriptor the library rejects. */
+size_t cssm_gated_plan_bytes(const cssm_gated_desc* d);
+size_t cssm_gated_workspace_bytes(const cssm_gated_desc* d);
+
+/* Weight-only precompute: centred pad of `kernel` to (H,W), rfft2,
+ * K*rho/(1+|K|), GOOM magnitude floor; RoPE cos/sin tables.
+ * Replaces cssm.py:505-529 (+ :29-46, goom.py:161-173) and the angle tables of
+ * apply_rope (cssm.py:121-248).  Call again whenever `kernel` changes. */
+int cssm_gated_plan_init(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                         void* plan, size_t plan_bytes, void* stream);
+
+/* Whole block: y = GatedCSSM(x), x and y (B,T,H,W,C) float32 on the device.
+ * Replaces GatedCSSM.__call__ -> _forward_depthwise, cssm.py:443-474, 476-585. */
+int cssm_gated_forward(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                       const void* plan, const float* x, float* y,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same block with x and y in HOST memory (pinned memory gives the overlap): the batch is
+ * cut into chunks whose host->device copy, kernels and device->host copy overlap on
+ * three streams ordered by events.  `workspace` must hold
+ * cssm_gated_host_workspace_bytes(d, chunk_b) bytes of DEVICE memory.  Synchronises the
+ * internal streams with `stream` before returning control (the call itself is still
+ * asynchronous with respect to the host only until its final event wait). */
+size_t cssm_gated_host_workspace_bytes(const cssm_gated_desc* d, int32_t chunk_b);
+int cssm_gated_forward_host(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                            const void* plan, const float* x_host, float* y_host,
+                            int32_t chunk_b, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* ---- stages of the gated block, exposed for tests, profiling and partial drop-in ---- */
+
+/* RoPE + in_proj: xz[(bt*2C + n)*H*W + hw] = sum_c rope(x)[bt,hw,c] * Wk[c,n] + b[n].
+ * Planes 0..C-1 of each frame are x_main, C..2C-1 are z.  cssm.py:462-463, 480-484. */
+int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                       const void* plan, const float* x, float* xz_planar, void* stream);
+
+/* Spatial depthwise conv + causal temporal conv + SiLU on the x_main planes, in place,
+ * and the per-plane sums that give ctx.  cssm.py:487-502, 536.
+ * ctx_sum is (B*T, C); divide by H*W for the mean. */
+int cssm_gated_short_conv(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                          float* xz_planar, float* ctx_sum, void* stream);
+
+/* Gate maps from ctx: per (b,t) and frequency bin the four floats
+ * {exp(-Delta), (Delta+1e-8)*B, C/(H*W), 1e-7*(Delta+1e-8)}.  cssm.py:538-567.
+ * The bin order inside a (b,t) map is internal to the library. */
+int cssm_gated_gates(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                     const float* ctx_sum, float* gate_maps, void* stream);
+
+/* Fused spectral kernel: for each (b,c): for t: rfft2(x_main[b,t,c]),
+ * h = K_hat*exp(-Delta)*h + (Delta+1e-8)*floor(B*X), y = irfft2(C*h) * silu(z[b,t,c]);
+ * y overwrites the x_main plane.  The state h never leaves the SM.
+ * Replaces cssm.py:532-533, 558-581 (rfft2, to_goom, associative_scan of
+ * math.py:24-54, from_goom, irfft2, SiLU gate) and the existing scan seam
+ * pallas_scalar_scan(A, X, h0), src/models/pallas_scan.py:341-401. */
+int cssm_gated_spectral(const cssm_gated_desc* d, const void* plan, const float* gate_maps,
+                        float* xz_planar, void* stream);
+
+/* out_proj from the planar y planes to channels-last y.  cssm.py:584-585. */
+int cssm_gated_out_proj(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                        const float* xz_planar, float* y, void* stream);
+
+/* Offsets (bytes) of the pieces of the gated workspace, for callers that drive stages. */
+typedef struct cssm_gated_ws_layout {
+  size_t xz_planar;   /* (B*T, 2C, H, W) float                */
+  size_t ctx_sum;     /* (B*T, C) float                       */
+  size_t gate_maps;   /* (B*T, H*(W/2+1), 4) float            */
+  size_t total;
+} cssm_gated_ws_layout;
+int cssm_gated_workspace_layout(const cssm_gated_desc* d, cssm_gated_ws_layout* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CSSM_B200_H_ */

@@ -1,0 +1,116 @@
+"""GPU parity of the gated block (through the C ABI) against the NumPy oracle.
+Tolerance: rel-L2 <= 1e-4 in fp32 (the figure the project's target states)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cssm_oracle as orc
+from cssm_b200 import GatedCSSM
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+
+def _run(B, T, H, W, C, ks, gate_type, rope, ksp, kt, seed=0, bias=0.1, act="softplus"):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((B, T, H, W, C)).astype(np.float32)
+    p = orc.init_gated_params(seed + 1, C, H, W, kernel_size=ks, gate_type=gate_type,
+                              short_conv_size=kt, short_conv_spatial_size=ksp, bias_scale=bias)
+    ref, inter = orc.gated_forward(p, x, kernel_size=ks, rope_mode=rope, gate_type=gate_type,
+                                   short_conv_size=kt, short_conv_spatial_size=ksp,
+                                   gate_activation_kind=act, return_intermediates=True)
+    mod = GatedCSSM(channels=C, kernel_size=ks, rope_mode=rope, gate_type=gate_type,
+                    short_conv_size=kt, short_conv_spatial_size=ksp, gate_activation=act)
+    bound = mod.bind({"params": p})
+    xd = torch.from_numpy(x).cuda()
+    return bound, xd, ref, inter
+
+
+CASES = [
+    # B, T, H, W, C, ks, gate, rope, ksp, kt
+    (2, 3, 64, 64, 8, 11, "factored", "spatiotemporal", 3, 4),
+    (1, 8, 64, 64, 4, 11, "dense", "none", 3, 4),
+    (2, 1, 64, 64, 8, 1, "factored", "mrope", 0, 0),
+    (2, 4, 8, 8, 8, 5, "dense", "spatiotemporal", 3, 4),
+    (3, 2, 7, 7, 12, 1, "factored", "none", 0, 4),
+    (1, 3, 14, 14, 16, 3, "factored", "spatial_only", 3, 0),
+    (2, 2, 32, 32, 8, 11, "dense", "temporal", 3, 4),
+    (1, 2, 6, 10, 4, 3, "factored", "spatiotemporal", 3, 4),
+    (1, 2, 4, 4, 4, 11, "dense", "none", 3, 2),      # kernel larger than the plane: crop
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c)))
+def test_block_parity(case):
+    bound, xd, ref, _ = _run(*case)
+    y = bound(xd).cpu().numpy()
+    assert np.isfinite(y).all()
+    assert orc.rel_l2(y, ref) <= TOL
+
+
+@pytest.mark.parametrize("case", CASES[:4], ids=lambda c: "x".join(map(str, c)))
+def test_stage_parity(case):
+    B, T, H, W, C = case[:5]
+    bound, xd, ref, inter = _run(*case)
+    st = bound.stages(xd, upto="short_conv")
+    xz = st["xz"].cpu().numpy().reshape(B, T, 2 * C, H, W)
+    x_main = xz[:, :, :C].transpose(0, 1, 3, 4, 2)
+    z = xz[:, :, C:].transpose(0, 1, 3, 4, 2)
+    assert orc.rel_l2(x_main, inter["x_main"]) <= 1e-5
+    assert orc.rel_l2(z, inter["z"]) <= 1e-5
+    ctx = st["ctx_sum"].cpu().numpy().reshape(B, T, C) / (H * W)
+    assert orc.rel_l2(ctx, inter["ctx"]) <= 1e-5
+    st = bound.stages(xd, upto="spectral")
+    xz = st["xz"].cpu().numpy().reshape(B, T, 2 * C, H, W)
+    ssm_gated = xz[:, :, :C].transpose(0, 1, 3, 4, 2)
+    want = inter["ssm"] * orc.silu(inter["z"])
+    assert orc.rel_l2(ssm_gated, want) <= TOL
+
+
+@pytest.mark.parametrize("act", ["sigmoid", "exp"])
+def test_gate_activations(act):
+    bound, xd, ref, _ = _run(1, 3, 8, 8, 8, 3, "dense", "none", 3, 4, act=act)
+    assert orc.rel_l2(bound(xd).cpu().numpy(), ref) <= TOL
+
+
+def test_zero_input_hits_goom_floor():
+    """x = 0 with zero biases: B*X_hat is exactly 0, so the reference's 1e-7 magnitude
+    floor is the only thing that drives the state; the kernel must reproduce it."""
+    B, T, H, W, C = 1, 3, 64, 64, 4
+    p = orc.init_gated_params(3, C, H, W, kernel_size=5, gate_type="dense", bias_scale=0.0)
+    # non-zero delta / C biases so the floored state is visible in the output
+    for n in ("delta_proj", "C_proj"):
+        p[n]["bias"] = np.full_like(p[n]["bias"], 0.5)
+    p["in_proj"]["bias"][C:] = 1.0          # z != 0
+    x = np.zeros((B, T, H, W, C), np.float32)
+    ref = orc.gated_forward(p, x, kernel_size=5, gate_type="dense")
+    mod = GatedCSSM(channels=C, kernel_size=5, gate_type="dense")
+    y = mod.apply({"params": p}, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.abs(ref).max() > 0
+    assert orc.rel_l2(y, ref) <= 1e-3
+
+
+def test_deterministic_and_radix_matches_generic_structure():
+    """Two runs are bitwise equal (no atomics on outputs)."""
+    bound, xd, ref, _ = _run(2, 3, 64, 64, 8, 11, "factored", "spatiotemporal", 3, 4)
+    y1 = bound(xd).clone()
+    y2 = bound(xd).clone()
+    assert torch.equal(y1, y2)
+
+
+def test_forward_host_matches_device():
+    import ctypes as C
+    from cssm_b200._lib import check
+    bound, xd, ref, _ = _run(5, 2, 64, 64, 4, 3, "factored", "spatiotemporal", 3, 4)
+    y_dev = bound(xd).cpu()
+    xh = xd.cpu().pin_memory()
+    yh = torch.empty_like(xh).pin_memory()
+    d = bound.desc(tuple(xh.shape))
+    pl = bound.plan(d)
+    n = bound.L.cssm_gated_host_workspace_bytes(C.byref(d), 2)
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    check(bound.L.cssm_gated_forward_host(C.byref(d), C.byref(bound.w), pl.data_ptr(),
+                                          xh.data_ptr(), yh.data_ptr(), 2, ws.data_ptr(), n,
+                                          torch.cuda.current_stream().cuda_stream), "forward_host")
+    torch.cuda.synchronize()
+    assert torch.equal(yh, y_dev)
