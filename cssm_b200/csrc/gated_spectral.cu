@@ -27,6 +27,10 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
   const int sub = lane & 3, a = lane >> 2;
   const int grp = warp * 4 + sub;            // row pair (row passes) / column (column passes)
   const bool row_on = warp < 8;
+  // Column passes run on whole warps (the exchange inside the FFT synchronises the warp):
+  // the three lanes groups of warp 8 beyond column 32 compute on in-bounds scratch and
+  // only their global loads and shared-memory results are suppressed.
+  const bool col_warp = warp < 9;
   const bool col_on = grp <= 32;
   cf* exg = EX + grp * EX_GROUP_STRIDE;
 
@@ -66,7 +70,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     __syncthreads();
 
     // ---- forward columns, recurrence, inverse columns ----
-    if (col_on) {
+    if (col_warp) {
       const int par = a & 1, ph = a >> 1;
       const int kneg = (64 - grp) & 63;
 #pragma unroll
@@ -80,7 +84,8 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       const float4* gp = gates + frame * (64 * 33) + (grp << 3) + a;
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        const float4 g = gp[q * (33 * 8)];   // {exp(-D), (D+1e-8)B, C/(HW), 1e-7(D+1e-8)}
+        // {exp(-D), (D+1e-8)B, C/(HW), 1e-7(D+1e-8)}
+        const float4 g = col_on ? gp[q * (33 * 8)] : make_float4(0.f, 0.f, 0.f, 0.f);
         cf A = mk(kh[q].x * g.x, kh[q].y * g.x);
         cf U = mk(g.y * v[q].x, g.y * v[q].y);
         if (U.x * U.x + U.y * U.y < g.w * g.w) U = mk(g.w, 0.f);
@@ -91,7 +96,8 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       }
       fft64_lane8<true>(v, tw, exg, a);
 #pragma unroll
-      for (int n1 = 0; n1 < 8; ++n1) GB[(a + 8 * n1) * R64_GB_STRIDE + grp] = v[n1];
+      for (int n1 = 0; n1 < 8; ++n1)
+        if (col_on) GB[(a + 8 * n1) * R64_GB_STRIDE + grp] = v[n1];
     }
     __syncthreads();
 
