@@ -114,3 +114,17 @@ def test_forward_host_matches_device():
                                           torch.cuda.current_stream().cuda_stream), "forward_host")
     torch.cuda.synchronize()
     assert torch.equal(yh, y_dev)
+
+
+def test_golden_fixtures_on_gpu():
+    """The committed golden vectors (tests/golden/*.npz, written by make_golden.py)."""
+    import os
+    from tests.golden import make_golden as mg
+    gdir = os.path.dirname(mg.__file__)
+    for fname, case in (("gated_small.npz", mg.gated_case), ("gated_64.npz", mg.gated_case_64)):
+        g = np.load(os.path.join(gdir, fname))
+        x, p, kw = case()
+        mod = GatedCSSM(channels=x.shape[-1], kernel_size=kw["kernel_size"],
+                        rope_mode=kw["rope_mode"], gate_type=kw["gate_type"])
+        y = mod.apply({"params": p}, torch.from_numpy(g["x"]).cuda()).cpu().numpy()
+        assert orc.rel_l2(y, g["y"]) <= TOL

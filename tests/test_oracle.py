@@ -1,0 +1,183 @@
+"""CPU tests of the oracle: its two tiers against each other, the reference's scan-operator
+test distributions against a sequential ground truth, structural invariants, the golden
+vectors, and the timed torch-CPU restatement against the NumPy oracle."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import cssm_oracle as orc
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _scan_inputs(seed, shape, mag_lo=0.1):
+    """|A| in [mag_lo, 0.95], uniform phase, U ~ N(0, .5^2) + i N(0, .5^2): the distributions
+    of the reference's scan tests (tests/test_complex32.py:81-93, tests/test_ssd.py:77-87)."""
+    rng = np.random.default_rng(seed)
+    A = rng.uniform(mag_lo, 0.95, shape) * np.exp(1j * rng.uniform(-np.pi, np.pi, shape))
+    U = 0.5 * rng.standard_normal(shape) + 0.5j * rng.standard_normal(shape)
+    return A.astype(np.complex64), U.astype(np.complex64)
+
+
+def _sequential(A, U):
+    """benchmarks/bench_scan_modes.py:194-203."""
+    h = np.zeros_like(A[:, 0], dtype=np.complex128)
+    out = []
+    for t in range(A.shape[1]):
+        h = A[:, t].astype(np.complex128) * h + U[:, t]
+        out.append(h)
+    return np.stack(out, axis=1)
+
+
+@pytest.mark.parametrize("T", [8, 16, 32])
+def test_goom_scalar_scan_matches_sequential(T):
+    A, U = _scan_inputs(T, (2, T, 4, 8, 5))
+    got = orc.goom_scalar_scan(A, U)
+    ref = _sequential(A, U)
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 5e-6
+
+
+@pytest.mark.parametrize("d", [2, 3, 4])
+def test_goom_matrix_scan_matches_sequential(d):
+    rng = np.random.default_rng(d)
+    shape = (2, 8, 3, 4, 3)
+    M = (0.4 * (rng.standard_normal(shape + (d, d)) + 1j * rng.standard_normal(shape + (d, d)))
+         ).astype(np.complex64)
+    U = (0.5 * (rng.standard_normal(shape + (d,)) + 1j * rng.standard_normal(shape + (d,)))
+         ).astype(np.complex64)
+    got = orc.goom_matrix_scan(M, U)
+    u = np.zeros(shape[:1] + shape[2:] + (d,), np.complex128)
+    ref = []
+    for t in range(shape[1]):
+        u = np.einsum("...ij,...j->...i", M[:, t].astype(np.complex128), u) + U[:, t]
+        ref.append(u)
+    ref = np.stack(ref, axis=1)
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 2e-5
+
+
+def test_goom_floor_semantics():
+    z = np.array([0.0, 5e-8, -5e-8j, 2e-7, -1.0], dtype=np.complex128)
+    f = orc.goom_floor(z)
+    assert f[0] == 1e-7 and f[1] == 1e-7 and f[2] == 1e-7
+    assert f[3] == 2e-7 and f[4] == -1.0
+
+
+GATED_CASES = [
+    dict(B=2, T=4, H=8, W=8, C=8, ks=5, gt="dense", rope="spatiotemporal"),
+    dict(B=1, T=8, H=16, W=16, C=4, ks=11, gt="factored", rope="mrope"),
+    dict(B=2, T=1, H=7, W=7, C=12, ks=1, gt="factored", rope="none"),
+    dict(B=1, T=32, H=8, W=8, C=4, ks=3, gt="dense", rope="temporal"),
+]
+
+
+@pytest.mark.parametrize("c", GATED_CASES, ids=lambda c: f"{c['H']}x{c['W']}T{c['T']}{c['gt']}")
+def test_gated_tiers_agree(c):
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((c["B"], c["T"], c["H"], c["W"], c["C"])).astype(np.float32)
+    p = orc.init_gated_params(1, c["C"], c["H"], c["W"], kernel_size=c["ks"], gate_type=c["gt"],
+                              bias_scale=0.1)
+    kw = dict(kernel_size=c["ks"], rope_mode=c["rope"], gate_type=c["gt"])
+    exact = orc.gated_forward(p, x, **kw)
+    literal = orc.gated_forward(p, x, dtype=np.float32, scan="goom", **kw)
+    assert orc.rel_l2(literal, exact) < 5e-6
+
+
+@pytest.mark.parametrize("gt", ["factored", "dense"])
+def test_gdn_tiers_agree(gt):
+    rng = np.random.default_rng(0)
+    B, T, H, W, C = 2, 4, 8, 8, 16
+    x = rng.standard_normal((B, T, H, W, C)).astype(np.float32)
+    p = orc.init_gdn_params(1, C, H, W, kernel_size=5, gate_type=gt, qkv_conv_size=5,
+                            bias_scale=0.1, perturb_rms=True)
+    kw = dict(kernel_size=5, rope_mode="mrope", gate_type=gt, qkv_conv_size=5)
+    exact = orc.gdn_forward(p, x, **kw)
+    literal = orc.gdn_forward(p, x, dtype=np.float32, scan="goom", **kw)
+    assert orc.rel_l2(literal, exact) < 2e-5
+
+
+def test_t1_output_independent_of_kernel():
+    """h_1 = U_1: at T=1 the spectral kernel has no effect (cssm.py:570-572)."""
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 1, 8, 8, 8)).astype(np.float32)
+    p = orc.init_gated_params(1, 8, 8, 8, kernel_size=3)
+    y1 = orc.gated_forward(p, x, kernel_size=3)
+    p2 = dict(p)
+    p2["kernel"] = p["kernel"] * 7.0 + 1.0
+    y2 = orc.gated_forward(p2, x, kernel_size=3)
+    assert orc.rel_l2(y1, y2) < 1e-12
+
+
+def test_kernel_size_one_gives_flat_spectrum():
+    """ks=1 is a single centred tap: |K_hat| is constant over bins (linear phase only)."""
+    k = np.random.default_rng(0).standard_normal((4, 1, 1)).astype(np.float32)
+    K = orc.spectral_kernel(k, 16, 16)
+    mag = np.abs(K)
+    assert np.allclose(mag, mag[:, :1, :1], rtol=1e-12)
+    assert (mag < 0.999).all()
+
+
+def test_circular_shift_equivariance_without_convs_and_rope():
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((1, 3, 8, 8, 4)).astype(np.float32)
+    p = orc.init_gated_params(1, 4, 8, 8, kernel_size=3, short_conv_size=0,
+                              short_conv_spatial_size=0, bias_scale=0.1)
+    kw = dict(kernel_size=3, short_conv_size=0, short_conv_spatial_size=0)
+    # the gates are indexed by frequency, so a spatial shift of the input shifts the output
+    y = orc.gated_forward(p, x, **kw)
+    ys = orc.gated_forward(p, np.roll(x, (2, 3), axis=(2, 3)), **kw)
+    assert orc.rel_l2(ys, np.roll(y, (2, 3), axis=(2, 3))) < 1e-10
+
+
+def test_irfft2_ignores_imag_of_dc_and_nyquist_columns():
+    rng = np.random.default_rng(4)
+    Y = rng.standard_normal((8, 5)) + 1j * rng.standard_normal((8, 5))
+    a = np.fft.irfft2(Y, s=(8, 8))
+    col = np.fft.ifft(Y, axis=0)
+    col[:, 0] = col[:, 0].real
+    col[:, 4] = col[:, 4].real
+    b = np.fft.irfft(col, n=8, axis=1)
+    assert np.abs(a - b).max() < 1e-14
+
+
+def test_rope_modes_pair_rotation_is_orthogonal():
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((1, 3, 4, 5, 16))
+    for mode in ("spatiotemporal", "temporal", "spatial_only", "mrope"):
+        y = orc.apply_rope(x, mode)
+        assert np.allclose((x ** 2).sum(-1), (y ** 2).sum(-1))
+        assert np.allclose(y[:, 0, 0, 0], x[:, 0, 0, 0])      # angle 0 at the origin
+    ft, fh, fw = orc.rope_axis_freqs(64, "spatiotemporal")
+    assert (ft[:10] > 0).all() and (ft[10:] == 0).all()
+    assert (fh[:11] > 0).all() and (fh[11:] == 0).all() and (fw[:11] > 0).all()
+    ft, fh, fw = orc.rope_axis_freqs(64, "mrope")
+    assert ((ft > 0).astype(int) + (fh > 0) + (fw > 0) == 1).all()   # one axis per pair
+
+
+def test_golden_vectors():
+    path = os.path.join(GOLDEN, "gated_small.npz")
+    g = np.load(path)
+    from tests.golden.make_golden import gated_case
+    x, p, kw = gated_case()
+    assert np.array_equal(x, g["x"])
+    y = orc.gated_forward(p, x, **kw)
+    assert orc.rel_l2(y, g["y"]) < 1e-12
+    g2 = np.load(os.path.join(GOLDEN, "gdn_small.npz"))
+    from tests.golden.make_golden import gdn_case
+    x, p, kw = gdn_case()
+    y = orc.gdn_forward(p, x, **kw)
+    assert orc.rel_l2(y, g2["y"]) < 1e-12
+
+
+def test_torch_cpu_restatement_matches_numpy_oracle():
+    import torch
+    from oracle import cssm_torch_cpu as tc
+    rng = np.random.default_rng(0)
+    B, T, H, W, C = 2, 3, 16, 16, 8
+    x = rng.standard_normal((B, T, H, W, C)).astype(np.float32)
+    for gt, rope in (("factored", "spatiotemporal"), ("dense", "mrope")):
+        p = orc.init_gated_params(1, C, H, W, kernel_size=11, gate_type=gt, bias_scale=0.1)
+        y = orc.gated_forward(p, x, kernel_size=11, rope_mode=rope, gate_type=gt)
+        yt = tc.gated_forward_torch(p, torch.from_numpy(x), kernel_size=11, rope_mode=rope,
+                                    gate_type=gt).numpy()
+        assert orc.rel_l2(yt, y) < 1e-5
