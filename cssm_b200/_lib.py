@@ -81,6 +81,9 @@ SIGNATURES = {
     "cssm_gated_spectral": (C.c_int, [C.POINTER(GatedDesc), _P, _P, _P, _P]),
     "cssm_gated_out_proj": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P]),
     "cssm_gated_workspace_layout": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWsLayout)]),
+    "cssm_static_scratch_bytes": (C.c_size_t, []),
+    "cssm_gated_forward_static": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
+                                            _P, _P]),
 }
 
 _lib = None

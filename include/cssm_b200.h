@@ -158,6 +158,25 @@ typedef struct cssm_gated_ws_layout {
 } cssm_gated_ws_layout;
 int cssm_gated_workspace_layout(const cssm_gated_desc* d, cssm_gated_ws_layout* out);
 
+/* ---- entry point that allocates nothing (no counterpart in the reference) ----
+ * The reference has nothing like this: it is for hosts that may not call cudaMalloc at all
+ * (a plugin running inside another framework's step, whose allocator owns the device memory;
+ * a sandboxed or latency-bound service that is only permitted to launch work).  It is
+ * cssm_gated_forward with the block's scratch memory taken from one fixed array inside the
+ * library image instead of a caller workspace.  The caller still passes plan, x and y.
+ *  - Limit: cssm_gated_workspace_bytes(d) must be <= cssm_static_scratch_bytes() (64 MiB);
+ *    larger problems return CSSM_ERR_SIZE_LIMIT.  Every GPU that loads the library carries
+ *    the 64 MiB array until the process exits.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call before starting any stream capture.
+ *  - All calls on a device share the array: two calls whose kernels overlap on the GPU
+ *    (different streams) race.  Nothing needs clearing between calls: each part of the
+ *    scratch is rewritten before it is read.
+ *  - Calls no cudaMalloc / cudaFree or any allocating routine. */
+size_t cssm_static_scratch_bytes(void);
+int cssm_gated_forward_static(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                              const void* plan, const float* x, float* y, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
