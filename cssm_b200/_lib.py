@@ -81,6 +81,11 @@ SIGNATURES = {
     "cssm_gated_spectral": (C.c_int, [C.POINTER(GatedDesc), _P, _P, _P, _P]),
     "cssm_gated_out_proj": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P]),
     "cssm_gated_workspace_layout": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWsLayout)]),
+    "cssm_gdn_plan_bytes": (C.c_size_t, [C.POINTER(GdnDesc)]),
+    "cssm_gdn_workspace_bytes": (C.c_size_t, [C.POINTER(GdnDesc)]),
+    "cssm_gdn_plan_init": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, C.c_size_t, _P]),
+    "cssm_gdn_forward": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
+                                   C.c_size_t, _P]),
     "cssm_static_scratch_bytes": (C.c_size_t, []),
     "cssm_gated_forward_static": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
                                             _P, _P]),

@@ -1,0 +1,155 @@
+// GDN fused spectral kernel for 64x64 planes, d_k = d_v = 4.  One CTA (288 threads) per
+// (batch, head).  Per step: the 8 q/k planes are transformed and their spectra parked in
+// shared memory in the column lanes' own bin order; the norms are applied in place; then each
+// of the 4 v planes is transformed, its state row updated and read out, and the output plane
+// inverse-transformed over the v plane.
+#include "r64.cuh"
+#include "kernels.cuh"
+#include "gdn_common.cuh"
+
+namespace cssm {
+
+constexpr int G64_SPEC_CF = 8 * 8 * R64_NT;     // [plane 0..7][q 0..7][thread]
+constexpr int G64_SMEM_CF = R64_EX_CF + R64_ZR_CF + R64_GB_CF + G64_SPEC_CF;
+
+__global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  cf* EX = reinterpret_cast<cf*>(smem_raw);
+  cf* ZR = EX + R64_EX_CF;
+  cf* GB = ZR + R64_ZR_CF;
+  cf* SPEC = GB + R64_GB_CF;
+  __shared__ float red[9][8];
+
+  R64Ctx c;
+  r64_init(c, EX, ZR, GB);
+  const int tid = threadIdx.x;
+  constexpr int HW = 4096, NB = 64 * 33, DK = 4;
+  const int nh = a.C / DK;
+  const int b = blockIdx.x / nh, hd = blockIdx.x % nh;
+
+  // state scratch: S[v][i][q][thread]; zero it (a thread only ever touches its own slots)
+  cf* S = a.state + (size_t)blockIdx.x * DK * DK * NB;   // 16 * 2112 = 16 * 8 * 264 slots
+  // lanes of column passes: slot index inside a (v,i) block is q*264 + (grp*8 + a), grp <= 32
+  const int cslot = c.grp * 8 + c.a;
+  if (c.col_on)
+    for (int vi = 0; vi < DK * DK; ++vi)
+#pragma unroll
+      for (int q = 0; q < 8; ++q) S[(size_t)vi * NB + q * 264 + cslot] = mk(0.f, 0.f);
+
+  cf wh[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    wh[q] = c.col_on ? a.what[(size_t)hd * NB + ((q * 33 + c.grp) << 3) + c.a] : mk(0.f, 0.f);
+  const float invHW = 1.0f / (float)HW;
+
+  for (int t = 0; t < a.T; ++t) {
+    const size_t frame = (size_t)(b * a.T + t);
+    float* base = a.qkv + frame * 3 * a.C * HW;
+    float ssq[8];
+    // ---- q planes (p = 0..3) and k planes (p = 4..7) ----
+#pragma unroll 1
+    for (int p = 0; p < 8; ++p) {
+      const float* plane = base + (size_t)((p < 4 ? 0 : a.C) + hd * DK + (p & 3)) * HW;
+      __syncthreads();                       // ZR free (previous column pass finished)
+      r64_row_fwd(c, plane);
+      __syncthreads();
+      float acc = 0.f;
+      if (c.col_warp) {
+        cf v[8];
+        r64_col_fwd(c, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          SPEC[(p * 8 + q) * R64_NT + tid] = v[q];
+          if (c.col_on) acc += v[q].x * v[q].x + v[q].y * v[q].y;
+        }
+      }
+      for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
+      ssq[p] = acc;                          // valid in lane 0 of each warp
+    }
+    if (c.lane == 0)
+#pragma unroll
+      for (int p = 0; p < 8; ++p) red[c.warp][p] = ssq[p];
+    __syncthreads();
+    float nrm[8];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 9; ++w) s += red[w][p];
+      nrm[p] = a.use_l2 ? rsqrtf(s + 1e-6f) : 1.f;
+    }
+    // ---- normalise own bins in place: q_hat = q*nq; k_hat = (k*nk) / sqrt(sum_i |.|^2 + 1e-6)
+    if (c.col_warp) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        cf kv[4];
+        float ks = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          cf z = SPEC[((4 + i) * 8 + q) * R64_NT + tid];
+          kv[i] = mk(z.x * nrm[4 + i], z.y * nrm[4 + i]);
+          ks += kv[i].x * kv[i].x + kv[i].y * kv[i].y;
+          cf qq = SPEC[(i * 8 + q) * R64_NT + tid];
+          SPEC[(i * 8 + q) * R64_NT + tid] = mk(qq.x * nrm[i], qq.y * nrm[i]);
+        }
+        const float kn = rsqrtf(ks + 1e-6f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          SPEC[((4 + i) * 8 + q) * R64_NT + tid] = mk(kv[i].x * kn, kv[i].y * kn);
+      }
+    }
+    const float2* abp = a.ab + frame * NB + (c.grp << 3) + c.a;
+    // ---- v rows: transform, state update, readout, inverse transform over the v plane ----
+#pragma unroll 1
+    for (int vr = 0; vr < DK; ++vr) {
+      float* vplane = base + (size_t)(2 * a.C + hd * DK + vr) * HW;
+      __syncthreads();                       // ZR free; GB reads of the previous row finished
+      r64_row_fwd(c, vplane);
+      __syncthreads();
+      if (c.col_warp) {
+        cf v[8];
+        r64_col_fwd(c, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          cf kk[4], qq[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            qq[i] = SPEC[(i * 8 + q) * R64_NT + tid];
+            kk[i] = SPEC[((4 + i) * 8 + q) * R64_NT + tid];
+          }
+          cf o = mk(0.f, 0.f);
+          if (c.col_on) {
+            const float2 g = abp[q * (33 * 8)];
+            const cf aw = mk(g.x * wh[q].x, g.x * wh[q].y);
+            o = gdn_bin_update_r64(S + (size_t)(vr * DK) * NB + q * 264 + cslot, NB, kk, qq, v[q],
+                                   aw, g.y);
+          }
+          v[q] = mk(o.x * invHW, o.y * invHW);
+        }
+        r64_col_inv(c, v);
+      }
+      __syncthreads();
+      if (c.row_on) {
+        cf v[8];
+        r64_row_inv(c, v);
+        float* y0 = vplane + (2 * c.grp) * 64 + c.a;
+#pragma unroll
+        for (int n1 = 0; n1 < 8; ++n1) {
+          y0[8 * n1] = v[n1].x;
+          y0[64 + 8 * n1] = v[n1].y;
+        }
+      }
+    }
+  }
+}
+
+int launch_gdn_spectral_r64(const GdnSpectralArgs& a, cudaStream_t st) {
+  const size_t smem = (size_t)G64_SMEM_CF * sizeof(cf);
+  cudaError_t e = cudaFuncSetAttribute(gdn_spectral_r64,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  gdn_spectral_r64<<<a.B * (a.C / 4), R64_NT, smem, st>>>(a);
+  return check_launch();
+}
+
+}  // namespace cssm

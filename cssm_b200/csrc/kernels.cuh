@@ -17,7 +17,8 @@ struct StencilArgs {
   const float* wsp; const float* bsp; int ksp;   // (k,k,1,C), (C)
   const float* wt; const float* bt; int kt;      // (k,1,C), (C)
   int act;
-  const float* post;                             // (B*T, H*W) or nullptr
+  const float* post;                             // per-pixel factor or nullptr:
+  int post_stride, post_off;                     //   post[(frame*H*W + px)*post_stride + post_off]
   float* sums;                                   // (B*T, C) or nullptr
 };
 int launch_plane_stencil(const StencilArgs& s, cudaStream_t st);
@@ -32,5 +33,35 @@ int launch_gated_gates(const GatedGateArgs& g, cudaStream_t st);
 int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float* gates,
                           float* xz, cudaStream_t st);
 size_t generic_smem_bytes(int H, int W);
+
+// ---- GDN block ----
+struct GdnDwArgs {
+  const float* x; float* out;            // channels-last (BT, H, W, C); out may be nullptr
+  const float* wk; const float* bias;    // (K,K,1,C), (C)
+  int ksz;                               // <= 1: no conv (only the context sums)
+  int BT, T, H, W, C;
+  const float2* rope_t; const float2* rope_h; const float2* rope_w;   // nullptr = no RoPE
+  float* ctx_part;                       // (BT, H, C) row sums of the rotated input
+};
+int launch_rope_dwconv_cl(const GdnDwArgs& a, cudaStream_t st);
+
+struct GdnGateArgs {
+  const float* ctx_part; const float* tcode;   // (BT,H,C), (T,C)
+  int BT, T, C, H, W, gate_type, use_input_gates, path;
+  const float* gk[8]; const float* gb[8];
+  float2* ab;                            // (BT, H*Wf) {alpha, beta} in spectral bin order
+  float2* bkv;                           // (BT, H*W)  {B_k, B_v}
+};
+int launch_gdn_gates(const GdnGateArgs& g, cudaStream_t st);
+
+struct GdnSpectralArgs {
+  float* qkv;                // planar (BT, 3C, H, W): q planes, k planes, v planes (o overwrites v)
+  const cf* what;            // (n_h, H*Wf) in spectral bin order
+  const float2* ab;          // (BT, H*Wf)
+  cf* state;                 // (B*n_h, dk, dk, H*Wf) scratch for the matrix state
+  int B, T, C, H, W, dk, use_l2;
+};
+int launch_gdn_spectral(const GdnSpectralArgs& a, cudaStream_t st);
+size_t gdn_generic_smem_bytes(int H, int W, int dk);
 
 }  // namespace cssm

@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_kernel(const Stencil
       // slot t % nh holds s_{t-nh}, which tap 0 has just consumed
       if (nh > 0) hist[(t % nh) * HW + i] = v;
       if (s.act) o = silu_f(o);
-      if (s.post) o *= s.post[frame * HW + i];
+      if (s.post) o *= s.post[(frame * HW + i) * s.post_stride + s.post_off];
       p[i] = o;
       lsum += o;
     }

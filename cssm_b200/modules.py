@@ -277,3 +277,222 @@ class BoundGated:
             if name == upto:
                 break
         return out
+
+
+# ============================================================================== GDN
+@dataclass
+class GatedDeltaNetCSSM:
+    """Gated DeltaNet spectral mixer (reference: GatedDeltaNetCSSM,
+    src/models/cssm.py:4264-5141).  Same fields and defaults as the Flax dataclass; fields the
+    d_k x d_k log-space path of the reference never reads (block_size, ssd_chunk_size,
+    learned_init, scan_mode, use_complex32/16 with use_log=True) are accepted and have no
+    effect here either."""
+    channels: int
+    delta_key_dim: int = 2
+    kernel_size: int = 11
+    rope_mode: str = "none"
+    rope_base: float = 10000.0
+    spectral_rho: float = 0.999
+    position_independent_gates: bool = False
+    block_size: int = 1
+    gate_type: str = "channel"
+    use_goom: bool = True
+    use_log: bool = True
+    use_complex32: bool = False
+    use_complex16: bool = False
+    scan_mode: str = "associative"
+    ssd_chunk_size: int = 8
+    learned_init: bool = False
+    short_conv_size: int = 4
+    output_norm: str = "rms"
+    use_input_gates: bool = True
+    output_gate_act: str = "silu"
+    use_spectral_l2_norm: bool = True
+    qkv_conv_size: int = 1
+    qkv_conv_separable: bool = True
+    cross_freq_conv_size: int = 0
+    no_spectral_clamp: bool = False
+    int_attention_mode: str = "none"
+    attn_kernel_size: int = 7
+    int_attn_dim: int = 16
+    static_image_fast_path: bool = False
+    num_timesteps: int = 0
+    ssl_proj_dim: int = 0
+    gate_proj_bias_init: float = 0.0
+    name: Optional[str] = None
+    _bound: Dict[Any, Any] = field(default_factory=dict, repr=False, compare=False)
+
+    GATES = ("alpha", "beta", "B_k", "B_v")
+
+    def param_shapes(self, H: int, W: int) -> Dict[str, Any]:
+        Cc, Wf = self.channels, W // 2 + 1
+        nh = Cc // self.delta_key_dim
+        s: Dict[str, Any] = {
+            "kernel": (nh, self.kernel_size, self.kernel_size),
+            "qkv_proj": {"kernel": (Cc, 3 * Cc), "bias": (3 * Cc,)},
+            "gate_proj": {"kernel": (Cc, Cc), "bias": (Cc,)},
+            "output_proj": {"kernel": (Cc, Cc), "bias": (Cc,)},
+        }
+        if self.output_norm == "rms":
+            s["rms_scale"] = (Cc,)
+        if self.qkv_conv_size > 1:
+            k = self.qkv_conv_size
+            s["qkv_dw"] = {"kernel": (k, k, 1, Cc), "bias": (Cc,)}
+        if self.short_conv_size > 0:
+            for n in ("short_conv_q", "short_conv_k", "short_conv_v"):
+                s[n] = {"kernel": (self.short_conv_size, 1, Cc), "bias": (Cc,)}
+        gates = self.GATES if self.use_input_gates else self.GATES[:2]
+        for n in gates:
+            wd = W if n.startswith("B_") else Wf
+            if self.gate_type == "factored":
+                s[f"{n}_h"] = {"kernel": (Cc, H), "bias": (H,)}
+                s[f"{n}_w"] = {"kernel": (Cc, wd), "bias": (wd,)}
+            else:
+                s[n] = {"kernel": (Cc, H * wd), "bias": (H * wd,)}
+        return s
+
+    def init(self, seed: int, x_shape, bias_scale: float = 0.0) -> Dict[str, Any]:
+        _, _, H, W, Cc = x_shape
+        rng = np.random.default_rng(seed)
+        out: Dict[str, Any] = {}
+        for k, v in self.param_shapes(H, W).items():
+            if isinstance(v, dict):
+                kern = v["kernel"]
+                fan_in = kern[0] * kern[1] if len(kern) == 4 else kern[0]
+                b = bias_scale * rng.standard_normal(v["bias"])
+                if k == "gate_proj":
+                    b = b + self.gate_proj_bias_init
+                out[k] = {"kernel": (rng.standard_normal(kern) / np.sqrt(fan_in)).astype(np.float32),
+                          "bias": b.astype(np.float32)}
+            elif k == "rms_scale":
+                out[k] = np.ones(v, np.float32)
+            else:   # spectral kernel, xavier-normal over (n_h, ks, ks)
+                std = np.sqrt(2.0 / (2 * v[0] * v[1]))
+                out[k] = (std * rng.standard_normal(v)).astype(np.float32)
+        return {"params": out}
+
+    def _check_fields(self):
+        bad = []
+        if self.gate_type not in GATE_TYPES:
+            bad.append(f"gate_type={self.gate_type!r} (have 'factored', 'dense')")
+        if not (self.use_log and self.use_goom) and (self.use_complex32 or self.use_complex16):
+            bad.append("bf16/fp8 split-precision scans")
+        if self.position_independent_gates:
+            bad.append("position_independent_gates")
+        if self.rope_mode not in ROPE_MODES:
+            bad.append(f"rope_mode={self.rope_mode!r}")
+        if self.output_norm not in ("rms", "none"):
+            bad.append(f"output_norm={self.output_norm!r}")
+        if self.qkv_conv_size > 1 and not self.qkv_conv_separable:
+            bad.append("non-separable qkv conv")
+        if self.cross_freq_conv_size or self.int_attention_mode != "none" or self.ssl_proj_dim:
+            bad.append("cross_freq_conv / int_attention / ssl_proj")
+        if self.static_image_fast_path:
+            bad.append("static_image_fast_path")
+        if self.output_gate_act not in ("silu", "sigmoid"):
+            bad.append(f"output_gate_act={self.output_gate_act!r}")
+        if self.delta_key_dim > 4:
+            bad.append("delta_key_dim > 4")
+        if bad:
+            raise NotImplementedError("GatedDeltaNetCSSM: no CUDA kernel for " + "; ".join(bad))
+
+    def _desc(self, shape) -> GdnDesc:
+        B, T, H, W, Cc = shape
+        if Cc != self.channels:
+            raise ValueError(f"x has {Cc} channels, module has {self.channels}")
+        if Cc % self.delta_key_dim:
+            raise AssertionError(f"channels={Cc} must be divisible by delta_key_dim={self.delta_key_dim}")
+        return GdnDesc(B, T, H, W, Cc, self.delta_key_dim, self.kernel_size,
+                       ROPE_MODES[self.rope_mode], float(self.rope_base), float(self.spectral_rho),
+                       GATE_TYPES[self.gate_type], self.short_conv_size,
+                       1 if self.output_norm == "rms" else 0, int(self.use_input_gates),
+                       0 if self.output_gate_act == "silu" else 1, int(self.use_spectral_l2_norm),
+                       self.qkv_conv_size, int(self.no_spectral_clamp))
+
+    def bind(self, variables, device="cuda") -> "BoundGdn":
+        self._check_fields()
+        return BoundGdn(self, variables["params"] if "params" in variables else variables,
+                        torch.device(device))
+
+    def apply(self, variables, x, injected_qkv_spatial=None):
+        key = id(variables)
+        bound = self._bound.get(key)
+        if bound is None or bound.variables_ref is not variables:
+            _require_cuda(x)
+            bound = self.bind(variables, x.device)
+            bound.variables_ref = variables
+            self._bound.clear()
+            self._bound[key] = bound
+        return bound(x)
+
+
+class BoundGdn:
+    def __init__(self, mod: GatedDeltaNetCSSM, p, device):
+        self.mod, self.device, self.variables_ref = mod, device, None
+        self.L = _lib.lib()
+        self.t: Dict[str, torch.Tensor] = {}
+
+        def put(name, arr):
+            self.t[name] = _dev_f32(arr, device)
+            return self.t[name].data_ptr()
+
+        w = GdnWeights()
+        w.kernel = put("kernel", p["kernel"])
+        if mod.qkv_conv_size > 1:
+            w.qkv_dw_kernel = put("dwk", p["qkv_dw"]["kernel"])
+            w.qkv_dw_bias = put("dwb", p["qkv_dw"]["bias"])
+        w.qkv_proj_kernel = put("qk", p["qkv_proj"]["kernel"])
+        w.qkv_proj_bias = put("qb", p["qkv_proj"]["bias"])
+        if mod.short_conv_size > 0:
+            for i, n in enumerate(("short_conv_q", "short_conv_k", "short_conv_v")):
+                w.conv_t_kernel[i] = put(f"ct{i}k", p[n]["kernel"])
+                w.conv_t_bias[i] = put(f"ct{i}b", p[n]["bias"])
+        gates = mod.GATES if mod.use_input_gates else mod.GATES[:2]
+        for g, n in enumerate(gates):
+            if mod.gate_type == "factored":
+                w.gate_kernel[2 * g] = put(f"g{g}hk", p[f"{n}_h"]["kernel"])
+                w.gate_bias[2 * g] = put(f"g{g}hb", p[f"{n}_h"]["bias"])
+                w.gate_kernel[2 * g + 1] = put(f"g{g}wk", p[f"{n}_w"]["kernel"])
+                w.gate_bias[2 * g + 1] = put(f"g{g}wb", p[f"{n}_w"]["bias"])
+            else:
+                w.gate_kernel[g] = put(f"g{g}k", p[n]["kernel"])
+                w.gate_bias[g] = put(f"g{g}b", p[n]["bias"])
+        w.gate_proj_kernel = put("gpk", p["gate_proj"]["kernel"])
+        w.gate_proj_bias = put("gpb", p["gate_proj"]["bias"])
+        if mod.output_norm == "rms":
+            w.rms_scale = put("rms", p["rms_scale"])
+        w.output_proj_kernel = put("opk", p["output_proj"]["kernel"])
+        w.output_proj_bias = put("opb", p["output_proj"]["bias"])
+        self.w = w
+        self.buf = _Buffers(device)
+        self._plans: Dict[Any, torch.Tensor] = {}
+
+    def desc(self, shape) -> GdnDesc:
+        return self.mod._desc(shape)
+
+    def plan(self, d: GdnDesc) -> torch.Tensor:
+        key = (d.T, d.H, d.W)
+        pl = self._plans.get(key)
+        if pl is None:
+            n = self.L.cssm_gdn_plan_bytes(C.byref(d))
+            if n == 0:
+                raise NotImplementedError(
+                    f"GatedDeltaNetCSSM: no CUDA kernel for {tuple(getattr(d, f[0]) for f in d._fields_)}")
+            pl = torch.empty(n, dtype=torch.uint8, device=self.device)
+            check(self.L.cssm_gdn_plan_init(C.byref(d), C.byref(self.w), pl.data_ptr(), n,
+                                            _stream_ptr(self.device)), "cssm_gdn_plan_init")
+            self._plans[key] = pl
+        return pl
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x)
+        x = x.contiguous()
+        d = self.desc(tuple(x.shape))
+        pl = self.plan(d)
+        n = self.L.cssm_gdn_workspace_bytes(C.byref(d))
+        ws = self.buf.get("ws", n)
+        y = torch.empty_like(x) if out is None else out
+        check(self.L.cssm_gdn_forward(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(),
+                                      y.data_ptr(), ws.data_ptr(), n, _stream_ptr(self.device)),
+              "cssm_gdn_forward")
+        return y

@@ -158,6 +158,59 @@ typedef struct cssm_gated_ws_layout {
 } cssm_gated_ws_layout;
 int cssm_gated_workspace_layout(const cssm_gated_desc* d, cssm_gated_ws_layout* out);
 
+/* -------------------------------------------------------- GatedDeltaNetCSSM --- */
+/* Fields of GatedDeltaNetCSSM (cssm.py:4298-4338) read by the general path with
+ * gate_type in {factored, dense}, d_k = d_v = delta_key_dim. */
+typedef struct cssm_gdn_desc {
+  int32_t B, T, H, W, C;
+  int32_t delta_key_dim;
+  int32_t kernel_size;
+  int32_t rope_mode;
+  float   rope_base;
+  float   spectral_rho;
+  int32_t gate_type;
+  int32_t short_conv_size;
+  int32_t output_norm;            /* 1 = 'rms', 0 = 'none'                            */
+  int32_t use_input_gates;
+  int32_t output_gate_act;        /* 0 = silu, 1 = sigmoid                            */
+  int32_t use_spectral_l2_norm;
+  int32_t qkv_conv_size;          /* 1 = Dense only, >1 = depthwise conv first        */
+  int32_t no_spectral_clamp;
+} cssm_gdn_desc;
+
+/* Parameter tree (cssm.py:4729-5141).  gate order: alpha, beta, B_k, B_v; factored:
+ * index 2*g = "<name>_h" (C,H), 2*g+1 = "<name>_w" (C, W/2+1 for alpha/beta, W for
+ * B_k/B_v); dense: index g = "<name>". */
+typedef struct cssm_gdn_weights {
+  const float* kernel;            /* (n_h, ks, ks)                     */
+  const float* qkv_dw_kernel;     /* (K,K,1,C) or NULL                 */
+  const float* qkv_dw_bias;
+  const float* qkv_proj_kernel;   /* (C, 3C)                           */
+  const float* qkv_proj_bias;
+  const float* conv_t_kernel[3];  /* short_conv_q/k/v (k,1,C) or NULL  */
+  const float* conv_t_bias[3];
+  const float* gate_kernel[8];
+  const float* gate_bias[8];
+  const float* gate_proj_kernel;  /* (C, C)                            */
+  const float* gate_proj_bias;
+  const float* rms_scale;         /* (C) or NULL when output_norm none */
+  const float* output_proj_kernel;/* (C, C)                            */
+  const float* output_proj_bias;
+} cssm_gdn_weights;
+
+size_t cssm_gdn_plan_bytes(const cssm_gdn_desc* d);
+size_t cssm_gdn_workspace_bytes(const cssm_gdn_desc* d);
+
+/* Weight-only precompute of W_hat (cssm.py:4713-4734), RoPE tables and the temporal
+ * context code (cssm.py:353-383). */
+int cssm_gdn_plan_init(const cssm_gdn_desc* d, const cssm_gdn_weights* w,
+                       void* plan, size_t plan_bytes, void* stream);
+
+/* Whole block: y = GatedDeltaNetCSSM(x).  Replaces cssm.py:4340-4352, 4685-5141. */
+int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                     const float* x, float* y, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
 /* ---- entry point that allocates nothing (no counterpart in the reference) ----
  * The reference has nothing like this: it is for hosts that may not call cudaMalloc at all
  * (a plugin running inside another framework's step, whose allocator owns the device memory;
