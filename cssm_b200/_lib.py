@@ -86,6 +86,8 @@ SIGNATURES = {
     "cssm_gdn_plan_init": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, C.c_size_t, _P]),
     "cssm_gdn_forward": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
                                    C.c_size_t, _P]),
+    "cssm_debug_set_gemm_backend": (C.c_int, [C.c_int]),
+    "cssm_debug_tc_error": (C.c_int, [C.POINTER(C.c_int)]),
     "cssm_static_scratch_bytes": (C.c_size_t, []),
     "cssm_gated_forward_static": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
                                             _P, _P]),

@@ -161,7 +161,7 @@ int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, co
     g.rope_w = (const float2*)(base + p.rope_w);
   }
   g.T = d->T; g.H = d->H; g.W = d->W;
-  return launch_gemm_simt<false, true>(g, (cudaStream_t)stream);
+  return launch_gemm<false, true>(g, (cudaStream_t)stream);
 }
 
 int cssm_gated_short_conv(const cssm_gated_desc* d, const cssm_gated_weights* w, float* xz,
@@ -224,7 +224,7 @@ int cssm_gated_out_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, c
   g.Wk = w->out_proj_kernel; g.bias = w->out_proj_bias;
   g.out = y;
   g.T = d->T; g.H = d->H; g.W = d->W;
-  return launch_gemm_simt<true, false>(g, (cudaStream_t)stream);
+  return launch_gemm<true, false>(g, (cudaStream_t)stream);
 }
 
 int cssm_gated_forward(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,

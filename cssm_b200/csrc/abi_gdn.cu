@@ -158,7 +158,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   g.T = d->T; g.H = d->H; g.W = d->W;
   if (d->qkv_conv_size > 1) { g.A = xdw; }
   else { g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; }
-  if ((s = launch_gemm_simt<false, true>(g, st)) != CSSM_OK) return s;
+  if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
   // 3. output gate projection of the rotated input -> planar, through SiLU / sigmoid
   memset(&g, 0, sizeof(g));
@@ -168,7 +168,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   g.out = gate; g.o_planes = C; g.o_plane0 = 0;
   g.T = d->T; g.H = d->H; g.W = d->W;
   g.out_act = d->output_gate_act == 0 ? 1 : 2;
-  if ((s = launch_gemm_simt<false, true>(g, st)) != CSSM_OK) return s;
+  if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
   // 4. gate maps
   GdnGateArgs ga;
@@ -212,7 +212,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   g.Wk = w->output_proj_kernel; g.bias = w->output_proj_bias;
   g.out = y;
   g.T = d->T; g.H = d->H; g.W = d->W;
-  return launch_gemm_simt<true, false>(g, st);
+  return launch_gemm<true, false>(g, st);
 }
 
 }  // extern "C"

@@ -173,4 +173,17 @@ inline int launch_gemm_simt(const GemmArgs& g, cudaStream_t st) {
   return check_launch();
 }
 
+// Tensor-core (tcgen05) variant for K = 64, N in {64, 128}, H*W a multiple of 128.
+bool gemm_tc_supported(const GemmArgs& g, bool a_planar);
+int launch_gemm_tc(const GemmArgs& g, bool a_planar, cudaStream_t st);
+int read_tc_error(int* out);
+
+// Picks the tensor-core kernel when it covers the problem, else the CUDA-core kernel.
+template <bool A_PLANAR, bool O_PLANAR>
+inline int launch_gemm(const GemmArgs& g, cudaStream_t st) {
+  static_assert(A_PLANAR != O_PLANAR, "projections change layout");
+  if (gemm_tc_supported(g, A_PLANAR)) return launch_gemm_tc(g, A_PLANAR, st);
+  return launch_gemm_simt<A_PLANAR, O_PLANAR>(g, st);
+}
+
 }  // namespace cssm

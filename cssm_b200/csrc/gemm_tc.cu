@@ -1,0 +1,312 @@
+// tcgen05 / TMEM GEMM for the K = 64 channel projections in fp32-equivalent precision
+// (3 x TF32: A_hi*B_hi + A_lo*B_hi + A_hi*B_lo, accumulated in fp32 in TMEM).
+//
+// Persistent kernel, one CTA per SM, 288 threads, warp-specialised:
+//   warps 0-3  producers : read a 128-pixel A tile from global memory (channels-last rows with
+//                          RoPE fused, or planar planes with the RMSNorm/gate prologue fused),
+//                          split every value into tf32 hi + remainder, and write both into the
+//                          128-byte-swizzled K-major operand layout of a 2-stage ring;
+//   warp  4    MMA issuer: one lane issues 24 tcgen05.mma (M128 x N x K8) per tile into one of
+//                          two TMEM accumulators and commits to mbarriers;
+//   warps 5-8  epilogue  : tcgen05.ld the accumulator (lane = pixel), add bias / activation,
+//                          store planar (coalesced over pixels) or channels-last rows.
+// The weight tile (both halves of the split) is prepared once per CTA and stays in shared memory.
+// Every mbarrier wait is bounded; on expiry the kernel records an error code and winds down.
+#include "kernels.cuh"
+#include "gemm_simt.cuh"
+#include "tc05.cuh"
+
+namespace cssm {
+
+__device__ int g_tc_error = 0;
+
+constexpr int TC_THREADS = 288;
+constexpr int TC_BM = 128;
+constexpr int TC_K = 64;
+constexpr uint32_t TC_A_HALF = 2u * TC_BM * 128u;      // one of hi / lo: 2 K-blocks x 128 rows x 128 B
+
+template <int N>
+struct TcSmem {
+  static constexpr uint32_t B_HALF = 2u * N * 128u;
+  static constexpr uint32_t B_OFF = 0;
+  static constexpr uint32_t A_OFF = 2u * B_HALF;                 // after B_hi, B_lo
+  static constexpr uint32_t BIAS_OFF = A_OFF + 2u * 2u * TC_A_HALF;
+  static constexpr uint32_t BAR_OFF = BIAS_OFF + N * 4u;
+  static constexpr uint32_t TOTAL = BAR_OFF + 128u;
+};
+
+template <int N, bool A_PLANAR>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g, int num_tiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // operand tiles need 1024-byte alignment (swizzle atoms); the launch adds 1024 bytes of slack
+  unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
+  using L = TcSmem<N>;
+  const uint32_t sbase = tc::smem_u32(smem);
+  float* bias_s = reinterpret_cast<float*>(smem + L::BIAS_OFF);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* full = bars;          // [2] A stage written (128 producer arrivals)
+  uint64_t* empty = bars + 2;     // [2] A stage consumed (tcgen05.commit)
+  uint64_t* accfull = bars + 4;   // [2] accumulator complete (tcgen05.commit)
+  uint64_t* accempty = bars + 6;  // [2] accumulator drained (128 epilogue arrivals)
+  uint64_t* done = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr uint32_t TMEM_COLS = (2 * N <= 32) ? 32 : (2 * N <= 64) ? 64 : (2 * N <= 128) ? 128
+                                 : (2 * N <= 256) ? 256 : 512;
+
+  if (tid == 0) {
+    tc::mbar_init(&full[0], 128); tc::mbar_init(&full[1], 128);
+    tc::mbar_init(&empty[0], 1); tc::mbar_init(&empty[1], 1);
+    tc::mbar_init(&accfull[0], 1); tc::mbar_init(&accfull[1], 1);
+    tc::mbar_init(&accempty[0], 128); tc::mbar_init(&accempty[1], 128);
+    tc::mbar_init(done, 1);
+    tc::fence_mbar_init();
+  }
+  if (warp == 4) {
+    tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  // ---- weights: W[k][n] -> B_hi / B_lo rows n, K-major swizzled ----
+  for (int item = tid; item < N * 16; item += TC_THREADS) {
+    const int n = item % N, c = item / N;               // c: 16-byte chunk of 4 k values
+    float hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) tc::split_tf32(g.Wk[(size_t)(4 * c + e) * g.N + n], hi[e], lo[e]);
+    const uint32_t off = (uint32_t)(c >> 3) * (N * 128u) + tc::sw128_offset(n, c & 7);
+    *reinterpret_cast<float4*>(smem + L::B_OFF + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<float4*>(smem + L::B_OFF + L::B_HALF + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+  }
+  for (int n = tid; n < N; n += TC_THREADS) bias_s[n] = g.bias ? g.bias[n] : 0.f;
+  tc::fence_proxy_async();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    // ================================ producers ================================
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      if (!tc::mbar_wait(&empty[s], ((it >> 1) & 1) ^ 1)) { atomicExch(&g_tc_error, 1); break; }
+      unsigned char* a_hi = smem + L::A_OFF + (uint32_t)s * 2u * TC_A_HALF;
+      unsigned char* a_lo = a_hi + TC_A_HALF;
+      const int m0 = tile * TC_BM;
+      if (!A_PLANAR) {
+#pragma unroll 4
+        for (int r = 0; r < 16; ++r) {
+          const int idx = r * 128 + tid;
+          const int row = idx >> 4, chunk = idx & 15;
+          const int m = m0 + row;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (m < g.M) {
+            v = *reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4);
+            if (g.rope_t != nullptr) {
+              const int px = m % g.HW, fr = m / g.HW;
+              const int t = fr % g.T, h = px / g.W, w = px % g.W;
+              const int i = chunk * 2;
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const float2 ct = g.rope_t[t * 32 + i + e];
+                const float2 ch = g.rope_h[h * 32 + i + e];
+                const float2 cw = g.rope_w[w * 32 + i + e];
+                const float cx = ct.x * ch.x - ct.y * ch.y, sx = ct.x * ch.y + ct.y * ch.x;
+                const float c2 = cx * cw.x - sx * cw.y, s2 = cx * cw.y + sx * cw.x;
+                float& xe = e ? v.z : v.x;
+                float& xo = e ? v.w : v.y;
+                const float ne = xe * c2 - xo * s2, no = xe * s2 + xo * c2;
+                xe = ne; xo = no;
+              }
+            }
+          }
+          float4 h4, l4;
+          tc::split_tf32(v.x, h4.x, l4.x); tc::split_tf32(v.y, h4.y, l4.y);
+          tc::split_tf32(v.z, h4.z, l4.z); tc::split_tf32(v.w, h4.w, l4.w);
+          const uint32_t off = (uint32_t)(chunk >> 3) * (TC_BM * 128u) + tc::sw128_offset(row, chunk & 7);
+          *reinterpret_cast<float4*>(a_hi + off) = h4;
+          *reinterpret_cast<float4*>(a_lo + off) = l4;
+        }
+      } else {
+        // thread = pixel row; planes are contiguous over pixels, so each k is a coalesced read
+        const int row = tid, m = m0 + row;
+        float v[TC_K];
+        if (m < g.M) {
+          const int fr = m / g.HW, px = m % g.HW;
+          const float* ap = g.A + ((size_t)fr * g.a_planes + g.a_plane0) * g.HW + px;
+#pragma unroll
+          for (int k = 0; k < TC_K; ++k) v[k] = ap[(size_t)k * g.HW];
+          if (g.rms_scale != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < TC_K; ++k) ss = fmaf(v[k], v[k], ss);
+            const float rinv = rsqrtf(ss * (1.0f / TC_K) + 1e-6f);
+#pragma unroll
+            for (int k = 0; k < TC_K; ++k) v[k] *= rinv * g.rms_scale[k];
+          }
+          if (g.gate != nullptr) {
+            const float* gp = g.gate + ((size_t)fr * g.g_planes + g.g_plane0) * g.HW + px;
+#pragma unroll
+            for (int k = 0; k < TC_K; ++k) v[k] *= gp[(size_t)k * g.HW];
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < TC_K; ++k) v[k] = 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float4 h4, l4;
+          tc::split_tf32(v[4 * c + 0], h4.x, l4.x); tc::split_tf32(v[4 * c + 1], h4.y, l4.y);
+          tc::split_tf32(v[4 * c + 2], h4.z, l4.z); tc::split_tf32(v[4 * c + 3], h4.w, l4.w);
+          const uint32_t off = (uint32_t)(c >> 3) * (TC_BM * 128u) + tc::sw128_offset(row, c & 7);
+          *reinterpret_cast<float4*>(a_hi + off) = h4;
+          *reinterpret_cast<float4*>(a_lo + off) = l4;
+        }
+      }
+      tc::fence_proxy_async();
+      tc::mbar_arrive(&full[s]);
+    }
+  } else if (warp == 4) {
+    // ================================ MMA issuer ================================
+    if (lane == 0) {
+      const uint32_t idesc = tc::make_idesc_tf32(TC_BM, N);
+      const uint32_t b_hi = sbase + L::B_OFF, b_lo = b_hi + L::B_HALF;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+        const int s = it & 1, ph = (it >> 1) & 1;
+        if (!tc::mbar_wait(&accempty[s], ph ^ 1) || !tc::mbar_wait(&full[s], ph)) {
+          atomicExch(&g_tc_error, 2); ok = false; break;
+        }
+        tc::fence_after_sync();
+        const uint32_t a_hi = sbase + L::A_OFF + (uint32_t)s * 2u * TC_A_HALF, a_lo = a_hi + TC_A_HALF;
+        const uint32_t d = tmem_base + (uint32_t)s * N;
+        uint32_t acc = 0;
+#pragma unroll
+        for (int pass = 0; pass < 3; ++pass) {
+          const uint32_t ab = pass == 1 ? a_lo : a_hi;
+          const uint32_t bb = pass == 2 ? b_lo : b_hi;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t koff = (uint32_t)(ks & 3) * 32u;
+            const uint64_t ad = tc::make_desc_sw128(ab + (uint32_t)(ks >> 2) * (TC_BM * 128u) + koff);
+            const uint64_t bd = tc::make_desc_sw128(bb + (uint32_t)(ks >> 2) * (N * 128u) + koff);
+            tc::mma_tf32(d, ad, bd, idesc, acc);
+            acc = 1;
+          }
+        }
+        tc::commit(&empty[s]);
+        tc::commit(&accfull[s]);
+      }
+      // nothing of this thread's tensor work may be in flight when TMEM is freed
+      tc::commit(done);
+      if (!tc::mbar_wait(done, 0) && ok) atomicExch(&g_tc_error, 3);
+    }
+    __syncwarp();
+  } else {
+    // ================================ epilogue ================================
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int row = q * 32 + lane;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1, ph = (it >> 1) & 1;
+      if (!tc::mbar_wait(&accfull[s], ph)) { atomicExch(&g_tc_error, 4); break; }
+      tc::fence_after_sync();
+      const int m = tile * TC_BM + row;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)s * N;
+#pragma unroll 1
+      for (int cc = 0; cc < N / 32; ++cc) {
+        uint32_t r[32];
+        tc::ld_32x32b_x32(taddr + cc * 32, r);
+        tc::wait_ld();
+        if (m < g.M) {
+          if (!A_PLANAR) {
+            // planar output: lanes = consecutive pixels -> 128-byte coalesced stores per column
+            const int fr = m / g.HW, px = m % g.HW;
+            float* op = g.out + ((size_t)fr * g.o_planes + g.o_plane0 + cc * 32) * g.HW + px;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float v = __uint_as_float(r[j]) + bias_s[cc * 32 + j];
+              if (g.out_act == 1) v = silu_f(v);
+              else if (g.out_act == 2) v = sigmoid_f(v);
+              op[(size_t)j * g.HW] = v;
+            }
+          } else {
+            float* op = g.out + (size_t)m * g.N + cc * 32;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v;
+              v.x = __uint_as_float(r[j + 0]) + bias_s[cc * 32 + j + 0];
+              v.y = __uint_as_float(r[j + 1]) + bias_s[cc * 32 + j + 1];
+              v.z = __uint_as_float(r[j + 2]) + bias_s[cc * 32 + j + 2];
+              v.w = __uint_as_float(r[j + 3]) + bias_s[cc * 32 + j + 3];
+              *reinterpret_cast<float4*>(op + j) = v;
+            }
+          }
+        }
+      }
+      tc::fence_before_sync();
+      tc::mbar_arrive(&accempty[s]);
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+static int g_force_simt = 0;
+void set_force_simt(int on) { g_force_simt = on; }
+
+// Whether the tensor-core kernel covers this problem (else the CUDA-core GEMM runs).
+bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
+  if (g_force_simt) return false;
+  if (g.K != TC_K || (g.N != 64 && g.N != 128)) return false;
+  if (g.HW % TC_BM != 0 || g.M % TC_BM != 0) return false;
+  if (!a_planar && g.rope_t != nullptr && g.K != 64) return false;
+  return true;
+}
+
+template <int N, bool A_PLANAR>
+static int launch_tc(const GemmArgs& g, cudaStream_t st) {
+  const int num_tiles = g.M / TC_BM;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  const size_t smem = TcSmem<N>::TOTAL + 1024;      // slack for the 1024-byte alignment
+  e = cudaFuncSetAttribute(gemm_tc_kernel<N, A_PLANAR>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  gemm_tc_kernel<N, A_PLANAR><<<grid, TC_THREADS, smem, st>>>(g, num_tiles);
+  return check_launch();
+}
+
+int launch_gemm_tc(const GemmArgs& g, bool a_planar, cudaStream_t st) {
+  if (!gemm_tc_supported(g, a_planar)) return CSSM_ERR_UNSUPPORTED;
+  if (!a_planar) return g.N == 128 ? launch_tc<128, false>(g, st) : launch_tc<64, false>(g, st);
+  return g.N == 128 ? launch_tc<128, true>(g, st) : launch_tc<64, true>(g, st);
+}
+
+int read_tc_error(int* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_tc_error, sizeof(int));
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  return CSSM_OK;
+}
+
+}  // namespace cssm
+
+extern "C" {
+int cssm_debug_set_gemm_backend(int backend) {
+  if (backend != 0 && backend != 1) return CSSM_ERR_UNSUPPORTED;
+  cssm::set_force_simt(backend);
+  return CSSM_OK;
+}
+int cssm_debug_tc_error(int* out) {
+  if (!out) return CSSM_ERR_NULL;
+  return cssm::read_tc_error(out);
+}
+}

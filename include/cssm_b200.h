@@ -211,6 +211,14 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
                      const float* x, float* y, void* workspace, size_t workspace_bytes,
                      void* stream);
 
+/* ---- diagnostics (no counterpart in the reference) ----
+ * cssm_debug_set_gemm_backend: 0 = tensor-core (tcgen05) projections where they apply
+ * (default), 1 = CUDA-core fp32 projections everywhere; process-wide, for A/B tests.
+ * cssm_debug_tc_error: copies the device-side error code of the tensor-core GEMM (0 = no
+ * bounded wait ever expired) to *out; synchronises the device. */
+int cssm_debug_set_gemm_backend(int backend);
+int cssm_debug_tc_error(int* out);
+
 /* ---- entry point that allocates nothing (no counterpart in the reference) ----
  * The reference has nothing like this: it is for hosts that may not call cudaMalloc at all
  * (a plugin running inside another framework's step, whose allocator owns the device memory;

@@ -128,3 +128,34 @@ def test_golden_fixtures_on_gpu():
                         rope_mode=kw["rope_mode"], gate_type=kw["gate_type"])
         y = mod.apply({"params": p}, torch.from_numpy(g["x"]).cuda()).cpu().numpy()
         assert orc.rel_l2(y, g["y"]) <= TOL
+
+
+def _tc_error(L):
+    import ctypes as C
+    v = C.c_int(-1)
+    assert L.cssm_debug_tc_error(C.byref(v)) == 0
+    return v.value
+
+
+@pytest.mark.parametrize("rope", ["spatiotemporal", "none"])
+def test_tensor_core_projections_c64(rope):
+    """C = 64 on 64x64 planes takes the tcgen05 3xTF32 projections; compare with the oracle,
+    with the CUDA-core projections, and check that no bounded wait expired."""
+    bound, xd, ref, inter = _run(2, 2, 64, 64, 64, 11, "factored", rope, 3, 4)
+    L = bound.L
+    B, T, H, W, C = 2, 2, 64, 64, 64
+    st = bound.stages(xd, upto="in_proj")
+    xz = st["xz"].cpu().numpy().reshape(B, T, 2 * C, H, W)
+    y_tc = bound(xd).cpu().numpy()
+    assert _tc_error(L) == 0
+    assert orc.rel_l2(y_tc, ref) <= TOL
+    assert L.cssm_debug_set_gemm_backend(1) == 0
+    try:
+        y_simt = bound(xd).cpu().numpy()
+    finally:
+        assert L.cssm_debug_set_gemm_backend(0) == 0
+    assert orc.rel_l2(y_simt, ref) <= TOL
+    assert orc.rel_l2(y_tc, y_simt) <= 2e-6
+    # stage level: the planar x_main / z planes straight out of in_proj
+    z = xz[:, :, C:].transpose(0, 1, 3, 4, 2)
+    assert orc.rel_l2(z, inter["z"]) <= 2e-6

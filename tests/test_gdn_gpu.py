@@ -40,6 +40,7 @@ CASES = [
     (1, 8, 64, 64, 4, 4, 11, "dense", "none", 4, 1),
     (1, 2, 64, 64, 8, 2, 11, "factored", "none", 0, 1),      # 64x64 with d_k=2: generic kernel
     (1, 2, 7, 7, 8, 4, 11, "factored", "temporal", 4, 3),    # kernel larger than the plane
+    (1, 2, 64, 64, 64, 4, 11, "factored", "mrope", 4, 5),    # C = 64: tensor-core projections
 ]
 
 
