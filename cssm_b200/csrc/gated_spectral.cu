@@ -1,133 +1,105 @@
 // Fused spectral kernels of the gated block: rfft2 -> gated complex recurrence over T with
 // the state on chip -> irfft2 -> * silu(z).  One CTA per (batch, channel) pair.
-#include "fft.cuh"
+#include "r64.cuh"
 #include "kernels.cuh"
 
 namespace cssm {
 
 // ============================================================== 64 x 64 planes ====
-// 288 threads.  lane = sub + 4*a.  Row passes: warp w < 8 owns row pairs 4w + sub (two
-// real rows packed into one complex 64-point FFT).  Column passes: warp w < 9 owns
-// half-spectrum columns kw = 4w + sub (kw <= 32); the lane keeps the state of bins
-// kh = a + 8b, b = 0..7, in registers for all T steps.
-constexpr int R64_THREADS = 288;
-constexpr int R64_ZR_STRIDE = 68;   // cf per packed row pair
-constexpr int R64_GB_STRIDE = 34;   // cf per spatial row of the inverse column output
-constexpr int R64_SMEM_CF = 36 * EX_GROUP_STRIDE + 32 * R64_ZR_STRIDE + 64 * R64_GB_STRIDE;
+// 288 threads; thread roles and shared-memory layout are those of r64.cuh.  The lane keeps the
+// state of its 8 bins (kh = a + 8q of column grp) in registers for all T steps.  Global loads
+// are issued one phase ahead of their use: the gate maps and K_hat at the top of the column
+// phase, z_t and the next step's x_main plane at the top of the inverse-row phase.
+constexpr int R64_THREADS = R64_NT;
+constexpr int R64_SMEM_CF = R64_EX_CF + R64_ZR_CF + R64_GB_CF;
 
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
-  cf* ZR = EX + 36 * EX_GROUP_STRIDE;
-  cf* GB = ZR + 32 * R64_ZR_STRIDE;
+  R64Ctx c;
+  r64_init(c, EX, EX + R64_EX_CF, EX + R64_EX_CF + R64_ZR_CF);
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int sub = lane & 3, a = lane >> 2;
-  const int grp = warp * 4 + sub;            // row pair (row passes) / column (column passes)
-  const bool row_on = warp < 8;
-  // Column passes run on whole warps (the exchange inside the FFT synchronises the warp):
-  // the three lanes groups of warp 8 beyond column 32 compute on in-bounds scratch and
-  // only their global loads and shared-memory results are suppressed.
-  const bool col_warp = warp < 9;
-  const bool col_on = grp <= 32;
-  cf* exg = EX + grp * EX_GROUP_STRIDE;
-
-  const int b = blockIdx.x / C, c = blockIdx.x % C;
+  const int b = blockIdx.x / C, ch = blockIdx.x % C;
   constexpr int HW = 64 * 64;
+  const cf* khp = khat + (size_t)ch * (64 * 33) + (c.grp << 3) + c.a;
 
-  cf tw[8];
+  cf hst[8];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    float s, co;
-    sincospif(-(float)(a * k) / 32.0f, &s, &co);
-    tw[k] = mk(co, s);
-  }
+  for (int q = 0; q < 8; ++q) hst[q] = mk(0.f, 0.f);
 
-  cf kh[8], hst[8];
+  // x_main rows of step 0 (row lanes: rows 2*grp and 2*grp+1, columns a + 8m)
+  const int roff = (2 * c.grp) * 64 + c.a;
+  cf xr[8];
+  {
+    const float* r0 = xz + ((size_t)(b * T) * 2 * C + ch) * HW + roff;
 #pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    hst[q] = mk(0.f, 0.f);
-    kh[q] = col_on ? khat[(size_t)c * (64 * 33) + ((q * 33 + grp) << 3) + a] : mk(0.f, 0.f);
+    for (int m = 0; m < 8; ++m) xr[m] = c.row_on ? mk(r0[8 * m], r0[64 + 8 * m]) : mk(0.f, 0.f);
   }
 
   for (int t = 0; t < T; ++t) {
     const size_t frame = (size_t)(b * T + t);
-    float* xp = xz + (frame * 2 * C + c) * HW;
-    const float* zp = xz + (frame * 2 * C + C + c) * HW;
-    cf v[8];
+    float* xp = xz + (frame * 2 * C + ch) * HW;
+    const float* zp = xz + (frame * 2 * C + C + ch) * HW;
 
-    // ---- forward rows: two real rows as one complex FFT ----
-    if (row_on) {
-      const float* r0 = xp + (2 * grp) * 64 + a;
+    // ---- forward rows ----
+    if (c.row_on) {
+      fft64_lane8<false>(xr, c.tw, c.exg, c.a);
 #pragma unroll
-      for (int m = 0; m < 8; ++m) v[m] = mk(r0[8 * m], r0[64 + 8 * m]);
-      fft64_lane8<false>(v, tw, exg, a);
-#pragma unroll
-      for (int k2 = 0; k2 < 8; ++k2) ZR[grp * R64_ZR_STRIDE + a + 8 * k2] = v[k2];
+      for (int k2 = 0; k2 < 8; ++k2) c.ZR[c.grp * R64_ZRS + c.a + 8 * k2] = xr[k2];
     }
     __syncthreads();
 
     // ---- forward columns, recurrence, inverse columns ----
-    if (col_warp) {
-      const int par = a & 1, ph = a >> 1;
-      const int kneg = (64 - grp) & 63;
-#pragma unroll
-      for (int m = 0; m < 8; ++m) {
-        cf z1 = ZR[(ph + 4 * m) * R64_ZR_STRIDE + grp];
-        cf z2 = ZR[(ph + 4 * m) * R64_ZR_STRIDE + kneg];
-        v[m] = par ? mk(0.5f * (z1.y + z2.y), 0.5f * (z2.x - z1.x))
-                   : mk(0.5f * (z1.x + z2.x), 0.5f * (z1.y - z2.y));
-      }
-      fft64_lane8<false>(v, tw, exg, a);
-      const float4* gp = gates + frame * (64 * 33) + (grp << 3) + a;
+    if (c.col_warp) {
+      float4 g[8];
+      cf kh[8];
+      const float4* gp = gates + frame * (64 * 33) + (c.grp << 3) + c.a;
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         // {exp(-D), (D+1e-8)B, C/(HW), 1e-7(D+1e-8)}
-        const float4 g = col_on ? gp[q * (33 * 8)] : make_float4(0.f, 0.f, 0.f, 0.f);
-        cf A = mk(kh[q].x * g.x, kh[q].y * g.x);
-        cf U = mk(g.y * v[q].x, g.y * v[q].y);
-        if (U.x * U.x + U.y * U.y < g.w * g.w) U = mk(g.w, 0.f);
+        g[q] = c.col_on ? __ldg(gp + q * (33 * 8)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        kh[q] = c.col_on ? khp[q * (33 * 8)] : mk(0.f, 0.f);
+      }
+      cf v[8];
+      r64_col_fwd(c, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const cf A = mk(kh[q].x * g[q].x, kh[q].y * g[q].x);
+        cf U = mk(g[q].y * v[q].x, g[q].y * v[q].y);
+        if (U.x * U.x + U.y * U.y < g[q].w * g[q].w) U = mk(g[q].w, 0.f);
         cf h = cmul(A, hst[q]);
         h.x += U.x; h.y += U.y;
         hst[q] = h;
-        v[q] = mk(g.z * h.x, g.z * h.y);
+        v[q] = mk(g[q].z * h.x, g[q].z * h.y);
       }
-      fft64_lane8<true>(v, tw, exg, a);
-#pragma unroll
-      for (int n1 = 0; n1 < 8; ++n1)
-        if (col_on) GB[(a + 8 * n1) * R64_GB_STRIDE + grp] = v[n1];
+      r64_col_inv(c, v);
     }
     __syncthreads();
 
-    // ---- inverse rows (C2R, two rows per complex FFT), * silu(z), store ----
-    if (row_on) {
-      const cf* ge = GB + (2 * grp) * R64_GB_STRIDE;
-      const cf* go = ge + R64_GB_STRIDE;
+    // ---- inverse rows, * silu(z), store; prefetch the next step's rows ----
+    if (c.row_on) {
+      cf zr[8];
+      const float* z0 = zp + roff;
 #pragma unroll
-      for (int m = 0; m < 8; ++m) {
-        const int n = a + 8 * m;
-        const int k = n <= 32 ? n : 64 - n;
-        cf e = ge[k], o = go[k];
-        if (m == 0 || m == 4) {           // n = a or a + 32: DC / Nyquist when a == 0
-          if (a == 0) { e.y = 0.f; o.y = 0.f; }
-        }
-        v[m] = (n <= 32) ? mk(e.x - o.y, e.y + o.x) : mk(e.x + o.y, o.x - e.y);
+      for (int n1 = 0; n1 < 8; ++n1) zr[n1] = mk(z0[8 * n1], z0[64 + 8 * n1]);
+      if (t + 1 < T) {
+        const float* r0 = xp + (size_t)2 * C * HW + roff;
+#pragma unroll
+        for (int m = 0; m < 8; ++m) xr[m] = mk(r0[8 * m], r0[64 + 8 * m]);
       }
-      fft64_lane8<true>(v, tw, exg, a);
-      const float* z0 = zp + (2 * grp) * 64 + a;
-      float* y0 = xp + (2 * grp) * 64 + a;
+      cf v[8];
+      r64_row_inv(c, v);
+      float* y0 = xp + roff;
 #pragma unroll
       for (int n1 = 0; n1 < 8; ++n1) {
-        float ze = z0[8 * n1], zo = z0[64 + 8 * n1];
-        y0[8 * n1] = v[n1].x * silu_f(ze);
-        y0[64 + 8 * n1] = v[n1].y * silu_f(zo);
+        y0[8 * n1] = v[n1].x * silu_f(zr[n1].x);
+        y0[64 + 8 * n1] = v[n1].y * silu_f(zr[n1].y);
       }
     }
-    // The next iteration's first shared-memory writes (EX: warp-private; ZR: last read
-    // before the barrier above) cannot race with this iteration's GB reads, because GB is
-    // next written only after the next iteration's first barrier.
+    // No barrier needed here: the next iteration writes EX (warp-private) and ZR (last read
+    // before the second barrier above); GB is next written after the next first barrier.
   }
 }
 

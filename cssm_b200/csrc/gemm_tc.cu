@@ -2,13 +2,15 @@
 // (3 x TF32: A_hi*B_hi + A_lo*B_hi + A_hi*B_lo, accumulated in fp32 in TMEM).
 //
 // Persistent kernel, one CTA per SM, 288 threads, warp-specialised:
-//   warps 0-3  producers : read a 128-pixel A tile from global memory (channels-last rows with
-//                          RoPE fused, or planar planes with the RMSNorm/gate prologue fused),
-//                          split every value into tf32 hi + remainder, and write both into the
-//                          128-byte-swizzled K-major operand layout of a 2-stage ring;
-//   warp  4    MMA issuer: one lane issues 24 tcgen05.mma (M128 x N x K8) per tile into one of
+//   warps 0-7  producers : read a 128-pixel A tile from global memory (channels-last rows with
+//                          RoPE fused, loaded one tile ahead into registers so a whole tile is
+//                          in flight per SM; or planar planes with the RMSNorm/gate prologue
+//                          fused, 4 warps), split every value into tf32 hi + remainder, and
+//                          write both into the 128-byte-swizzled K-major operand layout of a
+//                          2-stage ring;
+//   warp  8    MMA issuer: one lane issues 24 tcgen05.mma (M128 x N x K8) per tile into one of
 //                          two TMEM accumulators and commits to mbarriers;
-//   warps 5-8  epilogue  : tcgen05.ld the accumulator (lane = pixel), add bias / activation,
+//   warps 9-12 epilogue  : tcgen05.ld the accumulator (lane = pixel), add bias / activation,
 //                          store planar (coalesced over pixels) or channels-last rows.
 // The weight tile (both halves of the split) is prepared once per CTA and stays in shared memory.
 // Every mbarrier wait is bounded; on expiry the kernel records an error code and winds down.
@@ -20,7 +22,8 @@ namespace cssm {
 
 __device__ int g_tc_error = 0;
 
-constexpr int TC_THREADS = 288;
+constexpr int TC_THREADS = 416;      // 8 producer warps, 1 MMA warp, 4 epilogue warps
+constexpr int TC_MMA_WARP = 8;
 constexpr int TC_BM = 128;
 constexpr int TC_K = 64;
 constexpr uint32_t TC_A_HALF = 2u * TC_BM * 128u;      // one of hi / lo: 2 K-blocks x 128 rows x 128 B
@@ -52,18 +55,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int NPROD = A_PLANAR ? 128 : 256;       // producer threads that arrive on `full`
   constexpr uint32_t TMEM_COLS = (2 * N <= 32) ? 32 : (2 * N <= 64) ? 64 : (2 * N <= 128) ? 128
                                  : (2 * N <= 256) ? 256 : 512;
 
   if (tid == 0) {
-    tc::mbar_init(&full[0], 128); tc::mbar_init(&full[1], 128);
+    tc::mbar_init(&full[0], NPROD); tc::mbar_init(&full[1], NPROD);
     tc::mbar_init(&empty[0], 1); tc::mbar_init(&empty[1], 1);
     tc::mbar_init(&accfull[0], 1); tc::mbar_init(&accfull[1], 1);
     tc::mbar_init(&accempty[0], 128); tc::mbar_init(&accempty[1], 128);
     tc::mbar_init(done, 1);
     tc::fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == TC_MMA_WARP) {
     tc::tmem_alloc(tmem_slot, TMEM_COLS);
     tc::tmem_relinquish();
   }
@@ -84,40 +88,68 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < 8 && tid < NPROD) {
     // ================================ producers ================================
     int it = 0;
+    // channels-last mode: thread owns 16-byte chunk (tid & 15) of rows (tid >> 4) + 16*r,
+    // r = 0..7; its registers always hold the NEXT tile's values.
+    float4 pre[8];
+    const int chunk = tid & 15, row0 = tid >> 4;
+    if (!A_PLANAR) {
+      const int m0 = blockIdx.x * TC_BM;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int m = m0 + row0 + 16 * r;
+        pre[r] = (blockIdx.x < num_tiles && m < g.M)
+                     ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int s = it & 1;
+      const int m0 = tile * TC_BM;
+      float4 cur[8];
+      if (!A_PLANAR) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) cur[r] = pre[r];
+        const int nt = tile + gridDim.x;
+        if (nt < num_tiles) {
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int m = nt * TC_BM + row0 + 16 * r;
+            pre[r] = m < g.M ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+      }
       if (!tc::mbar_wait(&empty[s], ((it >> 1) & 1) ^ 1)) { atomicExch(&g_tc_error, 1); break; }
       unsigned char* a_hi = smem + L::A_OFF + (uint32_t)s * 2u * TC_A_HALF;
       unsigned char* a_lo = a_hi + TC_A_HALF;
-      const int m0 = tile * TC_BM;
       if (!A_PLANAR) {
-#pragma unroll 4
-        for (int r = 0; r < 16; ++r) {
-          const int idx = r * 128 + tid;
-          const int row = idx >> 4, chunk = idx & 15;
-          const int m = m0 + row;
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (m < g.M) {
-            v = *reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4);
-            if (g.rope_t != nullptr) {
-              const int px = m % g.HW, fr = m / g.HW;
-              const int t = fr % g.T, h = px / g.W, w = px % g.W;
-              const int i = chunk * 2;
+        float2 ct0 = make_float2(1.f, 0.f), ct1 = ct0;
+        if (g.rope_t != nullptr) {
+          const int t = (m0 / g.HW) % g.T;
+          ct0 = g.rope_t[t * 32 + chunk * 2];
+          ct1 = g.rope_t[t * 32 + chunk * 2 + 1];
+        }
 #pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const float2 ct = g.rope_t[t * 32 + i + e];
-                const float2 ch = g.rope_h[h * 32 + i + e];
-                const float2 cw = g.rope_w[w * 32 + i + e];
-                const float cx = ct.x * ch.x - ct.y * ch.y, sx = ct.x * ch.y + ct.y * ch.x;
-                const float c2 = cx * cw.x - sx * cw.y, s2 = cx * cw.y + sx * cw.x;
-                float& xe = e ? v.z : v.x;
-                float& xo = e ? v.w : v.y;
-                const float ne = xe * c2 - xo * s2, no = xe * s2 + xo * c2;
-                xe = ne; xo = no;
-              }
+        for (int r = 0; r < 8; ++r) {
+          const int row = row0 + 16 * r;
+          float4 v = cur[r];
+          if (g.rope_t != nullptr) {
+            const int px = (m0 + row) % g.HW;
+            const int h = px / g.W, w = px % g.W;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float2 ct = e ? ct1 : ct0;
+              const float2 ch = g.rope_h[h * 32 + chunk * 2 + e];
+              const float2 cw = g.rope_w[w * 32 + chunk * 2 + e];
+              const float cx = ct.x * ch.x - ct.y * ch.y, sx = ct.x * ch.y + ct.y * ch.x;
+              const float c2 = cx * cw.x - sx * cw.y, s2 = cx * cw.y + sx * cw.x;
+              float& xe = e ? v.z : v.x;
+              float& xo = e ? v.w : v.y;
+              const float ne = xe * c2 - xo * s2, no = xe * s2 + xo * c2;
+              xe = ne; xo = no;
             }
           }
           float4 h4, l4;
@@ -166,7 +198,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       tc::fence_proxy_async();
       tc::mbar_arrive(&full[s]);
     }
-  } else if (warp == 4) {
+  } else if (warp == TC_MMA_WARP) {
     // ================================ MMA issuer ================================
     if (lane == 0) {
       const uint32_t idesc = tc::make_idesc_tf32(TC_BM, N);
@@ -203,7 +235,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       if (!tc::mbar_wait(done, 0) && ok) atomicExch(&g_tc_error, 3);
     }
     __syncwarp();
-  } else {
+  } else if (warp > TC_MMA_WARP) {
     // ================================ epilogue ================================
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
     const int row = q * 32 + lane;
@@ -251,7 +283,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == TC_MMA_WARP) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, TMEM_COLS);
   }

@@ -215,8 +215,164 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_kernel(const Stencil
   }
 }
 
+// Fast path of the plane stencil for 64x64 and 32x32 planes: float4 loads with the next
+// step's plane prefetched into registers, the temporal history in registers, the spatial
+// conv from a zero-haloed shared tile, per-step sums reduced once at the end.
+// NP = float4 groups per thread = H*W / 1024.
+template <int KSP, int KT, int NP>
+__global__ void __launch_bounds__(ST_THREADS) plane_stencil_fast_kernel(const StencilArgs s) {
+  extern __shared__ __align__(16) float sm[];
+  const int H = s.H, W = s.W, HW = H * W;
+  const int RS = W + 8;                              // tile row stride (4-float pad each side)
+  float* tile = sm;                                  // [(H+2)][RS], used when KSP > 0
+  float* red = sm + (KSP > 0 ? (H + 2) * RS : 0);    // [T][8] per-warp partial sums
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.x / s.C, c = blockIdx.x % s.C;
+  constexpr int NHIST = KT > 0 ? KT - 1 : 0;
+
+  float wsp[KSP * KSP > 0 ? KSP * KSP : 1];
+  if (KSP > 0) {
+#pragma unroll
+    for (int i = 0; i < KSP * KSP; ++i) wsp[i] = s.wsp[(size_t)i * s.C + c];
+  }
+  const float bsp = KSP > 0 ? s.bsp[c] : 0.f;
+  float wt[KT > 0 ? KT : 1];
+  if (KT > 0) {
+#pragma unroll
+    for (int j = 0; j < KT; ++j) wt[j] = s.wt[(size_t)j * s.C + c];
+  }
+  const float btv = KT > 0 ? s.bt[c] : 0.f;
+  if (KSP > 0) {
+    for (int i = tid; i < (H + 2) * RS; i += ST_THREADS) tile[i] = 0.f;
+  }
+  float4 hist[NP][NHIST > 0 ? NHIST : 1];
+#pragma unroll
+  for (int j = 0; j < NP; ++j)
+#pragma unroll
+    for (int k = 0; k < NHIST; ++k) hist[j][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  const size_t pstride = (size_t)s.planes_per_frame * HW;       // plane of the next frame
+  float* p0 = s.buf + ((size_t)(b * s.T) * s.planes_per_frame + s.plane0 + c) * HW;
+  float4 cur[NP], nxt[NP];
+#pragma unroll
+  for (int j = 0; j < NP; ++j) cur[j] = reinterpret_cast<const float4*>(p0)[tid + j * ST_THREADS];
+  __syncthreads();
+
+  for (int t = 0; t < s.T; ++t) {
+    float* p = p0 + (size_t)t * pstride;
+    if (t + 1 < s.T) {
+#pragma unroll
+      for (int j = 0; j < NP; ++j)
+        nxt[j] = reinterpret_cast<const float4*>(p + pstride)[tid + j * ST_THREADS];
+    }
+    if (KSP > 0) {
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const int g4 = tid + j * ST_THREADS;
+        const int h = (g4 * 4) / W, w0 = (g4 * 4) % W;
+        *reinterpret_cast<float4*>(tile + (h + 1) * RS + 4 + w0) = cur[j];
+      }
+      __syncthreads();
+    }
+    float lsum = 0.f;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      const int g4 = tid + j * ST_THREADS;
+      float4 v = cur[j];
+      if (KSP > 0) {
+        constexpr int LO = (KSP - 1) / 2;
+        const int h = (g4 * 4) / W, w0 = (g4 * 4) % W;
+        float a0 = bsp, a1 = bsp, a2 = bsp, a3 = bsp;
+#pragma unroll
+        for (int di = 0; di < KSP; ++di) {
+          const float* rp = tile + (h + 1 + di - LO) * RS + 4 + w0;
+          float win[4 + 2 * LO];
+          const float4 mid = *reinterpret_cast<const float4*>(rp);
+          win[LO] = mid.x; win[LO + 1] = mid.y; win[LO + 2] = mid.z; win[LO + 3] = mid.w;
+#pragma unroll
+          for (int e = 0; e < LO; ++e) { win[e] = rp[e - LO]; win[LO + 4 + e] = rp[4 + e]; }
+#pragma unroll
+          for (int dj = 0; dj < KSP; ++dj) {
+            const float wv = wsp[di * KSP + dj];
+            a0 = fmaf(wv, win[dj], a0); a1 = fmaf(wv, win[dj + 1], a1);
+            a2 = fmaf(wv, win[dj + 2], a2); a3 = fmaf(wv, win[dj + 3], a3);
+          }
+        }
+        v = make_float4(a0, a1, a2, a3);
+      }
+      float4 o = v;
+      if (KT > 0) {
+        o = make_float4(btv + wt[KT - 1] * v.x, btv + wt[KT - 1] * v.y, btv + wt[KT - 1] * v.z,
+                        btv + wt[KT - 1] * v.w);
+        // hist[j][k] holds s_{t-1-k}; tap index of s_{t-1-k} is KT-2-k
+#pragma unroll
+        for (int k = 0; k < NHIST; ++k) {
+          const float wv = wt[KT - 2 - k];
+          o.x = fmaf(wv, hist[j][k].x, o.x); o.y = fmaf(wv, hist[j][k].y, o.y);
+          o.z = fmaf(wv, hist[j][k].z, o.z); o.w = fmaf(wv, hist[j][k].w, o.w);
+        }
+#pragma unroll
+        for (int k = NHIST - 1; k > 0; --k) hist[j][k] = hist[j][k - 1];
+        if (NHIST > 0) hist[j][0] = v;
+      }
+      if (s.act) { o.x = silu_f(o.x); o.y = silu_f(o.y); o.z = silu_f(o.z); o.w = silu_f(o.w); }
+      if (s.post) {
+        const float* pp = s.post + ((size_t)(b * s.T + t) * HW + (size_t)g4 * 4) * s.post_stride + s.post_off;
+        o.x *= pp[0]; o.y *= pp[s.post_stride]; o.z *= pp[2 * s.post_stride]; o.w *= pp[3 * s.post_stride];
+      }
+      reinterpret_cast<float4*>(p)[g4] = o;
+      lsum += (o.x + o.y) + (o.z + o.w);
+    }
+    if (s.sums) {
+      for (int off = 16; off > 0; off >>= 1) lsum += __shfl_down_sync(0xffffffffu, lsum, off);
+      if (lane == 0) red[t * 8 + warp] = lsum;
+    }
+    if (KSP > 0) __syncthreads();      // all conv reads done before the tile is overwritten
+#pragma unroll
+    for (int j = 0; j < NP; ++j) cur[j] = nxt[j];
+  }
+  if (s.sums) {
+    __syncthreads();
+    for (int t = tid; t < s.T; t += ST_THREADS) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) tot += red[t * 8 + w];
+      s.sums[(size_t)(b * s.T + t) * s.C + c] = tot;
+    }
+  }
+}
+
+template <int KSP, int KT, int NP>
+static int launch_stencil_fast(const StencilArgs& s, cudaStream_t st) {
+  const size_t smem = ((KSP > 0 ? (size_t)(s.H + 2) * (s.W + 8) : 0) + (size_t)s.T * 8) * sizeof(float);
+  if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
+  cudaError_t e = cudaFuncSetAttribute(plane_stencil_fast_kernel<KSP, KT, NP>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  plane_stencil_fast_kernel<KSP, KT, NP><<<s.B * s.C, ST_THREADS, smem, st>>>(s);
+  return check_launch();
+}
+
+template <int NP>
+static int dispatch_stencil_fast(const StencilArgs& s, cudaStream_t st, bool* handled) {
+  *handled = true;
+  if (s.ksp == 3 && s.kt == 4) return launch_stencil_fast<3, 4, NP>(s, st);
+  if (s.ksp == 0 && s.kt == 4) return launch_stencil_fast<0, 4, NP>(s, st);
+  if (s.ksp == 3 && s.kt == 0) return launch_stencil_fast<3, 0, NP>(s, st);
+  if (s.ksp == 0 && s.kt == 0) return launch_stencil_fast<0, 0, NP>(s, st);
+  *handled = false;
+  return CSSM_OK;
+}
+
 int launch_plane_stencil(const StencilArgs& s, cudaStream_t st) {
   if (s.ksp > 7 || s.kt > 8) return CSSM_ERR_UNSUPPORTED;
+  if (s.W % 4 == 0 && (s.H * s.W == 4096 || s.H * s.W == 1024) &&
+      (reinterpret_cast<uintptr_t>(s.buf) & 15u) == 0) {
+    bool handled = false;
+    const int rc = s.H * s.W == 4096 ? dispatch_stencil_fast<4>(s, st, &handled)
+                                     : dispatch_stencil_fast<1>(s, st, &handled);
+    if (handled) return rc;
+  }
   const int nh = s.kt > 0 ? s.kt - 1 : 0;
   const size_t smem = (size_t)(1 + nh) * s.H * s.W * sizeof(float);
   if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
