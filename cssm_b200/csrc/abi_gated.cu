@@ -31,6 +31,7 @@ GatedPlan gated_plan_layout(const cssm_gated_desc& d) {
   p.rope_t = off; off += round_up((size_t)d.T * n2 * sizeof(float2), 256);
   p.rope_h = off; off += round_up((size_t)d.H * n2 * sizeof(float2), 256);
   p.rope_w = off; off += round_up((size_t)d.W * n2 * sizeof(float2), 256);
+  p.rope_nz = off; off += round_up(n2 * sizeof(float), 256);
   p.total = off;
   return p;
 }
@@ -138,8 +139,8 @@ int cssm_gated_plan_init(const cssm_gated_desc* d, const cssm_gated_weights* w, 
                   d->spectral_rho, 1, 1, spectral_path(d->H, d->W), st);
   if (s != CSSM_OK) return s;
   return launch_rope_tables((float2*)(base + p.rope_t), (float2*)(base + p.rope_h),
-                            (float2*)(base + p.rope_w), d->T, d->H, d->W, d->C, d->rope_mode,
-                            d->rope_base, st);
+                            (float2*)(base + p.rope_w), (float*)(base + p.rope_nz), d->T, d->H,
+                            d->W, d->C, d->rope_mode, d->rope_base, st);
 }
 
 int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
@@ -155,10 +156,12 @@ int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, co
   g.M = d->B * d->T * d->H * d->W; g.N = 2 * d->C; g.K = d->C; g.HW = d->H * d->W;
   g.A = x; g.Wk = w->in_proj_kernel; g.bias = w->in_proj_bias;
   g.out = xz; g.o_planes = 2 * d->C; g.o_plane0 = 0;
+  g.out_act = 1; g.act_n0 = d->C;          // the z planes are stored as silu(z)
   if (d->rope_mode != CSSM_ROPE_NONE) {
     g.rope_t = (const float2*)(base + p.rope_t);
     g.rope_h = (const float2*)(base + p.rope_h);
     g.rope_w = (const float2*)(base + p.rope_w);
+    g.rope_nz = (const float*)(base + p.rope_nz);
   }
   g.T = d->T; g.H = d->H; g.W = d->W;
   return launch_gemm<false, true>(g, (cudaStream_t)stream);

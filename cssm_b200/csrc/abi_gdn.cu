@@ -9,7 +9,7 @@ static SpectralPath gdn_path(const cssm_gdn_desc& d) {
   return (spectral_path(d.H, d.W) == PATH_R64 && d.delta_key_dim == 4) ? PATH_R64 : PATH_GENERIC;
 }
 
-struct GdnPlan { size_t what, rope_t, rope_h, rope_w, tcode, total; };
+struct GdnPlan { size_t what, rope_t, rope_h, rope_w, rope_nz, tcode, total; };
 static GdnPlan gdn_plan_layout(const cssm_gdn_desc& d) {
   GdnPlan p;
   const size_t Wf = d.W / 2 + 1, n2 = d.C / 2, nh = d.C / d.delta_key_dim;
@@ -18,6 +18,7 @@ static GdnPlan gdn_plan_layout(const cssm_gdn_desc& d) {
   p.rope_t = off; off += round_up((size_t)d.T * n2 * sizeof(float2), 256);
   p.rope_h = off; off += round_up((size_t)d.H * n2 * sizeof(float2), 256);
   p.rope_w = off; off += round_up((size_t)d.W * n2 * sizeof(float2), 256);
+  p.rope_nz = off; off += round_up(n2 * sizeof(float), 256);
   p.tcode = off;  off += round_up((size_t)d.T * d.C * sizeof(float), 256);
   p.total = off;
   return p;
@@ -98,8 +99,8 @@ int cssm_gdn_plan_init(const cssm_gdn_desc* d, const cssm_gdn_weights* w, void* 
                   d->W, d->spectral_rho, d->no_spectral_clamp ? 0 : 1, 0, gdn_path(*d), st);
   if (s != CSSM_OK) return s;
   s = launch_rope_tables((float2*)(base + p.rope_t), (float2*)(base + p.rope_h),
-                         (float2*)(base + p.rope_w), d->T, d->H, d->W, d->C, d->rope_mode,
-                         d->rope_base, st);
+                         (float2*)(base + p.rope_w), (float*)(base + p.rope_nz), d->T, d->H, d->W,
+                         d->C, d->rope_mode, d->rope_base, st);
   if (s != CSSM_OK) return s;
   return launch_tcode((float*)(base + p.tcode), d->T, d->C, d->rope_base, st);
 }
@@ -135,6 +136,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   const float2* rt = rope ? (const float2*)(pl + p.rope_t) : nullptr;
   const float2* rh = rope ? (const float2*)(pl + p.rope_h) : nullptr;
   const float2* rw = rope ? (const float2*)(pl + p.rope_w) : nullptr;
+  const float* rnz = rope ? (const float*)(pl + p.rope_nz) : nullptr;
   float* xdw = (float*)(ws + l.xdw);
   float* qkv = (float*)(ws + l.qkv);
   float* gate = (float*)(ws + l.gate);
@@ -157,13 +159,13 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   g.out = qkv; g.o_planes = 3 * C; g.o_plane0 = 0;
   g.T = d->T; g.H = d->H; g.W = d->W;
   if (d->qkv_conv_size > 1) { g.A = xdw; }
-  else { g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; }
+  else { g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz; }
   if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
   // 3. output gate projection of the rotated input -> planar, through SiLU / sigmoid
   memset(&g, 0, sizeof(g));
   g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
-  g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw;
+  g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
   g.Wk = w->gate_proj_kernel; g.bias = w->gate_proj_bias;
   g.out = gate; g.o_planes = C; g.o_plane0 = 0;
   g.T = d->T; g.H = d->H; g.W = d->W;

@@ -5,6 +5,10 @@
 #include <stddef.h>
 #include "../../include/cssm_b200.h"
 
+#ifndef CSSM_F32X2
+#define CSSM_F32X2 1
+#endif
+
 namespace cssm {
 
 struct __align__(8) cf {
@@ -12,8 +16,34 @@ struct __align__(8) cf {
 };
 
 __device__ __forceinline__ cf mk(float x, float y) { cf r; r.x = x; r.y = y; return r; }
-__device__ __forceinline__ cf operator+(cf a, cf b) { return mk(a.x + b.x, a.y + b.y); }
-__device__ __forceinline__ cf operator-(cf a, cf b) { return mk(a.x - b.x, a.y - b.y); }
+// Complex add / subtract as one packed fp32x2 instruction (sm_100): halves the issue slots of
+// the FFT butterflies, which are mostly complex additions.
+__device__ __forceinline__ cf operator+(cf a, cf b) {
+#if CSSM_F32X2
+  unsigned long long pa, pb, pr;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(pa), "l"(pb));
+  cf r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(pr));
+  return r;
+#else
+  return mk(a.x + b.x, a.y + b.y);
+#endif
+}
+__device__ __forceinline__ cf operator-(cf a, cf b) {
+#if CSSM_F32X2
+  unsigned long long pa, pb, pr;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pb) : "f"(b.x), "f"(b.y));
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(pa), "l"(pb));
+  cf r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(pr));
+  return r;
+#else
+  return mk(a.x - b.x, a.y - b.y);
+#endif
+}
 __device__ __forceinline__ cf cmul(cf a, cf b) {
   return mk(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
@@ -37,6 +67,7 @@ struct GatedPlan {
   size_t rope_t;   // float2 [T][C/2]  (cos, sin)
   size_t rope_h;   // float2 [H][C/2]
   size_t rope_w;   // float2 [W][C/2]
+  size_t rope_nz;  // float  [C/2]  1 = pair rotated on some axis, 0 = angle identically zero
   size_t total;
 };
 GatedPlan gated_plan_layout(const cssm_gated_desc& d);

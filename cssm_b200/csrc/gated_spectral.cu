@@ -1,5 +1,6 @@
 // Fused spectral kernels of the gated block: rfft2 -> gated complex recurrence over T with
-// the state on chip -> irfft2 -> * silu(z).  One CTA per (batch, channel) pair.
+// the state on chip -> irfft2 -> * silu(z) (in_proj already stored the z planes through SiLU).
+// One CTA per (batch, channel) pair.
 #include "r64.cuh"
 #include "kernels.cuh"
 
@@ -94,8 +95,8 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       float* y0 = xp + roff;
 #pragma unroll
       for (int n1 = 0; n1 < 8; ++n1) {
-        y0[8 * n1] = v[n1].x * silu_f(zr[n1].x);
-        y0[64 + 8 * n1] = v[n1].y * silu_f(zr[n1].y);
+        y0[8 * n1] = v[n1].x * zr[n1].x;
+        y0[64 + 8 * n1] = v[n1].y * zr[n1].y;
       }
     }
     // No barrier needed here: the next iteration writes EX (warp-private) and ZR (last read
@@ -205,7 +206,7 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
         s2 += r[k].x * e.x + r[k].y * e.y;
       }
       acc += 2.f * s2;
-      xp[o] = acc * silu_f(zp[o]);
+      xp[o] = acc * zp[o];
     }
   }
 }

@@ -19,12 +19,14 @@ struct GemmArgs {
   int o_planes, o_plane0;
   // RoPE on a channels-last A (nullptr = off): float2 (cos, sin) tables
   const float2* rope_t; const float2* rope_h; const float2* rope_w;
+  const float* rope_nz;     // (K/2) 1 = pair is rotated, 0 = identity (may be nullptr: rotate all)
   int T, H, W;
   // planar-A prologue of the GDN output: a <- a * rsqrt(mean_k a^2 + eps) * scale[k] * gate
   const float* rms_scale;   // (K) or nullptr (no normalisation)
   const float* gate;        // planar, plane (frame*g_planes + g_plane0 + k), or nullptr
   int g_planes, g_plane0;
-  int out_act;              // 0 none, 1 silu, 2 sigmoid
+  int out_act;              // 0 none, 1 silu, 2 sigmoid; applied to output columns n >= act_n0
+  int act_n0;
 };
 
 constexpr int GEMM_BM = 128, GEMM_BK = 16, GEMM_THREADS = 256;
@@ -152,8 +154,10 @@ gemm_simt_kernel(const GemmArgs g) {
       const int n = n0 + (j < 4 ? tn * 4 + j : BN / 2 + tn * 4 + (j - 4));
       if (n >= g.N) continue;
       float v = acc[i][j] + (g.bias ? g.bias[n] : 0.f);
-      if (g.out_act == 1) v = silu_f(v);
-      else if (g.out_act == 2) v = sigmoid_f(v);
+      if (n >= g.act_n0) {
+        if (g.out_act == 1) v = silu_f(v);
+        else if (g.out_act == 2) v = sigmoid_f(v);
+      }
       if (O_PLANAR) g.out[((size_t)fr * g.o_planes + g.o_plane0 + n) * g.HW + px] = v;
       else g.out[(size_t)m * g.N + n] = v;
     }

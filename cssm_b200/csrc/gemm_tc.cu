@@ -5,7 +5,7 @@
 //   warps 0-7  producers : read a 128-pixel A tile from global memory (channels-last rows with
 //                          RoPE fused, loaded one tile ahead into registers so a whole tile is
 //                          in flight per SM; or planar planes with the RMSNorm/gate prologue
-//                          fused, 4 warps), split every value into tf32 hi + remainder, and
+//                          fused), split every value into tf32 hi + remainder, and
 //                          write both into the 128-byte-swizzled K-major operand layout of a
 //                          2-stage ring;
 //   warp  8    MMA issuer: one lane issues 24 tcgen05.mma (M128 x N x K8) per tile into one of
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr int NPROD = A_PLANAR ? 128 : 256;       // producer threads that arrive on `full`
+  constexpr int NPROD = 256;                        // producer threads that arrive on `full`
   constexpr uint32_t TMEM_COLS = (2 * N <= 32) ? 32 : (2 * N <= 64) ? 64 : (2 * N <= 128) ? 128
                                  : (2 * N <= 256) ? 256 : 512;
 
@@ -91,20 +91,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
   if (warp < 8 && tid < NPROD) {
     // ================================ producers ================================
     int it = 0;
-    // channels-last mode: thread owns 16-byte chunk (tid & 15) of rows (tid >> 4) + 16*r,
-    // r = 0..7; its registers always hold the NEXT tile's values.
+    // channels-last mode: warp w owns the 16-byte chunks 2w and 2w+1 (channel pairs 4w..4w+3)
+    // of every row, lane = (row & 15) * 2 + (chunk & 1); rows rsub + 16*r, r = 0..7.  All lanes
+    // of a warp rotate (or skip) the same channel pairs, and a load instruction still touches
+    // whole 32-byte sectors.  The registers `pre` always hold the NEXT tile's values.
     float4 pre[8];
-    const int chunk = tid & 15, row0 = tid >> 4;
+    const int chunk = 2 * warp + (lane & 1), rsub = lane >> 1;
+    bool rot = false;
     if (!A_PLANAR) {
       const int m0 = blockIdx.x * TC_BM;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const int m = m0 + row0 + 16 * r;
+        const int m = m0 + rsub + 16 * r;
         pre[r] = (blockIdx.x < num_tiles && m < g.M)
                      ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
                      : make_float4(0.f, 0.f, 0.f, 0.f);
       }
+      if (g.rope_t != nullptr) {
+        // warp-uniform: does any of the warp's four channel pairs rotate at all?
+        rot = g.rope_nz == nullptr;
+        if (!rot)
+          for (int e = 0; e < 4; ++e) rot = rot || g.rope_nz[4 * warp + e] != 0.f;
+      }
     }
+    const float invW = 1.0f / (float)g.W;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int s = it & 1;
       const int m0 = tile * TC_BM;
@@ -116,7 +126,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
         if (nt < num_tiles) {
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
-            const int m = nt * TC_BM + row0 + 16 * r;
+            const int m = nt * TC_BM + rsub + 16 * r;
             pre[r] = m < g.M ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
                              : make_float4(0.f, 0.f, 0.f, 0.f);
           }
@@ -127,18 +137,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       unsigned char* a_lo = a_hi + TC_A_HALF;
       if (!A_PLANAR) {
         float2 ct0 = make_float2(1.f, 0.f), ct1 = ct0;
-        if (g.rope_t != nullptr) {
-          const int t = (m0 / g.HW) % g.T;
+        int px0 = 0;
+        if (rot) {
+          const int fr = m0 / g.HW;
+          px0 = m0 - fr * g.HW;
+          const int t = fr % g.T;
           ct0 = g.rope_t[t * 32 + chunk * 2];
           ct1 = g.rope_t[t * 32 + chunk * 2 + 1];
         }
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-          const int row = row0 + 16 * r;
+          const int row = rsub + 16 * r;
           float4 v = cur[r];
-          if (g.rope_t != nullptr) {
-            const int px = (m0 + row) % g.HW;
-            const int h = px / g.W, w = px % g.W;
+          if (rot) {
+            const int px = px0 + row;
+            const int h = (int)(((float)px + 0.5f) * invW);     // exact for px < 2^22
+            const int w = px - h * g.W;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const float2 ct = e ? ct1 : ct0;
@@ -160,37 +174,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
           *reinterpret_cast<float4*>(a_lo + off) = l4;
         }
       } else {
-        // thread = pixel row; planes are contiguous over pixels, so each k is a coalesced read
-        const int row = tid, m = m0 + row;
-        float v[TC_K];
+        // thread = (pixel row, K half); planes are contiguous over pixels, so each k is a
+        // coalesced read across the lanes of a warp
+        const int row = tid & 127, kh = tid >> 7, m = m0 + row;
+        float v[32];
         if (m < g.M) {
-          const int fr = m / g.HW, px = m % g.HW;
-          const float* ap = g.A + ((size_t)fr * g.a_planes + g.a_plane0) * g.HW + px;
+          const int fr = m / g.HW, px = m - fr * g.HW;
+          const float* ap = g.A + ((size_t)fr * g.a_planes + g.a_plane0 + kh * 32) * g.HW + px;
 #pragma unroll
-          for (int k = 0; k < TC_K; ++k) v[k] = ap[(size_t)k * g.HW];
+          for (int k = 0; k < 32; ++k) v[k] = ap[(size_t)k * g.HW];
           if (g.rms_scale != nullptr) {
+            // the other K half of the row is re-read (cache hit: the partner thread loads it)
+            const float* op = g.A + ((size_t)fr * g.a_planes + g.a_plane0 + (1 - kh) * 32) * g.HW + px;
             float ss = 0.f;
 #pragma unroll
-            for (int k = 0; k < TC_K; ++k) ss = fmaf(v[k], v[k], ss);
+            for (int k = 0; k < 32; ++k) { const float o = op[(size_t)k * g.HW]; ss = fmaf(o, o, ss); }
+#pragma unroll
+            for (int k = 0; k < 32; ++k) ss = fmaf(v[k], v[k], ss);
             const float rinv = rsqrtf(ss * (1.0f / TC_K) + 1e-6f);
 #pragma unroll
-            for (int k = 0; k < TC_K; ++k) v[k] *= rinv * g.rms_scale[k];
+            for (int k = 0; k < 32; ++k) v[k] *= rinv * g.rms_scale[kh * 32 + k];
           }
           if (g.gate != nullptr) {
-            const float* gp = g.gate + ((size_t)fr * g.g_planes + g.g_plane0) * g.HW + px;
+            const float* gp = g.gate + ((size_t)fr * g.g_planes + g.g_plane0 + kh * 32) * g.HW + px;
 #pragma unroll
-            for (int k = 0; k < TC_K; ++k) v[k] *= gp[(size_t)k * g.HW];
+            for (int k = 0; k < 32; ++k) v[k] *= gp[(size_t)k * g.HW];
           }
         } else {
 #pragma unroll
-          for (int k = 0; k < TC_K; ++k) v[k] = 0.f;
+          for (int k = 0; k < 32; ++k) v[k] = 0.f;
         }
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           float4 h4, l4;
           tc::split_tf32(v[4 * c + 0], h4.x, l4.x); tc::split_tf32(v[4 * c + 1], h4.y, l4.y);
           tc::split_tf32(v[4 * c + 2], h4.z, l4.z); tc::split_tf32(v[4 * c + 3], h4.w, l4.w);
-          const uint32_t off = (uint32_t)(c >> 3) * (TC_BM * 128u) + tc::sw128_offset(row, c & 7);
+          const uint32_t off = (uint32_t)kh * (TC_BM * 128u) + tc::sw128_offset(row, c);
           *reinterpret_cast<float4*>(a_hi + off) = h4;
           *reinterpret_cast<float4*>(a_lo + off) = l4;
         }
@@ -254,14 +273,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
         if (m < g.M) {
           if (!A_PLANAR) {
             // planar output: lanes = consecutive pixels -> 128-byte coalesced stores per column
-            const int fr = m / g.HW, px = m % g.HW;
+            const int fr = m / g.HW, px = m - fr * g.HW;
             float* op = g.out + ((size_t)fr * g.o_planes + g.o_plane0 + cc * 32) * g.HW + px;
+            const float* bs = bias_s + cc * 32;
+            if (g.out_act == 0 || cc * 32 < g.act_n0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float v = __uint_as_float(r[j]) + bias_s[cc * 32 + j];
-              if (g.out_act == 1) v = silu_f(v);
-              else if (g.out_act == 2) v = sigmoid_f(v);
-              op[(size_t)j * g.HW] = v;
+              for (int j = 0; j < 32; ++j) { *op = __uint_as_float(r[j]) + bs[j]; op += g.HW; }
+            } else if (g.out_act == 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) { *op = silu_f(__uint_as_float(r[j]) + bs[j]); op += g.HW; }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) { *op = sigmoid_f(__uint_as_float(r[j]) + bs[j]); op += g.HW; }
             }
           } else {
             float* op = g.out + (size_t)m * g.N + cc * 32;
@@ -297,6 +320,7 @@ bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
   if (g_force_simt) return false;
   if (g.K != TC_K || (g.N != 64 && g.N != 128)) return false;
   if (g.HW % TC_BM != 0 || g.M % TC_BM != 0) return false;
+  if (g.out_act != 0 && g.act_n0 % 32 != 0) return false;
   if (!a_planar && g.rope_t != nullptr && g.K != 64) return false;
   return true;
 }

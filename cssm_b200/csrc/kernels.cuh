@@ -7,8 +7,8 @@ namespace cssm {
 
 int launch_khat(const float* k, cf* out, int nch, int ks, int H, int W, float rho, int squash,
                 int floor_eps, int path, cudaStream_t st);
-int launch_rope_tables(float2* tt, float2* th, float2* tw, int T, int H, int W, int C, int mode,
-                       float base, cudaStream_t st);
+int launch_rope_tables(float2* tt, float2* th, float2* tw, float* nz, int T, int H, int W, int C,
+                       int mode, float base, cudaStream_t st);
 int launch_tcode(float* out, int T, int C, float base, cudaStream_t st);
 
 struct StencilArgs {

@@ -85,11 +85,18 @@ __device__ double rope_freq(int axis, int i, int n, int mode, double base, int C
   return 0.0;
 }
 
-__global__ void rope_table_kernel(float2* tt, float2* th, float2* tw, int T, int H, int W, int C,
-                                  int mode, float base) {
+__global__ void rope_table_kernel(float2* tt, float2* th, float2* tw, float* nz, int T, int H,
+                                  int W, int C, int mode, float base) {
   const int n = C / 2;
   const int total = (T + H + W) * n;
   const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o < n) {
+    // 1 where the pair is rotated on some axis, 0 where its angle is identically zero
+    const bool any = rope_freq(0, o, n, mode, (double)base, C) != 0.0 ||
+                     rope_freq(1, o, n, mode, (double)base, C) != 0.0 ||
+                     rope_freq(2, o, n, mode, (double)base, C) != 0.0;
+    nz[o] = any ? 1.f : 0.f;
+  }
   if (o >= total) return;
   int pos = o / n, i = o % n, axis = 0;
   float2* dst = tt;
@@ -99,10 +106,10 @@ __global__ void rope_table_kernel(float2* tt, float2* th, float2* tw, int T, int
   dst[pos * n + i] = make_float2((float)cos(ang), (float)sin(ang));
 }
 
-int launch_rope_tables(float2* tt, float2* th, float2* tw, int T, int H, int W, int C, int mode,
-                       float base, cudaStream_t st) {
+int launch_rope_tables(float2* tt, float2* th, float2* tw, float* nz, int T, int H, int W, int C,
+                       int mode, float base, cudaStream_t st) {
   const int total = (T + H + W) * (C / 2);
-  rope_table_kernel<<<(total + 127) / 128, 128, 0, st>>>(tt, th, tw, T, H, W, C, mode, base);
+  rope_table_kernel<<<(total + 127) / 128, 128, 0, st>>>(tt, th, tw, nz, T, H, W, C, mode, base);
   return check_launch();
 }
 
@@ -254,8 +261,18 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_fast_kernel(const St
   const size_t pstride = (size_t)s.planes_per_frame * HW;       // plane of the next frame
   float* p0 = s.buf + ((size_t)(b * s.T) * s.planes_per_frame + s.plane0 + c) * HW;
   float4 cur[NP], nxt[NP];
+  int toff[NP];                    // tile offset of the thread's group j (interior origin)
+  const int gpr = W >> 2;          // float4 groups per image row; lanes are consecutive groups
+  bool left_edge[NP], right_edge[NP];
 #pragma unroll
-  for (int j = 0; j < NP; ++j) cur[j] = reinterpret_cast<const float4*>(p0)[tid + j * ST_THREADS];
+  for (int j = 0; j < NP; ++j) {
+    const int g4 = tid + j * ST_THREADS;
+    cur[j] = reinterpret_cast<const float4*>(p0)[g4];
+    const int h = g4 / gpr, gc = g4 - h * gpr;
+    toff[j] = (h + 1) * RS + 4 + gc * 4;
+    left_edge[j] = gc == 0 || lane == 0;
+    right_edge[j] = gc == gpr - 1 || lane == 31;
+  }
   __syncthreads();
 
   for (int t = 0; t < s.T; ++t) {
@@ -267,11 +284,7 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_fast_kernel(const St
     }
     if (KSP > 0) {
 #pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        const int g4 = tid + j * ST_THREADS;
-        const int h = (g4 * 4) / W, w0 = (g4 * 4) % W;
-        *reinterpret_cast<float4*>(tile + (h + 1) * RS + 4 + w0) = cur[j];
-      }
+      for (int j = 0; j < NP; ++j) *reinterpret_cast<float4*>(tile + toff[j]) = cur[j];
       __syncthreads();
     }
     float lsum = 0.f;
@@ -279,13 +292,31 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_fast_kernel(const St
     for (int j = 0; j < NP; ++j) {
       const int g4 = tid + j * ST_THREADS;
       float4 v = cur[j];
-      if (KSP > 0) {
+      if (KSP == 3) {
+        // 3x3: the row's float4 from the tile, its left / right neighbours from the adjacent
+        // lanes (adjacent float4 groups of the same image row) or from the zero halo
+        float a0 = bsp, a1 = bsp, a2 = bsp, a3 = bsp;
+#pragma unroll
+        for (int di = 0; di < 3; ++di) {
+          const float* rp = tile + toff[j] + (di - 1) * RS;
+          const float4 mid = *reinterpret_cast<const float4*>(rp);
+          float lf = __shfl_up_sync(0xffffffffu, mid.w, 1);
+          float rt = __shfl_down_sync(0xffffffffu, mid.x, 1);
+          if (left_edge[j]) lf = rp[-1];
+          if (right_edge[j]) rt = rp[4];
+          const float w0 = wsp[di * 3], w1 = wsp[di * 3 + 1], w2 = wsp[di * 3 + 2];
+          a0 = fmaf(w0, lf, a0);    a0 = fmaf(w1, mid.x, a0); a0 = fmaf(w2, mid.y, a0);
+          a1 = fmaf(w0, mid.x, a1); a1 = fmaf(w1, mid.y, a1); a1 = fmaf(w2, mid.z, a1);
+          a2 = fmaf(w0, mid.y, a2); a2 = fmaf(w1, mid.z, a2); a2 = fmaf(w2, mid.w, a2);
+          a3 = fmaf(w0, mid.z, a3); a3 = fmaf(w1, mid.w, a3); a3 = fmaf(w2, rt, a3);
+        }
+        v = make_float4(a0, a1, a2, a3);
+      } else if (KSP > 0) {
         constexpr int LO = (KSP - 1) / 2;
-        const int h = (g4 * 4) / W, w0 = (g4 * 4) % W;
         float a0 = bsp, a1 = bsp, a2 = bsp, a3 = bsp;
 #pragma unroll
         for (int di = 0; di < KSP; ++di) {
-          const float* rp = tile + (h + 1 + di - LO) * RS + 4 + w0;
+          const float* rp = tile + toff[j] + (di - LO) * RS;
           float win[4 + 2 * LO];
           const float4 mid = *reinterpret_cast<const float4*>(rp);
           win[LO] = mid.x; win[LO + 1] = mid.y; win[LO + 2] = mid.z; win[LO + 3] = mid.w;

@@ -28,9 +28,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: gives up after `limit` polls and returns false (the caller records an error
 // and leaves its loop; nothing in this library spins without a limit).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 24) {
-  for (uint32_t i = 0; i < limit; ++i)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 22) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (i > 4) __nanosleep(64);      // leave the issue slots to the warps that have work
+  }
   return false;
 }
 __device__ __forceinline__ void fence_mbar_init() {

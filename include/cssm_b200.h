@@ -120,7 +120,8 @@ int cssm_gated_forward_host(const cssm_gated_desc* d, const cssm_gated_weights* 
 /* ---- stages of the gated block, exposed for tests, profiling and partial drop-in ---- */
 
 /* RoPE + in_proj: xz[(bt*2C + n)*H*W + hw] = sum_c rope(x)[bt,hw,c] * Wk[c,n] + b[n].
- * Planes 0..C-1 of each frame are x_main, C..2C-1 are z.  cssm.py:462-463, 480-484. */
+ * Planes 0..C-1 of each frame are x_main; planes C..2C-1 hold silu(z) (the SiLU of the
+ * output gate, cssm.py:581, is applied where z is produced).  cssm.py:462-463, 480-484. */
 int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w,
                        const void* plan, const float* x, float* xz_planar, void* stream);
 
@@ -137,7 +138,7 @@ int cssm_gated_gates(const cssm_gated_desc* d, const cssm_gated_weights* w,
                      const float* ctx_sum, float* gate_maps, void* stream);
 
 /* Fused spectral kernel: for each (b,c): for t: rfft2(x_main[b,t,c]),
- * h = K_hat*exp(-Delta)*h + (Delta+1e-8)*floor(B*X), y = irfft2(C*h) * silu(z[b,t,c]);
+ * h = K_hat*exp(-Delta)*h + (Delta+1e-8)*floor(B*X), y = irfft2(C*h) * (stored silu(z))[b,t,c];
  * y overwrites the x_main plane.  The state h never leaves the SM.
  * Replaces cssm.py:532-533, 558-581 (rfft2, to_goom, associative_scan of
  * math.py:24-54, from_goom, irfft2, SiLU gate) and the existing scan seam

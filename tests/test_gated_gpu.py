@@ -57,7 +57,7 @@ def test_stage_parity(case):
     x_main = xz[:, :, :C].transpose(0, 1, 3, 4, 2)
     z = xz[:, :, C:].transpose(0, 1, 3, 4, 2)
     assert orc.rel_l2(x_main, inter["x_main"]) <= 1e-5
-    assert orc.rel_l2(z, inter["z"]) <= 1e-5
+    assert orc.rel_l2(z, orc.silu(inter["z"])) <= 1e-5      # z planes are stored through SiLU
     ctx = st["ctx_sum"].cpu().numpy().reshape(B, T, C) / (H * W)
     assert orc.rel_l2(ctx, inter["ctx"]) <= 1e-5
     st = bound.stages(xd, upto="spectral")
@@ -158,4 +158,4 @@ def test_tensor_core_projections_c64(rope):
     assert orc.rel_l2(y_tc, y_simt) <= 2e-6
     # stage level: the planar x_main / z planes straight out of in_proj
     z = xz[:, :, C:].transpose(0, 1, 3, 4, 2)
-    assert orc.rel_l2(z, inter["z"]) <= 2e-6
+    assert orc.rel_l2(z, orc.silu(inter["z"])) <= 2e-6
