@@ -30,8 +30,94 @@ WORKLOADS = {
     # small case for profiler captures (activations 134 MB > L2, < 1 GB on the device)
     "cfg2_small": dict(B=16, T=8, H=64, W=64, C=64, kernel_size=11, gate_type="factored",
                        rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
+    # BASELINE.json configs[2]: GDN-SCSSM, ks 11, qkv_conv 5, d_k 4, T=8, C=64, RMSNorm, mrope
+    "cfg3": dict(block="gdn", B=128, T=8, H=64, W=64, C=64, kernel_size=11, gate_type="factored",
+                 rope_mode="mrope", short_conv_size=4, qkv_conv_size=5, delta_key_dim=4),
+    "cfg3_small": dict(block="gdn", B=8, T=8, H=64, W=64, C=64, kernel_size=11,
+                       gate_type="factored", rope_mode="mrope", short_conv_size=4, qkv_conv_size=5,
+                       delta_key_dim=4),
+    # BASELINE.json configs[3]: GDN-SCSSM video, T=32, 32x32 block input, qkv_conv 1
+    "cfg4": dict(block="gdn", B=128, T=32, H=32, W=32, C=64, kernel_size=11, gate_type="factored",
+                 rope_mode="spatiotemporal", short_conv_size=4, qkv_conv_size=1, delta_key_dim=4),
 }
 METRIC = "fwd images/s (gated spectral block, cfg2)"
+GDN_STAGES = ["dwconv_ctx", "qkv_proj", "gate_proj", "gates", "short_convs", "spectral", "out_proj"]
+
+
+def run_gdn(args, cfg, rank, world, local):
+    """GDN block workloads (not the headline metric): whole-block throughput, per-stage CUDA-event
+    times through the library's stage-event hook, roofline of the fused GDN spectral kernel
+    (20*C*H*W algorithmic bytes per (b,t): read q,k,v and gate, write o)."""
+    import ctypes as C
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from cssm_b200 import GatedDeltaNetCSSM, shard
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, T, H, W, Cc = cfg["B"], cfg["T"], cfg["H"], cfg["W"], cfg["C"]
+    mod = GatedDeltaNetCSSM(channels=Cc, delta_key_dim=cfg["delta_key_dim"],
+                            kernel_size=cfg["kernel_size"], rope_mode=cfg["rope_mode"],
+                            gate_type=cfg["gate_type"], short_conv_size=cfg["short_conv_size"],
+                            qkv_conv_size=cfg["qkv_conv_size"])
+    bound = mod.bind(mod.init(0, (B, T, H, W, Cc)), dev)
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    x = torch.randn(B, T, H, W, Cc, generator=g).to(dev)
+    y = torch.empty_like(x)
+    st = torch.cuda.current_stream(dev)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(8)]
+    for _ in range(args.warmup):
+        bound(x, out=y)
+    torch.cuda.synchronize(dev)
+    # stage events: raw cudaEvent_t handles of torch events (created on first record)
+    for e in evs:
+        e.record(st)
+    torch.cuda.synchronize(dev)
+    arr = (C.c_void_p * 8)(*[e.cuda_event for e in evs])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stage_ms = {n: 0.0 for n in GDN_STAGES}
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    with ClockSampler(local) as clk:
+        e0.record(st)
+        for k in range(args.steps):
+            if k == args.steps - 1:
+                bound.L.cssm_debug_gdn_stage_events(arr)
+            bound(x, out=y)
+        bound.L.cssm_debug_gdn_stage_events(None)
+        e1.record(st)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+    for i, n in enumerate(GDN_STAGES):
+        stage_ms[n] = evs[i].elapsed_time(evs[i + 1])
+    total_ms = shard.max_over_ranks(e0.elapsed_time(e1), dev)
+    peak, peak_src = peaks()
+    alg = 20.0 * Cc * H * W * B * T
+    ach = alg / (stage_ms["spectral"] / 1e3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": f"fwd images/s (GDN spectral block, {args.workload})",
+            "value": world * B * args.steps / (total_ms / 1e3), "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "block": "GatedDeltaNetCSSM", "per_gpu_batch": B,
+                       "T": T, "H": H, "W": W, "C": Cc, "delta_key_dim": cfg["delta_key_dim"],
+                       "l2": "inputs larger than the 126 MB L2"},
+            "stage_ms": stage_ms,
+            "roofline": {"bound": "hbm", "kernel": "gdn_spectral", "achieved": ach, "peak": peak,
+                         "peak_source": peak_src, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "algorithmic_bytes_per_launch": alg, "ms_per_launch": stage_ms["spectral"]},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": 9 * args.steps,
+            "clocks": clk.summary(),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def peaks():
@@ -157,6 +243,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: cssm_b200 has no CPU path")
+    if cfg.get("block") == "gdn":
+        run_gdn(args, cfg, rank, world, local)
+        return
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:

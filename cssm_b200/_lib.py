@@ -88,6 +88,7 @@ SIGNATURES = {
                                    C.c_size_t, _P]),
     "cssm_debug_set_gemm_backend": (C.c_int, [C.c_int]),
     "cssm_debug_tc_error": (C.c_int, [C.POINTER(C.c_int)]),
+    "cssm_debug_gdn_stage_events": (C.c_int, [C.POINTER(C.c_void_p)]),
     "cssm_static_scratch_bytes": (C.c_size_t, []),
     "cssm_gated_forward_static": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
                                             _P, _P]),

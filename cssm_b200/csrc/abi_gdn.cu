@@ -67,6 +67,13 @@ static int gdn_validate(const cssm_gdn_desc* d) {
   return CSSM_OK;
 }
 
+// Optional per-stage timing hook (diagnostics): when set, cssm_gdn_forward records
+// events[i] on its stream before stage i (i = 0..6) and events[7] after the last stage.
+static thread_local cudaEvent_t* g_stage_events = nullptr;
+static inline void mark(int i, cudaStream_t st) {
+  if (g_stage_events != nullptr && g_stage_events[i] != nullptr) cudaEventRecord(g_stage_events[i], st);
+}
+
 }  // namespace cssm
 
 using namespace cssm;
@@ -142,6 +149,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   float* gate = (float*)(ws + l.gate);
 
   // 1. RoPE + depthwise conv (channels-last) and the context row sums of the rotated input
+  mark(0, st);
   GdnDwArgs dw;
   memset(&dw, 0, sizeof(dw));
   dw.x = x; dw.out = d->qkv_conv_size > 1 ? xdw : nullptr;
@@ -152,6 +160,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   if ((s = launch_rope_dwconv_cl(dw, st)) != CSSM_OK) return s;
 
   // 2. qkv projection -> planar (BT, 3C, H, W)
+  mark(1, st);
   GemmArgs g;
   memset(&g, 0, sizeof(g));
   g.M = BT * HW; g.N = 3 * C; g.K = C; g.HW = HW;
@@ -163,6 +172,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
   // 3. output gate projection of the rotated input -> planar, through SiLU / sigmoid
+  mark(2, st);
   memset(&g, 0, sizeof(g));
   g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
   g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
@@ -173,6 +183,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
   // 4. gate maps
+  mark(3, st);
   GdnGateArgs ga;
   memset(&ga, 0, sizeof(ga));
   ga.ctx_part = dw.ctx_part; ga.tcode = (const float*)(pl + p.tcode);
@@ -183,6 +194,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   if ((s = launch_gdn_gates(ga, st)) != CSSM_OK) return s;
 
   // 5. causal temporal conv + SiLU on q, k, v planes, input gates on k and v
+  mark(4, st);
   for (int i = 0; i < 3; ++i) {
     const bool has_post = d->use_input_gates && i > 0;
     if (d->short_conv_size == 0 && !has_post) continue;
@@ -198,6 +210,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   }
 
   // 6. fused spectral recurrence; the output planes overwrite the v planes
+  mark(5, st);
   GdnSpectralArgs sp;
   memset(&sp, 0, sizeof(sp));
   sp.qkv = qkv; sp.what = (const cf*)(pl + p.what); sp.ab = ga.ab; sp.state = (cf*)(ws + l.state);
@@ -206,6 +219,7 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   if ((s = launch_gdn_spectral(sp, st)) != CSSM_OK) return s;
 
   // 7. RMSNorm over channels, output gate, output projection -> channels-last y
+  mark(6, st);
   memset(&g, 0, sizeof(g));
   g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
   g.A = qkv; g.a_planes = 3 * C; g.a_plane0 = 2 * C;
@@ -214,7 +228,14 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   g.Wk = w->output_proj_kernel; g.bias = w->output_proj_bias;
   g.out = y;
   g.T = d->T; g.H = d->H; g.W = d->W;
-  return launch_gemm<true, false>(g, st);
+  s = launch_gemm<true, false>(g, st);
+  mark(7, st);
+  return s;
+}
+
+int cssm_debug_gdn_stage_events(void** events) {
+  g_stage_events = reinterpret_cast<cudaEvent_t*>(events);
+  return CSSM_OK;
 }
 
 }  // extern "C"

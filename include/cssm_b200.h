@@ -219,6 +219,11 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
  * bounded wait ever expired) to *out; synchronises the device. */
 int cssm_debug_set_gemm_backend(int backend);
 int cssm_debug_tc_error(int* out);
+/* cssm_debug_gdn_stage_events: `events` is an array of 8 cudaEvent_t (or NULL to switch the
+ * hook off, the default).  While set, cssm_gdn_forward called from the same host thread records
+ * events[i] before its stage i (0 dwconv+ctx, 1 qkv_proj, 2 gate_proj, 3 gates, 4 short convs,
+ * 5 fused spectral kernel, 6 norm+gate+output_proj) and events[7] at the end. */
+int cssm_debug_gdn_stage_events(void** events);
 
 /* ---- entry point that allocates nothing (no counterpart in the reference) ----
  * The reference has nothing like this: it is for hosts that may not call cudaMalloc at all
