@@ -3,54 +3,89 @@
 // One CTA per (batch, channel) pair.
 #include "r64.cuh"
 #include "kernels.cuh"
+#include "tc05.cuh"
 
 namespace cssm {
 
 // ============================================================== 64 x 64 planes ====
 // 288 threads; thread roles and shared-memory layout are those of r64.cuh.  The lane keeps the
-// state of its 8 bins (kh = a + 8q of column grp) in registers for all T steps.  Global loads
-// are issued one phase ahead of their use: the gate maps and K_hat at the top of the column
-// phase, z_t and the next step's x_main plane at the top of the inverse-row phase.
+// state of its 8 bins (kh = a + 8q of column grp) in registers for all T steps.
+// The x_main plane of step t+1 and the (SiLU'd) z plane of step t+1 are staged in shared memory
+// by TMA bulk copies (one 256-byte row per copy into rows padded to 272 bytes, issued by the
+// otherwise idle ninth warp right after the first barrier of step t) and land while step t
+// computes; gate maps and K_hat are loaded at the top of the column phase.
 constexpr int R64_THREADS = R64_NT;
-constexpr int R64_SMEM_CF = R64_EX_CF + R64_ZR_CF + R64_GB_CF;
+constexpr int R64_PRS = 68;                                   // floats per staged plane row
+constexpr int R64_PLANE_F = 64 * R64_PRS;
+constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64_PLANE_F * 4;
+
+__device__ int g_spec_error = 0;
 
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
+  float* xbuf = reinterpret_cast<float*>(EX + R64_EX_CF + R64_ZR_CF + R64_GB_CF);
+  float* zbuf = xbuf + R64_PLANE_F;                           // two buffers
+  __shared__ __align__(8) uint64_t bars[3];                   // x, z[0], z[1]
   R64Ctx c;
   r64_init(c, EX, EX + R64_EX_CF, EX + R64_EX_CF + R64_ZR_CF);
 
   const int b = blockIdx.x / C, ch = blockIdx.x % C;
   constexpr int HW = 64 * 64;
   const cf* khp = khat + (size_t)ch * (64 * 33) + (c.grp << 3) + c.a;
+  const float* x0 = xz + ((size_t)(b * T) * 2 * C + ch) * HW;          // x_main plane of step 0
+  const size_t fstride = (size_t)2 * C * HW;                            // next step's plane
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bars[0], 1); tc::mbar_init(&bars[1], 1); tc::mbar_init(&bars[2], 1);
+    tc::fence_mbar_init();
+  }
+  __syncthreads();
+  // stage step `tl`: x_main plane into xbuf (if want_x) and z plane into zbuf[tl & 1]
+  auto stage = [&](int tl, bool want_x) {
+    if (c.warp != 8) return;
+    tc::fence_proxy_async();             // earlier generic reads of the buffers come first
+    uint64_t* bz = &bars[1 + (tl & 1)];
+    if (c.lane == 0) {
+      if (want_x) tc::mbar_expect_tx(&bars[0], 64 * 256);
+      tc::mbar_expect_tx(bz, 64 * 256);
+    }
+    __syncwarp();
+    const float* xs = x0 + (size_t)tl * fstride;
+    const float* zs = xs + (size_t)C * HW;
+    float* zd = zbuf + (tl & 1) * R64_PLANE_F;
+#pragma unroll
+    for (int r = c.lane; r < 64; r += 32) {
+      if (want_x) tc::bulk_g2s(xbuf + r * R64_PRS, xs + r * 64, 256, &bars[0]);
+      tc::bulk_g2s(zd + r * R64_PRS, zs + r * 64, 256, bz);
+    }
+  };
+  stage(0, true);
 
   cf hst[8];
 #pragma unroll
   for (int q = 0; q < 8; ++q) hst[q] = mk(0.f, 0.f);
-
-  // x_main rows of step 0 (row lanes: rows 2*grp and 2*grp+1, columns a + 8m)
-  const int roff = (2 * c.grp) * 64 + c.a;
-  cf xr[8];
-  {
-    const float* r0 = xz + ((size_t)(b * T) * 2 * C + ch) * HW + roff;
-#pragma unroll
-    for (int m = 0; m < 8; ++m) xr[m] = c.row_on ? mk(r0[8 * m], r0[64 + 8 * m]) : mk(0.f, 0.f);
-  }
+  const int roff = (2 * c.grp) * 64 + c.a;              // global offset of the lane's row pair
+  const int soff = (2 * c.grp) * R64_PRS + c.a;         // same inside a staged plane
 
   for (int t = 0; t < T; ++t) {
     const size_t frame = (size_t)(b * T + t);
     float* xp = xz + (frame * 2 * C + ch) * HW;
-    const float* zp = xz + (frame * 2 * C + C + ch) * HW;
 
-    // ---- forward rows ----
+    // ---- forward rows (from the staged plane) ----
     if (c.row_on) {
-      fft64_lane8<false>(xr, c.tw, c.exg, c.a);
+      if (!tc::mbar_wait(&bars[0], t & 1)) atomicExch(&g_spec_error, 1);
+      cf v[8];
 #pragma unroll
-      for (int k2 = 0; k2 < 8; ++k2) c.ZR[c.grp * R64_ZRS + c.a + 8 * k2] = xr[k2];
+      for (int m = 0; m < 8; ++m) v[m] = mk(xbuf[soff + 8 * m], xbuf[soff + R64_PRS + 8 * m]);
+      fft64_lane8<false>(v, c.tw, c.exg, c.a);
+#pragma unroll
+      for (int k2 = 0; k2 < 8; ++k2) c.ZR[c.grp * R64_ZRS + c.a + 8 * k2] = v[k2];
     }
     __syncthreads();
+    if (t + 1 < T) stage(t + 1, true);
 
     // ---- forward columns, recurrence, inverse columns ----
     if (c.col_warp) {
@@ -79,29 +114,29 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     }
     __syncthreads();
 
-    // ---- inverse rows, * silu(z), store; prefetch the next step's rows ----
+    // ---- inverse rows, * staged silu(z), store ----
     if (c.row_on) {
-      cf zr[8];
-      const float* z0 = zp + roff;
-#pragma unroll
-      for (int n1 = 0; n1 < 8; ++n1) zr[n1] = mk(z0[8 * n1], z0[64 + 8 * n1]);
-      if (t + 1 < T) {
-        const float* r0 = xp + (size_t)2 * C * HW + roff;
-#pragma unroll
-        for (int m = 0; m < 8; ++m) xr[m] = mk(r0[8 * m], r0[64 + 8 * m]);
-      }
       cf v[8];
       r64_row_inv(c, v);
+      if (!tc::mbar_wait(&bars[1 + (t & 1)], (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
+      const float* zs = zbuf + (t & 1) * R64_PLANE_F + soff;
       float* y0 = xp + roff;
 #pragma unroll
       for (int n1 = 0; n1 < 8; ++n1) {
-        y0[8 * n1] = v[n1].x * zr[n1].x;
-        y0[64 + 8 * n1] = v[n1].y * zr[n1].y;
+        y0[8 * n1] = v[n1].x * zs[8 * n1];
+        y0[64 + 8 * n1] = v[n1].y * zs[R64_PRS + 8 * n1];
       }
     }
     // No barrier needed here: the next iteration writes EX (warp-private) and ZR (last read
-    // before the second barrier above); GB is next written after the next first barrier.
+    // before the second barrier above); GB is next written after the next first barrier; xbuf
+    // and zbuf[(t+1)&1] are refilled only after the next first barrier.
   }
+}
+
+int read_spec_error(int* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_spec_error, sizeof(int));
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  return CSSM_OK;
 }
 
 // ================================================================ generic planes ====
@@ -222,7 +257,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
   const SpectralPath path = spectral_path(d.H, d.W);
   const int grid = d.B * d.C;
   if (path == PATH_R64) {
-    const size_t smem = R64_SMEM_CF * sizeof(cf);
+    const size_t smem = R64_SMEM_BYTES;
     cudaError_t e = cudaFuncSetAttribute(gated_spectral_r64,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }

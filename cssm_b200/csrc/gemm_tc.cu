@@ -39,7 +39,7 @@ struct TcSmem {
 };
 
 template <int N, bool A_PLANAR>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g, int num_tiles) {
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment (swizzle atoms); the launch adds 1024 bytes of slack
   unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
             const int m = nt * TC_BM + rsub + 16 * r;
-            pre[r] = m < g.M ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
+            pre[r] = (m < g.M && !(dbg & 2)) ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
                              : make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
         uint32_t r[32];
         tc::ld_32x32b_x32(taddr + cc * 32, r);
         tc::wait_ld();
-        if (m < g.M) {
+        if (m < g.M && !(dbg & 1)) {
           if (!A_PLANAR) {
             // planar output: lanes = consecutive pixels -> 128-byte coalesced stores per column
             const int fr = m / g.HW, px = m - fr * g.HW;
@@ -313,7 +313,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
 }
 
 static int g_force_simt = 0;
-void set_force_simt(int on) { g_force_simt = on; }
+static int g_tc_dbg = 0;      // experiment switches (bit 1: skip epilogue stores, bit 2: skip A loads)
+void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = on >> 1; }
 
 // Whether the tensor-core kernel covers this problem (else the CUDA-core GEMM runs).
 bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
@@ -337,7 +338,7 @@ static int launch_tc(const GemmArgs& g, cudaStream_t st) {
   e = cudaFuncSetAttribute(gemm_tc_kernel<N, A_PLANAR>,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  gemm_tc_kernel<N, A_PLANAR><<<grid, TC_THREADS, smem, st>>>(g, num_tiles);
+  gemm_tc_kernel<N, A_PLANAR><<<grid, TC_THREADS, smem, st>>>(g, num_tiles, g_tc_dbg);
   return check_launch();
 }
 
@@ -357,12 +358,17 @@ int read_tc_error(int* out) {
 
 extern "C" {
 int cssm_debug_set_gemm_backend(int backend) {
-  if (backend != 0 && backend != 1) return CSSM_ERR_UNSUPPORTED;
+  if (backend < 0 || backend > 15) return CSSM_ERR_UNSUPPORTED;
   cssm::set_force_simt(backend);
   return CSSM_OK;
 }
 int cssm_debug_tc_error(int* out) {
   if (!out) return CSSM_ERR_NULL;
-  return cssm::read_tc_error(out);
+  int a = 0, b = 0;
+  int rc = cssm::read_tc_error(&a);
+  if (rc != CSSM_OK) return rc;
+  rc = cssm::read_spec_error(&b);
+  *out = a | (b << 8);           // low byte: tensor-core GEMM, next byte: fused spectral kernel
+  return rc;
 }
 }
