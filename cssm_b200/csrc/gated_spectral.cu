@@ -11,22 +11,26 @@ namespace cssm {
 // 288 threads; thread roles and shared-memory layout are those of r64.cuh.  The lane keeps the
 // state of its 8 bins (kh = a + 8q of column grp) in registers for all T steps.
 // The x_main plane of step t+1 and the (SiLU'd) z plane of step t+1 are staged in shared memory
-// by TMA bulk copies (one 256-byte row per copy into rows padded to 272 bytes, issued by the
-// otherwise idle ninth warp right after the first barrier of step t) and land while step t
-// computes; gate maps and K_hat are loaded at the top of the column phase.
+// by TMA bulk copies (one 16 KB copy per plane, issued by a lane of the otherwise idle ninth warp
+// right after the first barrier of step t) and land while step t computes; gate maps and K_hat
+// are loaded at the top of the column phase.  (One copy per 256-byte row into bank-conflict-free
+// padded rows is kept as variant <68>: it measured 20 % slower, the copy engine's per-request
+// cost outweighs the 4-way conflicts of the dense rows.)
 constexpr int R64_THREADS = R64_NT;
-constexpr int R64_PRS = 68;                                   // floats per staged plane row
-constexpr int R64_PLANE_F = 64 * R64_PRS;
+constexpr int R64_PLANE_F = 64 * 68;
 constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64_PLANE_F * 4;
 
 __device__ int g_spec_error = 0;
+int g_spec_variant = 0;
 
+template <int PRS>   // floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane)
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
   float* xbuf = reinterpret_cast<float*>(EX + R64_EX_CF + R64_ZR_CF + R64_GB_CF);
+  constexpr int R64_PRS = PRS;
   float* zbuf = xbuf + R64_PLANE_F;                           // two buffers
   __shared__ __align__(8) uint64_t bars[3];                   // x, z[0], z[1]
   R64Ctx c;
@@ -56,10 +60,17 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     const float* xs = x0 + (size_t)tl * fstride;
     const float* zs = xs + (size_t)C * HW;
     float* zd = zbuf + (tl & 1) * R64_PLANE_F;
+    if (PRS == 64) {
+      if (c.lane == 0) {
+        if (want_x) tc::bulk_g2s(xbuf, xs, 64 * 256, &bars[0]);
+        tc::bulk_g2s(zd, zs, 64 * 256, bz);
+      }
+    } else {
 #pragma unroll
-    for (int r = c.lane; r < 64; r += 32) {
-      if (want_x) tc::bulk_g2s(xbuf + r * R64_PRS, xs + r * 64, 256, &bars[0]);
-      tc::bulk_g2s(zd + r * R64_PRS, zs + r * 64, 256, bz);
+      for (int r = c.lane; r < 64; r += 32) {
+        if (want_x) tc::bulk_g2s(xbuf + r * R64_PRS, xs + r * 64, 256, &bars[0]);
+        tc::bulk_g2s(zd + r * R64_PRS, zs + r * 64, 256, bz);
+      }
     }
   };
   stage(0, true);
@@ -258,11 +269,12 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
   const int grid = d.B * d.C;
   if (path == PATH_R64) {
     const size_t smem = R64_SMEM_BYTES;
-    cudaError_t e = cudaFuncSetAttribute(gated_spectral_r64,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    auto kern = g_spec_variant == 1 ? gated_spectral_r64<68> : gated_spectral_r64<64>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-    gated_spectral_r64<<<grid, R64_THREADS, smem, st>>>(
-        xz, khat, reinterpret_cast<const float4*>(gates), d.T, d.C);
+    kern<<<grid, R64_THREADS, smem, st>>>(xz, khat, reinterpret_cast<const float4*>(gates), d.T,
+                                          d.C);
   } else {
     const size_t smem = generic_smem_bytes(d.H, d.W);
     if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;

@@ -5,75 +5,127 @@
 namespace cssm {
 
 // ------------------------------------------------- RoPE + depthwise KxK, channels-last ----
-// One CTA per (frame, output row).  The K input rows are rotated (RoPE) while they are
-// staged in shared memory; the conv runs from there.  The CTA also writes the sum over its
-// row of the ROTATED INPUT (not of the conv output) per channel: ctx is the mean of the
-// block input (cssm.py:4785-4786).
-__global__ void __launch_bounds__(256)
-rope_dwconv_cl_kernel(const GdnDwArgs a) {
+// One CTA per (frame, band of DW_ROWS output rows, group of 16 channels).  The band's input
+// rows (+ halo) are rotated (RoPE) while they are staged in shared memory as [row][w][16];
+// each thread then produces DW_ROWS x 4 outputs for one channel from there.  The CTA also
+// writes, per centre row and channel, the sum over w of the ROTATED INPUT (ctx is the mean of
+// the block input, cssm.py:4785-4786), not of the conv output.
+constexpr int DW_ROWS = 8, DW_THREADS = 256;
+
+template <int K, int DW_CG>
+__global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwArgs a) {
   extern __shared__ __align__(16) float sm[];
-  const int K = a.ksz > 1 ? a.ksz : 1;
-  const int lo = (K - 1) / 2;
-  const int fr = blockIdx.x / a.H, h = blockIdx.x % a.H;
-  const int t = fr % a.T;
-  const int WC = a.W * a.C, n2 = a.C / 2;
+  constexpr int LO = (K - 1) / 2, NR = DW_ROWS + K - 1;
+  const int W = a.W, C = a.C, n2 = C / 2;
+  const int bands = (a.H + DW_ROWS - 1) / DW_ROWS, cgs = C / DW_CG;
+  int bid = blockIdx.x;
+  const int cg = bid % cgs; bid /= cgs;
+  const int band = bid % bands;
+  const int fr = bid / bands;
+  const int t = fr % a.T, h0 = band * DW_ROWS, c0 = cg * DW_CG;
   const int tid = threadIdx.x;
-  // stage rows h-lo .. h-lo+K-1 (zeros outside the image)
-  for (int r = 0; r < K; ++r) {
-    const int hh = h + r - lo;
-    float* dst = sm + r * WC;
-    if (hh < 0 || hh >= a.H) {
-      for (int i = tid; i < WC; i += blockDim.x) dst[i] = 0.f;
-      continue;
-    }
-    const float* src = a.x + ((size_t)fr * a.H + hh) * WC;
-    for (int i = tid; i < WC / 2; i += blockDim.x) {
-      const int w = i / n2, pi = i % n2;
-      float2 v = *reinterpret_cast<const float2*>(src + 2 * i);
+  // ---- stage rows h0-LO .. h0+DW_ROWS-1+(K-1-LO), 16 channels, rotated ----
+  const int pairs_per_row = W * (DW_CG / 2);
+  for (int i = tid; i < NR * pairs_per_row; i += DW_THREADS) {
+    const int r = i / pairs_per_row, rem = i - r * pairs_per_row;
+    const int w = rem / (DW_CG / 2), pl = rem % (DW_CG / 2);
+    const int hh = h0 + r - LO;
+    float2 v = make_float2(0.f, 0.f);
+    if (hh >= 0 && hh < a.H) {
+      v = *reinterpret_cast<const float2*>(a.x + (((size_t)fr * a.H + hh) * W + w) * C + c0 + 2 * pl);
       if (a.rope_t != nullptr) {
+        const int pi = c0 / 2 + pl;
         const float2 ct = a.rope_t[t * n2 + pi], ch = a.rope_h[hh * n2 + pi], cw = a.rope_w[w * n2 + pi];
         const float cx = ct.x * ch.x - ct.y * ch.y, sx = ct.x * ch.y + ct.y * ch.x;
         const float c2 = cx * cw.x - sx * cw.y, s2 = cx * cw.y + sx * cw.x;
         v = make_float2(v.x * c2 - v.y * s2, v.x * s2 + v.y * c2);
       }
-      dst[2 * i] = v.x; dst[2 * i + 1] = v.y;
     }
+    *reinterpret_cast<float2*>(sm + ((size_t)r * W + w) * DW_CG + 2 * pl) = v;
   }
   __syncthreads();
-  // context partial sums of the centre row
-  if (a.ctx_part != nullptr) {
-    const float* ctr = sm + lo * WC;
-    for (int c = tid; c < a.C; c += blockDim.x) {
+  // ---- context partial sums of the centre rows ----
+  if (a.ctx_part != nullptr && tid < DW_ROWS * DW_CG) {
+    const int r = tid / DW_CG, c = tid % DW_CG;
+    if (h0 + r < a.H) {
       float s = 0.f;
-      for (int w = 0; w < a.W; ++w) s += ctr[w * a.C + c];
-      a.ctx_part[((size_t)fr * a.H + h) * a.C + c] = s;
+      for (int w = 0; w < W; ++w) s += sm[((size_t)(r + LO) * W + w) * DW_CG + c];
+      a.ctx_part[((size_t)fr * a.H + h0 + r) * C + c0 + c] = s;
     }
   }
-  if (a.out != nullptr) {
-    float* dst = a.out + ((size_t)fr * a.H + h) * WC;
-    for (int i = tid; i < WC; i += blockDim.x) {
-      const int w = i / a.C, c = i % a.C;
-      float acc = a.bias[c];
-      for (int r = 0; r < K; ++r)
-        for (int s = 0; s < K; ++s) {
-          const int ww = w + s - lo;
-          if (ww < 0 || ww >= a.W) continue;
-          acc = fmaf(a.wk[(size_t)(r * K + s) * a.C + c], sm[r * WC + ww * a.C + c], acc);
+  if (a.out == nullptr) return;
+  // ---- conv: thread = (channel c, group of 4 consecutive w), all DW_ROWS rows ----
+  const int c = tid % DW_CG;
+  float wk[K * K];
+#pragma unroll
+  for (int i = 0; i < K * K; ++i) wk[i] = a.wk[(size_t)i * C + c0 + c];
+  const float bias = a.bias[c0 + c];
+  for (int wg = tid / DW_CG; wg * 4 < W; wg += DW_THREADS / DW_CG) {
+    const int w0 = wg * 4;
+    float acc[DW_ROWS][4];
+#pragma unroll
+    for (int r = 0; r < DW_ROWS; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[r][j] = bias;
+#pragma unroll
+    for (int ir = 0; ir < NR; ++ir) {
+      float win[4 + K - 1];
+#pragma unroll
+      for (int j = 0; j < 4 + K - 1; ++j) {
+        const int ww = w0 + j - LO;
+        win[j] = (ww >= 0 && ww < W) ? sm[((size_t)ir * W + ww) * DW_CG + c] : 0.f;
+      }
+      // input row ir feeds output row r = ir - di for tap row di
+#pragma unroll
+      for (int di = 0; di < K; ++di) {
+        const int r = ir - di;
+        if (r < 0 || r >= DW_ROWS) continue;
+#pragma unroll
+        for (int dj = 0; dj < K; ++dj) {
+          const float wv = wk[di * K + dj];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[r][j] = fmaf(wv, win[j + dj], acc[r][j]);
         }
-      dst[i] = acc;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < DW_ROWS; ++r) {
+      if (h0 + r >= a.H) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (w0 + j < W)
+          a.out[(((size_t)fr * a.H + h0 + r) * W + w0 + j) * C + c0 + c] = acc[r][j];
     }
   }
 }
 
-int launch_rope_dwconv_cl(const GdnDwArgs& a, cudaStream_t st) {
-  const int K = a.ksz > 1 ? a.ksz : 1;
-  const size_t smem = (size_t)K * a.W * a.C * sizeof(float);
+template <int K, int DW_CG>
+static int launch_dw_cg(const GdnDwArgs& a, cudaStream_t st) {
+  const size_t smem = (size_t)(DW_ROWS + K - 1) * a.W * DW_CG * sizeof(float);
   if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
-  cudaError_t e = cudaFuncSetAttribute(rope_dwconv_cl_kernel,
+  cudaError_t e = cudaFuncSetAttribute(rope_dwconv_cl_kernel<K, DW_CG>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  rope_dwconv_cl_kernel<<<a.BT * a.H, 256, smem, st>>>(a);
+  const int bands = (a.H + DW_ROWS - 1) / DW_ROWS;
+  rope_dwconv_cl_kernel<K, DW_CG><<<a.BT * bands * (a.C / DW_CG), DW_THREADS, smem, st>>>(a);
   return check_launch();
+}
+
+// 16-channel groups (64-byte segments per pixel) when C allows, else 4-channel groups
+template <int K>
+static int launch_dw(const GdnDwArgs& a, cudaStream_t st) {
+  return a.C % 16 == 0 ? launch_dw_cg<K, 16>(a, st) : launch_dw_cg<K, 4>(a, st);
+}
+
+int launch_rope_dwconv_cl(const GdnDwArgs& a, cudaStream_t st) {
+  if (a.C % 4 != 0) return CSSM_ERR_UNSUPPORTED;
+  switch (a.ksz > 1 ? a.ksz : 1) {
+    case 1: return launch_dw<1>(a, st);
+    case 3: return launch_dw<3>(a, st);
+    case 5: return launch_dw<5>(a, st);
+    case 7: return launch_dw<7>(a, st);
+    default: return CSSM_ERR_UNSUPPORTED;
+  }
 }
 
 // ------------------------------------------------------------------- GDN gate maps ----

@@ -10,8 +10,9 @@
 //                          2-stage ring;
 //   warp  8    MMA issuer: one lane issues 24 tcgen05.mma (M128 x N x K8) per tile into one of
 //                          two TMEM accumulators and commits to mbarriers;
-//   warps 9-12 epilogue  : tcgen05.ld the accumulator (lane = pixel), add bias / activation,
-//                          store planar (coalesced over pixels) or channels-last rows.
+//   warps 9-16 epilogue  : tcgen05.ld the accumulator (lane = pixel; two warps per TMEM lane
+//                          quadrant, half of the columns each), add bias / activation, store
+//                          planar (coalesced over pixels) or channels-last rows.
 // The weight tile (both halves of the split) is prepared once per CTA and stays in shared memory.
 // Every mbarrier wait is bounded; on expiry the kernel records an error code and winds down.
 #include "kernels.cuh"
@@ -22,7 +23,7 @@ namespace cssm {
 
 __device__ int g_tc_error = 0;
 
-constexpr int TC_THREADS = 416;      // 8 producer warps, 1 MMA warp, 4 epilogue warps
+constexpr int TC_THREADS = 544;      // 8 producer warps, 1 MMA warp, 8 epilogue warps
 constexpr int TC_MMA_WARP = 8;
 constexpr int TC_BM = 128;
 constexpr int TC_K = 64;
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
     tc::mbar_init(&full[0], NPROD); tc::mbar_init(&full[1], NPROD);
     tc::mbar_init(&empty[0], 1); tc::mbar_init(&empty[1], 1);
     tc::mbar_init(&accfull[0], 1); tc::mbar_init(&accfull[1], 1);
-    tc::mbar_init(&accempty[0], 128); tc::mbar_init(&accempty[1], 128);
+    tc::mbar_init(&accempty[0], 256); tc::mbar_init(&accempty[1], 256);
     tc::mbar_init(done, 1);
     tc::fence_mbar_init();
   }
@@ -257,6 +258,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
   } else if (warp > TC_MMA_WARP) {
     // ================================ epilogue ================================
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - (TC_MMA_WARP + 1)) >> 2;   // which half of the N columns
     const int row = q * 32 + lane;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
@@ -266,12 +268,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       const int m = tile * TC_BM + row;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)s * N;
 #pragma unroll 1
-      for (int cc = 0; cc < N / 32; ++cc) {
+      for (int cc = half * (N / 64); cc < (half + 1) * (N / 64); ++cc) {
         uint32_t r[32];
         tc::ld_32x32b_x32(taddr + cc * 32, r);
         tc::wait_ld();
         if (m < g.M && !(dbg & 1)) {
-          if (!A_PLANAR) {
+          if (!A_PLANAR && (dbg & 4)) {
+            // experiment only: row-contiguous stores (wrong layout) to time the store pattern
+            float* op = g.out + (size_t)m * g.N + cc * 32;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(op + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          } else if (!A_PLANAR) {
             // planar output: lanes = consecutive pixels -> 128-byte coalesced stores per column
             const int fr = m / g.HW, px = m - fr * g.HW;
             float* op = g.out + ((size_t)fr * g.o_planes + g.o_plane0 + cc * 32) * g.HW + px;
@@ -314,15 +323,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
 
 static int g_force_simt = 0;
 static int g_tc_dbg = 0;      // experiment switches (bit 1: skip epilogue stores, bit 2: skip A loads)
-void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = on >> 1; }
+extern int g_spec_variant;
+void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = ((on >> 1) & 3) | ((on >> 4) & 1) << 2; g_spec_variant = (on >> 3) & 1; }
 
 // Whether the tensor-core kernel covers this problem (else the CUDA-core GEMM runs).
 bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
   if (g_force_simt) return false;
-  if (g.K != TC_K || (g.N != 64 && g.N != 128)) return false;
+  if (g.K != TC_K || (g.N != 64 && g.N != 128 && g.N != 192)) return false;
   if (g.HW % TC_BM != 0 || g.M % TC_BM != 0) return false;
   if (g.out_act != 0 && g.act_n0 % 32 != 0) return false;
-  if (!a_planar && g.rope_t != nullptr && g.K != 64) return false;
+  if (a_planar && g.N == 192) return false;
   return true;
 }
 
@@ -344,7 +354,10 @@ static int launch_tc(const GemmArgs& g, cudaStream_t st) {
 
 int launch_gemm_tc(const GemmArgs& g, bool a_planar, cudaStream_t st) {
   if (!gemm_tc_supported(g, a_planar)) return CSSM_ERR_UNSUPPORTED;
-  if (!a_planar) return g.N == 128 ? launch_tc<128, false>(g, st) : launch_tc<64, false>(g, st);
+  if (!a_planar)
+    return g.N == 192 ? launch_tc<192, false>(g, st)
+                      : g.N == 128 ? launch_tc<128, false>(g, st) : launch_tc<64, false>(g, st);
+  if (g.N == 192) return CSSM_ERR_UNSUPPORTED;
   return g.N == 128 ? launch_tc<128, true>(g, st) : launch_tc<64, true>(g, st);
 }
 
@@ -358,7 +371,7 @@ int read_tc_error(int* out) {
 
 extern "C" {
 int cssm_debug_set_gemm_backend(int backend) {
-  if (backend < 0 || backend > 15) return CSSM_ERR_UNSUPPORTED;
+  if (backend < 0 || backend > 31) return CSSM_ERR_UNSUPPORTED;
   cssm::set_force_simt(backend);
   return CSSM_OK;
 }
