@@ -129,25 +129,55 @@ def peaks():
 
 
 class ClockSampler:
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU while a region runs (NVML, read-only)."""
+    REASONS = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+               "sw_power_cap": 0x4}
 
     def __init__(self, index):
         self.index, self.samples, self.stop = index, [], threading.Event()
         self.th = threading.Thread(target=self.run, daemon=True)
+        self.max_mhz = None
 
     def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            while not self.stop.is_set():
+                self.samples.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                     int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))))
+                self.stop.wait(0.005)
+        except Exception:
+            self._run_smi()
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v for v in vis.split(",") if v.strip() != ""]
+            if self.index < len(ids) and ids[self.index].strip().isdigit():
+                return int(ids[self.index])
+        return self.index
+
+    def _run_smi(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         while not self.stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                      "--format=csv,noheader,nounits"], capture_output=True,
-                                     text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([s.strip() for s in out.split(",")])
+                out = subprocess.run(["nvidia-smi", "-i", str(self._physical_index()),
+                                      f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                f = [x.strip() for x in out.split(",")]
+                if len(f) >= 6:
+                    self.max_mhz = float(f[1])
+                    mask = sum(self.REASONS[n] for i, n in enumerate(names)
+                               if f[2 + i].lower().startswith("active"))
+                    self.samples.append((float(f[0]), mask))
             except Exception:
                 pass
-            self.stop.wait(0.1)
+            self.stop.wait(0.05)
 
     def __enter__(self):
         self.th.start()
@@ -159,13 +189,11 @@ class ClockSampler:
 
     def summary(self):
         if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        sm = sorted(float(s[0]) for s in self.samples)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names)
-                   if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]),
-                "reasons": reasons, "samples": len(sm)}
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        sm = sorted(s[0] for s in self.samples)
+        reasons = [n for n, bit in self.REASONS.items() if any(s[1] & bit for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons),
+                "samples": len(sm)}
 
 
 def cpu_reference_rate(cfg, sample_b, reps=1):
@@ -194,7 +222,7 @@ def cpu_reference_rate(cfg, sample_b, reps=1):
 def run_reference(args, cfg, rank):
     if rank != 0:
         return
-    sample_b = 4
+    sample_b = 16
     times = []
     for i in range(args.warmup + args.steps):
         rate, dt, cores = cpu_reference_rate(cfg, sample_b)
@@ -370,10 +398,10 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        rate, dt, cores = cpu_reference_rate(cfg, 4, reps=2)
+        rate, dt, cores = cpu_reference_rate(cfg, 16, reps=16)
         cpu = {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
-               "sample": f"4 images of the {args.workload} block input, 2 repetitions "
-                         f"({dt:.1f} s each), torch-CPU restatement of the reference block"}
+               "sample": f"16 images of the {args.workload} block input, 16 repetitions "
+                         f"({dt:.2f} s each), torch-CPU restatement of the reference block"}
 
     if rank == 0:
         print(json.dumps({

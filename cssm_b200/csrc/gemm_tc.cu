@@ -41,6 +41,11 @@ struct TcSmem {
 
 template <int N, bool A_PLANAR>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg) {
+  // tile schedule: round-robin over CTAs (default) or one contiguous range per CTA (dbg & 8)
+  const int per = (num_tiles + gridDim.x - 1) / gridDim.x;
+  const int t_first = (dbg & 8) ? blockIdx.x * per : blockIdx.x;
+  const int t_step = (dbg & 8) ? 1 : gridDim.x;
+  const int t_end = (dbg & 8) ? min(num_tiles, t_first + per) : num_tiles;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment (swizzle atoms); the launch adds 1024 bytes of slack
   unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -100,11 +105,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
     const int chunk = 2 * warp + (lane & 1), rsub = lane >> 1;
     bool rot = false;
     if (!A_PLANAR) {
-      const int m0 = blockIdx.x * TC_BM;
+      const int m0 = t_first * TC_BM;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         const int m = m0 + rsub + 16 * r;
-        pre[r] = (blockIdx.x < num_tiles && m < g.M)
+        pre[r] = (t_first < t_end && m < g.M)
                      ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
                      : make_float4(0.f, 0.f, 0.f, 0.f);
       }
@@ -116,15 +121,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       }
     }
     const float invW = 1.0f / (float)g.W;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = t_first; tile < t_end; tile += t_step, ++it) {
       const int s = it & 1;
       const int m0 = tile * TC_BM;
       float4 cur[8];
       if (!A_PLANAR) {
 #pragma unroll
         for (int r = 0; r < 8; ++r) cur[r] = pre[r];
-        const int nt = tile + gridDim.x;
-        if (nt < num_tiles) {
+        const int nt = tile + t_step;
+        if (nt < t_end) {
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
             const int m = nt * TC_BM + rsub + 16 * r;
@@ -225,7 +230,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       const uint32_t b_hi = sbase + L::B_OFF, b_lo = b_hi + L::B_HALF;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      for (int tile = t_first; tile < t_end; tile += t_step, ++it) {
         const int s = it & 1, ph = (it >> 1) & 1;
         if (!tc::mbar_wait(&accempty[s], ph ^ 1) || !tc::mbar_wait(&full[s], ph)) {
           atomicExch(&g_tc_error, 2); ok = false; break;
@@ -261,7 +266,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
     const int half = (warp - (TC_MMA_WARP + 1)) >> 2;   // which half of the N columns
     const int row = q * 32 + lane;
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = t_first; tile < t_end; tile += t_step, ++it) {
       const int s = it & 1, ph = (it >> 1) & 1;
       if (!tc::mbar_wait(&accfull[s], ph)) { atomicExch(&g_tc_error, 4); break; }
       tc::fence_after_sync();
@@ -324,7 +329,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
 static int g_force_simt = 0;
 static int g_tc_dbg = 0;      // experiment switches (bit 1: skip epilogue stores, bit 2: skip A loads)
 extern int g_spec_variant;
-void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = ((on >> 1) & 3) | ((on >> 4) & 1) << 2; g_spec_variant = (on >> 3) & 1; }
+void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = ((on >> 1) & 3) | (((on >> 4) & 1) << 2) | (((on >> 5) & 1) << 3); g_spec_variant = (on >> 3) & 1; }
 
 // Whether the tensor-core kernel covers this problem (else the CUDA-core GEMM runs).
 bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
@@ -371,7 +376,7 @@ int read_tc_error(int* out) {
 
 extern "C" {
 int cssm_debug_set_gemm_backend(int backend) {
-  if (backend < 0 || backend > 31) return CSSM_ERR_UNSUPPORTED;
+  if (backend < 0 || backend > 63) return CSSM_ERR_UNSUPPORTED;
   cssm::set_force_simt(backend);
   return CSSM_OK;
 }
