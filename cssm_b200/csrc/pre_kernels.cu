@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_kernel(const Stencil
 // conv from a zero-haloed shared tile, per-step sums reduced once at the end.
 // NP = float4 groups per thread = H*W / 1024.
 template <int KSP, int KT, int NP>
-__global__ void __launch_bounds__(ST_THREADS, 3) plane_stencil_fast_kernel(const StencilArgs s) {
+__global__ void __launch_bounds__(ST_THREADS) plane_stencil_fast_kernel(const StencilArgs s) {
   extern __shared__ __align__(16) float sm[];
   const int H = s.H, W = s.W, HW = H * W;
   const int RS = W + 8;                              // tile row stride (4-float pad each side)
