@@ -15,6 +15,8 @@
 //                          planar (coalesced over pixels) or channels-last rows.
 // The weight tile (both halves of the split) is prepared once per CTA and stays in shared memory.
 // Every mbarrier wait is bounded; on expiry the kernel records an error code and winds down.
+#include <cuda.h>
+#include <string.h>
 #include "kernels.cuh"
 #include "gemm_simt.cuh"
 #include "tc05.cuh"
@@ -29,18 +31,25 @@ constexpr int TC_BM = 128;
 constexpr int TC_K = 64;
 constexpr uint32_t TC_A_HALF = 2u * TC_BM * 128u;      // one of hi / lo: 2 K-blocks x 128 rows x 128 B
 
-template <int N>
+// STG = false: the epilogue warps store straight from registers.
+// STG = true : the epilogue stages 16 KB chunks (128 pixels x 32 output columns) in shared memory,
+//              one chunk buffer per half of the epilogue warps, and writes each chunk with one TMA
+//              tensor store (N <= 128: two A stages + two chunk buffers fit in 227 KB).
+template <int N, bool STG>
 struct TcSmem {
+  static constexpr uint32_t NSTAGE = 2u;
   static constexpr uint32_t B_HALF = 2u * N * 128u;
   static constexpr uint32_t B_OFF = 0;
   static constexpr uint32_t A_OFF = 2u * B_HALF;                 // after B_hi, B_lo
-  static constexpr uint32_t BIAS_OFF = A_OFF + 2u * 2u * TC_A_HALF;
+  static constexpr uint32_t OUT_OFF = A_OFF + NSTAGE * 2u * TC_A_HALF;   // 2 x 16 KB when STG
+  static constexpr uint32_t BIAS_OFF = OUT_OFF + (STG ? 2u * 16384u : 0u);
   static constexpr uint32_t BAR_OFF = BIAS_OFF + N * 4u;
   static constexpr uint32_t TOTAL = BAR_OFF + 128u;
 };
 
-template <int N, bool A_PLANAR>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg) {
+template <int N, bool A_PLANAR, bool STG>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__ CUtensorMap omap) {
   // tile schedule: round-robin over CTAs (default) or one contiguous range per CTA (dbg & 8)
   const int per = (num_tiles + gridDim.x - 1) / gridDim.x;
   const int t_first = (dbg & 8) ? blockIdx.x * per : blockIdx.x;
@@ -49,7 +58,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment (swizzle atoms); the launch adds 1024 bytes of slack
   unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
-  using L = TcSmem<N>;
+  using L = TcSmem<N, STG>;
+  constexpr int NSTAGE = L::NSTAGE;
   const uint32_t sbase = tc::smem_u32(smem);
   float* bias_s = reinterpret_cast<float*>(smem + L::BIAS_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -122,7 +132,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
     }
     const float invW = 1.0f / (float)g.W;
     for (int tile = t_first; tile < t_end; tile += t_step, ++it) {
-      const int s = it & 1;
+      const int s = it % NSTAGE;
       const int m0 = tile * TC_BM;
       float4 cur[8];
       if (!A_PLANAR) {
@@ -138,7 +148,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
           }
         }
       }
-      if (!tc::mbar_wait(&empty[s], ((it >> 1) & 1) ^ 1)) { atomicExch(&g_tc_error, 1); break; }
+      if (!tc::mbar_wait(&empty[s], ((it / NSTAGE) & 1) ^ 1)) { atomicExch(&g_tc_error, 1); break; }
       unsigned char* a_hi = smem + L::A_OFF + (uint32_t)s * 2u * TC_A_HALF;
       unsigned char* a_lo = a_hi + TC_A_HALF;
       if (!A_PLANAR) {
@@ -231,13 +241,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       int it = 0;
       bool ok = true;
       for (int tile = t_first; tile < t_end; tile += t_step, ++it) {
-        const int s = it & 1, ph = (it >> 1) & 1;
-        if (!tc::mbar_wait(&accempty[s], ph ^ 1) || !tc::mbar_wait(&full[s], ph)) {
+        const int s = it % NSTAGE, sph = (it / NSTAGE) & 1;    // A stage and its phase
+        const int ac = it & 1, ph = (it >> 1) & 1;              // accumulator and its phase
+        if (!tc::mbar_wait(&accempty[ac], ph ^ 1) || !tc::mbar_wait(&full[s], sph)) {
           atomicExch(&g_tc_error, 2); ok = false; break;
         }
         tc::fence_after_sync();
         const uint32_t a_hi = sbase + L::A_OFF + (uint32_t)s * 2u * TC_A_HALF, a_lo = a_hi + TC_A_HALF;
-        const uint32_t d = tmem_base + (uint32_t)s * N;
+        const uint32_t d = tmem_base + (uint32_t)ac * N;
         uint32_t acc = 0;
 #pragma unroll
         for (int pass = 0; pass < 3; ++pass) {
@@ -253,7 +264,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
           }
         }
         tc::commit(&empty[s]);
-        tc::commit(&accfull[s]);
+        tc::commit(&accfull[ac]);
       }
       // nothing of this thread's tensor work may be in flight when TMEM is freed
       tc::commit(done);
@@ -268,7 +279,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
     int it = 0;
     for (int tile = t_first; tile < t_end; tile += t_step, ++it) {
       const int s = it & 1, ph = (it >> 1) & 1;
-      if (!tc::mbar_wait(&accfull[s], ph)) { atomicExch(&g_tc_error, 4); break; }
+      bool ok = tc::mbar_wait(&accfull[s], ph);
+      if (STG) {
+        // the named barriers below need all 128 threads of the half: make the exit uniform
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.u32 p, %1, 0;\n\t"
+            "bar.red.and.pred q, %2, 128, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + half) : "memory");
+        ok = all_ok != 0;
+      }
+      if (!ok) { atomicExch(&g_tc_error, 4); break; }
       tc::fence_after_sync();
       const int m = tile * TC_BM + row;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)s * N;
@@ -277,6 +300,48 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
         uint32_t r[32];
         tc::ld_32x32b_x32(taddr + cc * 32, r);
         tc::wait_ld();
+        if (STG) {
+          // this half's 128 threads share two 16 KB staging chunks and named barrier 1 + half
+          const int grp_tid = tid - (TC_MMA_WARP + 1 + 4 * half) * 32;      // 0..127
+          float* stg = reinterpret_cast<float*>(smem + L::OUT_OFF) + half * 4096;
+          // the TMA store that last read this chunk buffer must have drained it
+          if (grp_tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+          const float* bs = bias_s + cc * 32;
+          const int act = (g.out_act != 0 && cc * 32 >= g.act_n0) ? g.out_act : 0;
+          if (!A_PLANAR) {
+            // chunk layout [column j][pixel]: lanes write consecutive pixels (conflict-free)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float v = __uint_as_float(r[j]) + bs[j];
+              if (act == 1) v = silu_f(v); else if (act == 2) v = sigmoid_f(v);
+              stg[j * 128 + row] = v;
+            }
+          } else {
+            // chunk layout [pixel][32 columns] in the 128-byte swizzle the tensor map expects
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v;
+              v.x = __uint_as_float(r[j + 0]) + bs[j + 0]; v.y = __uint_as_float(r[j + 1]) + bs[j + 1];
+              v.z = __uint_as_float(r[j + 2]) + bs[j + 2]; v.w = __uint_as_float(r[j + 3]) + bs[j + 3];
+              *reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(stg) +
+                                         tc::sw128_offset(row, j >> 2)) = v;
+            }
+          }
+          tc::fence_proxy_async();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+          if (grp_tid == 0 && !(dbg & 1)) {
+            const int m0 = tile * TC_BM;
+            if (!A_PLANAR) {
+              const int fr = m0 / g.HW, px0 = m0 - fr * g.HW;
+              tc::tma_store_3d(&omap, stg, px0, g.o_plane0 + cc * 32, fr);
+            } else {
+              tc::tma_store_2d(&omap, stg, cc * 32, m0);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          continue;
+        }
         if (m < g.M && !(dbg & 1)) {
           if (!A_PLANAR && (dbg & 4)) {
             // experiment only: row-contiguous stores (wrong layout) to time the store pattern
@@ -317,6 +382,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
       tc::fence_before_sync();
       tc::mbar_arrive(&accempty[s]);
     }
+    // shared memory must outlive the last TMA stores that read it
+    if (STG) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   }
   tc::fence_before_sync();
   __syncthreads();
@@ -329,7 +396,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmArgs g
 static int g_force_simt = 0;
 static int g_tc_dbg = 0;      // experiment switches (bit 1: skip epilogue stores, bit 2: skip A loads)
 extern int g_spec_variant;
-void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = ((on >> 1) & 3) | (((on >> 4) & 1) << 2) | (((on >> 5) & 1) << 3); g_spec_variant = (on >> 3) & 1; }
+void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = ((on >> 1) & 3) | (((on >> 4) & 1) << 2) | (((on >> 5) & 1) << 3) | (((on >> 6) & 1) << 4) |
+             (((on >> 7) & 1) << 5);
+  g_spec_variant = (on >> 3) & 1; }
 
 // Whether the tensor-core kernel covers this problem (else the CUDA-core GEMM runs).
 bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
@@ -341,20 +410,76 @@ bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
   return true;
 }
 
-template <int N, bool A_PLANAR>
-static int launch_tc(const GemmArgs& g, cudaStream_t st) {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Tensor map of the GEMM output for the TMA-store epilogue: 16 KB boxes of 128 pixels x 32 columns.
+static bool make_out_map(const GemmArgs& g, bool a_planar, CUtensorMap* map) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const cuuint32_t es[3] = {1, 1, 1};
+  CUresult r;
+  if (!a_planar) {
+    const cuuint64_t dims[3] = {(cuuint64_t)g.HW, (cuuint64_t)g.o_planes, (cuuint64_t)(g.M / g.HW)};
+    const cuuint64_t strides[2] = {(cuuint64_t)g.HW * 4, (cuuint64_t)g.o_planes * g.HW * 4};
+    const cuuint32_t box[3] = {128, 32, 1};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, g.out, dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    const cuuint64_t dims[2] = {(cuuint64_t)g.N, (cuuint64_t)g.M};
+    const cuuint64_t strides[1] = {(cuuint64_t)g.N * 4};
+    const cuuint32_t box[2] = {32, 128};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, g.out, dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  return r == CUDA_SUCCESS;
+}
+
+template <int N, bool A_PLANAR, bool STG>
+static int launch_tc_v(const GemmArgs& g, const CUtensorMap& map, cudaStream_t st) {
   const int num_tiles = g.M / TC_BM;
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const int grid = num_tiles < sms ? num_tiles : sms;
-  const size_t smem = TcSmem<N>::TOTAL + 1024;      // slack for the 1024-byte alignment
-  e = cudaFuncSetAttribute(gemm_tc_kernel<N, A_PLANAR>,
+  const size_t smem = TcSmem<N, STG>::TOTAL + 1024;      // slack for the 1024-byte alignment
+  e = cudaFuncSetAttribute(gemm_tc_kernel<N, A_PLANAR, STG>,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  gemm_tc_kernel<N, A_PLANAR><<<grid, TC_THREADS, smem, st>>>(g, num_tiles, g_tc_dbg);
+  gemm_tc_kernel<N, A_PLANAR, STG><<<grid, TC_THREADS, smem, st>>>(g, num_tiles, g_tc_dbg, map);
   return check_launch();
+}
+
+template <int N, bool A_PLANAR>
+static int launch_tc(const GemmArgs& g, cudaStream_t st) {
+  CUtensorMap map;
+  memset(&map, 0, sizeof(map));
+  // TMA-store epilogue for the channels-last output (planar A) unless switched off (debug bit) or
+  // the driver entry point is missing.  For the planar output it measured slower than direct
+  // stores (2.1 ms vs 1.44 ms on the in_proj of cfg2), so that direction keeps direct stores;
+  // debug bit 128 forces the TMA-store epilogue there for experiments.
+  const bool want = A_PLANAR || (g_tc_dbg & 32);
+  const bool stg = want && N <= 128 && !(g_tc_dbg & 16) && (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0 &&
+                   make_out_map(g, A_PLANAR, &map);
+  if (N <= 128 && stg) return launch_tc_v<N, A_PLANAR, (N <= 128)>(g, map, st);
+  return launch_tc_v<N, A_PLANAR, false>(g, map, st);
 }
 
 int launch_gemm_tc(const GemmArgs& g, bool a_planar, cudaStream_t st) {
@@ -362,7 +487,6 @@ int launch_gemm_tc(const GemmArgs& g, bool a_planar, cudaStream_t st) {
   if (!a_planar)
     return g.N == 192 ? launch_tc<192, false>(g, st)
                       : g.N == 128 ? launch_tc<128, false>(g, st) : launch_tc<64, false>(g, st);
-  if (g.N == 192) return CSSM_ERR_UNSUPPORTED;
   return g.N == 128 ? launch_tc<128, true>(g, st) : launch_tc<64, true>(g, st);
 }
 
@@ -376,7 +500,7 @@ int read_tc_error(int* out) {
 
 extern "C" {
 int cssm_debug_set_gemm_backend(int backend) {
-  if (backend < 0 || backend > 63) return CSSM_ERR_UNSUPPORTED;
+  if (backend < 0 || backend > 255) return CSSM_ERR_UNSUPPORTED;
   cssm::set_force_simt(backend);
   return CSSM_OK;
 }
