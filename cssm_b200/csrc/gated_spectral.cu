@@ -132,10 +132,14 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       if (!tc::mbar_wait(&bars[1 + (t & 1)], (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
       const float* zs = zbuf + (t & 1) * R64_PLANE_F + soff;
       float* y0 = xp + roff;
+      // finish all products before the first store: the stores go through a generic pointer,
+      // so shared-memory loads placed between them could not be hoisted
+#pragma unroll
+      for (int n1 = 0; n1 < 8; ++n1) v[n1] = mk(v[n1].x * zs[8 * n1], v[n1].y * zs[R64_PRS + 8 * n1]);
 #pragma unroll
       for (int n1 = 0; n1 < 8; ++n1) {
-        y0[8 * n1] = v[n1].x * zs[8 * n1];
-        y0[64 + 8 * n1] = v[n1].y * zs[R64_PRS + 8 * n1];
+        y0[8 * n1] = v[n1].x;
+        y0[64 + 8 * n1] = v[n1].y;
       }
     }
     // No barrier needed here: the next iteration writes EX (warp-private) and ZR (last read

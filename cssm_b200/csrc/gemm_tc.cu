@@ -158,8 +158,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
           const int fr = m0 / g.HW;
           px0 = m0 - fr * g.HW;
           const int t = fr % g.T;
-          ct0 = g.rope_t[t * 32 + chunk * 2];
-          ct1 = g.rope_t[t * 32 + chunk * 2 + 1];
+          ct0 = __ldg(&g.rope_t[t * 32 + chunk * 2]);
+          ct1 = __ldg(&g.rope_t[t * 32 + chunk * 2 + 1]);
         }
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
@@ -172,8 +172,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const float2 ct = e ? ct1 : ct0;
-              const float2 ch = g.rope_h[h * 32 + chunk * 2 + e];
-              const float2 cw = g.rope_w[w * 32 + chunk * 2 + e];
+              const float2 ch = __ldg(&g.rope_h[h * 32 + chunk * 2 + e]);
+              const float2 cw = __ldg(&g.rope_w[w * 32 + chunk * 2 + e]);
               const float cx = ct.x * ch.x - ct.y * ch.y, sx = ct.x * ch.y + ct.y * ch.x;
               const float c2 = cx * cw.x - sx * cw.y, s2 = cx * cw.y + sx * cw.x;
               float& xe = e ? v.z : v.x;
@@ -198,7 +198,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
           const int fr = m / g.HW, px = m - fr * g.HW;
           const float* ap = g.A + ((size_t)fr * g.a_planes + g.a_plane0 + kh * 32) * g.HW + px;
 #pragma unroll
-          for (int k = 0; k < 32; ++k) v[k] = ap[(size_t)k * g.HW];
+          for (int k = 0; k < 32; ++k) v[k] = __ldg(ap + (size_t)k * g.HW);
           if (g.rms_scale != nullptr) {
             // the other K half of the row is re-read (cache hit: the partner thread loads it)
             const float* op = g.A + ((size_t)fr * g.a_planes + g.a_plane0 + (1 - kh) * 32) * g.HW + px;
@@ -209,12 +209,12 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
             for (int k = 0; k < 32; ++k) ss = fmaf(v[k], v[k], ss);
             const float rinv = rsqrtf(ss * (1.0f / TC_K) + 1e-6f);
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] *= rinv * g.rms_scale[kh * 32 + k];
+            for (int k = 0; k < 32; ++k) v[k] *= rinv * __ldg(&g.rms_scale[kh * 32 + k]);
           }
           if (g.gate != nullptr) {
             const float* gp = g.gate + ((size_t)fr * g.g_planes + g.g_plane0 + kh * 32) * g.HW + px;
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] *= gp[(size_t)k * g.HW];
+            for (int k = 0; k < 32; ++k) v[k] *= __ldg(gp + (size_t)k * g.HW);
           }
         } else {
 #pragma unroll
@@ -311,22 +311,25 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
           const int act = (g.out_act != 0 && cc * 32 >= g.act_n0) ? g.out_act : 0;
           if (!A_PLANAR) {
             // chunk layout [column j][pixel]: lanes write consecutive pixels (conflict-free)
+            float vals[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               float v = __uint_as_float(r[j]) + bs[j];
               if (act == 1) v = silu_f(v); else if (act == 2) v = sigmoid_f(v);
-              stg[j * 128 + row] = v;
+              vals[j] = v;
             }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) stg[j * 128 + row] = vals[j];
           } else {
             // chunk layout [pixel][32 columns] in the 128-byte swizzle the tensor map expects
+            float vals[32];
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v;
-              v.x = __uint_as_float(r[j + 0]) + bs[j + 0]; v.y = __uint_as_float(r[j + 1]) + bs[j + 1];
-              v.z = __uint_as_float(r[j + 2]) + bs[j + 2]; v.w = __uint_as_float(r[j + 3]) + bs[j + 3];
+            for (int j = 0; j < 32; ++j) vals[j] = __uint_as_float(r[j]) + bs[j];
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
               *reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(stg) +
-                                         tc::sw128_offset(row, j >> 2)) = v;
-            }
+                                         tc::sw128_offset(row, j >> 2)) =
+                  make_float4(vals[j], vals[j + 1], vals[j + 2], vals[j + 3]);
           }
           tc::fence_proxy_async();
           asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
@@ -342,7 +345,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
           }
           continue;
         }
-        if (m < g.M && !(dbg & 1)) {
+        if (m < g.M) {
           if (!A_PLANAR && (dbg & 4)) {
             // experiment only: row-contiguous stores (wrong layout) to time the store pattern
             float* op = g.out + (size_t)m * g.N + cc * 32;
@@ -351,19 +354,25 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
               *reinterpret_cast<float4*>(op + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
                                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
           } else if (!A_PLANAR) {
-            // planar output: lanes = consecutive pixels -> 128-byte coalesced stores per column
+            // planar output: lanes = consecutive pixels -> 128-byte coalesced stores per column.
+            // All 32 values are finished in registers before the first store: the stores go
+            // through a generic pointer, so bias loads placed between them could not be hoisted.
             const int fr = m / g.HW, px = m - fr * g.HW;
             float* op = g.out + ((size_t)fr * g.o_planes + g.o_plane0 + cc * 32) * g.HW + px;
             const float* bs = bias_s + cc * 32;
-            if (g.out_act == 0 || cc * 32 < g.act_n0) {
+            float vals[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) { *op = __uint_as_float(r[j]) + bs[j]; op += g.HW; }
-            } else if (g.out_act == 1) {
+            for (int j = 0; j < 32; ++j) vals[j] = __uint_as_float(r[j]) + bs[j];
+            if (g.out_act == 1 && cc * 32 >= g.act_n0) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) { *op = silu_f(__uint_as_float(r[j]) + bs[j]); op += g.HW; }
-            } else {
+              for (int j = 0; j < 32; ++j) vals[j] = silu_f(vals[j]);
+            } else if (g.out_act == 2 && cc * 32 >= g.act_n0) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) { *op = sigmoid_f(__uint_as_float(r[j]) + bs[j]); op += g.HW; }
+              for (int j = 0; j < 32; ++j) vals[j] = sigmoid_f(vals[j]);
+            }
+            if (!(dbg & 1)) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) op[(size_t)j * g.HW] = vals[j];
             }
           } else {
             float* op = g.out + (size_t)m * g.N + cc * 32;

@@ -288,6 +288,7 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_fast_kernel(const St
       __syncthreads();
     }
     float lsum = 0.f;
+    float4 outv[NP];
 #pragma unroll
     for (int j = 0; j < NP; ++j) {
       const int g4 = tid + j * ST_THREADS;
@@ -351,9 +352,13 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_fast_kernel(const St
         const float* pp = s.post + ((size_t)(b * s.T + t) * HW + (size_t)g4 * 4) * s.post_stride + s.post_off;
         o.x *= pp[0]; o.y *= pp[s.post_stride]; o.z *= pp[2 * s.post_stride]; o.w *= pp[3 * s.post_stride];
       }
-      reinterpret_cast<float4*>(p)[g4] = o;
+      outv[j] = o;
       lsum += (o.x + o.y) + (o.z + o.w);
     }
+    // stores after all shared-memory reads of this step (generic-pointer stores would otherwise
+    // pin the following loads behind them)
+#pragma unroll
+    for (int j = 0; j < NP; ++j) reinterpret_cast<float4*>(p)[tid + j * ST_THREADS] = outv[j];
     if (s.sums) {
       for (int off = 16; off > 0; off >>= 1) lsum += __shfl_down_sync(0xffffffffu, lsum, off);
       if (lane == 0) red[t * 8 + warp] = lsum;
