@@ -1,6 +1,8 @@
 // Fused spectral kernels of the gated block: rfft2 -> gated complex recurrence over T with
 // the state on chip -> irfft2 -> * silu(z) (in_proj already stored the z planes through SiLU).
 // One CTA per (batch, channel) pair.
+#include <cuda.h>
+#include <string.h>
 #include "r64.cuh"
 #include "kernels.cuh"
 #include "tc05.cuh"
@@ -13,22 +15,28 @@ namespace cssm {
 // The x_main plane of step t+1 and the (SiLU'd) z plane of step t+1 are staged in shared memory
 // by TMA bulk copies (one 16 KB copy per plane, issued by a lane of the otherwise idle ninth warp
 // right after the first barrier of step t) and land while step t computes; gate maps and K_hat
-// are loaded at the top of the column phase.  (One copy per 256-byte row into bank-conflict-free
-// padded rows is kept as variant <68>: it measured 20 % slower, the copy engine's per-request
-// cost outweighs the 4-way conflicts of the dense rows.)
+// are loaded at the top of the column phase.  Variant <68> (default) uses one TMA tensor copy per
+// plane whose 68-wide box pads every row to 272 bytes, which makes the row passes' reads
+// bank-conflict free; variant <64> uses untiled bulk copies into dense rows (4-way conflicts).
 constexpr int R64_THREADS = R64_NT;
 constexpr int R64_PLANE_F = 64 * 68;
-constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64_PLANE_F * 4;
+constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64_PLANE_F * 4 + 128;
 
 __device__ int g_spec_error = 0;
-int g_spec_variant = 0;
+int g_spec_variant = 0;      // 0 padded rows via tensor TMA, 1 dense rows via bulk TMA, 2 warp-specialised pipeline
+int launch_gated_spectral_ws(float* xz, const cf* khat, const float* gates, int B, int T, int C,
+                             cudaStream_t st);
 
 template <int PRS>   // floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane)
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
-                   const float4* __restrict__ gates, int T, int C) {
+                   const float4* __restrict__ gates, int T, int C,
+                   const __grid_constant__ CUtensorMap pmap) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  cf* EX = reinterpret_cast<cf*>(smem_raw);
+  // TMA tensor copies need a 128-byte aligned destination; dynamic shared memory is only
+  // guaranteed 16-byte aligned, so the base is rounded up (the launch adds 128 bytes)
+  unsigned char* smem_al = smem_raw + ((128u - (tc::smem_u32(smem_raw) & 127u)) & 127u);
+  cf* EX = reinterpret_cast<cf*>(smem_al);
   float* xbuf = reinterpret_cast<float*>(EX + R64_EX_CF + R64_ZR_CF + R64_GB_CF);
   constexpr int R64_PRS = PRS;
   float* zbuf = xbuf + R64_PLANE_F;                           // two buffers
@@ -53,8 +61,8 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     tc::fence_proxy_async();             // earlier generic reads of the buffers come first
     uint64_t* bz = &bars[1 + (tl & 1)];
     if (c.lane == 0) {
-      if (want_x) tc::mbar_expect_tx(&bars[0], 64 * 256);
-      tc::mbar_expect_tx(bz, 64 * 256);
+      if (want_x) tc::mbar_expect_tx(&bars[0], 64 * PRS * 4);
+      tc::mbar_expect_tx(bz, 64 * PRS * 4);
     }
     __syncwarp();
     const float* xs = x0 + (size_t)tl * fstride;
@@ -66,10 +74,12 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
         tc::bulk_g2s(zd, zs, 64 * 256, bz);
       }
     } else {
-#pragma unroll
-      for (int r = c.lane; r < 64; r += 32) {
-        if (want_x) tc::bulk_g2s(xbuf + r * R64_PRS, xs + r * 64, 256, &bars[0]);
-        tc::bulk_g2s(zd + r * R64_PRS, zs + r * 64, 256, bz);
+      // one tensor copy per plane: the 68-wide box reads 4 columns past the 64-wide rows, which
+      // are out of bounds for the map and arrive as zeros, so the rows land 272 bytes apart
+      if (c.lane == 0) {
+        const int row0 = (int)((xs - xz) >> 6);           // first image row of the plane
+        if (want_x) tc::tma_load_2d(xbuf, &pmap, 0, row0, &bars[0]);
+        tc::tma_load_2d(zd, &pmap, 0, row0 + C * 64, bz);
       }
     }
   };
@@ -271,14 +281,41 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                           float* xz, cudaStream_t st) {
   const SpectralPath path = spectral_path(d.H, d.W);
   const int grid = d.B * d.C;
+  if (path == PATH_R64 && g_spec_variant == 2)
+    return launch_gated_spectral_ws(xz, khat, gates, d.B, d.T, d.C, st);
   if (path == PATH_R64) {
     const size_t smem = R64_SMEM_BYTES;
-    auto kern = g_spec_variant == 1 ? gated_spectral_r64<68> : gated_spectral_r64<64>;
+    // tensor map over the planar buffer as rows of 64 floats; box 68 x 64 (see the kernel)
+    CUtensorMap pmap;
+    memset(&pmap, 0, sizeof(pmap));
+    bool padded = g_spec_variant != 1;
+    if (padded) {
+      typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+      static EncodeFn enc = []() -> EncodeFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+          return nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+      }();
+      const cuuint64_t dims[2] = {64, (cuuint64_t)d.B * d.T * 2 * d.C * 64};
+      const cuuint64_t strides[1] = {256};
+      const cuuint32_t box[2] = {68, 64}, es[2] = {1, 1};
+      padded = enc != nullptr &&
+               enc(&pmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, xz, dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    auto kern = padded ? gated_spectral_r64<68> : gated_spectral_r64<64>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     kern<<<grid, R64_THREADS, smem, st>>>(xz, khat, reinterpret_cast<const float4*>(gates), d.T,
-                                          d.C);
+                                          d.C, pmap);
   } else {
     const size_t smem = generic_smem_bytes(d.H, d.W);
     if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;

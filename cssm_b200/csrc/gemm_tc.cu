@@ -407,7 +407,7 @@ static int g_tc_dbg = 0;      // experiment switches (bit 1: skip epilogue store
 extern int g_spec_variant;
 void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = ((on >> 1) & 3) | (((on >> 4) & 1) << 2) | (((on >> 5) & 1) << 3) | (((on >> 6) & 1) << 4) |
              (((on >> 7) & 1) << 5);
-  g_spec_variant = (on >> 3) & 1; }
+  g_spec_variant = ((on >> 3) & 1) | (((on >> 8) & 1) << 1); }
 
 // Whether the tensor-core kernel covers this problem (else the CUDA-core GEMM runs).
 bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
@@ -509,7 +509,7 @@ int read_tc_error(int* out) {
 
 extern "C" {
 int cssm_debug_set_gemm_backend(int backend) {
-  if (backend < 0 || backend > 255) return CSSM_ERR_UNSUPPORTED;
+  if (backend < 0 || backend > 511) return CSSM_ERR_UNSUPPORTED;
   cssm::set_force_simt(backend);
   return CSSM_OK;
 }
@@ -519,7 +519,11 @@ int cssm_debug_tc_error(int* out) {
   int rc = cssm::read_tc_error(&a);
   if (rc != CSSM_OK) return rc;
   rc = cssm::read_spec_error(&b);
-  *out = a | (b << 8);           // low byte: tensor-core GEMM, next byte: fused spectral kernel
+  if (rc != CSSM_OK) return rc;
+  int c = 0;
+  rc = cssm::read_ws_error(&c);
+  // low byte: tensor-core GEMM, next byte: fused spectral kernel, third: its pipelined variant
+  *out = a | (b << 8) | (c << 16);
   return rc;
 }
 }

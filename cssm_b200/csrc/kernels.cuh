@@ -34,6 +34,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                           float* xz, cudaStream_t st);
 size_t generic_smem_bytes(int H, int W);
 int read_spec_error(int* out);
+int read_ws_error(int* out);
 
 // ---- GDN block ----
 struct GdnDwArgs {

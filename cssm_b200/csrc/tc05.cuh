@@ -48,6 +48,14 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
       ::"r"(smem_u32(smem_dst)), "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes),
         "r"(smem_u32(bar)) : "memory");
 }
+// TMA tensor load global -> shared (2-D box), completion counted in bytes on the mbarrier.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* map, int c0, int c1,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1),
+        "r"(smem_u32(bar)) : "memory");
+}
 // TMA tensor stores shared -> global (bulk_group completion).  `map` is a CUtensorMap passed
 // to the kernel as a __grid_constant__ parameter; coordinates are innermost first.
 __device__ __forceinline__ void tma_store_2d(const void* map, const void* smem_src, int c0, int c1) {

@@ -216,9 +216,10 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
  * cssm_debug_set_gemm_backend: 0 = tensor-core (tcgen05) projections where they apply
  * (default), 1 = CUDA-core fp32 projections everywhere; process-wide, for A/B tests.  Higher
  * bits are timing-experiment switches of the tensor-core kernel (2/4 skip epilogue stores / A
- * loads, 8 per-row TMA staging in the spectral kernel, 16 row-contiguous stores, 32 contiguous
- * tile ranges, 64 no TMA-store epilogue, 128 TMA-store epilogue for planar outputs too); results
- * are only valid with 0, 1, 8, 32, 64 and 128.
+ * loads, 8 dense bulk-TMA staging in the spectral kernel, 16 row-contiguous stores, 32 contiguous
+ * tile ranges, 64 no TMA-store epilogue, 128 TMA-store epilogue for planar outputs too, 256
+ * warp-specialised pipelined spectral kernel); results are only valid with 0, 1, 8, 32, 64, 128
+ * and 256.
  * cssm_debug_tc_error: copies the device-side error code of the tensor-core GEMM (0 = no
  * bounded wait ever expired) to *out; synchronises the device. */
 int cssm_debug_set_gemm_backend(int backend);

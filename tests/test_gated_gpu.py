@@ -159,3 +159,21 @@ def test_tensor_core_projections_c64(rope):
     # stage level: the planar x_main / z planes straight out of in_proj
     z = xz[:, :, C:].transpose(0, 1, 3, 4, 2)
     assert orc.rel_l2(z, orc.silu(inter["z"])) <= 2e-6
+
+
+def test_spectral_kernel_variants_agree_bitwise():
+    """The three implementations of the 64x64 fused spectral kernel (padded tensor-TMA staging,
+    dense bulk-TMA staging, warp-specialised pipeline) run the same arithmetic in the same order:
+    identical bits, and no bounded wait expires in any of them."""
+    bound, xd, ref, _ = _run(2, 5, 64, 64, 8, 11, "factored", "spatiotemporal", 3, 4)
+    L = bound.L
+    outs = []
+    try:
+        for flag in (0, 8, 256):
+            assert L.cssm_debug_set_gemm_backend(flag) == 0
+            outs.append(bound(xd).clone())
+            assert _tc_error(L) == 0
+    finally:
+        assert L.cssm_debug_set_gemm_backend(0) == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert orc.rel_l2(outs[0].cpu().numpy(), ref) <= TOL
