@@ -253,6 +253,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-chunk", type=int, default=8, help="images per host<->device chunk")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
@@ -369,7 +370,7 @@ def main():
     # end to end through the host-buffer entry point (pinned host memory)
     e2e = None
     if not args.no_e2e:
-        chunk = min(16, B)
+        chunk = min(args.e2e_chunk, B)
         xh = x_host.pin_memory()
         yh = torch.empty_like(xh).pin_memory()
         n = L.cssm_gated_host_workspace_bytes(C.byref(d), chunk)
