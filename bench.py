@@ -30,6 +30,12 @@ WORKLOADS = {
     # small case for profiler captures (activations 134 MB > L2, < 1 GB on the device)
     "cfg2_small": dict(B=16, T=8, H=64, W=64, C=64, kernel_size=11, gate_type="factored",
                        rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
+    # BASELINE.json configs[0] (main.py defaults: dense gates, 2 stem layers -> 32x32), batch 8
+    "cfg1": dict(B=8, T=1, H=32, W=32, C=64, kernel_size=1, gate_type="dense",
+                 rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
+    # 32x32 planes at a bandwidth-relevant size (the gated block on the block-input shape of cfg 4)
+    "gated32": dict(B=128, T=32, H=32, W=32, C=64, kernel_size=11, gate_type="factored",
+                    rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
     # BASELINE.json configs[2]: GDN-SCSSM, ks 11, qkv_conv 5, d_k 4, T=8, C=64, RMSNorm, mrope
     "cfg3": dict(block="gdn", B=128, T=8, H=64, W=64, C=64, kernel_size=11, gate_type="factored",
                  rope_mode="mrope", short_conv_size=4, qkv_conv_size=5, delta_key_dim=4),
@@ -356,7 +362,7 @@ def main():
     peak, peak_src = peaks()
     alg_bytes = 12.0 * H * W * B * T * Cc
     achieved = alg_bytes / (stage_ms["spectral"] / 1e3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gated_spectral_r64", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": "gated_spectral_r64" if H == 64 else "gated_spectral_r32", "achieved": achieved, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8TBps": achieved / 8000.0, "traffic": None,
                 "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": stage_ms["spectral"]}

@@ -20,6 +20,7 @@ int check_launch() {
 
 SpectralPath spectral_path(int H, int W) {
   if (H == 64 && W == 64) return PATH_R64;
+  if (H == 32 && W == 32) return PATH_R32;
   return PATH_GENERIC;
 }
 

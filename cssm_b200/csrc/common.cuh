@@ -81,12 +81,13 @@ struct GatedPlan {
 GatedPlan gated_plan_layout(const cssm_gated_desc& d);
 
 // Which spectral kernel handles an (H, W) plane.
-enum SpectralPath { PATH_GENERIC = 0, PATH_R64 = 1 };
+enum SpectralPath { PATH_GENERIC = 0, PATH_R64 = 1, PATH_R32 = 2 };
 SpectralPath spectral_path(int H, int W);
 
 // Position of frequency bin (kh, kw) inside a per-(b,t) gate map / per-channel K_hat.
 __host__ __device__ inline int bin_index(int path, int kh, int kw, int H, int Wf) {
   if (path == PATH_R64) return (((kh >> 3) * 33 + kw) << 3) + (kh & 7);
+  if (path == PATH_R32) return ((((((kh >> 2) & 1) << 2) | (kh >> 3)) * 17 + kw) << 2) + (kh & 3);
   return kh * Wf + kw;
 }
 

@@ -24,6 +24,8 @@ constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64
 
 __device__ int g_spec_error = 0;
 int g_spec_variant = 0;      // 0 padded rows via tensor TMA, 1 dense rows via bulk TMA, 2 warp-specialised pipeline
+int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
+                              cudaStream_t st);
 int launch_gated_spectral_ws(float* xz, const cf* khat, const float* gates, int B, int T, int C,
                              cudaStream_t st);
 
@@ -281,6 +283,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                           float* xz, cudaStream_t st) {
   const SpectralPath path = spectral_path(d.H, d.W);
   const int grid = d.B * d.C;
+  if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, st);
   if (path == PATH_R64 && g_spec_variant == 2)
     return launch_gated_spectral_ws(xz, khat, gates, d.B, d.T, d.C, st);
   if (path == PATH_R64) {

@@ -35,6 +35,8 @@ CASES = [
     (3, 2, 7, 7, 12, 1, "factored", "none", 0, 4),
     (1, 3, 14, 14, 16, 3, "factored", "spatial_only", 3, 0),
     (2, 2, 32, 32, 8, 11, "dense", "temporal", 3, 4),
+    (3, 5, 32, 32, 12, 11, "factored", "spatiotemporal", 3, 4),   # 32x32 radix kernel, 3 channel groups
+    (8, 1, 32, 32, 64, 1, "dense", "spatiotemporal", 3, 4),       # BASELINE configs[0] shape (2 stem layers)
     (1, 2, 6, 10, 4, 3, "factored", "spatiotemporal", 3, 4),
     (1, 2, 4, 4, 4, 11, "dense", "none", 3, 2),      # kernel larger than the plane: crop
 ]
