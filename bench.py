@@ -295,7 +295,10 @@ def main():
 
     # synthetic block input: stem features of seeded stroke images (16 distinct images per
     # rank, tiled to the batch), disjoint seeds per rank
-    base = synth.stem_features(synth.stroke_batch(16, seed0=1000 + 16 * rank), T, Cc)
+    stem_layers = {64: 1, 32: 2}[H]          # 128x128 stroke images, one 2x pool per stem layer
+    base = synth.stem_features(synth.stroke_batch(16, seed0=1000 + 16 * rank), T, Cc,
+                               layers=stem_layers)
+    assert base.shape[2:4] == (H, W)
     x_host = torch.from_numpy(np.tile(base, (B // 16 + 1, 1, 1, 1, 1))[:B]).contiguous()
     x = x_host.to(dev)
     y = torch.empty_like(x)
