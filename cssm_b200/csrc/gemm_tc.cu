@@ -107,27 +107,30 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
   if (warp < 8 && tid < NPROD) {
     // ================================ producers ================================
     int it = 0;
-    // channels-last mode: warp w owns the 16-byte chunks 2w and 2w+1 (channel pairs 4w..4w+3)
-    // of every row, lane = (row & 15) * 2 + (chunk & 1); rows rsub + 16*r, r = 0..7.  All lanes
-    // of a warp rotate (or skip) the same channel pairs, and a load instruction still touches
-    // whole 32-byte sectors.  The registers `pre` always hold the NEXT tile's values.
+    // channels-last mode: the 128 x 16 float4 chunks of a tile are walked in two halves of four
+    // iterations: iteration r covers chunk (tid & 7) + 8*(r >> 2) of row (tid >> 3) + 32*(r & 3),
+    // so a warp load touches four rows x 128 contiguous bytes.  RoPE only rotates the low channel
+    // pairs in most modes: a lane rotates in the half whose chunk holds a rotated pair, which
+    // spreads the rotation evenly over all eight warps.  `pre` always holds the NEXT tile.
     float4 pre[8];
-    const int chunk = 2 * warp + (lane & 1), rsub = lane >> 1;
-    bool rot = false;
+    const int chunk_lo = tid & 7, rsub = tid >> 3;
+    bool rot[2] = {false, false};
     if (!A_PLANAR) {
       const int m0 = t_first * TC_BM;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const int m = m0 + rsub + 16 * r;
-        pre[r] = (t_first < t_end && m < g.M)
+        const int m = m0 + rsub + 32 * (r & 3);
+        const int chunk = chunk_lo + 8 * (r >> 2);
+        pre[r] = (t_first < t_end && m < g.M && !(dbg & 2))
                      ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
                      : make_float4(0.f, 0.f, 0.f, 0.f);
       }
       if (g.rope_t != nullptr) {
-        // warp-uniform: does any of the warp's four channel pairs rotate at all?
-        rot = g.rope_nz == nullptr;
-        if (!rot)
-          for (int e = 0; e < 4; ++e) rot = rot || g.rope_nz[4 * warp + e] != 0.f;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int pi = 2 * (chunk_lo + 8 * hf);
+          rot[hf] = g.rope_nz == nullptr || g.rope_nz[pi] != 0.f || g.rope_nz[pi + 1] != 0.f;
+        }
       }
     }
     const float invW = 1.0f / (float)g.W;
@@ -142,7 +145,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
         if (nt < t_end) {
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
-            const int m = nt * TC_BM + rsub + 16 * r;
+            const int m = nt * TC_BM + rsub + 32 * (r & 3);
+            const int chunk = chunk_lo + 8 * (r >> 2);
             pre[r] = (m < g.M && !(dbg & 2)) ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
                              : make_float4(0.f, 0.f, 0.f, 0.f);
           }
@@ -152,26 +156,24 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
       unsigned char* a_hi = smem + L::A_OFF + (uint32_t)s * 2u * TC_A_HALF;
       unsigned char* a_lo = a_hi + TC_A_HALF;
       if (!A_PLANAR) {
-        float2 ct0 = make_float2(1.f, 0.f), ct1 = ct0;
-        int px0 = 0;
-        if (rot) {
+        int px0 = 0, t = 0;
+        if (rot[0] || rot[1]) {
           const int fr = m0 / g.HW;
           px0 = m0 - fr * g.HW;
-          const int t = fr % g.T;
-          ct0 = __ldg(&g.rope_t[t * 32 + chunk * 2]);
-          ct1 = __ldg(&g.rope_t[t * 32 + chunk * 2 + 1]);
+          t = fr % g.T;
         }
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-          const int row = rsub + 16 * r;
+          const int row = rsub + 32 * (r & 3);
+          const int chunk = chunk_lo + 8 * (r >> 2);
           float4 v = cur[r];
-          if (rot) {
+          if (rot[r >> 2]) {
             const int px = px0 + row;
             const int h = (int)(((float)px + 0.5f) * invW);     // exact for px < 2^22
             const int w = px - h * g.W;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const float2 ct = e ? ct1 : ct0;
+              const float2 ct = __ldg(&g.rope_t[t * 32 + chunk * 2 + e]);
               const float2 ch = __ldg(&g.rope_h[h * 32 + chunk * 2 + e]);
               const float2 cw = __ldg(&g.rope_w[w * 32 + chunk * 2 + e]);
               const float cx = ct.x * ch.x - ct.y * ch.y, sx = ct.x * ch.y + ct.y * ch.x;
