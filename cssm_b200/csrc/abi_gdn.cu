@@ -6,7 +6,8 @@
 namespace cssm {
 
 static SpectralPath gdn_path(const cssm_gdn_desc& d) {
-  return (spectral_path(d.H, d.W) == PATH_R64 && d.delta_key_dim == 4) ? PATH_R64 : PATH_GENERIC;
+  const SpectralPath p = spectral_path(d.H, d.W);
+  return (p != PATH_GENERIC && d.delta_key_dim == 4) ? p : PATH_GENERIC;
 }
 
 struct GdnPlan { size_t what, rope_t, rope_h, rope_w, rope_nz, tcode, total; };

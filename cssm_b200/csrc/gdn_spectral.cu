@@ -180,10 +180,12 @@ size_t gdn_generic_smem_bytes(int H, int W, int dk) {
 }
 
 int launch_gdn_spectral_r64(const GdnSpectralArgs& a, cudaStream_t st);
+int launch_gdn_spectral_r32(const GdnSpectralArgs& a, cudaStream_t st);
 
 int launch_gdn_spectral(const GdnSpectralArgs& a, cudaStream_t st) {
   if (a.dk < 1 || a.dk > GDN_MAXDK || a.C % a.dk != 0) return CSSM_ERR_UNSUPPORTED;
   if (spectral_path(a.H, a.W) == PATH_R64 && a.dk == 4) return launch_gdn_spectral_r64(a, st);
+  if (spectral_path(a.H, a.W) == PATH_R32 && a.dk == 4) return launch_gdn_spectral_r32(a, st);
   const size_t smem = gdn_generic_smem_bytes(a.H, a.W, a.dk);
   if (smem > 220 * 1024) return CSSM_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(gdn_spectral_generic,

@@ -35,7 +35,8 @@ CASES = [
     (2, 3, 8, 8, 8, 4, 5, "factored", "mrope", 4, 5),
     (1, 4, 8, 8, 8, 2, 3, "dense", "none", 4, 1),
     (2, 2, 6, 10, 12, 3, 3, "factored", "spatiotemporal", 2, 3),
-    (1, 3, 32, 32, 8, 4, 11, "factored", "mrope", 4, 1),
+    (1, 3, 32, 32, 8, 4, 11, "factored", "mrope", 4, 1),       # 32x32 radix kernel, state on chip
+    (2, 5, 32, 32, 16, 4, 11, "dense", "spatiotemporal", 4, 3),
     (2, 3, 64, 64, 8, 4, 11, "factored", "mrope", 4, 5),
     (1, 8, 64, 64, 4, 4, 11, "dense", "none", 4, 1),
     (1, 2, 64, 64, 8, 2, 11, "factored", "none", 0, 1),      # 64x64 with d_k=2: generic kernel
