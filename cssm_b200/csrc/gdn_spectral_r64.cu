@@ -42,6 +42,16 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
     wh[q] = c.col_on ? a.what[(size_t)hd * NB + ((q * 33 + c.grp) << 3) + c.a] : mk(0.f, 0.f);
   const float invHW = 1.0f / (float)HW;
 
+  // plane idx 0..3 = q, 4..7 = k, 8..11 = v of step t; idx 12 = first plane of step t + 1
+  auto plane_of = [&](int t, int idx) -> float* {
+    if (idx >= 12) { idx -= 12; ++t; }
+    if (t >= a.T) { t = a.T - 1; idx = 0; }                 // harmless re-read past the end
+    const size_t frame = (size_t)(b * a.T + t);
+    return a.qkv + (frame * 3 * a.C + (size_t)(idx >> 2) * a.C + hd * DK + (idx & 3)) * HW;
+  };
+  cf nx[8];                                   // rows of the NEXT plane, fetched one pass ahead
+  r64_load_rows(c, plane_of(0, 0), nx);
+
   for (int t = 0; t < a.T; ++t) {
     const size_t frame = (size_t)(b * a.T + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
@@ -49,9 +59,14 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
     // ---- q planes (p = 0..3) and k planes (p = 4..7) ----
 #pragma unroll 1
     for (int p = 0; p < 8; ++p) {
-      const float* plane = base + (size_t)((p < 4 ? 0 : a.C) + hd * DK + (p & 3)) * HW;
       __syncthreads();                       // ZR free (previous column pass finished)
-      r64_row_fwd(c, plane);
+      {
+        cf cur[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) cur[m] = nx[m];
+        r64_load_rows(c, plane_of(t, p + 1), nx);
+        r64_row_fwd_regs(c, cur);
+      }
       __syncthreads();
       float acc = 0.f;
       if (c.col_warp) {
@@ -104,9 +119,28 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
     for (int vr = 0; vr < DK; ++vr) {
       float* vplane = base + (size_t)(2 * a.C + hd * DK + vr) * HW;
       __syncthreads();                       // ZR free; GB reads of the previous row finished
-      r64_row_fwd(c, vplane);
+      {
+        cf cur[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) cur[m] = nx[m];
+        r64_load_rows(c, plane_of(t, 8 + vr + 1), nx);
+        r64_row_fwd_regs(c, cur);
+      }
       __syncthreads();
       if (c.col_warp) {
+        // the state row of all 8 bins is fetched before the transform (the scratch is only
+        // L2-resident) and written back after the last bin, so the loads are not pinned behind
+        // the stores of the previous bin
+        cf sreg[8][4];
+        float2 gab[8];
+        cf* srow = S + (size_t)(vr * DK) * NB + cslot;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            sreg[q][i] = c.col_on ? srow[(size_t)i * NB + q * 264] : mk(0.f, 0.f);
+          gab[q] = c.col_on ? __ldg(abp + q * (33 * 8)) : make_float2(0.f, 0.f);
+        }
         cf v[8];
         r64_col_fwd(c, v);
 #pragma unroll
@@ -117,14 +151,15 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
             qq[i] = SPEC[(i * 8 + q) * R64_NT + tid];
             kk[i] = SPEC[((4 + i) * 8 + q) * R64_NT + tid];
           }
-          cf o = mk(0.f, 0.f);
-          if (c.col_on) {
-            const float2 g = abp[q * (33 * 8)];
-            const cf aw = mk(g.x * wh[q].x, g.x * wh[q].y);
-            o = gdn_bin_update_r64(S + (size_t)(vr * DK) * NB + q * 264 + cslot, NB, kk, qq, v[q],
-                                   aw, g.y);
-          }
+          const cf aw = mk(gab[q].x * wh[q].x, gab[q].x * wh[q].y);
+          const cf o = gdn_bin_update_regs<4>(sreg[q], kk, qq, v[q], aw, gab[q].y);
           v[q] = mk(o.x * invHW, o.y * invHW);
+        }
+        if (c.col_on) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) srow[(size_t)i * NB + q * 264] = sreg[q][i];
         }
         r64_col_inv(c, v);
       }

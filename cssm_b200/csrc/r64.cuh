@@ -51,6 +51,23 @@ __device__ __forceinline__ void r64_row_fwd(const R64Ctx& c, const float* __rest
   }
 }
 
+// the same with the row values already in registers: v[m] = (x[2*grp][a+8m], x[2*grp+1][a+8m])
+__device__ __forceinline__ void r64_row_fwd_regs(const R64Ctx& c, cf (&v)[8]) {
+  if (c.row_on) {
+    fft64_lane8<false>(v, c.tw, c.exg, c.a);
+#pragma unroll
+    for (int k2 = 0; k2 < 8; ++k2) c.ZR[c.grp * R64_ZRS + c.a + 8 * k2] = v[k2];
+  }
+}
+__device__ __forceinline__ void r64_load_rows(const R64Ctx& c, const float* __restrict__ plane,
+                                              cf (&v)[8]) {
+  if (c.row_on) {
+    const float* r0 = plane + (2 * c.grp) * 64 + c.a;
+#pragma unroll
+    for (int m = 0; m < 8; ++m) v[m] = mk(r0[8 * m], r0[64 + 8 * m]);
+  }
+}
+
 // columns: Hermitian separation folded into the loads, then the column FFT.
 // Only meaningful when c.col_warp; lanes with !col_on compute on in-bounds scratch.
 __device__ __forceinline__ void r64_col_fwd(const R64Ctx& c, cf (&v)[8]) {
