@@ -211,7 +211,7 @@ int cssm_gated_spectral(const cssm_gated_desc* d, const void* plan, const float*
   if (!plan || !gate_maps || !xz) return CSSM_ERR_NULL;
   if (!aligned16(plan) || !aligned16(gate_maps) || !aligned16(xz)) return CSSM_ERR_ALIGN;
   const GatedPlan p = gated_plan_layout(*d);
-  return launch_gated_spectral(*d, (const cf*)((const char*)plan + p.khat), gate_maps, xz,
+  return launch_gated_spectral(*d, (const cf*)((const char*)plan + p.khat), gate_maps, xz, 0,
                                (cudaStream_t)stream);
 }
 
@@ -231,15 +231,15 @@ int cssm_gated_out_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, c
   return launch_gemm<true, false>(g, (cudaStream_t)stream);
 }
 
-int cssm_gated_forward(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
-                       const float* x, float* y, void* workspace, size_t workspace_bytes,
-                       void* stream) {
+static int gated_forward_impl(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                              const void* plan, const float* x, float* y, void* workspace,
+                              size_t workspace_bytes, void* stream, int last_only) {
   int s = validate(d);
   if (s != CSSM_OK) return s;
   s = validate_weights(d, w);
   if (s != CSSM_OK) return s;
   if (!plan || !x || !y || !workspace) return CSSM_ERR_NULL;
-  if (!aligned16(workspace)) return CSSM_ERR_ALIGN;
+  if (!aligned16(workspace) || !aligned16(plan) || !aligned16(x) || !aligned16(y)) return CSSM_ERR_ALIGN;
   cssm_gated_ws_layout l;
   ws_layout(*d, &l);
   if (workspace_bytes < l.total) return CSSM_ERR_WORKSPACE;
@@ -250,8 +250,36 @@ int cssm_gated_forward(const cssm_gated_desc* d, const cssm_gated_weights* w, co
   if ((s = cssm_gated_in_proj(d, w, plan, x, xz, stream)) != CSSM_OK) return s;
   if ((s = cssm_gated_short_conv(d, w, xz, ctx, stream)) != CSSM_OK) return s;
   if ((s = cssm_gated_gates(d, w, ctx, gm, stream)) != CSSM_OK) return s;
-  if ((s = cssm_gated_spectral(d, plan, gm, xz, stream)) != CSSM_OK) return s;
-  return cssm_gated_out_proj(d, w, xz, y, stream);
+  if (!last_only) {
+    if ((s = cssm_gated_spectral(d, plan, gm, xz, stream)) != CSSM_OK) return s;
+    return cssm_gated_out_proj(d, w, xz, y, stream);
+  }
+  const GatedPlan p = gated_plan_layout(*d);
+  s = launch_gated_spectral(*d, (const cf*)((const char*)plan + p.khat), gm, xz, 1,
+                            (cudaStream_t)stream);
+  if (s != CSSM_OK) return s;
+  // out_proj of the last frame of every batch element only
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.M = d->B * d->H * d->W; g.N = d->C; g.K = d->C; g.HW = d->H * d->W;
+  g.A = xz; g.a_planes = 2 * d->C; g.a_plane0 = 0;
+  g.a_fmul = d->T; g.a_fadd = d->T - 1;
+  g.Wk = w->out_proj_kernel; g.bias = w->out_proj_bias;
+  g.out = y;
+  g.T = 1; g.H = d->H; g.W = d->W;
+  return launch_gemm<true, false>(g, (cudaStream_t)stream);
+}
+
+int cssm_gated_forward(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
+                       const float* x, float* y, void* workspace, size_t workspace_bytes,
+                       void* stream) {
+  return gated_forward_impl(d, w, plan, x, y, workspace, workspace_bytes, stream, 0);
+}
+
+int cssm_gated_forward_last(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
+                            const float* x, float* y_last, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  return gated_forward_impl(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1);
 }
 
 }  // extern "C"

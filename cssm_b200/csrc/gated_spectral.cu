@@ -25,14 +25,14 @@ constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64
 __device__ int g_spec_error = 0;
 int g_spec_variant = 0;      // 0 padded rows via tensor TMA, 1 dense rows via bulk TMA, 2 warp-specialised pipeline
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
-                              cudaStream_t st);
+                              int last_only, cudaStream_t st);
 int launch_gated_spectral_ws(float* xz, const cf* khat, const float* gates, int B, int T, int C,
                              cudaStream_t st);
 
 template <int PRS>   // floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane)
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
-                   const float4* __restrict__ gates, int T, int C,
+                   const float4* __restrict__ gates, int T, int C, int last_only,
                    const __grid_constant__ CUtensorMap pmap) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // TMA tensor copies need a 128-byte aligned destination; dynamic shared memory is only
@@ -60,11 +60,12 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
   // stage step `tl`: x_main plane into xbuf (if want_x) and z plane into zbuf[tl & 1]
   auto stage = [&](int tl, bool want_x) {
     if (c.warp != 8) return;
+    const bool want_z = !last_only || tl == T - 1;
     tc::fence_proxy_async();             // earlier generic reads of the buffers come first
     uint64_t* bz = &bars[1 + (tl & 1)];
     if (c.lane == 0) {
       if (want_x) tc::mbar_expect_tx(&bars[0], 64 * PRS * 4);
-      tc::mbar_expect_tx(bz, 64 * PRS * 4);
+      if (want_z) tc::mbar_expect_tx(bz, 64 * PRS * 4);
     }
     __syncwarp();
     const float* xs = x0 + (size_t)tl * fstride;
@@ -73,7 +74,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     if (PRS == 64) {
       if (c.lane == 0) {
         if (want_x) tc::bulk_g2s(xbuf, xs, 64 * 256, &bars[0]);
-        tc::bulk_g2s(zd, zs, 64 * 256, bz);
+        if (want_z) tc::bulk_g2s(zd, zs, 64 * 256, bz);
       }
     } else {
       // one tensor copy per plane: the 68-wide box reads 4 columns past the 64-wide rows, which
@@ -81,7 +82,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       if (c.lane == 0) {
         const int row0 = (int)((xs - xz) >> 6);           // first image row of the plane
         if (want_x) tc::tma_load_2d(xbuf, &pmap, 0, row0, &bars[0]);
-        tc::tma_load_2d(zd, &pmap, 0, row0 + C * 64, bz);
+        if (want_z) tc::tma_load_2d(zd, &pmap, 0, row0 + C * 64, bz);
       }
     }
   };
@@ -96,6 +97,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
   for (int t = 0; t < T; ++t) {
     const size_t frame = (size_t)(b * T + t);
     float* xp = xz + (frame * 2 * C + ch) * HW;
+    const bool emit = !last_only || t == T - 1;       // same for the whole CTA
 
     // ---- forward rows (from the staged plane) ----
     if (c.row_on) {
@@ -133,15 +135,16 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
         hst[q] = h;
         v[q] = mk(g[q].z * h.x, g[q].z * h.y);
       }
-      r64_col_inv(c, v);
+      if (emit) r64_col_inv(c, v);
     }
     __syncthreads();
 
     // ---- inverse rows, * staged silu(z), store ----
-    if (c.row_on) {
+    if (c.row_on && emit) {
       cf v[8];
       r64_row_inv(c, v);
-      if (!tc::mbar_wait(&bars[1 + (t & 1)], (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
+      // in last-only mode the z barrier of this slot completes exactly once (phase 0)
+      if (!tc::mbar_wait(&bars[1 + (t & 1)], last_only ? 0 : (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
       const float* zs = zbuf + (t & 1) * R64_PLANE_F + soff;
       float* y0 = xp + roff;
       // finish all products before the first store: the stores go through a generic pointer,
@@ -174,7 +177,7 @@ constexpr int GEN_THREADS = 256;
 
 __global__ void __launch_bounds__(GEN_THREADS)
 gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
-                       const float4* __restrict__ gates, int T, int C, int H, int W) {
+                       const float4* __restrict__ gates, int T, int C, int H, int W, int last_only) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Wf = W / 2 + 1, HW = H * W, NB = H * Wf;
   float* xs = reinterpret_cast<float*>(smem_raw);              // [H][W]
@@ -238,6 +241,7 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
       St[o] = hs;
       Fb[o] = mk(g.z * hs.x, g.z * hs.y);
     }
+    if (last_only && t != T - 1) continue;        // uniform: the next step starts with a barrier
     __syncthreads();
     // inverse columns: R[h][kw] = sum_kh F[kh][kw] e^{+2 pi i h kh / H}
     for (int o = tid; o < NB; o += GEN_THREADS) {
@@ -280,11 +284,11 @@ size_t generic_smem_bytes(int H, int W) {
 }
 
 int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float* gates,
-                          float* xz, cudaStream_t st) {
+                          float* xz, int last_only, cudaStream_t st) {
   const SpectralPath path = spectral_path(d.H, d.W);
   const int grid = d.B * d.C;
-  if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, st);
-  if (path == PATH_R64 && g_spec_variant == 2)
+  if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, last_only, st);
+  if (path == PATH_R64 && g_spec_variant == 2 && !last_only)
     return launch_gated_spectral_ws(xz, khat, gates, d.B, d.T, d.C, st);
   if (path == PATH_R64) {
     const size_t smem = R64_SMEM_BYTES;
@@ -318,7 +322,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                                          (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     kern<<<grid, R64_THREADS, smem, st>>>(xz, khat, reinterpret_cast<const float4*>(gates), d.T,
-                                          d.C, pmap);
+                                          d.C, last_only, pmap);
   } else {
     const size_t smem = generic_smem_bytes(d.H, d.W);
     if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
@@ -326,7 +330,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     gated_spectral_generic<<<grid, GEN_THREADS, smem, st>>>(
-        xz, khat, reinterpret_cast<const float4*>(gates), d.T, d.C, d.H, d.W);
+        xz, khat, reinterpret_cast<const float4*>(gates), d.T, d.C, d.H, d.W, last_only);
   }
   return check_launch();
 }

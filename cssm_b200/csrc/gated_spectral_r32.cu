@@ -19,7 +19,7 @@ constexpr int R32_SMEM_BYTES = (R32_EX_CF + R32_ZR_CF + R32_GB_CF) * 8;
 
 __global__ void __launch_bounds__(R32_THREADS, 2)
 gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
-                   const float4* __restrict__ gates, int T, int C) {
+                   const float4* __restrict__ gates, int T, int C, int last_only) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
   cf* ZR = EX + R32_EX_CF;
@@ -58,6 +58,7 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
     const size_t frame = (size_t)(b * T + t);
     float* xp = xz + (frame * 2 * C + c0 + rpl) * HW;           // row role's plane
     const float* zp = xp + (size_t)C * HW;
+    const bool emit = !last_only || t == T - 1;                  // same for the whole CTA
 
     // ---- forward rows ----
     if (row_on) {
@@ -103,16 +104,18 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
         hst[r] = h;
         v[r] = mk(g[r].z * h.x, g[r].z * h.y);
       }
-      fft32_inv(v, tw, exg, q);
-      cf* gb = GB + (cpl * 32) * R32_GBS;
+      if (emit) {
+        fft32_inv(v, tw, exg, q);
+        cf* gb = GB + (cpl * 32) * R32_GBS;
 #pragma unroll
-      for (int m = 0; m < 8; ++m)
-        if (col_on) gb[(q + 4 * m) * R32_GBS + kw] = v[m];
+        for (int m = 0; m < 8; ++m)
+          if (col_on) gb[(q + 4 * m) * R32_GBS + kw] = v[m];
+      }
     }
     __syncthreads();
 
     // ---- inverse rows (C2R; imaginary parts of the DC and Nyquist columns ignored) ----
-    if (row_on) {
+    if (row_on && emit) {
       float ze[8], zo[8];
       const float* z0 = zp + roff;
 #pragma unroll
@@ -144,12 +147,12 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
 }
 
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
-                              cudaStream_t st) {
+                              int last_only, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(gated_spectral_r32,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, R32_SMEM_BYTES);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   gated_spectral_r32<<<B * (C / 4), R32_THREADS, R32_SMEM_BYTES, st>>>(
-      xz, khat, reinterpret_cast<const float4*>(gates), T, C);
+      xz, khat, reinterpret_cast<const float4*>(gates), T, C, last_only);
   return check_launch();
 }
 

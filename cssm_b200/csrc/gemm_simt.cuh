@@ -13,6 +13,7 @@ struct GemmArgs {
   int M, N, K, HW;
   const float* A;         // channels-last: (M, K).  planar: plane (frame*a_planes + a_plane0 + k)
   int a_planes, a_plane0;
+  int a_fmul, a_fadd;     // planar A: source frame of output frame f is f*a_fmul + a_fadd (0,0 = f)
   const float* Wk;        // (K, N) row-major
   const float* bias;      // (N) or nullptr
   float* out;             // channels-last (M, N) or planar plane (frame*o_planes + o_plane0 + n)
@@ -28,6 +29,10 @@ struct GemmArgs {
   int out_act;              // 0 none, 1 silu, 2 sigmoid; applied to output columns n >= act_n0
   int act_n0;
 };
+
+__host__ __device__ inline int gemm_src_frame(const GemmArgs& g, int f) {
+  return g.a_fmul == 0 && g.a_fadd == 0 ? f : f * g.a_fmul + g.a_fadd;
+}
 
 constexpr int GEMM_BM = 128, GEMM_BK = 16, GEMM_THREADS = 256;
 
@@ -57,7 +62,7 @@ gemm_simt_kernel(const GemmArgs g) {
       const int m = m0 + tid;
       float ss = 0.f;
       if (m < g.M) {
-        const int fr = m / g.HW, px = m % g.HW;
+        const int fr = gemm_src_frame(g, m / g.HW), px = m % g.HW;
         const float* ap = g.A + ((size_t)fr * g.a_planes + g.a_plane0) * g.HW + px;
         for (int k = 0; k < g.K; ++k) { const float v = ap[(size_t)k * g.HW]; ss += v * v; }
       }
@@ -76,7 +81,7 @@ gemm_simt_kernel(const GemmArgs g) {
         const int m = m0 + mm, k = k0 + kk;
         float v = 0.f;
         if (m < g.M && k < g.K) {
-          const int fr = m / g.HW, px = m % g.HW;
+          const int fr = gemm_src_frame(g, m / g.HW), px = m % g.HW;
           v = g.A[((size_t)fr * g.a_planes + g.a_plane0 + k) * g.HW + px];
           if (g.rms_scale != nullptr) v *= rinv[mm] * g.rms_scale[k];
           if (g.gate != nullptr)

@@ -197,7 +197,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
         const int row = tid & 127, kh = tid >> 7, m = m0 + row;
         float v[32];
         if (m < g.M) {
-          const int fr = m / g.HW, px = m - fr * g.HW;
+          const int fo = m / g.HW, px = m - fo * g.HW;
+          const int fr = gemm_src_frame(g, fo);
           const float* ap = g.A + ((size_t)fr * g.a_planes + g.a_plane0 + kh * 32) * g.HW + px;
 #pragma unroll
           for (int k = 0; k < 32; ++k) v[k] = __ldg(ap + (size_t)k * g.HW);

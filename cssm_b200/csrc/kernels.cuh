@@ -30,8 +30,10 @@ struct GatedGateArgs {
 };
 int launch_gated_gates(const GatedGateArgs& g, cudaStream_t st);
 
+// last_only != 0: only the last step's output plane is produced (inverse transforms, the z
+// plane and the stores of earlier steps are skipped; the recurrence still runs over all T)
 int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float* gates,
-                          float* xz, cudaStream_t st);
+                          float* xz, int last_only, cudaStream_t st);
 size_t generic_smem_bytes(int H, int W);
 int read_spec_error(int* out);
 int read_ws_error(int* out);

@@ -221,17 +221,26 @@ class BoundGated:
     def desc(self, shape) -> GatedDesc:
         return self.mod._desc(shape)
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 last_frame_only: bool = False) -> torch.Tensor:
+        """y = block(x).  With last_frame_only=True returns block(x)[:, -1] of shape (B,H,W,C)
+        without computing the earlier output frames (for callers that read only the final
+        frame, as SimpleCSSM with frame_readout='last' and CSSMSHViTBlock do)."""
         _require_cuda(x)
         x = x.contiguous()
         d = self.desc(tuple(x.shape))
         pl = self.plan(d)
         n = self.L.cssm_gated_workspace_bytes(C.byref(d))
         ws = self.buf.get("ws", n)
-        y = torch.empty_like(x) if out is None else out
-        check(self.L.cssm_gated_forward(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(),
-                                        y.data_ptr(), ws.data_ptr(), n, _stream_ptr(self.device)),
-              "cssm_gated_forward")
+        if last_frame_only:
+            B, T, H, W, Cc = x.shape
+            y = torch.empty((B, H, W, Cc), dtype=x.dtype, device=x.device) if out is None else out
+            fn, what = self.L.cssm_gated_forward_last, "cssm_gated_forward_last"
+        else:
+            y = torch.empty_like(x) if out is None else out
+            fn, what = self.L.cssm_gated_forward, "cssm_gated_forward"
+        check(fn(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(), y.data_ptr(),
+                 ws.data_ptr(), n, _stream_ptr(self.device)), what)
         return y
 
     # ---- stage-level access (tests, profiling) ----

@@ -105,6 +105,16 @@ int cssm_gated_forward(const cssm_gated_desc* d, const cssm_gated_weights* w,
                        const void* plan, const float* x, float* y,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Last-frame-only variant: y_last (B,H,W,C) = GatedCSSM(x)[:, -1].  For callers that read only
+ * the final frame of a depth-1 stack (SimpleCSSM with frame_readout='last' takes x[:, -1] right
+ * after the block, src/models/simple_cssm.py:482, 524-526; CSSMSHViTBlock takes x[:, -1],
+ * src/models/cssm_shvit.py:214).  The recurrence still runs over all T steps; the inverse
+ * transforms, the SiLU(z) gate, the stores and the out_proj of the earlier frames are skipped.
+ * Same plan and workspace as cssm_gated_forward. */
+int cssm_gated_forward_last(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                            const void* plan, const float* x, float* y_last,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
 /* Same block with x and y in HOST memory (pinned memory gives the overlap): the batch is
  * cut into chunks whose host->device copy, kernels and device->host copy overlap on
  * three streams ordered by events.  `workspace` must hold

@@ -179,3 +179,21 @@ def test_spectral_kernel_variants_agree_bitwise():
         assert L.cssm_debug_set_gemm_backend(0) == 0
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     assert orc.rel_l2(outs[0].cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("case", [
+    (2, 5, 64, 64, 64, 11, "factored", "spatiotemporal", 3, 4),    # radix 64, tensor-core out_proj
+    (3, 4, 32, 32, 8, 11, "dense", "none", 3, 4),                  # radix 32
+    (2, 3, 14, 14, 8, 3, "factored", "mrope", 3, 4),               # generic kernel
+    (2, 1, 64, 64, 8, 1, "factored", "none", 0, 0),                # T = 1
+], ids=lambda c: "x".join(map(str, c)))
+def test_last_frame_only_matches_full_forward(case):
+    """cssm_gated_forward_last returns exactly the last frame of the full forward (same
+    arithmetic on the frames it keeps), and matches the oracle's last frame."""
+    bound, xd, ref, _ = _run(*case)
+    full = bound(xd)
+    last = bound(xd, last_frame_only=True)
+    assert last.shape == (case[0],) + tuple(case[2:5])
+    assert _tc_error(bound.L) == 0
+    assert torch.equal(last, full[:, -1])
+    assert orc.rel_l2(last.cpu().numpy(), ref[:, -1]) <= TOL
