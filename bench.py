@@ -50,6 +50,25 @@ METRIC = "fwd images/s (gated spectral block, cfg2)"
 GDN_STAGES = ["dwconv_ctx", "qkv_proj", "gate_proj", "gates", "short_convs", "spectral", "out_proj"]
 
 
+def time_last_frame(bound, x, steps, warmup, dev, world):
+    """Secondary figure: the same block through the last-frame-only entry point (what a model
+    with a last-frame readout consumes).  Returns ms per step, max over ranks."""
+    import torch
+    from cssm_b200 import shard
+    B, T, H, W, Cc = x.shape
+    out = torch.empty((B, H, W, Cc), dtype=x.dtype, device=dev)
+    for _ in range(max(1, warmup)):
+        bound(x, out=out, last_frame_only=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(steps):
+        bound(x, out=out, last_frame_only=True)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return shard.max_over_ranks(e0.elapsed_time(e1), dev) / steps
+
+
 def run_gdn(args, cfg, rank, world, local):
     """GDN block workloads (not the headline metric): whole-block throughput, per-stage CUDA-event
     times through the library's stage-event hook, roofline of the fused GDN spectral kernel
@@ -102,6 +121,7 @@ def run_gdn(args, cfg, rank, world, local):
     for i, n in enumerate(GDN_STAGES):
         stage_ms[n] = evs[i].elapsed_time(evs[i + 1])
     total_ms = shard.max_over_ranks(e0.elapsed_time(e1), dev)
+    last_ms = time_last_frame(bound, x, args.steps, args.warmup, dev, world)
     peak, peak_src = peaks()
     alg = 20.0 * Cc * H * W * B * T
     ach = alg / (stage_ms["spectral"] / 1e3) / 1e9
@@ -119,6 +139,8 @@ def run_gdn(args, cfg, rank, world, local):
             "roofline": {"bound": "hbm", "kernel": "gdn_spectral", "achieved": ach, "peak": peak,
                          "peak_source": peak_src, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "algorithmic_bytes_per_launch": alg, "ms_per_launch": stage_ms["spectral"]},
+            "last_frame_only": {"ms_per_step": last_ms, "value": world * B / (last_ms / 1e3),
+                                "unit": "images/s"},
             "cpu_baseline": None, "e2e": None, "gpu_launches": 9 * args.steps,
             "clocks": clk.summary(),
         }))
@@ -376,6 +398,8 @@ def main():
         if per_plane_step:
             roofline["traffic"] = per_plane_step * B * T * Cc
 
+    last_ms = time_last_frame(bound, x, args.steps, args.warmup, dev, world)
+
     # end to end through the host-buffer entry point (pinned host memory)
     e2e = None
     if not args.no_e2e:
@@ -425,7 +449,10 @@ def main():
                        "H": H, "W": W, "C": Cc, "kernel_size": cfg["kernel_size"],
                        "gate_type": cfg["gate_type"], "rope_mode": cfg["rope_mode"],
                        "l2": "inputs (1.07 GB per tensor at cfg2) larger than the 126 MB L2"},
-            "stage_ms": stage_ms, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "stage_ms": stage_ms, "roofline": roofline,
+            "last_frame_only": {"ms_per_step": last_ms, "value": world * B / (last_ms / 1e3),
+                                "unit": "images/s"},
+            "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": 5 * args.steps, "clocks": clk.summary(),
         }))
     if world > 1:

@@ -88,6 +88,8 @@ SIGNATURES = {
     "cssm_gdn_plan_init": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, C.c_size_t, _P]),
     "cssm_gdn_forward": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
                                    C.c_size_t, _P]),
+    "cssm_gdn_forward_last": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
+                                        C.c_size_t, _P]),
     "cssm_debug_set_gemm_backend": (C.c_int, [C.c_int]),
     "cssm_debug_tc_error": (C.c_int, [C.POINTER(C.c_int)]),
     "cssm_debug_gdn_stage_events": (C.c_int, [C.POINTER(C.c_void_p)]),

@@ -79,6 +79,10 @@ static inline void mark(int i, cudaStream_t st) {
 
 using namespace cssm;
 
+static int gdn_forward_impl(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                            const float* x, float* y, void* workspace, size_t workspace_bytes,
+                            void* stream, int last_only);
+
 extern "C" {
 
 size_t cssm_gdn_plan_bytes(const cssm_gdn_desc* d) {
@@ -116,6 +120,28 @@ int cssm_gdn_plan_init(const cssm_gdn_desc* d, const cssm_gdn_weights* w, void* 
 int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
                      const float* x, float* y, void* workspace, size_t workspace_bytes,
                      void* stream) {
+  return gdn_forward_impl(d, w, plan, x, y, workspace, workspace_bytes, stream, 0);
+}
+
+int cssm_gdn_forward_last(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                          const float* x, float* y_last, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  return gdn_forward_impl(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1);
+}
+
+int cssm_debug_gdn_stage_events(void** events) {
+  g_stage_events = reinterpret_cast<cudaEvent_t*>(events);
+  return CSSM_OK;
+}
+
+}  // extern "C"
+
+// last_only != 0: y is (B,H,W,C), the last frame of the block output.  The gate projection, the
+// readout, the inverse transforms, RMSNorm and the output projection then run for the last
+// frame of every batch element only; q/k/v, the gate maps and the state recurrence cover all T.
+static int gdn_forward_impl(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                            const float* x, float* y, void* workspace, size_t workspace_bytes,
+                            void* stream, int last_only) {
   int s = gdn_validate(d);
   if (s != CSSM_OK) return s;
   if (!w || !plan || !x || !y || !workspace) return CSSM_ERR_NULL;
@@ -173,9 +199,12 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
   // 3. output gate projection of the rotated input -> planar, through SiLU / sigmoid
+  //    (last_only: rows of frame T-1 of every batch element -> planes (B, C, H, W))
   mark(2, st);
+  const int Mout = last_only ? d->B * HW : BT * HW;
   memset(&g, 0, sizeof(g));
-  g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
+  g.M = Mout; g.N = C; g.K = C; g.HW = HW;
+  if (last_only) { g.a_fmul = d->T; g.a_fadd = d->T - 1; }
   g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
   g.Wk = w->gate_proj_kernel; g.bias = w->gate_proj_bias;
   g.out = gate; g.o_planes = C; g.o_plane0 = 0;
@@ -217,13 +246,15 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   sp.qkv = qkv; sp.what = (const cf*)(pl + p.what); sp.ab = ga.ab; sp.state = (cf*)(ws + l.state);
   sp.B = d->B; sp.T = d->T; sp.C = C; sp.H = d->H; sp.W = d->W; sp.dk = d->delta_key_dim;
   sp.use_l2 = d->use_spectral_l2_norm;
+  sp.last_only = last_only;
   if ((s = launch_gdn_spectral(sp, st)) != CSSM_OK) return s;
 
   // 7. RMSNorm over channels, output gate, output projection -> channels-last y
   mark(6, st);
   memset(&g, 0, sizeof(g));
-  g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
+  g.M = Mout; g.N = C; g.K = C; g.HW = HW;
   g.A = qkv; g.a_planes = 3 * C; g.a_plane0 = 2 * C;
+  if (last_only) { g.a_fmul = d->T; g.a_fadd = d->T - 1; g.g_compact = 1; }
   g.rms_scale = d->output_norm == 1 ? w->rms_scale : nullptr;
   g.gate = gate; g.g_planes = C; g.g_plane0 = 0;
   g.Wk = w->output_proj_kernel; g.bias = w->output_proj_bias;
@@ -233,10 +264,3 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
   mark(7, st);
   return s;
 }
-
-int cssm_debug_gdn_stage_events(void** events) {
-  g_stage_events = reinterpret_cast<cudaEvent_t*>(events);
-  return CSSM_OK;
-}
-
-}  // extern "C"

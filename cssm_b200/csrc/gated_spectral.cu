@@ -29,11 +29,15 @@ int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int
 int launch_gated_spectral_ws(float* xz, const cf* khat, const float* gates, int B, int T, int C,
                              cudaStream_t st);
 
-template <int PRS>   // floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane)
+// PRS: floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane).
+// LAST: only the last step's output plane is produced (compile-time, so that the all-frames
+// kernel carries none of the branches).
+template <int PRS, bool LAST>
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
-                   const float4* __restrict__ gates, int T, int C, int last_only,
+                   const float4* __restrict__ gates, int T, int C,
                    const __grid_constant__ CUtensorMap pmap) {
+  constexpr int last_only = LAST ? 1 : 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // TMA tensor copies need a 128-byte aligned destination; dynamic shared memory is only
   // guaranteed 16-byte aligned, so the base is rounded up (the launch adds 128 bytes)
@@ -317,12 +321,13 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     }
-    auto kern = padded ? gated_spectral_r64<68> : gated_spectral_r64<64>;
+    auto kern = padded ? (last_only ? gated_spectral_r64<68, true> : gated_spectral_r64<68, false>)
+                       : (last_only ? gated_spectral_r64<64, true> : gated_spectral_r64<64, false>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     kern<<<grid, R64_THREADS, smem, st>>>(xz, khat, reinterpret_cast<const float4*>(gates), d.T,
-                                          d.C, last_only, pmap);
+                                          d.C, pmap);
   } else {
     const size_t smem = generic_smem_bytes(d.H, d.W);
     if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;

@@ -17,9 +17,12 @@ constexpr int R32_ZR_CF = 4 * 16 * R32_ZRS;
 constexpr int R32_GB_CF = 4 * 32 * R32_GBS;
 constexpr int R32_SMEM_BYTES = (R32_EX_CF + R32_ZR_CF + R32_GB_CF) * 8;
 
+// LAST: only the last step's output planes are produced (compile-time switch).
+template <bool LAST>
 __global__ void __launch_bounds__(R32_THREADS, 2)
 gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
-                   const float4* __restrict__ gates, int T, int C, int last_only) {
+                   const float4* __restrict__ gates, int T, int C) {
+  constexpr int last_only = LAST ? 1 : 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
   cf* ZR = EX + R32_EX_CF;
@@ -148,11 +151,12 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
 
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
                               int last_only, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(gated_spectral_r32,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, R32_SMEM_BYTES);
+  auto kern = last_only ? gated_spectral_r32<true> : gated_spectral_r32<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       R32_SMEM_BYTES);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  gated_spectral_r32<<<B * (C / 4), R32_THREADS, R32_SMEM_BYTES, st>>>(
-      xz, khat, reinterpret_cast<const float4*>(gates), T, C, last_only);
+  kern<<<B * (C / 4), R32_THREADS, R32_SMEM_BYTES, st>>>(
+      xz, khat, reinterpret_cast<const float4*>(gates), T, C);
   return check_launch();
 }
 

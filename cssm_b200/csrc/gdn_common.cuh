@@ -7,7 +7,8 @@ namespace cssm {
 // One output row v of the d_v x d_k state at one frequency bin:
 //   d = sum_j conj(k_j) S_j;  S_i <- aw*(S_i - beta*k_i*d) + beta*v*conj(k_i);  o = sum_i S_i q_i
 // with aw = alpha * W_hat.  S points at S[v][0]; consecutive i are `ss` elements apart.
-template <int DK>
+// READ = false skips the readout (returns 0); the state arithmetic is the same.
+template <int DK, bool READ = true>
 __device__ __forceinline__ cf gdn_bin_update_t(cf* S, size_t ss, const cf* kk, const cf* qq, cf vv,
                                                cf aw, float beta) {
   cf s[DK];
@@ -27,15 +28,17 @@ __device__ __forceinline__ cf gdn_bin_update_t(cf* S, size_t ss, const cf* kk, c
     const cf wr = cmulc(vv, kk[i]);
     n.x += beta * wr.x; n.y += beta * wr.y;
     S[i * ss] = n;
-    const cf oq = cmul(n, qq[i]);
-    o.x += oq.x; o.y += oq.y;
+    if (READ) {
+      const cf oq = cmul(n, qq[i]);
+      o.x += oq.x; o.y += oq.y;
+    }
   }
   return o;
 }
 
 // Same update on a state row that the caller has already loaded into registers (s) and will
 // store itself: lets the caller batch the loads of several bins ahead of the stores.
-template <int DK>
+template <int DK, bool READ = true>
 __device__ __forceinline__ cf gdn_bin_update_regs(cf (&s)[DK], const cf* kk, const cf* qq, cf vv,
                                                   cf aw, float beta) {
   cf d = mk(0.f, 0.f);
@@ -53,8 +56,10 @@ __device__ __forceinline__ cf gdn_bin_update_regs(cf (&s)[DK], const cf* kk, con
     const cf wr = cmulc(vv, kk[i]);
     n.x += beta * wr.x; n.y += beta * wr.y;
     s[i] = n;
-    const cf oq = cmul(n, qq[i]);
-    o.x += oq.x; o.y += oq.y;
+    if (READ) {
+      const cf oq = cmul(n, qq[i]);
+      o.x += oq.x; o.y += oq.y;
+    }
   }
   return o;
 }

@@ -15,13 +15,14 @@ namespace cssm {
 
 constexpr int GDN_MAXDK = 4;
 
+template <bool READ>
 __device__ __forceinline__ cf gdn_bin_update(cf* S, size_t ss, int dk, const cf* kk, const cf* qq,
                                              cf vv, cf aw, float beta) {
   switch (dk) {
-    case 1: return gdn_bin_update_t<1>(S, ss, kk, qq, vv, aw, beta);
-    case 2: return gdn_bin_update_t<2>(S, ss, kk, qq, vv, aw, beta);
-    case 3: return gdn_bin_update_t<3>(S, ss, kk, qq, vv, aw, beta);
-    default: return gdn_bin_update_t<4>(S, ss, kk, qq, vv, aw, beta);
+    case 1: return gdn_bin_update_t<1, READ>(S, ss, kk, qq, vv, aw, beta);
+    case 2: return gdn_bin_update_t<2, READ>(S, ss, kk, qq, vv, aw, beta);
+    case 3: return gdn_bin_update_t<3, READ>(S, ss, kk, qq, vv, aw, beta);
+    default: return gdn_bin_update_t<4, READ>(S, ss, kk, qq, vv, aw, beta);
   }
 }
 
@@ -102,12 +103,16 @@ __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpec
   for (int t = 0; t < a.T; ++t) {
     const size_t frame = (size_t)(b * a.T + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
+    const bool emit = !a.last_only || t == a.T - 1;         // same for the whole CTA
     float nq[GDN_MAXDK], nk[GDN_MAXDK];
     for (int i = 0; i < dk; ++i) {
-      gen_fwd_plane(base + (size_t)(hd * dk + i) * HW, xs, Rb, SQ + (size_t)i * NB, twW, twH, H, W);
       float p = 0.f;
-      for (int o = tid; o < NB; o += GG_THREADS) { const cf z = SQ[(size_t)i * NB + o]; p += z.x * z.x + z.y * z.y; }
-      nq[i] = a.use_l2 ? rsqrtf(block_sum(p, red) + 1e-6f) : 1.f;
+      nq[i] = 1.f;
+      if (emit) {                                            // q is only needed for the readout
+        gen_fwd_plane(base + (size_t)(hd * dk + i) * HW, xs, Rb, SQ + (size_t)i * NB, twW, twH, H, W);
+        for (int o = tid; o < NB; o += GG_THREADS) { const cf z = SQ[(size_t)i * NB + o]; p += z.x * z.x + z.y * z.y; }
+        nq[i] = a.use_l2 ? rsqrtf(block_sum(p, red) + 1e-6f) : 1.f;
+      }
       gen_fwd_plane(base + (size_t)(a.C + hd * dk + i) * HW, xs, Rb, SK + (size_t)i * NB, twW, twH, H, W);
       p = 0.f;
       for (int o = tid; o < NB; o += GG_THREADS) { const cf z = SK[(size_t)i * NB + o]; p += z.x * z.x + z.y * z.y; }
@@ -121,8 +126,10 @@ __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpec
         const cf z = SK[(size_t)i * NB + o];
         kv[i] = mk(z.x * nk[i], z.y * nk[i]);
         ks += kv[i].x * kv[i].x + kv[i].y * kv[i].y;
-        const cf q = SQ[(size_t)i * NB + o];
-        SQ[(size_t)i * NB + o] = mk(q.x * nq[i], q.y * nq[i]);
+        if (emit) {
+          const cf q = SQ[(size_t)i * NB + o];
+          SQ[(size_t)i * NB + o] = mk(q.x * nq[i], q.y * nq[i]);
+        }
       }
       const float kn = rsqrtf(ks + 1e-6f);
       for (int i = 0; i < dk; ++i) SK[(size_t)i * NB + o] = mk(kv[i].x * kn, kv[i].y * kn);
@@ -137,9 +144,14 @@ __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpec
         const float2 g = ab[o];
         const cf w = wh[o];
         const cf aw = mk(g.x * w.x, g.x * w.y);
-        const cf ov = gdn_bin_update(S + (size_t)v * dk * NB + o, NB, dk, kk, qq, Fb[o], aw, g.y);
-        Fb[o] = mk(ov.x * invHW, ov.y * invHW);
+        if (emit) {
+          const cf ov = gdn_bin_update<true>(S + (size_t)v * dk * NB + o, NB, dk, kk, qq, Fb[o], aw, g.y);
+          Fb[o] = mk(ov.x * invHW, ov.y * invHW);
+        } else {
+          gdn_bin_update<false>(S + (size_t)v * dk * NB + o, NB, dk, kk, qq, Fb[o], aw, g.y);
+        }
       }
+      if (!emit) continue;
       __syncthreads();
       for (int o = tid; o < NB; o += GG_THREADS) {
         const int h = o / Wf, kw = o % Wf;

@@ -22,6 +22,8 @@ constexpr int G32_SPEC_CF = 8 * 8 * 17 * 4;            // [q planes 0-3, k plane
 constexpr int G32_STATE_CF = 4 * 8 * G32_THREADS;      // [i][r][thread]
 constexpr int G32_SMEM_BYTES = (G32_EX_CF + G32_ZR_CF + G32_GB_CF + G32_SPEC_CF + G32_STATE_CF) * 8;
 
+// LAST: only the last step's output planes are produced (compile-time switch).
+template <bool LAST>
 __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpectralArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
@@ -67,10 +69,11 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
     const size_t frame = (size_t)(b * a.T + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
     float ssq[2] = {0.f, 0.f};
+    const bool emit = !LAST || t == a.T - 1;         // same for the whole CTA
     cf v[8];
     // ---- passes 0 (q), 1 (k), 2 (v): forward transform of four planes at once ----
 #pragma unroll 1
-    for (int pass = 0; pass < 3; ++pass) {
+    for (int pass = emit ? 0 : 1; pass < 3; ++pass) {     // q is only needed for the readout
       __syncthreads();                       // ZR free (previous column pass finished)
       if (row_on) {
         const float* r0 = base + (size_t)(pass * a.C + hd * DK + rpl) * HW + roff;
@@ -102,7 +105,7 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
               acc += v[r].x * v[r].x + v[r].y * v[r].y;
             }
           }
-          ssq[pass] = acc;
+          if (pass == 0) ssq[0] = acc; else ssq[1] = acc;
         }
       }
     }
@@ -148,20 +151,26 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
         if (col_on) {
           const float2 g = abp[r * (17 * 4)];
           const cf aw = mk(g.x * wh[r].x, g.x * wh[r].y);
-          o = gdn_bin_update_t<4>(ST + r * G32_THREADS + tid, (size_t)8 * G32_THREADS, kk, qq, v[r],
-                                  aw, g.y);
+          if (emit)
+            o = gdn_bin_update_t<4, true>(ST + r * G32_THREADS + tid, (size_t)8 * G32_THREADS, kk,
+                                          qq, v[r], aw, g.y);
+          else
+            gdn_bin_update_t<4, false>(ST + r * G32_THREADS + tid, (size_t)8 * G32_THREADS, kk, qq,
+                                       v[r], aw, g.y);
         }
         v[r] = mk(o.x * invHW, o.y * invHW);
       }
-      fft32_inv(v, tw, exg, q);
-      cf* gb = GB + (cpl * 32) * G32_GBS;
+      if (emit) {
+        fft32_inv(v, tw, exg, q);
+        cf* gb = GB + (cpl * 32) * G32_GBS;
 #pragma unroll
-      for (int m = 0; m < 8; ++m)
-        if (col_on) gb[(q + 4 * m) * G32_GBS + kw] = v[m];
+        for (int m = 0; m < 8; ++m)
+          if (col_on) gb[(q + 4 * m) * G32_GBS + kw] = v[m];
+      }
     }
     __syncthreads();
     // ---- inverse rows of the four output planes, written over the v planes ----
-    if (row_on) {
+    if (row_on && emit) {
       const cf* ge = GB + (rpl * 32 + 2 * rpair) * G32_GBS;
       const cf* go = ge + G32_GBS;
       cf u[8];
@@ -185,10 +194,11 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
 }
 
 int launch_gdn_spectral_r32(const GdnSpectralArgs& a, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(gdn_spectral_r32,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, G32_SMEM_BYTES);
+  auto kern = a.last_only ? gdn_spectral_r32<true> : gdn_spectral_r32<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       G32_SMEM_BYTES);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  gdn_spectral_r32<<<a.B * (a.C / 4), G32_THREADS, G32_SMEM_BYTES, st>>>(a);
+  kern<<<a.B * (a.C / 4), G32_THREADS, G32_SMEM_BYTES, st>>>(a);
   return check_launch();
 }
 

@@ -12,6 +12,8 @@ namespace cssm {
 constexpr int G64_SPEC_CF = 8 * 8 * R64_NT;     // [plane 0..7][q 0..7][thread]
 constexpr int G64_SMEM_CF = R64_EX_CF + R64_ZR_CF + R64_GB_CF + G64_SPEC_CF;
 
+// LAST: only the last step's output planes are produced (compile-time switch).
+template <bool LAST>
 __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
@@ -43,22 +45,27 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
   const float invHW = 1.0f / (float)HW;
 
   // plane idx 0..3 = q, 4..7 = k, 8..11 = v of step t; idx 12 = first plane of step t + 1
+  // last_only: steps before the last one skip the q planes (their sequence starts at idx 4)
+  auto first_of = [&](int t) -> int { return (LAST && t < a.T - 1) ? 4 : 0; };
   auto plane_of = [&](int t, int idx) -> float* {
-    if (idx >= 12) { idx -= 12; ++t; }
+    if (idx >= 12) { ++t; idx = first_of(t); }
     if (t >= a.T) { t = a.T - 1; idx = 0; }                 // harmless re-read past the end
     const size_t frame = (size_t)(b * a.T + t);
     return a.qkv + (frame * 3 * a.C + (size_t)(idx >> 2) * a.C + hd * DK + (idx & 3)) * HW;
   };
   cf nx[8];                                   // rows of the NEXT plane, fetched one pass ahead
-  r64_load_rows(c, plane_of(0, 0), nx);
+  r64_load_rows(c, plane_of(0, first_of(0)), nx);
 
   for (int t = 0; t < a.T; ++t) {
     const size_t frame = (size_t)(b * a.T + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
+    const bool emit = !LAST || t == a.T - 1;         // same for the whole CTA
     float ssq[8];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) ssq[p] = 0.f;
     // ---- q planes (p = 0..3) and k planes (p = 4..7) ----
 #pragma unroll 1
-    for (int p = 0; p < 8; ++p) {
+    for (int p = first_of(t); p < 8; ++p) {
       __syncthreads();                       // ZR free (previous column pass finished)
       {
         cf cur[8];
@@ -79,7 +86,9 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
         }
       }
       for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
-      ssq[p] = acc;                          // valid in lane 0 of each warp
+      // valid in lane 0 of each warp (ssq is indexed statically to stay in registers)
+#pragma unroll
+      for (int pp = 0; pp < 8; ++pp) if (pp == p) ssq[pp] = acc;
     }
     if (c.lane == 0)
 #pragma unroll
@@ -104,8 +113,10 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
           cf z = SPEC[((4 + i) * 8 + q) * R64_NT + tid];
           kv[i] = mk(z.x * nrm[4 + i], z.y * nrm[4 + i]);
           ks += kv[i].x * kv[i].x + kv[i].y * kv[i].y;
-          cf qq = SPEC[(i * 8 + q) * R64_NT + tid];
-          SPEC[(i * 8 + q) * R64_NT + tid] = mk(qq.x * nrm[i], qq.y * nrm[i]);
+          if (emit) {
+            cf qq = SPEC[(i * 8 + q) * R64_NT + tid];
+            SPEC[(i * 8 + q) * R64_NT + tid] = mk(qq.x * nrm[i], qq.y * nrm[i]);
+          }
         }
         const float kn = rsqrtf(ks + 1e-6f);
 #pragma unroll
@@ -152,8 +163,12 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
             kk[i] = SPEC[((4 + i) * 8 + q) * R64_NT + tid];
           }
           const cf aw = mk(gab[q].x * wh[q].x, gab[q].x * wh[q].y);
-          const cf o = gdn_bin_update_regs<4>(sreg[q], kk, qq, v[q], aw, gab[q].y);
-          v[q] = mk(o.x * invHW, o.y * invHW);
+          if (emit) {
+            const cf o = gdn_bin_update_regs<4, true>(sreg[q], kk, qq, v[q], aw, gab[q].y);
+            v[q] = mk(o.x * invHW, o.y * invHW);
+          } else {
+            gdn_bin_update_regs<4, false>(sreg[q], kk, qq, v[q], aw, gab[q].y);
+          }
         }
         if (c.col_on) {
 #pragma unroll
@@ -161,10 +176,10 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
 #pragma unroll
             for (int i = 0; i < 4; ++i) srow[(size_t)i * NB + q * 264] = sreg[q][i];
         }
-        r64_col_inv(c, v);
+        if (emit) r64_col_inv(c, v);
       }
       __syncthreads();
-      if (c.row_on) {
+      if (c.row_on && emit) {
         cf v[8];
         r64_row_inv(c, v);
         float* y0 = vplane + (2 * c.grp) * 64 + c.a;
@@ -180,10 +195,10 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
 
 int launch_gdn_spectral_r64(const GdnSpectralArgs& a, cudaStream_t st) {
   const size_t smem = (size_t)G64_SMEM_CF * sizeof(cf);
-  cudaError_t e = cudaFuncSetAttribute(gdn_spectral_r64,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kern = a.last_only ? gdn_spectral_r64<true> : gdn_spectral_r64<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  gdn_spectral_r64<<<a.B * (a.C / 4), R64_NT, smem, st>>>(a);
+  kern<<<a.B * (a.C / 4), R64_NT, smem, st>>>(a);
   return check_launch();
 }
 

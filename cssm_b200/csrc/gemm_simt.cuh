@@ -13,7 +13,7 @@ struct GemmArgs {
   int M, N, K, HW;
   const float* A;         // channels-last: (M, K).  planar: plane (frame*a_planes + a_plane0 + k)
   int a_planes, a_plane0;
-  int a_fmul, a_fadd;     // planar A: source frame of output frame f is f*a_fmul + a_fadd (0,0 = f)
+  int a_fmul, a_fadd;     // source frame of output frame f is f*a_fmul + a_fadd (0,0 = f), both A layouts
   const float* Wk;        // (K, N) row-major
   const float* bias;      // (N) or nullptr
   float* out;             // channels-last (M, N) or planar plane (frame*o_planes + o_plane0 + n)
@@ -26,12 +26,20 @@ struct GemmArgs {
   const float* rms_scale;   // (K) or nullptr (no normalisation)
   const float* gate;        // planar, plane (frame*g_planes + g_plane0 + k), or nullptr
   int g_planes, g_plane0;
+  int g_compact;            // 1: the gate is indexed by the OUTPUT frame, 0: by the source frame
   int out_act;              // 0 none, 1 silu, 2 sigmoid; applied to output columns n >= act_n0
   int act_n0;
 };
 
 __host__ __device__ inline int gemm_src_frame(const GemmArgs& g, int f) {
   return g.a_fmul == 0 && g.a_fadd == 0 ? f : f * g.a_fmul + g.a_fadd;
+}
+
+// channels-last A: source row of output row m
+__host__ __device__ inline size_t gemm_src_row(const GemmArgs& g, int m) {
+  if (g.a_fmul == 0 && g.a_fadd == 0) return (size_t)m;
+  const int fo = m / g.HW;
+  return (size_t)(fo * g.a_fmul + g.a_fadd) * g.HW + (m - fo * g.HW);
 }
 
 constexpr int GEMM_BM = 128, GEMM_BK = 16, GEMM_THREADS = 256;
@@ -84,8 +92,10 @@ gemm_simt_kernel(const GemmArgs g) {
           const int fr = gemm_src_frame(g, m / g.HW), px = m % g.HW;
           v = g.A[((size_t)fr * g.a_planes + g.a_plane0 + k) * g.HW + px];
           if (g.rms_scale != nullptr) v *= rinv[mm] * g.rms_scale[k];
-          if (g.gate != nullptr)
-            v *= g.gate[((size_t)fr * g.g_planes + g.g_plane0 + k) * g.HW + px];
+          if (g.gate != nullptr) {
+            const int fg = g.g_compact ? m / g.HW : fr;
+            v *= g.gate[((size_t)fg * g.g_planes + g.g_plane0 + k) * g.HW + px];
+          }
         }
         As[kk][mm] = v;
       }
@@ -97,9 +107,9 @@ gemm_simt_kernel(const GemmArgs g) {
         const int m = m0 + mm, k = k0 + kq;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (m < g.M && k < g.K) {
-          v = *reinterpret_cast<const float4*>(g.A + (size_t)m * g.K + k);
+          v = *reinterpret_cast<const float4*>(g.A + gemm_src_row(g, m) * g.K + k);
           if (g.rope_t != nullptr) {
-            const int px = m % g.HW, fr = m / g.HW;
+            const int px = m % g.HW, fr = gemm_src_frame(g, m / g.HW);
             const int t = fr % g.T, h = px / g.W, w = px % g.W;
             const int n2 = g.K >> 1, i = k >> 1;
 #pragma unroll

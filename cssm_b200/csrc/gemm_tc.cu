@@ -116,13 +116,16 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
     const int chunk_lo = tid & 7, rsub = tid >> 3;
     bool rot[2] = {false, false};
     if (!A_PLANAR) {
+      // a tile never crosses a frame (H*W is a multiple of the tile height), so the source-frame
+      // remap is one row offset per tile
       const int m0 = t_first * TC_BM;
+      const float* a0 = g.A + gemm_src_row(g, m0 < g.M ? m0 : 0) * TC_K;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const int m = m0 + rsub + 32 * (r & 3);
+        const int row = rsub + 32 * (r & 3);
         const int chunk = chunk_lo + 8 * (r >> 2);
-        pre[r] = (t_first < t_end && m < g.M && !(dbg & 2))
-                     ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
+        pre[r] = (t_first < t_end && m0 + row < g.M && !(dbg & 2))
+                     ? __ldg(reinterpret_cast<const float4*>(a0 + (size_t)row * TC_K + chunk * 4))
                      : make_float4(0.f, 0.f, 0.f, 0.f);
       }
       if (g.rope_t != nullptr) {
@@ -143,12 +146,14 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
         for (int r = 0; r < 8; ++r) cur[r] = pre[r];
         const int nt = tile + t_step;
         if (nt < t_end) {
+          const float* a0 = g.A + gemm_src_row(g, nt * TC_BM) * TC_K;
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
-            const int m = nt * TC_BM + rsub + 32 * (r & 3);
+            const int row = rsub + 32 * (r & 3);
             const int chunk = chunk_lo + 8 * (r >> 2);
-            pre[r] = (m < g.M && !(dbg & 2)) ? __ldg(reinterpret_cast<const float4*>(g.A + (size_t)m * TC_K + chunk * 4))
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            pre[r] = (nt * TC_BM + row < g.M && !(dbg & 2))
+                         ? __ldg(reinterpret_cast<const float4*>(a0 + (size_t)row * TC_K + chunk * 4))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
       }
@@ -160,7 +165,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
         if (rot[0] || rot[1]) {
           const int fr = m0 / g.HW;
           px0 = m0 - fr * g.HW;
-          t = fr % g.T;
+          t = gemm_src_frame(g, fr) % g.T;
         }
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
@@ -215,7 +220,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
             for (int k = 0; k < 32; ++k) v[k] *= rinv * __ldg(&g.rms_scale[kh * 32 + k]);
           }
           if (g.gate != nullptr) {
-            const float* gp = g.gate + ((size_t)fr * g.g_planes + g.g_plane0 + kh * 32) * g.HW + px;
+            const float* gp = g.gate + ((size_t)(g.g_compact ? fo : fr) * g.g_planes + g.g_plane0 + kh * 32) * g.HW + px;
 #pragma unroll
             for (int k = 0; k < 32; ++k) v[k] *= __ldg(gp + (size_t)k * g.HW);
           }

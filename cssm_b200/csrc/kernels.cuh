@@ -64,6 +64,8 @@ struct GdnSpectralArgs {
   const float2* ab;          // (BT, H*Wf)
   cf* state;                 // (B*n_h, dk, dk, H*Wf) scratch for the matrix state
   int B, T, C, H, W, dk, use_l2;
+  int last_only;             // != 0: only the last step's output planes are produced (the q
+                             // transforms, readout and inverse transforms of earlier steps are skipped)
 };
 int launch_gdn_spectral(const GdnSpectralArgs& a, cudaStream_t st);
 size_t gdn_generic_smem_bytes(int H, int W, int dk);

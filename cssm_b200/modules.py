@@ -493,15 +493,24 @@ class BoundGdn:
             self._plans[key] = pl
         return pl
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 last_frame_only: bool = False) -> torch.Tensor:
+        """y = block(x).  With last_frame_only=True returns block(x)[:, -1] of shape (B,H,W,C)
+        (for callers with a last-frame readout): the readout, inverse transforms and output
+        projections of the earlier frames are not computed."""
         _require_cuda(x)
         x = x.contiguous()
         d = self.desc(tuple(x.shape))
         pl = self.plan(d)
         n = self.L.cssm_gdn_workspace_bytes(C.byref(d))
         ws = self.buf.get("ws", n)
-        y = torch.empty_like(x) if out is None else out
-        check(self.L.cssm_gdn_forward(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(),
-                                      y.data_ptr(), ws.data_ptr(), n, _stream_ptr(self.device)),
-              "cssm_gdn_forward")
+        if last_frame_only:
+            B, T, H, W, Cc = x.shape
+            y = torch.empty((B, H, W, Cc), dtype=x.dtype, device=x.device) if out is None else out
+            fn, what = self.L.cssm_gdn_forward_last, "cssm_gdn_forward_last"
+        else:
+            y = torch.empty_like(x) if out is None else out
+            fn, what = self.L.cssm_gdn_forward, "cssm_gdn_forward"
+        check(fn(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(), y.data_ptr(),
+                 ws.data_ptr(), n, _stream_ptr(self.device)), what)
         return y

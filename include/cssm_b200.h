@@ -222,6 +222,15 @@ int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const vo
                      const float* x, float* y, void* workspace, size_t workspace_bytes,
                      void* stream);
 
+/* Last-frame-only variant: y_last (B,H,W,C) = GatedDeltaNetCSSM(x)[:, -1], for callers with a
+ * last-frame readout (src/models/simple_cssm.py:482, 524-526).  q/k/v, the gate maps and the state
+ * recurrence cover all T steps; the q transforms, the readout, the inverse transforms, gate_proj,
+ * RMSNorm and output_proj run for the last frame only.  Same plan and workspace as
+ * cssm_gdn_forward. */
+int cssm_gdn_forward_last(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                          const float* x, float* y_last, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 /* ---- diagnostics (no counterpart in the reference) ----
  * cssm_debug_set_gemm_backend: 0 = tensor-core (tcgen05) projections where they apply
  * (default), 1 = CUDA-core fp32 projections everywhere; process-wide, for A/B tests.  Higher

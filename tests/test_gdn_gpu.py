@@ -12,7 +12,7 @@ TOL = 1e-4
 
 
 def _run(B, T, H, W, C, dk, ks, gate, rope, kt, qkvk, ig=True, norm="rms", act="silu", l2=True,
-         seed=0):
+         seed=0, last=False):
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((B, T, H, W, C)).astype(np.float32)
     p = orc.init_gdn_params(seed + 1, C, H, W, delta_key_dim=dk, kernel_size=ks, gate_type=gate,
@@ -26,7 +26,11 @@ def _run(B, T, H, W, C, dk, ks, gate, rope, kt, qkvk, ig=True, norm="rms", act="
                             gate_type=gate, short_conv_size=kt, qkv_conv_size=qkvk,
                             use_input_gates=ig, output_norm=norm, output_gate_act=act,
                             use_spectral_l2_norm=l2)
-    y = mod.apply({"params": p}, torch.from_numpy(x).cuda()).cpu().numpy()
+    xd = torch.from_numpy(x).cuda()
+    y = mod.apply({"params": p}, xd).cpu().numpy()
+    if last:
+        y_last = mod.bind({"params": p})(xd, last_frame_only=True).cpu().numpy()
+        return y, ref, y_last
     return y, ref
 
 
@@ -79,3 +83,15 @@ def test_deterministic():
     y1 = mod.apply(v, x).clone()
     y2 = mod.apply(v, x).clone()
     assert torch.equal(y1, y2)
+
+
+@pytest.mark.parametrize("case", [CASES[0], CASES[1], CASES[4], CASES[5], CASES[7], CASES[9]],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_last_frame_only_matches_full_forward(case):
+    """cssm_gdn_forward_last equals the last frame of the full forward (generic, 32x32 and 64x64
+    kernels; CUDA-core and tensor-core projections) and the oracle's last frame."""
+    y, ref, y_last = _run(*case, last=True)
+    assert y_last.shape == y[:, -1].shape
+    assert np.isfinite(y_last).all()
+    assert orc.rel_l2(y_last, y[:, -1]) <= 1e-6
+    assert orc.rel_l2(y_last, ref[:, -1]) <= TOL
