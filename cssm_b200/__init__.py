@@ -6,5 +6,6 @@ modules.  Importing the package does not load the library; the first compute cal
 raises if it has not been built."""
 from ._lib import CssmError, lib  # noqa: F401
 from .modules import GatedCSSM, GatedDeltaNetCSSM  # noqa: F401
+from .simple import SimpleCSSM  # noqa: F401
 
-__all__ = ["GatedCSSM", "GatedDeltaNetCSSM", "CssmError", "lib"]
+__all__ = ["GatedCSSM", "GatedDeltaNetCSSM", "SimpleCSSM", "CssmError", "lib"]

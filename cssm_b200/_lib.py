@@ -62,6 +62,22 @@ class GdnWeights(C.Structure):
 
 # name -> (restype, argtypes); every symbol include/cssm_b200.h declares
 _P = C.c_void_p
+class SimpleDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("B", "T", "Hin", "Win", "Cin", "image_input", "stem_mode", "stem_layers",
+                 "embed_dim", "block", "pool_type", "readout_norm", "num_classes")]
+
+
+class SimpleWeights(C.Structure):
+    _fields_ = [("conv_kernel", C.c_void_p * 4), ("conv_bias", C.c_void_p * 4),
+                ("norm_scale", C.c_void_p * 4), ("norm_bias", C.c_void_p * 4),
+                ("norm_pre_scale", C.c_void_p), ("norm_pre_bias", C.c_void_p),
+                ("norm_post_scale", C.c_void_p), ("norm_post_bias", C.c_void_p),
+                ("head_kernel", C.c_void_p), ("head_bias", C.c_void_p)]
+
+
+SIMPLE_LAST_FRAME_ONLY = 1
+
 SIGNATURES = {
     "cssm_strerror": (C.c_char_p, [C.c_int]),
     "cssm_last_cuda_error": (C.c_char_p, []),
@@ -90,6 +106,16 @@ SIGNATURES = {
                                    C.c_size_t, _P]),
     "cssm_gdn_forward_last": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
                                         C.c_size_t, _P]),
+    "cssm_simple_workspace_bytes": (C.c_size_t, [C.POINTER(SimpleDesc), _P]),
+    "cssm_simple_stem": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P, _P,
+                                   C.c_size_t, _P]),
+    "cssm_simple_readout": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), C.c_int32,
+                                      C.c_int32, _P, C.c_size_t, _P, C.c_size_t, _P, _P, _P]),
+    "cssm_simple_forward": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P, _P,
+                                      _P, _P, _P, C.c_size_t, C.c_int32, _P]),
+    "cssm_simple_host_workspace_bytes": (C.c_size_t, [C.POINTER(SimpleDesc), _P]),
+    "cssm_simple_forward_host": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P,
+                                           _P, _P, _P, _P, C.c_size_t, C.c_int32, _P]),
     "cssm_debug_set_gemm_backend": (C.c_int, [C.c_int]),
     "cssm_debug_tc_error": (C.c_int, [C.POINTER(C.c_int)]),
     "cssm_debug_gdn_stage_events": (C.c_int, [C.POINTER(C.c_void_p)]),

@@ -144,8 +144,19 @@ int cssm_gated_plan_init(const cssm_gated_desc* d, const cssm_gated_weights* w, 
                             d->W, d->C, d->rope_mode, d->rope_base, st);
 }
 
+static int gated_in_proj_impl(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                              const void* plan, const float* x, float* xz, void* stream,
+                              int x_bcast);
+
 int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
                        const float* x, float* xz, void* stream) {
+  return gated_in_proj_impl(d, w, plan, x, xz, stream, 0);
+}
+
+// x_bcast != 0: x is (B,H,W,C), one frame per batch element that stands for all T frames
+static int gated_in_proj_impl(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                              const void* plan, const float* x, float* xz, void* stream,
+                              int x_bcast) {
   int s = validate(d);
   if (s != CSSM_OK) return s;
   if (!w || !w->in_proj_kernel || !w->in_proj_bias || !plan || !x || !xz) return CSSM_ERR_NULL;
@@ -165,6 +176,7 @@ int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, co
     g.rope_nz = (const float*)(base + p.rope_nz);
   }
   g.T = d->T; g.H = d->H; g.W = d->W;
+  if (x_bcast) { g.a_fdiv = d->T; g.a_fmul = 1; g.a_fadd = 0; }
   return launch_gemm<false, true>(g, (cudaStream_t)stream);
 }
 
@@ -231,9 +243,12 @@ int cssm_gated_out_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, c
   return launch_gemm<true, false>(g, (cudaStream_t)stream);
 }
 
-static int gated_forward_impl(const cssm_gated_desc* d, const cssm_gated_weights* w,
-                              const void* plan, const float* x, float* y, void* workspace,
-                              size_t workspace_bytes, void* stream, int last_only) {
+}  // extern "C"
+
+namespace cssm {
+int gated_forward_internal(const cssm_gated_desc* d, const cssm_gated_weights* w,
+                           const void* plan, const float* x, float* y, void* workspace,
+                           size_t workspace_bytes, void* stream, int last_only, int x_bcast) {
   int s = validate(d);
   if (s != CSSM_OK) return s;
   s = validate_weights(d, w);
@@ -247,7 +262,7 @@ static int gated_forward_impl(const cssm_gated_desc* d, const cssm_gated_weights
   float* xz = (float*)(ws + l.xz_planar);
   float* ctx = (float*)(ws + l.ctx_sum);
   float* gm = (float*)(ws + l.gate_maps);
-  if ((s = cssm_gated_in_proj(d, w, plan, x, xz, stream)) != CSSM_OK) return s;
+  if ((s = gated_in_proj_impl(d, w, plan, x, xz, stream, x_bcast)) != CSSM_OK) return s;
   if ((s = cssm_gated_short_conv(d, w, xz, ctx, stream)) != CSSM_OK) return s;
   if ((s = cssm_gated_gates(d, w, ctx, gm, stream)) != CSSM_OK) return s;
   if (!last_only) {
@@ -269,17 +284,20 @@ static int gated_forward_impl(const cssm_gated_desc* d, const cssm_gated_weights
   g.T = 1; g.H = d->H; g.W = d->W;
   return launch_gemm<true, false>(g, (cudaStream_t)stream);
 }
+}  // namespace cssm
+
+extern "C" {
 
 int cssm_gated_forward(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
                        const float* x, float* y, void* workspace, size_t workspace_bytes,
                        void* stream) {
-  return gated_forward_impl(d, w, plan, x, y, workspace, workspace_bytes, stream, 0);
+  return gated_forward_internal(d, w, plan, x, y, workspace, workspace_bytes, stream, 0, 0);
 }
 
 int cssm_gated_forward_last(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
                             const float* x, float* y_last, void* workspace, size_t workspace_bytes,
                             void* stream) {
-  return gated_forward_impl(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1);
+  return gated_forward_internal(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1, 0);
 }
 
 }  // extern "C"

@@ -79,10 +79,6 @@ static inline void mark(int i, cudaStream_t st) {
 
 using namespace cssm;
 
-static int gdn_forward_impl(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
-                            const float* x, float* y, void* workspace, size_t workspace_bytes,
-                            void* stream, int last_only);
-
 extern "C" {
 
 size_t cssm_gdn_plan_bytes(const cssm_gdn_desc* d) {
@@ -120,13 +116,13 @@ int cssm_gdn_plan_init(const cssm_gdn_desc* d, const cssm_gdn_weights* w, void* 
 int cssm_gdn_forward(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
                      const float* x, float* y, void* workspace, size_t workspace_bytes,
                      void* stream) {
-  return gdn_forward_impl(d, w, plan, x, y, workspace, workspace_bytes, stream, 0);
+  return gdn_forward_internal(d, w, plan, x, y, workspace, workspace_bytes, stream, 0, 0);
 }
 
 int cssm_gdn_forward_last(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
                           const float* x, float* y_last, void* workspace, size_t workspace_bytes,
                           void* stream) {
-  return gdn_forward_impl(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1);
+  return gdn_forward_internal(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1, 0);
 }
 
 int cssm_debug_gdn_stage_events(void** events) {
@@ -139,9 +135,10 @@ int cssm_debug_gdn_stage_events(void** events) {
 // last_only != 0: y is (B,H,W,C), the last frame of the block output.  The gate projection, the
 // readout, the inverse transforms, RMSNorm and the output projection then run for the last
 // frame of every batch element only; q/k/v, the gate maps and the state recurrence cover all T.
-static int gdn_forward_impl(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
-                            const float* x, float* y, void* workspace, size_t workspace_bytes,
-                            void* stream, int last_only) {
+// x_bcast != 0: x is (B,H,W,C), one frame per batch element standing for all T frames.
+int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                               const float* x, float* y, void* workspace, size_t workspace_bytes,
+                               void* stream, int last_only, int x_bcast) {
   int s = gdn_validate(d);
   if (s != CSSM_OK) return s;
   if (!w || !plan || !x || !y || !workspace) return CSSM_ERR_NULL;
@@ -181,7 +178,7 @@ static int gdn_forward_impl(const cssm_gdn_desc* d, const cssm_gdn_weights* w, c
   memset(&dw, 0, sizeof(dw));
   dw.x = x; dw.out = d->qkv_conv_size > 1 ? xdw : nullptr;
   dw.wk = w->qkv_dw_kernel; dw.bias = w->qkv_dw_bias; dw.ksz = d->qkv_conv_size;
-  dw.BT = BT; dw.T = d->T; dw.H = d->H; dw.W = d->W; dw.C = C;
+  dw.BT = BT; dw.T = d->T; dw.H = d->H; dw.W = d->W; dw.C = C; dw.x_bcast = x_bcast;
   dw.rope_t = rt; dw.rope_h = rh; dw.rope_w = rw;
   dw.ctx_part = (float*)(ws + l.ctx_part);
   if ((s = launch_rope_dwconv_cl(dw, st)) != CSSM_OK) return s;
@@ -195,7 +192,10 @@ static int gdn_forward_impl(const cssm_gdn_desc* d, const cssm_gdn_weights* w, c
   g.out = qkv; g.o_planes = 3 * C; g.o_plane0 = 0;
   g.T = d->T; g.H = d->H; g.W = d->W;
   if (d->qkv_conv_size > 1) { g.A = xdw; }
-  else { g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz; }
+  else {
+    g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
+    if (x_bcast) { g.a_fdiv = d->T; g.a_fmul = 1; g.a_fadd = 0; }
+  }
   if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
   // 3. output gate projection of the rotated input -> planar, through SiLU / sigmoid
@@ -204,7 +204,12 @@ static int gdn_forward_impl(const cssm_gdn_desc* d, const cssm_gdn_weights* w, c
   const int Mout = last_only ? d->B * HW : BT * HW;
   memset(&g, 0, sizeof(g));
   g.M = Mout; g.N = C; g.K = C; g.HW = HW;
-  if (last_only) { g.a_fmul = d->T; g.a_fadd = d->T - 1; }
+  if (last_only) {
+    g.rope_tlast = 1;
+    if (!x_bcast) { g.a_fmul = d->T; g.a_fadd = d->T - 1; }     // else frame b is the source
+  } else if (x_bcast) {
+    g.a_fdiv = d->T; g.a_fmul = 1; g.a_fadd = 0;
+  }
   g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
   g.Wk = w->gate_proj_kernel; g.bias = w->gate_proj_bias;
   g.out = gate; g.o_planes = C; g.o_plane0 = 0;

@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwA
   const int band = bid % bands;
   const int fr = bid / bands;
   const int t = fr % a.T, h0 = band * DW_ROWS, c0 = cg * DW_CG;
+  const int fsrc = a.x_bcast ? fr / a.T : fr;
   const int tid = threadIdx.x;
   // ---- stage rows h0-LO .. h0+DW_ROWS-1+(K-1-LO), 16 channels, rotated ----
   const int pairs_per_row = W * (DW_CG / 2);
@@ -32,7 +33,7 @@ __global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwA
     const int hh = h0 + r - LO;
     float2 v = make_float2(0.f, 0.f);
     if (hh >= 0 && hh < a.H) {
-      v = *reinterpret_cast<const float2*>(a.x + (((size_t)fr * a.H + hh) * W + w) * C + c0 + 2 * pl);
+      v = *reinterpret_cast<const float2*>(a.x + (((size_t)fsrc * a.H + hh) * W + w) * C + c0 + 2 * pl);
       if (a.rope_t != nullptr) {
         const int pi = c0 / 2 + pl;
         const float2 ct = a.rope_t[t * n2 + pi], ch = a.rope_h[hh * n2 + pi], cw = a.rope_w[w * n2 + pi];

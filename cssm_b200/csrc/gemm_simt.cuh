@@ -13,7 +13,12 @@ struct GemmArgs {
   int M, N, K, HW;
   const float* A;         // channels-last: (M, K).  planar: plane (frame*a_planes + a_plane0 + k)
   int a_planes, a_plane0;
-  int a_fmul, a_fadd;     // source frame of output frame f is f*a_fmul + a_fadd (0,0 = f), both A layouts
+  // source frame of output frame f, both A layouts: (f / a_fdiv) * a_fmul + a_fadd, where
+  // a_fdiv <= 1 means no division and a_fmul == a_fadd == 0 means the identity.
+  //   last frame of every clip : a_fmul = T, a_fadd = T-1  (output frames = clips)
+  //   one frame repeated over T: a_fdiv = T, a_fmul = 1    (output frames = (clip, t))
+  int a_fdiv, a_fmul, a_fadd;
+  int rope_tlast;         // 1: every output frame is rotated as t = T-1; 0: t = output frame % T
   const float* Wk;        // (K, N) row-major
   const float* bias;      // (N) or nullptr
   float* out;             // channels-last (M, N) or planar plane (frame*o_planes + o_plane0 + n)
@@ -32,14 +37,18 @@ struct GemmArgs {
 };
 
 __host__ __device__ inline int gemm_src_frame(const GemmArgs& g, int f) {
-  return g.a_fmul == 0 && g.a_fadd == 0 ? f : f * g.a_fmul + g.a_fadd;
+  if (g.a_fmul == 0 && g.a_fadd == 0) return f;
+  return (g.a_fdiv > 1 ? f / g.a_fdiv : f) * g.a_fmul + g.a_fadd;
+}
+__host__ __device__ inline int gemm_rope_t(const GemmArgs& g, int f) {
+  return g.rope_tlast ? g.T - 1 : f % g.T;
 }
 
 // channels-last A: source row of output row m
 __host__ __device__ inline size_t gemm_src_row(const GemmArgs& g, int m) {
   if (g.a_fmul == 0 && g.a_fadd == 0) return (size_t)m;
   const int fo = m / g.HW;
-  return (size_t)(fo * g.a_fmul + g.a_fadd) * g.HW + (m - fo * g.HW);
+  return (size_t)gemm_src_frame(g, fo) * g.HW + (m - fo * g.HW);
 }
 
 constexpr int GEMM_BM = 128, GEMM_BK = 16, GEMM_THREADS = 256;
@@ -109,8 +118,8 @@ gemm_simt_kernel(const GemmArgs g) {
         if (m < g.M && k < g.K) {
           v = *reinterpret_cast<const float4*>(g.A + gemm_src_row(g, m) * g.K + k);
           if (g.rope_t != nullptr) {
-            const int px = m % g.HW, fr = gemm_src_frame(g, m / g.HW);
-            const int t = fr % g.T, h = px / g.W, w = px % g.W;
+            const int px = m % g.HW;
+            const int t = gemm_rope_t(g, m / g.HW), h = px / g.W, w = px % g.W;
             const int n2 = g.K >> 1, i = k >> 1;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {

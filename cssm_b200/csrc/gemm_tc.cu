@@ -165,7 +165,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
         if (rot[0] || rot[1]) {
           const int fr = m0 / g.HW;
           px0 = m0 - fr * g.HW;
-          t = gemm_src_frame(g, fr) % g.T;
+          t = gemm_rope_t(g, fr);
         }
 #pragma unroll
         for (int r = 0; r < 8; ++r) {

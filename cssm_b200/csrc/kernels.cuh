@@ -44,6 +44,7 @@ struct GdnDwArgs {
   const float* wk; const float* bias;    // (K,K,1,C), (C)
   int ksz;                               // <= 1: no conv (only the context sums)
   int BT, T, H, W, C;
+  int x_bcast;                           // 1: x holds one frame per clip (frame fr reads fr / T)
   const float2* rope_t; const float2* rope_h; const float2* rope_w;   // nullptr = no RoPE
   float* ctx_part;                       // (BT, H, C) row sums of the rotated input
 };
@@ -69,5 +70,15 @@ struct GdnSpectralArgs {
 };
 int launch_gdn_spectral(const GdnSpectralArgs& a, cudaStream_t st);
 size_t gdn_generic_smem_bytes(int H, int W, int dk);
+
+// ---- whole-block drivers shared by the C-ABI sources ----
+// last_only: y is (B,H,W,C), the last output frame.  x_bcast: x is (B,H,W,C), one frame per
+// batch element standing for all T frames (an image repeated over the sequence).
+int gated_forward_internal(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
+                           const float* x, float* y, void* workspace, size_t workspace_bytes,
+                           void* stream, int last_only, int x_bcast);
+int gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                         const float* x, float* y, void* workspace, size_t workspace_bytes,
+                         void* stream, int last_only, int x_bcast);
 
 }  // namespace cssm

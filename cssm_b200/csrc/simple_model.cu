@@ -1,0 +1,446 @@
+// SimpleCSSM model around one block: stem kernels, readout kernels and the extern "C" drivers.
+//   stem   : per layer conv (3x3 'SAME' or 1x1) + bias -> softplus -> LayerNorm over channels
+//            -> 2x2 max-pool (default stem only), one fused kernel per layer
+//   readout: (block output's last frame + residual frame) -> LayerNorm/softplus -> spatial pool
+//            -> LayerNorm -> Dense head
+// Reference: src/models/simple_cssm.py:244-281 (stem), 482 (residual), 523-556 (readout).
+#include <string.h>
+#include "kernels.cuh"
+
+namespace cssm {
+
+constexpr int SM_MAXC = 64;          // embed_dim limit (channel vectors live in registers)
+constexpr int STEM_THREADS = 128;
+
+__device__ __forceinline__ float softplus_f(float a) {
+  return fmaxf(a, 0.f) + __logf(1.0f + __expf(-fabsf(a)));
+}
+
+// LayerNorm over the C values of v (eps 1e-6, variance as E[x^2] - E[x]^2), in place.
+__device__ __forceinline__ void layer_norm_regs(float (&v)[SM_MAXC], int C, const float* __restrict__ scale,
+                                                const float* __restrict__ bias) {
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < SM_MAXC; ++c)
+    if (c < C) { s += v[c]; ss = fmaf(v[c], v[c], ss); }
+  const float mean = s / (float)C;
+  const float var = fmaxf(ss / (float)C - mean * mean, 0.f);
+  const float rinv = rsqrtf(var + 1e-6f);
+#pragma unroll
+  for (int c = 0; c < SM_MAXC; ++c)
+    if (c < C) v[c] = (v[c] - mean) * rinv * scale[c] + bias[c];
+}
+
+struct StemArgs {
+  const float* x; float* out;           // (N,Hin,Win,Cin) -> (N,Ho,Wo,C), channels-last
+  const float* wk; const float* bk;     // (KS,KS,Cin,C), (C)
+  const float* scale; const float* bias;
+  int N, Hin, Win, Cin, C, Ho, Wo;
+  int w_in_smem;                        // conv kernel staged in shared memory
+};
+
+// One thread per output pixel: the C channel values of each of its POOL x POOL pre-pool pixels
+// are built in registers (conv taps as broadcast float4 weight reads), normalised, and the
+// running maximum is kept.
+template <int KS, int POOL>
+__global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs a) {
+  extern __shared__ __align__(16) float sm[];
+  const int C = a.C, tid = threadIdx.x;
+  const int nw = KS * KS * a.Cin * C;
+  float* wsm = sm;                                   // [tap][ci][C] when w_in_smem
+  float* vec = sm + (a.w_in_smem ? nw : 0);          // bias, scale, lnbias
+  if (a.w_in_smem)
+    for (int i = tid; i < nw; i += STEM_THREADS) wsm[i] = a.wk[i];
+  for (int i = tid; i < C; i += STEM_THREADS) {
+    vec[i] = a.bk[i]; vec[C + i] = a.scale[i]; vec[2 * C + i] = a.bias[i];
+  }
+  __syncthreads();
+  const float* wsrc = a.w_in_smem ? wsm : a.wk;
+  const long long total = (long long)a.N * a.Ho * a.Wo;
+  const long long o = (long long)blockIdx.x * STEM_THREADS + tid;
+  if (o >= total) return;
+  const int wo = (int)(o % a.Wo), ho = (int)((o / a.Wo) % a.Ho), n = (int)(o / ((long long)a.Wo * a.Ho));
+  constexpr int LO = (KS - 1) / 2;
+  float mx[SM_MAXC];
+#pragma unroll
+  for (int c = 0; c < SM_MAXC; ++c) mx[c] = -INFINITY;
+#pragma unroll 1
+  for (int dq = 0; dq < POOL * POOL; ++dq) {
+    const int h = ho * POOL + dq / POOL, w = wo * POOL + dq % POOL;
+    if (h >= a.Hin || w >= a.Win) continue;          // 'SAME' pool padding (-inf) on odd sizes
+    float acc[SM_MAXC];
+#pragma unroll
+    for (int c = 0; c < SM_MAXC; ++c) acc[c] = c < C ? vec[c] : 0.f;
+#pragma unroll 1
+    for (int tap = 0; tap < KS * KS; ++tap) {
+      const int hh = h + tap / KS - LO, ww = w + tap % KS - LO;
+      if (hh < 0 || hh >= a.Hin || ww < 0 || ww >= a.Win) continue;
+      const float* xp = a.x + (((size_t)n * a.Hin + hh) * a.Win + ww) * a.Cin;
+      const float* wp = wsrc + (size_t)tap * a.Cin * C;
+#pragma unroll 1
+      for (int ci = 0; ci < a.Cin; ++ci) {
+        const float xv = __ldg(xp + ci);
+        const float4* w4 = reinterpret_cast<const float4*>(wp + (size_t)ci * C);
+#pragma unroll
+        for (int c4 = 0; c4 < SM_MAXC / 4; ++c4) {
+          if (4 * c4 < C) {
+            const float4 wv = w4[c4];
+            acc[4 * c4 + 0] = fmaf(xv, wv.x, acc[4 * c4 + 0]);
+            acc[4 * c4 + 1] = fmaf(xv, wv.y, acc[4 * c4 + 1]);
+            acc[4 * c4 + 2] = fmaf(xv, wv.z, acc[4 * c4 + 2]);
+            acc[4 * c4 + 3] = fmaf(xv, wv.w, acc[4 * c4 + 3]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < SM_MAXC; ++c)
+      if (c < C) acc[c] = softplus_f(acc[c]);
+    layer_norm_regs(acc, C, vec + C, vec + 2 * C);
+#pragma unroll
+    for (int c = 0; c < SM_MAXC; ++c) mx[c] = fmaxf(mx[c], acc[c]);
+  }
+  float4* op = reinterpret_cast<float4*>(a.out + (size_t)o * C);
+#pragma unroll
+  for (int c4 = 0; c4 < SM_MAXC / 4; ++c4)
+    if (4 * c4 < C) op[c4] = make_float4(mx[4 * c4], mx[4 * c4 + 1], mx[4 * c4 + 2], mx[4 * c4 + 3]);
+}
+
+template <int KS, int POOL>
+static int launch_stem_layer(StemArgs a, cudaStream_t st) {
+  const size_t wbytes = (size_t)KS * KS * a.Cin * a.C * sizeof(float);
+  a.w_in_smem = wbytes <= 160 * 1024 ? 1 : 0;
+  const size_t smem = (a.w_in_smem ? wbytes : 0) + 3 * (size_t)a.C * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(stem_layer_kernel<KS, POOL>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  const long long total = (long long)a.N * a.Ho * a.Wo;
+  const unsigned grid = (unsigned)((total + STEM_THREADS - 1) / STEM_THREADS);
+  stem_layer_kernel<KS, POOL><<<grid, STEM_THREADS, smem, st>>>(a);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------------- readout ----
+constexpr int RO_THREADS = 256, RO_ROWS = 8;
+
+struct ReadoutArgs {
+  const float* y; size_t y_stride;      // block output's last frame, per batch element
+  const float* res; size_t res_stride;  // residual frame
+  const float* pre_scale; const float* pre_bias;
+  const float* post_scale; const float* post_bias;
+  const float* head_k; const float* head_b;
+  float* partial; float* logits;
+  int B, H, W, C, pool_max, norm_post_order, ncls, bands;
+};
+
+// grid (bands, B): LayerNorm/softplus of (y + res) per pixel, pooled over the band's pixels
+__global__ void __launch_bounds__(RO_THREADS) readout_pool_kernel(const ReadoutArgs a) {
+  __shared__ float red[RO_THREADS / 32][SM_MAXC];
+  __shared__ float vec[2 * SM_MAXC];
+  const int C = a.C, tid = threadIdx.x, band = blockIdx.x, b = blockIdx.y;
+  for (int i = tid; i < C; i += RO_THREADS) { vec[i] = a.pre_scale[i]; vec[SM_MAXC + i] = a.pre_bias[i]; }
+  __syncthreads();
+  const int h0 = band * RO_ROWS, rows = min(RO_ROWS, a.H - h0);
+  const int npx = rows * a.W;
+  float pool[SM_MAXC];
+#pragma unroll
+  for (int c = 0; c < SM_MAXC; ++c) pool[c] = a.pool_max ? -INFINITY : 0.f;
+  for (int p = tid; p < npx; p += RO_THREADS) {
+    const size_t px = (size_t)h0 * a.W + p;
+    const float4* yp = reinterpret_cast<const float4*>(a.y + (size_t)b * a.y_stride + px * C);
+    const float4* rp = reinterpret_cast<const float4*>(a.res + (size_t)b * a.res_stride + px * C);
+    float v[SM_MAXC];
+#pragma unroll
+    for (int c4 = 0; c4 < SM_MAXC / 4; ++c4) {
+      if (4 * c4 < C) {
+        const float4 yv = __ldg(yp + c4), rv = __ldg(rp + c4);
+        v[4 * c4] = yv.x + rv.x; v[4 * c4 + 1] = yv.y + rv.y;
+        v[4 * c4 + 2] = yv.z + rv.z; v[4 * c4 + 3] = yv.w + rv.w;
+      } else {
+        v[4 * c4] = v[4 * c4 + 1] = v[4 * c4 + 2] = v[4 * c4 + 3] = 0.f;
+      }
+    }
+    if (a.norm_post_order) {
+#pragma unroll
+      for (int c = 0; c < SM_MAXC; ++c) if (c < C) v[c] = softplus_f(v[c]);
+      layer_norm_regs(v, C, vec, vec + SM_MAXC);
+    } else {
+      layer_norm_regs(v, C, vec, vec + SM_MAXC);
+#pragma unroll
+      for (int c = 0; c < SM_MAXC; ++c) if (c < C) v[c] = softplus_f(v[c]);
+    }
+#pragma unroll
+    for (int c = 0; c < SM_MAXC; ++c) pool[c] = a.pool_max ? fmaxf(pool[c], v[c]) : pool[c] + v[c];
+  }
+#pragma unroll
+  for (int c = 0; c < SM_MAXC; ++c) {
+    float r = pool[c];
+    for (int off = 16; off > 0; off >>= 1) {
+      const float o = __shfl_down_sync(0xffffffffu, r, off);
+      r = a.pool_max ? fmaxf(r, o) : r + o;
+    }
+    if ((tid & 31) == 0) red[tid >> 5][c] = r;
+  }
+  __syncthreads();
+  if (tid < C) {
+    float r = red[0][tid];
+    for (int w = 1; w < RO_THREADS / 32; ++w) r = a.pool_max ? fmaxf(r, red[w][tid]) : r + red[w][tid];
+    a.partial[((size_t)b * a.bands + band) * C + tid] = r;
+  }
+}
+
+// grid B, 64 threads: combine the band partials, LayerNorm (norm_post), Dense head
+__global__ void __launch_bounds__(SM_MAXC) readout_head_kernel(const ReadoutArgs a) {
+  __shared__ float v[SM_MAXC];
+  __shared__ float stats[2];
+  const int C = a.C, tid = threadIdx.x, b = blockIdx.x;
+  float r = 0.f;
+  if (tid < C) {
+    r = a.partial[(size_t)b * a.bands * C + tid];
+    for (int k = 1; k < a.bands; ++k) {
+      const float o = a.partial[((size_t)b * a.bands + k) * C + tid];
+      r = a.pool_max ? fmaxf(r, o) : r + o;
+    }
+    if (!a.pool_max) r /= (float)(a.H * a.W);
+    v[tid] = r;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.f, ss = 0.f;
+    for (int c = 0; c < C; ++c) { s += v[c]; ss = fmaf(v[c], v[c], ss); }
+    const float mean = s / (float)C;
+    stats[0] = mean;
+    stats[1] = rsqrtf(fmaxf(ss / (float)C - mean * mean, 0.f) + 1e-6f);
+  }
+  __syncthreads();
+  if (tid < C) v[tid] = (v[tid] - stats[0]) * stats[1] * a.post_scale[tid] + a.post_bias[tid];
+  __syncthreads();
+  if (tid < a.ncls) {
+    float acc = a.head_b[tid];
+    for (int c = 0; c < C; ++c) acc = fmaf(v[c], a.head_k[(size_t)c * a.ncls + tid], acc);
+    a.logits[(size_t)b * a.ncls + tid] = acc;
+  }
+}
+
+// ------------------------------------------------------------------- host helpers ----
+struct SimpleDims { int N, H, W; };   // stem output: N frames of H x W x embed_dim
+
+static int simple_validate(const cssm_simple_desc* d) {
+  if (!d) return CSSM_ERR_NULL;
+  if (d->B <= 0 || d->T <= 0 || d->Hin <= 0 || d->Win <= 0 || d->Cin <= 0 || d->num_classes <= 0)
+    return CSSM_ERR_DIMS;
+  if (d->embed_dim <= 0 || d->embed_dim % 4 != 0 || d->embed_dim > SM_MAXC) return CSSM_ERR_UNSUPPORTED;
+  if (d->num_classes > SM_MAXC) return CSSM_ERR_UNSUPPORTED;
+  if (d->stem_mode != 0 && d->stem_mode != 1) return CSSM_ERR_UNSUPPORTED;
+  if (d->stem_mode == 0 && (d->stem_layers < 1 || d->stem_layers > 4)) return CSSM_ERR_UNSUPPORTED;
+  if (d->block != 0 && d->block != 1) return CSSM_ERR_UNSUPPORTED;
+  if (d->pool_type != 0 && d->pool_type != 1) return CSSM_ERR_UNSUPPORTED;
+  if (d->readout_norm != 0 && d->readout_norm != 1) return CSSM_ERR_UNSUPPORTED;
+  return CSSM_OK;
+}
+
+static SimpleDims stem_out_dims(const cssm_simple_desc& d) {
+  SimpleDims o;
+  o.N = d.image_input ? d.B : d.B * d.T;
+  o.H = d.Hin; o.W = d.Win;
+  if (d.stem_mode == 0)
+    for (int i = 0; i < d.stem_layers; ++i) { o.H = (o.H + 1) / 2; o.W = (o.W + 1) / 2; }
+  return o;
+}
+
+static bool block_matches(const cssm_simple_desc& d, const void* bd) {
+  const SimpleDims o = stem_out_dims(d);
+  if (d.block == 0) {
+    const cssm_gated_desc* g = (const cssm_gated_desc*)bd;
+    return g->B == d.B && g->T == d.T && g->H == o.H && g->W == o.W && g->C == d.embed_dim;
+  }
+  const cssm_gdn_desc* g = (const cssm_gdn_desc*)bd;
+  return g->B == d.B && g->T == d.T && g->H == o.H && g->W == o.W && g->C == d.embed_dim;
+}
+
+struct SimpleWs { size_t feat, tmp, y, partial, block, total; };
+static SimpleWs simple_ws_layout(const cssm_simple_desc& d, const void* bd) {
+  SimpleWs l;
+  const SimpleDims o = stem_out_dims(d);
+  const size_t C = d.embed_dim;
+  const size_t N = o.N;
+  size_t off = 0;
+  l.feat = off; off += round_up(N * o.H * o.W * C * sizeof(float), 256);
+  // ping-pong buffers of a multi-layer stem: the first layer's output is the largest
+  size_t tmp = 0;
+  if (d.stem_mode == 0 && d.stem_layers > 1)
+    tmp = N * ((d.Hin + 1) / 2) * ((d.Win + 1) / 2) * C * sizeof(float);
+  l.tmp = off; off += 2 * round_up(tmp, 256);
+  l.y = off; off += round_up((size_t)d.B * d.T * o.H * o.W * C * sizeof(float), 256);
+  l.partial = off; off += round_up((size_t)d.B * ((o.H + RO_ROWS - 1) / RO_ROWS) * C * sizeof(float), 256);
+  l.block = off;
+  off += d.block == 0 ? cssm_gated_workspace_bytes((const cssm_gated_desc*)bd)
+                      : cssm_gdn_workspace_bytes((const cssm_gdn_desc*)bd);
+  l.total = round_up(off, 256);
+  return l;
+}
+
+static int run_stem(const cssm_simple_desc* d, const cssm_simple_weights* w, const float* x,
+                    float* feat, float* tmp0, float* tmp1, cudaStream_t st) {
+  StemArgs a;
+  memset(&a, 0, sizeof(a));
+  a.N = d->image_input ? d->B : d->B * d->T;
+  a.C = d->embed_dim;
+  if (d->stem_mode == 1) {
+    if (!w->conv_kernel[0] || !w->conv_bias[0] || !w->norm_scale[0] || !w->norm_bias[0]) return CSSM_ERR_NULL;
+    a.x = x; a.out = feat; a.wk = w->conv_kernel[0]; a.bk = w->conv_bias[0];
+    a.scale = w->norm_scale[0]; a.bias = w->norm_bias[0];
+    a.Hin = d->Hin; a.Win = d->Win; a.Cin = d->Cin; a.Ho = d->Hin; a.Wo = d->Win;
+    return launch_stem_layer<1, 1>(a, st);
+  }
+  const float* src = x;
+  int H = d->Hin, W = d->Win, Cin = d->Cin;
+  for (int i = 0; i < d->stem_layers; ++i) {
+    if (!w->conv_kernel[i] || !w->conv_bias[i] || !w->norm_scale[i] || !w->norm_bias[i]) return CSSM_ERR_NULL;
+    const bool last = i == d->stem_layers - 1;
+    float* dst = last ? feat : ((i & 1) ? tmp1 : tmp0);
+    a.x = src; a.out = dst; a.wk = w->conv_kernel[i]; a.bk = w->conv_bias[i];
+    a.scale = w->norm_scale[i]; a.bias = w->norm_bias[i];
+    a.Hin = H; a.Win = W; a.Cin = Cin; a.Ho = (H + 1) / 2; a.Wo = (W + 1) / 2;
+    const int s = launch_stem_layer<3, 2>(a, st);
+    if (s != CSSM_OK) return s;
+    src = dst; H = a.Ho; W = a.Wo; Cin = d->embed_dim;
+  }
+  return CSSM_OK;
+}
+
+static int run_readout(const cssm_simple_desc* d, const cssm_simple_weights* w, int H, int W,
+                       const float* y, size_t ys, const float* res, size_t rs, float* partial,
+                       float* logits, cudaStream_t st) {
+  if (!w->norm_pre_scale || !w->norm_pre_bias || !w->norm_post_scale || !w->norm_post_bias ||
+      !w->head_kernel || !w->head_bias)
+    return CSSM_ERR_NULL;
+  ReadoutArgs a;
+  memset(&a, 0, sizeof(a));
+  a.y = y; a.y_stride = ys; a.res = res; a.res_stride = rs;
+  a.pre_scale = w->norm_pre_scale; a.pre_bias = w->norm_pre_bias;
+  a.post_scale = w->norm_post_scale; a.post_bias = w->norm_post_bias;
+  a.head_k = w->head_kernel; a.head_b = w->head_bias;
+  a.partial = partial; a.logits = logits;
+  a.B = d->B; a.H = H; a.W = W; a.C = d->embed_dim; a.pool_max = d->pool_type;
+  a.norm_post_order = d->readout_norm; a.ncls = d->num_classes;
+  a.bands = (H + RO_ROWS - 1) / RO_ROWS;
+  readout_pool_kernel<<<dim3(a.bands, d->B), RO_THREADS, 0, st>>>(a);
+  int s = check_launch();
+  if (s != CSSM_OK) return s;
+  readout_head_kernel<<<d->B, SM_MAXC, 0, st>>>(a);
+  return check_launch();
+}
+
+}  // namespace cssm
+
+using namespace cssm;
+
+extern "C" {
+
+size_t cssm_simple_workspace_bytes(const cssm_simple_desc* d, const void* block_desc) {
+  if (simple_validate(d) != CSSM_OK || !block_desc || !block_matches(*d, block_desc)) return 0;
+  return simple_ws_layout(*d, block_desc).total;
+}
+
+int cssm_simple_stem(const cssm_simple_desc* d, const cssm_simple_weights* w, const float* x,
+                     float* feat, void* workspace, size_t workspace_bytes, void* stream) {
+  int s = simple_validate(d);
+  if (s != CSSM_OK) return s;
+  if (!w || !x || !feat) return CSSM_ERR_NULL;
+  if (!aligned16(x) || !aligned16(feat)) return CSSM_ERR_ALIGN;
+  float* t0 = nullptr;
+  float* t1 = nullptr;
+  if (d->stem_mode == 0 && d->stem_layers > 1) {
+    const SimpleDims o = stem_out_dims(*d);
+    const size_t tmp = round_up((size_t)o.N * ((d->Hin + 1) / 2) * ((d->Win + 1) / 2) * d->embed_dim * sizeof(float), 256);
+    if (!workspace) return CSSM_ERR_NULL;
+    if (!aligned16(workspace)) return CSSM_ERR_ALIGN;
+    if (workspace_bytes < 2 * tmp) return CSSM_ERR_WORKSPACE;
+    t0 = (float*)workspace; t1 = (float*)((char*)workspace + tmp);
+  }
+  return run_stem(d, w, x, feat, t0, t1, (cudaStream_t)stream);
+}
+
+int cssm_simple_readout(const cssm_simple_desc* d, const cssm_simple_weights* w, int32_t H,
+                        int32_t W, const float* y_last, size_t y_stride, const float* res,
+                        size_t res_stride, float* partial, float* logits, void* stream) {
+  int s = simple_validate(d);
+  if (s != CSSM_OK) return s;
+  if (!w || !y_last || !res || !partial || !logits) return CSSM_ERR_NULL;
+  if (H <= 0 || W <= 0) return CSSM_ERR_DIMS;
+  if (!aligned16(y_last) || !aligned16(res) || y_stride % 4 != 0 || res_stride % 4 != 0) return CSSM_ERR_ALIGN;
+  return run_readout(d, w, H, W, y_last, y_stride, res, res_stride, partial, logits, (cudaStream_t)stream);
+}
+
+int cssm_simple_forward(const cssm_simple_desc* d, const cssm_simple_weights* w,
+                        const void* block_desc, const void* block_weights, const void* block_plan,
+                        const float* x, float* logits, void* workspace, size_t workspace_bytes,
+                        int32_t flags, void* stream) {
+  int s = simple_validate(d);
+  if (s != CSSM_OK) return s;
+  if (!w || !block_desc || !block_weights || !block_plan || !x || !logits || !workspace) return CSSM_ERR_NULL;
+  if (!block_matches(*d, block_desc)) return CSSM_ERR_DIMS;
+  if (!aligned16(x) || !aligned16(workspace)) return CSSM_ERR_ALIGN;
+  const SimpleWs l = simple_ws_layout(*d, block_desc);
+  if (workspace_bytes < l.total) return CSSM_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  const SimpleDims o = stem_out_dims(*d);
+  float* feat = (float*)(ws + l.feat);
+  float* y = (float*)(ws + l.y);
+  const size_t tmp_half = (l.y - l.tmp) / 2;
+  s = run_stem(d, w, x, feat, (float*)(ws + l.tmp), (float*)(ws + l.tmp + tmp_half), st);
+  if (s != CSSM_OK) return s;
+  const int last_only = (flags & CSSM_SIMPLE_LAST_FRAME_ONLY) ? 1 : 0;
+  const size_t bws = l.total - l.block;
+  if (d->block == 0)
+    s = gated_forward_internal((const cssm_gated_desc*)block_desc, (const cssm_gated_weights*)block_weights,
+                               block_plan, feat, y, ws + l.block, bws, stream, last_only, d->image_input);
+  else
+    s = gdn_forward_internal((const cssm_gdn_desc*)block_desc, (const cssm_gdn_weights*)block_weights,
+                             block_plan, feat, y, ws + l.block, bws, stream, last_only, d->image_input);
+  if (s != CSSM_OK) return s;
+  const size_t frame = (size_t)o.H * o.W * d->embed_dim;
+  const float* y_last = last_only ? y : y + (size_t)(d->T - 1) * frame;
+  const size_t ys = last_only ? frame : (size_t)d->T * frame;
+  const float* res = d->image_input ? feat : feat + (size_t)(d->T - 1) * frame;
+  const size_t rs = d->image_input ? frame : (size_t)d->T * frame;
+  return run_readout(d, w, o.H, o.W, y_last, ys, res, rs, (float*)(ws + l.partial), logits, st);
+}
+
+size_t cssm_simple_host_workspace_bytes(const cssm_simple_desc* d, const void* block_desc) {
+  const size_t base = cssm_simple_workspace_bytes(d, block_desc);
+  if (base == 0) return 0;
+  const size_t nx = (size_t)(d->image_input ? d->B : d->B * d->T) * d->Hin * d->Win * d->Cin * sizeof(float);
+  return base + round_up(nx, 256) + round_up((size_t)d->B * d->num_classes * sizeof(float), 256);
+}
+
+int cssm_simple_forward_host(const cssm_simple_desc* d, const cssm_simple_weights* w,
+                             const void* block_desc, const void* block_weights,
+                             const void* block_plan, const float* x_host, float* logits_host,
+                             void* workspace, size_t workspace_bytes, int32_t flags, void* stream) {
+  const size_t base = cssm_simple_workspace_bytes(d, block_desc);
+  if (base == 0) return simple_validate(d) != CSSM_OK ? simple_validate(d) : CSSM_ERR_DIMS;
+  if (!x_host || !logits_host || !workspace) return CSSM_ERR_NULL;
+  if (!aligned16(workspace)) return CSSM_ERR_ALIGN;
+  if (workspace_bytes < cssm_simple_host_workspace_bytes(d, block_desc)) return CSSM_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t nx = (size_t)(d->image_input ? d->B : d->B * d->T) * d->Hin * d->Win * d->Cin * sizeof(float);
+  const size_t nl = (size_t)d->B * d->num_classes * sizeof(float);
+  char* ws = (char*)workspace;
+  float* xd = (float*)(ws + base);
+  float* ld = (float*)(ws + base + round_up(nx, 256));
+  cudaError_t e = cudaMemcpyAsync(xd, x_host, nx, cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  const int s = cssm_simple_forward(d, w, block_desc, block_weights, block_plan, xd, ld, workspace,
+                                    base, flags, stream);
+  if (s != CSSM_OK) return s;
+  e = cudaMemcpyAsync(logits_host, ld, nl, cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  return CSSM_OK;
+}
+
+}  // extern "C"

@@ -231,6 +231,78 @@ int cssm_gdn_forward_last(const cssm_gdn_desc* d, const cssm_gdn_weights* w, con
                           const float* x, float* y_last, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* ================================================================ SimpleCSSM model ====
+ * Inference forward of the reference's SimpleCSSM wrapper around ONE block (depth 1):
+ *   stem -> x + block(x) -> last frame -> norm_pre/act -> spatial pool -> norm_post -> head.
+ * Replaces SimpleCSSM.__call__ (src/models/simple_cssm.py:173-558) for stem_norm_order 'post',
+ * act 'softplus', norm 'layer', frame_readout 'last', pos_embed passed to the block as RoPE
+ * (src/models/simple_cssm.py:318-332), no register tokens.  Parameter names: conv{i}/norm{i}
+ * (stem layer i = 1..), cssm_0 (the block), norm_pre, norm_post, head. */
+typedef struct cssm_simple_desc {
+  int32_t B;             /* images or clips                                                   */
+  int32_t T;             /* frames per clip; for image input the seq_len the image repeats to */
+  int32_t Hin, Win, Cin; /* one input frame (Hin, Win, Cin), channels-last                    */
+  int32_t image_input;   /* 1: x is (B,Hin,Win,Cin) (simple_cssm.py:238-241); 0: (B,T,Hin,Win,Cin) */
+  int32_t stem_mode;     /* 0 'default': stem_layers x [conv3x3 SAME, softplus, LayerNorm,
+                            2x2 max-pool]; 1 'pathtracker': conv1x1, softplus, LayerNorm       */
+  int32_t stem_layers;   /* 1..4 for the default stem                                         */
+  int32_t embed_dim;     /* multiple of 4, <= 64                                              */
+  int32_t block;         /* 0 GatedCSSM (block_desc is a cssm_gated_desc), 1 GatedDeltaNetCSSM */
+  int32_t pool_type;     /* 0 mean, 1 max                                                     */
+  int32_t readout_norm;  /* 0 'pre' (norm -> act), 1 'post' (act -> norm)                     */
+  int32_t num_classes;   /* 1..64                                                             */
+} cssm_simple_desc;
+
+typedef struct cssm_simple_weights {
+  const float* conv_kernel[4];   /* stem conv i: (k,k,cin_i,embed_dim), k = 3 (default) or 1   */
+  const float* conv_bias[4];     /* (embed_dim)                                                */
+  const float* norm_scale[4];    /* stem LayerNorm i                                           */
+  const float* norm_bias[4];
+  const float* norm_pre_scale;   /* (embed_dim)                                                */
+  const float* norm_pre_bias;
+  const float* norm_post_scale;
+  const float* norm_post_bias;
+  const float* head_kernel;      /* (embed_dim, num_classes)                                   */
+  const float* head_bias;        /* (num_classes)                                              */
+} cssm_simple_weights;
+
+/* flags of cssm_simple_forward* */
+#define CSSM_SIMPLE_LAST_FRAME_ONLY 1   /* evaluate the block through its last-frame-only entry
+                                           point (same logits; the earlier output frames, which
+                                           the readout never reads, are not produced) */
+
+/* block_desc: the cssm_gated_desc / cssm_gdn_desc of the block; its B, T, H, W, C must equal the
+ * stem's output (B, T, Hin >> stem_layers rounded up, ..., embed_dim).  0 if inconsistent. */
+size_t cssm_simple_workspace_bytes(const cssm_simple_desc* d, const void* block_desc);
+
+/* Stem alone: x frames -> features.  Image input: feat is (B,H,W,C) (the frame that the block
+ * then reads for every t); clip input: (B,T,H,W,C).  Replaces simple_cssm.py:244-281. */
+int cssm_simple_stem(const cssm_simple_desc* d, const cssm_simple_weights* w, const float* x,
+                     float* feat, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Readout alone: logits (B,num_classes) from the block's last output frame y_last (B,H,W,C)
+ * plus the residual frame res (B,H,W,C) (simple_cssm.py:482, 523-556).  y_stride / res_stride:
+ * floats between consecutive batch elements of each (H*W*C when packed).  partial: scratch of
+ * B * ceil(H/8) * C floats. */
+int cssm_simple_readout(const cssm_simple_desc* d, const cssm_simple_weights* w, int32_t H,
+                        int32_t W, const float* y_last, size_t y_stride, const float* res,
+                        size_t res_stride, float* partial, float* logits, void* stream);
+
+/* Whole model on device buffers: x as described by image_input, logits (B, num_classes). */
+int cssm_simple_forward(const cssm_simple_desc* d, const cssm_simple_weights* w,
+                        const void* block_desc, const void* block_weights, const void* block_plan,
+                        const float* x, float* logits, void* workspace, size_t workspace_bytes,
+                        int32_t flags, void* stream);
+
+/* Same with x and logits in HOST memory (pinned for full copy speed): copies x to the device
+ * (staging area inside the workspace: cssm_simple_host_workspace_bytes), runs the model, copies
+ * the logits back and waits for the stream. */
+size_t cssm_simple_host_workspace_bytes(const cssm_simple_desc* d, const void* block_desc);
+int cssm_simple_forward_host(const cssm_simple_desc* d, const cssm_simple_weights* w,
+                             const void* block_desc, const void* block_weights,
+                             const void* block_plan, const float* x_host, float* logits_host,
+                             void* workspace, size_t workspace_bytes, int32_t flags, void* stream);
+
 /* ---- diagnostics (no counterpart in the reference) ----
  * cssm_debug_set_gemm_backend: 0 = tensor-core (tcgen05) projections where they apply
  * (default), 1 = CUDA-core fp32 projections everywhere; process-wide, for A/B tests.  Higher

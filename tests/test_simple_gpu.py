@@ -1,0 +1,84 @@
+"""GPU parity of the SimpleCSSM model path (stem, block + residual, last-frame readout) through
+the C ABI against the NumPy oracle.  Tolerance: rel-L2 <= 1e-4 on features and logits (fp32)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cssm_oracle as orc
+from oracle import simple_oracle as so
+from cssm_b200 import SimpleCSSM
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+
+def _model(cssm_type, E, ks, pos, stem_mode, stem_layers, pool, rnorm, **extra):
+    return SimpleCSSM(num_classes=extra.pop("num_classes", 2), embed_dim=E, cssm_type=cssm_type,
+                      kernel_size=ks, pos_embed=pos, stem_mode=stem_mode, stem_layers=stem_layers,
+                      pool_type=pool, readout_norm=rnorm, gate_type="factored", **extra)
+
+
+def _block_kwargs(m):
+    rope = m.pos_embed if m.pos_embed != "none" else "none"
+    if m.cssm_type == "gated":
+        return dict(kernel_size=m.kernel_size, rope_mode=rope, gate_type=m.gate_type,
+                    short_conv_size=m.short_conv_size,
+                    short_conv_spatial_size=m.short_conv_spatial_size)
+    return dict(delta_key_dim=m.delta_key_dim, kernel_size=m.kernel_size, rope_mode=rope,
+                gate_type=m.gate_type, short_conv_size=m.short_conv_size,
+                qkv_conv_size=m.qkv_conv_size)
+
+
+CASES = [
+    # cssm_type, E, ks, pos_embed, stem_mode, stem_layers, pool, readout_norm, x shape, extra
+    ("gated", 8, 5, "spatiotemporal", "default", 1, "max", "pre", (3, 16, 16, 1), dict(seq_len=3)),
+    ("gated", 8, 3, "none", "default", 2, "mean", "post", (2, 20, 20, 3), dict(seq_len=2)),
+    ("gated", 64, 11, "spatiotemporal", "default", 1, "max", "pre", (2, 128, 128, 1), dict(seq_len=4)),
+    ("gated", 16, 5, "mrope", "default", 1, "mean", "pre", (2, 3, 14, 18, 2), dict()),        # clips, odd pool
+    ("gdn", 8, 5, "mrope", "pathtracker", 1, "mean", "pre", (2, 4, 8, 8, 3), dict(delta_key_dim=4)),
+    ("gdn", 64, 11, "spatiotemporal", "pathtracker", 1, "max", "pre", (2, 5, 32, 32, 3),
+     dict(delta_key_dim=4, num_classes=3)),
+    ("gdn", 16, 11, "mrope", "default", 1, "max", "pre", (2, 64, 64, 1),
+     dict(delta_key_dim=4, qkv_conv_size=5, seq_len=3)),                                     # image input, dwconv
+    ("gdn", 8, 3, "none", "default", 1, "mean", "pre", (2, 16, 16, 1),
+     dict(delta_key_dim=4, qkv_conv_size=1, seq_len=3)),                                     # image input, no dwconv
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"{c[0]}-E{c[1]}-{c[4]}{c[5]}-{'x'.join(map(str, c[8]))}")
+def test_model_parity(case):
+    cssm_type, E, ks, pos, stem_mode, layers, pool, rnorm, xshape, extra = case
+    m = _model(cssm_type, E, ks, pos, stem_mode, layers, pool, rnorm, **dict(extra))
+    rng = np.random.default_rng(3)
+    x = rng.random(xshape).astype(np.float32)
+    H, W = m.feature_hw(xshape[-3], xshape[-2])
+    bkw = _block_kwargs(m)
+    p = so.init_simple_params(5, cin=xshape[-1], embed_dim=E, H=H, W=W, num_classes=m.num_classes,
+                              cssm_type=cssm_type, stem_mode=stem_mode, stem_layers=layers,
+                              bias_scale=0.1, block_kwargs=bkw)
+    ref, inter = so.simple_forward(p, x, cssm_type=cssm_type, seq_len=m.seq_len, stem_mode=stem_mode,
+                                   stem_layers=layers, pool_type=pool, readout_norm=rnorm,
+                                   block_kwargs=bkw, return_intermediates=True)
+    bound = m.bind({"params": p})
+    xd = torch.from_numpy(x).cuda()
+    feat = bound.stem(xd).cpu().numpy()
+    ref_feat = inter["stem"][:, 0] if len(xshape) == 4 else inter["stem"]
+    assert orc.rel_l2(feat, ref_feat) <= TOL
+    logits = bound(xd).cpu().numpy()
+    assert np.isfinite(logits).all()
+    assert orc.rel_l2(logits, ref) <= TOL
+    # the last-frame-only evaluation of the block gives the same logits
+    logits_last = bound(xd, last_frame_only=True).cpu().numpy()
+    assert orc.rel_l2(logits_last, logits) <= 1e-5
+    # host-buffer entry point
+    lh = bound.forward_host(torch.from_numpy(x).pin_memory()).numpy()
+    assert np.array_equal(lh, logits)
+
+
+def test_unsupported_fields_raise():
+    with pytest.raises(NotImplementedError):
+        SimpleCSSM(cssm_type="gated", depth=2).bind({"params": {}})
+    with pytest.raises(NotImplementedError):
+        SimpleCSSM(cssm_type="hgru_bi").bind({"params": {}})
+    with pytest.raises(NotImplementedError):
+        SimpleCSSM(cssm_type="gated", embed_dim=128).bind({"params": {}})
