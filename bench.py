@@ -1,12 +1,18 @@
-"""Benchmark of the gated spectral block forward (the hot path) on B200.
+"""Benchmark of the CSSM spectral-block forward on B200 (model-level images/s, block stage times,
+roofline of the fused spectral kernel, end-to-end figure through the host-buffer entry point).
 
     python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload cfg2]
 
-One step = one GatedCSSM block forward over one per-GPU batch of synthetic block inputs.
-Prints ONE JSON line (rank 0).  `value` is device-resident throughput; `e2e` goes through
-the host-buffer C-ABI entry point with pinned host memory; `roofline` is the fused
-spectral kernel timed with CUDA events on its launch stream; `cpu_baseline` is the CPU
-restatement of the reference block on the host cores (JAX is not installable here).
+One step = one forward over one per-GPU batch of synthetic inputs of the workload's model: the
+reference's SimpleCSSM wrapper (stem -> spectral block + residual -> last-frame readout) around
+one GatedCSSM or GatedDeltaNetCSSM block.  Prints ONE JSON line (rank 0):
+  value     images/s, images resident on the device, all T output frames of the block computed
+  e2e       the same through cssm_simple_forward_host: pinned host images in, host logits out
+  block     the block alone on its (B,T,H,W,C) input: per-stage CUDA-event times
+  roofline  the fused spectral kernel: algorithmic bytes / its CUDA-event time, vs measured peak
+  last_frame_only   the same model with the block evaluated through its last-frame-only entry
+  cpu_baseline      the CPU restatement of the same model on the host cores (JAX cannot be
+                    installed here, so the reference itself cannot run)
 """
 from __future__ import annotations
 
@@ -22,130 +28,71 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+_GATED = dict(cssm_type="gated", embed_dim=64, num_classes=2, short_conv_size=4, short_conv_spatial_size=3)
+_GDN = dict(cssm_type="gdn", embed_dim=64, num_classes=2, short_conv_size=4, delta_key_dim=4,
+            gate_type="factored", output_norm="rms")
 WORKLOADS = {
-    # BASELINE.json configs[1]: Mamba-SCSSM gated, ks 11, factored gates, T=8, C=64, one stem
-    # layer (128x128 image -> 64x64 block input), per-GPU batch 128.
-    "cfg2": dict(B=128, T=8, H=64, W=64, C=64, kernel_size=11, gate_type="factored",
-                 rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
-    # small case for profiler captures (activations 134 MB > L2, < 1 GB on the device)
-    "cfg2_small": dict(B=16, T=8, H=64, W=64, C=64, kernel_size=11, gate_type="factored",
-                       rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
-    # BASELINE.json configs[0] (main.py defaults: dense gates, 2 stem layers -> 32x32), batch 8
-    "cfg1": dict(B=8, T=1, H=32, W=32, C=64, kernel_size=1, gate_type="dense",
-                 rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
-    # 32x32 planes at a bandwidth-relevant size (the gated block on the block-input shape of cfg 4)
-    "gated32": dict(B=128, T=32, H=32, W=32, C=64, kernel_size=11, gate_type="factored",
-                    rope_mode="spatiotemporal", short_conv_size=4, short_conv_spatial_size=3),
-    # BASELINE.json configs[2]: GDN-SCSSM, ks 11, qkv_conv 5, d_k 4, T=8, C=64, RMSNorm, mrope
-    "cfg3": dict(block="gdn", B=128, T=8, H=64, W=64, C=64, kernel_size=11, gate_type="factored",
-                 rope_mode="mrope", short_conv_size=4, qkv_conv_size=5, delta_key_dim=4),
-    "cfg3_small": dict(block="gdn", B=8, T=8, H=64, W=64, C=64, kernel_size=11,
-                       gate_type="factored", rope_mode="mrope", short_conv_size=4, qkv_conv_size=5,
-                       delta_key_dim=4),
-    # BASELINE.json configs[3]: GDN-SCSSM video, T=32, 32x32 block input, qkv_conv 1
-    "cfg4": dict(block="gdn", B=128, T=32, H=32, W=32, C=64, kernel_size=11, gate_type="factored",
-                 rope_mode="spatiotemporal", short_conv_size=4, qkv_conv_size=1, delta_key_dim=4),
+    # BASELINE.json configs[1]: Mamba-SCSSM gated, ks 11, factored gates, T=8 (image repeated),
+    # embed_dim 64, depth 1, one stem layer (128x128 -> 64x64), max-pool + linear 2-way head
+    "cfg2": dict(model=dict(_GATED, kernel_size=11, gate_type="factored", seq_len=8, stem_layers=1,
+                            pool_type="max", pos_embed="spatiotemporal"),
+                 B=128, data="strokes"),
+    # the same model at a size for profiler captures (activations 134 MB > L2, < 1 GB on the device)
+    "cfg2_small": dict(model=dict(_GATED, kernel_size=11, gate_type="factored", seq_len=8, stem_layers=1,
+                                  pool_type="max", pos_embed="spatiotemporal"),
+                       B=16, data="strokes"),
+    # BASELINE.json configs[0] (main.py defaults: dense gates, two stem layers -> 32x32, mean pool)
+    "cfg1": dict(model=dict(_GATED, kernel_size=1, gate_type="dense", seq_len=1, stem_layers=2,
+                            pool_type="mean", pos_embed="spatiotemporal"),
+                 B=8, data="strokes"),
+    # 32x32 planes at a bandwidth-relevant size: the gated model on the clip input of configs[3]
+    "gated32": dict(model=dict(_GATED, kernel_size=11, gate_type="factored", stem_mode="pathtracker",
+                               pool_type="max", pos_embed="spatiotemporal"),
+                    B=128, data="dots"),
+    # BASELINE.json configs[2]: GDN-SCSSM, ks 11, qkv_conv 5, d_k 4, T=8, RMSNorm, mrope
+    "cfg3": dict(model=dict(_GDN, kernel_size=11, qkv_conv_size=5, seq_len=8, stem_layers=1,
+                            pool_type="max", pos_embed="mrope"),
+                 B=128, data="strokes"),
+    "cfg3_small": dict(model=dict(_GDN, kernel_size=11, qkv_conv_size=5, seq_len=8, stem_layers=1,
+                                  pool_type="max", pos_embed="mrope"),
+                       B=8, data="strokes"),
+    # BASELINE.json configs[3]: GDN-SCSSM video, T=32 native 32x32x3 frames, last-frame readout
+    "cfg4": dict(model=dict(_GDN, kernel_size=11, qkv_conv_size=1, stem_mode="pathtracker",
+                            pool_type="max", pos_embed="spatiotemporal"),
+                 B=128, data="dots"),
 }
-METRIC = "fwd images/s (gated spectral block, cfg2)"
+GATED_STAGES = ["in_proj", "short_conv", "gates", "spectral", "out_proj"]
 GDN_STAGES = ["dwconv_ctx", "qkv_proj", "gate_proj", "gates", "short_convs", "spectral", "out_proj"]
 
 
-def time_last_frame(bound, x, steps, warmup, dev, world):
-    """Secondary figure: the same block through the last-frame-only entry point (what a model
-    with a last-frame readout consumes).  Returns ms per step, max over ranks."""
-    import torch
-    from cssm_b200 import shard
-    B, T, H, W, Cc = x.shape
-    out = torch.empty((B, H, W, Cc), dtype=x.dtype, device=dev)
-    for _ in range(max(1, warmup)):
-        bound(x, out=out, last_frame_only=True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize(dev)
-    e0.record()
-    for _ in range(steps):
-        bound(x, out=out, last_frame_only=True)
-    e1.record()
-    torch.cuda.synchronize(dev)
-    return shard.max_over_ranks(e0.elapsed_time(e1), dev) / steps
+def metric_name(workload):
+    return f"fwd images/s (SimpleCSSM {WORKLOADS[workload]['model']['cssm_type']} model, {workload})"
 
 
-def run_gdn(args, cfg, rank, world, local):
-    """GDN block workloads (not the headline metric): whole-block throughput, per-stage CUDA-event
-    times through the library's stage-event hook, roofline of the fused GDN spectral kernel
-    (20*C*H*W algorithmic bytes per (b,t): read q,k,v and gate, write o)."""
-    import ctypes as C
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-    from cssm_b200 import GatedDeltaNetCSSM, shard
+def make_model(workload):
+    from cssm_b200 import SimpleCSSM
+    return SimpleCSSM(**WORKLOADS[workload]["model"])
 
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    B, T, H, W, Cc = cfg["B"], cfg["T"], cfg["H"], cfg["W"], cfg["C"]
-    mod = GatedDeltaNetCSSM(channels=Cc, delta_key_dim=cfg["delta_key_dim"],
-                            kernel_size=cfg["kernel_size"], rope_mode=cfg["rope_mode"],
-                            gate_type=cfg["gate_type"], short_conv_size=cfg["short_conv_size"],
-                            qkv_conv_size=cfg["qkv_conv_size"])
-    bound = mod.bind(mod.init(0, (B, T, H, W, Cc)), dev)
-    g = torch.Generator(device="cpu").manual_seed(100 + rank)
-    x = torch.randn(B, T, H, W, Cc, generator=g).to(dev)
-    y = torch.empty_like(x)
-    st = torch.cuda.current_stream(dev)
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(8)]
-    for _ in range(args.warmup):
-        bound(x, out=y)
-    torch.cuda.synchronize(dev)
-    # stage events: raw cudaEvent_t handles of torch events (created on first record)
-    for e in evs:
-        e.record(st)
-    torch.cuda.synchronize(dev)
-    arr = (C.c_void_p * 8)(*[e.cuda_event for e in evs])
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    stage_ms = {n: 0.0 for n in GDN_STAGES}
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(dev)
-    with ClockSampler(local) as clk:
-        e0.record(st)
-        for k in range(args.steps):
-            if k == args.steps - 1:
-                bound.L.cssm_debug_gdn_stage_events(arr)
-            bound(x, out=y)
-        bound.L.cssm_debug_gdn_stage_events(None)
-        e1.record(st)
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-    for i, n in enumerate(GDN_STAGES):
-        stage_ms[n] = evs[i].elapsed_time(evs[i + 1])
-    total_ms = shard.max_over_ranks(e0.elapsed_time(e1), dev)
-    last_ms = time_last_frame(bound, x, args.steps, args.warmup, dev, world)
-    peak, peak_src = peaks()
-    alg = 20.0 * Cc * H * W * B * T
-    ach = alg / (stage_ms["spectral"] / 1e3) / 1e9
-    if rank == 0:
-        print(json.dumps({
-            "metric": f"fwd images/s (GDN spectral block, {args.workload})",
-            "value": world * B * args.steps / (total_ms / 1e3), "unit": "images/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "block": "GatedDeltaNetCSSM", "per_gpu_batch": B,
-                       "T": T, "H": H, "W": W, "C": Cc, "delta_key_dim": cfg["delta_key_dim"],
-                       "l2": "inputs larger than the 126 MB L2"},
-            "stage_ms": stage_ms,
-            "roofline": {"bound": "hbm", "kernel": "gdn_spectral", "achieved": ach, "peak": peak,
-                         "peak_source": peak_src, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                         "algorithmic_bytes_per_launch": alg, "ms_per_launch": stage_ms["spectral"]},
-            "last_frame_only": {"ms_per_step": last_ms, "value": world * B / (last_ms / 1e3),
-                                "unit": "images/s"},
-            "cpu_baseline": None, "e2e": None, "gpu_launches": 9 * args.steps,
-            "clocks": clk.summary(),
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+
+def make_inputs(workload, n, seed0):
+    """Seeded synthetic inputs: dashed-stroke images (B,128,128,1) or random-walk dot clips
+    (B,32,32,32,3)."""
+    from cssm_b200 import synth
+    if WORKLOADS[workload]["data"] == "strokes":
+        return synth.stroke_batch(n, seed0=seed0)
+    return synth.dot_clips(n, seed0=seed0)
+
+
+def block_kwargs(model):
+    """Keyword arguments of the oracle block functions for a SimpleCSSM mirror."""
+    rope = model.pos_embed if model.pos_embed in ("spatiotemporal", "spatial_only", "temporal", "mrope") else "none"
+    if model.cssm_type == "gated":
+        return dict(kernel_size=model.kernel_size, rope_mode=rope, gate_type=model.gate_type,
+                    short_conv_size=model.short_conv_size,
+                    short_conv_spatial_size=model.short_conv_spatial_size)
+    return dict(delta_key_dim=model.delta_key_dim, kernel_size=model.kernel_size, rope_mode=rope,
+                gate_type=model.gate_type, short_conv_size=model.short_conv_size,
+                qkv_conv_size=model.qkv_conv_size)
 
 
 def peaks():
@@ -224,44 +171,57 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_reference_rate(cfg, sample_b, reps=1):
-    """images/s of the CPU restatement (torch-CPU, all host threads) on `sample_b` images of
-    the workload."""
+def cpu_model_rate(workload, sample_b, reps=1):
+    """images/s of the CPU restatement of the workload's model (torch-CPU, all host threads) on
+    `sample_b` inputs.  Returns (images/s, seconds per repetition, threads)."""
     import numpy as np
     import torch
-    from oracle import cssm_oracle as orc
+    from oracle import simple_oracle as so
     from oracle import cssm_torch_cpu as tc
-    p = orc.init_gated_params(1, cfg["C"], cfg["H"], cfg["W"], kernel_size=cfg["kernel_size"],
-                              gate_type=cfg["gate_type"], short_conv_size=cfg["short_conv_size"],
-                              short_conv_spatial_size=cfg["short_conv_spatial_size"])
-    g = torch.Generator().manual_seed(0)
-    x = torch.randn(sample_b, cfg["T"], cfg["H"], cfg["W"], cfg["C"], generator=g)
-    kw = dict(kernel_size=cfg["kernel_size"], rope_mode=cfg["rope_mode"], gate_type=cfg["gate_type"],
-              short_conv_size=cfg["short_conv_size"],
-              short_conv_spatial_size=cfg["short_conv_spatial_size"])
-    tc.gated_forward_torch(p, x[:1], **kw)           # touch code paths once
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        tc.gated_forward_torch(p, x, **kw)
-    dt = (time.perf_counter() - t0) / reps
+    m = make_model(workload)
+    x = make_inputs(workload, sample_b, seed0=3000)
+    H, W = m.feature_hw(x.shape[-3], x.shape[-2])
+    kw = block_kwargs(m)
+    p = so.init_simple_params(1, cin=x.shape[-1], embed_dim=m.embed_dim, H=H, W=W,
+                              num_classes=m.num_classes, cssm_type=m.cssm_type,
+                              stem_mode=m.stem_mode, stem_layers=m.stem_layers, bias_scale=0.0,
+                              block_kwargs=kw)
+    xt = torch.from_numpy(np.ascontiguousarray(x))
+    run = lambda xx: tc.simple_forward_torch(p, xx, cssm_type=m.cssm_type, seq_len=m.seq_len,
+                                             stem_mode=m.stem_mode, stem_layers=m.stem_layers,
+                                             pool_type=m.pool_type, readout_norm=m.readout_norm,
+                                             block_kwargs=kw)
+    with torch.no_grad():
+        run(xt[:1])                                  # touch code paths once
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            run(xt)
+        dt = (time.perf_counter() - t0) / reps
     return sample_b / dt, dt, torch.get_num_threads()
 
 
-def run_reference(args, cfg, rank):
+def cpu_sample_size(workload):
+    """Inputs per CPU step, sized so that a step takes seconds, not minutes."""
+    return 4 if WORKLOADS[workload]["model"]["cssm_type"] == "gdn" else 16
+
+
+def run_reference(args, rank):
+    """Reference arm: the CPU restatement of the same model on the host cores (rank 0 only)."""
     if rank != 0:
         return
-    sample_b = 16
+    sample_b = min(cpu_sample_size(args.workload), WORKLOADS[args.workload]["B"])
     times = []
+    cores = 0
     for i in range(args.warmup + args.steps):
-        rate, dt, cores = cpu_reference_rate(cfg, sample_b)
+        _, dt, cores = cpu_model_rate(args.workload, sample_b)
         if i >= args.warmup:
             times.append(dt)
     ms = 1e3 * sum(times) / len(times)
     value = sample_b / (ms / 1e3)
-    sample = (f"{sample_b} images of the {args.workload} block input per step "
-              f"(T={cfg['T']}, {cfg['H']}x{cfg['W']}, C={cfg['C']}), torch-CPU restatement")
+    sample = (f"{sample_b} inputs of the {args.workload} model per step, torch-CPU restatement of "
+              f"the reference model (stem on all B*T frames, all T block frames)")
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s",
+        "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": args.workload, "sample_batch": sample_b},
@@ -273,6 +233,86 @@ def run_reference(args, cfg, rank):
     }))
 
 
+def time_region(fn, steps, dev, st):
+    """CUDA-event time of `steps` calls of fn on stream st (ms), max over ranks."""
+    import torch
+    from cssm_b200 import shard
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    e0.record(st)
+    for _ in range(steps):
+        fn()
+    e1.record(st)
+    torch.cuda.synchronize(dev)
+    return shard.max_over_ranks(e0.elapsed_time(e1), dev)
+
+
+def block_stage_times(bound, feat5, steps, dev, st):
+    """Per-stage CUDA-event times (ms, mean over `steps`) of the block alone on its (B,T,H,W,C)
+    input.  Gated block: the five stage entry points with an event pair around each; GDN block:
+    the library's stage-event hook."""
+    import torch
+    from cssm_b200._lib import check
+    blk = bound.block
+    L = blk.L
+    if bound.mod.cssm_type == "gated":
+        d = blk.desc(tuple(feat5.shape))
+        pl = blk.plan(d)
+        lay = blk.workspace_layout(d)
+        ws = blk.buf.get("ws", lay.total)
+        y = torch.empty_like(feat5)
+        wsb, sp = ws.data_ptr(), st.cuda_stream
+        calls = [
+            lambda: L.cssm_gated_in_proj(C.byref(d), C.byref(blk.w), pl.data_ptr(), feat5.data_ptr(),
+                                         wsb + lay.xz_planar, sp),
+            lambda: L.cssm_gated_short_conv(C.byref(d), C.byref(blk.w), wsb + lay.xz_planar,
+                                            wsb + lay.ctx_sum, sp),
+            lambda: L.cssm_gated_gates(C.byref(d), C.byref(blk.w), wsb + lay.ctx_sum,
+                                       wsb + lay.gate_maps, sp),
+            lambda: L.cssm_gated_spectral(C.byref(d), pl.data_ptr(), wsb + lay.gate_maps,
+                                          wsb + lay.xz_planar, sp),
+            lambda: L.cssm_gated_out_proj(C.byref(d), C.byref(blk.w), wsb + lay.xz_planar,
+                                          y.data_ptr(), sp),
+        ]
+        evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                for _ in GATED_STAGES] for _ in range(steps)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for c in calls:
+            check(c(), "stage")                       # warm
+        torch.cuda.synchronize(dev)
+        e0.record(st)
+        for k in range(steps):
+            for i, c in enumerate(calls):
+                evs[k][i][0].record(st)
+                check(c(), GATED_STAGES[i])
+                evs[k][i][1].record(st)
+        e1.record(st)
+        torch.cuda.synchronize(dev)
+        stage = {n: sum(evs[k][i][0].elapsed_time(evs[k][i][1]) for k in range(steps)) / steps
+                 for i, n in enumerate(GATED_STAGES)}
+        return stage, e0.elapsed_time(e1) / steps
+    y = torch.empty_like(feat5)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(8)]
+    blk(feat5, out=y)
+    for e in evs:
+        e.record(st)                                  # creates the raw cudaEvent_t handles
+    torch.cuda.synchronize(dev)
+    arr = (C.c_void_p * 8)(*[e.cuda_event for e in evs])
+    stage = {n: 0.0 for n in GDN_STAGES}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for k in range(steps):
+        L.cssm_debug_gdn_stage_events(arr)
+        blk(feat5, out=y)
+        L.cssm_debug_gdn_stage_events(None)
+        torch.cuda.synchronize(dev)
+        for i, n in enumerate(GDN_STAGES):
+            stage[n] += evs[i].elapsed_time(evs[i + 1]) / steps
+    e1.record(st)
+    torch.cuda.synchronize(dev)
+    return stage, sum(stage.values())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -281,79 +321,44 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--e2e-chunk", type=int, default=8, help="images per host<->device chunk")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
-    cfg = WORKLOADS[args.workload]
+    wl = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, cfg, rank)
+        run_reference(args, rank)
         return
 
     import numpy as np
     import torch
     import torch.distributed as dist
-    from cssm_b200 import GatedCSSM, synth
-    from cssm_b200._lib import check
+    from cssm_b200 import shard
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: cssm_b200 has no CPU path")
-    if cfg.get("block") == "gdn":
-        run_gdn(args, cfg, rank, world, local)
-        return
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-
-    B, T, H, W, Cc = cfg["B"], cfg["T"], cfg["H"], cfg["W"], cfg["C"]
-    mod = GatedCSSM(channels=Cc, kernel_size=cfg["kernel_size"], rope_mode=cfg["rope_mode"],
-                    gate_type=cfg["gate_type"], short_conv_size=cfg["short_conv_size"],
-                    short_conv_spatial_size=cfg["short_conv_spatial_size"])
-    variables = mod.init(0, (B, T, H, W, Cc))
-    bound = mod.bind(variables, dev)
-
-    # synthetic block input: stem features of seeded stroke images (16 distinct images per
-    # rank, tiled to the batch), disjoint seeds per rank
-    stem_layers = {64: 1, 32: 2}[H]          # 128x128 stroke images, one 2x pool per stem layer
-    base = synth.stem_features(synth.stroke_batch(16, seed0=1000 + 16 * rank), T, Cc,
-                               layers=stem_layers)
-    assert base.shape[2:4] == (H, W)
-    x_host = torch.from_numpy(np.tile(base, (B // 16 + 1, 1, 1, 1, 1))[:B]).contiguous()
-    x = x_host.to(dev)
-    y = torch.empty_like(x)
-
-    d = bound.desc(tuple(x.shape))
-    pl = bound.plan(d)
-    lay = bound.workspace_layout(d)
-    ws = torch.empty(lay.total, dtype=torch.uint8, device=dev)
-    L = bound.L
     st = torch.cuda.current_stream(dev)
-    sp = st.cuda_stream
-    wsb = ws.data_ptr()
-    stage_names = ["in_proj", "short_conv", "gates", "spectral", "out_proj"]
 
-    def step(evs=None):
-        calls = [
-            lambda: L.cssm_gated_in_proj(C.byref(d), C.byref(bound.w), pl.data_ptr(), x.data_ptr(),
-                                         wsb + lay.xz_planar, sp),
-            lambda: L.cssm_gated_short_conv(C.byref(d), C.byref(bound.w), wsb + lay.xz_planar,
-                                            wsb + lay.ctx_sum, sp),
-            lambda: L.cssm_gated_gates(C.byref(d), C.byref(bound.w), wsb + lay.ctx_sum,
-                                       wsb + lay.gate_maps, sp),
-            lambda: L.cssm_gated_spectral(C.byref(d), pl.data_ptr(), wsb + lay.gate_maps,
-                                          wsb + lay.xz_planar, sp),
-            lambda: L.cssm_gated_out_proj(C.byref(d), C.byref(bound.w), wsb + lay.xz_planar,
-                                          y.data_ptr(), sp),
-        ]
-        for i, c in enumerate(calls):
-            if evs is not None:
-                evs[i][0].record(st)
-            check(c(), stage_names[i])
-            if evs is not None:
-                evs[i][1].record(st)
+    # model, weights, inputs (disjoint seeds per rank: every rank works on its own shard)
+    B = wl["B"]
+    model = make_model(args.workload)
+    x_np = make_inputs(args.workload, B, seed0=1000 + B * rank)
+    variables = model.init(0, x_np.shape)
+    bound = model.bind(variables, dev)
+    x_host = torch.from_numpy(np.ascontiguousarray(x_np)).pin_memory()
+    x = x_host.to(dev)
+    image_input = x.dim() == 4
+    T = model.seq_len if image_input else x.shape[1]
+    H, W = model.feature_hw(x.shape[-3], x.shape[-2])
+    Cc = model.embed_dim
+    gdn = model.cssm_type == "gdn"
+    n_stem = 1 if model.stem_mode == "pathtracker" else model.stem_layers
+    launches_per_step = n_stem + (9 if gdn else 5) + 2
 
     def barrier():
         if world > 1:
@@ -361,99 +366,90 @@ def main():
         torch.cuda.synchronize(dev)
 
     for _ in range(args.warmup):
-        step()
-    evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-            for _ in stage_names] for _ in range(args.steps)]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        bound(x)
     barrier()
     clk = ClockSampler(local)
     clk.__enter__()                       # sampled over the device-timed and the e2e regions
-    e0.record(st)
-    for k in range(args.steps):
-        step(evs[k])
-    e1.record(st)
+    # ---- headline: images on the device -> logits, all T block frames computed ----
+    total_ms = time_region(lambda: bound(x), args.steps, dev, st)
     barrier()
-    total_ms = e0.elapsed_time(e1)
-    if world > 1:
-        tt = torch.tensor([total_ms], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        total_ms = float(tt.item())
     ms_step = total_ms / args.steps
     value = world * B * args.steps / (total_ms / 1e3)
-    stage_ms = {n: sum(evs[k][i][0].elapsed_time(evs[k][i][1]) for k in range(args.steps)) / args.steps
-                for i, n in enumerate(stage_names)}
+    # ---- the same with the block's last-frame-only entry point ----
+    bound(x, last_frame_only=True)
+    last_ms = time_region(lambda: bound(x, last_frame_only=True), args.steps, dev, st) / args.steps
+    # ---- the block alone, stage by stage, on the stem features ----
+    feat = bound.stem(x)
+    feat5 = feat[:, None].expand(-1, T, -1, -1, -1).contiguous() if image_input else feat
+    stem_ms = time_region(lambda: bound.stem(x), args.steps, dev, st) / args.steps
+    stage_ms, block_ms = block_stage_times(bound, feat5, args.steps, dev, st)
+    del feat5
 
-    # roofline of the fused spectral kernel: 12*H*W bytes per (b,t,c) plane-step
+    # roofline of the fused spectral kernel
     peak, peak_src = peaks()
-    alg_bytes = 12.0 * H * W * B * T * Cc
+    per_unit = 20.0 * Cc * H * W if gdn else 12.0 * H * W * Cc      # bytes per (b,t)
+    alg_bytes = per_unit * B * T
     achieved = alg_bytes / (stage_ms["spectral"] / 1e3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gated_spectral_r64" if H == 64 else "gated_spectral_r32", "achieved": achieved, "peak": peak,
+    kname = ("gdn_spectral_" if gdn else "gated_spectral_") + {64: "r64", 32: "r32"}.get(H, "generic")
+    roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8TBps": achieved / 8000.0, "traffic": None,
                 "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": stage_ms["spectral"]}
     tr = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tr):
+    if os.path.exists(tr) and kname == "gated_spectral_r64":
         with open(tr) as f:
             per_plane_step = json.load(f).get("gated_spectral_r64_dram_bytes_per_plane_step")
         if per_plane_step:
             roofline["traffic"] = per_plane_step * B * T * Cc
 
-    last_ms = time_last_frame(bound, x, args.steps, args.warmup, dev, world)
-
-    # end to end through the host-buffer entry point (pinned host memory)
+    # ---- end to end: pinned host images -> host logits through the host-buffer entry point ----
     e2e = None
     if not args.no_e2e:
-        chunk = min(args.e2e_chunk, B)
-        xh = x_host.pin_memory()
-        yh = torch.empty_like(xh).pin_memory()
-        n = L.cssm_gated_host_workspace_bytes(C.byref(d), chunk)
-        hws = torch.empty(n, dtype=torch.uint8, device=dev)
+        lh = torch.empty((B, model.num_classes), dtype=torch.float32).pin_memory()
 
-        def host_step():
-            check(L.cssm_gated_forward_host(C.byref(d), C.byref(bound.w), pl.data_ptr(),
-                                            xh.data_ptr(), yh.data_ptr(), chunk, hws.data_ptr(), n, sp),
-                  "forward_host")
-        for _ in range(max(1, min(args.warmup, 3))):
-            host_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            host_step()
-        torch.cuda.synchronize(dev)
-        dt = time.perf_counter() - t0
-        if world > 1:
-            tt = torch.tensor([dt], device=dev)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            dt = float(tt.item())
-        nbytes = x.numel() * 4
+        def host_rate(last):
+            for _ in range(max(1, min(args.warmup, 3))):
+                bound.forward_host(x_host, lh, last_frame_only=last)
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                bound.forward_host(x_host, lh, last_frame_only=last)   # returns after the logits arrived
+            return shard.max_over_ranks(time.perf_counter() - t0, dev)
+        dt = host_rate(False)
+        dt_last = host_rate(True)
         e2e = {"value": world * B * args.steps / dt, "unit": "images/s",
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-               "ms_per_step": 1e3 * dt / args.steps, "chunk_batch": chunk}
-        del hws, xh, yh
+               "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": lh.numel() * 4,
+               "ms_per_step": 1e3 * dt / args.steps,
+               "last_frame_only_value": world * B * args.steps / dt_last}
     clk.__exit__(None, None, None)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        rate, dt, cores = cpu_reference_rate(cfg, 16, reps=16)
+        sb = min(cpu_sample_size(args.workload), B)
+        reps = 4 if gdn else 8
+        rate, dt, cores = cpu_model_rate(args.workload, sb, reps=reps)
         cpu = {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
-               "sample": f"16 images of the {args.workload} block input, 16 repetitions "
-                         f"({dt:.2f} s each), torch-CPU restatement of the reference block"}
+               "sample": f"{sb} inputs of the {args.workload} model, {reps} repetitions ({dt:.2f} s "
+                         f"each), torch-CPU restatement of the reference model"}
 
     if rank == 0:
         print(json.dumps({
-            "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
+            "metric": metric_name(args.workload), "value": value, "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": args.workload, "block": "GatedCSSM", "per_gpu_batch": B, "T": T,
-                       "H": H, "W": W, "C": Cc, "kernel_size": cfg["kernel_size"],
-                       "gate_type": cfg["gate_type"], "rope_mode": cfg["rope_mode"],
-                       "l2": "inputs (1.07 GB per tensor at cfg2) larger than the 126 MB L2"},
+            "config": {"workload": args.workload, "model": "SimpleCSSM depth 1", "block": model.cssm_type,
+                       "per_gpu_batch": B, "input": list(x.shape[1:]), "T": T, "H": H, "W": W, "C": Cc,
+                       "kernel_size": model.kernel_size, "gate_type": model.gate_type,
+                       "pos_embed": model.pos_embed, "stem": model.stem_mode, "pool": model.pool_type,
+                       "l2": "block activations (1.07 GB per tensor at cfg2-4) larger than the 126 MB L2"},
+            "block": {"ms_per_step": block_ms, "stage_ms": stage_ms, "stem_ms": stem_ms,
+                      "value": world * B / (block_ms / 1e3), "unit": "images/s"},
             "stage_ms": stage_ms, "roofline": roofline,
             "last_frame_only": {"ms_per_step": last_ms, "value": world * B / (last_ms / 1e3),
                                 "unit": "images/s"},
             "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": 5 * args.steps, "clocks": clk.summary(),
+            "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary(),
         }))
     if world > 1:
         dist.destroy_process_group()

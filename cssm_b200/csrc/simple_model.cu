@@ -10,7 +10,7 @@
 namespace cssm {
 
 constexpr int SM_MAXC = 64;          // embed_dim limit (channel vectors live in registers)
-constexpr int STEM_THREADS = 128;
+constexpr int STEM_THREADS = 256;
 
 __device__ __forceinline__ float softplus_f(float a) {
   return fmaxf(a, 0.f) + __logf(1.0f + __expf(-fabsf(a)));
@@ -39,14 +39,21 @@ struct StemArgs {
   int w_in_smem;                        // conv kernel staged in shared memory
 };
 
-// One thread per output pixel: the C channel values of each of its POOL x POOL pre-pool pixels
-// are built in registers (conv taps as broadcast float4 weight reads), normalised, and the
-// running maximum is kept.
-template <int KS, int POOL>
+// Four lanes share one pre-pool pixel: lane g of the quad owns the float4 channel groups
+// j = g + 4k (k = 0..3, j < C/4), i.e. channels 4j..4j+3.  LayerNorm sums cross the quad by two
+// shuffles.  With pooling the four pixels of a 2x2 window sit in the same warp (lane bits 2-3),
+// the maximum crosses them by two more shuffles per value, and window pixel k stores group
+// g + 4k, so every lane issues one 16-byte store and a quad writes 64 contiguous bytes.
+//   POOL = 2: lane = g | dq << 2 | window << 4   (2 windows per warp, 16 per CTA)
+//   POOL = 1: lane = g | pixel << 2              (8 pixels per warp, 64 per CTA)
+// CIN > 0: compile-time input channel count (the tap loops unroll fully, so all input loads of
+// a pixel are in flight together); CIN = 0: run-time a.Cin.
+template <int KS, int POOL, int CIN>
 __global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs a) {
   extern __shared__ __align__(16) float sm[];
-  const int C = a.C, tid = threadIdx.x;
-  const int nw = KS * KS * a.Cin * C;
+  const int C = a.C, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int Cin = CIN > 0 ? CIN : a.Cin;
+  const int nw = KS * KS * Cin * C;
   float* wsm = sm;                                   // [tap][ci][C] when w_in_smem
   float* vec = sm + (a.w_in_smem ? nw : 0);          // bias, scale, lnbias
   if (a.w_in_smem)
@@ -56,68 +63,138 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs
   }
   __syncthreads();
   const float* wsrc = a.w_in_smem ? wsm : a.wk;
+  const int g = lane & 3, ngrp = C >> 2;
   const long long total = (long long)a.N * a.Ho * a.Wo;
-  const long long o = (long long)blockIdx.x * STEM_THREADS + tid;
-  if (o >= total) return;
-  const int wo = (int)(o % a.Wo), ho = (int)((o / a.Wo) % a.Ho), n = (int)(o / ((long long)a.Wo * a.Ho));
+  constexpr int WARPS = STEM_THREADS / 32;
+  const int dq = POOL == 2 ? (lane >> 2) & 3 : 0;
+  constexpr int PER_WARP = POOL == 2 ? 2 : 8;        // output pixels per warp and iteration
+  // grid-stride over groups of PER_WARP output pixels; the trip count is the same for all lanes
+  for (long long grp = (long long)blockIdx.x * WARPS + warp; grp * PER_WARP < total;
+       grp += (long long)gridDim.x * WARPS) {
+  const long long o = grp * PER_WARP + (POOL == 2 ? (lane >> 4) : (lane >> 2));
+  const bool valid = o < total;
+  const long long oc = valid ? o : 0;
+  const int wo = (int)(oc % a.Wo), ho = (int)((oc / a.Wo) % a.Ho), n = (int)(oc / ((long long)a.Wo * a.Ho));
+  const int h = ho * POOL + (dq >> 1), w = wo * POOL + (dq & 1);
+  const bool inb = valid && h < a.Hin && w < a.Win;   // false: 'SAME' pool padding on odd sizes
   constexpr int LO = (KS - 1) / 2;
-  float mx[SM_MAXC];
+  float acc[4][4];
 #pragma unroll
-  for (int c = 0; c < SM_MAXC; ++c) mx[c] = -INFINITY;
-#pragma unroll 1
-  for (int dq = 0; dq < POOL * POOL; ++dq) {
-    const int h = ho * POOL + dq / POOL, w = wo * POOL + dq % POOL;
-    if (h >= a.Hin || w >= a.Win) continue;          // 'SAME' pool padding (-inf) on odd sizes
-    float acc[SM_MAXC];
+  for (int k = 0; k < 4; ++k) {
+    const int j = g + 4 * k;
 #pragma unroll
-    for (int c = 0; c < SM_MAXC; ++c) acc[c] = c < C ? vec[c] : 0.f;
+    for (int e = 0; e < 4; ++e) acc[k][e] = j < ngrp ? vec[4 * j + e] : 0.f;
+  }
+  auto tap_ci = [&](const float4* w4, int ci, float xv) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = g + 4 * k;
+      if (j < ngrp) {
+        const float4 wv = w4[ci * ngrp + j];
+        acc[k][0] = fmaf(xv, wv.x, acc[k][0]);
+        acc[k][1] = fmaf(xv, wv.y, acc[k][1]);
+        acc[k][2] = fmaf(xv, wv.z, acc[k][2]);
+        acc[k][3] = fmaf(xv, wv.w, acc[k][3]);
+      }
+    }
+  };
+  if (CIN > 0) {
+    // all taps' inputs first (zero outside the frame: a zero input adds nothing), then the FMAs
+    float xin[KS * KS * (CIN > 0 ? CIN : 1)];
+#pragma unroll
+    for (int tap = 0; tap < KS * KS; ++tap) {
+      const int hh = h + tap / KS - LO, ww = w + tap % KS - LO;
+      const bool ok = inb && hh >= 0 && hh < a.Hin && ww >= 0 && ww < a.Win;
+      const float* xp = a.x + (((size_t)n * a.Hin + (ok ? hh : 0)) * a.Win + (ok ? ww : 0)) * Cin;
+#pragma unroll
+      for (int ci = 0; ci < (CIN > 0 ? CIN : 1); ++ci) xin[tap * (CIN > 0 ? CIN : 1) + ci] = ok ? __ldg(xp + ci) : 0.f;
+    }
+#pragma unroll
+    for (int tap = 0; tap < KS * KS; ++tap) {
+      const float4* w4 = reinterpret_cast<const float4*>(wsrc + (size_t)tap * Cin * C);
+#pragma unroll
+      for (int ci = 0; ci < (CIN > 0 ? CIN : 1); ++ci) tap_ci(w4, ci, xin[tap * (CIN > 0 ? CIN : 1) + ci]);
+    }
+  } else if (inb) {
 #pragma unroll 1
     for (int tap = 0; tap < KS * KS; ++tap) {
       const int hh = h + tap / KS - LO, ww = w + tap % KS - LO;
       if (hh < 0 || hh >= a.Hin || ww < 0 || ww >= a.Win) continue;
-      const float* xp = a.x + (((size_t)n * a.Hin + hh) * a.Win + ww) * a.Cin;
-      const float* wp = wsrc + (size_t)tap * a.Cin * C;
-#pragma unroll 1
-      for (int ci = 0; ci < a.Cin; ++ci) {
-        const float xv = __ldg(xp + ci);
-        const float4* w4 = reinterpret_cast<const float4*>(wp + (size_t)ci * C);
-#pragma unroll
-        for (int c4 = 0; c4 < SM_MAXC / 4; ++c4) {
-          if (4 * c4 < C) {
-            const float4 wv = w4[c4];
-            acc[4 * c4 + 0] = fmaf(xv, wv.x, acc[4 * c4 + 0]);
-            acc[4 * c4 + 1] = fmaf(xv, wv.y, acc[4 * c4 + 1]);
-            acc[4 * c4 + 2] = fmaf(xv, wv.z, acc[4 * c4 + 2]);
-            acc[4 * c4 + 3] = fmaf(xv, wv.w, acc[4 * c4 + 3]);
-          }
+      const float* xp = a.x + (((size_t)n * a.Hin + hh) * a.Win + ww) * Cin;
+      const float4* w4 = reinterpret_cast<const float4*>(wsrc + (size_t)tap * Cin * C);
+      // float4 input reads when the channel count allows (it does for embed_dim inputs)
+      if ((Cin & 3) == 0) {
+#pragma unroll 2
+        for (int c4 = 0; c4 < Cin; c4 += 4) {
+          const float4 xv = __ldg(reinterpret_cast<const float4*>(xp + c4));
+          tap_ci(w4, c4, xv.x); tap_ci(w4, c4 + 1, xv.y); tap_ci(w4, c4 + 2, xv.z); tap_ci(w4, c4 + 3, xv.w);
         }
+      } else {
+        for (int ci = 0; ci < Cin; ++ci) tap_ci(w4, ci, __ldg(xp + ci));
       }
     }
-#pragma unroll
-    for (int c = 0; c < SM_MAXC; ++c)
-      if (c < C) acc[c] = softplus_f(acc[c]);
-    layer_norm_regs(acc, C, vec + C, vec + 2 * C);
-#pragma unroll
-    for (int c = 0; c < SM_MAXC; ++c) mx[c] = fmaxf(mx[c], acc[c]);
   }
-  float4* op = reinterpret_cast<float4*>(a.out + (size_t)o * C);
+  // softplus, then LayerNorm over the C channels of the pixel (the quad's 4 x 16 values)
+  float s = 0.f, ss = 0.f;
 #pragma unroll
-  for (int c4 = 0; c4 < SM_MAXC / 4; ++c4)
-    if (4 * c4 < C) op[c4] = make_float4(mx[4 * c4], mx[4 * c4 + 1], mx[4 * c4 + 2], mx[4 * c4 + 3]);
+  for (int k = 0; k < 4; ++k)
+    if (g + 4 * k < ngrp) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float v = softplus_f(acc[k][e]);
+        acc[k][e] = v; s += v; ss = fmaf(v, v, ss);
+      }
+    }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  const float mean = s / (float)C;
+  const float rinv = rsqrtf(fmaxf(ss / (float)C - mean * mean, 0.f) + 1e-6f);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int j = g + 4 * k;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float v = -INFINITY;
+      if (inb && j < ngrp) v = (acc[k][e] - mean) * rinv * vec[C + 4 * j + e] + vec[2 * C + 4 * j + e];
+      if (POOL == 2) {
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+      }
+      acc[k][e] = v;
+    }
+  }
+  float4* op = reinterpret_cast<float4*>(a.out + (size_t)oc * C);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int j = g + 4 * k;
+    if (valid && j < ngrp && (POOL == 1 || k == dq))
+      op[j] = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+  }
+  }
 }
 
-template <int KS, int POOL>
-static int launch_stem_layer(StemArgs a, cudaStream_t st) {
+template <int KS, int POOL, int CIN>
+static int launch_stem_layer_cin(StemArgs a, cudaStream_t st) {
   const size_t wbytes = (size_t)KS * KS * a.Cin * a.C * sizeof(float);
   a.w_in_smem = wbytes <= 160 * 1024 ? 1 : 0;
   const size_t smem = (a.w_in_smem ? wbytes : 0) + 3 * (size_t)a.C * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(stem_layer_kernel<KS, POOL>,
+  cudaError_t e = cudaFuncSetAttribute(stem_layer_kernel<KS, POOL, CIN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const long long total = (long long)a.N * a.Ho * a.Wo;
-  const unsigned grid = (unsigned)((total + STEM_THREADS - 1) / STEM_THREADS);
-  stem_layer_kernel<KS, POOL><<<grid, STEM_THREADS, smem, st>>>(a);
+  const long long per_cta = (STEM_THREADS / 32) * (POOL == 2 ? 2 : 8);
+  const long long need = (total + per_cta - 1) / per_cta;
+  // a few resident waves of CTAs that loop, so that the per-CTA weight staging is amortised
+  const unsigned grid = (unsigned)(need < 148 * 16 ? need : 148 * 16);
+  stem_layer_kernel<KS, POOL, CIN><<<grid, STEM_THREADS, smem, st>>>(a);
   return check_launch();
+}
+
+template <int KS, int POOL>
+static int launch_stem_layer(const StemArgs& a, cudaStream_t st) {
+  if (a.Cin == 1) return launch_stem_layer_cin<KS, POOL, 1>(a, st);
+  if (a.Cin == 3) return launch_stem_layer_cin<KS, POOL, 3>(a, st);
+  return launch_stem_layer_cin<KS, POOL, 0>(a, st);
 }
 
 // ------------------------------------------------------------------------- readout ----
@@ -133,54 +210,76 @@ struct ReadoutArgs {
   int B, H, W, C, pool_max, norm_post_order, ncls, bands;
 };
 
-// grid (bands, B): LayerNorm/softplus of (y + res) per pixel, pooled over the band's pixels
+// grid (bands, B): LayerNorm/softplus of (y + res) per pixel, pooled over the band's pixels.
+// Four lanes per pixel as in the stem (lane g owns float4 groups g + 4k); 8 pixels per warp.
 __global__ void __launch_bounds__(RO_THREADS) readout_pool_kernel(const ReadoutArgs a) {
   __shared__ float red[RO_THREADS / 32][SM_MAXC];
   __shared__ float vec[2 * SM_MAXC];
-  const int C = a.C, tid = threadIdx.x, band = blockIdx.x, b = blockIdx.y;
+  const int C = a.C, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int band = blockIdx.x, b = blockIdx.y;
   for (int i = tid; i < C; i += RO_THREADS) { vec[i] = a.pre_scale[i]; vec[SM_MAXC + i] = a.pre_bias[i]; }
   __syncthreads();
+  const int g = lane & 3, ps = lane >> 2, ngrp = C >> 2;
   const int h0 = band * RO_ROWS, rows = min(RO_ROWS, a.H - h0);
   const int npx = rows * a.W;
-  float pool[SM_MAXC];
+  const float init = a.pool_max ? -INFINITY : 0.f;
+  float pool[4][4];
 #pragma unroll
-  for (int c = 0; c < SM_MAXC; ++c) pool[c] = a.pool_max ? -INFINITY : 0.f;
-  for (int p = tid; p < npx; p += RO_THREADS) {
-    const size_t px = (size_t)h0 * a.W + p;
+  for (int k = 0; k < 4; ++k)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) pool[k][e] = init;
+  for (int p0 = warp * 8; p0 < npx; p0 += (RO_THREADS / 32) * 8) {      // uniform per warp
+    const int p = p0 + ps;
+    const bool on = p < npx;
+    const size_t px = (size_t)h0 * a.W + (on ? p : 0);
     const float4* yp = reinterpret_cast<const float4*>(a.y + (size_t)b * a.y_stride + px * C);
     const float4* rp = reinterpret_cast<const float4*>(a.res + (size_t)b * a.res_stride + px * C);
-    float v[SM_MAXC];
+    float v[4][4];
+    float s = 0.f, ss = 0.f;
 #pragma unroll
-    for (int c4 = 0; c4 < SM_MAXC / 4; ++c4) {
-      if (4 * c4 < C) {
-        const float4 yv = __ldg(yp + c4), rv = __ldg(rp + c4);
-        v[4 * c4] = yv.x + rv.x; v[4 * c4 + 1] = yv.y + rv.y;
-        v[4 * c4 + 2] = yv.z + rv.z; v[4 * c4 + 3] = yv.w + rv.w;
-      } else {
-        v[4 * c4] = v[4 * c4 + 1] = v[4 * c4 + 2] = v[4 * c4 + 3] = 0.f;
+    for (int k = 0; k < 4; ++k) {
+      const int j = g + 4 * k;
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < ngrp) {
+        const float4 yv = __ldg(yp + j), rv = __ldg(rp + j);
+        t = make_float4(yv.x + rv.x, yv.y + rv.y, yv.z + rv.z, yv.w + rv.w);
+        if (a.norm_post_order) t = make_float4(softplus_f(t.x), softplus_f(t.y), softplus_f(t.z), softplus_f(t.w));
+        s += t.x + t.y + t.z + t.w;
+        ss = fmaf(t.x, t.x, fmaf(t.y, t.y, fmaf(t.z, t.z, fmaf(t.w, t.w, ss))));
+      }
+      v[k][0] = t.x; v[k][1] = t.y; v[k][2] = t.z; v[k][3] = t.w;
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    const float mean = s / (float)C;
+    const float rinv = rsqrtf(fmaxf(ss / (float)C - mean * mean, 0.f) + 1e-6f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = g + 4 * k;
+      if (on && j < ngrp) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float x = (v[k][e] - mean) * rinv * vec[4 * j + e] + vec[SM_MAXC + 4 * j + e];
+          if (!a.norm_post_order) x = softplus_f(x);
+          pool[k][e] = a.pool_max ? fmaxf(pool[k][e], x) : pool[k][e] + x;
+        }
       }
     }
-    if (a.norm_post_order) {
-#pragma unroll
-      for (int c = 0; c < SM_MAXC; ++c) if (c < C) v[c] = softplus_f(v[c]);
-      layer_norm_regs(v, C, vec, vec + SM_MAXC);
-    } else {
-      layer_norm_regs(v, C, vec, vec + SM_MAXC);
-#pragma unroll
-      for (int c = 0; c < SM_MAXC; ++c) if (c < C) v[c] = softplus_f(v[c]);
-    }
-#pragma unroll
-    for (int c = 0; c < SM_MAXC; ++c) pool[c] = a.pool_max ? fmaxf(pool[c], v[c]) : pool[c] + v[c];
   }
+  // over the warp's 8 pixel slots, then over the warps
 #pragma unroll
-  for (int c = 0; c < SM_MAXC; ++c) {
-    float r = pool[c];
-    for (int off = 16; off > 0; off >>= 1) {
-      const float o = __shfl_down_sync(0xffffffffu, r, off);
-      r = a.pool_max ? fmaxf(r, o) : r + o;
+  for (int k = 0; k < 4; ++k)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float r = pool[k][e];
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, r, off);
+        r = a.pool_max ? fmaxf(r, o) : r + o;
+      }
+      const int j = g + 4 * k;
+      if (ps == 0 && j < ngrp) red[warp][4 * j + e] = r;
     }
-    if ((tid & 31) == 0) red[tid >> 5][c] = r;
-  }
   __syncthreads();
   if (tid < C) {
     float r = red[0][tid];

@@ -28,7 +28,24 @@ def test_workloads_match_baseline_configs():
     sys.path.insert(0, ROOT)
     import bench
     w = bench.WORKLOADS
-    assert w["cfg2"]["B"] == 128 and w["cfg2"]["T"] == 8 and w["cfg2"]["kernel_size"] == 11
-    assert w["cfg2"]["gate_type"] == "factored" and w["cfg2"]["C"] == 64
-    assert w["cfg3"]["block"] == "gdn" and w["cfg3"]["delta_key_dim"] == 4 and w["cfg3"]["qkv_conv_size"] == 5
-    assert w["cfg4"]["T"] == 32 and w["cfg4"]["H"] == 32
+    m2 = w["cfg2"]["model"]
+    assert w["cfg2"]["B"] == 128 and m2["seq_len"] == 8 and m2["kernel_size"] == 11
+    assert m2["gate_type"] == "factored" and m2["embed_dim"] == 64 and m2["stem_layers"] == 1
+    assert m2["cssm_type"] == "gated" and m2["pool_type"] == "max" and m2["num_classes"] == 2
+    m3 = w["cfg3"]["model"]
+    assert m3["cssm_type"] == "gdn" and m3["delta_key_dim"] == 4 and m3["qkv_conv_size"] == 5
+    assert m3["pos_embed"] == "mrope" and m3["output_norm"] == "rms"
+    m4 = w["cfg4"]["model"]
+    assert m4["cssm_type"] == "gdn" and m4["stem_mode"] == "pathtracker" and w["cfg4"]["data"] == "dots"
+    x = bench.make_inputs("cfg4", 2, seed0=1)
+    assert x.shape == (2, 32, 32, 32, 3)
+    assert bench.make_inputs("cfg2", 1, seed0=1).shape == (1, 128, 128, 1)
+
+
+def test_gdn_reference_arm_runs():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
+                          "--workload", "cfg4", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    d = json.loads(out.stdout.strip().splitlines()[-1])
+    assert d["impl"] == "reference" and d["value"] > 0 and d["config"]["workload"] == "cfg4"
