@@ -62,6 +62,15 @@ class GdnWeights(C.Structure):
 
 # name -> (restype, argtypes); every symbol include/cssm_b200.h declares
 _P = C.c_void_p
+class NoGateDesc(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("W", C.c_int32),
+                ("C", C.c_int32), ("kernel_size", C.c_int32), ("spectral_rho", C.c_float)]
+
+
+class NoGateWeights(C.Structure):
+    _fields_ = [("kernel", C.c_void_p), ("out_proj_kernel", C.c_void_p), ("out_proj_bias", C.c_void_p)]
+
+
 class SimpleDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("B", "T", "Hin", "Win", "Cin", "image_input", "stem_mode", "stem_layers",
@@ -106,6 +115,11 @@ SIGNATURES = {
                                    C.c_size_t, _P]),
     "cssm_gdn_forward_last": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
                                         C.c_size_t, _P]),
+    "cssm_nogate_plan_bytes": (C.c_size_t, [C.POINTER(NoGateDesc)]),
+    "cssm_nogate_workspace_bytes": (C.c_size_t, [C.POINTER(NoGateDesc)]),
+    "cssm_nogate_plan_init": (C.c_int, [C.POINTER(NoGateDesc), C.POINTER(NoGateWeights), _P, C.c_size_t, _P]),
+    "cssm_nogate_forward": (C.c_int, [C.POINTER(NoGateDesc), C.POINTER(NoGateWeights), _P, _P, _P, _P,
+                                      C.c_size_t, _P]),
     "cssm_simple_workspace_bytes": (C.c_size_t, [C.POINTER(SimpleDesc), _P]),
     "cssm_simple_stem": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P, _P,
                                    C.c_size_t, _P]),

@@ -25,14 +25,15 @@ constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64
 __device__ int g_spec_error = 0;
 int g_spec_variant = 0;      // 0 padded rows via tensor TMA, 1 dense rows via bulk TMA, 2 warp-specialised pipeline
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
-                              int last_only, cudaStream_t st);
+                              int last_only, int nogate, cudaStream_t st);
 int launch_gated_spectral_ws(float* xz, const cf* khat, const float* gates, int B, int T, int C,
                              cudaStream_t st);
 
 // PRS: floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane).
 // LAST: only the last step's output plane is produced (compile-time, so that the all-frames
 // kernel carries none of the branches).
-template <int PRS, bool LAST>
+// NOG: the ungated recurrence S_t = K_hat S_{t-1} + X_hat_t of NoGateCSSM (no gate maps, no z plane).
+template <int PRS, bool LAST, bool NOG>
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C,
@@ -64,7 +65,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
   // stage step `tl`: x_main plane into xbuf (if want_x) and z plane into zbuf[tl & 1]
   auto stage = [&](int tl, bool want_x) {
     if (c.warp != 8) return;
-    const bool want_z = !last_only || tl == T - 1;
+    const bool want_z = !NOG && (!last_only || tl == T - 1);
     tc::fence_proxy_async();             // earlier generic reads of the buffers come first
     uint64_t* bz = &bars[1 + (tl & 1)];
     if (c.lane == 0) {
@@ -124,20 +125,27 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         // {exp(-D), (D+1e-8)B, C/(HW), 1e-7(D+1e-8)}
-        g[q] = c.col_on ? __ldg(gp + q * (33 * 8)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!NOG) g[q] = c.col_on ? __ldg(gp + q * (33 * 8)) : make_float4(0.f, 0.f, 0.f, 0.f);
         kh[q] = c.col_on ? khp[q * (33 * 8)] : mk(0.f, 0.f);
       }
       cf v[8];
       r64_col_fwd(c, v);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        const cf A = mk(kh[q].x * g[q].x, kh[q].y * g[q].x);
-        cf U = mk(g[q].y * v[q].x, g[q].y * v[q].y);
-        if (U.x * U.x + U.y * U.y < g[q].w * g[q].w) U = mk(g[q].w, 0.f);
-        cf h = cmul(A, hst[q]);
-        h.x += U.x; h.y += U.y;
-        hst[q] = h;
-        v[q] = mk(g[q].z * h.x, g[q].z * h.y);
+        if (NOG) {
+          cf h = cmul(kh[q], hst[q]);
+          h.x += v[q].x; h.y += v[q].y;
+          hst[q] = h;
+          v[q] = mk(h.x * (1.0f / HW), h.y * (1.0f / HW));
+        } else {
+          const cf A = mk(kh[q].x * g[q].x, kh[q].y * g[q].x);
+          cf U = mk(g[q].y * v[q].x, g[q].y * v[q].y);
+          if (U.x * U.x + U.y * U.y < g[q].w * g[q].w) U = mk(g[q].w, 0.f);
+          cf h = cmul(A, hst[q]);
+          h.x += U.x; h.y += U.y;
+          hst[q] = h;
+          v[q] = mk(g[q].z * h.x, g[q].z * h.y);
+        }
       }
       if (emit) r64_col_inv(c, v);
     }
@@ -147,14 +155,16 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     if (c.row_on && emit) {
       cf v[8];
       r64_row_inv(c, v);
-      // in last-only mode the z barrier of this slot completes exactly once (phase 0)
-      if (!tc::mbar_wait(&bars[1 + (t & 1)], last_only ? 0 : (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
-      const float* zs = zbuf + (t & 1) * R64_PLANE_F + soff;
       float* y0 = xp + roff;
-      // finish all products before the first store: the stores go through a generic pointer,
-      // so shared-memory loads placed between them could not be hoisted
+      if (!NOG) {
+        // in last-only mode the z barrier of this slot completes exactly once (phase 0)
+        if (!tc::mbar_wait(&bars[1 + (t & 1)], last_only ? 0 : (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
+        const float* zs = zbuf + (t & 1) * R64_PLANE_F + soff;
+        // finish all products before the first store: the stores go through a generic pointer,
+        // so shared-memory loads placed between them could not be hoisted
 #pragma unroll
-      for (int n1 = 0; n1 < 8; ++n1) v[n1] = mk(v[n1].x * zs[8 * n1], v[n1].y * zs[R64_PRS + 8 * n1]);
+        for (int n1 = 0; n1 < 8; ++n1) v[n1] = mk(v[n1].x * zs[8 * n1], v[n1].y * zs[R64_PRS + 8 * n1]);
+      }
 #pragma unroll
       for (int n1 = 0; n1 < 8; ++n1) {
         y0[8 * n1] = v[n1].x;
@@ -181,7 +191,8 @@ constexpr int GEN_THREADS = 256;
 
 __global__ void __launch_bounds__(GEN_THREADS)
 gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
-                       const float4* __restrict__ gates, int T, int C, int H, int W, int last_only) {
+                       const float4* __restrict__ gates, int T, int C, int H, int W, int last_only,
+                       int nog) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Wf = W / 2 + 1, HW = H * W, NB = H * Wf;
   float* xs = reinterpret_cast<float*>(smem_raw);              // [H][W]
@@ -235,7 +246,8 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
         ax += r.x * e.x - r.y * e.y; ay += r.x * e.y + r.y * e.x;
         idx += kh; if (idx >= H) idx -= H;
       }
-      const float4 g = gp[o];
+      // ungated mode: A = K_hat, U = X_hat, output scale 1/(H*W), no floor
+      const float4 g = nog ? make_float4(1.f, 1.f, 1.0f / (float)HW, 0.f) : gp[o];
       const cf k = khc[o];
       cf A = mk(k.x * g.x, k.y * g.x);
       cf U = mk(g.y * ax, g.y * ay);
@@ -276,7 +288,7 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
         s2 += r[k].x * e.x + r[k].y * e.y;
       }
       acc += 2.f * s2;
-      xp[o] = acc * zp[o];
+      xp[o] = nog ? acc : acc * zp[o];
     }
   }
 }
@@ -289,10 +301,16 @@ size_t generic_smem_bytes(int H, int W) {
 
 int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float* gates,
                           float* xz, int last_only, cudaStream_t st) {
+  return launch_spectral(d.B, d.T, d.H, d.W, d.C, khat, gates, xz, last_only, 0, st);
+}
+
+int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const float* gates,
+                    float* xz, int last_only, int nogate, cudaStream_t st) {
+  struct { int B, T, H, W, C; } d = {B, T, H, W, C};
   const SpectralPath path = spectral_path(d.H, d.W);
   const int grid = d.B * d.C;
-  if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, last_only, st);
-  if (path == PATH_R64 && g_spec_variant == 2 && !last_only)
+  if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, last_only, nogate, st);
+  if (path == PATH_R64 && g_spec_variant == 2 && !last_only && !nogate)
     return launch_gated_spectral_ws(xz, khat, gates, d.B, d.T, d.C, st);
   if (path == PATH_R64) {
     const size_t smem = R64_SMEM_BYTES;
@@ -321,8 +339,12 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     }
-    auto kern = padded ? (last_only ? gated_spectral_r64<68, true> : gated_spectral_r64<68, false>)
-                       : (last_only ? gated_spectral_r64<64, true> : gated_spectral_r64<64, false>);
+    auto kern = padded ? (last_only ? gated_spectral_r64<68, true, false> : gated_spectral_r64<68, false, false>)
+                       : (last_only ? gated_spectral_r64<64, true, false> : gated_spectral_r64<64, false, false>);
+    if (nogate) {
+      if (!padded) return CSSM_ERR_CUDA;          // the ungated variant exists for the padded staging only
+      kern = last_only ? gated_spectral_r64<68, true, true> : gated_spectral_r64<68, false, true>;
+    }
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
@@ -335,7 +357,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     gated_spectral_generic<<<grid, GEN_THREADS, smem, st>>>(
-        xz, khat, reinterpret_cast<const float4*>(gates), d.T, d.C, d.H, d.W, last_only);
+        xz, khat, reinterpret_cast<const float4*>(gates), d.T, d.C, d.H, d.W, last_only, nogate);
   }
   return check_launch();
 }

@@ -18,7 +18,8 @@ constexpr int R32_GB_CF = 4 * 32 * R32_GBS;
 constexpr int R32_SMEM_BYTES = (R32_EX_CF + R32_ZR_CF + R32_GB_CF) * 8;
 
 // LAST: only the last step's output planes are produced (compile-time switch).
-template <bool LAST>
+// NOG: ungated recurrence S_t = K_hat S_{t-1} + X_hat_t (no gate maps, no z planes).
+template <bool LAST, bool NOG>
 __global__ void __launch_bounds__(R32_THREADS, 2)
 gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C) {
@@ -83,7 +84,7 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
       const float4* gp = gates + frame * NB + (kw << 2) + q;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        g[r] = col_on ? __ldg(gp + r * (17 * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!NOG) g[r] = col_on ? __ldg(gp + r * (17 * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
         kh[r] = col_on ? khp[r * (17 * 4)] : mk(0.f, 0.f);
       }
       cf v[8];
@@ -99,13 +100,20 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
       fft32_fwd(v, tw, exg, q);
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const cf A = mk(kh[r].x * g[r].x, kh[r].y * g[r].x);
-        cf U = mk(g[r].y * v[r].x, g[r].y * v[r].y);
-        if (U.x * U.x + U.y * U.y < g[r].w * g[r].w) U = mk(g[r].w, 0.f);
-        cf h = cmul(A, hst[r]);
-        h.x += U.x; h.y += U.y;
-        hst[r] = h;
-        v[r] = mk(g[r].z * h.x, g[r].z * h.y);
+        if (NOG) {
+          cf h = cmul(kh[r], hst[r]);
+          h.x += v[r].x; h.y += v[r].y;
+          hst[r] = h;
+          v[r] = mk(h.x * (1.0f / HW), h.y * (1.0f / HW));
+        } else {
+          const cf A = mk(kh[r].x * g[r].x, kh[r].y * g[r].x);
+          cf U = mk(g[r].y * v[r].x, g[r].y * v[r].y);
+          if (U.x * U.x + U.y * U.y < g[r].w * g[r].w) U = mk(g[r].w, 0.f);
+          cf h = cmul(A, hst[r]);
+          h.x += U.x; h.y += U.y;
+          hst[r] = h;
+          v[r] = mk(g[r].z * h.x, g[r].z * h.y);
+        }
       }
       if (emit) {
         fft32_inv(v, tw, exg, q);
@@ -122,7 +130,10 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
       float ze[8], zo[8];
       const float* z0 = zp + roff;
 #pragma unroll
-      for (int m = 0; m < 8; ++m) { ze[m] = __ldg(z0 + 4 * m); zo[m] = __ldg(z0 + 32 + 4 * m); }
+      for (int m = 0; m < 8; ++m) {
+        ze[m] = NOG ? 1.f : __ldg(z0 + 4 * m);
+        zo[m] = NOG ? 1.f : __ldg(z0 + 32 + 4 * m);
+      }
       const cf* ge = GB + (rpl * 32 + 2 * rpair) * R32_GBS;
       const cf* go = ge + R32_GBS;
       cf v[8];
@@ -150,8 +161,9 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
 }
 
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
-                              int last_only, cudaStream_t st) {
-  auto kern = last_only ? gated_spectral_r32<true> : gated_spectral_r32<false>;
+                              int last_only, int nogate, cudaStream_t st) {
+  auto kern = nogate ? (last_only ? gated_spectral_r32<true, true> : gated_spectral_r32<false, true>)
+                     : (last_only ? gated_spectral_r32<true, false> : gated_spectral_r32<false, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        R32_SMEM_BYTES);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }

@@ -34,6 +34,7 @@ struct GemmArgs {
   int g_compact;            // 1: the gate is indexed by the OUTPUT frame, 0: by the source frame
   int out_act;              // 0 none, 1 silu, 2 sigmoid; applied to output columns n >= act_n0
   int act_n0;
+  const float* sub;         // channels-last output only: (M, N) tensor subtracted from the result, or nullptr
 };
 
 __host__ __device__ inline int gemm_src_frame(const GemmArgs& g, int f) {
@@ -183,7 +184,7 @@ gemm_simt_kernel(const GemmArgs g) {
         else if (g.out_act == 2) v = sigmoid_f(v);
       }
       if (O_PLANAR) g.out[((size_t)fr * g.o_planes + g.o_plane0 + n) * g.HW + px] = v;
-      else g.out[(size_t)m * g.N + n] = v;
+      else g.out[(size_t)m * g.N + n] = g.sub ? v - g.sub[(size_t)m * g.N + n] : v;
     }
   }
 }

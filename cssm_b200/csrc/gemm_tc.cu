@@ -333,6 +333,14 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
             float vals[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) vals[j] = __uint_as_float(r[j]) + bs[j];
+            if (g.sub != nullptr) {
+              const float4* sp = reinterpret_cast<const float4*>(g.sub + (size_t)m * g.N + cc * 32);
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float4 sv = __ldg(sp + (j >> 2));
+                vals[j] -= sv.x; vals[j + 1] -= sv.y; vals[j + 2] -= sv.z; vals[j + 3] -= sv.w;
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
               *reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(stg) +
@@ -391,6 +399,10 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
               v.y = __uint_as_float(r[j + 1]) + bias_s[cc * 32 + j + 1];
               v.z = __uint_as_float(r[j + 2]) + bias_s[cc * 32 + j + 2];
               v.w = __uint_as_float(r[j + 3]) + bias_s[cc * 32 + j + 3];
+              if (g.sub != nullptr) {
+                const float4 sv = __ldg(reinterpret_cast<const float4*>(g.sub + (size_t)m * g.N + cc * 32 + j));
+                v.x -= sv.x; v.y -= sv.y; v.z -= sv.z; v.w -= sv.w;
+              }
               *reinterpret_cast<float4*>(op + j) = v;
             }
           }

@@ -514,3 +514,94 @@ class BoundGdn:
         check(fn(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(), y.data_ptr(),
                  ws.data_ptr(), n, _stream_ptr(self.device)), what)
         return y
+
+
+# ========================================================================== no gate
+@dataclass
+class NoGateCSSM:
+    """Ungated spectral block (reference: NoGateCSSM, src/models/cssm.py:6101-6175):
+    rfft2(x) -> S_t = K_hat S_{t-1} + X_hat_t -> irfft2 -> out_proj, returned minus x.
+    Fields the reference accepts for interface compatibility and never reads
+    (rope_mode, short_conv_*, block_size, gate_type, ...) are accepted here too."""
+    channels: int
+    kernel_size: int = 11
+    spectral_rho: float = 0.999
+    rope_mode: str = "none"
+    rope_base: float = 10000.0
+    short_conv_size: int = 4
+    short_conv_spatial_size: int = 0
+    block_size: int = 1
+    position_independent_gates: bool = False
+    gate_type: str = "dense"
+    name: Optional[str] = None
+    _bound: Dict[Any, Any] = field(default_factory=dict, repr=False, compare=False)
+
+    def param_shapes(self, H: int, W: int) -> Dict[str, Any]:
+        Cc = self.channels
+        return {"kernel": (Cc, self.kernel_size, self.kernel_size),
+                "out_proj": {"kernel": (Cc, Cc), "bias": (Cc,)}}
+
+    def init(self, seed: int, x_shape, bias_scale: float = 0.0) -> Dict[str, Any]:
+        rng = np.random.default_rng(seed)
+        Cc = self.channels
+        return {"params": {
+            "kernel": (0.02 * rng.standard_normal((Cc, self.kernel_size, self.kernel_size))).astype(np.float32),
+            "out_proj": {"kernel": (rng.standard_normal((Cc, Cc)) / np.sqrt(Cc)).astype(np.float32),
+                         "bias": (bias_scale * rng.standard_normal(Cc)).astype(np.float32)}}}
+
+    def bind(self, variables, device="cuda") -> "BoundNoGate":
+        return BoundNoGate(self, variables["params"] if "params" in variables else variables,
+                           torch.device(device))
+
+    def apply(self, variables, x, injected_qkv_spatial=None):
+        key = id(variables)
+        bound = self._bound.get(key)
+        if bound is None or bound.variables_ref is not variables:
+            _require_cuda(x)
+            bound = self.bind(variables, x.device)
+            bound.variables_ref = variables
+            self._bound.clear()
+            self._bound[key] = bound
+        return bound(x)
+
+
+class BoundNoGate:
+    """A NoGateCSSM with its weights resident on one GPU and its plan cached per (H, W)."""
+
+    def __init__(self, mod: NoGateCSSM, params, device):
+        self.mod, self.device, self.variables_ref = mod, device, None
+        self.L = _lib.lib()
+        self.t = {"k": _dev_f32(params["kernel"], device),
+                  "ok": _dev_f32(params["out_proj"]["kernel"], device),
+                  "ob": _dev_f32(params["out_proj"]["bias"], device)}
+        self.w = _lib.NoGateWeights(self.t["k"].data_ptr(), self.t["ok"].data_ptr(), self.t["ob"].data_ptr())
+        self.buf = _Buffers(device)
+        self._plans: Dict[Any, torch.Tensor] = {}
+
+    def desc(self, shape):
+        B, T, H, W, Cc = shape
+        if Cc != self.mod.channels:
+            raise ValueError(f"x has {Cc} channels, module has {self.mod.channels}")
+        return _lib.NoGateDesc(B, T, H, W, Cc, self.mod.kernel_size, float(self.mod.spectral_rho))
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x)
+        x = x.contiguous()
+        d = self.desc(tuple(x.shape))
+        key = (d.H, d.W)
+        pl = self._plans.get(key)
+        if pl is None:
+            n = self.L.cssm_nogate_plan_bytes(C.byref(d))
+            if n == 0:
+                raise NotImplementedError("NoGateCSSM: no CUDA kernel for this shape")
+            pl = torch.empty(n, dtype=torch.uint8, device=self.device)
+            check(self.L.cssm_nogate_plan_init(C.byref(d), C.byref(self.w), pl.data_ptr(), n,
+                                               _stream_ptr(self.device)), "cssm_nogate_plan_init")
+            self._plans[key] = pl
+        n = self.L.cssm_nogate_workspace_bytes(C.byref(d))
+        ws = self.buf.get("ws", n)
+        y = torch.empty_like(x) if out is None else out
+        check(self.L.cssm_nogate_forward(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(),
+                                         y.data_ptr(), ws.data_ptr(), n, _stream_ptr(self.device)),
+              "cssm_nogate_forward")
+        return y

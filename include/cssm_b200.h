@@ -231,6 +231,32 @@ int cssm_gdn_forward_last(const cssm_gdn_desc* d, const cssm_gdn_weights* w, con
                           const float* x, float* y_last, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* ================================================================== NoGateCSSM ====
+ * The ungated spectral block (src/models/cssm.py:6101-6175): rfft2 of the raw input (no in_proj,
+ * no short convs, no RoPE: the reference's __call__ applies none), S_t = K_hat S_{t-1} + X_hat_t
+ * in plain complex arithmetic, irfft2, Dense out_proj, minus the input.  x, y: (B,T,H,W,C). */
+typedef struct cssm_nogate_desc {
+  int32_t B, T, H, W, C;
+  int32_t kernel_size;
+  float   spectral_rho;     /* 0.999 */
+} cssm_nogate_desc;
+
+typedef struct cssm_nogate_weights {
+  const float* kernel;           /* (C, ks, ks)   */
+  const float* out_proj_kernel;  /* (C, C)        */
+  const float* out_proj_bias;    /* (C)           */
+} cssm_nogate_weights;
+
+size_t cssm_nogate_plan_bytes(const cssm_nogate_desc* d);
+size_t cssm_nogate_workspace_bytes(const cssm_nogate_desc* d);
+/* K_hat = squash(rfft2(pad(kernel))) (cssm.py:6127-6147), once per weight set. */
+int cssm_nogate_plan_init(const cssm_nogate_desc* d, const cssm_nogate_weights* w, void* plan,
+                          size_t plan_bytes, void* stream);
+/* y = NoGateCSSM(x) (cssm.py:6124-6175). */
+int cssm_nogate_forward(const cssm_nogate_desc* d, const cssm_nogate_weights* w, const void* plan,
+                        const float* x, float* y, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
 /* ================================================================ SimpleCSSM model ====
  * Inference forward of the reference's SimpleCSSM wrapper around ONE block (depth 1):
  *   stem -> x + block(x) -> last frame -> norm_pre/act -> spatial pool -> norm_post -> head.

@@ -303,6 +303,25 @@ def gated_forward(params, x, *, kernel_size, rope_mode="none", rope_base=10000.0
 
 
 # ------------------------------------------------------------------------ GDN block
+def nogate_forward(params, x, *, kernel_size, spectral_rho=0.999, dtype=np.float64):
+    """NoGateCSSM.__call__ (cssm.py:6124-6175): rfft2 of the raw input, the plain complex scan
+    S_t = K_hat S_{t-1} + X_hat_t (direct_scalar_scan_op: no log space, no magnitude floor),
+    irfft2, Dense out_proj, minus the input."""
+    cdt = np.complex128 if dtype == np.float64 else np.complex64
+    x = np.asarray(x, dtype=dtype)
+    B, T, H, W, C = x.shape
+    K = spectral_kernel(params["kernel"], H, W, spectral_rho).astype(cdt)          # (C,H,Wf)
+    U = np.fft.rfft2(x.transpose(0, 1, 4, 2, 3), axes=(3, 4)).astype(cdt)          # (B,T,C,H,Wf)
+    s = np.zeros_like(U[:, 0])
+    outs = []
+    for t in range(T):
+        s = K[None] * s + U[:, t]
+        outs.append(s)
+    S = np.stack(outs, axis=1)
+    y = np.fft.irfft2(S, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2).astype(dtype)
+    return dense(y, params["out_proj"]) - x
+
+
 def rms_norm(x, w, eps=1e-6):
     """cssm.py:49-52."""
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps) * w

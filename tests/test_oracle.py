@@ -181,3 +181,25 @@ def test_torch_cpu_restatement_matches_numpy_oracle():
         yt = tc.gated_forward_torch(p, torch.from_numpy(x), kernel_size=11, rope_mode=rope,
                                     gate_type=gt).numpy()
         assert orc.rel_l2(yt, y) < 1e-5
+
+
+def test_nogate_oracle_is_a_circular_convolution_recurrence():
+    """NoGateCSSM in the spatial domain: s_t = k (*) s_{t-1} + x_t with circular convolution by the
+    inverse transform of the squashed kernel spectrum."""
+    rng = np.random.default_rng(4)
+    B, T, H, W, C, ks = 1, 3, 8, 8, 2, 3
+    x = rng.standard_normal((B, T, H, W, C))
+    p = {"kernel": 0.3 * rng.standard_normal((C, ks, ks)),
+         "out_proj": {"kernel": np.eye(C), "bias": np.zeros(C)}}
+    out = orc.nogate_forward(p, x, kernel_size=ks) + x           # undo the residual, identity out_proj
+    K = orc.spectral_kernel(p["kernel"], H, W, 0.999)
+    ksp = np.fft.irfft2(K, s=(H, W), axes=(1, 2))                 # (C,H,W) effective spatial kernel
+    s = np.zeros((B, H, W, C))
+    for t in range(T):
+        nxt = np.zeros_like(s)
+        for c in range(C):
+            for dh in range(H):
+                for dw in range(W):
+                    nxt[..., c] += ksp[c, dh, dw] * np.roll(s[..., c], (dh, dw), axis=(1, 2))
+        s = nxt + x[:, t]
+        assert np.allclose(out[:, t], s, atol=1e-9)
