@@ -115,6 +115,8 @@ SIGNATURES = {
                                    C.c_size_t, _P]),
     "cssm_gdn_forward_last": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
                                         C.c_size_t, _P]),
+    "cssm_gdn_forward_static_image": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P,
+                                                _P, C.c_size_t, _P]),
     "cssm_nogate_plan_bytes": (C.c_size_t, [C.POINTER(NoGateDesc)]),
     "cssm_nogate_workspace_bytes": (C.c_size_t, [C.POINTER(NoGateDesc)]),
     "cssm_nogate_plan_init": (C.c_int, [C.POINTER(NoGateDesc), C.POINTER(NoGateWeights), _P, C.c_size_t, _P]),

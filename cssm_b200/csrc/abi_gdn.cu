@@ -125,6 +125,12 @@ int cssm_gdn_forward_last(const cssm_gdn_desc* d, const cssm_gdn_weights* w, con
   return gdn_forward_internal(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1, 0);
 }
 
+int cssm_gdn_forward_static_image(const cssm_gdn_desc* d, const cssm_gdn_weights* w,
+                                  const void* plan, const float* x, float* y, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+  return gdn_forward_internal(d, w, plan, x, y, workspace, workspace_bytes, stream, 0, 2);
+}
+
 int cssm_debug_gdn_stage_events(void** events) {
   g_stage_events = reinterpret_cast<cudaEvent_t*>(events);
   return CSSM_OK;
@@ -136,9 +142,19 @@ int cssm_debug_gdn_stage_events(void** events) {
 // readout, the inverse transforms, RMSNorm and the output projection then run for the last
 // frame of every batch element only; q/k/v, the gate maps and the state recurrence cover all T.
 // x_bcast != 0: x is (B,H,W,C), one frame per batch element standing for all T frames.
+// x_bcast == 2: static-image fast path (cssm.py:4353-4683): x and y are (B,H,W,C), d->T is the
+// number of gate steps; q, k, v and gate_val are computed once per image, the gates for all T.
 int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
                                const float* x, float* y, void* workspace, size_t workspace_bytes,
                                void* stream, int last_only, int x_bcast) {
+  const int static_image = x_bcast == 2 ? 1 : 0;
+  if (static_image) {
+    x_bcast = 0;
+    if (last_only) return CSSM_ERR_UNSUPPORTED;
+    // preconditions asserted by the reference (cssm.py:4354-4370)
+    if (d && (d->short_conv_size != 0 || d->use_input_gates != 0 || d->rope_mode != CSSM_ROPE_NONE))
+      return CSSM_ERR_UNSUPPORTED;
+  }
   int s = gdn_validate(d);
   if (s != CSSM_OK) return s;
   if (!w || !plan || !x || !y || !workspace) return CSSM_ERR_NULL;
@@ -162,7 +178,8 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   cudaStream_t st = (cudaStream_t)stream;
   char* ws = (char*)workspace;
   const char* pl = (const char*)plan;
-  const int BT = d->B * d->T, HW = d->H * d->W, C = d->C;
+  const int Tdata = static_image ? 1 : d->T;            // frames of x per batch element
+  const int BT = d->B * Tdata, HW = d->H * d->W, C = d->C;
   const bool rope = d->rope_mode != CSSM_ROPE_NONE;
   const float2* rt = rope ? (const float2*)(pl + p.rope_t) : nullptr;
   const float2* rh = rope ? (const float2*)(pl + p.rope_h) : nullptr;
@@ -178,7 +195,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   memset(&dw, 0, sizeof(dw));
   dw.x = x; dw.out = d->qkv_conv_size > 1 ? xdw : nullptr;
   dw.wk = w->qkv_dw_kernel; dw.bias = w->qkv_dw_bias; dw.ksz = d->qkv_conv_size;
-  dw.BT = BT; dw.T = d->T; dw.H = d->H; dw.W = d->W; dw.C = C; dw.x_bcast = x_bcast;
+  dw.BT = BT; dw.T = Tdata; dw.H = d->H; dw.W = d->W; dw.C = C; dw.x_bcast = x_bcast;
   dw.rope_t = rt; dw.rope_h = rh; dw.rope_w = rw;
   dw.ctx_part = (float*)(ws + l.ctx_part);
   if ((s = launch_rope_dwconv_cl(dw, st)) != CSSM_OK) return s;
@@ -190,7 +207,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   g.M = BT * HW; g.N = 3 * C; g.K = C; g.HW = HW;
   g.Wk = w->qkv_proj_kernel; g.bias = w->qkv_proj_bias;
   g.out = qkv; g.o_planes = 3 * C; g.o_plane0 = 0;
-  g.T = d->T; g.H = d->H; g.W = d->W;
+  g.T = Tdata; g.H = d->H; g.W = d->W;
   if (d->qkv_conv_size > 1) { g.A = xdw; }
   else {
     g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
@@ -213,7 +230,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
   g.Wk = w->gate_proj_kernel; g.bias = w->gate_proj_bias;
   g.out = gate; g.o_planes = C; g.o_plane0 = 0;
-  g.T = d->T; g.H = d->H; g.W = d->W;
+  g.T = Tdata; g.H = d->H; g.W = d->W;
   g.out_act = d->output_gate_act == 0 ? 1 : 2;
   if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
@@ -222,7 +239,8 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   GdnGateArgs ga;
   memset(&ga, 0, sizeof(ga));
   ga.ctx_part = dw.ctx_part; ga.tcode = (const float*)(pl + p.tcode);
-  ga.BT = BT; ga.T = d->T; ga.C = C; ga.H = d->H; ga.W = d->W;
+  ga.BT = d->B * d->T; ga.T = d->T; ga.C = C; ga.H = d->H; ga.W = d->W;
+  ga.ctx_per_clip = static_image;
   ga.gate_type = d->gate_type; ga.use_input_gates = d->use_input_gates; ga.path = gdn_path(*d);
   for (int i = 0; i < nptr; ++i) { ga.gk[i] = w->gate_kernel[i]; ga.gb[i] = w->gate_bias[i]; }
   ga.ab = (float2*)(ws + l.ab); ga.bkv = (float2*)(ws + l.bkv);
@@ -236,7 +254,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
     StencilArgs sa;
     memset(&sa, 0, sizeof(sa));
     sa.buf = qkv; sa.planes_per_frame = 3 * C; sa.plane0 = i * C;
-    sa.B = d->B; sa.T = d->T; sa.C = C; sa.H = d->H; sa.W = d->W;
+    sa.B = d->B; sa.T = Tdata; sa.C = C; sa.H = d->H; sa.W = d->W;
     sa.ksp = 0; sa.kt = d->short_conv_size;
     sa.wt = w->conv_t_kernel[i]; sa.bt = w->conv_t_bias[i];
     sa.act = d->short_conv_size > 0 ? 1 : 0;
@@ -252,6 +270,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   sp.B = d->B; sp.T = d->T; sp.C = C; sp.H = d->H; sp.W = d->W; sp.dk = d->delta_key_dim;
   sp.use_l2 = d->use_spectral_l2_norm;
   sp.last_only = last_only;
+  sp.static_image = static_image;
   if ((s = launch_gdn_spectral(sp, st)) != CSSM_OK) return s;
 
   // 7. RMSNorm over channels, output gate, output projection -> channels-last y
@@ -264,7 +283,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   g.gate = gate; g.g_planes = C; g.g_plane0 = 0;
   g.Wk = w->output_proj_kernel; g.bias = w->output_proj_bias;
   g.out = y;
-  g.T = d->T; g.H = d->H; g.W = d->W;
+  g.T = Tdata; g.H = d->H; g.W = d->W;
   s = launch_gemm<true, false>(g, st);
   mark(7, st);
   return s;

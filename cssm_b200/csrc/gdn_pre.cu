@@ -143,7 +143,8 @@ __global__ void __launch_bounds__(256) gdn_gates_kernel(const GdnGateArgs g) {
   const float inv = 1.0f / (float)HW;
   for (int c = tid; c < g.C; c += blockDim.x) {
     float s = 0.f;
-    for (int h = 0; h < g.H; ++h) s += g.ctx_part[((size_t)fr * g.H + h) * g.C + c];
+    const int fsrc = g.ctx_per_clip ? fr / g.T : fr;
+    for (int h = 0; h < g.H; ++h) s += g.ctx_part[((size_t)fsrc * g.H + h) * g.C + c];
     ctx[c] = s * inv + g.tcode[t * g.C + c];
   }
   __syncthreads();

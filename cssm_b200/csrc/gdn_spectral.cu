@@ -96,14 +96,16 @@ __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpec
     float s, co; sincospif(-2.0f * (float)i / (float)H, &s, &co); twH[i] = mk(co, s);
   }
   cf* S = a.state + (size_t)blockIdx.x * dk * dk * NB;
-  for (int i = tid; i < dk * dk * NB; i += GG_THREADS) S[i] = mk(0.f, 0.f);
+  if (!a.static_image)
+    for (int i = tid; i < dk * dk * NB; i += GG_THREADS) S[i] = mk(0.f, 0.f);
   const cf* wh = a.what + (size_t)hd * NB;
   const float invHW = 1.0f / (float)HW;
+  const int Tdata = a.static_image ? 1 : a.T;      // frames of q, k, v per batch element
 
-  for (int t = 0; t < a.T; ++t) {
-    const size_t frame = (size_t)(b * a.T + t);
+  for (int t = 0; t < Tdata; ++t) {
+    const size_t frame = (size_t)(b * Tdata + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
-    const bool emit = !a.last_only || t == a.T - 1;         // same for the whole CTA
+    const bool emit = !a.last_only || t == Tdata - 1;       // same for the whole CTA
     float nq[GDN_MAXDK], nk[GDN_MAXDK];
     for (int i = 0; i < dk; ++i) {
       float p = 0.f;
@@ -134,13 +136,24 @@ __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpec
       const float kn = rsqrtf(ks + 1e-6f);
       for (int i = 0; i < dk; ++i) SK[(size_t)i * NB + o] = mk(kv[i].x * kn, kv[i].y * kn);
     }
-    const float2* ab = a.ab + frame * NB;
+    const float2* ab = a.ab + (a.static_image ? (size_t)b * a.T : frame) * NB;
     for (int v = 0; v < dk; ++v) {
       float* vplane = base + (size_t)(2 * a.C + hd * dk + v) * HW;
       gen_fwd_plane(vplane, xs, Rb, Fb, twW, twH, H, W);
       for (int o = tid; o < NB; o += GG_THREADS) {
         cf kk[GDN_MAXDK], qq[GDN_MAXDK];
         for (int i = 0; i < dk; ++i) { kk[i] = SK[(size_t)i * NB + o]; qq[i] = SQ[(size_t)i * NB + o]; }
+        if (a.static_image) {
+          cf ov;
+          switch (dk) {
+            case 1: ov = gdn_bin_static<1>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
+            case 2: ov = gdn_bin_static<2>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
+            case 3: ov = gdn_bin_static<3>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
+            default: ov = gdn_bin_static<4>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
+          }
+          Fb[o] = mk(ov.x * invHW, ov.y * invHW);
+          continue;
+        }
         const float2 g = ab[o];
         const cf w = wh[o];
         const cf aw = mk(g.x * w.x, g.x * w.y);

@@ -23,7 +23,8 @@ constexpr int G32_STATE_CF = 4 * 8 * G32_THREADS;      // [i][r][thread]
 constexpr int G32_SMEM_BYTES = (G32_EX_CF + G32_ZR_CF + G32_GB_CF + G32_SPEC_CF + G32_STATE_CF) * 8;
 
 // LAST: only the last step's output planes are produced (compile-time switch).
-template <bool LAST>
+// STATIC: static-image fast path (one data frame per batch element, the T gate steps run per bin).
+template <bool LAST, bool STATIC>
 __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpectralArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
@@ -65,11 +66,12 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
     wh[r] = col_on ? a.what[(size_t)hd * NB + ((r * 17 + kw) << 2) + q] : mk(0.f, 0.f);
   const float invHW = 1.0f / (float)HW;
 
-  for (int t = 0; t < a.T; ++t) {
-    const size_t frame = (size_t)(b * a.T + t);
+  const int Tdata = STATIC ? 1 : a.T;          // frames of q, k, v per batch element
+  for (int t = 0; t < Tdata; ++t) {
+    const size_t frame = (size_t)(b * Tdata + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
     float ssq[2] = {0.f, 0.f};
-    const bool emit = !LAST || t == a.T - 1;         // same for the whole CTA
+    const bool emit = !LAST || t == Tdata - 1;       // same for the whole CTA
     cf v[8];
     // ---- passes 0 (q), 1 (k), 2 (v): forward transform of four planes at once ----
 #pragma unroll 1
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
         for (int w = 0; w < 9; ++w) s += red[w][p];
         nrm[p] = a.use_l2 ? rsqrtf(s + 1e-6f) : 1.f;
       }
-      const float2* abp = a.ab + frame * NB + (kw << 2) + q;
+      const float2* abp = a.ab + (STATIC ? (size_t)b * a.T : frame) * NB + (kw << 2) + q;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         cf kk[4], qq[4];
@@ -148,7 +150,9 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
 #pragma unroll
         for (int i = 0; i < 4; ++i) kk[i] = mk(kk[i].x * kn, kk[i].y * kn);
         cf o = mk(0.f, 0.f);
-        if (col_on) {
+        if (STATIC) {
+          if (col_on) o = gdn_bin_static<4>(kk, qq, v[r], wh[r], abp + r * (17 * 4), NB, a.T);
+        } else if (col_on) {
           const float2 g = abp[r * (17 * 4)];
           const cf aw = mk(g.x * wh[r].x, g.x * wh[r].y);
           if (emit)
@@ -194,7 +198,8 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
 }
 
 int launch_gdn_spectral_r32(const GdnSpectralArgs& a, cudaStream_t st) {
-  auto kern = a.last_only ? gdn_spectral_r32<true> : gdn_spectral_r32<false>;
+  auto kern = a.static_image ? gdn_spectral_r32<false, true>
+                             : (a.last_only ? gdn_spectral_r32<true, false> : gdn_spectral_r32<false, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        G32_SMEM_BYTES);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }

@@ -13,7 +13,8 @@ constexpr int G64_SPEC_CF = 8 * 8 * R64_NT;     // [plane 0..7][q 0..7][thread]
 constexpr int G64_SMEM_CF = R64_EX_CF + R64_ZR_CF + R64_GB_CF + G64_SPEC_CF;
 
 // LAST: only the last step's output planes are produced (compile-time switch).
-template <bool LAST>
+// STATIC: static-image fast path (one data frame per batch element, the T gate steps run per bin).
+template <bool LAST, bool STATIC>
 __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
@@ -28,12 +29,13 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
   constexpr int HW = 4096, NB = 64 * 33, DK = 4;
   const int nh = a.C / DK;
   const int b = blockIdx.x / nh, hd = blockIdx.x % nh;
+  const int Tdata = STATIC ? 1 : a.T;          // frames of q, k, v per batch element
 
   // state scratch: S[v][i][q][thread]; zero it (a thread only ever touches its own slots)
   cf* S = a.state + (size_t)blockIdx.x * DK * DK * NB;   // 16 * 2112 = 16 * 8 * 264 slots
   // lanes of column passes: slot index inside a (v,i) block is q*264 + (grp*8 + a), grp <= 32
   const int cslot = c.grp * 8 + c.a;
-  if (c.col_on)
+  if (c.col_on && !STATIC)
     for (int vi = 0; vi < DK * DK; ++vi)
 #pragma unroll
       for (int q = 0; q < 8; ++q) S[(size_t)vi * NB + q * 264 + cslot] = mk(0.f, 0.f);
@@ -46,20 +48,20 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
 
   // plane idx 0..3 = q, 4..7 = k, 8..11 = v of step t; idx 12 = first plane of step t + 1
   // last_only: steps before the last one skip the q planes (their sequence starts at idx 4)
-  auto first_of = [&](int t) -> int { return (LAST && t < a.T - 1) ? 4 : 0; };
+  auto first_of = [&](int t) -> int { return (LAST && t < Tdata - 1) ? 4 : 0; };
   auto plane_of = [&](int t, int idx) -> float* {
     if (idx >= 12) { ++t; idx = first_of(t); }
-    if (t >= a.T) { t = a.T - 1; idx = 0; }                 // harmless re-read past the end
-    const size_t frame = (size_t)(b * a.T + t);
+    if (t >= Tdata) { t = Tdata - 1; idx = 0; }             // harmless re-read past the end
+    const size_t frame = (size_t)(b * Tdata + t);
     return a.qkv + (frame * 3 * a.C + (size_t)(idx >> 2) * a.C + hd * DK + (idx & 3)) * HW;
   };
   cf nx[8];                                   // rows of the NEXT plane, fetched one pass ahead
   r64_load_rows(c, plane_of(0, first_of(0)), nx);
 
-  for (int t = 0; t < a.T; ++t) {
-    const size_t frame = (size_t)(b * a.T + t);
+  for (int t = 0; t < Tdata; ++t) {
+    const size_t frame = (size_t)(b * Tdata + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
-    const bool emit = !LAST || t == a.T - 1;         // same for the whole CTA
+    const bool emit = !LAST || t == Tdata - 1;       // same for the whole CTA
     float ssq[8];
 #pragma unroll
     for (int p = 0; p < 4; ++p) ssq[p] = 0.f;
@@ -124,7 +126,8 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
           SPEC[((4 + i) * 8 + q) * R64_NT + tid] = mk(kv[i].x * kn, kv[i].y * kn);
       }
     }
-    const float2* abp = a.ab + frame * NB + (c.grp << 3) + c.a;
+    // gates: of this frame, or (static path) of step 0 of this batch element's T steps
+    const float2* abp = a.ab + (STATIC ? (size_t)b * a.T : frame) * NB + (c.grp << 3) + c.a;
     // ---- v rows: transform, state update, readout, inverse transform over the v plane ----
 #pragma unroll 1
     for (int vr = 0; vr < DK; ++vr) {
@@ -145,12 +148,14 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
         cf sreg[8][4];
         float2 gab[8];
         cf* srow = S + (size_t)(vr * DK) * NB + cslot;
+        if (!STATIC) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+          for (int q = 0; q < 8; ++q) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            sreg[q][i] = c.col_on ? srow[(size_t)i * NB + q * 264] : mk(0.f, 0.f);
-          gab[q] = c.col_on ? __ldg(abp + q * (33 * 8)) : make_float2(0.f, 0.f);
+            for (int i = 0; i < 4; ++i)
+              sreg[q][i] = c.col_on ? srow[(size_t)i * NB + q * 264] : mk(0.f, 0.f);
+            gab[q] = c.col_on ? __ldg(abp + q * (33 * 8)) : make_float2(0.f, 0.f);
+          }
         }
         cf v[8];
         r64_col_fwd(c, v);
@@ -162,6 +167,12 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
             qq[i] = SPEC[(i * 8 + q) * R64_NT + tid];
             kk[i] = SPEC[((4 + i) * 8 + q) * R64_NT + tid];
           }
+          if (STATIC) {
+            cf o = mk(0.f, 0.f);
+            if (c.col_on) o = gdn_bin_static<4>(kk, qq, v[q], wh[q], abp + q * (33 * 8), NB, a.T);
+            v[q] = mk(o.x * invHW, o.y * invHW);
+            continue;
+          }
           const cf aw = mk(gab[q].x * wh[q].x, gab[q].x * wh[q].y);
           if (emit) {
             const cf o = gdn_bin_update_regs<4, true>(sreg[q], kk, qq, v[q], aw, gab[q].y);
@@ -170,7 +181,7 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
             gdn_bin_update_regs<4, false>(sreg[q], kk, qq, v[q], aw, gab[q].y);
           }
         }
-        if (c.col_on) {
+        if (c.col_on && !STATIC) {
 #pragma unroll
           for (int q = 0; q < 8; ++q)
 #pragma unroll
@@ -195,7 +206,8 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
 
 int launch_gdn_spectral_r64(const GdnSpectralArgs& a, cudaStream_t st) {
   const size_t smem = (size_t)G64_SMEM_CF * sizeof(cf);
-  auto kern = a.last_only ? gdn_spectral_r64<true> : gdn_spectral_r64<false>;
+  auto kern = a.static_image ? gdn_spectral_r64<false, true>
+                             : (a.last_only ? gdn_spectral_r64<true, false> : gdn_spectral_r64<false, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   kern<<<a.B * (a.C / 4), R64_NT, smem, st>>>(a);

@@ -57,6 +57,7 @@ int launch_rope_dwconv_cl(const GdnDwArgs& a, cudaStream_t st);
 struct GdnGateArgs {
   const float* ctx_part; const float* tcode;   // (BT,H,C), (T,C)
   int BT, T, C, H, W, gate_type, use_input_gates, path;
+  int ctx_per_clip;                      // 1: ctx_part holds one frame per clip (frame fr reads fr / T)
   const float* gk[8]; const float* gb[8];
   float2* ab;                            // (BT, H*Wf) {alpha, beta} in spectral bin order
   float2* bkv;                           // (BT, H*W)  {B_k, B_v}
@@ -69,6 +70,9 @@ struct GdnSpectralArgs {
   const float2* ab;          // (BT, H*Wf)
   cf* state;                 // (B*n_h, dk, dk, H*Wf) scratch for the matrix state
   int B, T, C, H, W, dk, use_l2;
+  int static_image;          // != 0: static-image fast path: qkv holds ONE frame per batch element
+                             // (B, 3C, H, W); ab holds the gates of T steps; the whole scan runs per
+                             // bin with a bf16 carry and only the final readout is produced
   int last_only;             // != 0: only the last step's output planes are produced (the q
                              // transforms, readout and inverse transforms of earlier steps are skipped)
 };

@@ -397,7 +397,14 @@ class GatedDeltaNetCSSM:
         if self.cross_freq_conv_size or self.int_attention_mode != "none" or self.ssl_proj_dim:
             bad.append("cross_freq_conv / int_attention / ssl_proj")
         if self.static_image_fast_path:
-            bad.append("static_image_fast_path")
+            # the reference asserts these (cssm.py:4354-4370)
+            if self.short_conv_size != 0 or self.use_input_gates or self.rope_mode != "none":
+                raise AssertionError("static_image_fast_path requires short_conv_size=0, "
+                                     "use_input_gates=False, rope_mode='none'")
+            if self.num_timesteps <= 0:
+                raise AssertionError("static_image_fast_path requires num_timesteps > 0")
+            if self.output_norm == "layer":
+                bad.append("output_norm='layer'")
         if self.output_gate_act not in ("silu", "sigmoid"):
             bad.append(f"output_gate_act={self.output_gate_act!r}")
         if self.delta_key_dim > 4:
@@ -497,9 +504,25 @@ class BoundGdn:
                  last_frame_only: bool = False) -> torch.Tensor:
         """y = block(x).  With last_frame_only=True returns block(x)[:, -1] of shape (B,H,W,C)
         (for callers with a last-frame readout): the readout, inverse transforms and output
-        projections of the earlier frames are not computed."""
+        projections of the earlier frames are not computed.  A 4-D x (B,H,W,C) takes the
+        static-image fast path when the module was built with static_image_fast_path=True
+        (T = num_timesteps gate steps, bf16 carry, final readout; returns (B,H,W,C))."""
         _require_cuda(x)
         x = x.contiguous()
+        if x.dim() == 4:
+            if not self.mod.static_image_fast_path:
+                raise ValueError("GatedDeltaNetCSSM: a 4-D input needs static_image_fast_path=True")
+            B, H, W, Cc = x.shape
+            d = self.desc((B, self.mod.num_timesteps, H, W, Cc))
+            pl = self.plan(d)
+            n = self.L.cssm_gdn_workspace_bytes(C.byref(d))
+            ws = self.buf.get("ws", n)
+            y = torch.empty_like(x) if out is None else out
+            check(self.L.cssm_gdn_forward_static_image(C.byref(d), C.byref(self.w), pl.data_ptr(),
+                                                       x.data_ptr(), y.data_ptr(), ws.data_ptr(), n,
+                                                       _stream_ptr(self.device)),
+                  "cssm_gdn_forward_static_image")
+            return y
         d = self.desc(tuple(x.shape))
         pl = self.plan(d)
         n = self.L.cssm_gdn_workspace_bytes(C.byref(d))

@@ -231,6 +231,18 @@ int cssm_gdn_forward_last(const cssm_gdn_desc* d, const cssm_gdn_weights* w, con
                           const float* x, float* y_last, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* Static-image fast path (GatedDeltaNetCSSM with static_image_fast_path=True and a 4-D input,
+ * src/models/cssm.py:4353-4683): x, y are (B,H,W,C); d->T is num_timesteps.  q, k, v, their
+ * spectra and gate_val are computed once per image; alpha_t, beta_t come from the spatial mean of
+ * x plus the temporal code; the scan carries M_t, Delta_t and the state rounded to bfloat16 real /
+ * imaginary parts with fp32 accumulation (cssm.py:4598-4632) and only the final state is read
+ * out.  Requires short_conv_size = 0, use_input_gates = 0, rope_mode none (the reference asserts
+ * the same, cssm.py:4354-4370), else CSSM_ERR_UNSUPPORTED.  Plan and workspace: those of
+ * cssm_gdn_plan_init / cssm_gdn_workspace_bytes for the same desc. */
+int cssm_gdn_forward_static_image(const cssm_gdn_desc* d, const cssm_gdn_weights* w,
+                                  const void* plan, const float* x, float* y, void* workspace,
+                                  size_t workspace_bytes, void* stream);
+
 /* ================================================================== NoGateCSSM ====
  * The ungated spectral block (src/models/cssm.py:6101-6175): rfft2 of the raw input (no in_proj,
  * no short convs, no RoPE: the reference's __call__ applies none), S_t = K_hat S_{t-1} + X_hat_t

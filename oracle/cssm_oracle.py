@@ -303,6 +303,85 @@ def gated_forward(params, x, *, kernel_size, rope_mode="none", rope_base=10000.0
 
 
 # ------------------------------------------------------------------------ GDN block
+def bf16_round(a):
+    """Round float values to the nearest bfloat16 (ties to even) and return them as float32:
+    what `x.astype(jnp.bfloat16).astype(jnp.float32)` gives."""
+    f = np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+    u = f.view(np.uint32)
+    r = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000))
+    return r.view(np.float32).reshape(f.shape)
+
+
+def gdn_static_forward(params, x, *, num_timesteps, delta_key_dim=4, kernel_size=11,
+                       rope_base=10000.0, spectral_rho=0.999, gate_type="factored",
+                       output_norm="rms", output_gate_act="silu", use_spectral_l2_norm=True,
+                       qkv_conv_size=1, no_spectral_clamp=False, carry="bf16"):
+    """GatedDeltaNetCSSM static-image fast path (cssm.py:4353-4683): x is (B,H,W,C); q, k, v and
+    their spectra are T-invariant, only the gates alpha_t, beta_t vary (the spatial mean of x plus
+    the temporal code); the scan S_t = M_t S_{t-1} + Delta_t carries the state in the
+    "linear split" bf16 format (M, Delta and the carry are rounded to bf16 real / imaginary parts,
+    the products accumulate in fp32: cssm.py:4598-4632); only the final state is read out.
+    Preconditions of the reference (cssm.py:4354-4370): short_conv_size=0, use_input_gates=False,
+    rope_mode='none'.  carry='fp64' skips the bf16 rounding (to measure what it costs)."""
+    x = np.asarray(x, np.float64)
+    B, H, W, C = x.shape
+    T, Wf, dk = num_timesteps, W // 2 + 1, delta_key_dim
+    nh = C // dk
+    W_hat = spectral_kernel(params["kernel"], H, W, spectral_rho, squash=not no_spectral_clamp)
+    qkv_in = dwconv2d_same(x, params["qkv_dw"]) if qkv_conv_size > 1 else x
+    qkv = dense(qkv_in, params["qkv_proj"])
+    q_in, k_in, v_in = qkv[..., :C], qkv[..., C:2 * C], qkv[..., 2 * C:]
+    gate_val = dense(x, params["gate_proj"])
+    gate_val = silu(gate_val) if output_gate_act == "silu" else sigmoid(gate_val)
+
+    def spec(a):
+        return np.fft.rfft2(a.reshape(B, H, W, nh, dk).transpose(0, 3, 4, 1, 2), axes=(3, 4))
+
+    q_s, k_s, v_s = spec(q_in), spec(k_in), spec(v_in)                         # (B,nh,dk,H,Wf)
+
+    def l2(z):
+        if not use_spectral_l2_norm:
+            return z
+        return z / np.sqrt(np.sum(np.abs(z) ** 2, axis=(3, 4), keepdims=True) + 1e-6)
+
+    k_n = l2(k_s)
+    k_n = k_n / np.sqrt(np.sum(np.abs(k_n) ** 2, axis=2, keepdims=True) + 1e-6)
+    q_n = l2(q_s)
+    k_outer = k_n[:, :, :, None] * np.conj(k_n[:, :, None, :])                 # (B,nh,i,j,H,Wf)
+    vk_outer = v_s[:, :, :, None] * np.conj(k_n[:, :, None, :])                # (B,nh,v,j,H,Wf)
+
+    ctx = x.mean(axis=(1, 2))[:, None, :] + temporal_ctx_code(T, C, rope_base)[None]   # (B,T,C)
+
+    def gate(name, bounded):
+        if gate_type == "factored":
+            raw = sigmoid(dense(ctx, params[f"{name}_h"])[..., :, None]
+                          + dense(ctx, params[f"{name}_w"])[..., None, :])
+        elif gate_type == "dense":
+            raw = sigmoid(dense(ctx, params[name])).reshape(B, T, H, Wf)
+        else:
+            raise NotImplementedError(gate_type)
+        return 0.1 + 0.89 * raw if bounded else raw                            # (B,T,H,Wf)
+
+    alpha, beta = gate("alpha", True), gate("beta", False)
+    eye = np.eye(dk).reshape(1, 1, dk, dk, 1, 1)
+    rnd = (lambda z: bf16_round(z.real).astype(np.float64) + 1j * bf16_round(z.imag).astype(np.float64)) \
+        if carry == "bf16" else (lambda z: z)
+    S = np.zeros((B, nh, dk, dk, H, Wf), dtype=np.complex128)                  # [v, i]
+    for t in range(T):
+        a_t = alpha[:, t][:, None, None, None]                                 # (B,1,1,1,H,Wf)
+        b_t = beta[:, t][:, None, None, None]
+        M = rnd(a_t * W_hat[None, :, None, None] * (eye - b_t * k_outer))      # (B,nh,i,j,H,Wf)
+        D = rnd(b_t * vk_outer)                                                # (B,nh,v,j,H,Wf)
+        S = rnd(np.einsum("bhijyx,bhvjyx->bhviyx", M, S) + D)
+    o_hat = np.sum(S * q_n[:, :, None], axis=3).reshape(B, C, H, Wf)
+    o = np.fft.irfft2(o_hat, s=(H, W), axes=(2, 3)).transpose(0, 2, 3, 1)
+    if output_norm == "rms":
+        o = rms_norm(o, np.asarray(params["rms_scale"], np.float64))
+    elif output_norm != "none":
+        raise NotImplementedError(output_norm)
+    return dense(o * gate_val, params["output_proj"])
+
+
 def nogate_forward(params, x, *, kernel_size, spectral_rho=0.999, dtype=np.float64):
     """NoGateCSSM.__call__ (cssm.py:6124-6175): rfft2 of the raw input, the plain complex scan
     S_t = K_hat S_{t-1} + X_hat_t (direct_scalar_scan_op: no log space, no magnitude floor),

@@ -95,3 +95,48 @@ def test_last_frame_only_matches_full_forward(case):
     assert np.isfinite(y_last).all()
     assert orc.rel_l2(y_last, y[:, -1]) <= 1e-6
     assert orc.rel_l2(y_last, ref[:, -1]) <= TOL
+
+
+STATIC_CASES = [
+    # B, T, H, W, C, dk, ks, gate, qkv_conv
+    (2, 4, 8, 8, 8, 4, 5, "factored", 3),          # generic kernel
+    (2, 6, 32, 32, 8, 4, 11, "dense", 1),          # 32x32 radix kernel
+    (2, 5, 64, 64, 8, 4, 11, "factored", 5),       # 64x64 radix kernel
+    (1, 3, 64, 64, 64, 4, 11, "factored", 1),      # tensor-core projections
+    (1, 3, 14, 14, 8, 2, 3, "factored", 1),        # d_k = 2
+]
+
+
+@pytest.mark.parametrize("case", STATIC_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_static_image_fast_path(case):
+    """4-D input through cssm_gdn_forward_static_image against the oracle of the reference's
+    static-image path, which carries M_t, Delta_t and the state in bfloat16: tolerance rel-L2
+    <= 2e-2 (the bf16 tolerance).  Two kernels that round at slightly different fp32 inputs may
+    land on neighbouring bf16 values, so exact fp32-level agreement is not expected; the error
+    against the SAME scan carried in fp64 must be of the size the oracle's own bf16 rounding
+    costs."""
+    B, T, H, W, C, dk, ks, gate, qkvk = case
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((B, H, W, C)).astype(np.float32)
+    p = orc.init_gdn_params(8, C, H, W, delta_key_dim=dk, kernel_size=ks, gate_type=gate,
+                            short_conv_size=0, qkv_conv_size=qkvk, use_input_gates=False,
+                            bias_scale=0.1, perturb_rms=True)
+    kw = dict(num_timesteps=T, delta_key_dim=dk, kernel_size=ks, gate_type=gate, qkv_conv_size=qkvk)
+    ref = orc.gdn_static_forward(p, x, **kw)
+    ref64 = orc.gdn_static_forward(p, x, carry="fp64", **kw)
+    mod = GatedDeltaNetCSSM(channels=C, delta_key_dim=dk, kernel_size=ks, rope_mode="none",
+                            gate_type=gate, short_conv_size=0, qkv_conv_size=qkvk,
+                            use_input_gates=False, static_image_fast_path=True, num_timesteps=T)
+    y = mod.apply({"params": p}, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert y.shape == x.shape and np.isfinite(y).all()
+    assert orc.rel_l2(y, ref) <= 2e-2
+    assert orc.rel_l2(y, ref64) <= 2.0 * orc.rel_l2(ref, ref64) + 1e-4
+
+
+def test_static_image_preconditions():
+    with pytest.raises(AssertionError):
+        GatedDeltaNetCSSM(channels=8, delta_key_dim=4, static_image_fast_path=True, num_timesteps=4,
+                          short_conv_size=4, use_input_gates=False, gate_type="factored").bind({"params": {}})
+    with pytest.raises(AssertionError):
+        GatedDeltaNetCSSM(channels=8, delta_key_dim=4, static_image_fast_path=True, num_timesteps=0,
+                          short_conv_size=0, use_input_gates=False, gate_type="factored").bind({"params": {}})

@@ -203,3 +203,28 @@ def test_nogate_oracle_is_a_circular_convolution_recurrence():
                     nxt[..., c] += ksp[c, dh, dw] * np.roll(s[..., c], (dh, dw), axis=(1, 2))
         s = nxt + x[:, t]
         assert np.allclose(out[:, t], s, atol=1e-9)
+
+
+def test_gdn_static_image_oracle_equals_general_path_last_frame():
+    """With the bf16 carry switched off, the static-image fast path is the general path on the
+    clip that repeats the image, read at the last frame (no short conv, no input gates, no RoPE)."""
+    rng = np.random.default_rng(1)
+    B, H, W, C, T = 2, 8, 8, 8, 4
+    x = rng.standard_normal((B, H, W, C))
+    p = orc.init_gdn_params(3, C, H, W, delta_key_dim=4, kernel_size=5, gate_type="factored",
+                            short_conv_size=0, qkv_conv_size=3, use_input_gates=False,
+                            bias_scale=0.1, perturb_rms=True)
+    y64 = orc.gdn_static_forward(p, x, num_timesteps=T, kernel_size=5, qkv_conv_size=3, carry="fp64")
+    yg = orc.gdn_forward(p, np.repeat(x[:, None], T, axis=1), delta_key_dim=4, kernel_size=5,
+                         rope_mode="none", gate_type="factored", short_conv_size=0, qkv_conv_size=3,
+                         use_input_gates=False)
+    assert orc.rel_l2(y64, yg[:, -1]) <= 1e-12
+    y = orc.gdn_static_forward(p, x, num_timesteps=T, kernel_size=5, qkv_conv_size=3)
+    assert 1e-5 < orc.rel_l2(y, y64) < 2e-2          # what the bf16 carry costs
+
+
+def test_bf16_round_matches_torch():
+    import torch
+    a = (np.random.default_rng(0).standard_normal(4096) * 3).astype(np.float32)
+    ref = torch.from_numpy(a).to(torch.bfloat16).to(torch.float32).numpy()
+    assert np.array_equal(orc.bf16_round(a), ref)
