@@ -97,3 +97,63 @@ def test_module_param_tree_names_match_flax():
     assert set(m.param_shapes(16, 16)) == {"in_proj", "kernel", "out_proj", "delta_proj", "B_proj",
                                            "C_proj"}
     assert m.param_shapes(16, 16)["delta_proj"]["kernel"] == (8, 16 * 9)
+
+
+def _gdn_desc(**kw):
+    d = dict(B=2, T=3, H=8, W=8, C=8, delta_key_dim=4, kernel_size=3, rope_mode=0, rope_base=10000.0,
+             spectral_rho=0.999, gate_type=1, short_conv_size=0, output_norm=1, use_input_gates=0,
+             output_gate_act=0, use_spectral_l2_norm=1, qkv_conv_size=1, no_spectral_clamp=0)
+    d.update(kw)
+    return _lib.GdnDesc(**d)
+
+
+def test_last_frame_and_static_entry_points_validate_without_gpu():
+    L = _built()
+    w = _lib.GatedWeights()
+    # NULL pointers: rejected before any CUDA call
+    assert L.cssm_gated_forward_last(C.byref(_desc()), C.byref(w), None, None, None, None, 0, None) == 1
+    gw = _lib.GdnWeights()
+    assert L.cssm_gdn_forward_last(C.byref(_gdn_desc()), C.byref(gw), None, None, None, None, 0, None) == 1
+    # the static-image path refuses descriptors the reference would assert on
+    for bad in (dict(short_conv_size=4), dict(use_input_gates=1), dict(rope_mode=1)):
+        assert L.cssm_gdn_forward_static_image(C.byref(_gdn_desc(**bad)), C.byref(gw), None, None, None,
+                                               None, 0, None) == 3, bad
+    assert L.cssm_gdn_forward_static_image(C.byref(_gdn_desc()), C.byref(gw), None, None, None,
+                                           None, 0, None) == 1
+
+
+def test_nogate_descriptor_validation_without_gpu():
+    L = _built()
+    d = _lib.NoGateDesc(2, 3, 8, 8, 8, 3, 0.999)
+    assert L.cssm_nogate_plan_bytes(C.byref(d)) >= 8 * 8 * 5 * 8
+    assert L.cssm_nogate_workspace_bytes(C.byref(d)) == 2 * 3 * 2 * 8 * 8 * 8 * 4
+    assert L.cssm_nogate_plan_bytes(C.byref(_lib.NoGateDesc(2, 3, 8, 8, 6, 3, 0.999))) == 0     # C % 4
+    assert L.cssm_nogate_plan_bytes(C.byref(_lib.NoGateDesc(0, 3, 8, 8, 8, 3, 0.999))) == 0
+    w = _lib.NoGateWeights()
+    assert L.cssm_nogate_forward(C.byref(d), C.byref(w), None, None, None, None, 0, None) == 1
+
+
+def _simple_desc(**kw):
+    d = dict(B=2, T=3, Hin=16, Win=16, Cin=1, image_input=1, stem_mode=0, stem_layers=1, embed_dim=8,
+             block=0, pool_type=1, readout_norm=0, num_classes=2)
+    d.update(kw)
+    return _lib.SimpleDesc(**d)
+
+
+def test_simple_model_descriptor_validation_without_gpu():
+    L = _built()
+    bd = _desc(B=2, T=3, H=8, W=8, C=8)
+    n = L.cssm_simple_workspace_bytes(C.byref(_simple_desc()), C.byref(bd))
+    assert n > L.cssm_gated_workspace_bytes(C.byref(bd))
+    assert L.cssm_simple_host_workspace_bytes(C.byref(_simple_desc()), C.byref(bd)) > n
+    # the block descriptor must describe the stem's output
+    assert L.cssm_simple_workspace_bytes(C.byref(_simple_desc()), C.byref(_desc(B=2, T=3, H=16, W=16, C=8))) == 0
+    assert L.cssm_simple_workspace_bytes(C.byref(_simple_desc(stem_layers=2)), C.byref(bd)) == 0
+    assert L.cssm_simple_workspace_bytes(C.byref(_simple_desc(Hin=15, Win=15)), C.byref(bd)) == n      # ceil(15/2) = 8
+    for bad in (dict(embed_dim=128), dict(embed_dim=6), dict(stem_mode=2), dict(stem_layers=0),
+                dict(pool_type=2), dict(num_classes=0), dict(block=3)):
+        assert L.cssm_simple_workspace_bytes(C.byref(_simple_desc(**bad)), C.byref(bd)) == 0, bad
+    w = _lib.SimpleWeights()
+    assert L.cssm_simple_forward(C.byref(_simple_desc()), C.byref(w), C.byref(bd), None, None, None,
+                                 None, None, 0, 0, None) == 1
+    assert L.cssm_simple_stem(C.byref(_simple_desc(embed_dim=128)), C.byref(w), None, None, None, 0, None) == 3
