@@ -178,6 +178,11 @@ def cpu_model_rate(workload, sample_b, reps=1):
     import torch
     from oracle import simple_oracle as so
     from oracle import cssm_torch_cpu as tc
+    # all host threads this process may use (torchrun presets OMP_NUM_THREADS=1 for its workers)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     m = make_model(workload)
     x = make_inputs(workload, sample_b, seed0=3000)
     H, W = m.feature_hw(x.shape[-3], x.shape[-2])
@@ -341,9 +346,10 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # keep stdout to the one JSON line: NCCL prints its version banner there at INFO/VERSION
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "INFO"):
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # keep stdout to the one JSON line: NCCL prints a version banner there at the VERSION, WARN
+        # and INFO levels (an unrecognised level name means "none")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "WARN", "INFO"):
+            os.environ["NCCL_DEBUG"] = "NONE"
         dist.init_process_group("nccl", device_id=dev)
     st = torch.cuda.current_stream(dev)
 
