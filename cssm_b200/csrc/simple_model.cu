@@ -525,62 +525,21 @@ int cssm_simple_forward_host(const cssm_simple_desc* d, const cssm_simple_weight
   if (!aligned16(workspace)) return CSSM_ERR_ALIGN;
   if (workspace_bytes < cssm_simple_host_workspace_bytes(d, block_desc)) return CSSM_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t per_item = (size_t)(d->image_input ? 1 : d->T) * d->Hin * d->Win * d->Cin;   // floats
-  const size_t nx = (size_t)d->B * per_item * sizeof(float);
+  const size_t nx = (size_t)(d->image_input ? d->B : d->B * d->T) * d->Hin * d->Win * d->Cin * sizeof(float);
   const size_t nl = (size_t)d->B * d->num_classes * sizeof(float);
   char* ws = (char*)workspace;
   float* xd = (float*)(ws + base);
   float* ld = (float*)(ws + base + round_up(nx, 256));
-
-  // The batch goes through in up to four chunks: the copies of all chunks are queued on a second
-  // stream and the model of chunk i starts as soon as its images have arrived, so that all but
-  // the first copy overlap with compute.  Every chunk reuses the same model workspace.
-  constexpr int MAXCH = 4;
-  int nch = 1;
-  if (d->B >= 64 && d->B % MAXCH == 0 && (per_item * (d->B / MAXCH) * sizeof(float)) % 16 == 0) nch = MAXCH;
-  const int cb = d->B / nch;
-  cssm_simple_desc dc = *d;
-  dc.B = cb;
-  cssm_gated_desc bg;
-  cssm_gdn_desc bn;
-  const void* bd = block_desc;
-  if (d->block == 0) { bg = *(const cssm_gated_desc*)block_desc; bg.B = cb; bd = &bg; }
-  else { bn = *(const cssm_gdn_desc*)block_desc; bn.B = cb; bd = &bn; }
-
-  cudaStream_t cs = nullptr;
-  cudaEvent_t ev[MAXCH + 1] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-  int rc = CSSM_OK;
-  cudaError_t e = cudaSuccess;
-  auto fail = [&](cudaError_t err) { set_cuda_error(err); rc = CSSM_ERR_CUDA; };
-  if (nch > 1) {
-    if ((e = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking)) != cudaSuccess) fail(e);
-    for (int i = 0; i <= nch && rc == CSSM_OK; ++i)
-      if ((e = cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming)) != cudaSuccess) fail(e);
-    // the staging area may still be read by earlier work on the caller's stream
-    if (rc == CSSM_OK && (e = cudaEventRecord(ev[nch], st)) != cudaSuccess) fail(e);
-    if (rc == CSSM_OK && (e = cudaStreamWaitEvent(cs, ev[nch], 0)) != cudaSuccess) fail(e);
-  }
-  for (int i = 0; i < nch && rc == CSSM_OK; ++i) {
-    const size_t off = (size_t)i * cb * per_item;
-    e = cudaMemcpyAsync(xd + off, x_host + off, (size_t)cb * per_item * sizeof(float),
-                        cudaMemcpyHostToDevice, nch > 1 ? cs : st);
-    if (e != cudaSuccess) { fail(e); break; }
-    if (nch > 1 && (e = cudaEventRecord(ev[i], cs)) != cudaSuccess) fail(e);
-  }
-  for (int i = 0; i < nch && rc == CSSM_OK; ++i) {
-    if (nch > 1 && (e = cudaStreamWaitEvent(st, ev[i], 0)) != cudaSuccess) { fail(e); break; }
-    rc = cssm_simple_forward(&dc, w, bd, block_weights, block_plan, xd + (size_t)i * cb * per_item,
-                             ld + (size_t)i * cb * d->num_classes, workspace, base, flags, stream);
-  }
-  if (rc == CSSM_OK && (e = cudaMemcpyAsync(logits_host, ld, nl, cudaMemcpyDeviceToHost, st)) != cudaSuccess) fail(e);
-  // always drain both streams before the events and the stream go away
-  if (cs != nullptr) cudaStreamSynchronize(cs);
+  cudaError_t e = cudaMemcpyAsync(xd, x_host, nx, cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  const int s = cssm_simple_forward(d, w, block_desc, block_weights, block_plan, xd, ld, workspace,
+                                    base, flags, stream);
+  if (s != CSSM_OK) return s;
+  e = cudaMemcpyAsync(logits_host, ld, nl, cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   e = cudaStreamSynchronize(st);
-  if (rc == CSSM_OK && e != cudaSuccess) fail(e);
-  for (int i = 0; i <= MAXCH; ++i)
-    if (ev[i] != nullptr) cudaEventDestroy(ev[i]);
-  if (cs != nullptr) cudaStreamDestroy(cs);
-  return rc;
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  return CSSM_OK;
 }
 
 }  // extern "C"

@@ -334,9 +334,7 @@ int cssm_simple_forward(const cssm_simple_desc* d, const cssm_simple_weights* w,
 
 /* Same with x and logits in HOST memory (pinned for full copy speed): copies x to the device
  * (staging area inside the workspace: cssm_simple_host_workspace_bytes), runs the model, copies
- * the logits back and waits for the stream.  Batches of 64 or more (divisible by 4) go through
- * in four chunks whose copies run on an internal second stream (created and destroyed inside the
- * call) so that they overlap with the model of the previous chunk. */
+ * the logits back and waits for the stream. */
 size_t cssm_simple_host_workspace_bytes(const cssm_simple_desc* d, const void* block_desc);
 int cssm_simple_forward_host(const cssm_simple_desc* d, const cssm_simple_weights* w,
                              const void* block_desc, const void* block_weights,
