@@ -48,10 +48,11 @@ struct StemArgs {
 //   POOL = 1: lane = g | pixel << 2              (8 pixels per warp, 64 per CTA)
 // CIN > 0: compile-time input channel count (the tap loops unroll fully, so all input loads of
 // a pixel are in flight together); CIN = 0: run-time a.Cin.
-template <int KS, int POOL, int CIN>
+// FULLC: C == 64, every lane's four channel groups are live (no run-time group checks).
+template <int KS, int POOL, int CIN, bool FULLC>
 __global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs a) {
   extern __shared__ __align__(16) float sm[];
-  const int C = a.C, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int C = FULLC ? SM_MAXC : a.C, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Cin = CIN > 0 ? CIN : a.Cin;
   const int nw = KS * KS * Cin * C;
   float* wsm = sm;                                   // [tap][ci][C] when w_in_smem
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs
   }
   __syncthreads();
   const float* wsrc = a.w_in_smem ? wsm : a.wk;
-  const int g = lane & 3, ngrp = C >> 2;
+  const int g = lane & 3, ngrp = FULLC ? SM_MAXC / 4 : C >> 2;
   const long long total = (long long)a.N * a.Ho * a.Wo;
   constexpr int WARPS = STEM_THREADS / 32;
   const int dq = POOL == 2 ? (lane >> 2) & 3 : 0;
@@ -173,12 +174,12 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs
   }
 }
 
-template <int KS, int POOL, int CIN>
-static int launch_stem_layer_cin(StemArgs a, cudaStream_t st) {
+template <int KS, int POOL, int CIN, bool FULLC>
+static int launch_stem_layer_v(StemArgs a, cudaStream_t st) {
   const size_t wbytes = (size_t)KS * KS * a.Cin * a.C * sizeof(float);
   a.w_in_smem = wbytes <= 160 * 1024 ? 1 : 0;
   const size_t smem = (a.w_in_smem ? wbytes : 0) + 3 * (size_t)a.C * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(stem_layer_kernel<KS, POOL, CIN>,
+  cudaError_t e = cudaFuncSetAttribute(stem_layer_kernel<KS, POOL, CIN, FULLC>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const long long total = (long long)a.N * a.Ho * a.Wo;
@@ -186,8 +187,14 @@ static int launch_stem_layer_cin(StemArgs a, cudaStream_t st) {
   const long long need = (total + per_cta - 1) / per_cta;
   // a few resident waves of CTAs that loop, so that the per-CTA weight staging is amortised
   const unsigned grid = (unsigned)(need < 148 * 16 ? need : 148 * 16);
-  stem_layer_kernel<KS, POOL, CIN><<<grid, STEM_THREADS, smem, st>>>(a);
+  stem_layer_kernel<KS, POOL, CIN, FULLC><<<grid, STEM_THREADS, smem, st>>>(a);
   return check_launch();
+}
+
+template <int KS, int POOL, int CIN>
+static int launch_stem_layer_cin(const StemArgs& a, cudaStream_t st) {
+  return a.C == SM_MAXC ? launch_stem_layer_v<KS, POOL, CIN, true>(a, st)
+                        : launch_stem_layer_v<KS, POOL, CIN, false>(a, st);
 }
 
 template <int KS, int POOL>
