@@ -1,6 +1,7 @@
 // extern "C" entry points of the gated (GatedCSSM) block and the shared error plumbing.
 #include <string.h>
 #include <stdio.h>
+#include <cuda_bf16.h>
 #include "kernels.cuh"
 #include "gemm_simt.cuh"
 
@@ -298,6 +299,78 @@ int cssm_gated_forward_last(const cssm_gated_desc* d, const cssm_gated_weights* 
                             const float* x, float* y_last, void* workspace, size_t workspace_bytes,
                             void* stream) {
   return gated_forward_internal(d, w, plan, x, y_last, workspace, workspace_bytes, stream, 1, 0);
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------ bf16 activations ----
+namespace cssm {
+// 8 elements per thread; n8 = number of 8-element groups, tail handled by the last threads
+__global__ void __launch_bounds__(256) bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in,
+                                                          float* __restrict__ out, size_t n) {
+  const size_t i = ((size_t)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (i + 8 <= n) {
+    const uint4 v = *reinterpret_cast<const uint4*>(in + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float4 a, b;
+    float2 t;
+    t = __bfloat1622float2(h[0]); a.x = t.x; a.y = t.y;
+    t = __bfloat1622float2(h[1]); a.z = t.x; a.w = t.y;
+    t = __bfloat1622float2(h[2]); b.x = t.x; b.y = t.y;
+    t = __bfloat1622float2(h[3]); b.z = t.x; b.w = t.y;
+    *reinterpret_cast<float4*>(out + i) = a;
+    *reinterpret_cast<float4*>(out + i + 4) = b;
+  } else {
+    for (size_t j = i; j < n; ++j) out[j] = __bfloat162float(in[j]);
+  }
+}
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ in,
+                                                          __nv_bfloat16* __restrict__ out, size_t n) {
+  const size_t i = ((size_t)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (i + 8 <= n) {
+    const float4 a = *reinterpret_cast<const float4*>(in + i);
+    const float4 b = *reinterpret_cast<const float4*>(in + i + 4);
+    __nv_bfloat162 h[4];
+    h[0] = __floats2bfloat162_rn(a.x, a.y); h[1] = __floats2bfloat162_rn(a.z, a.w);
+    h[2] = __floats2bfloat162_rn(b.x, b.y); h[3] = __floats2bfloat162_rn(b.z, b.w);
+    *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<const uint4*>(h);
+  } else {
+    for (size_t j = i; j < n; ++j) out[j] = __float2bfloat16_rn(in[j]);
+  }
+}
+}  // namespace cssm
+
+extern "C" {
+
+size_t cssm_gated_bf16_workspace_bytes(const cssm_gated_desc* d) {
+  const size_t base = cssm_gated_workspace_bytes(d);
+  if (base == 0) return 0;
+  const size_t act = round_up((size_t)d->B * d->T * d->H * d->W * d->C * sizeof(float), 256);
+  return base + 2 * act;
+}
+
+int cssm_gated_forward_bf16(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
+                            const void* x_bf16, void* y_bf16, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  const size_t base = cssm_gated_workspace_bytes(d);
+  if (base == 0) return validate(d) != CSSM_OK ? validate(d) : CSSM_ERR_DIMS;
+  if (!x_bf16 || !y_bf16 || !workspace) return CSSM_ERR_NULL;
+  if (!aligned16(x_bf16) || !aligned16(y_bf16) || !aligned16(workspace)) return CSSM_ERR_ALIGN;
+  if (workspace_bytes < cssm_gated_bf16_workspace_bytes(d)) return CSSM_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n = (size_t)d->B * d->T * d->H * d->W * d->C;
+  const size_t act = round_up(n * sizeof(float), 256);
+  char* ws = (char*)workspace;
+  float* xf = (float*)(ws + base);
+  float* yf = (float*)(ws + base + act);
+  const unsigned grid = (unsigned)((n + 2047) / 2048);
+  bf16_to_f32_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x_bf16, xf, n);
+  int s = check_launch();
+  if (s != CSSM_OK) return s;
+  s = gated_forward_internal(d, w, plan, xf, yf, workspace, base, stream, 0, 0);
+  if (s != CSSM_OK) return s;
+  f32_to_bf16_kernel<<<grid, 256, 0, st>>>(yf, (__nv_bfloat16*)y_bf16, n);
+  return check_launch();
 }
 
 }  // extern "C"

@@ -32,11 +32,11 @@ def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _require_cuda(x):
+def _require_cuda(x, allow_bf16=False):
     if not isinstance(x, torch.Tensor) or not x.is_cuda:
         raise TypeError("x must be a CUDA torch.Tensor (use forward_host for host arrays); "
                         "cssm_b200 has no CPU path")
-    if x.dtype != torch.float32:
+    if x.dtype != torch.float32 and not (allow_bf16 and x.dtype == torch.bfloat16):
         raise TypeError(f"x must be float32, got {x.dtype}")
 
 
@@ -153,7 +153,7 @@ class GatedCSSM:
         key = id(variables)
         bound = self._bound.get(key)
         if bound is None or bound.variables_ref is not variables:
-            _require_cuda(x)
+            _require_cuda(x, allow_bf16=True)
             bound = self.bind(variables, x.device)
             bound.variables_ref = variables
             self._bound.clear()
@@ -225,11 +225,23 @@ class BoundGated:
                  last_frame_only: bool = False) -> torch.Tensor:
         """y = block(x).  With last_frame_only=True returns block(x)[:, -1] of shape (B,H,W,C)
         without computing the earlier output frames (for callers that read only the final
-        frame, as SimpleCSSM with frame_readout='last' and CSSMSHViTBlock do)."""
-        _require_cuda(x)
+        frame, as SimpleCSSM with frame_readout='last' and CSSMSHViTBlock do).  A bfloat16 x
+        (the SHViT mixers run in a bf16 model) is widened to fp32, as Flax promotion does with
+        the block's fp32 parameters, and the result comes back in bfloat16."""
+        _require_cuda(x, allow_bf16=True)
         x = x.contiguous()
         d = self.desc(tuple(x.shape))
         pl = self.plan(d)
+        if x.dtype == torch.bfloat16:
+            if last_frame_only:
+                raise NotImplementedError("GatedCSSM: last_frame_only with bfloat16 activations")
+            n = self.L.cssm_gated_bf16_workspace_bytes(C.byref(d))
+            ws = self.buf.get("ws", n)
+            y = torch.empty_like(x) if out is None else out
+            check(self.L.cssm_gated_forward_bf16(C.byref(d), C.byref(self.w), pl.data_ptr(),
+                                                 x.data_ptr(), y.data_ptr(), ws.data_ptr(), n,
+                                                 _stream_ptr(self.device)), "cssm_gated_forward_bf16")
+            return y
         n = self.L.cssm_gated_workspace_bytes(C.byref(d))
         ws = self.buf.get("ws", n)
         if last_frame_only:

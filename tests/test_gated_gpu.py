@@ -197,3 +197,33 @@ def test_last_frame_only_matches_full_forward(case):
     assert _tc_error(bound.L) == 0
     assert torch.equal(last, full[:, -1])
     assert orc.rel_l2(last.cpu().numpy(), ref[:, -1]) <= TOL
+
+
+@pytest.mark.parametrize("case", [
+    (4, 1, 14, 14, 256),      # SHViT-s1 stage 2 mixer shape (batch reduced)
+    (4, 1, 7, 7, 384),        # stage 3
+    (2, 4, 64, 64, 64),       # bf16 activations through the radix kernel and tensor-core projections
+], ids=lambda c: "x".join(map(str, c)))
+def test_bf16_activations(case):
+    """bfloat16 x and y with fp32 weights (the SHViT configuration: kernel_size 1, factored gates,
+    no spatial short conv, temporal conv 4, no RoPE).  Checked against the fp64 oracle on the SAME
+    bf16-rounded input; tolerance rel-L2 <= 2e-2 (the bf16 tolerance; the only bf16 rounding here
+    is that of the output)."""
+    B, T, H, W, C = case
+    rng = np.random.default_rng(5)
+    xb = torch.from_numpy(rng.standard_normal((B, T, H, W, C)).astype(np.float32)).to(torch.bfloat16)
+    x = xb.to(torch.float32).numpy()
+    p = orc.init_gated_params(6, C, H, W, kernel_size=1, gate_type="factored", short_conv_size=4,
+                              short_conv_spatial_size=0, bias_scale=0.1)
+    kw = dict(kernel_size=1, rope_mode="none", gate_type="factored", short_conv_size=4,
+              short_conv_spatial_size=0)
+    ref = orc.gated_forward(p, x, **kw)
+    mod = GatedCSSM(channels=C, kernel_size=1, rope_mode="none", gate_type="factored",
+                    short_conv_size=4, short_conv_spatial_size=0)
+    y = mod.apply({"params": p}, xb.cuda())
+    assert y.dtype == torch.bfloat16 and y.shape == xb.shape
+    err = orc.rel_l2(y.to(torch.float32).cpu().numpy(), ref)
+    assert err <= 2e-2
+    # and the same block on the widened input agrees to fp32 accuracy before the output rounding
+    y32 = mod.apply({"params": p}, xb.to(torch.float32).cuda()).cpu().numpy()
+    assert orc.rel_l2(y32, ref) <= TOL
