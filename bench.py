@@ -56,6 +56,9 @@ WORKLOADS = {
     "cfg3_small": dict(model=dict(_GDN, kernel_size=11, qkv_conv_size=5, seq_len=8, stem_layers=1,
                                   pool_type="max", pos_embed="mrope"),
                        B=8, data="strokes"),
+    "cfg4_small": dict(model=dict(_GDN, kernel_size=11, qkv_conv_size=1, stem_mode="pathtracker",
+                                  pool_type="max", pos_embed="spatiotemporal"),
+                       B=8, data="dots"),
     # BASELINE.json configs[3]: GDN-SCSSM video, T=32 native 32x32x3 frames, last-frame readout
     "cfg4": dict(model=dict(_GDN, kernel_size=11, qkv_conv_size=1, stem_mode="pathtracker",
                             pool_type="max", pos_embed="spatiotemporal"),
