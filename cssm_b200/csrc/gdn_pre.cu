@@ -12,11 +12,22 @@ namespace cssm {
 // the block input, cssm.py:4785-4786), not of the conv output.
 constexpr int DW_ROWS = 8, DW_THREADS = 256;
 
+// Position of (padded column col, channel c) inside a staged row.  With 16 channels per pixel two
+// pixels share a 32-float line; the halves swap with bit 2 of the column, so that the two
+// half-warps of a window read (columns col and col + 4, same channels) hit different banks.
+template <int DW_CG>
+__device__ __forceinline__ int dw_pos(int col, int c) {
+  if (DW_CG == 16) return ((col >> 1) << 5) + ((((col & 1) ^ ((col >> 2) & 1))) << 4) + c;
+  return col * DW_CG + c;
+}
+
 template <int K, int DW_CG>
-__global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwArgs a) {
+__global__ void __launch_bounds__(DW_THREADS, (K <= 5 ? 3 : 2)) rope_dwconv_cl_kernel(const GdnDwArgs a) {
   extern __shared__ __align__(16) float sm[];
   constexpr int LO = (K - 1) / 2, NR = DW_ROWS + K - 1;
   const int W = a.W, C = a.C, n2 = C / 2;
+  const int WP = (W + K - 1 + 1) & ~1;                 // padded columns per staged row (even)
+  const int rpitch = WP * DW_CG;                        // floats per staged row
   const int bands = (a.H + DW_ROWS - 1) / DW_ROWS, cgs = C / DW_CG;
   int bid = blockIdx.x;
   const int cg = bid % cgs; bid /= cgs;
@@ -25,24 +36,43 @@ __global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwA
   const int t = fr % a.T, h0 = band * DW_ROWS, c0 = cg * DW_CG;
   const int fsrc = a.x_bcast ? fr / a.T : fr;
   const int tid = threadIdx.x;
-  // ---- stage rows h0-LO .. h0+DW_ROWS-1+(K-1-LO), 16 channels, rotated ----
-  const int pairs_per_row = W * (DW_CG / 2);
-  for (int i = tid; i < NR * pairs_per_row; i += DW_THREADS) {
-    const int r = i / pairs_per_row, rem = i - r * pairs_per_row;
-    const int w = rem / (DW_CG / 2), pl = rem % (DW_CG / 2);
+  // ---- zero the pad columns (left LO, right up to WP) of every staged row ----
+  for (int i = tid; i < NR * (WP - W) * DW_CG; i += DW_THREADS) {
+    const int r = i / ((WP - W) * DW_CG), rem = i - r * (WP - W) * DW_CG;
+    const int pc = rem / DW_CG, c = rem - pc * DW_CG;
+    const int col = pc < LO ? pc : W + pc;               // 0..LO-1, then W+LO..WP-1
+    sm[r * rpitch + dw_pos<DW_CG>(col, c)] = 0.f;
+  }
+  // ---- stage rows h0-LO .. h0+DW_ROWS-1+(K-1-LO), DW_CG channels, rotated ----
+  // DW_THREADS is a multiple of the pairs per pixel, so a thread keeps its channel pair: the
+  // t part of the angle is loaded once, the h part once per row, the w part per element.
+  constexpr int PP = DW_CG / 2;                         // pairs per pixel in this channel group
+  const int pl = tid % PP, pi = c0 / 2 + pl;
+  const bool rope = a.rope_t != nullptr;
+  float2 ct = make_float2(1.f, 0.f);
+  if (rope) ct = a.rope_t[t * n2 + pi];
+  for (int r = 0; r < NR; ++r) {
     const int hh = h0 + r - LO;
-    float2 v = make_float2(0.f, 0.f);
-    if (hh >= 0 && hh < a.H) {
-      v = *reinterpret_cast<const float2*>(a.x + (((size_t)fsrc * a.H + hh) * W + w) * C + c0 + 2 * pl);
-      if (a.rope_t != nullptr) {
-        const int pi = c0 / 2 + pl;
-        const float2 ct = a.rope_t[t * n2 + pi], ch = a.rope_h[hh * n2 + pi], cw = a.rope_w[w * n2 + pi];
-        const float cx = ct.x * ch.x - ct.y * ch.y, sx = ct.x * ch.y + ct.y * ch.x;
-        const float c2 = cx * cw.x - sx * cw.y, s2 = cx * cw.y + sx * cw.x;
-        v = make_float2(v.x * c2 - v.y * s2, v.x * s2 + v.y * c2);
-      }
+    const bool rin = hh >= 0 && hh < a.H;
+    float cth = 1.f, sth = 0.f;
+    if (rope && rin) {
+      const float2 ch = a.rope_h[hh * n2 + pi];
+      cth = ct.x * ch.x - ct.y * ch.y; sth = ct.x * ch.y + ct.y * ch.x;
     }
-    *reinterpret_cast<float2*>(sm + ((size_t)r * W + w) * DW_CG + 2 * pl) = v;
+    const float* xr = a.x + (((size_t)fsrc * a.H + (rin ? hh : 0)) * W) * C + c0 + 2 * pl;
+    float* srow = sm + r * rpitch;
+    for (int w = tid / PP; w < W; w += DW_THREADS / PP) {
+      float2 v = make_float2(0.f, 0.f);
+      if (rin) {
+        v = __ldg(reinterpret_cast<const float2*>(xr + (size_t)w * C));
+        if (rope) {
+          const float2 cw = __ldg(&a.rope_w[w * n2 + pi]);
+          const float c2 = cth * cw.x - sth * cw.y, s2 = cth * cw.y + sth * cw.x;
+          v = make_float2(v.x * c2 - v.y * s2, v.x * s2 + v.y * c2);
+        }
+      }
+      *reinterpret_cast<float2*>(srow + dw_pos<DW_CG>(w + LO, 2 * pl)) = v;
+    }
   }
   __syncthreads();
   // ---- context partial sums of the centre rows ----
@@ -50,7 +80,8 @@ __global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwA
     const int r = tid / DW_CG, c = tid % DW_CG;
     if (h0 + r < a.H) {
       float s = 0.f;
-      for (int w = 0; w < W; ++w) s += sm[((size_t)(r + LO) * W + w) * DW_CG + c];
+      const float* srow = sm + (r + LO) * rpitch;
+      for (int w = 0; w < W; ++w) s += srow[dw_pos<DW_CG>(w + LO, c)];
       a.ctx_part[((size_t)fr * a.H + h0 + r) * C + c0 + c] = s;
     }
   }
@@ -68,14 +99,16 @@ __global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwA
     for (int r = 0; r < DW_ROWS; ++r)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[r][j] = bias;
+    // offsets of the window's padded columns w0 .. w0+K+2 inside a staged row (same for all rows)
+    int off[4 + K - 1];
+#pragma unroll
+    for (int j = 0; j < 4 + K - 1; ++j) off[j] = dw_pos<DW_CG>(min(w0 + j, WP - 1), c);
 #pragma unroll
     for (int ir = 0; ir < NR; ++ir) {
+      const float* srow = sm + ir * rpitch;
       float win[4 + K - 1];
 #pragma unroll
-      for (int j = 0; j < 4 + K - 1; ++j) {
-        const int ww = w0 + j - LO;
-        win[j] = (ww >= 0 && ww < W) ? sm[((size_t)ir * W + ww) * DW_CG + c] : 0.f;
-      }
+      for (int j = 0; j < 4 + K - 1; ++j) win[j] = srow[off[j]];   // pad columns hold zeros
       // input row ir feeds output row r = ir - di for tap row di
 #pragma unroll
       for (int di = 0; di < K; ++di) {
@@ -89,20 +122,56 @@ __global__ void __launch_bounds__(DW_THREADS) rope_dwconv_cl_kernel(const GdnDwA
         }
       }
     }
+    float* orow = a.out + (((size_t)fr * a.H + h0) * W + w0) * C + c0 + c;
 #pragma unroll
     for (int r = 0; r < DW_ROWS; ++r) {
       if (h0 + r >= a.H) continue;
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        if (w0 + j < W)
-          a.out[(((size_t)fr * a.H + h0 + r) * W + w0 + j) * C + c0 + c] = acc[r][j];
+        if (w0 + j < W) orow[((size_t)r * W + j) * C] = acc[r][j];
     }
+  }
+}
+
+// ------------------------------------------- context row sums without a conv (K = 1) ----
+// ctx_part[(frame, h, c)] = sum over w of the rotated input.  One warp per image row: a lane
+// owns channel pairs lane, lane + 32, ... and walks the row, so every load is a coalesced
+// C*4-byte line and no cross-lane reduction is needed.  The t and h parts of the angle are
+// combined once per row, the w part comes from the table per element.
+constexpr int CTX_WARPS = 8;
+__global__ void __launch_bounds__(CTX_WARPS * 32) rope_ctx_rowsum_kernel(const GdnDwArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long row = (long long)blockIdx.x * CTX_WARPS + warp;        // (frame, h)
+  if (row >= (long long)a.BT * a.H) return;
+  const int fr = (int)(row / a.H), h = (int)(row % a.H);
+  const int t = fr % a.T, n2 = a.C / 2;
+  const int fsrc = a.x_bcast ? fr / a.T : fr;
+  const float* xr = a.x + ((size_t)fsrc * a.H + h) * a.W * a.C;
+  for (int pi = lane; pi < n2; pi += 32) {
+    float cth = 1.f, sth = 0.f;
+    if (a.rope_t != nullptr) {
+      const float2 ct = a.rope_t[t * n2 + pi], ch = a.rope_h[h * n2 + pi];
+      cth = ct.x * ch.x - ct.y * ch.y; sth = ct.x * ch.y + ct.y * ch.x;
+    }
+    float se = 0.f, so = 0.f;
+#pragma unroll 4
+    for (int w = 0; w < a.W; ++w) {
+      const float2 v = __ldg(reinterpret_cast<const float2*>(xr + (size_t)w * a.C + 2 * pi));
+      if (a.rope_t != nullptr) {
+        const float2 cw = __ldg(&a.rope_w[w * n2 + pi]);
+        const float c2 = cth * cw.x - sth * cw.y, s2 = cth * cw.y + sth * cw.x;
+        se += v.x * c2 - v.y * s2; so += v.x * s2 + v.y * c2;
+      } else {
+        se += v.x; so += v.y;
+      }
+    }
+    *reinterpret_cast<float2*>(a.ctx_part + (size_t)row * a.C + 2 * pi) = make_float2(se, so);
   }
 }
 
 template <int K, int DW_CG>
 static int launch_dw_cg(const GdnDwArgs& a, cudaStream_t st) {
-  const size_t smem = (size_t)(DW_ROWS + K - 1) * a.W * DW_CG * sizeof(float);
+  const size_t smem = (size_t)(DW_ROWS + K - 1) * ((a.W + K - 1 + 1) & ~1) * DW_CG * sizeof(float);
   if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(rope_dwconv_cl_kernel<K, DW_CG>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -120,6 +189,12 @@ static int launch_dw(const GdnDwArgs& a, cudaStream_t st) {
 
 int launch_rope_dwconv_cl(const GdnDwArgs& a, cudaStream_t st) {
   if (a.C % 4 != 0) return CSSM_ERR_UNSUPPORTED;
+  if (a.ksz <= 1 && a.out == nullptr) {
+    if (a.ctx_part == nullptr) return CSSM_OK;
+    const long long rows = (long long)a.BT * a.H;
+    rope_ctx_rowsum_kernel<<<(unsigned)((rows + CTX_WARPS - 1) / CTX_WARPS), CTX_WARPS * 32, 0, st>>>(a);
+    return check_launch();
+  }
   switch (a.ksz > 1 ? a.ksz : 1) {
     case 1: return launch_dw<1>(a, st);
     case 3: return launch_dw<3>(a, st);
