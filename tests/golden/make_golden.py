@@ -9,6 +9,7 @@ import os
 import numpy as np
 
 from oracle import cssm_oracle as orc
+from oracle import simple_oracle as so
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -39,6 +40,38 @@ def gdn_case():
     return x, p, kw
 
 
+SIMPLE_KW = dict(kernel_size=5, rope_mode="spatiotemporal", gate_type="factored", short_conv_size=4,
+                 short_conv_spatial_size=3)
+
+
+def simple_case():
+    """SimpleCSSM (one stem layer, gated block, max-pool head) on 3 images of 16x16."""
+    x = np.random.default_rng(41).random((3, 16, 16, 1)).astype(np.float32)
+    p = so.init_simple_params(42, cin=1, embed_dim=8, H=8, W=8, stem_layers=1, bias_scale=0.1,
+                              block_kwargs=SIMPLE_KW)
+    return x, p
+
+
+def nogate_case():
+    B, T, H, W, C, ks = 2, 4, 8, 8, 8, 3
+    rng = np.random.default_rng(51)
+    x = rng.standard_normal((B, T, H, W, C)).astype(np.float32)
+    p = {"kernel": (0.3 * rng.standard_normal((C, ks, ks))).astype(np.float32),
+         "out_proj": {"kernel": (rng.standard_normal((C, C)) / np.sqrt(C)).astype(np.float32),
+                      "bias": (0.1 * rng.standard_normal(C)).astype(np.float32)}}
+    return x, p, ks
+
+
+def gdn_static_case():
+    B, H, W, C, ks, T = 2, 8, 8, 8, 5, 4
+    x = np.random.default_rng(61).standard_normal((B, H, W, C)).astype(np.float32)
+    p = orc.init_gdn_params(62, C, H, W, delta_key_dim=4, kernel_size=ks, gate_type="factored",
+                            short_conv_size=0, qkv_conv_size=3, use_input_gates=False,
+                            bias_scale=0.1, perturb_rms=True)
+    kw = dict(num_timesteps=T, delta_key_dim=4, kernel_size=ks, gate_type="factored", qkv_conv_size=3)
+    return x, p, kw
+
+
 def main():
     x, p, kw = gated_case()
     np.savez_compressed(os.path.join(HERE, "gated_small.npz"), x=x,
@@ -49,6 +82,16 @@ def main():
     x, p, kw = gdn_case()
     np.savez_compressed(os.path.join(HERE, "gdn_small.npz"), x=x,
                         y=orc.gdn_forward(p, x, **kw).astype(np.float64))
+    x, p = simple_case()
+    np.savez_compressed(os.path.join(HERE, "simple_small.npz"), x=x,
+                        y=so.simple_forward(p, x, seq_len=3, stem_layers=1, pool_type="max",
+                                            block_kwargs=SIMPLE_KW).astype(np.float64))
+    x, p, ks = nogate_case()
+    np.savez_compressed(os.path.join(HERE, "nogate_small.npz"), x=x,
+                        y=orc.nogate_forward(p, x, kernel_size=ks).astype(np.float64))
+    x, p, kw = gdn_static_case()
+    np.savez_compressed(os.path.join(HERE, "gdn_static_small.npz"), x=x,
+                        y=orc.gdn_static_forward(p, x, **kw).astype(np.float64))
 
 
 if __name__ == "__main__":

@@ -140,3 +140,17 @@ def test_static_image_preconditions():
     with pytest.raises(AssertionError):
         GatedDeltaNetCSSM(channels=8, delta_key_dim=4, static_image_fast_path=True, num_timesteps=0,
                           short_conv_size=0, use_input_gates=False, gate_type="factored").bind({"params": {}})
+
+
+def test_static_image_golden_fixture_on_gpu():
+    """The committed fixture of the static-image path (tests/golden/gdn_static_small.npz)."""
+    import os
+    from tests.golden import make_golden as mg
+    g = np.load(os.path.join(os.path.dirname(mg.__file__), "gdn_static_small.npz"))
+    _, p, kw = mg.gdn_static_case()
+    mod = GatedDeltaNetCSSM(channels=g["x"].shape[-1], delta_key_dim=4, kernel_size=kw["kernel_size"],
+                            rope_mode="none", gate_type="factored", short_conv_size=0,
+                            qkv_conv_size=kw["qkv_conv_size"], use_input_gates=False,
+                            static_image_fast_path=True, num_timesteps=kw["num_timesteps"])
+    y = mod.apply({"params": p}, torch.from_numpy(g["x"]).cuda()).cpu().numpy()
+    assert orc.rel_l2(y, g["y"]) <= 2e-2

@@ -45,3 +45,14 @@ def test_recurrence_carries_state():
     y = mod.apply({"params": p}, torch.from_numpy(x).cuda()).cpu().numpy()
     assert np.abs(ref[:, 2]).max() > 1e-3
     assert orc.rel_l2(y, ref) <= TOL
+
+
+def test_golden_fixture_on_gpu():
+    """The committed fixture (tests/golden/nogate_small.npz, written by make_golden.py)."""
+    import os
+    from tests.golden import make_golden as mg
+    g = np.load(os.path.join(os.path.dirname(mg.__file__), "nogate_small.npz"))
+    _, p, ks = mg.nogate_case()
+    y = NoGateCSSM(channels=g["x"].shape[-1], kernel_size=ks).apply(
+        {"params": p}, torch.from_numpy(g["x"]).cuda()).cpu().numpy()
+    assert orc.rel_l2(y, g["y"]) <= TOL

@@ -228,3 +228,23 @@ def test_bf16_round_matches_torch():
     a = (np.random.default_rng(0).standard_normal(4096) * 3).astype(np.float32)
     ref = torch.from_numpy(a).to(torch.bfloat16).to(torch.float32).numpy()
     assert np.array_equal(orc.bf16_round(a), ref)
+
+
+def test_golden_vectors_of_the_widened_paths():
+    """Committed fixtures of the SimpleCSSM model, NoGateCSSM and the GDN static-image path
+    (tests/golden/make_golden.py) pin the oracle against drift."""
+    from oracle import simple_oracle as so
+    from tests.golden import make_golden as mg
+    g = np.load(os.path.join(GOLDEN, "simple_small.npz"))
+    x, p = mg.simple_case()
+    assert np.array_equal(x, g["x"])
+    y = so.simple_forward(p, x, seq_len=3, stem_layers=1, pool_type="max", block_kwargs=mg.SIMPLE_KW)
+    assert orc.rel_l2(y, g["y"]) < 1e-12
+    g = np.load(os.path.join(GOLDEN, "nogate_small.npz"))
+    x, p, ks = mg.nogate_case()
+    assert np.array_equal(x, g["x"])
+    assert orc.rel_l2(orc.nogate_forward(p, x, kernel_size=ks), g["y"]) < 1e-12
+    g = np.load(os.path.join(GOLDEN, "gdn_static_small.npz"))
+    x, p, kw = mg.gdn_static_case()
+    assert np.array_equal(x, g["x"])
+    assert orc.rel_l2(orc.gdn_static_forward(p, x, **kw), g["y"]) < 1e-12

@@ -82,3 +82,15 @@ def test_unsupported_fields_raise():
         SimpleCSSM(cssm_type="hgru_bi").bind({"params": {}})
     with pytest.raises(NotImplementedError):
         SimpleCSSM(cssm_type="gated", embed_dim=128).bind({"params": {}})
+
+
+def test_golden_fixture_on_gpu():
+    """The committed model fixture (tests/golden/simple_small.npz, written by make_golden.py)."""
+    import os
+    from tests.golden import make_golden as mg
+    g = np.load(os.path.join(os.path.dirname(mg.__file__), "simple_small.npz"))
+    _, p = mg.simple_case()
+    m = SimpleCSSM(cssm_type="gated", embed_dim=8, kernel_size=5, pos_embed="spatiotemporal",
+                   gate_type="factored", seq_len=3, stem_layers=1, pool_type="max")
+    logits = m.apply({"params": p}, torch.from_numpy(g["x"]).cuda()).cpu().numpy()
+    assert orc.rel_l2(logits, g["y"]) <= TOL
