@@ -418,11 +418,15 @@ def main():
                 "frac_of_nominal_8TBps": achieved / 8000.0, "traffic": None,
                 "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": stage_ms["spectral"]}
     tr = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tr) and kname == "gated_spectral_r64":
+    if os.path.exists(tr):
+        # DRAM bytes per unit from the committed ncu captures on the small workloads, scaled by
+        # the units of this launch (traffic is proportional to them)
         with open(tr) as f:
-            per_plane_step = json.load(f).get("gated_spectral_r64_dram_bytes_per_plane_step")
-        if per_plane_step:
-            roofline["traffic"] = per_plane_step * B * T * Cc
+            tj = json.load(f)
+        if kname == "gated_spectral_r64" and tj.get("gated_spectral_r64_dram_bytes_per_plane_step"):
+            roofline["traffic"] = tj["gated_spectral_r64_dram_bytes_per_plane_step"] * B * T * Cc
+        elif gdn and tj.get(f"{kname}_dram_bytes_per_head_step"):
+            roofline["traffic"] = tj[f"{kname}_dram_bytes_per_head_step"] * B * T * (Cc // model.delta_key_dim)
 
     # ---- end to end: pinned host images -> host logits through the host-buffer entry point ----
     e2e = None

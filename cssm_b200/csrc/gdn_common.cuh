@@ -115,9 +115,4 @@ __device__ __forceinline__ cf gdn_bin_static(const cf* kk, const cf* qq, cf vv, 
   return o;
 }
 
-__device__ __forceinline__ cf gdn_bin_update_r64(cf* S, size_t ss, const cf* kk, const cf* qq, cf vv,
-                                                 cf aw, float beta) {
-  return gdn_bin_update_t<4>(S, ss, kk, qq, vv, aw, beta);
-}
-
 }  // namespace cssm

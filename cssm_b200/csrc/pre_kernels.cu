@@ -198,12 +198,12 @@ __global__ void __launch_bounds__(ST_THREADS) plane_stencil_kernel(const Stencil
 #pragma unroll
         for (int j = 0; j < kt - 1; ++j) {
           const int f = t - (kt - 1) + j;
-          if (f >= 0) o = fmaf(wt[j], hist[(f % nh) * HW + i], o);
+          if (f >= 0) o = fmaf(wt[j], hist[(f % (nh > 0 ? nh : 1)) * HW + i], o);
         }
       }
       // each thread owns pixel i in every pass, so the ring can be updated in place:
       // slot t % nh holds s_{t-nh}, which tap 0 has just consumed
-      if (nh > 0) hist[(t % nh) * HW + i] = v;
+      if (nh > 0) hist[(t % (nh > 0 ? nh : 1)) * HW + i] = v;
       if (s.act) o = silu_f(o);
       if (s.post) o *= s.post[(frame * HW + i) * s.post_stride + s.post_off];
       p[i] = o;
