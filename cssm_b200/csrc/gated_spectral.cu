@@ -293,6 +293,122 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
   }
 }
 
+// ================================================================ small planes ====
+// Planes of at most 16 x 16 pixels (the 14 x 14 and 7 x 7 stages of the SHViT backbone): one
+// WARP per (batch, channel) plane, eight planes in flight per CTA, CTAs loop over the planes.
+// Same direct-DFT arithmetic as the generic kernel, synchronised with __syncwarp() only, and the
+// twiddle tables are built once per CTA instead of once per plane.
+constexpr int SMALL_WARPS = 8, SMALL_MAX_HW = 256;
+
+__global__ void __launch_bounds__(SMALL_WARPS * 32)
+gated_spectral_small(float* __restrict__ xz, const cf* __restrict__ khat,
+                     const float4* __restrict__ gates, int nplanes, int T, int C, int H, int W,
+                     int last_only, int nog) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int Wf = W / 2 + 1, HW = H * W, NB = H * Wf;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  cf* twW = reinterpret_cast<cf*>(smem_raw);                   // [W]  e^{-2 pi i k/W}
+  cf* twH = twW + W;                                           // [H]
+  const int per_warp = ((HW + 1) & ~1) / 2 + 3 * NB;           // in cf units: xs, Rb, Fb, St
+  cf* mine = twH + H + (size_t)warp * per_warp;
+  float* xs = reinterpret_cast<float*>(mine);                  // [H][W]
+  cf* Rb = mine + ((HW + 1) & ~1) / 2;                         // [H][Wf]
+  cf* Fb = Rb + NB;
+  cf* St = Fb + NB;
+  for (int i = threadIdx.x; i < W; i += SMALL_WARPS * 32) {
+    float s, co; sincospif(-2.0f * (float)i / (float)W, &s, &co); twW[i] = mk(co, s);
+  }
+  for (int i = threadIdx.x; i < H; i += SMALL_WARPS * 32) {
+    float s, co; sincospif(-2.0f * (float)i / (float)H, &s, &co); twH[i] = mk(co, s);
+  }
+  __syncthreads();
+  const float invHW = 1.0f / (float)HW;
+  const int kmax = (W - 1) / 2;
+  for (int plane = blockIdx.x * SMALL_WARPS + warp; plane < nplanes; plane += gridDim.x * SMALL_WARPS) {
+    const int b = plane / C, c = plane % C;
+    const cf* khc = khat + (size_t)c * NB;
+    for (int i = lane; i < NB; i += 32) St[i] = mk(0.f, 0.f);
+    for (int t = 0; t < T; ++t) {
+      const size_t frame = (size_t)(b * T + t);
+      float* xp = xz + (frame * 2 * C + c) * HW;
+      const float* zp = xp + (size_t)C * HW;
+      __syncwarp();
+      for (int i = lane; i < HW; i += 32) xs[i] = xp[i];
+      __syncwarp();
+      for (int o = lane; o < NB; o += 32) {                    // rows
+        const int h = o / Wf, kw = o - h * Wf;
+        float ax = 0.f, ay = 0.f;
+        int idx = 0;
+        for (int w = 0; w < W; ++w) {
+          const cf e = twW[idx];
+          const float xv = xs[h * W + w];
+          ax += xv * e.x; ay += xv * e.y;
+          idx += kw; if (idx >= W) idx -= W;
+        }
+        Rb[o] = mk(ax, ay);
+      }
+      __syncwarp();
+      const float4* gp = gates + frame * NB;
+      for (int o = lane; o < NB; o += 32) {                    // columns + recurrence
+        const int kh = o / Wf, kw = o - kh * Wf;
+        float ax = 0.f, ay = 0.f;
+        int idx = 0;
+        for (int h = 0; h < H; ++h) {
+          const cf e = twH[idx];
+          const cf r = Rb[h * Wf + kw];
+          ax += r.x * e.x - r.y * e.y; ay += r.x * e.y + r.y * e.x;
+          idx += kh; if (idx >= H) idx -= H;
+        }
+        const float4 g = nog ? make_float4(1.f, 1.f, invHW, 0.f) : __ldg(gp + o);
+        const cf k = khc[o];
+        const cf A = mk(k.x * g.x, k.y * g.x);
+        cf U = mk(g.y * ax, g.y * ay);
+        if (U.x * U.x + U.y * U.y < g.w * g.w) U = mk(g.w, 0.f);
+        cf hs = cmul(A, St[o]);
+        hs.x += U.x; hs.y += U.y;
+        St[o] = hs;
+        Fb[o] = mk(g.z * hs.x, g.z * hs.y);
+      }
+      if (last_only && t != T - 1) continue;                   // same for the whole warp
+      __syncwarp();
+      for (int o = lane; o < NB; o += 32) {                    // inverse columns
+        const int h = o / Wf, kw = o - h * Wf;
+        float ax = 0.f, ay = 0.f;
+        int idx = 0;
+        for (int kh = 0; kh < H; ++kh) {
+          const cf e = twH[idx];
+          const cf f = Fb[kh * Wf + kw];
+          ax += f.x * e.x + f.y * e.y; ay += f.y * e.x - f.x * e.y;
+          idx += h; if (idx >= H) idx -= H;
+        }
+        Rb[o] = mk(ax, ay);
+      }
+      __syncwarp();
+      for (int o = lane; o < HW; o += 32) {                    // inverse rows (C2R), * silu(z)
+        const int h = o / W, w = o - h * W;
+        const cf* r = Rb + h * Wf;
+        float acc = r[0].x;
+        if ((W & 1) == 0) acc += (w & 1) ? -r[W / 2].x : r[W / 2].x;
+        int idx = 0;
+        float s2 = 0.f;
+        for (int k = 1; k <= kmax; ++k) {
+          idx += w; if (idx >= W) idx -= W;
+          const cf e = twW[idx];
+          s2 += r[k].x * e.x + r[k].y * e.y;
+        }
+        acc += 2.f * s2;
+        xp[o] = nog ? acc : acc * zp[o];
+      }
+    }
+  }
+}
+
+static size_t small_smem_bytes(int H, int W) {
+  const size_t NB = (size_t)H * (W / 2 + 1), HW = (size_t)H * W;
+  const size_t per_warp = ((HW + 1) & ~(size_t)1) / 2 + 3 * NB;
+  return (W + H + SMALL_WARPS * per_warp) * sizeof(cf);
+}
+
 size_t generic_smem_bytes(int H, int W) {
   const int Wf = W / 2 + 1;
   size_t fl = ((size_t)H * W + 1) & ~(size_t)1;
@@ -350,6 +466,15 @@ int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const flo
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     kern<<<grid, R64_THREADS, smem, st>>>(xz, khat, reinterpret_cast<const float4*>(gates), d.T,
                                           d.C, pmap);
+  } else if (d.H * d.W <= SMALL_MAX_HW && !(g_spec_variant == 1)) {
+    const size_t smem = small_smem_bytes(d.H, d.W);
+    cudaError_t e = cudaFuncSetAttribute(gated_spectral_small,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+    const int need = (grid + SMALL_WARPS - 1) / SMALL_WARPS;
+    const int ctas = need < 148 * 6 ? need : 148 * 6;
+    gated_spectral_small<<<ctas, SMALL_WARPS * 32, smem, st>>>(
+        xz, khat, reinterpret_cast<const float4*>(gates), grid, d.T, d.C, d.H, d.W, last_only, nogate);
   } else {
     const size_t smem = generic_smem_bytes(d.H, d.W);
     if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
