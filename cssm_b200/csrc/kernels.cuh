@@ -23,6 +23,15 @@ struct StencilArgs {
 };
 int launch_plane_stencil(const StencilArgs& s, cudaStream_t st);
 
+// temporal conv + SiLU (+ input gates) on the q, k, v planes of the GDN block in one launch
+struct QkvTconvArgs {
+  float* buf;                     // planar (B*T, 3C, H*W), in place
+  int B, T, C, HW, kt;
+  const float* wt[3]; const float* bt[3];   // short_conv_q/k/v: (kt,1,C), (C)
+  const float2* bkv;              // (B*T, H*W) {B_k, B_v} or nullptr (no input gates)
+};
+int launch_qkv_temporal_conv(const QkvTconvArgs& a, cudaStream_t st);   // CSSM_ERR_UNSUPPORTED: use the plane stencil
+
 struct GatedGateArgs {
   const float* ctx_sum; int BT, C, H, W, gate_type, act, path;
   const float* gk[6]; const float* gb[6];

@@ -426,6 +426,75 @@ int launch_plane_stencil(const StencilArgs& s, cudaStream_t st) {
   return go(plane_stencil_kernel<-1, -1>);
 }
 
+// ------------------------------------------- temporal conv on q, k, v (GDN) ----
+// Causal depthwise temporal conv (KT taps) + SiLU + optional per-pixel input gate on the 3C planar
+// planes of q, k and v in ONE elementwise launch: a thread owns four consecutive pixels of one
+// plane and walks t with the KT-1 previous raw values in registers and the next frame's load in
+// flight, so every plane is read once and written once at full occupancy.
+template <int KT>
+__global__ void __launch_bounds__(256) qkv_temporal_conv_kernel(const QkvTconvArgs a) {
+  const int HW4 = a.HW >> 2;
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long total = (long long)a.B * 3 * a.C * HW4;
+  if (gid >= total) return;
+  const int g4 = (int)(gid % HW4);
+  const int p = (int)((gid / HW4) % (3 * a.C));
+  const int b = (int)(gid / ((long long)HW4 * 3 * a.C));
+  const int grp = p / a.C, c = p - grp * a.C;
+  const float* wtp = grp == 0 ? a.wt[0] : grp == 1 ? a.wt[1] : a.wt[2];
+  const float* btp = grp == 0 ? a.bt[0] : grp == 1 ? a.bt[1] : a.bt[2];
+  float w[KT];
+#pragma unroll
+  for (int j = 0; j < KT; ++j) w[j] = wtp[(size_t)j * a.C + c];
+  const float bias = btp[c];
+  const int poff = grp - 1;                                   // k: B_k, v: B_v, q: none
+  const bool gated = a.bkv != nullptr && grp > 0;
+  float4 hist[KT - 1];
+#pragma unroll
+  for (int k = 0; k < KT - 1; ++k) hist[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const size_t fstride = (size_t)3 * a.C * HW4;               // float4 units between frames
+  float4* ptr = reinterpret_cast<float4*>(a.buf) + ((size_t)b * a.T * 3 * a.C + p) * HW4 + g4;
+  float4 cur = *ptr;
+  for (int t = 0; t < a.T; ++t) {
+    float4 nxt = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t + 1 < a.T) nxt = ptr[fstride];
+    // out[t] = bias + sum_j w[j] * s[t - (KT-1) + j]; hist[k] holds s[t - (KT-1) + k]
+    float4 o = make_float4(fmaf(w[KT - 1], cur.x, bias), fmaf(w[KT - 1], cur.y, bias),
+                           fmaf(w[KT - 1], cur.z, bias), fmaf(w[KT - 1], cur.w, bias));
+#pragma unroll
+    for (int k = 0; k < KT - 1; ++k) {
+      o.x = fmaf(w[k], hist[k].x, o.x); o.y = fmaf(w[k], hist[k].y, o.y);
+      o.z = fmaf(w[k], hist[k].z, o.z); o.w = fmaf(w[k], hist[k].w, o.w);
+    }
+#pragma unroll
+    for (int k = 0; k + 1 < KT - 1; ++k) hist[k] = hist[k + 1];
+    if (KT > 1) hist[KT - 2] = cur;
+    o = make_float4(silu_f(o.x), silu_f(o.y), silu_f(o.z), silu_f(o.w));
+    if (gated) {
+      const float4* gp = reinterpret_cast<const float4*>(a.bkv + ((size_t)(b * a.T + t) * a.HW + 4 * g4));
+      const float4 g0 = __ldg(gp), g1 = __ldg(gp + 1);        // {Bk,Bv} of pixels 0,1 and 2,3
+      o.x *= poff ? g0.y : g0.x; o.y *= poff ? g0.w : g0.z;
+      o.z *= poff ? g1.y : g1.x; o.w *= poff ? g1.w : g1.z;
+    }
+    *ptr = o;
+    ptr += fstride;
+    cur = nxt;
+  }
+}
+
+int launch_qkv_temporal_conv(const QkvTconvArgs& a, cudaStream_t st) {
+  if (a.HW % 4 != 0 || a.kt < 1) return CSSM_ERR_UNSUPPORTED;
+  const long long total = (long long)a.B * 3 * a.C * (a.HW >> 2);
+  const unsigned grid = (unsigned)((total + 255) / 256);
+  switch (a.kt) {
+    case 2: qkv_temporal_conv_kernel<2><<<grid, 256, 0, st>>>(a); break;
+    case 3: qkv_temporal_conv_kernel<3><<<grid, 256, 0, st>>>(a); break;
+    case 4: qkv_temporal_conv_kernel<4><<<grid, 256, 0, st>>>(a); break;
+    default: return CSSM_ERR_UNSUPPORTED;
+  }
+  return check_launch();
+}
+
 // ----------------------------------------------------------- gated gate maps ----
 // One CTA per (b,t).  ctx = ctx_sum / (H*W).  Writes, per bin, the float4
 // {exp(-D), (D+1e-8)*Bg, Cg/(H*W), 1e-7*(D+1e-8)} at bin_index(path, kh, kw).
