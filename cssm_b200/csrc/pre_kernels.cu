@@ -527,7 +527,10 @@ __global__ void __launch_bounds__(256) gated_gates_kernel(const GatedGateArgs g)
     }
     __syncthreads();
   }
-  for (int bin = tid; bin < NB; bin += blockDim.x) {
+  // the bins of a frame are split over gridDim.y CTAs (few frames, many bins: dense gates)
+  const int per_cta = (NB + gridDim.y - 1) / gridDim.y;
+  const int bin_end = min(NB, (int)(blockIdx.y + 1) * per_cta);
+  for (int bin = blockIdx.y * per_cta + tid; bin < bin_end; bin += blockDim.x) {
     const int kh = bin / Wf, kw = bin % Wf;
     float r[3];
     if (g.gate_type == CSSM_GATE_FACTORED) {
@@ -556,7 +559,15 @@ __global__ void __launch_bounds__(256) gated_gates_kernel(const GatedGateArgs g)
 int launch_gated_gates(const GatedGateArgs& g, cudaStream_t st) {
   const int Wf = g.W / 2 + 1;
   const size_t smem = (size_t)(g.C + 3 * (g.H + Wf)) * sizeof(float);
-  gated_gates_kernel<<<g.BT, 256, smem, st>>>(g);
+  // enough CTAs to cover the GPU when there are few frames: up to one CTA per 256 bins
+  const int NB = g.H * Wf;
+  int chunks = 1;
+  if (g.BT < 296) {
+    chunks = (296 + g.BT - 1) / g.BT;
+    const int maxc = (NB + 255) / 256;
+    if (chunks > maxc) chunks = maxc;
+  }
+  gated_gates_kernel<<<dim3(g.BT, chunks), 256, smem, st>>>(g);
   return check_launch();
 }
 

@@ -49,8 +49,10 @@ struct StemArgs {
 // CIN > 0: compile-time input channel count (the tap loops unroll fully, so all input loads of
 // a pixel are in flight together); CIN = 0: run-time a.Cin.
 // FULLC: C == 64, every lane's four channel groups are live (no run-time group checks).
-template <int KS, int POOL, int CIN, bool FULLC>
-__global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs a) {
+// NT: threads per CTA.  256 by default; 1024 when the conv weights fill most of the shared memory
+// (a 64 -> 64 channel 3x3 layer: 147 KB), so that the one resident CTA still has 32 warps.
+template <int KS, int POOL, int CIN, bool FULLC, int NT>
+__global__ void __launch_bounds__(NT) stem_layer_kernel(const StemArgs a) {
   extern __shared__ __align__(16) float sm[];
   const int C = FULLC ? SM_MAXC : a.C, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Cin = CIN > 0 ? CIN : a.Cin;
@@ -58,15 +60,15 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs
   float* wsm = sm;                                   // [tap][ci][C] when w_in_smem
   float* vec = sm + (a.w_in_smem ? nw : 0);          // bias, scale, lnbias
   if (a.w_in_smem)
-    for (int i = tid; i < nw; i += STEM_THREADS) wsm[i] = a.wk[i];
-  for (int i = tid; i < C; i += STEM_THREADS) {
+    for (int i = tid; i < nw; i += NT) wsm[i] = a.wk[i];
+  for (int i = tid; i < C; i += NT) {
     vec[i] = a.bk[i]; vec[C + i] = a.scale[i]; vec[2 * C + i] = a.bias[i];
   }
   __syncthreads();
   const float* wsrc = a.w_in_smem ? wsm : a.wk;
   const int g = lane & 3, ngrp = FULLC ? SM_MAXC / 4 : C >> 2;
   const long long total = (long long)a.N * a.Ho * a.Wo;
-  constexpr int WARPS = STEM_THREADS / 32;
+  constexpr int WARPS = NT / 32;
   const int dq = POOL == 2 ? (lane >> 2) & 3 : 0;
   constexpr int PER_WARP = POOL == 2 ? 2 : 8;        // output pixels per warp and iteration
   // grid-stride over groups of PER_WARP output pixels; the trip count is the same for all lanes
@@ -174,27 +176,173 @@ __global__ void __launch_bounds__(STEM_THREADS) stem_layer_kernel(const StemArgs
   }
 }
 
-template <int KS, int POOL, int CIN, bool FULLC>
+// Stem layer with many input channels (the second and later layers: Cin = embed_dim).  The conv
+// weights (K*K*Cin*C floats, 147 KB at 3x3x64x64) fill most of the shared memory and every FMA
+// needs one of them, so the kernel is bound by shared-memory reads unless a weight is reused: here
+// a lane owns ALL FOUR pixels of a 2x2 pool window (for its float4 channel groups g + 4k), loads a
+// weight float4 once and uses it for the four pixels; the max-pool then needs no shuffles.
+// lane = g | window << 2 (8 windows per warp).  One CTA of 512 threads per SM loops over windows.
+constexpr int STEMW_THREADS = 512;
+template <int KS>
+__global__ void __launch_bounds__(STEMW_THREADS) stem_layer_wide_kernel(const StemArgs a) {
+  extern __shared__ __align__(16) float sm[];
+  const int C = a.C, Cin = a.Cin, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nw = KS * KS * Cin * C;
+  float* wsm = sm;
+  float* vec = sm + nw;
+  for (int i = tid; i < nw; i += STEMW_THREADS) wsm[i] = a.wk[i];
+  for (int i = tid; i < C; i += STEMW_THREADS) {
+    vec[i] = a.bk[i]; vec[C + i] = a.scale[i]; vec[2 * C + i] = a.bias[i];
+  }
+  __syncthreads();
+  const int g = lane & 3, ngrp = C >> 2;
+  constexpr int LO = (KS - 1) / 2, WARPS = STEMW_THREADS / 32;
+  const long long total = (long long)a.N * a.Ho * a.Wo;
+  for (long long grp = (long long)blockIdx.x * WARPS + warp; grp * 8 < total;
+       grp += (long long)gridDim.x * WARPS) {
+    const long long o = grp * 8 + (lane >> 2);
+    const bool valid = o < total;
+    const long long oc = valid ? o : 0;
+    const int wo = (int)(oc % a.Wo), ho = (int)((oc / a.Wo) % a.Ho), n = (int)(oc / ((long long)a.Wo * a.Ho));
+    float acc[4][4][4];                               // [window pixel][group k][element]
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int j = g + 4 * k;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[p][k][e] = j < ngrp ? vec[4 * j + e] : 0.f;
+      }
+    if (valid) {
+#pragma unroll 1
+      for (int tap = 0; tap < KS * KS; ++tap) {
+        const float* xp[4];
+        bool ok[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const int hh = 2 * ho + (p >> 1) + tap / KS - LO, ww = 2 * wo + (p & 1) + tap % KS - LO;
+          ok[p] = hh >= 0 && hh < a.Hin && ww >= 0 && ww < a.Win;
+          xp[p] = a.x + (((size_t)n * a.Hin + (ok[p] ? hh : 0)) * a.Win + (ok[p] ? ww : 0)) * Cin;
+        }
+        const float4* w4 = reinterpret_cast<const float4*>(wsm + (size_t)tap * Cin * C);
+#pragma unroll 1
+        for (int c4 = 0; c4 < Cin; c4 += 4) {
+          float xv[4][4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const float4 t = ok[p] ? __ldg(reinterpret_cast<const float4*>(xp[p] + c4))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            xv[p][0] = t.x; xv[p][1] = t.y; xv[p][2] = t.z; xv[p][3] = t.w;
+          }
+#pragma unroll
+          for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int j = g + 4 * k;
+              if (j < ngrp) {
+                const float4 wv = w4[(c4 + ci) * ngrp + j];
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                  acc[p][k][0] = fmaf(xv[p][ci], wv.x, acc[p][k][0]);
+                  acc[p][k][1] = fmaf(xv[p][ci], wv.y, acc[p][k][1]);
+                  acc[p][k][2] = fmaf(xv[p][ci], wv.z, acc[p][k][2]);
+                  acc[p][k][3] = fmaf(xv[p][ci], wv.w, acc[p][k][3]);
+                }
+              }
+            }
+        }
+      }
+    }
+    // per window pixel: softplus, LayerNorm over the quad's channels; running max over the pixels
+    float mx[4][4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) mx[k][e] = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float s = 0.f, ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (g + 4 * k < ngrp) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float v = softplus_f(acc[p][k][e]);
+            acc[p][k][e] = v; s += v; ss = fmaf(v, v, ss);
+          }
+        }
+      s += __shfl_xor_sync(0xffffffffu, s, 1);  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      const float mean = s / (float)C;
+      const float rinv = rsqrtf(fmaxf(ss / (float)C - mean * mean, 0.f) + 1e-6f);
+      const bool inb = 2 * ho + (p >> 1) < a.Hin && 2 * wo + (p & 1) < a.Win;   // else pool padding
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int j = g + 4 * k;
+        if (inb && j < ngrp) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            mx[k][e] = fmaxf(mx[k][e], (acc[p][k][e] - mean) * rinv * vec[C + 4 * j + e] + vec[2 * C + 4 * j + e]);
+        }
+      }
+    }
+    float4* op = reinterpret_cast<float4*>(a.out + (size_t)oc * C);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = g + 4 * k;
+      if (valid && j < ngrp) op[j] = make_float4(mx[k][0], mx[k][1], mx[k][2], mx[k][3]);
+    }
+  }
+}
+
+template <int KS>
+static int launch_stem_layer_wide(StemArgs a, cudaStream_t st) {
+  const size_t smem = ((size_t)KS * KS * a.Cin * a.C + 3 * (size_t)a.C) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(stem_layer_wide_kernel<KS>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  const long long total = (long long)a.N * a.Ho * a.Wo;
+  const long long per_cta = (STEMW_THREADS / 32) * 8;
+  const long long need = (total + per_cta - 1) / per_cta;
+  stem_layer_wide_kernel<KS><<<(unsigned)(need < 148 ? need : 148), STEMW_THREADS, smem, st>>>(a);
+  return check_launch();
+}
+
+template <int KS, int POOL, int CIN, bool FULLC, int NT>
 static int launch_stem_layer_v(StemArgs a, cudaStream_t st) {
   const size_t wbytes = (size_t)KS * KS * a.Cin * a.C * sizeof(float);
   a.w_in_smem = wbytes <= 160 * 1024 ? 1 : 0;
   const size_t smem = (a.w_in_smem ? wbytes : 0) + 3 * (size_t)a.C * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(stem_layer_kernel<KS, POOL, CIN, FULLC>,
+  cudaError_t e = cudaFuncSetAttribute(stem_layer_kernel<KS, POOL, CIN, FULLC, NT>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const long long total = (long long)a.N * a.Ho * a.Wo;
-  const long long per_cta = (STEM_THREADS / 32) * (POOL == 2 ? 2 : 8);
+  const long long per_cta = (NT / 32) * (POOL == 2 ? 2 : 8);
   const long long need = (total + per_cta - 1) / per_cta;
   // a few resident waves of CTAs that loop, so that the per-CTA weight staging is amortised
-  const unsigned grid = (unsigned)(need < 148 * 16 ? need : 148 * 16);
-  stem_layer_kernel<KS, POOL, CIN, FULLC><<<grid, STEM_THREADS, smem, st>>>(a);
+  const long long cap = NT == 1024 ? 148 : 148 * 16;
+  const unsigned grid = (unsigned)(need < cap ? need : cap);
+  stem_layer_kernel<KS, POOL, CIN, FULLC, NT><<<grid, NT, smem, st>>>(a);
   return check_launch();
 }
 
 template <int KS, int POOL, int CIN>
 static int launch_stem_layer_cin(const StemArgs& a, cudaStream_t st) {
-  return a.C == SM_MAXC ? launch_stem_layer_v<KS, POOL, CIN, true>(a, st)
-                        : launch_stem_layer_v<KS, POOL, CIN, false>(a, st);
+  // many input channels, pooled: the weight-reusing kernel (needs the weights in shared memory
+  // and float4 input reads)
+  const size_t wbytes = (size_t)KS * KS * a.Cin * a.C * sizeof(float);
+  // it needs one full wave of windows to pay (measured at 64 -> 64 channels on 128x128 images:
+  // batch 8: 0.20 ms narrow vs 0.24 ms wide; batch 128: 2.67 vs 1.71 ms, both layers)
+  const long long windows = (long long)a.N * a.Ho * a.Wo;
+  if (CIN == 0 && POOL == 2 && a.Cin % 4 == 0 && a.Cin >= 16 && wbytes <= 200 * 1024 &&
+      windows >= 148LL * (STEMW_THREADS / 32) * 8)
+    return launch_stem_layer_wide<KS>(a, st);
+  // otherwise: weights beyond 64 KB leave room for one CTA per SM only, give that CTA 32 warps
+  if (CIN == 0 && wbytes > 64 * 1024)
+    return a.C == SM_MAXC ? launch_stem_layer_v<KS, POOL, 0, true, 1024>(a, st)
+                          : launch_stem_layer_v<KS, POOL, 0, false, 1024>(a, st);
+  return a.C == SM_MAXC ? launch_stem_layer_v<KS, POOL, CIN, true, STEM_THREADS>(a, st)
+                        : launch_stem_layer_v<KS, POOL, CIN, false, STEM_THREADS>(a, st);
 }
 
 template <int KS, int POOL>

@@ -15,7 +15,8 @@ TOL = 1e-4
 def _model(cssm_type, E, ks, pos, stem_mode, stem_layers, pool, rnorm, **extra):
     return SimpleCSSM(num_classes=extra.pop("num_classes", 2), embed_dim=E, cssm_type=cssm_type,
                       kernel_size=ks, pos_embed=pos, stem_mode=stem_mode, stem_layers=stem_layers,
-                      pool_type=pool, readout_norm=rnorm, gate_type="factored", **extra)
+                      pool_type=pool, readout_norm=rnorm, gate_type=extra.pop("gate_type", "factored"),
+                      **extra)
 
 
 def _block_kwargs(m):
@@ -34,6 +35,11 @@ CASES = [
     ("gated", 8, 5, "spatiotemporal", "default", 1, "max", "pre", (3, 16, 16, 1), dict(seq_len=3)),
     ("gated", 8, 3, "none", "default", 2, "mean", "post", (2, 20, 20, 3), dict(seq_len=2)),
     ("gated", 64, 11, "spatiotemporal", "default", 1, "max", "pre", (2, 128, 128, 1), dict(seq_len=4)),
+    # two stem layers with 16 / 64 channels: the second layer runs the weight-reusing kernel
+    ("gated", 16, 3, "none", "default", 2, "max", "pre", (2, 22, 26, 1), dict(seq_len=2)),
+    ("gated", 16, 3, "none", "default", 2, "max", "pre", (40, 90, 94, 1), dict(seq_len=1)),   # a full wave of windows
+    ("gated", 64, 1, "spatiotemporal", "default", 2, "mean", "pre", (2, 128, 128, 1),
+     dict(seq_len=1, gate_type="dense")),
     ("gated", 16, 5, "mrope", "default", 1, "mean", "pre", (2, 3, 14, 18, 2), dict()),        # clips, odd pool
     ("gdn", 8, 5, "mrope", "pathtracker", 1, "mean", "pre", (2, 4, 8, 8, 3), dict(delta_key_dim=4)),
     ("gdn", 64, 11, "spatiotemporal", "pathtracker", 1, "max", "pre", (2, 5, 32, 32, 3),
