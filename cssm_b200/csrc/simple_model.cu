@@ -594,6 +594,10 @@ extern "C" {
 
 size_t cssm_simple_workspace_bytes(const cssm_simple_desc* d, const void* block_desc) {
   if (simple_validate(d) != CSSM_OK || !block_desc || !block_matches(*d, block_desc)) return 0;
+  // a block descriptor its own library entry points reject makes the model unsupported too
+  const size_t bws = d->block == 0 ? cssm_gated_workspace_bytes((const cssm_gated_desc*)block_desc)
+                                   : cssm_gdn_workspace_bytes((const cssm_gdn_desc*)block_desc);
+  if (bws == 0) return 0;
   return simple_ws_layout(*d, block_desc).total;
 }
 

@@ -153,6 +153,8 @@ def test_simple_model_descriptor_validation_without_gpu():
     for bad in (dict(embed_dim=128), dict(embed_dim=6), dict(stem_mode=2), dict(stem_layers=0),
                 dict(pool_type=2), dict(num_classes=0), dict(block=3)):
         assert L.cssm_simple_workspace_bytes(C.byref(_simple_desc(**bad)), C.byref(bd)) == 0, bad
+    # a block descriptor the block entry points reject (unknown gate type) is rejected here too
+    assert L.cssm_simple_workspace_bytes(C.byref(_simple_desc()), C.byref(_desc(B=2, T=3, H=8, W=8, C=8, gate_type=5))) == 0
     w = _lib.SimpleWeights()
     assert L.cssm_simple_forward(C.byref(_simple_desc()), C.byref(w), C.byref(bd), None, None, None,
                                  None, None, 0, 0, None) == 1
