@@ -67,6 +67,18 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
   const float invHW = 1.0f / (float)HW;
 
   const int Tdata = STATIC ? 1 : a.T;          // frames of q, k, v per batch element
+  // rows of the NEXT pass's planes, fetched one pass ahead (the kernel runs nine warps per SM,
+  // so a load issued where it is needed is not hidden by other warps)
+  auto first_pass = [&](int t) -> int { return (LAST && t < Tdata - 1) ? 1 : 0; };
+  auto rows_of = [&](int t, int pass) -> const float* {
+    return a.qkv + ((size_t)(b * Tdata + t) * 3 * a.C + (size_t)pass * a.C + hd * DK + rpl) * HW + roff;
+  };
+  cf nx[8];
+  if (row_on) {
+    const float* r0 = rows_of(0, first_pass(0));
+#pragma unroll
+    for (int m = 0; m < 8; ++m) nx[m] = mk(r0[4 * m], r0[32 + 4 * m]);
+  }
   for (int t = 0; t < Tdata; ++t) {
     const size_t frame = (size_t)(b * Tdata + t);
     float* base = a.qkv + frame * 3 * a.C * HW;
@@ -78,10 +90,17 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
     for (int pass = emit ? 0 : 1; pass < 3; ++pass) {     // q is only needed for the readout
       __syncthreads();                       // ZR free (previous column pass finished)
       if (row_on) {
-        const float* r0 = base + (size_t)(pass * a.C + hd * DK + rpl) * HW + roff;
         cf u[8];
 #pragma unroll
-        for (int m = 0; m < 8; ++m) u[m] = mk(r0[4 * m], r0[32 + 4 * m]);
+        for (int m = 0; m < 8; ++m) u[m] = nx[m];
+        // the v planes of this step are overwritten by its output at the end of the step, after
+        // this prefetch of the next step's first planes (q or k) has long been consumed
+        const int nt = pass < 2 ? t : t + 1;
+        if (nt < Tdata) {
+          const float* r0 = rows_of(nt, pass < 2 ? pass + 1 : first_pass(nt));
+#pragma unroll
+          for (int m = 0; m < 8; ++m) nx[m] = mk(r0[4 * m], r0[32 + 4 * m]);
+        }
         fft32_fwd(u, tw, exg, q);
         cf* zr = ZR + (rpl * 16 + rpair) * G32_ZRS;
 #pragma unroll
