@@ -147,7 +147,7 @@ int cssm_gated_plan_init(const cssm_gated_desc* d, const cssm_gated_weights* w, 
 
 static int gated_in_proj_impl(const cssm_gated_desc* d, const cssm_gated_weights* w,
                               const void* plan, const float* x, float* xz, void* stream,
-                              int x_bcast);
+                              int x_bcast, int z_last_only = 0);
 
 int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
                        const float* x, float* xz, void* stream) {
@@ -155,9 +155,10 @@ int cssm_gated_in_proj(const cssm_gated_desc* d, const cssm_gated_weights* w, co
 }
 
 // x_bcast != 0: x is (B,H,W,C), one frame per batch element that stands for all T frames
+// z_last_only != 0: the silu(z) planes are only written for the last frame of every clip
 static int gated_in_proj_impl(const cssm_gated_desc* d, const cssm_gated_weights* w,
                               const void* plan, const float* x, float* xz, void* stream,
-                              int x_bcast) {
+                              int x_bcast, int z_last_only) {
   int s = validate(d);
   if (s != CSSM_OK) return s;
   if (!w || !w->in_proj_kernel || !w->in_proj_bias || !plan || !x || !xz) return CSSM_ERR_NULL;
@@ -178,6 +179,7 @@ static int gated_in_proj_impl(const cssm_gated_desc* d, const cssm_gated_weights
   }
   g.T = d->T; g.H = d->H; g.W = d->W;
   if (x_bcast) { g.a_fdiv = d->T; g.a_fmul = 1; g.a_fadd = 0; }
+  g.z_last_only = z_last_only;
   return launch_gemm<false, true>(g, (cudaStream_t)stream);
 }
 
@@ -263,7 +265,7 @@ int gated_forward_internal(const cssm_gated_desc* d, const cssm_gated_weights* w
   float* xz = (float*)(ws + l.xz_planar);
   float* ctx = (float*)(ws + l.ctx_sum);
   float* gm = (float*)(ws + l.gate_maps);
-  if ((s = gated_in_proj_impl(d, w, plan, x, xz, stream, x_bcast)) != CSSM_OK) return s;
+  if ((s = gated_in_proj_impl(d, w, plan, x, xz, stream, x_bcast, last_only)) != CSSM_OK) return s;
   if ((s = cssm_gated_short_conv(d, w, xz, ctx, stream)) != CSSM_OK) return s;
   if ((s = cssm_gated_gates(d, w, ctx, gm, stream)) != CSSM_OK) return s;
   if (!last_only) {

@@ -34,6 +34,7 @@ struct GemmArgs {
   int g_compact;            // 1: the gate is indexed by the OUTPUT frame, 0: by the source frame
   int out_act;              // 0 none, 1 silu, 2 sigmoid; applied to output columns n >= act_n0
   int act_n0;
+  int z_last_only;          // planar output: columns n >= act_n0 are only stored for frames with t == T-1
   const float* sub;         // channels-last output only: (M, N) tensor subtracted from the result, or nullptr
 };
 
@@ -183,7 +184,10 @@ gemm_simt_kernel(const GemmArgs g) {
         if (g.out_act == 1) v = silu_f(v);
         else if (g.out_act == 2) v = sigmoid_f(v);
       }
-      if (O_PLANAR) g.out[((size_t)fr * g.o_planes + g.o_plane0 + n) * g.HW + px] = v;
+      if (O_PLANAR) {
+        if (g.z_last_only && n >= g.act_n0 && fr % g.T != g.T - 1) continue;
+        g.out[((size_t)fr * g.o_planes + g.o_plane0 + n) * g.HW + px] = v;
+      }
       else g.out[(size_t)m * g.N + n] = g.sub ? v - g.sub[(size_t)m * g.N + n] : v;
     }
   }

@@ -47,7 +47,10 @@ struct TcSmem {
   static constexpr uint32_t TOTAL = BAR_OFF + 128u;
 };
 
-template <int N, bool A_PLANAR, bool STG>
+// ZLAST: the output columns from act_n0 on (the z half of the in_proj) are only produced for the
+// last frame of every clip (last-frame-only forward); a compile-time variant so that the default
+// kernel carries no extra test.
+template <int N, bool A_PLANAR, bool STG, bool ZLAST = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__ CUtensorMap omap) {
   // tile schedule: round-robin over CTAs (default) or one contiguous range per CTA (dbg & 8)
@@ -305,6 +308,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)s * N;
 #pragma unroll 1
       for (int cc = half * (N / 64); cc < (half + 1) * (N / 64); ++cc) {
+        if (ZLAST && cc * 32 >= g.act_n0 && (m / g.HW) % g.T != g.T - 1) continue;   // tile-uniform
         uint32_t r[32];
         tc::ld_32x32b_x32(taddr + cc * 32, r);
         tc::wait_ld();
@@ -480,7 +484,7 @@ static bool make_out_map(const GemmArgs& g, bool a_planar, CUtensorMap* map) {
   return r == CUDA_SUCCESS;
 }
 
-template <int N, bool A_PLANAR, bool STG>
+template <int N, bool A_PLANAR, bool STG, bool ZLAST = false>
 static int launch_tc_v(const GemmArgs& g, const CUtensorMap& map, cudaStream_t st) {
   const int num_tiles = g.M / TC_BM;
   int dev = 0, sms = 0;
@@ -489,10 +493,10 @@ static int launch_tc_v(const GemmArgs& g, const CUtensorMap& map, cudaStream_t s
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const int grid = num_tiles < sms ? num_tiles : sms;
   const size_t smem = TcSmem<N, STG>::TOTAL + 1024;      // slack for the 1024-byte alignment
-  e = cudaFuncSetAttribute(gemm_tc_kernel<N, A_PLANAR, STG>,
+  e = cudaFuncSetAttribute(gemm_tc_kernel<N, A_PLANAR, STG, ZLAST>,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  gemm_tc_kernel<N, A_PLANAR, STG><<<grid, TC_THREADS, smem, st>>>(g, num_tiles, g_tc_dbg, map);
+  gemm_tc_kernel<N, A_PLANAR, STG, ZLAST><<<grid, TC_THREADS, smem, st>>>(g, num_tiles, g_tc_dbg, map);
   return check_launch();
 }
 
@@ -513,6 +517,11 @@ static int launch_tc(const GemmArgs& g, cudaStream_t st) {
 
 int launch_gemm_tc(const GemmArgs& g, bool a_planar, cudaStream_t st) {
   if (!gemm_tc_supported(g, a_planar)) return CSSM_ERR_UNSUPPORTED;
+  if (g.z_last_only && !a_planar && g.N == 128) {
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    return launch_tc_v<128, false, false, true>(g, map, st);
+  }
   if (!a_planar)
     return g.N == 192 ? launch_tc<192, false>(g, st)
                       : g.N == 128 ? launch_tc<128, false>(g, st) : launch_tc<64, false>(g, st);
