@@ -403,7 +403,7 @@ def main():
     # ---- the block alone, stage by stage, on the stem features ----
     feat = bound.stem(x)
     feat5 = feat[:, None].expand(-1, T, -1, -1, -1).contiguous() if image_input else feat
-    stem_ms = time_region(lambda: bound.stem(x), args.steps, dev, st) / args.steps
+    stem_ms = time_region(lambda: bound.stem(x, out=feat), args.steps, dev, st) / args.steps
     stage_ms, block_ms = block_stage_times(bound, feat5, args.steps, dev, st)
     del feat5
 

@@ -32,8 +32,10 @@ int launch_gated_spectral_ws(float* xz, const cf* khat, const float* gates, int 
 // PRS: floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane).
 // LAST: only the last step's output plane is produced (compile-time, so that the all-frames
 // kernel carries none of the branches).
-// NOG: the ungated recurrence S_t = K_hat S_{t-1} + X_hat_t of NoGateCSSM (no gate maps, no z plane).
-template <int PRS, bool LAST, bool NOG>
+// MODE 0: gated block (gate maps, output times the silu(z) plane).  MODE 1: the ungated recurrence
+// S_t = K_hat S_{t-1} + X_hat_t of NoGateCSSM (no gate maps, no z plane).  MODE 2: gate maps but no
+// z plane (the single-state AdditiveCSSM).
+template <int PRS, bool LAST, int MODE>
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C,
@@ -65,7 +67,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
   // stage step `tl`: x_main plane into xbuf (if want_x) and z plane into zbuf[tl & 1]
   auto stage = [&](int tl, bool want_x) {
     if (c.warp != 8) return;
-    const bool want_z = !NOG && (!last_only || tl == T - 1);
+    const bool want_z = MODE == 0 && (!last_only || tl == T - 1);
     tc::fence_proxy_async();             // earlier generic reads of the buffers come first
     uint64_t* bz = &bars[1 + (tl & 1)];
     if (c.lane == 0) {
@@ -125,14 +127,14 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         // {exp(-D), (D+1e-8)B, C/(HW), 1e-7(D+1e-8)}
-        if (!NOG) g[q] = c.col_on ? __ldg(gp + q * (33 * 8)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE != 1) g[q] = c.col_on ? __ldg(gp + q * (33 * 8)) : make_float4(0.f, 0.f, 0.f, 0.f);
         kh[q] = c.col_on ? khp[q * (33 * 8)] : mk(0.f, 0.f);
       }
       cf v[8];
       r64_col_fwd(c, v);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        if (NOG) {
+        if (MODE == 1) {
           cf h = cmul(kh[q], hst[q]);
           h.x += v[q].x; h.y += v[q].y;
           hst[q] = h;
@@ -156,7 +158,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       cf v[8];
       r64_row_inv(c, v);
       float* y0 = xp + roff;
-      if (!NOG) {
+      if (MODE == 0) {
         // in last-only mode the z barrier of this slot completes exactly once (phase 0)
         if (!tc::mbar_wait(&bars[1 + (t & 1)], last_only ? 0 : (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
         const float* zs = zbuf + (t & 1) * R64_PLANE_F + soff;
@@ -247,7 +249,7 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
         idx += kh; if (idx >= H) idx -= H;
       }
       // ungated mode: A = K_hat, U = X_hat, output scale 1/(H*W), no floor
-      const float4 g = nog ? make_float4(1.f, 1.f, 1.0f / (float)HW, 0.f) : gp[o];
+      const float4 g = nog == 1 ? make_float4(1.f, 1.f, 1.0f / (float)HW, 0.f) : gp[o];
       const cf k = khc[o];
       cf A = mk(k.x * g.x, k.y * g.x);
       cf U = mk(g.y * ax, g.y * ay);
@@ -288,7 +290,7 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
         s2 += r[k].x * e.x + r[k].y * e.y;
       }
       acc += 2.f * s2;
-      xp[o] = nog ? acc : acc * zp[o];
+      xp[o] = nog != 0 ? acc : acc * zp[o];
     }
   }
 }
@@ -359,7 +361,7 @@ gated_spectral_small(float* __restrict__ xz, const cf* __restrict__ khat,
           ax += r.x * e.x - r.y * e.y; ay += r.x * e.y + r.y * e.x;
           idx += kh; if (idx >= H) idx -= H;
         }
-        const float4 g = nog ? make_float4(1.f, 1.f, invHW, 0.f) : __ldg(gp + o);
+        const float4 g = nog == 1 ? make_float4(1.f, 1.f, invHW, 0.f) : __ldg(gp + o);
         const cf k = khc[o];
         const cf A = mk(k.x * g.x, k.y * g.x);
         cf U = mk(g.y * ax, g.y * ay);
@@ -397,7 +399,7 @@ gated_spectral_small(float* __restrict__ xz, const cf* __restrict__ khat,
           s2 += r[k].x * e.x + r[k].y * e.y;
         }
         acc += 2.f * s2;
-        xp[o] = nog ? acc : acc * zp[o];
+        xp[o] = nog != 0 ? acc : acc * zp[o];
       }
     }
   }
@@ -455,11 +457,12 @@ int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const flo
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     }
-    auto kern = padded ? (last_only ? gated_spectral_r64<68, true, false> : gated_spectral_r64<68, false, false>)
-                       : (last_only ? gated_spectral_r64<64, true, false> : gated_spectral_r64<64, false, false>);
+    auto kern = padded ? (last_only ? gated_spectral_r64<68, true, 0> : gated_spectral_r64<68, false, 0>)
+                       : (last_only ? gated_spectral_r64<64, true, 0> : gated_spectral_r64<64, false, 0>);
     if (nogate) {
-      if (!padded) return CSSM_ERR_CUDA;          // the ungated variant exists for the padded staging only
-      kern = last_only ? gated_spectral_r64<68, true, true> : gated_spectral_r64<68, false, true>;
+      if (!padded) return CSSM_ERR_CUDA;          // these variants exist for the padded staging only
+      if (nogate == 1) kern = last_only ? gated_spectral_r64<68, true, 1> : gated_spectral_r64<68, false, 1>;
+      else kern = last_only ? gated_spectral_r64<68, true, 2> : gated_spectral_r64<68, false, 2>;
     }
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);

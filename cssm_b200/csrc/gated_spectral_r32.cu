@@ -18,8 +18,9 @@ constexpr int R32_GB_CF = 4 * 32 * R32_GBS;
 constexpr int R32_SMEM_BYTES = (R32_EX_CF + R32_ZR_CF + R32_GB_CF) * 8;
 
 // LAST: only the last step's output planes are produced (compile-time switch).
-// NOG: ungated recurrence S_t = K_hat S_{t-1} + X_hat_t (no gate maps, no z planes).
-template <bool LAST, bool NOG>
+// MODE 0: gate maps and z planes; 1: ungated recurrence S_t = K_hat S_{t-1} + X_hat_t (neither);
+// 2: gate maps, no z planes.
+template <bool LAST, int MODE>
 __global__ void __launch_bounds__(R32_THREADS, 2)
 gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C) {
@@ -84,7 +85,7 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
       const float4* gp = gates + frame * NB + (kw << 2) + q;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        if (!NOG) g[r] = col_on ? __ldg(gp + r * (17 * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE != 1) g[r] = col_on ? __ldg(gp + r * (17 * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
         kh[r] = col_on ? khp[r * (17 * 4)] : mk(0.f, 0.f);
       }
       cf v[8];
@@ -100,7 +101,7 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
       fft32_fwd(v, tw, exg, q);
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        if (NOG) {
+        if (MODE == 1) {
           cf h = cmul(kh[r], hst[r]);
           h.x += v[r].x; h.y += v[r].y;
           hst[r] = h;
@@ -131,8 +132,8 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
       const float* z0 = zp + roff;
 #pragma unroll
       for (int m = 0; m < 8; ++m) {
-        ze[m] = NOG ? 1.f : __ldg(z0 + 4 * m);
-        zo[m] = NOG ? 1.f : __ldg(z0 + 32 + 4 * m);
+        ze[m] = MODE != 0 ? 1.f : __ldg(z0 + 4 * m);
+        zo[m] = MODE != 0 ? 1.f : __ldg(z0 + 32 + 4 * m);
       }
       const cf* ge = GB + (rpl * 32 + 2 * rpair) * R32_GBS;
       const cf* go = ge + R32_GBS;
@@ -162,8 +163,9 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
 
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
                               int last_only, int nogate, cudaStream_t st) {
-  auto kern = nogate ? (last_only ? gated_spectral_r32<true, true> : gated_spectral_r32<false, true>)
-                     : (last_only ? gated_spectral_r32<true, false> : gated_spectral_r32<false, false>);
+  auto kern = last_only ? gated_spectral_r32<true, 0> : gated_spectral_r32<false, 0>;
+  if (nogate == 1) kern = last_only ? gated_spectral_r32<true, 1> : gated_spectral_r32<false, 1>;
+  if (nogate == 2) kern = last_only ? gated_spectral_r32<true, 2> : gated_spectral_r32<false, 2>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        R32_SMEM_BYTES);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }

@@ -43,8 +43,9 @@ int launch_gated_gates(const GatedGateArgs& g, cudaStream_t st);
 // plane and the stores of earlier steps are skipped; the recurrence still runs over all T)
 int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float* gates,
                           float* xz, int last_only, cudaStream_t st);
-// nogate != 0: the ungated recurrence S_t = K_hat S_{t-1} + X_hat_t (NoGateCSSM): `gates` is not
-// read and the z planes of the (B*T, 2C, H, W) buffer are neither read nor written
+// nogate == 1: the ungated recurrence S_t = K_hat S_{t-1} + X_hat_t (NoGateCSSM): `gates` is not
+// read and the z planes of the (B*T, 2C, H, W) buffer are neither read nor written.
+// nogate == 2: gate maps as in the gated block, but no z planes (single-state AdditiveCSSM)
 int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const float* gates,
                     float* xz, int last_only, int nogate, cudaStream_t st);
 size_t generic_smem_bytes(int H, int W);

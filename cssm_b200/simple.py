@@ -217,14 +217,21 @@ class BoundSimple:
         H, W = self.mod.feature_hw(d.Hin, d.Win)
         return self.block.desc((d.B, d.T, H, W, d.embed_dim))
 
-    def stem(self, x: torch.Tensor) -> torch.Tensor:
-        """Stem features: (B,H,W,E) for image input, (B,T,H,W,E) for clips."""
+    def stem(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Stem features: (B,H,W,E) for image input, (B,T,H,W,E) for clips.  `out`, when given,
+        is a contiguous fp32 tensor of that shape on the same device and receives the result."""
         _require_cuda(x)
         x = x.contiguous()
         d = self.desc(tuple(x.shape))
         H, W = self.mod.feature_hw(d.Hin, d.Win)
         shape = (d.B, H, W, d.embed_dim) if d.image_input else (d.B, d.T, H, W, d.embed_dim)
-        feat = torch.empty(shape, dtype=torch.float32, device=x.device)
+        if out is None:
+            feat = torch.empty(shape, dtype=torch.float32, device=x.device)
+        else:
+            if tuple(out.shape) != shape or out.dtype != torch.float32 or not out.is_contiguous() \
+                    or out.device != x.device:
+                raise ValueError(f"out must be a contiguous float32 {shape} tensor on {x.device}")
+            feat = out
         frames = d.B if d.image_input else d.B * d.T
         half = frames * ((d.Hin + 1) // 2) * ((d.Win + 1) // 2) * d.embed_dim * 4
         ws = self.buf.get("stem", 2 * ((half + 255) // 256 * 256))

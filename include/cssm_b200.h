@@ -279,6 +279,53 @@ int cssm_nogate_forward(const cssm_nogate_desc* d, const cssm_nogate_weights* w,
                         const float* x, float* y, void* workspace, size_t workspace_bytes,
                         void* stream);
 
+/* ============================================================ AdditiveCSSM (1 state) ====
+ * The single-state path of AdditiveCSSM (single_state=True, "add_kqv_1";
+ * src/models/cssm.py:2961-3359, 3580-3626): RoPE (optional) -> Dense x_proj -> rfft2 ->
+ *   h_t = (d_X,t * K_hat) h_{t-1} + B_X,t * X_hat_t,  h_0 = 0  ->  C_gate,t * h_t -> irfft2 ->
+ * Dense output_proj.  The three gates are computed from ctx = mean_{H,W}(rotated x) + temporal
+ * code (cssm.py:3127-3131, 353-383): d_X = 0.1 + 0.89 sigmoid(.), B_X = sigmoid(.),
+ * C_gate = sigmoid(.), each a per-bin map (H, W/2+1) shared by the channels; gate_type 'dense'
+ * (one Dense(H*Wf)) or 'factored' (sigmoid(row + col), cssm.py:3201-3207).  Replaces every
+ * scan_mode of that path (associative / ssd / quadratic / pallas, cssm.py:3294-3359): they
+ * evaluate the same recurrence.  goom_floor = 1 keeps the 1e-7 magnitude floors of the
+ * log-space scan (to_goom, src/models/goom.py:161-173) on K_hat and on B_X * X_hat; 0 is the
+ * plain complex recurrence of the other scan modes.  Gates of type conv / channel /
+ * dense_decay / dense_io / spectral_conv / low_rank / scalar, learned_init,
+ * position_independent_gates and the 2- and 3-state paths are rejected. */
+typedef struct cssm_additive_desc {
+  int32_t B, T, H, W, C;
+  int32_t kernel_size;
+  int32_t rope_mode;        /* CSSM_ROPE_* */
+  float   rope_base;        /* 10000 */
+  float   spectral_rho;     /* 0.999 */
+  int32_t gate_type;        /* CSSM_GATE_DENSE or CSSM_GATE_FACTORED */
+  int32_t single_state;     /* must be 1 */
+  int32_t goom_floor;       /* 1: scan_mode 'associative' with use_goom; 0: linear scan modes */
+} cssm_additive_desc;
+
+typedef struct cssm_additive_weights {
+  const float* kernel;              /* (C, ks, ks)                                            */
+  const float* x_proj_kernel;       /* (C, C)                                                 */
+  const float* x_proj_bias;         /* (C)                                                    */
+  /* dense: [0..2] = d_X, B_X, C_gate, kernels (C, H*Wf), biases (H*Wf).
+     factored: [0..5] = d_X_h, d_X_w, B_X_h, B_X_w, C_gate_h, C_gate_w, kernels (C,H) / (C,Wf) */
+  const float* gate_kernel[6];
+  const float* gate_bias[6];
+  const float* output_proj_kernel;  /* (C, C)                                                 */
+  const float* output_proj_bias;    /* (C)                                                    */
+} cssm_additive_weights;
+
+size_t cssm_additive_plan_bytes(const cssm_additive_desc* d);
+size_t cssm_additive_workspace_bytes(const cssm_additive_desc* d);
+/* K_hat = squash(rfft2(pad(kernel))) (cssm.py:3097-3104), RoPE tables, temporal code. */
+int cssm_additive_plan_init(const cssm_additive_desc* d, const cssm_additive_weights* w, void* plan,
+                            size_t plan_bytes, void* stream);
+/* y = AdditiveCSSM(single_state=True)(x); x, y: (B,T,H,W,C) fp32 channels-last. */
+int cssm_additive_forward(const cssm_additive_desc* d, const cssm_additive_weights* w,
+                          const void* plan, const float* x, float* y, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 /* ================================================================ SimpleCSSM model ====
  * Inference forward of the reference's SimpleCSSM wrapper around ONE block (depth 1):
  *   stem -> x + block(x) -> last frame -> norm_pre/act -> spatial pool -> norm_post -> head.

@@ -401,6 +401,77 @@ def nogate_forward(params, x, *, kernel_size, spectral_rho=0.999, dtype=np.float
     return dense(y, params["out_proj"]) - x
 
 
+def additive1_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=10000.0,
+                      spectral_rho=0.999, gate_type="dense", scan_mode="associative",
+                      dtype=np.float64, scan="direct"):
+    """AdditiveCSSM.__call__ with single_state=True (cssm.py:3061-3359, 3580-3626), gate_type
+    'dense' or 'factored', position_independent_gates=False, learned_init=False, use_goom=True.
+
+    x_proj = Dense(C)(rope(x)); ctx = mean_{H,W}(rope(x)) + temporal code (cssm.py:3127-3131);
+    d_X = 0.1 + 0.89 sigmoid(.) (bounded), B_X = C_gate = sigmoid(.), each (B,T,1,H,Wf)
+    (cssm.py:3201-3207, 3224-3228); A = d_X * K_hat, U = rfft2(x_proj) * B_X (cssm.py:3282-3289);
+    h_t = A_t h_{t-1} + U_t from h_0 = 0; irfft2(h * C_gate); Dense output_proj.
+    scan_mode 'associative' is the log-space scan: to_goom floors the magnitudes of A and U at
+    1e-7 (cssm.py:3346-3347); 'ssd' / 'quadratic' / 'pallas' evaluate the same recurrence in
+    plain complex arithmetic (cssm.py:3294-3345), i.e. without the floors.
+    scan='goom' (associative only) runs the literal complex64 log-space operators."""
+    cdt = np.complex128 if dtype == np.float64 else np.complex64
+    x = np.asarray(x, dtype=dtype)
+    B, T, H, W, C = x.shape
+    Wf = W // 2 + 1
+    x = apply_rope(x, rope_mode, rope_base)
+    x_proj = dense(x, params["x_proj"])
+    ctx = x.mean(axis=(2, 3)) + temporal_ctx_code(T, C, rope_base)[None]
+
+    def gate(name, bounded=False):
+        if gate_type == "factored":
+            row = dense(ctx, params[f"{name}_h"])
+            col = dense(ctx, params[f"{name}_w"])
+            raw = sigmoid(row[..., :, None] + col[..., None, :])
+        else:
+            raw = sigmoid(dense(ctx, params[name]))
+        raw = raw.reshape(B, T, 1, H, Wf)
+        return 0.1 + 0.89 * raw if bounded else raw
+
+    d_X, B_X, C_gate = gate("d_X", True), gate("B_X"), gate("C_gate")
+    K_hat = spectral_kernel(params["kernel"], H, W, spectral_rho).astype(cdt)
+    A = d_X.astype(cdt) * K_hat[None, None]
+    U = np.fft.rfft2(x_proj.transpose(0, 1, 4, 2, 3), axes=(3, 4)).astype(cdt) * B_X
+    if scan == "goom":
+        assert scan_mode == "associative"
+        V = goom_scalar_scan(A, U).astype(cdt)
+    else:
+        if scan_mode == "associative":
+            A, U = goom_floor(A), goom_floor(U)
+        h = np.zeros_like(U[:, 0])
+        hs = []
+        for t in range(T):
+            h = A[:, t] * h + U[:, t]
+            hs.append(h)
+        V = np.stack(hs, axis=1)
+    out = np.fft.irfft2(V * C_gate, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2).astype(dtype)
+    return dense(out, params["output_proj"])
+
+
+def init_additive1_params(seed, C, H, W, *, kernel_size=11, gate_type="dense", bias_scale=0.0):
+    """Parameter tree of the single-state AdditiveCSSM (cssm.py:3097, 3113, 3280-3282, 3626):
+    kernel (C,ks,ks) xavier-normal, x_proj, d_X / B_X / C_gate (or their _h / _w factors),
+    output_proj."""
+    rng = np.random.default_rng(seed)
+    Wf = W // 2 + 1
+    std = np.sqrt(2.0 / (2 * kernel_size * C))          # xavier_normal on (C, ks, ks)
+    p = {"kernel": (std * rng.standard_normal((C, kernel_size, kernel_size))).astype(np.float32),
+         "x_proj": _dense_p(rng, C, C, bias_scale),
+         "output_proj": _dense_p(rng, C, C, bias_scale)}
+    for n in ("d_X", "B_X", "C_gate"):
+        if gate_type == "factored":
+            p[f"{n}_h"] = _dense_p(rng, C, H, bias_scale)
+            p[f"{n}_w"] = _dense_p(rng, C, Wf, bias_scale)
+        else:
+            p[n] = _dense_p(rng, C, H * Wf, bias_scale)
+    return p
+
+
 def rms_norm(x, w, eps=1e-6):
     """cssm.py:49-52."""
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps) * w

@@ -62,6 +62,14 @@ def nogate_case():
     return x, p, ks
 
 
+def additive1_case():
+    B, T, H, W, C, ks = 2, 4, 8, 8, 8, 5
+    x = np.random.default_rng(71).standard_normal((B, T, H, W, C)).astype(np.float32)
+    p = orc.init_additive1_params(72, C, H, W, kernel_size=ks, gate_type="factored", bias_scale=0.1)
+    kw = dict(kernel_size=ks, gate_type="factored", rope_mode="spatiotemporal")
+    return x, p, kw
+
+
 def gdn_static_case():
     B, H, W, C, ks, T = 2, 8, 8, 8, 5, 4
     x = np.random.default_rng(61).standard_normal((B, H, W, C)).astype(np.float32)
@@ -89,6 +97,9 @@ def main():
     x, p, ks = nogate_case()
     np.savez_compressed(os.path.join(HERE, "nogate_small.npz"), x=x,
                         y=orc.nogate_forward(p, x, kernel_size=ks).astype(np.float64))
+    x, p, kw = additive1_case()
+    np.savez_compressed(os.path.join(HERE, "additive1_small.npz"), x=x,
+                        y=orc.additive1_forward(p, x, **kw).astype(np.float64))
     x, p, kw = gdn_static_case()
     np.savez_compressed(os.path.join(HERE, "gdn_static_small.npz"), x=x,
                         y=orc.gdn_static_forward(p, x, **kw).astype(np.float64))

@@ -133,6 +133,41 @@ def test_nogate_descriptor_validation_without_gpu():
     assert L.cssm_nogate_forward(C.byref(d), C.byref(w), None, None, None, None, 0, None) == 1
 
 
+def test_additive_descriptor_validation_without_gpu():
+    L = _built()
+
+    def desc(**kw):
+        f = dict(B=2, T=3, H=8, W=8, C=8, kernel_size=3, rope_mode=0, rope_base=10000.0,
+                 spectral_rho=0.999, gate_type=0, single_state=1, goom_floor=1)
+        f.update(kw)
+        return _lib.AdditiveDesc(**f)
+    d = desc()
+    assert L.cssm_additive_plan_bytes(C.byref(d)) >= 8 * 8 * 5 * 8
+    assert L.cssm_additive_workspace_bytes(C.byref(d)) >= 2 * 3 * 2 * 8 * 8 * 8 * 4
+    for bad in (desc(single_state=0), desc(gate_type=2), desc(C=6), desc(B=0), desc(goom_floor=2),
+                desc(rope_mode=9)):
+        assert L.cssm_additive_plan_bytes(C.byref(bad)) == 0
+        assert L.cssm_additive_workspace_bytes(C.byref(bad)) == 0
+    w = _lib.AdditiveWeights()
+    assert L.cssm_additive_forward(C.byref(d), C.byref(w), None, None, None, None, 0, None) == 1
+    assert L.cssm_additive_forward(C.byref(desc(single_state=0)), C.byref(w), None, None, None, None,
+                                   0, None) == 3
+
+
+def test_additive_module_rejects_unbuilt_variants():
+    from cssm_b200 import AdditiveCSSM
+    with pytest.raises(NotImplementedError):
+        AdditiveCSSM(channels=8).init(0, (1, 2, 8, 8, 8))                      # 3-state default
+    with pytest.raises(NotImplementedError):
+        AdditiveCSSM(channels=8, single_state=True, gate_type="channel").init(0, (1, 2, 8, 8, 8))
+    with pytest.raises(NotImplementedError):
+        AdditiveCSSM(channels=8, single_state=True, learned_init=True).init(0, (1, 2, 8, 8, 8))
+    m = AdditiveCSSM(channels=8, single_state=True, gate_type="factored", kernel_size=5)
+    p = m.init(0, (1, 2, 8, 6, 8))["params"]
+    assert p["d_X_h"]["kernel"].shape == (8, 8) and p["C_gate_w"]["kernel"].shape == (8, 4)
+    assert m._floor() == 1 and AdditiveCSSM(channels=8, single_state=True, scan_mode="pallas")._floor() == 0
+
+
 def _simple_desc(**kw):
     d = dict(B=2, T=3, Hin=16, Win=16, Cin=1, image_input=1, stem_mode=0, stem_layers=1, embed_dim=8,
              block=0, pool_type=1, readout_norm=0, num_classes=2)

@@ -183,6 +183,36 @@ def test_torch_cpu_restatement_matches_numpy_oracle():
         assert orc.rel_l2(yt, y) < 1e-5
 
 
+def test_additive1_oracle_scan_forms_agree():
+    """Single-state AdditiveCSSM: the direct recurrence with the floors, the literal complex64
+    log-space scan and the floor-free linear recurrence (ssd / quadratic / pallas modes) agree to
+    fp32 rounding; with the gates forced to constants the block is the ungated recurrence scaled."""
+    rng = np.random.default_rng(9)
+    B, T, H, W, C, ks = 2, 5, 8, 6, 4, 3
+    x = rng.standard_normal((B, T, H, W, C))
+    for gt in ("dense", "factored"):
+        p = orc.init_additive1_params(3, C, H, W, kernel_size=ks, gate_type=gt, bias_scale=0.1)
+        a = orc.additive1_forward(p, x, kernel_size=ks, gate_type=gt, rope_mode="mrope")
+        b = orc.additive1_forward(p, x, kernel_size=ks, gate_type=gt, rope_mode="mrope", scan="goom")
+        c = orc.additive1_forward(p, x, kernel_size=ks, gate_type=gt, rope_mode="mrope", scan_mode="ssd")
+        assert orc.rel_l2(b, a) < 5e-6
+        assert orc.rel_l2(c, a) < 1e-6
+    # zero gate weights: every gate is sigmoid(0) = 0.5 (d_X = 0.545), identity projections
+    p = orc.init_additive1_params(4, C, H, W, kernel_size=ks, gate_type="dense")
+    for n in ("d_X", "B_X", "C_gate"):
+        p[n]["kernel"][:] = 0
+    p["x_proj"] = {"kernel": np.eye(C), "bias": np.zeros(C)}
+    p["output_proj"] = {"kernel": np.eye(C), "bias": np.zeros(C)}
+    y = orc.additive1_forward(p, x, kernel_size=ks, scan_mode="pallas")
+    K = orc.spectral_kernel(p["kernel"], H, W, 0.999)
+    U = np.fft.rfft2(x.transpose(0, 1, 4, 2, 3), axes=(3, 4))
+    h = np.zeros_like(U[:, 0])
+    for t in range(T):
+        h = 0.545 * K[None] * h + 0.5 * U[:, t]
+        ref_t = np.fft.irfft2(0.5 * h, s=(H, W), axes=(2, 3)).transpose(0, 2, 3, 1)
+        assert np.allclose(y[:, t], ref_t, atol=1e-12)
+
+
 def test_nogate_oracle_is_a_circular_convolution_recurrence():
     """NoGateCSSM in the spatial domain: s_t = k (*) s_{t-1} + x_t with circular convolution by the
     inverse transform of the squashed kernel spectrum."""
@@ -244,6 +274,10 @@ def test_golden_vectors_of_the_widened_paths():
     x, p, ks = mg.nogate_case()
     assert np.array_equal(x, g["x"])
     assert orc.rel_l2(orc.nogate_forward(p, x, kernel_size=ks), g["y"]) < 1e-12
+    g = np.load(os.path.join(GOLDEN, "additive1_small.npz"))
+    x, p, kw = mg.additive1_case()
+    assert np.array_equal(x, g["x"])
+    assert orc.rel_l2(orc.additive1_forward(p, x, **kw), g["y"]) < 1e-12
     g = np.load(os.path.join(GOLDEN, "gdn_static_small.npz"))
     x, p, kw = mg.gdn_static_case()
     assert np.array_equal(x, g["x"])
