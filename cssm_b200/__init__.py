@@ -5,7 +5,7 @@ This package holds the ctypes binding and host-side mirrors of the reference's F
 modules.  Importing the package does not load the library; the first compute call does and
 raises if it has not been built."""
 from ._lib import CssmError, lib  # noqa: F401
-from .modules import AdditiveCSSM, GatedCSSM, GatedDeltaNetCSSM, NoGateCSSM  # noqa: F401
+from .modules import AdditiveCSSM, DeltaNetCSSM, GatedCSSM, GatedDeltaNetCSSM, NoGateCSSM  # noqa: F401
 from .simple import SimpleCSSM  # noqa: F401
 
-__all__ = ["GatedCSSM", "GatedDeltaNetCSSM", "NoGateCSSM", "AdditiveCSSM", "SimpleCSSM", "CssmError", "lib"]
+__all__ = ["GatedCSSM", "GatedDeltaNetCSSM", "NoGateCSSM", "AdditiveCSSM", "DeltaNetCSSM", "SimpleCSSM", "CssmError", "lib"]

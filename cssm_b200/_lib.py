@@ -84,6 +84,19 @@ class AdditiveWeights(C.Structure):
                 ("output_proj_kernel", C.c_void_p), ("output_proj_bias", C.c_void_p)]
 
 
+class DeltaNetDesc(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("W", C.c_int32),
+                ("C", C.c_int32), ("kernel_size", C.c_int32), ("rope_mode", C.c_int32),
+                ("rope_base", C.c_float), ("spectral_rho", C.c_float), ("gate_type", C.c_int32),
+                ("goom_floor", C.c_int32)]
+
+
+class DeltaNetWeights(C.Structure):
+    _fields_ = [("kernel", C.c_void_p), ("qkv_proj_kernel", C.c_void_p), ("qkv_proj_bias", C.c_void_p),
+                ("gate_kernel", C.c_void_p * 10), ("gate_bias", C.c_void_p * 10),
+                ("output_proj_kernel", C.c_void_p), ("output_proj_bias", C.c_void_p)]
+
+
 class SimpleDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("B", "T", "Hin", "Win", "Cin", "image_input", "stem_mode", "stem_layers",
@@ -143,6 +156,12 @@ SIGNATURES = {
     "cssm_additive_plan_init": (C.c_int, [C.POINTER(AdditiveDesc), C.POINTER(AdditiveWeights), _P,
                                           C.c_size_t, _P]),
     "cssm_additive_forward": (C.c_int, [C.POINTER(AdditiveDesc), C.POINTER(AdditiveWeights), _P, _P,
+                                        _P, _P, C.c_size_t, _P]),
+    "cssm_deltanet_plan_bytes": (C.c_size_t, [C.POINTER(DeltaNetDesc)]),
+    "cssm_deltanet_workspace_bytes": (C.c_size_t, [C.POINTER(DeltaNetDesc)]),
+    "cssm_deltanet_plan_init": (C.c_int, [C.POINTER(DeltaNetDesc), C.POINTER(DeltaNetWeights), _P,
+                                          C.c_size_t, _P]),
+    "cssm_deltanet_forward": (C.c_int, [C.POINTER(DeltaNetDesc), C.POINTER(DeltaNetWeights), _P, _P,
                                         _P, _P, C.c_size_t, _P]),
     "cssm_simple_workspace_bytes": (C.c_size_t, [C.POINTER(SimpleDesc), _P]),
     "cssm_simple_stem": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P, _P,

@@ -10,6 +10,7 @@
 #include "fft.cuh"
 #include "kernels.cuh"
 #include "gdn_common.cuh"
+#include "generic_dft.cuh"
 
 namespace cssm {
 
@@ -27,52 +28,6 @@ __device__ __forceinline__ cf gdn_bin_update(cf* S, size_t ss, int dk, const cf*
 }
 
 // ================================================================ generic planes ====
-constexpr int GG_THREADS = 256;
-
-__device__ void gen_fwd_plane(const float* __restrict__ plane, float* xs, cf* Rb, cf* out,
-                              const cf* twW, const cf* twH, int H, int W) {
-  const int Wf = W / 2 + 1, HW = H * W, NB = H * Wf, tid = threadIdx.x;
-  __syncthreads();
-  for (int i = tid; i < HW; i += GG_THREADS) xs[i] = plane[i];
-  __syncthreads();
-  for (int o = tid; o < NB; o += GG_THREADS) {
-    const int h = o / Wf, kw = o % Wf;
-    float ax = 0.f, ay = 0.f;
-    int idx = 0;
-    for (int w = 0; w < W; ++w) {
-      const cf e = twW[idx];
-      const float xv = xs[h * W + w];
-      ax += xv * e.x; ay += xv * e.y;
-      idx += kw; if (idx >= W) idx -= W;
-    }
-    Rb[o] = mk(ax, ay);
-  }
-  __syncthreads();
-  for (int o = tid; o < NB; o += GG_THREADS) {
-    const int kh = o / Wf, kw = o % Wf;
-    float ax = 0.f, ay = 0.f;
-    int idx = 0;
-    for (int h = 0; h < H; ++h) {
-      const cf e = twH[idx];
-      const cf r = Rb[h * Wf + kw];
-      ax += r.x * e.x - r.y * e.y; ay += r.x * e.y + r.y * e.x;
-      idx += kh; if (idx >= H) idx -= H;
-    }
-    out[o] = mk(ax, ay);
-  }
-}
-
-__device__ float block_sum(float v, float* red) {
-  const int tid = threadIdx.x;
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-  __syncthreads();
-  if ((tid & 31) == 0) red[tid >> 5] = v;
-  __syncthreads();
-  float tot = 0.f;
-  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
-  return tot;
-}
-
 __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpectralArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int H = a.H, W = a.W, dk = a.dk;

@@ -810,3 +810,162 @@ class BoundAdditive:
                                            y.data_ptr(), ws.data_ptr(), n, _stream_ptr(self.device)),
               "cssm_additive_forward")
         return y
+
+
+# ============================================================================ DeltaNet (scalar)
+@dataclass
+class DeltaNetCSSM:
+    """Scalar spectral delta rule (reference: DeltaNetCSSM, src/models/cssm.py:3628-3930).
+    Field names and defaults are the reference's.  The CUDA path covers gate_type 'dense' and
+    'factored'; the reference's default 'channel' (spatial 1x1-conv gates) and the other gate
+    types raise NotImplementedError, as do learned_init, position_independent_gates and the
+    bf16 / fp8 split scans (no fallback)."""
+    channels: int
+    kernel_size: int = 11
+    rope_mode: str = "none"
+    rope_base: float = 10000.0
+    spectral_rho: float = 0.999
+    position_independent_gates: bool = False
+    block_size: int = 1
+    gate_type: str = "channel"
+    use_goom: bool = True
+    use_complex32: bool = False
+    use_complex16: bool = False
+    scan_mode: str = "associative"
+    ssd_chunk_size: int = 8
+    learned_init: bool = False
+    name: Optional[str] = None
+    _bound: Dict[Any, Any] = field(default_factory=dict, repr=False, compare=False)
+
+    GATES = ("alpha", "beta", "B_k", "B_v", "C_gate")
+
+    def _check(self):
+        if self.gate_type not in ("dense", "factored"):
+            raise NotImplementedError(f"DeltaNetCSSM: gate_type {self.gate_type!r} not built "
+                                      "(supported: 'dense', 'factored')")
+        if self.rope_mode not in ROPE_MODES:
+            raise NotImplementedError(f"DeltaNetCSSM: rope_mode {self.rope_mode!r} not built")
+        if self.position_independent_gates or self.learned_init:
+            raise NotImplementedError("DeltaNetCSSM: position_independent_gates / learned_init not built")
+        if self.use_complex32 or self.use_complex16:
+            raise NotImplementedError("DeltaNetCSSM: the bf16 / fp8 linear-split scans are not built")
+        if self.scan_mode not in ("associative", "ssd", "quadratic", "pallas"):
+            raise ValueError(f"DeltaNetCSSM: unknown scan_mode {self.scan_mode!r}")
+        if not self.use_goom and self._floor():
+            raise NotImplementedError("DeltaNetCSSM: use_goom=False with the associative scan not built")
+
+    def _floor(self) -> int:
+        return 1 if self.scan_mode == "associative" else 0
+
+    def param_shapes(self, H: int, W: int) -> Dict[str, Any]:
+        Cc, Wf = self.channels, W // 2 + 1
+        p = {"kernel": (Cc, self.kernel_size, self.kernel_size),
+             "qkv_proj": {"kernel": (Cc, 3 * Cc), "bias": (3 * Cc,)},
+             "output_proj": {"kernel": (Cc, Cc), "bias": (Cc,)}}
+        for n in self.GATES:
+            if self.gate_type == "factored":
+                p[f"{n}_h"] = {"kernel": (Cc, H), "bias": (H,)}
+                p[f"{n}_w"] = {"kernel": (Cc, Wf), "bias": (Wf,)}
+            else:
+                p[n] = {"kernel": (Cc, H * Wf), "bias": (H * Wf,)}
+        return p
+
+    def init(self, seed: int, x_shape, bias_scale: float = 0.0) -> Dict[str, Any]:
+        """Seeded stand-ins for the Flax initialisers, in the reference's parameter tree."""
+        self._check()
+        _, _, H, W, _ = x_shape
+        rng = np.random.default_rng(seed)
+
+        def fill(shape_tree, name=""):
+            if isinstance(shape_tree, dict):
+                return {k: fill(v, k) for k, v in shape_tree.items()}
+            if name == "bias":
+                return (bias_scale * rng.standard_normal(shape_tree)).astype(np.float32)
+            fan_in = shape_tree[0] if len(shape_tree) == 2 else self.kernel_size * self.channels
+            return (rng.standard_normal(shape_tree) / np.sqrt(fan_in)).astype(np.float32)
+        return {"params": fill(self.param_shapes(H, W))}
+
+    def bind(self, variables, device="cuda") -> "BoundDeltaNet":
+        self._check()
+        return BoundDeltaNet(self, variables["params"] if "params" in variables else variables,
+                             torch.device(device))
+
+    def apply(self, variables, x, injected_qkv_spatial=None):
+        # the reference ignores injected_qkv_spatial in this block (cssm.py:3675-3676)
+        key = id(variables)
+        bound = self._bound.get(key)
+        if bound is None or bound.variables_ref is not variables:
+            _require_cuda(x)
+            bound = self.bind(variables, x.device)
+            bound.variables_ref = variables
+            self._bound.clear()
+            self._bound[key] = bound
+        return bound(x)
+
+
+class BoundDeltaNet:
+    """A DeltaNetCSSM with its weights on one GPU and its plan cached per (T, H, W)."""
+
+    def __init__(self, mod: DeltaNetCSSM, params, device):
+        self.mod, self.device, self.variables_ref = mod, device, None
+        self.L = _lib.lib()
+        self.t: Dict[str, torch.Tensor] = {}
+        w = _lib.DeltaNetWeights()
+        w.kernel = self._put("kernel", params["kernel"])
+        w.qkv_proj_kernel = self._put("qk", params["qkv_proj"]["kernel"])
+        w.qkv_proj_bias = self._put("qb", params["qkv_proj"]["bias"])
+        w.output_proj_kernel = self._put("ok", params["output_proj"]["kernel"])
+        w.output_proj_bias = self._put("ob", params["output_proj"]["bias"])
+        names = ([f"{n}_{s}" for n in mod.GATES for s in ("h", "w")]
+                 if mod.gate_type == "factored" else list(mod.GATES))
+        for i, n in enumerate(names):
+            if n not in params:
+                raise KeyError(f"DeltaNetCSSM: parameter {n!r} missing (gate_type={mod.gate_type!r})")
+            w.gate_kernel[i] = self._put(f"gk{i}", params[n]["kernel"])
+            w.gate_bias[i] = self._put(f"gb{i}", params[n]["bias"])
+        self.w = w
+        self.buf = _Buffers(device)
+        self._plans: Dict[Any, torch.Tensor] = {}
+
+    def _put(self, key, arr) -> int:
+        self.t[key] = _dev_f32(arr, self.device)
+        return self.t[key].data_ptr()
+
+    def desc(self, shape):
+        B, T, H, W, Cc = shape
+        m = self.mod
+        if Cc != m.channels:
+            raise ValueError(f"x has {Cc} channels, module has {m.channels}")
+        Wf = W // 2 + 1
+        gshape = tuple(self.t["gk0"].shape)
+        want = (Cc, H) if m.gate_type == "factored" else (Cc, H * Wf)
+        if gshape != want:
+            raise ValueError(f"DeltaNetCSSM: gate weights {gshape} were made for another plane size "
+                             f"(this input needs {want})")
+        return _lib.DeltaNetDesc(B, T, H, W, Cc, m.kernel_size, ROPE_MODES[m.rope_mode],
+                                 float(m.rope_base), float(m.spectral_rho), GATE_TYPES[m.gate_type],
+                                 m._floor())
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x)
+        if x.dim() != 5:
+            raise ValueError("DeltaNetCSSM expects (B,T,H,W,C)")
+        x = x.contiguous()
+        d = self.desc(tuple(x.shape))
+        key = (d.T, d.H, d.W)
+        pl = self._plans.get(key)
+        if pl is None:
+            n = self.L.cssm_deltanet_plan_bytes(C.byref(d))
+            if n == 0:
+                raise NotImplementedError("DeltaNetCSSM: no CUDA kernel for this shape")
+            pl = torch.empty(n, dtype=torch.uint8, device=self.device)
+            check(self.L.cssm_deltanet_plan_init(C.byref(d), C.byref(self.w), pl.data_ptr(), n,
+                                                 _stream_ptr(self.device)), "cssm_deltanet_plan_init")
+            self._plans[key] = pl
+        n = self.L.cssm_deltanet_workspace_bytes(C.byref(d))
+        ws = self.buf.get("ws", n)
+        y = torch.empty_like(x) if out is None else out
+        check(self.L.cssm_deltanet_forward(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(),
+                                           y.data_ptr(), ws.data_ptr(), n, _stream_ptr(self.device)),
+              "cssm_deltanet_forward")
+        return y

@@ -326,6 +326,51 @@ int cssm_additive_forward(const cssm_additive_desc* d, const cssm_additive_weigh
                           const void* plan, const float* x, float* y, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* ================================================================== DeltaNetCSSM ====
+ * The scalar spectral delta rule (src/models/cssm.py:3628-3930): RoPE (optional) -> Dense
+ * qkv_proj -> rfft2 of q, k, v per channel; k and v times the spectral input gates B_k, B_v; q
+ * and k L2-normalised over the (H, W/2+1) bins of their plane (eps 1e-6 under the root);
+ *   A_t = squash(alpha_t W_hat (1 - beta_t |k_t|^2)),  U_t = beta_t v_t conj(k_t),
+ *   h_t = A_t h_{t-1} + U_t (h_0 = 0),  o_t = C_gate,t h_t q_t  -> irfft2 -> Dense output_proj.
+ * Gates from ctx = mean_{H,W}(rotated x) + temporal code: alpha = 0.1 + 0.89 sigmoid(.), the
+ * others sigmoid(.), per-bin maps shared by the channels; gate_type 'dense' or 'factored'
+ * (cssm.py:3756-3793).  Replaces every scan_mode of the block (cssm.py:3818-3912); goom_floor
+ * as for the additive block (floors on A_t and U_t).  The reference's default gate_type
+ * 'channel' (1x1-conv spatial gates), 'scalar', learned_init, position_independent_gates and
+ * the bf16 / fp8 split scans are rejected. */
+typedef struct cssm_deltanet_desc {
+  int32_t B, T, H, W, C;
+  int32_t kernel_size;
+  int32_t rope_mode;        /* CSSM_ROPE_* */
+  float   rope_base;        /* 10000 */
+  float   spectral_rho;     /* 0.999 */
+  int32_t gate_type;        /* CSSM_GATE_DENSE or CSSM_GATE_FACTORED */
+  int32_t goom_floor;       /* 1: scan_mode 'associative' with use_goom; 0: linear scan modes */
+} cssm_deltanet_desc;
+
+typedef struct cssm_deltanet_weights {
+  const float* kernel;              /* (C, ks, ks)                                            */
+  const float* qkv_proj_kernel;     /* (C, 3C)                                                */
+  const float* qkv_proj_bias;       /* (3C)                                                   */
+  /* dense: [0..4] = alpha, beta, B_k, B_v, C_gate, kernels (C, H*Wf), biases (H*Wf).
+     factored: [0..9] = alpha_h, alpha_w, beta_h, beta_w, B_k_h, B_k_w, B_v_h, B_v_w, C_gate_h,
+     C_gate_w, kernels (C,H) / (C,Wf) */
+  const float* gate_kernel[10];
+  const float* gate_bias[10];
+  const float* output_proj_kernel;  /* (C, C)                                                 */
+  const float* output_proj_bias;    /* (C)                                                    */
+} cssm_deltanet_weights;
+
+size_t cssm_deltanet_plan_bytes(const cssm_deltanet_desc* d);
+size_t cssm_deltanet_workspace_bytes(const cssm_deltanet_desc* d);
+/* W_hat = squash(rfft2(pad(kernel))) (cssm.py:3712-3732), RoPE tables, temporal code. */
+int cssm_deltanet_plan_init(const cssm_deltanet_desc* d, const cssm_deltanet_weights* w, void* plan,
+                            size_t plan_bytes, void* stream);
+/* y = DeltaNetCSSM(x); x, y: (B,T,H,W,C) fp32 channels-last. */
+int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weights* w,
+                          const void* plan, const float* x, float* y, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 /* ================================================================ SimpleCSSM model ====
  * Inference forward of the reference's SimpleCSSM wrapper around ONE block (depth 1):
  *   stem -> x + block(x) -> last frame -> norm_pre/act -> spatial pool -> norm_post -> head.

@@ -70,6 +70,15 @@ def additive1_case():
     return x, p, kw
 
 
+def deltanet_case():
+    B, T, H, W, C, ks = 2, 4, 8, 8, 8, 5
+    x = np.random.default_rng(81).standard_normal((B, T, H, W, C)).astype(np.float32)
+    p = orc.init_deltanet_params(82, C, H, W, kernel_size=ks, gate_type="dense", bias_scale=0.1)
+    p["output_proj"]["bias"][:] = 0          # the signal is small next to a 0.1-scale bias
+    kw = dict(kernel_size=ks, gate_type="dense", rope_mode="mrope")
+    return x, p, kw
+
+
 def gdn_static_case():
     B, H, W, C, ks, T = 2, 8, 8, 8, 5, 4
     x = np.random.default_rng(61).standard_normal((B, H, W, C)).astype(np.float32)
@@ -100,6 +109,9 @@ def main():
     x, p, kw = additive1_case()
     np.savez_compressed(os.path.join(HERE, "additive1_small.npz"), x=x,
                         y=orc.additive1_forward(p, x, **kw).astype(np.float64))
+    x, p, kw = deltanet_case()
+    np.savez_compressed(os.path.join(HERE, "deltanet_small.npz"), x=x,
+                        y=orc.deltanet_forward(p, x, **kw).astype(np.float64))
     x, p, kw = gdn_static_case()
     np.savez_compressed(os.path.join(HERE, "gdn_static_small.npz"), x=x,
                         y=orc.gdn_static_forward(p, x, **kw).astype(np.float64))

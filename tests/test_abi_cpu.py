@@ -168,6 +168,29 @@ def test_additive_module_rejects_unbuilt_variants():
     assert m._floor() == 1 and AdditiveCSSM(channels=8, single_state=True, scan_mode="pallas")._floor() == 0
 
 
+def test_deltanet_descriptor_validation_without_gpu():
+    L = _built()
+
+    def desc(**kw):
+        f = dict(B=2, T=3, H=8, W=8, C=8, kernel_size=3, rope_mode=0, rope_base=10000.0,
+                 spectral_rho=0.999, gate_type=1, goom_floor=1)
+        f.update(kw)
+        return _lib.DeltaNetDesc(**f)
+    d = desc()
+    assert L.cssm_deltanet_plan_bytes(C.byref(d)) >= 8 * 8 * 5 * 8
+    assert L.cssm_deltanet_workspace_bytes(C.byref(d)) >= 2 * 3 * 3 * 8 * 8 * 8 * 4
+    for bad in (desc(gate_type=2), desc(C=6), desc(T=0), desc(goom_floor=-1), desc(rope_mode=9),
+                desc(H=128, W=128)):                     # plane too large for one CTA's shared memory
+        assert L.cssm_deltanet_plan_bytes(C.byref(bad)) == 0
+    w = _lib.DeltaNetWeights()
+    assert L.cssm_deltanet_forward(C.byref(d), C.byref(w), None, None, None, None, 0, None) == 1
+    from cssm_b200 import DeltaNetCSSM
+    with pytest.raises(NotImplementedError):
+        DeltaNetCSSM(channels=8).init(0, (1, 2, 8, 8, 8))          # default gate_type 'channel'
+    p = DeltaNetCSSM(channels=8, gate_type="factored").init(0, (1, 2, 8, 6, 8))["params"]
+    assert p["qkv_proj"]["kernel"].shape == (8, 24) and p["B_v_w"]["kernel"].shape == (8, 4)
+
+
 def _simple_desc(**kw):
     d = dict(B=2, T=3, Hin=16, Win=16, Cin=1, image_input=1, stem_mode=0, stem_layers=1, embed_dim=8,
              block=0, pool_type=1, readout_norm=0, num_classes=2)

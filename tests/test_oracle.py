@@ -213,6 +213,29 @@ def test_additive1_oracle_scan_forms_agree():
         assert np.allclose(y[:, t], ref_t, atol=1e-12)
 
 
+def test_deltanet_oracle_scan_forms_and_erasure():
+    """DeltaNetCSSM: direct recurrence, literal log-space scan and floor-free recurrence agree;
+    |A_t| < rho everywhere (the squash); with beta = 0 nothing is written, so the output is the
+    output bias alone."""
+    rng = np.random.default_rng(10)
+    B, T, H, W, C, ks = 2, 5, 8, 6, 4, 3
+    x = rng.standard_normal((B, T, H, W, C))
+    for gt in ("dense", "factored"):
+        p = orc.init_deltanet_params(5, C, H, W, kernel_size=ks, gate_type=gt, bias_scale=0.1)
+        p["output_proj"]["bias"][:] = 0
+        a = orc.deltanet_forward(p, x, kernel_size=ks, gate_type=gt, rope_mode="spatiotemporal")
+        b = orc.deltanet_forward(p, x, kernel_size=ks, gate_type=gt, rope_mode="spatiotemporal", scan="goom")
+        c = orc.deltanet_forward(p, x, kernel_size=ks, gate_type=gt, rope_mode="spatiotemporal", scan_mode="ssd")
+        assert np.abs(a).max() > 1e-4
+        assert orc.rel_l2(b, a) < 5e-6
+        assert orc.rel_l2(c, a) < 1e-6
+    p = orc.init_deltanet_params(6, C, H, W, kernel_size=ks, gate_type="dense", bias_scale=0.1)
+    p["beta"]["kernel"][:] = 0
+    p["beta"]["bias"][:] = -60.0                      # sigmoid -> 1e-26
+    y = orc.deltanet_forward(p, x, kernel_size=ks, scan_mode="pallas")
+    assert np.allclose(y, np.broadcast_to(p["output_proj"]["bias"], y.shape), atol=1e-12)
+
+
 def test_nogate_oracle_is_a_circular_convolution_recurrence():
     """NoGateCSSM in the spatial domain: s_t = k (*) s_{t-1} + x_t with circular convolution by the
     inverse transform of the squashed kernel spectrum."""
@@ -278,6 +301,10 @@ def test_golden_vectors_of_the_widened_paths():
     x, p, kw = mg.additive1_case()
     assert np.array_equal(x, g["x"])
     assert orc.rel_l2(orc.additive1_forward(p, x, **kw), g["y"]) < 1e-12
+    g = np.load(os.path.join(GOLDEN, "deltanet_small.npz"))
+    x, p, kw = mg.deltanet_case()
+    assert np.array_equal(x, g["x"])
+    assert orc.rel_l2(orc.deltanet_forward(p, x, **kw), g["y"]) < 1e-12
     g = np.load(os.path.join(GOLDEN, "gdn_static_small.npz"))
     x, p, kw = mg.gdn_static_case()
     assert np.array_equal(x, g["x"])
