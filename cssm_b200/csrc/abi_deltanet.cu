@@ -14,9 +14,9 @@ namespace cssm {
 
 struct DnGateArgs {
   const float* ctx_part; const float* tcode;   // (BT,H,C) row sums of the rotated input, (T,C)
-  int BT, T, C, H, W, gate_type;
+  int BT, T, C, H, W, gate_type, path;
   const float* gk[10]; const float* gb[10];    // alpha, beta, B_k, B_v, C_gate (x {h, w} if factored)
-  float4* abkv;                                // (BT, H*Wf) {alpha, beta, B_k, B_v}
+  float4* abkv;                                // (BT, H*Wf) {alpha, beta, B_k, B_v} at bin_index(path, ...)
   float* cg;                                   // (BT, H*Wf) C_gate / (H*W)
 };
 
@@ -68,20 +68,12 @@ __global__ void __launch_bounds__(256) deltanet_gates_kernel(const DnGateArgs g)
         r[gi] = acc;
       }
     }
-    g.abkv[(size_t)fr * NB + bin] = make_float4(0.1f + 0.89f * dn_sigmoid(r[0]), dn_sigmoid(r[1]),
+    const size_t oi = (size_t)fr * NB + bin_index(g.path, kh, kw, g.H, Wf);
+    g.abkv[oi] = make_float4(0.1f + 0.89f * dn_sigmoid(r[0]), dn_sigmoid(r[1]),
                                                 dn_sigmoid(r[2]), dn_sigmoid(r[3]));
-    g.cg[(size_t)fr * NB + bin] = dn_sigmoid(r[4]) * inv;
+    g.cg[oi] = dn_sigmoid(r[4]) * inv;
   }
 }
-
-struct DnSpectralArgs {
-  float* qkv;               // planar (BT, 3C, H, W): q, k, v; the output overwrites the v planes
-  const cf* what;           // (C, H*Wf) squashed kernel spectrum, natural bin order
-  const float4* abkv; const float* cg;
-  int B, T, C, H, W;
-  float rho;
-  int goom_floor;
-};
 
 __global__ void __launch_bounds__(GG_THREADS) deltanet_spectral_kernel(const DnSpectralArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -165,6 +157,10 @@ static size_t deltanet_smem_bytes(int H, int W) {
   return fl * 4 + (W + H + 5 * NB) * sizeof(cf);
 }
 
+static int deltanet_path(const cssm_deltanet_desc& d) {
+  return spectral_path(d.H, d.W) == PATH_R64 ? PATH_R64 : PATH_GENERIC;
+}
+
 static int deltanet_validate(const cssm_deltanet_desc* d) {
   if (!d) return CSSM_ERR_NULL;
   if (d->B <= 0 || d->T <= 0 || d->H <= 0 || d->W <= 0 || d->C <= 0 || d->kernel_size <= 0)
@@ -234,7 +230,7 @@ int cssm_deltanet_plan_init(const cssm_deltanet_desc* d, const cssm_deltanet_wei
   char* base = (char*)plan;
   // W_hat is squashed but not floored: the floor of the log-space scan acts on A_t and U_t
   s = launch_khat(w->kernel, (cf*)(base + p.what), d->C, d->kernel_size, d->H, d->W,
-                  d->spectral_rho, 1, 0, PATH_GENERIC, st);
+                  d->spectral_rho, 1, 0, deltanet_path(*d), st);
   if (s != CSSM_OK) return s;
   s = launch_rope_tables((float2*)(base + p.rope_t), (float2*)(base + p.rope_h),
                          (float2*)(base + p.rope_w), (float*)(base + p.rope_nz), d->T, d->H, d->W,
@@ -294,6 +290,7 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   memset(&ga, 0, sizeof(ga));
   ga.ctx_part = dw.ctx_part; ga.tcode = (const float*)(pl + p.tcode);
   ga.BT = BT; ga.T = d->T; ga.C = C; ga.H = d->H; ga.W = d->W; ga.gate_type = d->gate_type;
+  ga.path = deltanet_path(*d);
   for (int i = 0; i < nptr; ++i) { ga.gk[i] = w->gate_kernel[i]; ga.gb[i] = w->gate_bias[i]; }
   ga.abkv = (float4*)(ws + l.abkv); ga.cg = (float*)(ws + l.cg);
   {
@@ -315,7 +312,9 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   sp.qkv = qkv; sp.what = (const cf*)(pl + p.what); sp.abkv = ga.abkv; sp.cg = ga.cg;
   sp.B = d->B; sp.T = d->T; sp.C = C; sp.H = d->H; sp.W = d->W;
   sp.rho = d->spectral_rho; sp.goom_floor = d->goom_floor;
-  {
+  if (deltanet_path(*d) == PATH_R64) {
+    if ((s = launch_deltanet_spectral_r64(sp, st)) != CSSM_OK) return s;
+  } else {
     const size_t smem = deltanet_smem_bytes(d->H, d->W);
     cudaError_t e = cudaFuncSetAttribute(deltanet_spectral_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

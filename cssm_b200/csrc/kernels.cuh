@@ -52,6 +52,18 @@ size_t generic_smem_bytes(int H, int W);
 int read_spec_error(int* out);
 int read_ws_error(int* out);
 
+// ---- DeltaNet block (scalar delta rule) ----
+struct DnSpectralArgs {
+  float* qkv;               // planar (BT, 3C, H, W): q, k, v; the output overwrites the v planes
+  const cf* what;           // (C, H*Wf) squashed kernel spectrum, bins at bin_index(path, ...)
+  const float4* abkv;       // (BT, H*Wf) {alpha, beta, B_k, B_v}, same bin order
+  const float* cg;          // (BT, H*Wf) C_gate / (H*W)
+  int B, T, C, H, W;
+  float rho;
+  int goom_floor;
+};
+int launch_deltanet_spectral_r64(const DnSpectralArgs& a, cudaStream_t st);
+
 // ---- GDN block ----
 struct GdnDwArgs {
   const float* x; float* out;            // channels-last (BT, H, W, C); out may be nullptr

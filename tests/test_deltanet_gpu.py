@@ -32,8 +32,9 @@ def _run(case, gate_type, rope, scan_mode="associative", seed=0):
 
 
 @pytest.mark.parametrize("case,gate_type,rope", [
-    ((2, 4, 64, 64, 64, 11), "factored", "spatiotemporal"),   # tensor-core GEMMs
-    ((1, 3, 64, 64, 8, 11), "dense", "none"),
+    ((2, 4, 64, 64, 64, 11), "factored", "spatiotemporal"),   # 64x64 radix kernel, tensor-core GEMMs
+    ((1, 3, 64, 64, 8, 11), "dense", "none"),                 # 64x64 radix kernel, dense gates
+    ((3, 9, 64, 64, 4, 5), "factored", "mrope"),              # 64x64, nine steps of state
     ((3, 6, 32, 32, 8, 11), "dense", "mrope"),
     ((2, 3, 14, 10, 12, 3), "factored", "spatial_only"),      # ragged plane
     ((2, 5, 16, 16, 8, 7), "dense", "temporal"),
@@ -46,6 +47,7 @@ def test_block_parity(case, gate_type, rope):
 @pytest.mark.parametrize("scan_mode", ["ssd", "quadratic", "pallas"])
 def test_linear_scan_modes(scan_mode):
     assert _run((2, 6, 32, 32, 8, 5), "factored", "spatiotemporal", scan_mode=scan_mode) <= TOL
+    assert _run((1, 4, 64, 64, 8, 5), "dense", "none", scan_mode=scan_mode, seed=2) <= TOL
 
 
 def test_long_sequence_state():
