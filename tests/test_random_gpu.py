@@ -1,4 +1,4 @@
-"""Seeded random sweep over shapes and fields of the four module mirrors on the GPU, each case
+"""Seeded random sweeps over shapes and fields of the six module mirrors on the GPU, each case
 checked against the NumPy oracle (rel-L2 <= 1e-4, fp32), including the last-frame-only calls."""
 import numpy as np
 import pytest
@@ -6,7 +6,8 @@ import torch
 
 from oracle import cssm_oracle as orc
 from oracle import simple_oracle as so
-from cssm_b200 import GatedCSSM, GatedDeltaNetCSSM, NoGateCSSM, SimpleCSSM
+from cssm_b200 import (AdditiveCSSM, DeltaNetCSSM, GatedCSSM, GatedDeltaNetCSSM, NoGateCSSM,
+                       SimpleCSSM)
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-4
@@ -97,3 +98,45 @@ def test_random_configuration(seed):
         got = got.cpu().numpy()
         assert np.isfinite(got).all()
         assert orc.rel_l2(got, ref) <= TOL
+
+
+def _scalar_case(seed):
+    """Single-state AdditiveCSSM / DeltaNetCSSM with random shape, gates, RoPE and scan mode."""
+    rng = np.random.default_rng(seed)
+
+    def pick(*a):
+        return a[rng.integers(len(a))]
+
+    kind = pick("additive", "deltanet")
+    size = pick("rand", "rand", "r32", "r64")
+    H, W = {"r32": (32, 32), "r64": (64, 64)}.get(size, (int(rng.integers(3, 19)), int(rng.integers(3, 19))))
+    B, T = int(rng.integers(1, 4)), int(rng.integers(1, 7))
+    C = int(pick(4, 8, 12, 16)) if size == "rand" else int(pick(4, 8, 64))
+    if C == 64:
+        B, T = 1, int(rng.integers(1, 4))
+    ks = int(pick(1, 3, 5, 7, 11))
+    if (ks > H) != (ks > W):
+        ks = 1
+    rope = pick("none", "spatiotemporal", "mrope", "temporal", "spatial_only")
+    gate = pick("factored", "dense")
+    mode = pick("associative", "associative", "ssd", "quadratic", "pallas")
+    x = rng.standard_normal((B, T, H, W, C)).astype(np.float32)
+    kw = dict(kernel_size=ks, gate_type=gate, rope_mode=rope, scan_mode=mode)
+    if kind == "additive":
+        p = orc.init_additive1_params(seed, C, H, W, kernel_size=ks, gate_type=gate, bias_scale=0.1)
+        ref = orc.additive1_forward(p, x, **kw)
+        mod = AdditiveCSSM(channels=C, single_state=True, **kw)
+    else:
+        p = orc.init_deltanet_params(seed, C, H, W, kernel_size=ks, gate_type=gate, bias_scale=0.1)
+        p["output_proj"]["bias"][:] = 0
+        ref = orc.deltanet_forward(p, x, **kw)
+        mod = DeltaNetCSSM(channels=C, **kw)
+    return mod.apply({"params": p}, torch.from_numpy(x).cuda()), ref
+
+
+@pytest.mark.parametrize("seed", range(200, 232))
+def test_random_scalar_scan_configuration(seed):
+    got, ref = _scalar_case(seed)
+    got = got.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert orc.rel_l2(got, ref) <= TOL
