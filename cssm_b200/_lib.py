@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(HERE, "libcssm_b200.so")
 
 ROPE_MODES = {"none": 0, "spatiotemporal": 1, "temporal": 2, "spatial_only": 3, "mrope": 4}
 GATE_TYPES = {"dense": 0, "factored": 1}
+DELTANET_GATE_TYPES = {"dense": 0, "factored": 1, "channel": 2}   # CSSM_GATE_CHANNEL: DeltaNet only
 GATE_ACTS = {"softplus": 0, "sigmoid": 1, "exp": 2}
 
 

@@ -106,6 +106,9 @@ __global__ void __launch_bounds__(GG_THREADS) deltanet_spectral_kernel(const DnS
     float* base = a.qkv + frame * 3 * a.C * HW;
     const float4* gm = a.abkv + frame * NB;
     const float* cg = a.cg + frame * NB;
+    const bool chan = a.chan != nullptr;
+    const float2 ab = chan ? a.chan[frame * a.C + ch] : make_float2(0.f, 0.f);
+    const float invHW = 1.0f / (float)HW;
     // q: spectrum and its L2 norm over the half-spectrum bins
     gen_fwd_plane(base + (size_t)ch * HW, xs, Rb, SQ, twW, twH, H, W);
     float p = 0.f;
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(GG_THREADS) deltanet_spectral_kernel(const DnS
     gen_fwd_plane(base + (size_t)(a.C + ch) * HW, xs, Rb, SK, twW, twH, H, W);
     p = 0.f;
     for (int o = tid; o < NB; o += GG_THREADS) {
-      const float bk = gm[o].z;
+      const float bk = chan ? 1.f : gm[o].z;
       const cf z = mk(SK[o].x * bk, SK[o].y * bk);
       SK[o] = z;
       p += z.x * z.x + z.y * z.y;
@@ -126,7 +129,7 @@ __global__ void __launch_bounds__(GG_THREADS) deltanet_spectral_kernel(const DnS
     gen_fwd_plane(vplane, xs, Rb, Fb, twW, twH, H, W);
     // per-bin delta rule (each thread owns its bins)
     for (int o = tid; o < NB; o += GG_THREADS) {
-      const float4 g = gm[o];
+      const float4 g = chan ? make_float4(ab.x, ab.y, 1.f, 1.f) : gm[o];
       const cf k = mk(SK[o].x * nk, SK[o].y * nk);
       const cf q = mk(SQ[o].x * nq, SQ[o].y * nq);
       const cf v = mk(Fb[o].x * g.w, Fb[o].y * g.w);
@@ -144,11 +147,55 @@ __global__ void __launch_bounds__(GG_THREADS) deltanet_spectral_kernel(const DnS
       h.x += U.x; h.y += U.y;
       hst[o] = h;
       const cf oq = cmul(h, q);
-      const float c = cg[o];
+      const float c = chan ? invHW : cg[o];
       Fb[o] = mk(oq.x * c, oq.y * c);
     }
     gen_inv_plane(Fb, Rb, vplane, twW, twH, H, W);
   }
+}
+
+// gate_type 'channel': alpha, beta = per-channel scalars from Dense(C)(ctx) (cssm.py:3764-3768).
+// One CTA per frame.
+struct DnChanArgs {
+  const float* ctx_part; const float* tcode;
+  int BT, T, C, H, W;
+  const float* ak; const float* ab; const float* bk; const float* bb;   // (C,C), (C) x 2
+  float2* chan;                                                          // (BT, C) {alpha, beta}
+};
+__global__ void __launch_bounds__(128) deltanet_chan_gates_kernel(const DnChanArgs g) {
+  extern __shared__ float sh[];          // ctx [C]
+  const int fr = blockIdx.x, tid = threadIdx.x, t = fr % g.T;
+  const float inv = 1.0f / (float)(g.H * g.W);
+  for (int c = tid; c < g.C; c += blockDim.x) {
+    float s = 0.f;
+    for (int h = 0; h < g.H; ++h) s += g.ctx_part[((size_t)fr * g.H + h) * g.C + c];
+    sh[c] = s * inv + g.tcode[t * g.C + c];
+  }
+  __syncthreads();
+  for (int o = tid; o < g.C; o += blockDim.x) {
+    float aa = g.ab[o], bb = g.bb[o];
+    for (int c = 0; c < g.C; ++c) {
+      aa = fmaf(sh[c], g.ak[(size_t)c * g.C + o], aa);
+      bb = fmaf(sh[c], g.bk[(size_t)c * g.C + o], bb);
+    }
+    g.chan[(size_t)fr * g.C + o] = make_float2(0.1f + 0.89f * dn_sigmoid(aa), dn_sigmoid(bb));
+  }
+}
+
+// k, v planes times their spatial gate planes: for every frame the 2C planes C..3C of the
+// (frames, 3C, HW) q/k/v buffer are multiplied by planes 0..2C of the (frames, 3C, HW) gate buffer
+__global__ void __launch_bounds__(256) deltanet_kv_gate_kernel(float* __restrict__ qkv,
+                                                               const float* __restrict__ gsp,
+                                                               size_t per_frame4, size_t fstride4,
+                                                               size_t total4, size_t koff4) {
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total4) return;
+  const size_t fr = i / per_frame4, r = i - fr * per_frame4;
+  float4* d = reinterpret_cast<float4*>(qkv) + fr * fstride4 + koff4 + r;
+  const float4 gv = __ldg(reinterpret_cast<const float4*>(gsp) + fr * fstride4 + r);
+  float4 v = *d;
+  v.x *= gv.x; v.y *= gv.y; v.z *= gv.z; v.w *= gv.w;
+  *d = v;
 }
 
 static size_t deltanet_smem_bytes(int H, int W) {
@@ -168,8 +215,10 @@ static int deltanet_validate(const cssm_deltanet_desc* d) {
   if (d->goom_floor != 0 && d->goom_floor != 1) return CSSM_ERR_UNSUPPORTED;
   if (d->C % 4 != 0) return CSSM_ERR_UNSUPPORTED;
   if (d->rope_mode < CSSM_ROPE_NONE || d->rope_mode > CSSM_ROPE_MROPE) return CSSM_ERR_UNSUPPORTED;
-  if (d->gate_type != CSSM_GATE_DENSE && d->gate_type != CSSM_GATE_FACTORED)
+  if (d->gate_type != CSSM_GATE_DENSE && d->gate_type != CSSM_GATE_FACTORED &&
+      d->gate_type != CSSM_GATE_CHANNEL)
     return CSSM_ERR_UNSUPPORTED;
+  if (d->gate_type == CSSM_GATE_CHANNEL && ((size_t)d->H * d->W) % 4 != 0) return CSSM_ERR_UNSUPPORTED;
   const bool crop_h = d->kernel_size > d->H, crop_w = d->kernel_size > d->W;
   if (crop_h != crop_w) return CSSM_ERR_UNSUPPORTED;
   if (deltanet_smem_bytes(d->H, d->W) > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
@@ -191,7 +240,7 @@ static DnPlan deltanet_plan_layout(const cssm_deltanet_desc& d) {
   return p;
 }
 
-struct DnWs { size_t qkv, ctx_part, abkv, cg, total; };
+struct DnWs { size_t qkv, ctx_part, abkv, cg, gsp, chan, total; };
 static DnWs deltanet_ws_layout(const cssm_deltanet_desc& d) {
   DnWs l;
   const size_t BT = (size_t)d.B * d.T, HW = (size_t)d.H * d.W, NB = (size_t)d.H * (d.W / 2 + 1);
@@ -200,6 +249,9 @@ static DnWs deltanet_ws_layout(const cssm_deltanet_desc& d) {
   l.ctx_part = off; off += round_up(BT * d.H * d.C * sizeof(float), 256);
   l.abkv = off;     off += round_up(BT * NB * sizeof(float4), 256);
   l.cg = off;       off += round_up(BT * NB * sizeof(float), 256);
+  const bool ch = d.gate_type == CSSM_GATE_CHANNEL;
+  l.gsp = off;      off += ch ? round_up(BT * 3 * d.C * HW * sizeof(float), 256) : 0;   // B_k, B_v, C_gate planes
+  l.chan = off;     off += ch ? round_up(BT * d.C * sizeof(float2), 256) : 0;
   l.total = off;
   return l;
 }
@@ -247,6 +299,7 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   if (!w || !plan || !x || !y || !workspace) return CSSM_ERR_NULL;
   if (!w->qkv_proj_kernel || !w->qkv_proj_bias || !w->output_proj_kernel || !w->output_proj_bias)
     return CSSM_ERR_NULL;
+  const bool chan = d->gate_type == CSSM_GATE_CHANNEL;
   const int nptr = d->gate_type == CSSM_GATE_FACTORED ? 10 : 5;
   for (int i = 0; i < nptr; ++i)
     if (!w->gate_kernel[i] || !w->gate_bias[i]) return CSSM_ERR_NULL;
@@ -285,7 +338,7 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   g.T = d->T; g.H = d->H; g.W = d->W;
   if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
 
-  // 3. gate maps
+  // 3. gate maps (dense / factored) or channel gates
   DnGateArgs ga;
   memset(&ga, 0, sizeof(ga));
   ga.ctx_part = dw.ctx_part; ga.tcode = (const float*)(pl + p.tcode);
@@ -293,7 +346,34 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   ga.path = deltanet_path(*d);
   for (int i = 0; i < nptr; ++i) { ga.gk[i] = w->gate_kernel[i]; ga.gb[i] = w->gate_bias[i]; }
   ga.abkv = (float4*)(ws + l.abkv); ga.cg = (float*)(ws + l.cg);
-  {
+  if (chan) {
+    DnChanArgs ca;
+    memset(&ca, 0, sizeof(ca));
+    ca.ctx_part = dw.ctx_part; ca.tcode = ga.tcode;
+    ca.BT = BT; ca.T = d->T; ca.C = C; ca.H = d->H; ca.W = d->W;
+    ca.ak = w->gate_kernel[0]; ca.ab = w->gate_bias[0]; ca.bk = w->gate_kernel[1]; ca.bb = w->gate_bias[1];
+    ca.chan = (float2*)(ws + l.chan);
+    deltanet_chan_gates_kernel<<<BT, 128, (size_t)C * sizeof(float), st>>>(ca);
+    if ((s = check_launch()) != CSSM_OK) return s;
+    // spatial gates sigmoid(Conv1x1(rotated x)) -> planes (BT, 3C, H, W): B_k, B_v, C_gate
+    float* gsp = (float*)(ws + l.gsp);
+    for (int i = 0; i < 3; ++i) {
+      memset(&g, 0, sizeof(g));
+      g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
+      g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
+      g.Wk = w->gate_kernel[2 + i]; g.bias = w->gate_bias[2 + i];
+      g.out = gsp; g.o_planes = 3 * C; g.o_plane0 = i * C;
+      g.T = d->T; g.H = d->H; g.W = d->W;
+      g.out_act = 2; g.act_n0 = 0;
+      if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
+    }
+    // k *= B_k, v *= B_v in the spatial domain
+    const size_t per_frame4 = (size_t)2 * C * HW / 4, fstride4 = (size_t)3 * C * HW / 4;
+    const size_t total4 = per_frame4 * BT;
+    deltanet_kv_gate_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, st>>>(
+        qkv, gsp, per_frame4, fstride4, total4, (size_t)C * HW / 4);
+    if ((s = check_launch()) != CSSM_OK) return s;
+  } else {
     const int Wf = d->W / 2 + 1, NB = d->H * Wf;
     const size_t smem = (size_t)(C + 5 * (d->H + Wf)) * sizeof(float);
     int chunks = 1;
@@ -312,6 +392,7 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   sp.qkv = qkv; sp.what = (const cf*)(pl + p.what); sp.abkv = ga.abkv; sp.cg = ga.cg;
   sp.B = d->B; sp.T = d->T; sp.C = C; sp.H = d->H; sp.W = d->W;
   sp.rho = d->spectral_rho; sp.goom_floor = d->goom_floor;
+  sp.chan = chan ? (const float2*)(ws + l.chan) : nullptr;
   if (deltanet_path(*d) == PATH_R64) {
     if ((s = launch_deltanet_spectral_r64(sp, st)) != CSSM_OK) return s;
   } else {
@@ -327,6 +408,7 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   memset(&g, 0, sizeof(g));
   g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
   g.A = qkv; g.a_planes = 3 * C; g.a_plane0 = 2 * C;
+  if (chan) { g.gate = (const float*)(ws + l.gsp); g.g_planes = 3 * C; g.g_plane0 = 2 * C; }   // * C_gate
   g.Wk = w->output_proj_kernel; g.bias = w->output_proj_bias;
   g.out = y;
   g.T = d->T; g.H = d->H; g.W = d->W;

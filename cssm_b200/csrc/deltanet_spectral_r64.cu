@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(R64_NT, 2) deltanet_spectral_r64(const DnSpect
   const int boff = (c.grp << 3) + c.a;                   // the lane's first bin (kh = a, kw = grp)
   const cf* whp = a.what + (size_t)ch * NB + boff;
   const float floor_mag = a.goom_floor ? 1e-7f : 0.f;
+  const bool chan = a.chan != nullptr;                   // same for the whole grid
   const int roff = (2 * c.grp) * 64 + c.a;
 
   cf hst[8];
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(R64_NT, 2) deltanet_spectral_r64(const DnSpect
       r64_col_fwd(c, v);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        const float bk = c.col_on ? __ldg(&a.abkv[gbase + q * (33 * 8)].z) : 0.f;
+        const float bk = !c.col_on ? 0.f : (chan ? 1.f : __ldg(&a.abkv[gbase + q * (33 * 8)].z));
         v[q] = mk(v[q].x * bk, v[q].y * bk);
         SK[q * R64_NT + tid] = v[q];
         pk += v[q].x * v[q].x + v[q].y * v[q].y;
@@ -94,14 +95,21 @@ __global__ void __launch_bounds__(R64_NT, 2) deltanet_spectral_r64(const DnSpect
       const float nq = rsqrtf(sq + 1e-6f), nk = rsqrtf(sk + 1e-6f);
       cf v[8];
       r64_col_fwd(c, v);
+      float2 ab = make_float2(0.f, 0.f);
+      if (chan) ab = __ldg(&a.chan[(size_t)(b * a.T + t) * a.C + ch]);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
         float cgv = 0.f;
         cf w = mk(0.f, 0.f);
         if (c.col_on) {
-          g = __ldg(&a.abkv[gbase + q * (33 * 8)]);
-          cgv = __ldg(&a.cg[gbase + q * (33 * 8)]);
+          if (chan) {
+            g = make_float4(ab.x, ab.y, 1.f, 1.f);
+            cgv = 1.0f / (float)HW;
+          } else {
+            g = __ldg(&a.abkv[gbase + q * (33 * 8)]);
+            cgv = __ldg(&a.cg[gbase + q * (33 * 8)]);
+          }
           w = whp[q * (33 * 8)];
         }
         const cf ks = SK[q * R64_NT + tid], qs = SQ[q * R64_NT + tid];

@@ -58,6 +58,8 @@ struct DnSpectralArgs {
   const cf* what;           // (C, H*Wf) squashed kernel spectrum, bins at bin_index(path, ...)
   const float4* abkv;       // (BT, H*Wf) {alpha, beta, B_k, B_v}, same bin order
   const float* cg;          // (BT, H*Wf) C_gate / (H*W)
+  const float2* chan;       // channel gates: (BT, C) {alpha, beta}; then abkv and cg are not read
+                            // (B_k = B_v = 1, output scale 1/(H*W)); nullptr = per-bin maps
   int B, T, C, H, W;
   float rho;
   int goom_floor;

@@ -816,10 +816,10 @@ class BoundAdditive:
 @dataclass
 class DeltaNetCSSM:
     """Scalar spectral delta rule (reference: DeltaNetCSSM, src/models/cssm.py:3628-3930).
-    Field names and defaults are the reference's.  The CUDA path covers gate_type 'dense' and
-    'factored'; the reference's default 'channel' (spatial 1x1-conv gates) and the other gate
-    types raise NotImplementedError, as do learned_init, position_independent_gates and the
-    bf16 / fp8 split scans (no fallback)."""
+    Field names and defaults are the reference's.  The CUDA path covers gate_type 'channel' (the
+    default: per-channel decay scalars, 1x1-conv spatial I/O gates), 'dense' and 'factored'; the
+    other gate types raise NotImplementedError, as do learned_init, position_independent_gates
+    and the bf16 / fp8 split scans (no fallback)."""
     channels: int
     kernel_size: int = 11
     rope_mode: str = "none"
@@ -840,9 +840,9 @@ class DeltaNetCSSM:
     GATES = ("alpha", "beta", "B_k", "B_v", "C_gate")
 
     def _check(self):
-        if self.gate_type not in ("dense", "factored"):
+        if self.gate_type not in _lib.DELTANET_GATE_TYPES:
             raise NotImplementedError(f"DeltaNetCSSM: gate_type {self.gate_type!r} not built "
-                                      "(supported: 'dense', 'factored')")
+                                      "(supported: 'channel', 'dense', 'factored')")
         if self.rope_mode not in ROPE_MODES:
             raise NotImplementedError(f"DeltaNetCSSM: rope_mode {self.rope_mode!r} not built")
         if self.position_independent_gates or self.learned_init:
@@ -863,7 +863,10 @@ class DeltaNetCSSM:
              "qkv_proj": {"kernel": (Cc, 3 * Cc), "bias": (3 * Cc,)},
              "output_proj": {"kernel": (Cc, Cc), "bias": (Cc,)}}
         for n in self.GATES:
-            if self.gate_type == "factored":
+            if self.gate_type == "channel":
+                # alpha, beta: Dense(C); B_k, B_v, C_gate: Conv 1x1 (HWIO)
+                p[n] = {"kernel": (Cc, Cc) if n in ("alpha", "beta") else (1, 1, Cc, Cc), "bias": (Cc,)}
+            elif self.gate_type == "factored":
                 p[f"{n}_h"] = {"kernel": (Cc, H), "bias": (H,)}
                 p[f"{n}_w"] = {"kernel": (Cc, Wf), "bias": (Wf,)}
             else:
@@ -881,7 +884,8 @@ class DeltaNetCSSM:
                 return {k: fill(v, k) for k, v in shape_tree.items()}
             if name == "bias":
                 return (bias_scale * rng.standard_normal(shape_tree)).astype(np.float32)
-            fan_in = shape_tree[0] if len(shape_tree) == 2 else self.kernel_size * self.channels
+            fan_in = (shape_tree[0] if len(shape_tree) == 2 else
+                      self.channels if len(shape_tree) == 4 else self.kernel_size * self.channels)
             return (rng.standard_normal(shape_tree) / np.sqrt(fan_in)).astype(np.float32)
         return {"params": fill(self.param_shapes(H, W))}
 
@@ -938,13 +942,13 @@ class BoundDeltaNet:
             raise ValueError(f"x has {Cc} channels, module has {m.channels}")
         Wf = W // 2 + 1
         gshape = tuple(self.t["gk0"].shape)
-        want = (Cc, H) if m.gate_type == "factored" else (Cc, H * Wf)
+        want = {"factored": (Cc, H), "dense": (Cc, H * Wf), "channel": (Cc, Cc)}[m.gate_type]
         if gshape != want:
             raise ValueError(f"DeltaNetCSSM: gate weights {gshape} were made for another plane size "
                              f"(this input needs {want})")
         return _lib.DeltaNetDesc(B, T, H, W, Cc, m.kernel_size, ROPE_MODES[m.rope_mode],
-                                 float(m.rope_base), float(m.spectral_rho), GATE_TYPES[m.gate_type],
-                                 m._floor())
+                                 float(m.rope_base), float(m.spectral_rho),
+                                 _lib.DELTANET_GATE_TYPES[m.gate_type], m._floor())
 
     def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         _require_cuda(x)

@@ -40,7 +40,9 @@ typedef enum cssm_rope_mode {      /* apply_rope modes, cssm.py:94-262 */
   CSSM_ROPE_MROPE = 4
 } cssm_rope_mode;
 
-typedef enum cssm_gate_type { CSSM_GATE_DENSE = 0, CSSM_GATE_FACTORED = 1 } cssm_gate_type;
+/* CSSM_GATE_CHANNEL (per-channel decay scalars, 1x1-conv spatial I/O gates) exists for the
+   DeltaNet block only; the other blocks reject it. */
+typedef enum cssm_gate_type { CSSM_GATE_DENSE = 0, CSSM_GATE_FACTORED = 1, CSSM_GATE_CHANNEL = 2 } cssm_gate_type;
 
 typedef enum cssm_gate_act {       /* GatedCSSM._compute_gate, cssm.py:432-441 */
   CSSM_ACT_SOFTPLUS = 0,
@@ -333,18 +335,21 @@ int cssm_additive_forward(const cssm_additive_desc* d, const cssm_additive_weigh
  *   A_t = squash(alpha_t W_hat (1 - beta_t |k_t|^2)),  U_t = beta_t v_t conj(k_t),
  *   h_t = A_t h_{t-1} + U_t (h_0 = 0),  o_t = C_gate,t h_t q_t  -> irfft2 -> Dense output_proj.
  * Gates from ctx = mean_{H,W}(rotated x) + temporal code: alpha = 0.1 + 0.89 sigmoid(.), the
- * others sigmoid(.), per-bin maps shared by the channels; gate_type 'dense' or 'factored'
- * (cssm.py:3756-3793).  Replaces every scan_mode of the block (cssm.py:3818-3912); goom_floor
- * as for the additive block (floors on A_t and U_t).  The reference's default gate_type
- * 'channel' (1x1-conv spatial gates), 'scalar', learned_init, position_independent_gates and
- * the bf16 / fp8 split scans are rejected. */
+ * others sigmoid(.), per-bin maps shared by the channels for gate_type 'dense' or 'factored'
+ * (cssm.py:3769-3793).  gate_type 'channel' (the reference's default, cssm.py:3758-3768):
+ * alpha, beta are per-channel scalars Dense(C)(ctx); B_k, B_v, C_gate are per-pixel, per-channel
+ * maps sigmoid(Conv1x1(C)(rotated x)) applied in the spatial domain (k, v before their
+ * transforms, C_gate after the inverse transform).  Replaces every scan_mode of the block
+ * (cssm.py:3818-3912); goom_floor as for the additive block (floors on A_t and U_t).
+ * gate_type 'scalar', learned_init, position_independent_gates and the bf16 / fp8 split scans
+ * are rejected. */
 typedef struct cssm_deltanet_desc {
   int32_t B, T, H, W, C;
   int32_t kernel_size;
   int32_t rope_mode;        /* CSSM_ROPE_* */
   float   rope_base;        /* 10000 */
   float   spectral_rho;     /* 0.999 */
-  int32_t gate_type;        /* CSSM_GATE_DENSE or CSSM_GATE_FACTORED */
+  int32_t gate_type;        /* CSSM_GATE_DENSE, CSSM_GATE_FACTORED or CSSM_GATE_CHANNEL */
   int32_t goom_floor;       /* 1: scan_mode 'associative' with use_goom; 0: linear scan modes */
 } cssm_deltanet_desc;
 
@@ -354,7 +359,9 @@ typedef struct cssm_deltanet_weights {
   const float* qkv_proj_bias;       /* (3C)                                                   */
   /* dense: [0..4] = alpha, beta, B_k, B_v, C_gate, kernels (C, H*Wf), biases (H*Wf).
      factored: [0..9] = alpha_h, alpha_w, beta_h, beta_w, B_k_h, B_k_w, B_v_h, B_v_w, C_gate_h,
-     C_gate_w, kernels (C,H) / (C,Wf) */
+     C_gate_w, kernels (C,H) / (C,Wf).
+     channel: [0..4] = alpha, beta (Dense kernels (C,C)), B_k, B_v, C_gate (Conv kernels
+     (1,1,C,C), i.e. (C_in, C_out) row-major), biases (C) */
   const float* gate_kernel[10];
   const float* gate_bias[10];
   const float* output_proj_kernel;  /* (C, C)                                                 */

@@ -475,14 +475,19 @@ def init_additive1_params(seed, C, H, W, *, kernel_size=11, gate_type="dense", b
 def deltanet_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=10000.0,
                      spectral_rho=0.999, gate_type="dense", scan_mode="associative",
                      dtype=np.float64, scan="direct"):
-    """DeltaNetCSSM.__call__ (cssm.py:3628-3930) for gate_type 'dense' or 'factored',
-    position_independent_gates=False, learned_init=False, use_goom=True: the scalar delta rule
+    """DeltaNetCSSM.__call__ (cssm.py:3628-3930) for gate_type 'channel' (the default), 'dense'
+    or 'factored', position_independent_gates=False, learned_init=False, use_goom=True: the
+    scalar delta rule
     per channel and frequency bin,
         A_t = squash(alpha_t W_hat (1 - beta_t |k_t|^2)),  U_t = beta_t v_t conj(k_t),
         h_t = A_t h_{t-1} + U_t,  o_t = h_t q_t,
     with q, k spectrally L2-normalised per (b,t,c) (sum over the H x Wf half-spectrum bins, eps
     1e-6 under the root; k after its input gate), k and v gated by the spectral maps B_k, B_v and
-    the output by C_gate (cssm.py:3756-3761, 3789-3812, 3914-3928).  scan_mode 'associative' is
+    the output by C_gate (cssm.py:3756-3761, 3789-3812, 3914-3928).  With gate_type 'channel'
+    alpha and beta are per-channel scalars Dense(C)(ctx) and B_k, B_v, C_gate are per-pixel,
+    per-channel maps sigmoid(Conv1x1(C)(rotated x)) applied in the spatial domain: k and v
+    before their transforms, C_gate after the inverse transform (cssm.py:3758-3768, 3781-3786,
+    3918-3921).  scan_mode 'associative' is
     the log-space scan whose to_goom floors |A_t| and |U_t| at 1e-7 (cssm.py:3889-3890); the
     other modes run the same recurrence in plain complex arithmetic."""
     cdt = np.complex128 if dtype == np.float64 else np.complex64
@@ -494,7 +499,13 @@ def deltanet_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=1
     q_in, k_in, v_in = qkv[..., :C], qkv[..., C:2 * C], qkv[..., 2 * C:]
     ctx = x.mean(axis=(2, 3)) + temporal_ctx_code(T, C, rope_base)[None]
 
-    def gate(name, bounded=False):
+    def gate(name, bounded=False, spatial=False):
+        if gate_type == "channel":
+            if spatial:                                   # 1x1 conv, HWIO kernel (1,1,C,C)
+                kern = np.asarray(params[name]["kernel"], dtype=dtype).reshape(C, C)
+                return sigmoid(x @ kern + np.asarray(params[name]["bias"], dtype=dtype))
+            raw = sigmoid(dense(ctx, params[name])).reshape(B, T, C, 1, 1)
+            return 0.1 + 0.89 * raw if bounded else raw
         if gate_type == "factored":
             row = dense(ctx, params[f"{name}_h"])
             col = dense(ctx, params[f"{name}_w"])
@@ -505,7 +516,7 @@ def deltanet_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=1
         return 0.1 + 0.89 * raw if bounded else raw
 
     alpha, beta = gate("alpha", True), gate("beta")
-    B_k, B_v, C_gate = gate("B_k"), gate("B_v"), gate("C_gate")
+    B_k, B_v, C_gate = gate("B_k", spatial=True), gate("B_v", spatial=True), gate("C_gate", spatial=True)
 
     def spec(z):
         return np.fft.rfft2(z.transpose(0, 1, 4, 2, 3), axes=(3, 4)).astype(cdt)
@@ -513,7 +524,10 @@ def deltanet_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=1
     def l2n(z):
         return z / np.sqrt(np.sum(np.abs(z) ** 2, axis=(3, 4), keepdims=True) + 1e-6)
 
-    k_hat, v_hat, q_hat = l2n(spec(k_in) * B_k), spec(v_in) * B_v, l2n(spec(q_in))
+    if gate_type == "channel":
+        k_hat, v_hat, q_hat = l2n(spec(k_in * B_k)), spec(v_in * B_v), l2n(spec(q_in))
+    else:
+        k_hat, v_hat, q_hat = l2n(spec(k_in) * B_k), spec(v_in) * B_v, l2n(spec(q_in))
     W_hat = spectral_kernel(params["kernel"], H, W, spectral_rho).astype(cdt)[None, None]
     A = alpha * W_hat * (1.0 - beta * np.abs(k_hat) ** 2)
     A = A * spectral_rho / (1.0 + np.abs(A))
@@ -530,7 +544,10 @@ def deltanet_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=1
             h = A[:, t] * h + U[:, t]
             hs.append(h)
         h_all = np.stack(hs, axis=1)
-    o = np.fft.irfft2(h_all * q_hat * C_gate, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2)
+    if gate_type == "channel":
+        o = np.fft.irfft2(h_all * q_hat, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2) * C_gate
+    else:
+        o = np.fft.irfft2(h_all * q_hat * C_gate, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2)
     return dense(o.astype(dtype), params["output_proj"])
 
 
@@ -543,7 +560,11 @@ def init_deltanet_params(seed, C, H, W, *, kernel_size=11, gate_type="dense", bi
          "qkv_proj": _dense_p(rng, C, 3 * C, bias_scale),
          "output_proj": _dense_p(rng, C, C, bias_scale)}
     for n in ("alpha", "beta", "B_k", "B_v", "C_gate"):
-        if gate_type == "factored":
+        if gate_type == "channel":
+            p[n] = _dense_p(rng, C, C, bias_scale)
+            if n in ("B_k", "B_v", "C_gate"):
+                p[n]["kernel"] = p[n]["kernel"].reshape(1, 1, C, C)
+        elif gate_type == "factored":
             p[f"{n}_h"] = _dense_p(rng, C, H, bias_scale)
             p[f"{n}_w"] = _dense_p(rng, C, Wf, bias_scale)
         else:

@@ -179,14 +179,18 @@ def test_deltanet_descriptor_validation_without_gpu():
     d = desc()
     assert L.cssm_deltanet_plan_bytes(C.byref(d)) >= 8 * 8 * 5 * 8
     assert L.cssm_deltanet_workspace_bytes(C.byref(d)) >= 2 * 3 * 3 * 8 * 8 * 8 * 4
-    for bad in (desc(gate_type=2), desc(C=6), desc(T=0), desc(goom_floor=-1), desc(rope_mode=9),
+    for bad in (desc(gate_type=3), desc(C=6), desc(T=0), desc(goom_floor=-1), desc(rope_mode=9),
                 desc(H=128, W=128)):                     # plane too large for one CTA's shared memory
         assert L.cssm_deltanet_plan_bytes(C.byref(bad)) == 0
     w = _lib.DeltaNetWeights()
     assert L.cssm_deltanet_forward(C.byref(d), C.byref(w), None, None, None, None, 0, None) == 1
+    assert L.cssm_deltanet_workspace_bytes(C.byref(desc(gate_type=2))) > L.cssm_deltanet_workspace_bytes(C.byref(d))
+    assert L.cssm_deltanet_plan_bytes(C.byref(desc(gate_type=2, H=7, W=7, kernel_size=3))) == 0   # H*W % 4
     from cssm_b200 import DeltaNetCSSM
     with pytest.raises(NotImplementedError):
-        DeltaNetCSSM(channels=8).init(0, (1, 2, 8, 8, 8))          # default gate_type 'channel'
+        DeltaNetCSSM(channels=8, gate_type="scalar").init(0, (1, 2, 8, 8, 8))
+    pc = DeltaNetCSSM(channels=8).init(0, (1, 2, 8, 8, 8))["params"]      # default gate_type 'channel'
+    assert pc["alpha"]["kernel"].shape == (8, 8) and pc["C_gate"]["kernel"].shape == (1, 1, 8, 8)
     p = DeltaNetCSSM(channels=8, gate_type="factored").init(0, (1, 2, 8, 6, 8))["params"]
     assert p["qkv_proj"]["kernel"].shape == (8, 24) and p["B_v_w"]["kernel"].shape == (8, 4)
 

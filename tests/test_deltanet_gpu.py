@@ -39,6 +39,11 @@ def _run(case, gate_type, rope, scan_mode="associative", seed=0):
     ((2, 3, 14, 10, 12, 3), "factored", "spatial_only"),      # ragged plane
     ((2, 5, 16, 16, 8, 7), "dense", "temporal"),
     ((1, 1, 7, 7, 4, 11), "factored", "none"),                # T = 1, kernel larger than the plane
+    ((2, 4, 64, 64, 64, 11), "channel", "spatiotemporal"),    # the reference's default gate type
+    ((2, 5, 64, 64, 8, 5), "channel", "none"),
+    ((2, 6, 32, 32, 8, 11), "channel", "mrope"),
+    ((2, 3, 14, 10, 12, 3), "channel", "spatial_only"),
+    ((1, 1, 6, 6, 4, 3), "channel", "temporal"),
 ], ids=lambda c: "x".join(map(str, c)) if isinstance(c, tuple) else str(c))
 def test_block_parity(case, gate_type, rope):
     assert _run(case, gate_type, rope) <= TOL
