@@ -487,7 +487,7 @@ static int simple_validate(const cssm_simple_desc* d) {
   if (d->num_classes > SM_MAXC) return CSSM_ERR_UNSUPPORTED;
   if (d->stem_mode != 0 && d->stem_mode != 1) return CSSM_ERR_UNSUPPORTED;
   if (d->stem_mode == 0 && (d->stem_layers < 1 || d->stem_layers > 4)) return CSSM_ERR_UNSUPPORTED;
-  if (d->block != 0 && d->block != 1) return CSSM_ERR_UNSUPPORTED;
+  if (d->block < 0 || d->block > 4) return CSSM_ERR_UNSUPPORTED;
   if (d->pool_type != 0 && d->pool_type != 1) return CSSM_ERR_UNSUPPORTED;
   if (d->readout_norm != 0 && d->readout_norm != 1) return CSSM_ERR_UNSUPPORTED;
   return CSSM_OK;
@@ -502,17 +502,35 @@ static SimpleDims stem_out_dims(const cssm_simple_desc& d) {
   return o;
 }
 
+// every block descriptor starts with int32 B, T, H, W, C
+struct BlockDims { int32_t B, T, H, W, C; };
 static bool block_matches(const cssm_simple_desc& d, const void* bd) {
   const SimpleDims o = stem_out_dims(d);
-  if (d.block == 0) {
-    const cssm_gated_desc* g = (const cssm_gated_desc*)bd;
-    return g->B == d.B && g->T == d.T && g->H == o.H && g->W == o.W && g->C == d.embed_dim;
-  }
-  const cssm_gdn_desc* g = (const cssm_gdn_desc*)bd;
+  const BlockDims* g = (const BlockDims*)bd;
   return g->B == d.B && g->T == d.T && g->H == o.H && g->W == o.W && g->C == d.embed_dim;
 }
 
-struct SimpleWs { size_t feat, tmp, y, partial, block, total; };
+static size_t block_ws_bytes(int block, const void* bd) {
+  switch (block) {
+    case 0: return cssm_gated_workspace_bytes((const cssm_gated_desc*)bd);
+    case 1: return cssm_gdn_workspace_bytes((const cssm_gdn_desc*)bd);
+    case 2: return cssm_nogate_workspace_bytes((const cssm_nogate_desc*)bd);
+    case 3: return cssm_additive_workspace_bytes((const cssm_additive_desc*)bd);
+    default: return cssm_deltanet_workspace_bytes((const cssm_deltanet_desc*)bd);
+  }
+}
+
+// one feature frame per image -> T equal frames per clip (the scalar-scan blocks read clips)
+__global__ void __launch_bounds__(256) repeat_frames_kernel(const float4* __restrict__ in,
+                                                            float4* __restrict__ out, size_t frame4,
+                                                            int T, size_t total4) {
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total4) return;
+  const size_t fo = i / frame4, r = i - fo * frame4;
+  out[i] = __ldg(in + (fo / T) * frame4 + r);
+}
+
+struct SimpleWs { size_t feat, tmp, y, partial, rep, block, total; };
 static SimpleWs simple_ws_layout(const cssm_simple_desc& d, const void* bd) {
   SimpleWs l;
   const SimpleDims o = stem_out_dims(d);
@@ -527,9 +545,11 @@ static SimpleWs simple_ws_layout(const cssm_simple_desc& d, const void* bd) {
   l.tmp = off; off += 2 * round_up(tmp, 256);
   l.y = off; off += round_up((size_t)d.B * d.T * o.H * o.W * C * sizeof(float), 256);
   l.partial = off; off += round_up((size_t)d.B * ((o.H + RO_ROWS - 1) / RO_ROWS) * C * sizeof(float), 256);
+  // blocks 2..4 take clips only: an image batch's features are repeated over T for them
+  l.rep = off;
+  if (d.block >= 2 && d.image_input) off += round_up((size_t)d.B * d.T * o.H * o.W * C * sizeof(float), 256);
   l.block = off;
-  off += d.block == 0 ? cssm_gated_workspace_bytes((const cssm_gated_desc*)bd)
-                      : cssm_gdn_workspace_bytes((const cssm_gdn_desc*)bd);
+  off += block_ws_bytes(d.block, bd);
   l.total = round_up(off, 256);
   return l;
 }
@@ -595,8 +615,7 @@ extern "C" {
 size_t cssm_simple_workspace_bytes(const cssm_simple_desc* d, const void* block_desc) {
   if (simple_validate(d) != CSSM_OK || !block_desc || !block_matches(*d, block_desc)) return 0;
   // a block descriptor its own library entry points reject makes the model unsupported too
-  const size_t bws = d->block == 0 ? cssm_gated_workspace_bytes((const cssm_gated_desc*)block_desc)
-                                   : cssm_gdn_workspace_bytes((const cssm_gdn_desc*)block_desc);
+  const size_t bws = block_ws_bytes(d->block, block_desc);
   if (bws == 0) return 0;
   return simple_ws_layout(*d, block_desc).total;
 }
@@ -650,9 +669,30 @@ int cssm_simple_forward(const cssm_simple_desc* d, const cssm_simple_weights* w,
   const size_t tmp_half = (l.y - l.tmp) / 2;
   s = run_stem(d, w, x, feat, (float*)(ws + l.tmp), (float*)(ws + l.tmp + tmp_half), st);
   if (s != CSSM_OK) return s;
-  const int last_only = (flags & CSSM_SIMPLE_LAST_FRAME_ONLY) ? 1 : 0;
+  // the scalar-scan blocks have no last-frame-only entry point: they produce all T frames
+  const int last_only = ((flags & CSSM_SIMPLE_LAST_FRAME_ONLY) && d->block < 2) ? 1 : 0;
   const size_t bws = l.total - l.block;
-  if (d->block == 0)
+  if (d->block >= 2) {
+    const float* clips = feat;
+    if (d->image_input) {
+      const size_t frame4 = (size_t)o.H * o.W * d->embed_dim / 4, total4 = frame4 * d->B * d->T;
+      repeat_frames_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, st>>>(
+          (const float4*)feat, (float4*)(ws + l.rep), frame4, d->T, total4);
+      if ((s = check_launch()) != CSSM_OK) return s;
+      clips = (const float*)(ws + l.rep);
+    }
+    if (d->block == 2)
+      s = cssm_nogate_forward((const cssm_nogate_desc*)block_desc, (const cssm_nogate_weights*)block_weights,
+                              block_plan, clips, y, ws + l.block, bws, stream);
+    else if (d->block == 3)
+      s = cssm_additive_forward((const cssm_additive_desc*)block_desc,
+                                (const cssm_additive_weights*)block_weights, block_plan, clips, y,
+                                ws + l.block, bws, stream);
+    else
+      s = cssm_deltanet_forward((const cssm_deltanet_desc*)block_desc,
+                                (const cssm_deltanet_weights*)block_weights, block_plan, clips, y,
+                                ws + l.block, bws, stream);
+  } else if (d->block == 0)
     s = gated_forward_internal((const cssm_gated_desc*)block_desc, (const cssm_gated_weights*)block_weights,
                                block_plan, feat, y, ws + l.block, bws, stream, last_only, d->image_input);
   else

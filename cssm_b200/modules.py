@@ -619,10 +619,8 @@ class BoundNoGate:
             raise ValueError(f"x has {Cc} channels, module has {self.mod.channels}")
         return _lib.NoGateDesc(B, T, H, W, Cc, self.mod.kernel_size, float(self.mod.spectral_rho))
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        _require_cuda(x)
-        x = x.contiguous()
-        d = self.desc(tuple(x.shape))
+    def plan(self, d) -> torch.Tensor:
+        """The weight-only plan (K_hat) for descriptor d, built once per plane size."""
         key = (d.H, d.W)
         pl = self._plans.get(key)
         if pl is None:
@@ -633,6 +631,13 @@ class BoundNoGate:
             check(self.L.cssm_nogate_plan_init(C.byref(d), C.byref(self.w), pl.data_ptr(), n,
                                                _stream_ptr(self.device)), "cssm_nogate_plan_init")
             self._plans[key] = pl
+        return pl
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x)
+        x = x.contiguous()
+        d = self.desc(tuple(x.shape))
+        pl = self.plan(d)
         n = self.L.cssm_nogate_workspace_bytes(C.byref(d))
         ws = self.buf.get("ws", n)
         y = torch.empty_like(x) if out is None else out
@@ -787,12 +792,8 @@ class BoundAdditive:
                                  float(m.rope_base), float(m.spectral_rho), GATE_TYPES[m.gate_type],
                                  1, m._floor())
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        _require_cuda(x)
-        if x.dim() != 5:
-            raise ValueError("AdditiveCSSM expects (B,T,H,W,C)")
-        x = x.contiguous()
-        d = self.desc(tuple(x.shape))
+    def plan(self, d) -> torch.Tensor:
+        """The weight-only plan (kernel spectrum, RoPE tables, temporal code) for descriptor d."""
         key = (d.T, d.H, d.W)
         pl = self._plans.get(key)
         if pl is None:
@@ -803,6 +804,15 @@ class BoundAdditive:
             check(self.L.cssm_additive_plan_init(C.byref(d), C.byref(self.w), pl.data_ptr(), n,
                                                  _stream_ptr(self.device)), "cssm_additive_plan_init")
             self._plans[key] = pl
+        return pl
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x)
+        if x.dim() != 5:
+            raise ValueError("AdditiveCSSM expects (B,T,H,W,C)")
+        x = x.contiguous()
+        d = self.desc(tuple(x.shape))
+        pl = self.plan(d)
         n = self.L.cssm_additive_workspace_bytes(C.byref(d))
         ws = self.buf.get("ws", n)
         y = torch.empty_like(x) if out is None else out
@@ -950,12 +960,8 @@ class BoundDeltaNet:
                                  float(m.rope_base), float(m.spectral_rho),
                                  _lib.DELTANET_GATE_TYPES[m.gate_type], m._floor())
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        _require_cuda(x)
-        if x.dim() != 5:
-            raise ValueError("DeltaNetCSSM expects (B,T,H,W,C)")
-        x = x.contiguous()
-        d = self.desc(tuple(x.shape))
+    def plan(self, d) -> torch.Tensor:
+        """The weight-only plan (kernel spectrum, RoPE tables, temporal code) for descriptor d."""
         key = (d.T, d.H, d.W)
         pl = self._plans.get(key)
         if pl is None:
@@ -966,6 +972,15 @@ class BoundDeltaNet:
             check(self.L.cssm_deltanet_plan_init(C.byref(d), C.byref(self.w), pl.data_ptr(), n,
                                                  _stream_ptr(self.device)), "cssm_deltanet_plan_init")
             self._plans[key] = pl
+        return pl
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x)
+        if x.dim() != 5:
+            raise ValueError("DeltaNetCSSM expects (B,T,H,W,C)")
+        x = x.contiguous()
+        d = self.desc(tuple(x.shape))
+        pl = self.plan(d)
         n = self.L.cssm_deltanet_workspace_bytes(C.byref(d))
         ws = self.buf.get("ws", n)
         y = torch.empty_like(x) if out is None else out

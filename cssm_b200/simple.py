@@ -1,7 +1,8 @@
 """Host-side mirror of the reference's SimpleCSSM wrapper (src/models/simple_cssm.py:62-558)
-for inference with ONE gated or GDN block: stem -> x + block(x) -> last-frame readout -> logits.
+for inference with ONE spectral block: stem -> x + block(x) -> last-frame readout -> logits.
 
-Field names and defaults are the reference's.  Supported: depth 1; cssm_type 'gated' / 'gdn';
+Field names and defaults are the reference's.  Supported: depth 1; cssm_type 'gated' / 'gdn' /
+'no_gate' / 'add_kqv_1' / 'deltanet' (CSSM_REGISTRY names, simple_cssm.py:21-60);
 stem_mode 'default' (stem_layers x [conv3x3, softplus, LayerNorm, 2x2 max-pool]) and
 'pathtracker' (conv1x1, softplus, LayerNorm); stem_norm_order 'post'; act_type 'softplus';
 norm_type 'layer'; frame_readout 'last'; pool_type 'mean' / 'max'; readout_norm 'pre' / 'post';
@@ -19,7 +20,8 @@ import torch
 
 from . import _lib
 from ._lib import SIMPLE_LAST_FRAME_ONLY, SimpleDesc, SimpleWeights, check
-from .modules import (GatedCSSM, GatedDeltaNetCSSM, _Buffers, _dev_f32, _require_cuda, _stream_ptr)
+from .modules import (AdditiveCSSM, DeltaNetCSSM, GatedCSSM, GatedDeltaNetCSSM, NoGateCSSM, _Buffers,
+                      _dev_f32, _require_cuda, _stream_ptr)
 
 
 @dataclass
@@ -54,6 +56,13 @@ class SimpleCSSM:
     qkv_conv_separable: bool = True
     delta_key_dim: int = 2
     no_spectral_clamp: bool = False
+    use_goom: bool = True
+    learned_init: bool = False
+    use_complex32: bool = False
+    use_complex16: bool = False
+    use_ssd: bool = False
+    scan_mode: str = "associative"
+    ssd_chunk_size: int = 8
     _bound: Dict[Any, Any] = field(default_factory=dict, repr=False, compare=False)
 
     # -- the block this model wraps (simple_cssm.py:318-481) -----------------------------
@@ -74,8 +83,22 @@ class SimpleCSSM:
                                      qkv_conv_separable=self.qkv_conv_separable,
                                      delta_key_dim=self.delta_key_dim,
                                      no_spectral_clamp=self.no_spectral_clamp)
+        if self.cssm_type == "no_gate":                      # simple_cssm.py:344-347
+            return NoGateCSSM(channels=self.embed_dim, kernel_size=self.kernel_size, rope_mode=rope,
+                              block_size=self.block_size, short_conv_size=self.short_conv_size,
+                              short_conv_spatial_size=self.short_conv_spatial_size)
+        scan = dict(use_goom=self.use_goom, gate_type=self.gate_type, learned_init=self.learned_init,
+                    use_complex32=self.use_complex32, use_complex16=self.use_complex16,
+                    scan_mode=self.scan_mode, ssd_chunk_size=self.ssd_chunk_size)
+        if self.cssm_type == "add_kqv_1":                    # simple_cssm.py:368-381
+            return AdditiveCSSM(channels=self.embed_dim, kernel_size=self.kernel_size, rope_mode=rope,
+                                block_size=self.block_size, single_state=True, use_ssd=self.use_ssd,
+                                **scan)
+        if self.cssm_type == "deltanet":                     # simple_cssm.py:385-393
+            return DeltaNetCSSM(channels=self.embed_dim, kernel_size=self.kernel_size, rope_mode=rope,
+                                block_size=self.block_size, **scan)
         raise NotImplementedError(f"SimpleCSSM: cssm_type={self.cssm_type!r} has no CUDA kernel "
-                                  "(have 'gated', 'gdn')")
+                                  "(have 'gated', 'gdn', 'no_gate', 'add_kqv_1', 'deltanet')")
 
     def _check_fields(self):
         bad = []
@@ -102,6 +125,9 @@ class SimpleCSSM:
             bad.append(f"embed_dim={self.embed_dim}")
         if bad:
             raise NotImplementedError("SimpleCSSM: no CUDA kernel for " + "; ".join(bad))
+        check_block = getattr(self.block(), "_check", None)     # field combinations of the block
+        if check_block is not None:
+            check_block()
 
     def feature_hw(self, Hin: int, Win: int):
         H, W = Hin, Win
@@ -209,7 +235,8 @@ class BoundSimple:
         T = m.seq_len if image else x_shape[1]
         Hin, Win, Cin = x_shape[-3:]
         return SimpleDesc(B, T, Hin, Win, Cin, int(image), 1 if m.stem_mode == "pathtracker" else 0,
-                          m.stem_layers, m.embed_dim, 0 if m.cssm_type == "gated" else 1,
+                          m.stem_layers, m.embed_dim,
+                          {"gated": 0, "gdn": 1, "no_gate": 2, "add_kqv_1": 3, "deltanet": 4}[m.cssm_type],
                           1 if m.pool_type == "max" else 0, 1 if m.readout_norm == "post" else 0,
                           m.num_classes)
 

@@ -394,7 +394,9 @@ typedef struct cssm_simple_desc {
                             2x2 max-pool]; 1 'pathtracker': conv1x1, softplus, LayerNorm       */
   int32_t stem_layers;   /* 1..4 for the default stem                                         */
   int32_t embed_dim;     /* multiple of 4, <= 64                                              */
-  int32_t block;         /* 0 GatedCSSM (block_desc is a cssm_gated_desc), 1 GatedDeltaNetCSSM */
+  int32_t block;         /* 0 GatedCSSM (block_desc is a cssm_gated_desc), 1 GatedDeltaNetCSSM,
+                            2 NoGateCSSM, 3 AdditiveCSSM single-state, 4 DeltaNetCSSM (their own
+                            descriptors; these three ignore CSSM_SIMPLE_LAST_FRAME_ONLY)       */
   int32_t pool_type;     /* 0 mean, 1 max                                                     */
   int32_t readout_norm;  /* 0 'pre' (norm -> act), 1 'post' (act -> norm)                     */
   int32_t num_classes;   /* 1..64                                                             */

@@ -104,6 +104,10 @@ def simple_forward(params, x, *, cssm_type="gated", seq_len=8, stem_mode="defaul
         y = orc.gated_forward(params["cssm_0"], f, **kw)
     elif cssm_type == "gdn":
         y = orc.gdn_forward(params["cssm_0"], f, **kw)
+    elif cssm_type in _SCALAR_BLOCKS:
+        fwd = _SCALAR_BLOCKS[cssm_type][0]
+        accepted = set(inspect.signature(fwd).parameters)
+        y = fwd(params["cssm_0"], f, **{k: v for k, v in kw.items() if k in accepted})
     else:
         raise ValueError(cssm_type)
     post = f + y
@@ -111,6 +115,19 @@ def simple_forward(params, x, *, cssm_type="gated", seq_len=8, stem_mode="defaul
     if return_intermediates:
         return logits, {"stem": f, "post_cssm_last": post[:, -1]}
     return logits
+
+
+def _init_nogate(seed, C, H, W, *, kernel_size=11, bias_scale=0.0):
+    rng = np.random.default_rng(seed)
+    return {"kernel": (0.3 * rng.standard_normal((C, kernel_size, kernel_size))).astype(np.float32),
+            "out_proj": {"kernel": (rng.standard_normal((C, C)) / np.sqrt(C)).astype(np.float32),
+                         "bias": (bias_scale * rng.standard_normal(C)).astype(np.float32)}}
+
+
+# CSSM_REGISTRY names (simple_cssm.py:21-60) of the scalar-scan blocks -> (forward, init)
+_SCALAR_BLOCKS = {"no_gate": (orc.nogate_forward, _init_nogate),
+                  "add_kqv_1": (orc.additive1_forward, orc.init_additive1_params),
+                  "deltanet": (orc.deltanet_forward, orc.init_deltanet_params)}
 
 
 def init_simple_params(seed, *, cin, embed_dim, H, W, num_classes=2, cssm_type="gated",
@@ -136,7 +153,10 @@ def init_simple_params(seed, *, cin, embed_dim, H, W, num_classes=2, cssm_type="
         for i in range(stem_layers):
             p[f"conv{i + 1}"], p[f"norm{i + 1}"] = conv(3, ci, embed_dim), norm(embed_dim)
             ci = embed_dim
-    init = orc.init_gated_params if cssm_type == "gated" else orc.init_gdn_params
+    if cssm_type in _SCALAR_BLOCKS:
+        init = _SCALAR_BLOCKS[cssm_type][1]
+    else:
+        init = orc.init_gated_params if cssm_type == "gated" else orc.init_gdn_params
     accepted = set(inspect.signature(init).parameters)
     kw = {k: v for k, v in (block_kwargs or {}).items() if k in accepted}
     p["cssm_0"] = init(seed + 1, embed_dim, H, W, bias_scale=bias_scale, **kw)

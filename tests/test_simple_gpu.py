@@ -25,6 +25,11 @@ def _block_kwargs(m):
         return dict(kernel_size=m.kernel_size, rope_mode=rope, gate_type=m.gate_type,
                     short_conv_size=m.short_conv_size,
                     short_conv_spatial_size=m.short_conv_spatial_size)
+    if m.cssm_type == "no_gate":
+        return dict(kernel_size=m.kernel_size)
+    if m.cssm_type in ("add_kqv_1", "deltanet"):
+        return dict(kernel_size=m.kernel_size, rope_mode=rope, gate_type=m.gate_type,
+                    scan_mode=m.scan_mode)
     return dict(delta_key_dim=m.delta_key_dim, kernel_size=m.kernel_size, rope_mode=rope,
                 gate_type=m.gate_type, short_conv_size=m.short_conv_size,
                 qkv_conv_size=m.qkv_conv_size)
@@ -48,6 +53,17 @@ CASES = [
      dict(delta_key_dim=4, qkv_conv_size=5, seq_len=3)),                                     # image input, dwconv
     ("gdn", 8, 3, "none", "default", 1, "mean", "pre", (2, 16, 16, 1),
      dict(delta_key_dim=4, qkv_conv_size=1, seq_len=3)),                                     # image input, no dwconv
+    # the scalar-scan blocks under their registry names: image input (features repeated over T) and clips
+    ("no_gate", 8, 5, "none", "default", 1, "max", "pre", (2, 16, 16, 1), dict(seq_len=3)),
+    ("no_gate", 16, 11, "none", "pathtracker", 1, "mean", "pre", (2, 4, 32, 32, 3), dict()),
+    ("add_kqv_1", 8, 5, "spatiotemporal", "default", 1, "max", "pre", (2, 16, 16, 1), dict(seq_len=3)),
+    ("add_kqv_1", 64, 11, "mrope", "default", 1, "max", "pre", (2, 128, 128, 1),
+     dict(seq_len=4, gate_type="dense", scan_mode="ssd")),
+    ("add_kqv_1", 16, 3, "none", "pathtracker", 1, "mean", "post", (2, 5, 32, 32, 3), dict()),
+    ("deltanet", 8, 5, "spatiotemporal", "default", 1, "max", "pre", (2, 16, 16, 1),
+     dict(seq_len=3, gate_type="channel")),
+    ("deltanet", 16, 11, "mrope", "default", 1, "mean", "pre", (2, 128, 128, 1), dict(seq_len=3)),
+    ("deltanet", 8, 3, "none", "pathtracker", 1, "max", "pre", (2, 4, 12, 10, 3), dict(gate_type="dense")),
 ]
 
 
@@ -86,6 +102,10 @@ def test_unsupported_fields_raise():
         SimpleCSSM(cssm_type="gated", depth=2).bind({"params": {}})
     with pytest.raises(NotImplementedError):
         SimpleCSSM(cssm_type="hgru_bi").bind({"params": {}})
+    with pytest.raises(NotImplementedError):
+        SimpleCSSM(cssm_type="add_kqv_1", learned_init=True).bind({"params": {}})
+    with pytest.raises(NotImplementedError):
+        SimpleCSSM(cssm_type="deltanet", gate_type="scalar").bind({"params": {}})
     with pytest.raises(NotImplementedError):
         SimpleCSSM(cssm_type="gated", embed_dim=128).bind({"params": {}})
 
