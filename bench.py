@@ -328,6 +328,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--strong", action="store_true",
+                    help="strong scaling: the workload's batch is the GLOBAL batch, split evenly "
+                         "over the ranks (default: weak scaling, that batch per GPU)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -358,6 +361,10 @@ def main():
 
     # model, weights, inputs (disjoint seeds per rank: every rank works on its own shard)
     B = wl["B"]
+    if args.strong:
+        if B % world:
+            raise SystemExit(f"--strong: batch {B} does not divide over {world} ranks")
+        B //= world
     model = make_model(args.workload)
     x_np = make_inputs(args.workload, B, seed0=1000 + B * rank)
     variables = model.init(0, x_np.shape)
@@ -462,7 +469,8 @@ def main():
         print(json.dumps({
             "metric": metric_name(args.workload), "value": value, "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "higher_is_better": True, "scaling": "strong" if args.strong else "weak",
+            "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": args.workload, "model": "SimpleCSSM depth 1", "block": model.cssm_type,
                        "per_gpu_batch": B, "input": list(x.shape[1:]), "T": T, "H": H, "W": W, "C": Cc,
