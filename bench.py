@@ -435,6 +435,17 @@ def main():
         elif gdn and tj.get(f"{kname}_dram_bytes_per_head_step"):
             roofline["traffic"] = tj[f"{kname}_dram_bytes_per_head_step"] * B * T * (Cc // model.delta_key_dim)
 
+    # the whole block against the same peak: bytes a block with every stage fused to its
+    # neighbours' GEMMs would still move (projection inputs / outputs and the fused kernel's planes)
+    if gdn:
+        blk_unit, blk_formula = 52.0, "(16 qkv_proj + 8 gate_proj + 20 spectral + 8 output_proj) * C*H*W per (b,t)"
+    else:
+        blk_unit, blk_formula = 32.0, "(12 in_proj + 12 spectral + 8 out_proj) * C*H*W per (b,t)"
+    blk_bytes = blk_unit * Cc * H * W * B * T
+    block_hbm = {"algorithmic_bytes": blk_bytes, "formula": blk_formula,
+                 "achieved": blk_bytes / (block_ms / 1e3) / 1e9, "unit": "GB/s",
+                 "frac": blk_bytes / (block_ms / 1e3) / 1e9 / peak, "peak": peak, "peak_source": peak_src}
+
     # ---- end to end: pinned host images -> host logits through the host-buffer entry point ----
     e2e = None
     if not args.no_e2e:
@@ -478,7 +489,7 @@ def main():
                        "pos_embed": model.pos_embed, "stem": model.stem_mode, "pool": model.pool_type,
                        "collective": "all-gather of the logits per step" if world > 1 else None,
                        "l2": "block activations (1.07 GB per tensor at cfg2-4) larger than the 126 MB L2"},
-            "block": {"ms_per_step": block_ms, "stage_ms": stage_ms, "stem_ms": stem_ms,
+            "block": {"ms_per_step": block_ms, "stage_ms": stage_ms, "stem_ms": stem_ms, "hbm": block_hbm,
                       "value": world * B / (block_ms / 1e3), "unit": "images/s"},
             "stage_ms": stage_ms, "roofline": roofline,
             "last_frame_only": {"ms_per_step": last_ms, "value": world * B / (last_ms / 1e3),
