@@ -16,13 +16,17 @@ __device__ __forceinline__ float softplus_f(float a) {
   return fmaxf(a, 0.f) + __logf(1.0f + __expf(-fabsf(a)));
 }
 
-// LayerNorm over the C values of v (eps 1e-6, variance as E[x^2] - E[x]^2), in place.
+// LayerNorm over the C values of v (eps 1e-6, variance as E[d^2] - E[d]^2 of d = v - v[0]), in place.
 __device__ __forceinline__ void layer_norm_regs(float (&v)[SM_MAXC], int C, const float* __restrict__ scale,
                                                 const float* __restrict__ bias) {
+  // moments of v - v[0] (same mean-centred values and variance): a pixel whose channels are all
+  // equal then normalises to exactly zero, where a plain fp32 sum leaves a 1-ulp residue that the
+  // 1e-6 epsilon magnifies a thousandfold
+  const float vref = v[0];
   float s = 0.f, ss = 0.f;
 #pragma unroll
   for (int c = 0; c < SM_MAXC; ++c)
-    if (c < C) { s += v[c]; ss = fmaf(v[c], v[c], ss); }
+    if (c < C) { v[c] -= vref; s += v[c]; ss = fmaf(v[c], v[c], ss); }
   const float mean = s / (float)C;
   const float var = fmaxf(ss / (float)C - mean * mean, 0.f);
   const float rinv = rsqrtf(var + 1e-6f);
@@ -138,13 +142,15 @@ __global__ void __launch_bounds__(NT) stem_layer_kernel(const StemArgs a) {
     }
   }
   // softplus, then LayerNorm over the C channels of the pixel (the quad's 4 x 16 values)
+  // (moments of the values minus the pixel's first channel: see layer_norm_regs)
   float s = 0.f, ss = 0.f;
+  const float vref = __shfl_sync(0xffffffffu, softplus_f(acc[0][0]), lane & ~3);
 #pragma unroll
   for (int k = 0; k < 4; ++k)
     if (g + 4 * k < ngrp) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float v = softplus_f(acc[k][e]);
+        const float v = softplus_f(acc[k][e]) - vref;
         acc[k][e] = v; s += v; ss = fmaf(v, v, ss);
       }
     }
@@ -262,12 +268,13 @@ __global__ void __launch_bounds__(STEMW_THREADS) stem_layer_wide_kernel(const St
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       float s = 0.f, ss = 0.f;
+      const float vref = __shfl_sync(0xffffffffu, softplus_f(acc[p][0][0]), lane & ~3);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         if (g + 4 * k < ngrp) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float v = softplus_f(acc[p][k][e]);
+            const float v = softplus_f(acc[p][k][e]) - vref;
             acc[p][k][e] = v; s += v; ss = fmaf(v, v, ss);
           }
         }
@@ -399,11 +406,17 @@ __global__ void __launch_bounds__(RO_THREADS) readout_pool_kernel(const ReadoutA
         const float4 yv = __ldg(yp + j), rv = __ldg(rp + j);
         t = make_float4(yv.x + rv.x, yv.y + rv.y, yv.z + rv.z, yv.w + rv.w);
         if (a.norm_post_order) t = make_float4(softplus_f(t.x), softplus_f(t.y), softplus_f(t.z), softplus_f(t.w));
-        s += t.x + t.y + t.z + t.w;
-        ss = fmaf(t.x, t.x, fmaf(t.y, t.y, fmaf(t.z, t.z, fmaf(t.w, t.w, ss))));
       }
       v[k][0] = t.x; v[k][1] = t.y; v[k][2] = t.z; v[k][3] = t.w;
     }
+    // moments of the values minus the pixel's first channel (see layer_norm_regs)
+    const float vref = __shfl_sync(0xffffffffu, v[0][0], lane & ~3);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (g + 4 * k < ngrp) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { v[k][e] -= vref; s += v[k][e]; ss = fmaf(v[k][e], v[k][e], ss); }
+      }
     s += __shfl_xor_sync(0xffffffffu, s, 1);  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
     const float mean = s / (float)C;
@@ -461,9 +474,10 @@ __global__ void __launch_bounds__(SM_MAXC) readout_head_kernel(const ReadoutArgs
   __syncthreads();
   if (tid == 0) {
     float s = 0.f, ss = 0.f;
-    for (int c = 0; c < C; ++c) { s += v[c]; ss = fmaf(v[c], v[c], ss); }
+    const float vref = v[0];
+    for (int c = 0; c < C; ++c) { const float d = v[c] - vref; s += d; ss = fmaf(d, d, ss); }
     const float mean = s / (float)C;
-    stats[0] = mean;
+    stats[0] = mean + vref;
     stats[1] = rsqrtf(fmaxf(ss / (float)C - mean * mean, 0.f) + 1e-6f);
   }
   __syncthreads();
