@@ -66,11 +66,14 @@ def test_block_at_full_size(workload, T, HW):
     assert not torch.equal(y2[:, t0:], y[:, t0:])
 
 
-@pytest.mark.parametrize("workload", ["cfg2", "cfg3", "cfg4"])
+@pytest.mark.parametrize("workload", ["cfg2", "cfg3", "cfg4", "gated32", "cfg1"])
 def test_model_at_full_size(workload):
     """The bench's own model, weights and synthetic inputs: logits of picked samples against the
-    oracle model, logits through the last-frame-only path and through the host-buffer call."""
-    model, B = _model_and_block(workload)
+    oracle model, logits through the last-frame-only path and through the host-buffer call.
+    (cfg1 is the batch-8 configuration: all of its samples are compared.)"""
+    model = bench.make_model(workload)
+    B = bench.WORKLOADS[workload]["B"]
+    PICK = [0, 77, 127] if B == 128 else list(range(B))
     x_np = bench.make_inputs(workload, B, seed0=1000)
     variables = model.init(0, x_np.shape)
     bound = model.bind(variables)
