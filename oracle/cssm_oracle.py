@@ -44,7 +44,8 @@ def silu(x):
 
 
 def sigmoid(x):
-    return 1.0 / (1.0 + np.exp(-x))
+    z = np.exp(-np.abs(x))                      # no overflow for large |x|
+    return np.where(np.asarray(x) >= 0, 1.0 / (1.0 + z), z / (1.0 + z))
 
 
 def softplus(x):
