@@ -40,7 +40,7 @@ GOOM_EPS = 1e-7
 
 # --------------------------------------------------------------------------- basics
 def silu(x):
-    return x / (1.0 + np.exp(-x))
+    return x * sigmoid(x)
 
 
 def sigmoid(x):

@@ -97,6 +97,32 @@ def test_model_parity(case):
     assert np.array_equal(lh, logits)
 
 
+@pytest.mark.parametrize("cssm_type", ["gated", "gdn", "no_gate", "add_kqv_1", "deltanet"])
+def test_sparse_stroke_images(cssm_type):
+    """The benchmark's stroke images (94 % background): most stem pixels have all channels equal,
+    which LayerNorm must map to exactly zero; every mixer follows the stem."""
+    from cssm_b200 import synth
+    extra = dict(delta_key_dim=4, qkv_conv_size=3) if cssm_type == "gdn" else {}
+    m = _model(cssm_type, 16, 5, "spatiotemporal" if cssm_type != "no_gate" else "none", "default", 1,
+               "max", "pre", seq_len=3, **extra)
+    x = synth.stroke_batch(3, seed0=4000)
+    H, W = m.feature_hw(128, 128)
+    bkw = _block_kwargs(m)
+    p = so.init_simple_params(9, cin=1, embed_dim=16, H=H, W=W, num_classes=2, cssm_type=cssm_type,
+                              stem_mode="default", stem_layers=1, bias_scale=0.0, block_kwargs=bkw)
+    ref, inter = so.simple_forward(p, x, cssm_type=cssm_type, seq_len=3, stem_mode="default",
+                                   stem_layers=1, pool_type="max", readout_norm="pre",
+                                   block_kwargs=bkw, return_intermediates=True)
+    bound = m.bind({"params": p})
+    xd = torch.from_numpy(x).cuda()
+    feat = bound.stem(xd).cpu().numpy()
+    assert orc.rel_l2(feat, inter["stem"][:, 0]) <= 1e-5
+    background = np.abs(inter["stem"][:, 0]).max(-1) == 0          # exact zeros in the oracle
+    assert background.mean() > 0.5
+    assert np.abs(feat[background]).max() == 0.0
+    assert orc.rel_l2(bound(xd).cpu().numpy(), ref) <= TOL
+
+
 def test_unsupported_fields_raise():
     with pytest.raises(NotImplementedError):
         SimpleCSSM(cssm_type="gated", depth=2).bind({"params": {}})
