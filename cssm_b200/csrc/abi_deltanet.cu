@@ -218,7 +218,6 @@ static int deltanet_validate(const cssm_deltanet_desc* d) {
   if (d->gate_type != CSSM_GATE_DENSE && d->gate_type != CSSM_GATE_FACTORED &&
       d->gate_type != CSSM_GATE_CHANNEL)
     return CSSM_ERR_UNSUPPORTED;
-  if (d->gate_type == CSSM_GATE_CHANNEL && ((size_t)d->H * d->W) % 4 != 0) return CSSM_ERR_UNSUPPORTED;
   const bool crop_h = d->kernel_size > d->H, crop_w = d->kernel_size > d->W;
   if (crop_h != crop_w) return CSSM_ERR_UNSUPPORTED;
   if (deltanet_smem_bytes(d->H, d->W) > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
@@ -368,6 +367,7 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
       if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
     }
     // k *= B_k, v *= B_v in the spatial domain
+    // C is a multiple of 4, so every frame's planes start and end on a float4 boundary
     const size_t per_frame4 = (size_t)2 * C * HW / 4, fstride4 = (size_t)3 * C * HW / 4;
     const size_t total4 = per_frame4 * BT;
     deltanet_kv_gate_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, st>>>(

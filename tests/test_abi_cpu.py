@@ -185,7 +185,7 @@ def test_deltanet_descriptor_validation_without_gpu():
     w = _lib.DeltaNetWeights()
     assert L.cssm_deltanet_forward(C.byref(d), C.byref(w), None, None, None, None, 0, None) == 1
     assert L.cssm_deltanet_workspace_bytes(C.byref(desc(gate_type=2))) > L.cssm_deltanet_workspace_bytes(C.byref(d))
-    assert L.cssm_deltanet_plan_bytes(C.byref(desc(gate_type=2, H=7, W=7, kernel_size=3))) == 0   # H*W % 4
+    assert L.cssm_deltanet_plan_bytes(C.byref(desc(gate_type=2, H=7, W=7, kernel_size=3))) > 0
     from cssm_b200 import DeltaNetCSSM
     with pytest.raises(NotImplementedError):
         DeltaNetCSSM(channels=8, gate_type="scalar").init(0, (1, 2, 8, 8, 8))

@@ -44,6 +44,8 @@ def _run(case, gate_type, rope, scan_mode="associative", seed=0):
     ((2, 6, 32, 32, 8, 11), "channel", "mrope"),
     ((2, 3, 14, 10, 12, 3), "channel", "spatial_only"),
     ((1, 1, 6, 6, 4, 3), "channel", "temporal"),
+    ((2, 3, 7, 7, 4, 3), "channel", "spatiotemporal"),          # H*W not a multiple of 4
+    ((2, 2, 7, 5, 12, 3), "channel", "none"),
 ], ids=lambda c: "x".join(map(str, c)) if isinstance(c, tuple) else str(c))
 def test_block_parity(case, gate_type, rope):
     assert _run(case, gate_type, rope) <= TOL

@@ -60,7 +60,7 @@ def _block(name, shape, rng):
         p = orc.init_additive1_params(3, C, H, W, kernel_size=ks, gate_type="dense", bias_scale=0.1)
         return AdditiveCSSM(channels=C, single_state=True, **kw), p, orc.additive1_forward, kw
     if name == "deltanet":
-        gt = "channel" if (H * W) % 4 == 0 else "dense"
+        gt = "channel"
         kw = dict(kernel_size=ks, rope_mode="spatiotemporal", gate_type=gt)
         p = orc.init_deltanet_params(4, C, H, W, kernel_size=ks, gate_type=gt, bias_scale=0.1)
         p["output_proj"]["bias"][:] = 0
