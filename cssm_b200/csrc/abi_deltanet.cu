@@ -224,7 +224,7 @@ static int deltanet_validate(const cssm_deltanet_desc* d) {
   return CSSM_OK;
 }
 
-struct DnPlan { size_t what, rope_t, rope_h, rope_w, rope_nz, tcode, total; };
+struct DnPlan { size_t what, rope_t, rope_h, rope_w, rope_nz, tcode, gw, gb, total; };
 static DnPlan deltanet_plan_layout(const cssm_deltanet_desc& d) {
   DnPlan p;
   const size_t Wf = d.W / 2 + 1, n2 = d.C / 2;
@@ -235,6 +235,10 @@ static DnPlan deltanet_plan_layout(const cssm_deltanet_desc& d) {
   p.rope_w = off; off += round_up((size_t)d.W * n2 * sizeof(float2), 256);
   p.rope_nz = off; off += round_up(n2 * sizeof(float), 256);
   p.tcode = off;  off += round_up((size_t)d.T * d.C * sizeof(float), 256);
+  // channel gates: the B_k, B_v, C_gate conv kernels packed side by side as one (C, 3C) matrix
+  const bool ch = d.gate_type == CSSM_GATE_CHANNEL;
+  p.gw = off;     off += ch ? round_up((size_t)d.C * 3 * d.C * sizeof(float), 256) : 0;
+  p.gb = off;     off += ch ? round_up((size_t)3 * d.C * sizeof(float), 256) : 0;
   p.total = off;
   return p;
 }
@@ -287,6 +291,17 @@ int cssm_deltanet_plan_init(const cssm_deltanet_desc* d, const cssm_deltanet_wei
                          (float2*)(base + p.rope_w), (float*)(base + p.rope_nz), d->T, d->H, d->W,
                          d->C, d->rope_mode, d->rope_base, st);
   if (s != CSSM_OK) return s;
+  if (d->gate_type == CSSM_GATE_CHANNEL) {
+    const size_t cb = (size_t)d->C * sizeof(float);
+    for (int i = 0; i < 3; ++i) {
+      if (!w->gate_kernel[2 + i] || !w->gate_bias[2 + i]) return CSSM_ERR_NULL;
+      cudaError_t e = cudaMemcpy2DAsync(base + p.gw + i * cb, 3 * cb, w->gate_kernel[2 + i], cb, cb,
+                                        (size_t)d->C, cudaMemcpyDeviceToDevice, st);
+      if (e == cudaSuccess)
+        e = cudaMemcpyAsync(base + p.gb + i * cb, w->gate_bias[2 + i], cb, cudaMemcpyDeviceToDevice, st);
+      if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+    }
+  }
   return launch_tcode((float*)(base + p.tcode), d->T, d->C, d->rope_base, st);
 }
 
@@ -356,16 +371,14 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
     if ((s = check_launch()) != CSSM_OK) return s;
     // spatial gates sigmoid(Conv1x1(rotated x)) -> planes (BT, 3C, H, W): B_k, B_v, C_gate
     float* gsp = (float*)(ws + l.gsp);
-    for (int i = 0; i < 3; ++i) {
-      memset(&g, 0, sizeof(g));
-      g.M = BT * HW; g.N = C; g.K = C; g.HW = HW;
-      g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
-      g.Wk = w->gate_kernel[2 + i]; g.bias = w->gate_bias[2 + i];
-      g.out = gsp; g.o_planes = 3 * C; g.o_plane0 = i * C;
-      g.T = d->T; g.H = d->H; g.W = d->W;
-      g.out_act = 2; g.act_n0 = 0;
-      if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
-    }
+    memset(&g, 0, sizeof(g));
+    g.M = BT * HW; g.N = 3 * C; g.K = C; g.HW = HW;
+    g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
+    g.Wk = (const float*)(pl + p.gw); g.bias = (const float*)(pl + p.gb);     // packed by plan_init
+    g.out = gsp; g.o_planes = 3 * C; g.o_plane0 = 0;
+    g.T = d->T; g.H = d->H; g.W = d->W;
+    g.out_act = 2; g.act_n0 = 0;
+    if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
     // k *= B_k, v *= B_v in the spatial domain
     // C is a multiple of 4, so every frame's planes start and end on a float4 boundary
     const size_t per_frame4 = (size_t)2 * C * HW / 4, fstride4 = (size_t)3 * C * HW / 4;

@@ -370,7 +370,8 @@ typedef struct cssm_deltanet_weights {
 
 size_t cssm_deltanet_plan_bytes(const cssm_deltanet_desc* d);
 size_t cssm_deltanet_workspace_bytes(const cssm_deltanet_desc* d);
-/* W_hat = squash(rfft2(pad(kernel))) (cssm.py:3712-3732), RoPE tables, temporal code. */
+/* W_hat = squash(rfft2(pad(kernel))) (cssm.py:3712-3732), RoPE tables, temporal code; with
+ * channel gates also the B_k / B_v / C_gate conv kernels packed side by side (weights only). */
 int cssm_deltanet_plan_init(const cssm_deltanet_desc* d, const cssm_deltanet_weights* w, void* plan,
                             size_t plan_bytes, void* stream);
 /* y = DeltaNetCSSM(x); x, y: (B,T,H,W,C) fp32 channels-last. */
