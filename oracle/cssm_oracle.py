@@ -585,7 +585,7 @@ def gdn_forward(params, x, *, delta_key_dim=4, kernel_size=11, rope_mode="none",
                 no_spectral_clamp=False, dtype=np.float64, scan="direct",
                 return_intermediates=False):
     """GatedDeltaNetCSSM.__call__, general path (cssm.py:4685-5141), for
-    gate_type in {'factored','dense'}, separable qkv conv, no learned_t rope, no InT
+    gate_type in {'factored','dense','channel','scalar'}, separable qkv conv, no learned_t rope, no InT
     attention, no cross-frequency conv, no SSL head.
 
     The reference materialises M_t (d_k x d_k) and Delta_t (d_v x d_k) per bin, repeats
@@ -600,7 +600,7 @@ def gdn_forward(params, x, *, delta_key_dim=4, kernel_size=11, rope_mode="none",
     dv = dk
     assert C % dk == 0
     nh = C // dk
-    if gate_type not in ("factored", "dense"):
+    if gate_type not in ("factored", "dense", "channel", "scalar"):
         raise NotImplementedError(gate_type)
     x = apply_rope(x, rope_mode, rope_base)
 
@@ -620,6 +620,15 @@ def gdn_forward(params, x, *, delta_key_dim=4, kernel_size=11, rope_mode="none",
 
     def gate(name, bounded=False, spatial=False):
         Wd = W if spatial else Wf
+        if gate_type == "channel":       # cssm.py:4800-4810: per-pixel 1x1 conv / per-head scalars
+            if spatial:
+                kern = params[name]["kernel"].reshape(C, C).astype(dtype)
+                return sigmoid(x @ kern + params[name]["bias"].astype(dtype))      # (B,T,H,W,C)
+            raw = sigmoid(dense(ctx, params[name])).reshape(B, T, nh, 1, 1)
+            return 0.1 + 0.89 * raw if bounded else raw
+        if gate_type == "scalar":        # cssm.py:4825-4833: one scalar per frame
+            raw = sigmoid(dense(ctx, params[name])).reshape(B, T, 1, 1, 1)
+            return raw if spatial or not bounded else 0.1 + 0.89 * raw
         if gate_type == "factored":
             raw = sigmoid(dense(ctx, params[f"{name}_h"])[..., :, None]
                           + dense(ctx, params[f"{name}_w"])[..., None, :])
