@@ -4,10 +4,12 @@ TEST INFRASTRUCTURE ONLY.  Nothing that ships (the `cssm_b200` package) may impo
 this file; it is the checker for the CUDA path (tests, the smoke check and the
 `cpu_baseline` / reference leg of the benchmark).
 
-PARITY UNPINNED at the block level: the reference implementation is Python/JAX/Flax
-and neither JAX nor Flax can be imported where this repository is built, and the
-reference's own tests hold no stored vectors for `GatedCSSM` / `GatedDeltaNetCSSM`.
-What pins this restatement instead:
+PINNED to the reference's own code: tests/golden/make_reference_golden.py imports the
+reference's unmodified src/models/*.py on NumPy stand-ins for jax / flax.linen (oracle/_shim)
+and stores what they compute in double precision; tests/test_reference_pin.py requires every
+function here to reproduce those outputs to 1e-9 (all RoPE modes, gate types and activations,
+kernel larger than the plane, ragged planes, the BASELINE block shapes, the GDN static-image
+path, the scalar-scan blocks).  Further checks that need no reference checkout:
   * NumPy's FFT has the same conventions as `jnp.fft.rfft2/irfft2` (unnormalised
     forward, 1/(H*W) inverse, C2R ignoring the imaginary part of the DC / Nyquist
     columns);

@@ -2,9 +2,9 @@
 last-frame readout -> logits.
 
 TEST INFRASTRUCTURE ONLY (same rule as cssm_oracle.py: only tests, the smoke check and the CPU
-legs of the benchmark may import it).  PARITY UNPINNED for the same reason as the block oracle:
-the reference is JAX/Flax, which cannot be imported where this repository is built, and its
-tests store no vectors for this model.
+legs of the benchmark may import it).  PINNED like the block oracle: tests/test_reference_pin.py
+compares it with outputs of the reference's own, unmodified src/models/simple_cssm.py run on
+NumPy stand-ins for jax / flax.linen (tests/golden/ref/simple_*.npz), to 1e-9.
 
 Reference lines followed (paths inside drewlinsley/CSSM):
   src/models/simple_cssm.py:86-157   fields and defaults

@@ -76,7 +76,13 @@ def run_reference(case, params=None, stats=None):
     module = getattr(mod, case["ref_class"])(**kwargs)
     x = rc.make_input(case).astype(np.float64)
     call_kw = case.get("call_kwargs", {})
-    if params is None:
+    if params is None and "seeded_params" in case:
+        params, stats = rc.seeded_params(case)
+        tree = module.init(jax.random.PRNGKey(0), x[:1], **call_kw)
+        shapes = lambda t: {k: v.shape for k, v in rc.flatten(t).items()}
+        assert shapes(tree["params"]) == shapes(params), "seeded tree differs from the reference's"
+        assert shapes(tree["batch_stats"]) == shapes(stats)
+    elif params is None:
         variables = module.init(jax.random.PRNGKey(case["seed"]), x, **call_kw)
         rng = np.random.default_rng(case["seed"] + 7)
         params = perturb(variables["params"], rng, case)
@@ -91,8 +97,10 @@ def run_reference(case, params=None, stats=None):
 def write_case(case):
     params, stats, y = run_reference(case)
     pos = rc.stored_positions(case["name"], y.size)
-    arrays = {"p:" + k: v for k, v in rc.flatten(params).items()}
-    if stats is not None:
+    arrays = {}
+    if "seeded_params" not in case:
+        arrays = {"p:" + k: v for k, v in rc.flatten(params).items()}
+    if stats is not None and "seeded_params" not in case:
         arrays.update({"s:" + k: v for k, v in rc.flatten(stats).items()})
     arrays["y"] = rc.pick(y, pos)
     arrays["y_shape"] = np.asarray(y.shape)

@@ -60,12 +60,23 @@ def unflatten(flat):
     return tree
 
 
+def seeded_params(case):
+    """Parameter trees that are regenerated from a seed instead of stored (the full-size model)."""
+    from oracle import shvit_oracle as sv
+    kind, seed, kw = case["seeded_params"]
+    assert kind == "shvit"
+    return sv.init_shvit_params(seed, **kw)
+
+
 def load(name):
     """-> (params tree (float32), batch_stats tree or None, stored reference values (float64),
     positions or None)."""
     with np.load(os.path.join(REF_DIR, name + ".npz")) as z:
-        params = unflatten({k[2:]: z[k] for k in z.files if k.startswith("p:")})
-        stats = unflatten({k[2:]: z[k] for k in z.files if k.startswith("s:")}) or None
+        if "seeded_params" in BY_NAME[name]:
+            params, stats = seeded_params(BY_NAME[name])
+        else:
+            params = unflatten({k[2:]: z[k] for k in z.files if k.startswith("p:")})
+            stats = unflatten({k[2:]: z[k] for k in z.files if k.startswith("s:")}) or None
         pos = z["positions"] if "positions" in z.files else None
         return params, stats, z["y"], pos
 
@@ -139,6 +150,33 @@ def _simple(name, shape, seed, block_kwargs, **kw):
                 oracle="simple_forward", block_kwargs=block_kwargs, mirror="SimpleCSSM",
                 mirror_kwargs=ref, shape=shape, seed=seed, input="uniform", call_kwargs=dict(training=False))
 
+
+def _shvit(name, shape, seed, seeded=None, mirror_dtype="float32", **kw):
+    """CSSMSHViT with gated mixers; kw are CSSMSHViT fields."""
+    ref = dict(cssm_type="gated", **kw)
+    okw = {k: v for k, v in kw.items() if k not in ("num_classes", "mlp_ratio", "drop_path_rate")}
+    c = dict(name=name, family="shvit", ref_class="CSSMSHViT", ref_kwargs=ref,
+             oracle="shvit_forward", oracle_kwargs=okw, mirror="CSSMSHViT",
+             mirror_kwargs=dict(ref, dtype=mirror_dtype), shape=shape, seed=seed,
+             call_kwargs=dict(training=False),
+             tol_gpu=2e-2 if mirror_dtype == "bfloat16" else 1e-4)
+    if seeded is not None:
+        init_kw = {k: v for k, v in kw.items() if k in (
+            "embed_dims", "depths", "use_cssm_stages", "kernel_sizes", "num_classes", "mlp_ratio",
+            "gate_type", "short_conv_size", "short_conv_spatial_size", "use_pos_conv", "use_dwconv")}
+        c["seeded_params"] = ("shvit", seeded, dict(in_hw=shape[1:3], **init_kw))
+    return c
+
+
+def _shvit_block(name, shape, seed, **kw):
+    ref = dict(dim=shape[-1], cssm_type="gated", **kw)
+    okw = dict(kw)
+    return dict(name=name, family="shvit_block", ref_class="CSSMSHViTBlock", ref_kwargs=ref,
+                oracle="cssm_block", oracle_kwargs=okw, mirror="CSSMSHViTBlock",
+                mirror_kwargs=ref, shape=shape, seed=seed)
+
+
+_S1 = dict(embed_dims=(64, 128, 256, 384), depths=(1, 2, 2, 1), num_classes=1000)
 
 CASES = [
     # ---- GatedCSSM: the BASELINE block configurations at small batch / channel counts
@@ -237,6 +275,20 @@ CASES = [
             cssm_type="gdn", embed_dim=8, kernel_size=5, gate_type="factored",
             stem_mode="pathtracker", pool_type="mean", pos_embed="spatiotemporal",
             delta_key_dim=4, num_classes=2),
+    # ---- CSSM-SHViT around the gated mixer (BASELINE configs[4]: T = 1, kernel_size 1)
+    _shvit_block("shvit_block_stage2_14", (2, 14, 14, 32), 501, num_timesteps=1, kernel_size=1,
+                 short_conv_spatial_size=0, gate_type="factored"),
+    _shvit_block("shvit_block_stage3_7_T3_ks3", (2, 7, 7, 24), 502, num_timesteps=3, kernel_size=3,
+                 gate_type="factored", rope_mode="spatiotemporal"),
+    _shvit_block("shvit_block_no_posconv_no_dwconv", (2, 8, 8, 16), 503, num_timesteps=2,
+                 kernel_size=3, gate_type="dense", use_pos_conv=False, use_dwconv=False),
+    _shvit("shvit_tiny_64", (2, 64, 64, 3), 511, embed_dims=(16, 32, 48, 64), depths=(1, 2, 2, 1),
+           num_classes=10, num_timesteps=1, kernel_sizes=(1, 1, 1, 1), short_conv_spatial_size=0),
+    _shvit("shvit_tiny_T2_ks3_meanpool", (2, 32, 32, 3), 512, embed_dims=(16, 16, 32, 32),
+           depths=(1, 1, 1, 1), num_classes=5, num_timesteps=2, kernel_sizes=(3, 3, 3, 3),
+           head_pool="mean"),
+    _shvit("shvit_s1_224_cfg5", (2, 224, 224, 3), 513, seeded=5130, mirror_dtype="bfloat16",
+           num_timesteps=1, kernel_sizes=(1, 1, 1, 1), short_conv_spatial_size=0, **_S1),
 ]
 
 BY_NAME = {c["name"]: c for c in CASES}

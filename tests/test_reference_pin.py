@@ -30,8 +30,9 @@ def oracle_output(case, params, stats=None):
                                  block_kwargs=case["block_kwargs"])
     if fam in ("shvit", "shvit_block"):
         from oracle import shvit_oracle as sv
-        fn = getattr(sv, case["oracle"])
-        return fn(params, stats, x, **case["oracle_kwargs"])
+        if fam == "shvit_block":
+            return sv.cssm_block(x, params, **case["oracle_kwargs"])
+        return sv.shvit_forward(params, stats, x, **case["oracle_kwargs"])
     return getattr(orc, case["oracle"])(params, x, **case["oracle_kwargs"])
 
 
@@ -44,7 +45,7 @@ def test_oracle_reproduces_reference(name):
     assert err <= case.get("tol_oracle", TOL), f"{name}: {err:.3e}"
 
 
-_LIVE = ["gated_rope_mrope_c8", "gdn_dense_gates", "gdn_static_T4_16", "nogate_ks3",
+_LIVE = ["shvit_tiny_64", "shvit_block_stage2_14", "gated_rope_mrope_c8", "gdn_dense_gates", "gdn_static_T4_16", "nogate_ks3",
          "additive1_factored", "deltanet_channel", "simple_gated_cfg2"]
 
 
