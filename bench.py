@@ -302,6 +302,9 @@ def block_stage_times(bound, feat5, steps, dev, st):
     y = torch.empty_like(feat5)
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(8)]
     blk(feat5, out=y)
+    d = blk.desc(tuple(feat5.shape))
+    plan = blk.plan(d)
+    ws = blk.buf.get("ws", L.cssm_gdn_workspace_bytes(C.byref(d)))
     for e in evs:
         e.record(st)                                  # creates the raw cudaEvent_t handles
     torch.cuda.synchronize(dev)
@@ -310,9 +313,9 @@ def block_stage_times(bound, feat5, steps, dev, st):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(st)
     for k in range(steps):
-        L.cssm_debug_gdn_stage_events(arr)
-        blk(feat5, out=y)
-        L.cssm_debug_gdn_stage_events(None)
+        check(L.cssm_gdn_forward_timed(C.byref(d), C.byref(blk.w), plan.data_ptr(), feat5.data_ptr(),
+                                       y.data_ptr(), ws.data_ptr(), ws.numel(), st.cuda_stream, arr),
+              "gdn_forward_timed")
         torch.cuda.synchronize(dev)
         for i, n in enumerate(GDN_STAGES):
             stage[n] += evs[i].elapsed_time(evs[i + 1]) / steps

@@ -143,6 +143,8 @@ SIGNATURES = {
     "cssm_gdn_plan_init": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, C.c_size_t, _P]),
     "cssm_gdn_forward": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
                                    C.c_size_t, _P]),
+    "cssm_gdn_forward_timed": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
+                                         C.c_size_t, _P, C.POINTER(C.c_void_p)]),
     "cssm_gdn_forward_last": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P, _P,
                                         C.c_size_t, _P]),
     "cssm_gdn_forward_static_image": (C.c_int, [C.POINTER(GdnDesc), C.POINTER(GdnWeights), _P, _P, _P,
@@ -174,9 +176,7 @@ SIGNATURES = {
     "cssm_simple_host_workspace_bytes": (C.c_size_t, [C.POINTER(SimpleDesc), _P]),
     "cssm_simple_forward_host": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P,
                                            _P, _P, _P, _P, C.c_size_t, C.c_int32, _P]),
-    "cssm_debug_set_gemm_backend": (C.c_int, [C.c_int]),
-    "cssm_debug_tc_error": (C.c_int, [C.POINTER(C.c_int)]),
-    "cssm_debug_gdn_stage_events": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "cssm_device_error": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "cssm_static_scratch_bytes": (C.c_size_t, []),
     "cssm_gated_forward_static": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
                                             _P, _P]),

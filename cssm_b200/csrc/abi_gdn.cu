@@ -68,8 +68,9 @@ static int gdn_validate(const cssm_gdn_desc* d) {
   return CSSM_OK;
 }
 
-// Optional per-stage timing hook (diagnostics): when set, cssm_gdn_forward records
-// events[i] on its stream before stage i (i = 0..6) and events[7] after the last stage.
+// Stage events of the call in progress on this thread (cssm_gdn_forward_timed sets it for the
+// duration of its own call only): events[i] is recorded on the stream before stage i
+// (i = 0..6) and events[7] after the last stage.
 static thread_local cudaEvent_t* g_stage_events = nullptr;
 static inline void mark(int i, cudaStream_t st) {
   if (g_stage_events != nullptr && g_stage_events[i] != nullptr) cudaEventRecord(g_stage_events[i], st);
@@ -131,9 +132,13 @@ int cssm_gdn_forward_static_image(const cssm_gdn_desc* d, const cssm_gdn_weights
   return gdn_forward_internal(d, w, plan, x, y, workspace, workspace_bytes, stream, 0, 2);
 }
 
-int cssm_debug_gdn_stage_events(void** events) {
-  g_stage_events = reinterpret_cast<cudaEvent_t*>(events);
-  return CSSM_OK;
+int cssm_gdn_forward_timed(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                           const float* x, float* y, void* workspace, size_t workspace_bytes,
+                           void* stream, void** stage_events) {
+  g_stage_events = reinterpret_cast<cudaEvent_t*>(stage_events);
+  const int s = gdn_forward_internal(d, w, plan, x, y, workspace, workspace_bytes, stream, 0, 0);
+  g_stage_events = nullptr;
+  return s;
 }
 
 }  // extern "C"

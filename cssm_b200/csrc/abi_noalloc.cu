@@ -21,7 +21,10 @@ constexpr int MAX_DEVICES = 64;
 static std::mutex g_mu;
 static void* g_scratch_ptr[MAX_DEVICES] = {nullptr};
 
-// Device address of the scratch array on the CURRENT device; resolved once per device.
+// Device address of the scratch array on the CURRENT device; resolved once per device and kept
+// for the life of the process.  The address belongs to the device's primary context: after
+// cudaDeviceReset (or after a host framework has destroyed and re-created that context) it is
+// stale and this entry point must not be called again in that process.
 static int static_scratch(void** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);

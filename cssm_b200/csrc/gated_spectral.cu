@@ -13,34 +13,34 @@ namespace cssm {
 // 288 threads; thread roles and shared-memory layout are those of r64.cuh.  The lane keeps the
 // state of its 8 bins (kh = a + 8q of column grp) in registers for all T steps.
 // The x_main plane of step t+1 and the (SiLU'd) z plane of step t+1 are staged in shared memory
-// by TMA bulk copies (one 16 KB copy per plane, issued by a lane of the otherwise idle ninth warp
-// right after the first barrier of step t) and land while step t computes; gate maps and K_hat
-// are loaded at the top of the column phase.  Variant <68> (default) uses one TMA tensor copy per
-// plane whose 68-wide box pads every row to 272 bytes, which makes the row passes' reads
-// bank-conflict free; variant <64> uses untiled bulk copies into dense rows (4-way conflicts).
+// by TMA tensor copies (one per plane, issued by a lane of the otherwise idle ninth warp right
+// after the first barrier of step t) and land while step t computes; gate maps and K_hat are
+// loaded at the top of the column phase.  The copy's 68-wide box over the 64-wide rows pads every
+// row to 272 bytes (the four out-of-bounds columns arrive as zeros), which makes the row passes'
+// reads bank-conflict free.
+// A bounded mbarrier wait that expires records a code in g_spec_error (read it with
+// cssm_device_error) and the whole CTA leaves its step loop at the next barrier without storing
+// anything more.
 constexpr int R64_THREADS = R64_NT;
 constexpr int R64_PLANE_F = 64 * 68;
 constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64_PLANE_F * 4 + 128;
 
 __device__ int g_spec_error = 0;
-int g_spec_variant = 0;      // 0 padded rows via tensor TMA, 1 dense rows via bulk TMA, 2 warp-specialised pipeline
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
                               int last_only, int nogate, cudaStream_t st);
-int launch_gated_spectral_ws(float* xz, const cf* khat, const float* gates, int B, int T, int C,
-                             cudaStream_t st);
 
-// PRS: floats per staged row: 68 = padded (one copy per row), 64 = dense (one per plane).
 // LAST: only the last step's output plane is produced (compile-time, so that the all-frames
 // kernel carries none of the branches).
 // MODE 0: gated block (gate maps, output times the silu(z) plane).  MODE 1: the ungated recurrence
 // S_t = K_hat S_{t-1} + X_hat_t of NoGateCSSM (no gate maps, no z plane).  MODE 2: gate maps but no
 // z plane (the single-state AdditiveCSSM).
-template <int PRS, bool LAST, int MODE>
+template <bool LAST, int MODE>
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C,
                    const __grid_constant__ CUtensorMap pmap) {
   constexpr int last_only = LAST ? 1 : 0;
+  constexpr int PRS = 68;                                     // floats per staged row
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // TMA tensor copies need a 128-byte aligned destination; dynamic shared memory is only
   // guaranteed 16-byte aligned, so the base is rounded up (the launch adds 128 bytes)
@@ -50,6 +50,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
   constexpr int R64_PRS = PRS;
   float* zbuf = xbuf + R64_PLANE_F;                           // two buffers
   __shared__ __align__(8) uint64_t bars[3];                   // x, z[0], z[1]
+  __shared__ int s_bad;                                       // a bounded wait expired
   R64Ctx c;
   r64_init(c, EX, EX + R64_EX_CF, EX + R64_EX_CF + R64_ZR_CF);
 
@@ -62,6 +63,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
   if (threadIdx.x == 0) {
     tc::mbar_init(&bars[0], 1); tc::mbar_init(&bars[1], 1); tc::mbar_init(&bars[2], 1);
     tc::fence_mbar_init();
+    s_bad = 0;
   }
   __syncthreads();
   // stage step `tl`: x_main plane into xbuf (if want_x) and z plane into zbuf[tl & 1]
@@ -78,19 +80,12 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     const float* xs = x0 + (size_t)tl * fstride;
     const float* zs = xs + (size_t)C * HW;
     float* zd = zbuf + (tl & 1) * R64_PLANE_F;
-    if (PRS == 64) {
-      if (c.lane == 0) {
-        if (want_x) tc::bulk_g2s(xbuf, xs, 64 * 256, &bars[0]);
-        if (want_z) tc::bulk_g2s(zd, zs, 64 * 256, bz);
-      }
-    } else {
-      // one tensor copy per plane: the 68-wide box reads 4 columns past the 64-wide rows, which
-      // are out of bounds for the map and arrive as zeros, so the rows land 272 bytes apart
-      if (c.lane == 0) {
-        const int row0 = (int)((xs - xz) >> 6);           // first image row of the plane
-        if (want_x) tc::tma_load_2d(xbuf, &pmap, 0, row0, &bars[0]);
-        if (want_z) tc::tma_load_2d(zd, &pmap, 0, row0 + C * 64, bz);
-      }
+    // one tensor copy per plane: the 68-wide box reads 4 columns past the 64-wide rows, which
+    // are out of bounds for the map and arrive as zeros, so the rows land 272 bytes apart
+    if (c.lane == 0) {
+      const int row0 = (int)((xs - xz) >> 6);           // first image row of the plane
+      if (want_x) tc::tma_load_2d(xbuf, &pmap, 0, row0, &bars[0]);
+      if (want_z) tc::tma_load_2d(zd, &pmap, 0, row0 + C * 64, bz);
     }
   };
   stage(0, true);
@@ -108,7 +103,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
 
     // ---- forward rows (from the staged plane) ----
     if (c.row_on) {
-      if (!tc::mbar_wait(&bars[0], t & 1)) atomicExch(&g_spec_error, 1);
+      if (!tc::mbar_wait(&bars[0], t & 1)) { atomicExch(&g_spec_error, 1); s_bad = 1; }
       cf v[8];
 #pragma unroll
       for (int m = 0; m < 8; ++m) v[m] = mk(xbuf[soff + 8 * m], xbuf[soff + R64_PRS + 8 * m]);
@@ -117,6 +112,7 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       for (int k2 = 0; k2 < 8; ++k2) c.ZR[c.grp * R64_ZRS + c.a + 8 * k2] = v[k2];
     }
     __syncthreads();
+    if (s_bad) break;                                 // same for the whole CTA (read after the barrier)
     if (t + 1 < T) stage(t + 1, true);
 
     // ---- forward columns, recurrence, inverse columns ----
@@ -160,7 +156,10 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       float* y0 = xp + roff;
       if (MODE == 0) {
         // in last-only mode the z barrier of this slot completes exactly once (phase 0)
-        if (!tc::mbar_wait(&bars[1 + (t & 1)], last_only ? 0 : (t >> 1) & 1)) atomicExch(&g_spec_error, 2);
+        if (!tc::mbar_wait(&bars[1 + (t & 1)], last_only ? 0 : (t >> 1) & 1)) {
+          atomicExch(&g_spec_error, 2); s_bad = 1;
+          continue;                 // no store; the CTA leaves at the next step's first barrier
+        }
         const float* zs = zbuf + (t & 1) * R64_PLANE_F + soff;
         // finish all products before the first store: the stores go through a generic pointer,
         // so shared-memory loads placed between them could not be hoisted
@@ -177,10 +176,18 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
     // before the second barrier above); GB is next written after the next first barrier; xbuf
     // and zbuf[(t+1)&1] are refilled only after the next first barrier.
   }
+  // error path only: give copies that may still be in flight a bounded time (~1 ms) to land before
+  // the CTA's shared memory is released
+  if (s_bad)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
 }
 
-int read_spec_error(int* out) {
+int read_spec_error(int* out, int clear) {
   cudaError_t e = cudaMemcpyFromSymbol(out, g_spec_error, sizeof(int));
+  if (e == cudaSuccess && clear && *out != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_spec_error, &zero, sizeof(int));
+  }
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   return CSSM_OK;
 }
@@ -428,48 +435,40 @@ int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const flo
   const SpectralPath path = spectral_path(d.H, d.W);
   const int grid = d.B * d.C;
   if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, last_only, nogate, st);
-  if (path == PATH_R64 && g_spec_variant == 2 && !last_only && !nogate)
-    return launch_gated_spectral_ws(xz, khat, gates, d.B, d.T, d.C, st);
   if (path == PATH_R64) {
     const size_t smem = R64_SMEM_BYTES;
     // tensor map over the planar buffer as rows of 64 floats; box 68 x 64 (see the kernel)
     CUtensorMap pmap;
     memset(&pmap, 0, sizeof(pmap));
-    bool padded = g_spec_variant != 1;
-    if (padded) {
-      typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                   CUtensorMapFloatOOBfill);
-      static EncodeFn enc = []() -> EncodeFn {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-          return nullptr;
-        return reinterpret_cast<EncodeFn>(p);
-      }();
-      const cuuint64_t dims[2] = {64, (cuuint64_t)d.B * d.T * 2 * d.C * 64};
-      const cuuint64_t strides[1] = {256};
-      const cuuint32_t box[2] = {68, 64}, es[2] = {1, 1};
-      padded = enc != nullptr &&
-               enc(&pmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, xz, dims, strides, box, es,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-    }
-    auto kern = padded ? (last_only ? gated_spectral_r64<68, true, 0> : gated_spectral_r64<68, false, 0>)
-                       : (last_only ? gated_spectral_r64<64, true, 0> : gated_spectral_r64<64, false, 0>);
-    if (nogate) {
-      if (!padded) return CSSM_ERR_CUDA;          // these variants exist for the padded staging only
-      if (nogate == 1) kern = last_only ? gated_spectral_r64<68, true, 1> : gated_spectral_r64<68, false, 1>;
-      else kern = last_only ? gated_spectral_r64<68, true, 2> : gated_spectral_r64<68, false, 2>;
-    }
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+    static EncodeFn enc = []() -> EncodeFn {
+      void* p = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+          q != cudaDriverEntryPointSuccess)
+        return nullptr;
+      return reinterpret_cast<EncodeFn>(p);
+    }();
+    const cuuint64_t dims[2] = {64, (cuuint64_t)d.B * d.T * 2 * d.C * 64};
+    const cuuint64_t strides[1] = {256};
+    const cuuint32_t box[2] = {68, 64}, es[2] = {1, 1};
+    if (enc == nullptr ||
+        enc(&pmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, xz, dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return CSSM_ERR_CUDA;
+    auto kern = last_only ? gated_spectral_r64<true, 0> : gated_spectral_r64<false, 0>;
+    if (nogate == 1) kern = last_only ? gated_spectral_r64<true, 1> : gated_spectral_r64<false, 1>;
+    else if (nogate == 2) kern = last_only ? gated_spectral_r64<true, 2> : gated_spectral_r64<false, 2>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     kern<<<grid, R64_THREADS, smem, st>>>(xz, khat, reinterpret_cast<const float4*>(gates), d.T,
                                           d.C, pmap);
-  } else if (d.H * d.W <= SMALL_MAX_HW && !(g_spec_variant == 1)) {
+  } else if (d.H * d.W <= SMALL_MAX_HW) {
     const size_t smem = small_smem_bytes(d.H, d.W);
     cudaError_t e = cudaFuncSetAttribute(gated_spectral_small,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -1,7 +1,7 @@
 // tcgen05 / TMEM GEMM for the K = 64 channel projections in fp32-equivalent precision
 // (3 x TF32: A_hi*B_hi + A_lo*B_hi + A_hi*B_lo, accumulated in fp32 in TMEM).
 //
-// Persistent kernel, one CTA per SM, 288 threads, warp-specialised:
+// Persistent kernel, one CTA per SM, 544 threads, warp-specialised:
 //   warps 0-7  producers : read a 128-pixel A tile from global memory (channels-last rows with
 //                          RoPE fused, loaded one tile ahead into registers so a whole tile is
 //                          in flight per SM; or planar planes with the RMSNorm/gate prologue
@@ -52,12 +52,9 @@ struct TcSmem {
 // kernel carries no extra test.
 template <int N, bool A_PLANAR, bool STG, bool ZLAST = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__ CUtensorMap omap) {
-  // tile schedule: round-robin over CTAs (default) or one contiguous range per CTA (dbg & 8)
-  const int per = (num_tiles + gridDim.x - 1) / gridDim.x;
-  const int t_first = (dbg & 8) ? blockIdx.x * per : blockIdx.x;
-  const int t_step = (dbg & 8) ? 1 : gridDim.x;
-  const int t_end = (dbg & 8) ? min(num_tiles, t_first + per) : num_tiles;
+gemm_tc_kernel(const GemmArgs g, int num_tiles, const __grid_constant__ CUtensorMap omap) {
+  // tile schedule: round-robin over the CTAs
+  const int t_first = blockIdx.x, t_step = gridDim.x, t_end = num_tiles;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment (swizzle atoms); the launch adds 1024 bytes of slack
   unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -127,7 +124,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
       for (int r = 0; r < 8; ++r) {
         const int row = rsub + 32 * (r & 3);
         const int chunk = chunk_lo + 8 * (r >> 2);
-        pre[r] = (t_first < t_end && m0 + row < g.M && !(dbg & 2))
+        pre[r] = (t_first < t_end && m0 + row < g.M)
                      ? __ldg(reinterpret_cast<const float4*>(a0 + (size_t)row * TC_K + chunk * 4))
                      : make_float4(0.f, 0.f, 0.f, 0.f);
       }
@@ -154,7 +151,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
           for (int r = 0; r < 8; ++r) {
             const int row = rsub + 32 * (r & 3);
             const int chunk = chunk_lo + 8 * (r >> 2);
-            pre[r] = (nt * TC_BM + row < g.M && !(dbg & 2))
+            pre[r] = (nt * TC_BM + row < g.M)
                          ? __ldg(reinterpret_cast<const float4*>(a0 + (size_t)row * TC_K + chunk * 4))
                          : make_float4(0.f, 0.f, 0.f, 0.f);
           }
@@ -353,7 +350,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
           }
           tc::fence_proxy_async();
           asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-          if (grp_tid == 0 && !(dbg & 1)) {
+          if (grp_tid == 0) {
             const int m0 = tile * TC_BM;
             if (!A_PLANAR) {
               const int fr = m0 / g.HW, px0 = m0 - fr * g.HW;
@@ -366,14 +363,7 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
           continue;
         }
         if (m < g.M) {
-          if (!A_PLANAR && (dbg & 4)) {
-            // experiment only: row-contiguous stores (wrong layout) to time the store pattern
-            float* op = g.out + (size_t)m * g.N + cc * 32;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(op + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          } else if (!A_PLANAR) {
+          if (!A_PLANAR) {
             // planar output: lanes = consecutive pixels -> 128-byte coalesced stores per column.
             // All 32 values are finished in registers before the first store: the stores go
             // through a generic pointer, so bias loads placed between them could not be hoisted.
@@ -390,10 +380,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
 #pragma unroll
               for (int j = 0; j < 32; ++j) vals[j] = sigmoid_f(vals[j]);
             }
-            if (!(dbg & 1)) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) op[(size_t)j * g.HW] = vals[j];
-            }
+            for (int j = 0; j < 32; ++j) op[(size_t)j * g.HW] = vals[j];
           } else {
             float* op = g.out + (size_t)m * g.N + cc * 32;
 #pragma unroll
@@ -426,16 +414,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, int dbg, const __grid_constant__
   }
 }
 
-static int g_force_simt = 0;
-static int g_tc_dbg = 0;      // experiment switches (bit 1: skip epilogue stores, bit 2: skip A loads)
-extern int g_spec_variant;
-void set_force_simt(int on) { g_force_simt = on & 1; g_tc_dbg = ((on >> 1) & 3) | (((on >> 4) & 1) << 2) | (((on >> 5) & 1) << 3) | (((on >> 6) & 1) << 4) |
-             (((on >> 7) & 1) << 5);
-  g_spec_variant = ((on >> 3) & 1) | (((on >> 8) & 1) << 1); }
-
 // Whether the tensor-core kernel covers this problem (else the CUDA-core GEMM runs).
 bool gemm_tc_supported(const GemmArgs& g, bool a_planar) {
-  if (g_force_simt) return false;
   if (g.K != TC_K || (g.N != 64 && g.N != 128 && g.N != 192)) return false;
   if (g.HW % TC_BM != 0 || g.M % TC_BM != 0) return false;
   if (g.out_act != 0 && g.act_n0 % 32 != 0) return false;
@@ -496,7 +476,7 @@ static int launch_tc_v(const GemmArgs& g, const CUtensorMap& map, cudaStream_t s
   e = cudaFuncSetAttribute(gemm_tc_kernel<N, A_PLANAR, STG, ZLAST>,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  gemm_tc_kernel<N, A_PLANAR, STG, ZLAST><<<grid, TC_THREADS, smem, st>>>(g, num_tiles, g_tc_dbg, map);
+  gemm_tc_kernel<N, A_PLANAR, STG, ZLAST><<<grid, TC_THREADS, smem, st>>>(g, num_tiles, map);
   return check_launch();
 }
 
@@ -504,12 +484,10 @@ template <int N, bool A_PLANAR>
 static int launch_tc(const GemmArgs& g, cudaStream_t st) {
   CUtensorMap map;
   memset(&map, 0, sizeof(map));
-  // TMA-store epilogue for the channels-last output (planar A) unless switched off (debug bit) or
-  // the driver entry point is missing.  For the planar output it measured slower than direct
-  // stores (2.1 ms vs 1.44 ms on the in_proj of cfg2), so that direction keeps direct stores;
-  // debug bit 128 forces the TMA-store epilogue there for experiments.
-  const bool want = A_PLANAR || (g_tc_dbg & 32);
-  const bool stg = want && N <= 128 && !(g_tc_dbg & 16) && (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0 &&
+  // TMA-store epilogue for the channels-last output (planar A) unless the driver entry point is
+  // missing.  For the planar output it measured slower than direct stores (2.1 ms vs 1.44 ms on
+  // the in_proj of cfg2), so that direction keeps direct stores.
+  const bool stg = A_PLANAR && N <= 128 && (reinterpret_cast<uintptr_t>(g.out) & 15u) == 0 &&
                    make_out_map(g, A_PLANAR, &map);
   if (N <= 128 && stg) return launch_tc_v<N, A_PLANAR, (N <= 128)>(g, map, st);
   return launch_tc_v<N, A_PLANAR, false>(g, map, st);
@@ -528,8 +506,12 @@ int launch_gemm_tc(const GemmArgs& g, bool a_planar, cudaStream_t st) {
   return g.N == 128 ? launch_tc<128, true>(g, st) : launch_tc<64, true>(g, st);
 }
 
-int read_tc_error(int* out) {
+int read_tc_error(int* out, int clear) {
   cudaError_t e = cudaMemcpyFromSymbol(out, g_tc_error, sizeof(int));
+  if (e == cudaSuccess && clear && *out != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+  }
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   return CSSM_OK;
 }
@@ -537,22 +519,14 @@ int read_tc_error(int* out) {
 }  // namespace cssm
 
 extern "C" {
-int cssm_debug_set_gemm_backend(int backend) {
-  if (backend < 0 || backend > 511) return CSSM_ERR_UNSUPPORTED;
-  cssm::set_force_simt(backend);
-  return CSSM_OK;
-}
-int cssm_debug_tc_error(int* out) {
+int cssm_device_error(int* out, int clear) {
   if (!out) return CSSM_ERR_NULL;
   int a = 0, b = 0;
-  int rc = cssm::read_tc_error(&a);
+  int rc = cssm::read_tc_error(&a, clear);
   if (rc != CSSM_OK) return rc;
-  rc = cssm::read_spec_error(&b);
-  if (rc != CSSM_OK) return rc;
-  int c = 0;
-  rc = cssm::read_ws_error(&c);
-  // low byte: tensor-core GEMM, next byte: fused spectral kernel, third: its pipelined variant
-  *out = a | (b << 8) | (c << 16);
+  rc = cssm::read_spec_error(&b, clear);
+  // low byte: tensor-core GEMMs, next byte: fused spectral kernels
+  *out = a | (b << 8);
   return rc;
 }
 }

@@ -49,8 +49,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
 int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const float* gates,
                     float* xz, int last_only, int nogate, cudaStream_t st);
 size_t generic_smem_bytes(int H, int W);
-int read_spec_error(int* out);
-int read_ws_error(int* out);
+int read_spec_error(int* out, int clear);
 
 // ---- DeltaNet block (scalar delta rule) ----
 struct DnSpectralArgs {

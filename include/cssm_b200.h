@@ -453,23 +453,26 @@ int cssm_simple_forward_host(const cssm_simple_desc* d, const cssm_simple_weight
                              const void* block_plan, const float* x_host, float* logits_host,
                              void* workspace, size_t workspace_bytes, int32_t flags, void* stream);
 
-/* ---- diagnostics (no counterpart in the reference) ----
- * cssm_debug_set_gemm_backend: 0 = tensor-core (tcgen05) projections where they apply
- * (default), 1 = CUDA-core fp32 projections everywhere; process-wide, for A/B tests.  Higher
- * bits are timing-experiment switches of the tensor-core kernel (2/4 skip epilogue stores / A
- * loads, 8 dense bulk-TMA staging in the spectral kernel, 16 row-contiguous stores, 32 contiguous
- * tile ranges, 64 no TMA-store epilogue, 128 TMA-store epilogue for planar outputs too, 256
- * warp-specialised pipelined spectral kernel); results are only valid with 0, 1, 8, 32, 64, 128
- * and 256.
- * cssm_debug_tc_error: copies the device-side error code of the tensor-core GEMM (0 = no
- * bounded wait ever expired) to *out; synchronises the device. */
-int cssm_debug_set_gemm_backend(int backend);
-int cssm_debug_tc_error(int* out);
-/* cssm_debug_gdn_stage_events: `events` is an array of 8 cudaEvent_t (or NULL to switch the
- * hook off, the default).  While set, cssm_gdn_forward called from the same host thread records
- * events[i] before its stage i (0 dwconv+ctx, 1 qkv_proj, 2 gate_proj, 3 gates, 4 short convs,
- * 5 fused spectral kernel, 6 norm+gate+output_proj) and events[7] at the end. */
-int cssm_debug_gdn_stage_events(void** events);
+/* ---- device-side error word (no counterpart in the reference) ----
+ * Kernels of this library wait on hardware barriers (TMA copies landing, tensor-core tiles
+ * finishing) with an iteration limit.  A wait that runs out does not hang or trap: the CTA records
+ * a code in a device word, stops storing results and winds down, and the forward call that
+ * launched it has long since returned CSSM_OK (calls are asynchronous).  After synchronising the
+ * stream, cssm_device_error copies that word to *out: 0 = no wait ever expired on the current
+ * device since the last clear; low byte = tensor-core projection kernels (1 producer, 2 MMA
+ * issuer, 3 drain, 4 epilogue), next byte = fused spectral kernels (1 input plane, 2 z plane).
+ * A non-zero value means the outputs of the calls since the last clear are not to be trusted.
+ * clear != 0 resets the word after reading it.  The call copies from the device on the legacy
+ * default stream (it waits for work on blocking streams). */
+int cssm_device_error(int* out, int clear);
+
+/* cssm_gdn_forward with per-stage timing: `stage_events` is an array of 8 cudaEvent_t created by
+ * the caller; events[i] is recorded on `stream` before stage i (0 dwconv+ctx, 1 qkv_proj,
+ * 2 gate_proj, 3 gates, 4 short convs, 5 fused spectral kernel, 6 norm+gate+output_proj) and
+ * events[7] at the end.  Nothing is kept after the call returns. */
+int cssm_gdn_forward_timed(const cssm_gdn_desc* d, const cssm_gdn_weights* w, const void* plan,
+                           const float* x, float* y, void* workspace, size_t workspace_bytes,
+                           void* stream, void** stage_events);
 
 /* ---- entry point that allocates nothing (no counterpart in the reference) ----
  * The reference has nothing like this: it is for hosts that may not call cudaMalloc at all
@@ -481,7 +484,9 @@ int cssm_debug_gdn_stage_events(void** events);
  *    larger problems return CSSM_ERR_SIZE_LIMIT.  Every GPU that loads the library carries
  *    the 64 MiB array until the process exits.
  *  - The first call on each device looks up the array's device address (with that device
- *    current); make that first call before starting any stream capture.
+ *    current) and keeps it for the life of the process; make that first call before starting
+ *    any stream capture.  The address dies with the device's primary context: do not call
+ *    this entry point again after cudaDeviceReset.
  *  - All calls on a device share the array: two calls whose kernels overlap on the GPU
  *    (different streams) race.  Nothing needs clearing between calls: each part of the
  *    scratch is rewritten before it is read.

@@ -135,14 +135,14 @@ def test_golden_fixtures_on_gpu():
 def _tc_error(L):
     import ctypes as C
     v = C.c_int(-1)
-    assert L.cssm_debug_tc_error(C.byref(v)) == 0
+    assert L.cssm_device_error(C.byref(v), 0) == 0
     return v.value
 
 
 @pytest.mark.parametrize("rope", ["spatiotemporal", "none"])
 def test_tensor_core_projections_c64(rope):
-    """C = 64 on 64x64 planes takes the tcgen05 3xTF32 projections; compare with the oracle,
-    with the CUDA-core projections, and check that no bounded wait expired."""
+    """C = 64 on 64x64 planes takes the tcgen05 3xTF32 projections; compare with the oracle
+    (block and in_proj stage) and check that no bounded wait expired."""
     bound, xd, ref, inter = _run(2, 2, 64, 64, 64, 11, "factored", rope, 3, 4)
     L = bound.L
     B, T, H, W, C = 2, 2, 64, 64, 64
@@ -151,34 +151,9 @@ def test_tensor_core_projections_c64(rope):
     y_tc = bound(xd).cpu().numpy()
     assert _tc_error(L) == 0
     assert orc.rel_l2(y_tc, ref) <= TOL
-    assert L.cssm_debug_set_gemm_backend(1) == 0
-    try:
-        y_simt = bound(xd).cpu().numpy()
-    finally:
-        assert L.cssm_debug_set_gemm_backend(0) == 0
-    assert orc.rel_l2(y_simt, ref) <= TOL
-    assert orc.rel_l2(y_tc, y_simt) <= 2e-6
     # stage level: the planar x_main / z planes straight out of in_proj
     z = xz[:, :, C:].transpose(0, 1, 3, 4, 2)
     assert orc.rel_l2(z, orc.silu(inter["z"])) <= 2e-6
-
-
-def test_spectral_kernel_variants_agree_bitwise():
-    """The three implementations of the 64x64 fused spectral kernel (padded tensor-TMA staging,
-    dense bulk-TMA staging, warp-specialised pipeline) run the same arithmetic in the same order:
-    identical bits, and no bounded wait expires in any of them."""
-    bound, xd, ref, _ = _run(2, 5, 64, 64, 8, 11, "factored", "spatiotemporal", 3, 4)
-    L = bound.L
-    outs = []
-    try:
-        for flag in (0, 8, 256):
-            assert L.cssm_debug_set_gemm_backend(flag) == 0
-            outs.append(bound(xd).clone())
-            assert _tc_error(L) == 0
-    finally:
-        assert L.cssm_debug_set_gemm_backend(0) == 0
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
-    assert orc.rel_l2(outs[0].cpu().numpy(), ref) <= TOL
 
 
 @pytest.mark.parametrize("case", [

@@ -18,21 +18,25 @@ from cssm_b200._lib import check
 pytestmark = pytest.mark.gpu
 
 
+_KW = dict(kernel_size=11, rope_mode="spatiotemporal", gate_type="factored")
+
+
 def _setup(seed):
-    B, T, H, W, Cc, ks = 2, 3, 64, 64, 8, 11
+    B, T, H, W, Cc = 2, 3, 64, 64, 8
     rng = np.random.default_rng(seed)
     x = torch.from_numpy(rng.standard_normal((B, T, H, W, Cc)).astype(np.float32)).cuda()
-    p = orc.init_gated_params(seed + 1, Cc, H, W, kernel_size=ks, gate_type="factored",
-                              bias_scale=0.1)
-    mod = GatedCSSM(channels=Cc, kernel_size=ks, rope_mode="spatiotemporal", gate_type="factored")
-    bound = mod.bind({"params": p})
+    p = orc.init_gated_params(seed + 1, Cc, H, W, kernel_size=_KW["kernel_size"],
+                              gate_type="factored", bias_scale=0.1)
+    bound = GatedCSSM(channels=Cc, **_KW).bind({"params": p})
+    bound.params_np = p
     return bound, x
 
 
 def test_static_scratch_entry_matches_workspace_entry_twice():
     """Two calls in a row (different inputs, so stale scratch contents would show) give the
     same output as the workspace entry point: same kernels, same order, so bit-equal, which
-    is inside the 1e-4 rel-L2 tolerance the other GPU tests use."""
+    is inside the 1e-4 rel-L2 tolerance the other GPU tests use; and both match the NumPy oracle,
+    so the test stands without the other entry point."""
     bound, x1 = _setup(0)
     L = bound.L
     x2 = x1.flip(0) * 1.5 + 0.25
@@ -49,6 +53,8 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
         assert torch.isfinite(got).all()
         assert orc.rel_l2(got.cpu().numpy(), want.cpu().numpy()) <= 1e-4
         assert torch.equal(got, want)
+        ref = orc.gated_forward(bound.params_np, x.cpu().numpy(), **_KW)
+        assert orc.rel_l2(got.cpu().numpy(), ref) <= 1e-4
 
 
 def test_static_scratch_entry_rejects_oversize():
