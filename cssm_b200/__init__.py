@@ -7,5 +7,7 @@ raises if it has not been built."""
 from ._lib import CssmError, lib  # noqa: F401
 from .modules import AdditiveCSSM, DeltaNetCSSM, GatedCSSM, GatedDeltaNetCSSM, NoGateCSSM  # noqa: F401
 from .simple import SimpleCSSM  # noqa: F401
+from .shvit import CSSMSHViT, CSSMSHViTBlock, ConvBlock, cssm_shvit_s1  # noqa: F401
 
-__all__ = ["GatedCSSM", "GatedDeltaNetCSSM", "NoGateCSSM", "AdditiveCSSM", "DeltaNetCSSM", "SimpleCSSM", "CssmError", "lib"]
+__all__ = ["GatedCSSM", "GatedDeltaNetCSSM", "NoGateCSSM", "AdditiveCSSM", "DeltaNetCSSM", "SimpleCSSM", "CSSMSHViT",
+           "CSSMSHViTBlock", "ConvBlock", "cssm_shvit_s1", "CssmError", "lib"]

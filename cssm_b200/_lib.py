@@ -35,6 +35,52 @@ class GatedWeights(C.Structure):
                 ("out_proj_kernel", C.c_void_p), ("out_proj_bias", C.c_void_p)]
 
 
+class ShvitBlockDesc(C.Structure):
+    _fields_ = [("B", C.c_int32), ("H", C.c_int32), ("W", C.c_int32), ("C", C.c_int32),
+                ("is_cssm", C.c_int32), ("hidden", C.c_int32), ("num_timesteps", C.c_int32),
+                ("kernel_size", C.c_int32), ("use_pos_conv", C.c_int32), ("use_dwconv", C.c_int32),
+                ("rope_mode", C.c_int32), ("rope_base", C.c_float), ("spectral_rho", C.c_float),
+                ("gate_activation", C.c_int32), ("short_conv_size", C.c_int32),
+                ("short_conv_spatial_size", C.c_int32), ("gate_type", C.c_int32)]
+
+
+class ShvitBlockWeights(C.Structure):
+    _fields_ = [("norm1_scale", C.c_void_p), ("norm1_bias", C.c_void_p),
+                ("norm2_scale", C.c_void_p), ("norm2_bias", C.c_void_p),
+                ("dw_kernel", C.c_void_p), ("dw_bias", C.c_void_p),
+                ("pw_kernel", C.c_void_p), ("pw_bias", C.c_void_p),
+                ("fc1_kernel", C.c_void_p), ("fc1_bias", C.c_void_p),
+                ("fc2_kernel", C.c_void_p), ("fc2_bias", C.c_void_p),
+                ("mlp_dw_kernel", C.c_void_p), ("mlp_dw_bias", C.c_void_p),
+                ("cssm", GatedWeights)]
+
+
+class ShvitConvBN(C.Structure):
+    _fields_ = [("kernel", C.c_void_p), ("bn_scale", C.c_void_p), ("bn_bias", C.c_void_p),
+                ("bn_mean", C.c_void_p), ("bn_var", C.c_void_p)]
+
+
+SHVIT_MAX_BLOCKS = 16
+
+
+class ShvitDesc(C.Structure):
+    _fields_ = [("B", C.c_int32), ("H", C.c_int32), ("W", C.c_int32), ("Cin", C.c_int32),
+                ("embed_dims", C.c_int32 * 4), ("depths", C.c_int32 * 4),
+                ("use_cssm", C.c_int32 * 4), ("kernel_sizes", C.c_int32 * 4),
+                ("num_classes", C.c_int32), ("num_timesteps", C.c_int32), ("mlp_ratio", C.c_float),
+                ("use_pos_conv", C.c_int32), ("use_dwconv", C.c_int32), ("head_pool", C.c_int32),
+                ("rope_mode", C.c_int32), ("rope_base", C.c_float), ("spectral_rho", C.c_float),
+                ("gate_activation", C.c_int32), ("short_conv_size", C.c_int32),
+                ("short_conv_spatial_size", C.c_int32), ("gate_type", C.c_int32)]
+
+
+class ShvitWeights(C.Structure):
+    _fields_ = [("patch", ShvitConvBN * 2), ("down", ShvitConvBN * 3),
+                ("blocks", ShvitBlockWeights * SHVIT_MAX_BLOCKS),
+                ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p),
+                ("head_kernel", C.c_void_p), ("head_bias", C.c_void_p)]
+
+
 class GatedWsLayout(C.Structure):
     _fields_ = [("xz_planar", C.c_size_t), ("ctx_sum", C.c_size_t),
                 ("gate_maps", C.c_size_t), ("total", C.c_size_t)]
@@ -177,6 +223,25 @@ SIGNATURES = {
     "cssm_simple_forward_host": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P,
                                            _P, _P, _P, _P, C.c_size_t, C.c_int32, _P]),
     "cssm_device_error": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
+    "cssm_shvit_block_plan_bytes": (C.c_size_t, [C.POINTER(ShvitBlockDesc)]),
+    "cssm_shvit_block_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitBlockDesc)]),
+    "cssm_shvit_block_plan_init": (C.c_int, [C.POINTER(ShvitBlockDesc), C.POINTER(ShvitBlockWeights), _P,
+                                             C.c_size_t, _P]),
+    "cssm_shvit_block_forward": (C.c_int, [C.POINTER(ShvitBlockDesc), C.POINTER(ShvitBlockWeights), _P,
+                                           _P, _P, _P, C.c_size_t, _P]),
+    "cssm_shvit_plan_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
+    "cssm_shvit_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
+    "cssm_shvit_plan_init": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, C.c_size_t, _P]),
+    "cssm_shvit_forward": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
+                                     C.c_size_t, _P]),
+    "cssm_shvit_host_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
+    "cssm_shvit_forward_host": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
+                                          C.c_size_t, _P]),
+    "cssm_bf16_packed_ld": (C.c_int32, [C.c_int32]),
+    "cssm_bf16_pack_weight": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P]),
+    "cssm_bf16_gemm": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _P, C.c_int32, _P, _P, _P]),
+    "cssm_bf16_conv3x3s2": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, _P,
+                                      C.c_int32, _P, _P]),
     "cssm_static_scratch_bytes": (C.c_size_t, []),
     "cssm_gated_forward_static": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
                                             _P, _P]),

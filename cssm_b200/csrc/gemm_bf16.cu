@@ -1,0 +1,348 @@
+// bf16 tcgen05 / TMEM GEMM with a K loop, for the channel contractions of the CSSM-SHViT model
+// (Dense layers with K = 64 ... 1536, and the 3x3 stride-2 ConvBN layers as implicit GEMMs).
+//
+//   out[m, n] = act( sum_k A[m, k] * Wt[n, k] + bias[n] ) (+ res[m, n]),  bf16 in, fp32 accumulate.
+//
+// Persistent kernel, one CTA per SM, 320 threads, warp-specialised:
+//   warp 0     TMA producer: one lane issues cp.async.bulk.tensor loads of the A tile (128 rows x
+//              64 k, plain mode) and the weight tile (BN rows x 64 k) of every K block into a
+//              4-stage ring of 128-byte-swizzled K-major operand tiles;
+//   warp 1     MMA issuer: one lane issues 4 tcgen05.mma.kind::f16 (M128 x BN x K16) per K block
+//              into one of two TMEM accumulators; tcgen05.commit frees the stage / publishes the
+//              accumulator;
+//   warps 2-5  epilogue: tcgen05.ld (lane = output row), bias, GELU / SiLU, residual, bf16 stores;
+//              overlaps the next tile's main loop through the second accumulator;
+//   warps 6-9  im2col producers (conv mode only): thread = output pixel of the tile; gathers the
+//              eight 16-byte channel chunks of each K block from the channels-last input (zero
+//              outside the image) and writes them in the same swizzled layout.
+// Every mbarrier wait is bounded; on expiry the kernel records an error code (cssm_device_error)
+// and winds down.  No multicast, no cluster: each CTA loads its own tiles.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <string.h>
+#include "kernels.cuh"
+#include "tc05.cuh"
+#include "bf16_ops.cuh"
+
+namespace cssm {
+
+__device__ int g_bf16_error = 0;
+
+constexpr int GB_THREADS = 320;
+constexpr int GB_BM = 128, GB_BK = 64, GB_STAGES = 4;
+constexpr uint32_t GB_A_BYTES = GB_BM * 128u;            // one A stage: 128 rows x 128 bytes
+
+__device__ __forceinline__ uint32_t make_idesc_bf16(uint32_t M, uint32_t N) {
+  uint32_t d = 0;
+  d |= 1u << 4;            // D format: f32
+  d |= 1u << 7;            // A format: bf16
+  d |= 1u << 10;           // B format: bf16
+  d |= (N >> 3) << 17;     // N / 8
+  d |= (M >> 4) << 24;     // M / 16
+  return d;
+}
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <bool IM2COL>
+__global__ void __launch_bounds__(GB_THREADS, 1)
+gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
+                 const __grid_constant__ CUtensorMap bmap) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t sbase = tc::smem_u32(smem);
+  const uint32_t BN = (uint32_t)g.BN;
+  const uint32_t stage_bytes = GB_A_BYTES + BN * 128u;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GB_STAGES * stage_bytes);
+  uint64_t* full = bars;                    // [4] operands landed
+  uint64_t* empty = bars + GB_STAGES;       // [4] stage consumed
+  uint64_t* accfull = bars + 2 * GB_STAGES; // [2]
+  uint64_t* accempty = accfull + 2;         // [2]
+  uint64_t* done = accempty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m_tiles = (g.M + GB_BM - 1) / GB_BM, n_tiles = g.N / g.BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int kblocks = g.Kpad / GB_BK;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < 2 * BN) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < GB_STAGES; ++s) {
+      tc::mbar_init(&full[s], IM2COL ? 1 + 128 : 1);
+      tc::mbar_init(&empty[s], 1);
+    }
+    tc::mbar_init(&accfull[0], 1); tc::mbar_init(&accfull[1], 1);
+    tc::mbar_init(&accempty[0], 128); tc::mbar_init(&accempty[1], 128);
+    tc::mbar_init(done, 1);
+    tc::fence_mbar_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, tmem_cols);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool bad = false;
+
+  if (warp == 0) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % GB_STAGES;
+          if (!tc::mbar_wait(&empty[s], ((it / GB_STAGES) & 1) ^ 1)) { atomicExch(&g_bf16_error, 5); bad = true; break; }
+          unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
+          unsigned char* b_s = a_s + GB_A_BYTES;
+          tc::mbar_expect_tx(&full[s], (IM2COL ? 0u : GB_A_BYTES) + BN * 128u);
+          if (!IM2COL) tc::tma_load_2d(a_s, &amap, kb * GB_BK, m0, &full[s]);
+          tc::tma_load_2d(b_s, &bmap, kb * GB_BK, n0, &full[s]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================================ MMA issuer ================================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(GB_BM, BN);
+      int it = 0, tcnt = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x, ++tcnt) {
+        const int ac = tcnt & 1, aph = (tcnt >> 1) & 1;
+        if (!tc::mbar_wait(&accempty[ac], aph ^ 1)) { atomicExch(&g_bf16_error, 6); bad = true; break; }
+        tc::fence_after_sync();
+        const uint32_t d = tmem_base + (uint32_t)ac * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % GB_STAGES;
+          if (!tc::mbar_wait(&full[s], (it / GB_STAGES) & 1)) { atomicExch(&g_bf16_error, 6); bad = true; break; }
+          tc::fence_after_sync();
+          const uint32_t a_s = sbase + (uint32_t)s * stage_bytes, b_s = a_s + GB_A_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = tc::make_desc_sw128(a_s + (uint32_t)ks * 32u);
+            const uint64_t bd = tc::make_desc_sw128(b_s + (uint32_t)ks * 32u);
+            mma_bf16(d, ad, bd, idesc, (kb | ks) ? 1u : 0u);
+          }
+          tc::commit(&empty[s]);
+        }
+        if (bad) break;
+        tc::commit(&accfull[ac]);
+      }
+      // nothing of this thread's tensor work may be in flight when TMEM is freed
+      tc::commit(done);
+      if (!tc::mbar_wait(done, 0) && !bad) atomicExch(&g_bf16_error, 7);
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ================================ epilogue ================================
+    const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int row = q * 32 + lane;
+    int tcnt = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcnt) {
+      const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
+      const int ac = tcnt & 1, aph = (tcnt >> 1) & 1;
+      if (!tc::mbar_wait(&accfull[ac], aph)) { atomicExch(&g_bf16_error, 8); break; }
+      tc::fence_after_sync();
+      const int m = m0 + row;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)ac * BN;
+      for (int cc = 0; cc < g.BN / 32; ++cc) {
+        uint32_t r[32];
+        tc::ld_32x32b_x32(taddr + cc * 32, r);
+        tc::wait_ld();
+        const int n = n0 + cc * 32;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (g.bias != nullptr) {
+          const float4* bp = reinterpret_cast<const float4*>(g.bias + n);
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 b4 = __ldg(bp + (j >> 2));
+            v[j] += b4.x; v[j + 1] += b4.y; v[j + 2] += b4.z; v[j + 3] += b4.w;
+          }
+        }
+        if (g.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f(v[j]);
+        } else if (g.act == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = silu_f(v[j]);
+        }
+        if (m < g.M) {
+          if (g.res != nullptr) {
+            const uint4* rp = reinterpret_cast<const uint4*>(g.res + (size_t)m * g.ldr + n);
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+              const uint4 u = __ldg(rp + j4);
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = bf16x2_to_float2(w[e]);
+                v[j4 * 8 + 2 * e] += f.x; v[j4 * 8 + 2 * e + 1] += f.y;
+              }
+            }
+          }
+          if (g.out_f32 != nullptr) {
+            float4* op = reinterpret_cast<float4*>(g.out_f32 + (size_t)m * g.ldo + n);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) op[j >> 2] = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            uint4* op = reinterpret_cast<uint4*>(g.out + (size_t)m * g.ldo + n);
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+              uint4 u;
+              u.x = float2_to_bf16x2(v[j4 * 8 + 0], v[j4 * 8 + 1]);
+              u.y = float2_to_bf16x2(v[j4 * 8 + 2], v[j4 * 8 + 3]);
+              u.z = float2_to_bf16x2(v[j4 * 8 + 4], v[j4 * 8 + 5]);
+              u.w = float2_to_bf16x2(v[j4 * 8 + 6], v[j4 * 8 + 7]);
+              op[j4] = u;
+            }
+          }
+        }
+      }
+      tc::fence_before_sync();
+      tc::mbar_arrive(&accempty[ac]);
+    }
+  } else if (IM2COL) {
+    // ================================ im2col producers ================================
+    const int row = tid - 6 * 32;                 // 0..127: output pixel of the tile
+    const int HWo = g.Ho * g.Wo;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x) {
+      const int m = (tile / n_tiles) * GB_BM + row;
+      const bool live = m < g.M;
+      const int b = live ? m / HWo : 0;
+      const int px = live ? m - b * HWo : 0;
+      const int ho = px / g.Wo, wo = px - ho * g.Wo;
+      const int hi0 = ho * g.stride - g.pad_h, wi0 = wo * g.stride - g.pad_w;
+      const __nv_bfloat16* xb = g.A + (size_t)b * g.Hi * g.Wi * g.Cin;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % GB_STAGES;
+        uint4 v[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int k0 = kb * GB_BK + c * 8;
+          const int tap = k0 / g.Cin, c0 = k0 - tap * g.Cin;
+          const int ti = tap / g.ksz, tj = tap - ti * g.ksz;
+          const int hi = hi0 + ti, wi = wi0 + tj;
+          const bool in = live && k0 < g.K && hi >= 0 && hi < g.Hi && wi >= 0 && wi < g.Wi;
+          v[c] = in ? __ldg(reinterpret_cast<const uint4*>(xb + ((size_t)hi * g.Wi + wi) * g.Cin + c0))
+                    : make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (!tc::mbar_wait(&empty[s], ((it / GB_STAGES) & 1) ^ 1)) { atomicExch(&g_bf16_error, 9); bad = true; break; }
+        unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(a_s + tc::sw128_offset(row, c)) = v[c];
+        tc::fence_proxy_async();
+        tc::mbar_arrive(&full[s]);
+      }
+    }
+  }
+  // error path only: give copies that may still be in flight a bounded time to land
+  if (bad)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// K-major bf16 matrix [rows][kcols] (row stride ld elements) -> boxes of 64 k x box_rows rows
+static bool make_kmajor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t kcols,
+                            uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {kcols, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {64, box_rows}, es[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int read_bf16_error(int* out, int clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_bf16_error, sizeof(int));
+  if (e == cudaSuccess && clear && *out != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_bf16_error, &zero, sizeof(int));
+  }
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  return CSSM_OK;
+}
+
+int gemm_bf16_pick_bn(int N) {
+  if (N <= 256) return (N % 32 == 0) ? N : 0;
+  if (N % 256 == 0) return 256;
+  if (N % 192 == 0) return 192;
+  if (N % 128 == 0) return 128;
+  if (N % 64 == 0) return 64;
+  return 0;
+}
+
+int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return CSSM_ERR_DIMS;
+  g.Kpad = (g.K + GB_BK - 1) / GB_BK * GB_BK;
+  g.BN = gemm_bf16_pick_bn(g.N);
+  if (g.BN == 0 || g.ldw < g.Kpad || (g.ldw % 8) != 0) return CSSM_ERR_UNSUPPORTED;
+  if (g.ldo % 8 != 0 || (g.res != nullptr && g.ldr % 8 != 0)) return CSSM_ERR_UNSUPPORTED;
+  if (!aligned16(g.A) || !aligned16(g.Wt) || (g.out && !aligned16(g.out)) ||
+      (g.out_f32 && !aligned16(g.out_f32)) || (g.res && !aligned16(g.res)))
+    return CSSM_ERR_ALIGN;
+  const bool im2col = g.ksz > 0;
+  if (im2col) {
+    if (g.Cin % 8 != 0 || g.K != g.ksz * g.ksz * g.Cin) return CSSM_ERR_UNSUPPORTED;
+  } else if (g.K % 8 != 0 || g.lda % 8 != 0 || g.lda < g.K) {
+    return CSSM_ERR_UNSUPPORTED;
+  }
+  CUtensorMap amap, bmap;
+  memset(&amap, 0, sizeof(amap));
+  memset(&bmap, 0, sizeof(bmap));
+  // A: out-of-range k columns (K < Kpad) and rows (M not a multiple of 128) arrive as zeros
+  if (!im2col && !make_kmajor_map(&amap, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, GB_BM))
+    return CSSM_ERR_CUDA;
+  if (!make_kmajor_map(&bmap, g.Wt, (uint64_t)g.N, (uint64_t)g.Kpad, (uint64_t)g.ldw, (uint32_t)g.BN))
+    return CSSM_ERR_CUDA;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  const int tiles = ((g.M + GB_BM - 1) / GB_BM) * (g.N / g.BN);
+  const int grid = tiles < sms ? tiles : sms;
+  const size_t smem = (size_t)GB_STAGES * (GB_A_BYTES + (size_t)g.BN * 128u) + 256 + 1024;
+  auto kern = im2col ? gemm_bf16_kernel<true> : gemm_bf16_kernel<false>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  kern<<<grid, GB_THREADS, smem, st>>>(g, amap, bmap);
+  return check_launch();
+}
+
+}  // namespace cssm

@@ -525,8 +525,11 @@ int cssm_device_error(int* out, int clear) {
   int rc = cssm::read_tc_error(&a, clear);
   if (rc != CSSM_OK) return rc;
   rc = cssm::read_spec_error(&b, clear);
-  // low byte: tensor-core GEMMs, next byte: fused spectral kernels
-  *out = a | (b << 8);
+  if (rc != CSSM_OK) return rc;
+  int c = 0;
+  rc = cssm::read_bf16_error(&c, clear);
+  // low byte: fp32 tensor-core GEMMs, next byte: fused spectral kernels, third: bf16 GEMM
+  *out = a | (b << 8) | (c << 16);
   return rc;
 }
 }

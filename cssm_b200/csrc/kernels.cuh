@@ -1,6 +1,7 @@
 // Argument structs and host launchers of the kernels, shared by the kernel sources and the
 // C-ABI sources.
 #pragma once
+#include <cuda_bf16.h>
 #include "common.cuh"
 
 namespace cssm {
@@ -101,6 +102,58 @@ struct GdnSpectralArgs {
 };
 int launch_gdn_spectral(const GdnSpectralArgs& a, cudaStream_t st);
 size_t gdn_generic_smem_bytes(int H, int W, int dk);
+
+// ---- bf16 tensor-core GEMM with a K loop (csrc/gemm_bf16.cu) ----
+struct Bf16GemmArgs {
+  // plain mode (ksz == 0): A is (M, K) bf16 row-major with row stride lda.
+  // conv mode (ksz > 0): A is a channels-last image batch (Bimg, Hi, Wi, Cin) and row m is output
+  //   pixel (b, ho, wo); K = ksz*ksz*Cin in (tap row, tap column, channel) order; zero padding of
+  //   pad_h / pad_w pixels before the first row / column (whatever falls outside the image is 0).
+  const __nv_bfloat16* A;
+  int M, N, K, lda;
+  int ksz, stride, Hi, Wi, Cin, Ho, Wo, pad_h, pad_w;
+  const __nv_bfloat16* Wt;   // (N, ldw) bf16: weights transposed to K-major, ldw >= round_up(K, 64), zero padded
+  int ldw;
+  const float* bias;         // (N) or nullptr
+  int act;                   // 0 none, 1 gelu (tanh form), 2 silu
+  const __nv_bfloat16* res;  // (M, ldr) added after the activation, or nullptr
+  int ldr;
+  __nv_bfloat16* out;        // (M, ldo) bf16 ...
+  float* out_f32;            // ... or (M, ldo) float32 when not nullptr
+  int ldo;
+  int Kpad, BN;              // filled in by the launcher
+};
+int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st);
+int gemm_bf16_pick_bn(int N);
+int read_bf16_error(int* out, int clear);
+
+// ---- bf16 model kernels (csrc/shvit_kernels.cu, csrc/spectral_cl.cu) ----
+int launch_pack_wt(const float* src, int K, int N, const float* colscale, __nv_bfloat16* dst, int ldw,
+                   cudaStream_t st);
+int launch_bn_fold(const float* scale, const float* bias, const float* mean, const float* var, int C,
+                   float* oscale, float* obias, cudaStream_t st);
+int launch_affine_vec(const float* a, const float* s, const float* b, int C, float* out, cudaStream_t st);
+int launch_fill(float* p, int n, float v, cudaStream_t st);
+int launch_scale_cols(const float* src, int K, int N, const float* s, float* out, cudaStream_t st);
+int launch_stem_conv1(const __nv_bfloat16* x, const float* wk, const float* bias, __nv_bfloat16* y,
+                      int Nimg, int Hi, int Wi, int Cin, int Co, int gelu, cudaStream_t st);
+// wk == nullptr: no taps (only the pre-affine / centre term)
+int launch_dwconv_cl(const __nv_bfloat16* x, const float* wk, const float* bias, const float* pre_a,
+                     const float* pre_b, __nv_bfloat16* y, float* y_f32, int Nimg, int H, int W, int C,
+                     int ks, int add_centre, int gelu, cudaStream_t st);
+int launch_layernorm_cl(const __nv_bfloat16* x, const float* scale, const float* bias, __nv_bfloat16* y,
+                        long long npix, int C, cudaStream_t st);
+int launch_sample_norm(const __nv_bfloat16* x, const float* scale, const float* bias, float* a, float* b,
+                       int Nimg, int per, int C, cudaStream_t st);
+int launch_plane_sum_cl(const __nv_bfloat16* x, int ld, int Nimg, int P, int C, float* sums, cudaStream_t st);
+int launch_pool_cl(const __nv_bfloat16* x, int Nimg, int P, int C, int use_max, float* pooled, cudaStream_t st);
+int launch_head(const float* pooled, const float* W, const float* b, float* logits, int Nimg, int C, int K,
+                cudaStream_t st);
+int launch_f32_to_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t st);
+int launch_add_res(const __nv_bfloat16* res, const float* yv, __nv_bfloat16* out, long long n, cudaStream_t st);
+bool spectral_cl_supported(int H, int W, int C, int T);
+int launch_gated_spectral_cl(const __nv_bfloat16* xz, int ld, int Nimg, int H, int W, int C,
+                             const float* gates, __nv_bfloat16* y, int ldy, cudaStream_t st);
 
 // ---- whole-block drivers shared by the C-ABI sources ----
 // last_only: y is (B,H,W,C), the last output frame.  x_bcast: x is (B,H,W,C), one frame per

@@ -1,0 +1,477 @@
+// Pointwise / stencil / reduction kernels of the bf16 CSSM-SHViT forward (channels-last bf16
+// activations, fp32 arithmetic), and the weight-packing kernels of its plan.
+#include "kernels.cuh"
+#include "bf16_ops.cuh"
+
+namespace cssm {
+
+// ------------------------------------------------------------------ plan: weight packing ----
+// src (K, N) fp32 row-major (a Dense kernel, or an HWIO conv kernel flattened over its taps and
+// input channels) -> dst (N, ldw) bf16, K-major, zero padded to ldw, column n scaled by
+// colscale[n] (BatchNorm fold, temporal tap of the mixer) when given.
+__global__ void pack_wt_kernel(const float* __restrict__ src, int K, int N, const float* __restrict__ colscale,
+                               __nv_bfloat16* __restrict__ dst, int ldw) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N * ldw) return;
+  const int n = i / ldw, k = i - n * ldw;
+  float v = 0.f;
+  if (k < K) {
+    v = src[(size_t)k * N + n];
+    if (colscale) v *= colscale[n];
+  }
+  dst[i] = __float2bfloat16(v);
+}
+int launch_pack_wt(const float* src, int K, int N, const float* colscale, __nv_bfloat16* dst, int ldw,
+                   cudaStream_t st) {
+  const int n = N * ldw;
+  pack_wt_kernel<<<(n + 255) / 256, 256, 0, st>>>(src, K, N, colscale, dst, ldw);
+  return check_launch();
+}
+
+// BatchNorm (running statistics, eps 1e-5) after a bias-free conv as a per-channel scale and bias
+__global__ void bn_fold_kernel(const float* scale, const float* bias, const float* mean, const float* var,
+                               int C, float* oscale, float* obias) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float s = scale[c] * rsqrtf(var[c] + 1e-5f);
+  oscale[c] = s;
+  obias[c] = bias[c] - mean[c] * s;
+}
+int launch_bn_fold(const float* scale, const float* bias, const float* mean, const float* var, int C,
+                   float* oscale, float* obias, cudaStream_t st) {
+  bn_fold_kernel<<<(C + 127) / 128, 128, 0, st>>>(scale, bias, mean, var, C, oscale, obias);
+  return check_launch();
+}
+
+// out[c] = a[c] * s[c] + b[c]   (bias of the in_proj with the T = 1 temporal tap folded in)
+__global__ void affine_vec_kernel(const float* a, const float* s, const float* b, int C, float* out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < C) out[c] = (s ? a[c] * s[c] : a[c]) + (b ? b[c] : 0.f);
+}
+int launch_affine_vec(const float* a, const float* s, const float* b, int C, float* out, cudaStream_t st) {
+  affine_vec_kernel<<<(C + 127) / 128, 128, 0, st>>>(a, s, b, C, out);
+  return check_launch();
+}
+
+__global__ void fill_kernel(float* p, int n, float v) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+int launch_fill(float* p, int n, float v, cudaStream_t st) {
+  fill_kernel<<<(n + 127) / 128, 128, 0, st>>>(p, n, v);
+  return check_launch();
+}
+
+// out[k, n] = src[k, n] * s[n], float32 (the first stem conv keeps float32 weights)
+__global__ void scale_cols_kernel(const float* __restrict__ src, int K, int N, const float* __restrict__ s,
+                                  float* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < K * N) out[i] = src[i] * s[i % N];
+}
+int launch_scale_cols(const float* src, int K, int N, const float* s, float* out, cudaStream_t st) {
+  scale_cols_kernel<<<(K * N + 255) / 256, 256, 0, st>>>(src, K, N, s, out);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ first stem conv ----
+// 3x3 stride-2 'SAME' conv of the image (few input channels), BatchNorm folded, GELU.
+// x (Nimg, Hi, Wi, Cin) bf16 -> y (Nimg, Ho, Wo, Co) bf16.  wk (9*Cin, Co) fp32 already scaled by the
+// BatchNorm factor, bias (Co).  Thread = (output pixel, 8 output channels).
+__global__ void __launch_bounds__(256)
+stem_conv1_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
+                  const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int Nimg, int Hi,
+                  int Wi, int Cin, int Ho, int Wo, int Co, int pad_h, int pad_w, int gelu) {
+  extern __shared__ float ws[];                    // (9*Cin, Co) + (Co)
+  const int K = 9 * Cin;
+  for (int i = threadIdx.x; i < K * Co; i += blockDim.x) ws[i] = wk[i];
+  for (int i = threadIdx.x; i < Co; i += blockDim.x) ws[K * Co + i] = bias[i];
+  __syncthreads();
+  const int groups = Co / 8;
+  const long long total = (long long)Nimg * Ho * Wo * groups;
+  for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < total;
+       it += (long long)gridDim.x * blockDim.x) {
+    const int cg = (int)(it % groups);
+    const long long px = it / groups;
+    const int wo = (int)(px % Wo), ho = (int)((px / Wo) % Ho), n = (int)(px / ((long long)Wo * Ho));
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = ws[K * Co + cg * 8 + j];
+    for (int ti = 0; ti < 3; ++ti) {
+      const int hi = ho * 2 + ti - pad_h;
+      if (hi < 0 || hi >= Hi) continue;
+      for (int tj = 0; tj < 3; ++tj) {
+        const int wi = wo * 2 + tj - pad_w;
+        if (wi < 0 || wi >= Wi) continue;
+        const __nv_bfloat16* xp = x + (((size_t)n * Hi + hi) * Wi + wi) * Cin;
+        for (int c = 0; c < Cin; ++c) {
+          const float xv = __bfloat162float(xp[c]);
+          const float* wr = ws + ((ti * 3 + tj) * Cin + c) * Co + cg * 8;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, wr[j], acc[j]);
+        }
+      }
+    }
+    if (gelu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = gelu_tanh_f(acc[j]);
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)px * Co + cg * 8) = pack8(acc);
+  }
+}
+int launch_stem_conv1(const __nv_bfloat16* x, const float* wk, const float* bias, __nv_bfloat16* y,
+                      int Nimg, int Hi, int Wi, int Cin, int Co, int gelu, cudaStream_t st) {
+  if (Co % 8 != 0 || Cin > 16) return CSSM_ERR_UNSUPPORTED;
+  const int Ho = (Hi + 1) / 2, Wo = (Wi + 1) / 2;
+  const int pad_h = ((Ho - 1) * 2 + 3 - Hi > 0 ? (Ho - 1) * 2 + 3 - Hi : 0) / 2;
+  const int pad_w = ((Wo - 1) * 2 + 3 - Wi > 0 ? (Wo - 1) * 2 + 3 - Wi : 0) / 2;
+  const size_t smem = (size_t)(9 * Cin * Co + Co) * 4;
+  const long long total = (long long)Nimg * Ho * Wo * (Co / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  stem_conv1_kernel<<<(int)blocks, 256, smem, st>>>(x, wk, bias, y, Nimg, Hi, Wi, Cin, Ho, Wo, Co, pad_h,
+                                                     pad_w, gelu);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ depthwise conv ----
+// Depthwise KS x KS 'SAME' conv (zero padding) on channels-last bf16, thread = (strip of RH output
+// rows of one column, 8 channels): every input value of the strip's (RH + KS - 1) x KS window is
+// loaded once and feeds up to RH outputs.
+//   v    = pre ? pre_a[n, c] * x + pre_b[n, c] : x          (LayerNorm over a whole sample, applied on load)
+//   out  = (add_centre ? v_centre : 0) + sum_taps w * v + bias;  then GELU when gelu != 0.
+template <int KS, int RH>
+__global__ void __launch_bounds__(256)
+dwconv_cl_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
+                 const float* __restrict__ bias, const float* __restrict__ pre_a,
+                 const float* __restrict__ pre_b, __nv_bfloat16* __restrict__ y, float* __restrict__ y_f32,
+                 int Nimg, int H, int W, int C, int add_centre, int gelu) {
+  extern __shared__ float ws[];                    // (KS*KS, C) + (C)
+  for (int i = threadIdx.x; i < KS * KS * C; i += blockDim.x) ws[i] = wk ? wk[i] : 0.f;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) ws[KS * KS * C + i] = (wk && bias) ? bias[i] : 0.f;
+  __syncthreads();
+  constexpr int P = (KS - 1) / 2;
+  const int groups = C / 8, strips = (H + RH - 1) / RH;
+  const long long total = (long long)Nimg * strips * W * groups;
+  for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < total;
+       it += (long long)gridDim.x * blockDim.x) {
+    const int cg = (int)(it % groups);
+    long long r = it / groups;
+    const int w = (int)(r % W); r /= W;
+    const int sp = (int)(r % strips), n = (int)(r / strips);
+    const int h0 = sp * RH, c0 = cg * 8;
+    float pa[8], pb[8];
+    if (pre_a != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { pa[j] = pre_a[(size_t)n * C + c0 + j]; pb[j] = pre_b[(size_t)n * C + c0 + j]; }
+    }
+    float acc[RH][8];
+#pragma unroll
+    for (int o = 0; o < RH; ++o)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[o][j] = ws[KS * KS * C + c0 + j];
+    const __nv_bfloat16* xn = x + (size_t)n * H * W * C + c0;
+#pragma unroll
+    for (int ir = 0; ir < RH + KS - 1; ++ir) {
+      const int hi = h0 + ir - P;
+      if (hi < 0 || hi >= H) continue;
+#pragma unroll
+      for (int tj = 0; tj < KS; ++tj) {
+        const int wi = w + tj - P;
+        if (wi < 0 || wi >= W) continue;
+        float v[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(xn + ((size_t)hi * W + wi) * C)), v);
+        if (pre_a != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = fmaf(pa[j], v[j], pb[j]);
+        }
+#pragma unroll
+        for (int o = 0; o < RH; ++o) {
+          const int ti = ir - o;                   // tap row that maps input row ir to output row o
+          if (ti < 0 || ti >= KS) continue;
+          const float* wr = ws + (ti * KS + tj) * C + c0;
+          const float4 w0 = *reinterpret_cast<const float4*>(wr), w1 = *reinterpret_cast<const float4*>(wr + 4);
+          acc[o][0] = fmaf(v[0], w0.x, acc[o][0]); acc[o][1] = fmaf(v[1], w0.y, acc[o][1]);
+          acc[o][2] = fmaf(v[2], w0.z, acc[o][2]); acc[o][3] = fmaf(v[3], w0.w, acc[o][3]);
+          acc[o][4] = fmaf(v[4], w1.x, acc[o][4]); acc[o][5] = fmaf(v[5], w1.y, acc[o][5]);
+          acc[o][6] = fmaf(v[6], w1.z, acc[o][6]); acc[o][7] = fmaf(v[7], w1.w, acc[o][7]);
+          if (add_centre && ti == P && tj == P) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[o][j] += v[j];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 0; o < RH; ++o) {
+      const int h = h0 + o;
+      if (h >= H) continue;
+      if (gelu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[o][j] = gelu_tanh_f(acc[o][j]);
+      }
+      const size_t off = (((size_t)n * H + h) * W + w) * C + c0;
+      if (y_f32 != nullptr) {
+        *reinterpret_cast<float4*>(y_f32 + off) = make_float4(acc[o][0], acc[o][1], acc[o][2], acc[o][3]);
+        *reinterpret_cast<float4*>(y_f32 + off + 4) = make_float4(acc[o][4], acc[o][5], acc[o][6], acc[o][7]);
+      } else {
+        *reinterpret_cast<uint4*>(y + off) = pack8(acc[o]);
+      }
+    }
+  }
+}
+
+int launch_dwconv_cl(const __nv_bfloat16* x, const float* wk, const float* bias, const float* pre_a,
+                     const float* pre_b, __nv_bfloat16* y, float* y_f32, int Nimg, int H, int W, int C,
+                     int ks, int add_centre, int gelu, cudaStream_t st) {
+  if (C % 8 != 0 || (ks != 3 && ks != 7)) return CSSM_ERR_UNSUPPORTED;
+  constexpr int RH = 4;
+  const size_t smem = (size_t)(ks * ks * C + C) * 4;
+  const long long total = (long long)Nimg * ((H + RH - 1) / RH) * W * (C / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  cudaError_t e;
+  if (ks == 3) {
+    e = cudaFuncSetAttribute(dwconv_cl_kernel<3, RH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+    dwconv_cl_kernel<3, RH><<<(int)blocks, 256, smem, st>>>(x, wk, bias, pre_a, pre_b, y, y_f32, Nimg, H, W, C,
+                                                             add_centre, gelu);
+  } else {
+    e = cudaFuncSetAttribute(dwconv_cl_kernel<7, RH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+    dwconv_cl_kernel<7, RH><<<(int)blocks, 256, smem, st>>>(x, wk, bias, pre_a, pre_b, y, y_f32, Nimg, H, W, C,
+                                                             add_centre, gelu);
+  }
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ LayerNorm over C ----
+// Per-pixel LayerNorm (eps 1e-6) on channels-last bf16.  A pixel is handled by C/8 consecutive
+// threads (8 channels = 16 bytes each); partial sums meet in shared memory; two passes (mean,
+// then squared deviations) on the values kept in registers.
+__global__ void __launch_bounds__(256)
+layernorm_cl_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                    const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, long long npix, int C,
+                    int ppb) {
+  __shared__ float part[256];
+  __shared__ float stat[256];
+  const int chunks = C / 8;
+  const int lp = threadIdx.x / chunks, ck = threadIdx.x - lp * chunks;
+  const long long px = (long long)blockIdx.x * ppb + lp;
+  const bool on = lp < ppb && px < npix;
+  float v[8];
+  if (on) unpack8(__ldg(reinterpret_cast<const uint4*>(x + px * C + ck * 8)), v);
+  else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s += v[j];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  if (on && ck == 0) {
+    float t = 0.f;
+    for (int i = 0; i < chunks; ++i) t += part[lp * chunks + i];
+    stat[lp] = t / (float)C;
+  }
+  __syncthreads();
+  const float mean = on ? stat[lp] : 0.f;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { const float d = v[j] - mean; q = fmaf(d, d, q); }
+  __syncthreads();
+  part[threadIdx.x] = q;
+  __syncthreads();
+  if (on && ck == 0) {
+    float t = 0.f;
+    for (int i = 0; i < chunks; ++i) t += part[lp * chunks + i];
+    stat[lp] = rsqrtf(t / (float)C + 1e-6f);
+  }
+  __syncthreads();
+  if (!on) return;
+  const float rstd = stat[lp];
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * __ldg(scale + ck * 8 + j) + __ldg(bias + ck * 8 + j);
+  *reinterpret_cast<uint4*>(y + px * C + ck * 8) = pack8(o);
+}
+int launch_layernorm_cl(const __nv_bfloat16* x, const float* scale, const float* bias, __nv_bfloat16* y,
+                        long long npix, int C, cudaStream_t st) {
+  if (C % 8 != 0 || C / 8 > 256) return CSSM_ERR_UNSUPPORTED;
+  const int chunks = C / 8, ppb = 256 / chunks;
+  const long long blocks = (npix + ppb - 1) / ppb;
+  layernorm_cl_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, scale, bias, y, npix, C, ppb);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ LayerNorm over a sample ----
+// Moments over all H*W*C values of each sample (two passes over the L2-resident sample), written as
+// the per-(sample, channel) affine the consumer applies on load:
+//   a[n, c] = rstd_n * scale[c],  b[n, c] = bias[c] - mean_n * rstd_n * scale[c].
+__global__ void __launch_bounds__(512)
+sample_norm_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                   const float* __restrict__ bias, float* __restrict__ a, float* __restrict__ b, int per,
+                   int C) {
+  __shared__ float red[16];
+  __shared__ float bc;
+  const int n = blockIdx.x;
+  const uint4* xs = reinterpret_cast<const uint4*>(x + (size_t)n * per);
+  const int chunks = per / 8;
+  auto block_sum = [&](float s) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+      bc = t;
+    }
+    __syncthreads();
+    return bc;
+  };
+  float s = 0.f;
+  for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+    float v[8];
+    unpack8(__ldg(xs + i), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[j];
+  }
+  const float mean = block_sum(s) / (float)per;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+    float v[8];
+    unpack8(__ldg(xs + i), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float d = v[j] - mean; q = fmaf(d, d, q); }
+  }
+  const float rstd = rsqrtf(block_sum(q) / (float)per + 1e-6f);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float sc = rstd * scale[c];
+    a[(size_t)n * C + c] = sc;
+    b[(size_t)n * C + c] = bias[c] - mean * sc;
+  }
+}
+int launch_sample_norm(const __nv_bfloat16* x, const float* scale, const float* bias, float* a, float* b,
+                       int Nimg, int per, int C, cudaStream_t st) {
+  if (per % 8 != 0) return CSSM_ERR_UNSUPPORTED;
+  sample_norm_kernel<<<Nimg, 512, 0, st>>>(x, scale, bias, a, b, per, C);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ plane sums ----
+// sums[n, c] = sum over the P pixels of x[n, p, c] (x has row stride ld): thread = 8 channels of a
+// slice of the pixels; deterministic order.
+__global__ void __launch_bounds__(256)
+plane_sum_cl_kernel(const __nv_bfloat16* __restrict__ x, int ld, int P, int C, float* __restrict__ sums) {
+  __shared__ float part[8][33][8];
+  const int chunks = C / 8;                          // blockDim.x = 32 chunk lanes, blockDim.y = 8 pixel slices
+  const int n = blockIdx.y, ck = blockIdx.x * 32 + threadIdx.x;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (ck < chunks) {
+    const __nv_bfloat16* xp = x + (size_t)n * P * ld + ck * 8;
+    for (int p = threadIdx.y; p < P; p += 8) {
+      float v[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(xp + (size_t)p * ld)), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[threadIdx.y][threadIdx.x][j] = acc[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && ck < chunks) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = 0.f;
+      for (int s = 0; s < 8; ++s) t += part[s][threadIdx.x][j];
+      sums[(size_t)n * C + ck * 8 + j] = t;
+    }
+  }
+}
+int launch_plane_sum_cl(const __nv_bfloat16* x, int ld, int Nimg, int P, int C, float* sums, cudaStream_t st) {
+  if (C % 8 != 0 || ld % 8 != 0) return CSSM_ERR_UNSUPPORTED;
+  dim3 grid((C / 8 + 31) / 32, Nimg), block(32, 8);
+  plane_sum_cl_kernel<<<grid, block, 0, st>>>(x, ld, P, C, sums);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ readout ----
+// pooled[n, c] = max (or mean) over the P pixels of x[n, p, c], float32.
+__global__ void pool_cl_kernel(const __nv_bfloat16* __restrict__ x, int P, int C, int use_max,
+                               float* __restrict__ pooled) {
+  const int n = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const __nv_bfloat16* xp = x + (size_t)n * P * C + c;
+  float m = use_max ? -INFINITY : 0.f;
+  for (int p = 0; p < P; ++p) {
+    const float v = __bfloat162float(xp[(size_t)p * C]);
+    m = use_max ? fmaxf(m, v) : m + v;
+  }
+  pooled[(size_t)n * C + c] = use_max ? m : m / (float)P;
+}
+int launch_pool_cl(const __nv_bfloat16* x, int Nimg, int P, int C, int use_max, float* pooled, cudaStream_t st) {
+  dim3 grid((C + 127) / 128, Nimg);
+  pool_cl_kernel<<<grid, 128, 0, st>>>(x, P, C, use_max, pooled);
+  return check_launch();
+}
+
+// logits[n, k] = pooled[n, :] . W[:, k] + b[k], float32 (the reference keeps its head in float32)
+__global__ void head_kernel(const float* __restrict__ pooled, const float* __restrict__ W,
+                            const float* __restrict__ b, float* __restrict__ logits, int C, int K) {
+  extern __shared__ float ps[];
+  const int n = blockIdx.y;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) ps[i] = pooled[(size_t)n * C + i];
+  __syncthreads();
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  float acc = b[k];
+  for (int c = 0; c < C; ++c) acc = fmaf(ps[c], __ldg(W + (size_t)c * K + k), acc);
+  logits[(size_t)n * K + k] = acc;
+}
+int launch_head(const float* pooled, const float* W, const float* b, float* logits, int Nimg, int C, int K,
+                cudaStream_t st) {
+  dim3 grid((K + 127) / 128, Nimg);
+  head_kernel<<<grid, 128, (size_t)C * 4, st>>>(pooled, W, b, logits, C, K);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ conversions ----
+__global__ void f32_to_bf16_vec_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * i), b = __ldg(reinterpret_cast<const float4*>(x) + 2 * i + 1);
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    reinterpret_cast<uint4*>(y)[i] = pack8(v);
+  }
+}
+int launch_f32_to_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t st) {
+  if (n % 8 != 0) return CSSM_ERR_UNSUPPORTED;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  f32_to_bf16_vec_kernel<<<(int)blocks, 256, 0, st>>>(x, y, n / 8);
+  return check_launch();
+}
+
+// out = res + y (res bf16, y float32) -> bf16: the residual after the general (float32) mixer path
+__global__ void add_res_kernel(const __nv_bfloat16* __restrict__ res, const float* __restrict__ yv,
+                               __nv_bfloat16* __restrict__ out, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float r[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(res) + i), r);
+    const float4 a = __ldg(reinterpret_cast<const float4*>(yv) + 2 * i), b = __ldg(reinterpret_cast<const float4*>(yv) + 2 * i + 1);
+    r[0] += a.x; r[1] += a.y; r[2] += a.z; r[3] += a.w; r[4] += b.x; r[5] += b.y; r[6] += b.z; r[7] += b.w;
+    reinterpret_cast<uint4*>(out)[i] = pack8(r);
+  }
+}
+int launch_add_res(const __nv_bfloat16* res, const float* yv, __nv_bfloat16* out, long long n, cudaStream_t st) {
+  if (n % 8 != 0) return CSSM_ERR_UNSUPPORTED;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  add_res_kernel<<<(int)blocks, 256, 0, st>>>(res, yv, out, n / 8);
+  return check_launch();
+}
+
+}  // namespace cssm

@@ -453,14 +453,118 @@ int cssm_simple_forward_host(const cssm_simple_desc* d, const cssm_simple_weight
                              const void* block_plan, const float* x_host, float* logits_host,
                              void* workspace, size_t workspace_bytes, int32_t flags, void* stream);
 
+/* ------------------------------------------------------------ CSSM-SHViT (bf16) --- */
+/* Inference forward of the CSSM-SHViT image classifier around gated mixers (src/models/
+ * cssm_shvit.py:269-460 with the layers of src/models/shvit.py:34-262), as the reference runs it
+ * with dtype = bfloat16: activations are bfloat16 channels-last, parameters float32 in the
+ * reference's layout (Dense (in, out), conv HWIO, BatchNorm scale / bias / running mean / var),
+ * accumulation float32, logits float32.  Image input only (the model repeats it over
+ * num_timesteps), cssm_type 'gated', block_norm 'global_layer', inference (deterministic) mode.
+ * The Dense layers and the 3x3 stride-2 ConvBN layers run as bf16 tcgen05 GEMMs (the convs as
+ * implicit GEMMs), BatchNorm folded into the weights. */
+#define CSSM_SHVIT_MAX_BLOCKS 16
+
+/* One block of a stage.  is_cssm = 0: ConvBlock (shvit.py:219-262); 1: CSSMSHViTBlock with a
+ * GatedCSSM mixer (cssm_shvit.py:19-266). */
+typedef struct cssm_shvit_block_desc {
+  int32_t B, H, W, C;               /* block input (B,H,W,C)                              */
+  int32_t is_cssm;
+  int32_t hidden;                   /* int(dim * mlp_ratio)                               */
+  int32_t num_timesteps;            /* T of the mixer                                     */
+  int32_t kernel_size;              /* spectral kernel of the mixer                       */
+  int32_t use_pos_conv, use_dwconv;
+  int32_t rope_mode; float rope_base; float spectral_rho;
+  int32_t gate_activation, short_conv_size, short_conv_spatial_size, gate_type;
+} cssm_shvit_block_desc;
+
+typedef struct cssm_shvit_block_weights {
+  const float* norm1_scale; const float* norm1_bias;     /* (C)                           */
+  const float* norm2_scale; const float* norm2_bias;
+  const float* dw_kernel; const float* dw_bias;          /* ConvBlock dwconv (7,7,1,C); CSSM block pos_conv (3,3,1,C) or NULL */
+  const float* pw_kernel; const float* pw_bias;          /* ConvBlock pwconv (C,C)        */
+  const float* fc1_kernel; const float* fc1_bias;        /* (C,hidden)                    */
+  const float* fc2_kernel; const float* fc2_bias;        /* (hidden,C)                    */
+  const float* mlp_dw_kernel; const float* mlp_dw_bias;  /* CSSM block Mlp dwconv (3,3,1,hidden) or NULL */
+  cssm_gated_weights cssm;                               /* CSSM block: the mixer         */
+} cssm_shvit_block_weights;
+
+typedef struct cssm_shvit_convbn {       /* ConvBN, shvit.py:34-61 */
+  const float* kernel;                   /* (3,3,Cin,Cout), no bias */
+  const float* bn_scale; const float* bn_bias; const float* bn_mean; const float* bn_var;
+} cssm_shvit_convbn;
+
+typedef struct cssm_shvit_desc {
+  int32_t B, H, W, Cin;             /* images (B,H,W,Cin) bfloat16                         */
+  int32_t embed_dims[4], depths[4], use_cssm[4], kernel_sizes[4];
+  int32_t num_classes, num_timesteps;
+  float   mlp_ratio;
+  int32_t use_pos_conv, use_dwconv;
+  int32_t head_pool;                /* 0 max, 1 mean (cssm_shvit.py:436-439)               */
+  int32_t rope_mode; float rope_base; float spectral_rho;
+  int32_t gate_activation, short_conv_size, short_conv_spatial_size, gate_type;
+} cssm_shvit_desc;
+
+typedef struct cssm_shvit_weights {
+  cssm_shvit_convbn patch[2];                            /* patch_embed/ConvBN_0, ConvBN_1 */
+  cssm_shvit_convbn down[3];                             /* downsample1..3/ConvBN_0        */
+  cssm_shvit_block_weights blocks[CSSM_SHVIT_MAX_BLOCKS]; /* stage0_block0, ... in order   */
+  const float* norm_scale; const float* norm_bias;       /* final LayerNorm                */
+  const float* head_kernel; const float* head_bias;      /* (C3, num_classes)              */
+} cssm_shvit_weights;
+
+/* One block on device buffers: x, y (B,H,W,C) bfloat16.  Replaces ConvBlock.__call__
+ * (shvit.py:232-262) / CSSMSHViTBlock.__call__ for a 4-D input (cssm_shvit.py:66-266). */
+size_t cssm_shvit_block_plan_bytes(const cssm_shvit_block_desc* d);
+size_t cssm_shvit_block_workspace_bytes(const cssm_shvit_block_desc* d);
+int cssm_shvit_block_plan_init(const cssm_shvit_block_desc* d, const cssm_shvit_block_weights* w,
+                               void* plan, size_t plan_bytes, void* stream);
+int cssm_shvit_block_forward(const cssm_shvit_block_desc* d, const cssm_shvit_block_weights* w,
+                             const void* plan, const void* x_bf16, void* y_bf16, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
+/* Whole model: logits (B, num_classes) float32 = CSSMSHViT(x, training=False)
+ * (cssm_shvit.py:324-460).  The plan holds the packed bf16 weights (call plan_init again when the
+ * parameters change). */
+size_t cssm_shvit_plan_bytes(const cssm_shvit_desc* d);
+size_t cssm_shvit_workspace_bytes(const cssm_shvit_desc* d);
+int cssm_shvit_plan_init(const cssm_shvit_desc* d, const cssm_shvit_weights* w, void* plan,
+                         size_t plan_bytes, void* stream);
+int cssm_shvit_forward(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
+                       const void* x_bf16, float* logits, void* workspace, size_t workspace_bytes,
+                       void* stream);
+/* Same with the images and the logits in HOST memory (pinned for full copy speed); the workspace
+ * (cssm_shvit_host_workspace_bytes) holds the staging copies.  Waits for the stream. */
+size_t cssm_shvit_host_workspace_bytes(const cssm_shvit_desc* d);
+int cssm_shvit_forward_host(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
+                            const void* x_bf16_host, float* logits_host, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
+/* The bf16 tensor-core GEMM of the model's Dense layers on its own (nn.Dense with dtype bfloat16:
+ * shvit.py:165-180; cssm.py:481, 584 inside a bf16 model):
+ *   out (M,N) bf16 = act(A (M,K) bf16 @ kernel (K,N) + bias) [+ res (M,N) bf16]
+ * `wt` is the kernel packed by cssm_bf16_pack_weight: (N, ldw) bf16, ldw = cssm_bf16_packed_ld(K).
+ * act: 0 none, 1 gelu (tanh form, jax.nn.gelu's default), 2 silu.  K and N multiples of 32. */
+int32_t cssm_bf16_packed_ld(int32_t K);
+int cssm_bf16_pack_weight(const float* kernel, int32_t K, int32_t N, const float* col_scale,
+                          void* wt, void* stream);
+int cssm_bf16_gemm(const void* A, int32_t M, int32_t K, const void* wt, int32_t N, const float* bias,
+                   int32_t act, const void* res, void* out, void* stream);
+/* 3x3 stride-2 'SAME' convolution (nn.Conv inside ConvBN, shvit.py:45-54) as an implicit GEMM:
+ * x (B,Hi,Wi,Cin) bf16 -> out (B,ceil(Hi/2),ceil(Wi/2),Cout) bf16; `wt` = the HWIO kernel viewed as
+ * (9*Cin, Cout) and packed by cssm_bf16_pack_weight (col_scale = the BatchNorm factor). */
+int cssm_bf16_conv3x3s2(const void* x, int32_t B, int32_t Hi, int32_t Wi, int32_t Cin, const void* wt,
+                        int32_t Cout, const float* bias, int32_t act, void* out, void* stream);
+
 /* ---- device-side error word (no counterpart in the reference) ----
  * Kernels of this library wait on hardware barriers (TMA copies landing, tensor-core tiles
  * finishing) with an iteration limit.  A wait that runs out does not hang or trap: the CTA records
  * a code in a device word, stops storing results and winds down, and the forward call that
  * launched it has long since returned CSSM_OK (calls are asynchronous).  After synchronising the
  * stream, cssm_device_error copies that word to *out: 0 = no wait ever expired on the current
- * device since the last clear; low byte = tensor-core projection kernels (1 producer, 2 MMA
- * issuer, 3 drain, 4 epilogue), next byte = fused spectral kernels (1 input plane, 2 z plane).
+ * device since the last clear; low byte = fp32 tensor-core projection kernels (1 producer, 2 MMA
+ * issuer, 3 drain, 4 epilogue), next byte = fused spectral kernels (1 input plane, 2 z plane),
+ * third byte = bf16 tensor-core GEMM (5 TMA producer, 6 MMA issuer, 7 drain, 8 epilogue, 9 im2col
+ * producer).
  * A non-zero value means the outputs of the calls since the last clear are not to be trusted.
  * clear != 0 resets the word after reading it.  The call copies from the device on the legacy
  * default stream (it waits for work on blocking streams). */

@@ -151,7 +151,7 @@ def _simple(name, shape, seed, block_kwargs, **kw):
                 mirror_kwargs=ref, shape=shape, seed=seed, input="uniform", call_kwargs=dict(training=False))
 
 
-def _shvit(name, shape, seed, seeded=None, mirror_dtype="float32", **kw):
+def _shvit(name, shape, seed, seeded=None, mirror_dtype="bfloat16", **kw):
     """CSSMSHViT with gated mixers; kw are CSSMSHViT fields."""
     ref = dict(cssm_type="gated", **kw)
     okw = {k: v for k, v in kw.items() if k not in ("num_classes", "mlp_ratio", "drop_path_rate")}
@@ -173,7 +173,7 @@ def _shvit_block(name, shape, seed, **kw):
     okw = dict(kw)
     return dict(name=name, family="shvit_block", ref_class="CSSMSHViTBlock", ref_kwargs=ref,
                 oracle="cssm_block", oracle_kwargs=okw, mirror="CSSMSHViTBlock",
-                mirror_kwargs=ref, shape=shape, seed=seed)
+                mirror_kwargs=ref, shape=shape, seed=seed, tol_gpu=2e-2)
 
 
 _S1 = dict(embed_dims=(64, 128, 256, 384), depths=(1, 2, 2, 1), num_classes=1000)
@@ -287,7 +287,7 @@ CASES = [
     _shvit("shvit_tiny_T2_ks3_meanpool", (2, 32, 32, 3), 512, embed_dims=(16, 16, 32, 32),
            depths=(1, 1, 1, 1), num_classes=5, num_timesteps=2, kernel_sizes=(3, 3, 3, 3),
            head_pool="mean"),
-    _shvit("shvit_s1_224_cfg5", (2, 224, 224, 3), 513, seeded=5130, mirror_dtype="bfloat16",
+    _shvit("shvit_s1_224_cfg5", (2, 224, 224, 3), 513, seeded=5130,
            num_timesteps=1, kernel_sizes=(1, 1, 1, 1), short_conv_spatial_size=0, **_S1),
 ]
 

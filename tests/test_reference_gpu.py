@@ -2,8 +2,9 @@
 
 tests/golden/ref/*.npz hold what the reference's unmodified model files computed in double
 precision on the same seeded inputs and parameters (see tests/golden/make_reference_golden.py).
-Tolerance: 1e-4 of the output's variation for the fp32 paths, 2e-2 for the bf16-carry GDN
-static-image path."""
+Tolerance: 1e-4 of the output's variation for the fp32 paths, 2e-2 for the bf16 paths (the
+bf16-carry GDN static-image scan; the CSSM-SHViT blocks and models, which run with bfloat16
+activations against the reference's double-precision result)."""
 import numpy as np
 import pytest
 import torch
@@ -24,7 +25,10 @@ def test_cuda_path_reproduces_reference(name):
     cls = getattr(cssm_b200, case["mirror"])
     try:
         mod = cls(**case["mirror_kwargs"])
-        y = mod.apply({"params": params}, x, **({"training": False} if case["family"] == "simple" else {}))
+        variables = {"params": params}
+        if stats is not None:
+            variables["batch_stats"] = stats
+        y = mod.apply(variables, x, **({"training": False} if case["family"] in ("simple", "shvit") else {}))
     except NotImplementedError as e:
         pytest.skip(f"no kernel for this field combination: {e}")
     got = rc.pick(y.float().cpu().numpy(), pos)

@@ -1,0 +1,115 @@
+"""GPU tests of the bf16 kernels under the CSSM-SHViT model, through the C ABI: the tcgen05 GEMM
+with its K loop and epilogue options, the 3x3 stride-2 convolution as an implicit GEMM (both
+against float32 torch references on the same bf16-rounded operands), the model's intermediate
+activations against the NumPy oracle, and run-to-run determinism.  Tolerance 2e-2 (bf16)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from cssm_b200 import CSSMSHViT, lib
+from cssm_b200._lib import check
+from oracle import cssm_oracle as orc
+from oracle import shvit_oracle as sv
+
+pytestmark = pytest.mark.gpu
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _pack(L, kernel, K, N, col_scale=None):
+    ld = L.cssm_bf16_packed_ld(K)
+    wt = torch.empty((N, ld), dtype=torch.bfloat16, device="cuda")
+    cs = col_scale.data_ptr() if col_scale is not None else None
+    check(L.cssm_bf16_pack_weight(kernel.data_ptr(), K, N, cs, wt.data_ptr(), _st()), "pack")
+    return wt
+
+
+@pytest.mark.parametrize("M,K,N,act,res", [
+    (300, 64, 64, 0, False), (1000, 256, 512, 1, False), (777, 1024, 256, 0, True),
+    (128, 384, 1536, 1, False), (5000, 1536, 384, 0, True), (1, 64, 128, 2, False),
+    (20000, 128, 128, 2, True), (257, 512, 768, 2, False), (129, 64, 1024, 0, False)])
+def test_bf16_gemm(M, K, N, act, res):
+    L = lib()
+    g = torch.Generator(device="cuda").manual_seed(M + K + N)
+    A = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
+    W = (torch.randn((K, N), device="cuda", generator=g) / K ** 0.5)
+    b = torch.randn((N,), device="cuda", generator=g)
+    R = torch.randn((M, N), device="cuda", generator=g).to(torch.bfloat16) if res else None
+    wt = _pack(L, W, K, N)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    check(L.cssm_bf16_gemm(A.data_ptr(), M, K, wt.data_ptr(), N, b.data_ptr(), act,
+                           R.data_ptr() if res else None, out.data_ptr(), _st()), "gemm")
+    ref = A.float() @ W.to(torch.bfloat16).float() + b
+    if act == 1:
+        ref = F.gelu(ref, approximate="tanh")
+    elif act == 2:
+        ref = F.silu(ref)
+    if res:
+        ref = ref + R.float()
+    torch.cuda.synchronize()
+    err = (out.float() - ref).norm() / ref.norm()
+    assert err < 6e-3, float(err)          # one bf16 rounding of the output
+
+
+@pytest.mark.parametrize("B,Hi,Wi,Cin,Cout", [(2, 16, 16, 32, 64), (3, 14, 14, 128, 256),
+                                              (2, 7, 9, 64, 128), (1, 56, 56, 64, 128),
+                                              (2, 112, 112, 32, 64)])
+def test_bf16_conv3x3s2(B, Hi, Wi, Cin, Cout):
+    L = lib()
+    g = torch.Generator(device="cuda").manual_seed(Hi * Cin)
+    x = torch.randn((B, Hi, Wi, Cin), device="cuda", generator=g).to(torch.bfloat16)
+    W = torch.randn((3, 3, Cin, Cout), device="cuda", generator=g) / (9 * Cin) ** 0.5
+    scale = 1.0 + 0.2 * torch.randn((Cout,), device="cuda", generator=g)
+    b = torch.randn((Cout,), device="cuda", generator=g)
+    wt = _pack(L, W, 9 * Cin, Cout, scale)
+    Ho, Wo = (Hi + 1) // 2, (Wi + 1) // 2
+    out = torch.empty((B, Ho, Wo, Cout), dtype=torch.bfloat16, device="cuda")
+    check(L.cssm_bf16_conv3x3s2(x.data_ptr(), B, Hi, Wi, Cin, wt.data_ptr(), Cout, b.data_ptr(), 0,
+                                out.data_ptr(), _st()), "conv")
+    th, tw = max((Ho - 1) * 2 + 3 - Hi, 0), max((Wo - 1) * 2 + 3 - Wi, 0)
+    xp = F.pad(x.float().permute(0, 3, 1, 2), (tw // 2, tw - tw // 2, th // 2, th - th // 2))
+    wq = (W * scale).to(torch.bfloat16).float().permute(3, 2, 0, 1)
+    ref = F.conv2d(xp, wq, b, stride=2).permute(0, 2, 3, 1)
+    torch.cuda.synchronize()
+    assert out.shape == ref.shape
+    err = (out.float() - ref).norm() / ref.norm()
+    assert err < 6e-3, float(err)
+
+
+_TINY = dict(embed_dims=(32, 64, 64, 128), depths=(1, 1, 2, 1), num_classes=10, num_timesteps=1,
+             kernel_sizes=(1, 1, 1, 1), short_conv_spatial_size=0)
+
+
+def test_model_fast_path_matches_oracle_and_is_deterministic():
+    """A small CSSM-SHViT whose CSSM stages have 14x14 and 7x7 planes (224-pixel input), so the
+    bf16 channels-last mixer path runs; logits against the fp64 oracle, twice, bit-identical."""
+    p, s = sv.init_shvit_params(7, (224, 224), **{k: v for k, v in _TINY.items() if k != "num_timesteps"})
+    x = np.random.default_rng(3).standard_normal((3, 224, 224, 3)).astype(np.float32)
+    xb = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    ref = sv.shvit_forward(p, s, xb.float().cpu().numpy().astype(np.float64),
+                           **{k: v for k, v in _TINY.items() if k != "num_classes"})
+    model = CSSMSHViT(**_TINY)
+    variables = {"params": p, "batch_stats": s}
+    y1 = model.apply(variables, xb).clone()
+    y2 = model.apply(variables, xb)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+    assert orc.rel_l2(y1.cpu().numpy(), ref) <= 2e-2
+
+
+def test_host_entry_matches_device_entry():
+    p, s = sv.init_shvit_params(8, (64, 64), embed_dims=(32, 32, 64, 64), depths=(1, 1, 1, 1), num_classes=7,
+                                kernel_sizes=(3, 3, 3, 3))
+    model = CSSMSHViT(embed_dims=(32, 32, 64, 64), depths=(1, 1, 1, 1), num_classes=7, num_timesteps=2,
+                      kernel_sizes=(3, 3, 3, 3))
+    bound = model.bind({"params": p, "batch_stats": s})
+    x = torch.randn((2, 64, 64, 3)).to(torch.bfloat16)
+    want = bound(x.cuda()).cpu()
+    xh, lh = x.pin_memory(), torch.empty((2, 7), dtype=torch.float32).pin_memory()
+    bound.forward_host(xh, lh)
+    assert torch.equal(lh, want)
