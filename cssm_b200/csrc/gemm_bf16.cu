@@ -3,18 +3,22 @@
 //
 //   out[m, n] = act( sum_k A[m, k] * Wt[n, k] + bias[n] ) (+ res[m, n]),  bf16 in, fp32 accumulate.
 //
-// Persistent kernel, one CTA per SM, 320 threads, warp-specialised:
+// Persistent kernel, one CTA per SM, 320 threads (448 in conv mode), warp-specialised:
 //   warp 0     TMA producer: one lane issues cp.async.bulk.tensor loads of the A tile (128 rows x
 //              64 k, plain mode) and the weight tile (BN rows x 64 k) of every K block into a
 //              4-stage ring of 128-byte-swizzled K-major operand tiles;
 //   warp 1     MMA issuer: one lane issues 4 tcgen05.mma.kind::f16 (M128 x BN x K16) per K block
 //              into one of two TMEM accumulators; tcgen05.commit frees the stage / publishes the
 //              accumulator;
-//   warps 2-5  epilogue: tcgen05.ld (lane = output row), bias, GELU / SiLU, residual, bf16 stores;
-//              overlaps the next tile's main loop through the second accumulator;
-//   warps 6-9  im2col producers (conv mode only): thread = output pixel of the tile; gathers the
-//              eight 16-byte channel chunks of each K block from the channels-last input (zero
-//              outside the image) and writes them in the same swizzled layout.
+//   warps 2-9  epilogue, two warps per TMEM lane quadrant: tcgen05.ld (lane = output row), bias,
+//              GELU / SiLU, residual; each half (one warp per quadrant) stages boxes of 128 rows x 64
+//              bf16 columns in the 128-byte swizzle and writes them with one TMA tensor store
+//              (N a multiple of 64; otherwise direct 16-byte stores); overlaps the next tile's
+//              main loop through the second accumulator;
+//   warps 10-13 im2col producers (conv mode only): eight consecutive lanes fetch the eight 16-byte
+//              channel chunks of one output pixel's K block from the channels-last input (zero
+//              outside the image), four pixels per warp instruction, and write them in the same
+//              swizzled layout; the loads of the next two K blocks are in flight meanwhile.
 // Every mbarrier wait is bounded; on expiry the kernel records an error code (cssm_device_error)
 // and winds down.  No multicast, no cluster: each CTA loads its own tiles.
 #include <cuda.h>
@@ -28,8 +32,9 @@ namespace cssm {
 
 __device__ int g_bf16_error = 0;
 
-constexpr int GB_THREADS = 320;
-constexpr int GB_BM = 128, GB_BK = 64, GB_STAGES = 4;
+constexpr int GB_THREADS_PLAIN = 320, GB_THREADS_CONV = 448;
+constexpr uint32_t GB_OUT_BYTES = 2u * 16384u;           // one 128 x 64 bf16 staging box per epilogue half
+constexpr int GB_BM = 128, GB_BK = 64, GB_MAX_STAGES = 4;
 constexpr uint32_t GB_A_BYTES = GB_BM * 128u;            // one A stage: 128 rows x 128 bytes
 
 __device__ __forceinline__ uint32_t make_idesc_bf16(uint32_t M, uint32_t N) {
@@ -50,19 +55,21 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-template <bool IM2COL>
-__global__ void __launch_bounds__(GB_THREADS, 1)
+template <bool IM2COL, bool TMA_OUT>
+__global__ void __launch_bounds__(IM2COL ? GB_THREADS_CONV : GB_THREADS_PLAIN, 1)
 gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
-                 const __grid_constant__ CUtensorMap bmap) {
+                 const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap omap) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = tc::smem_u32(smem);
   const uint32_t BN = (uint32_t)g.BN;
   const uint32_t stage_bytes = GB_A_BYTES + BN * 128u;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GB_STAGES * stage_bytes);
-  uint64_t* full = bars;                    // [4] operands landed
-  uint64_t* empty = bars + GB_STAGES;       // [4] stage consumed
-  uint64_t* accfull = bars + 2 * GB_STAGES; // [2]
+  const int NS = g.stages;                                  // ring depth (3 when BN = 256 and TMA_OUT)
+  unsigned char* out_s = smem + (uint32_t)NS * stage_bytes; // TMA_OUT: 2 x 16 KB staging boxes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + (TMA_OUT ? GB_OUT_BYTES : 0u));
+  uint64_t* full = bars;                        // [4] operands landed
+  uint64_t* empty = bars + GB_MAX_STAGES;       // [4] stage consumed
+  uint64_t* accfull = bars + 2 * GB_MAX_STAGES; // [2]
   uint64_t* accempty = accfull + 2;         // [2]
   uint64_t* done = accempty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
@@ -75,12 +82,12 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
   while (tmem_cols < 2 * BN) tmem_cols <<= 1;
 
   if (tid == 0) {
-    for (int s = 0; s < GB_STAGES; ++s) {
+    for (int s = 0; s < NS; ++s) {
       tc::mbar_init(&full[s], IM2COL ? 1 + 128 : 1);
       tc::mbar_init(&empty[s], 1);
     }
     tc::mbar_init(&accfull[0], 1); tc::mbar_init(&accfull[1], 1);
-    tc::mbar_init(&accempty[0], 128); tc::mbar_init(&accempty[1], 128);
+    tc::mbar_init(&accempty[0], 256); tc::mbar_init(&accempty[1], 256);
     tc::mbar_init(done, 1);
     tc::fence_mbar_init();
   }
@@ -101,8 +108,8 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
       for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x) {
         const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % GB_STAGES;
-          if (!tc::mbar_wait(&empty[s], ((it / GB_STAGES) & 1) ^ 1)) { atomicExch(&g_bf16_error, 5); bad = true; break; }
+          const int s = it % NS;
+          if (!tc::mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { atomicExch(&g_bf16_error, 5); bad = true; break; }
           unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
           unsigned char* b_s = a_s + GB_A_BYTES;
           tc::mbar_expect_tx(&full[s], (IM2COL ? 0u : GB_A_BYTES) + BN * 128u);
@@ -123,8 +130,8 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
         tc::fence_after_sync();
         const uint32_t d = tmem_base + (uint32_t)ac * BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % GB_STAGES;
-          if (!tc::mbar_wait(&full[s], (it / GB_STAGES) & 1)) { atomicExch(&g_bf16_error, 6); bad = true; break; }
+          const int s = it % NS;
+          if (!tc::mbar_wait(&full[s], (it / NS) & 1)) { atomicExch(&g_bf16_error, 6); bad = true; break; }
           tc::fence_after_sync();
           const uint32_t a_s = sbase + (uint32_t)s * stage_bytes, b_s = a_s + GB_A_BYTES;
 #pragma unroll
@@ -143,24 +150,39 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
       if (!tc::mbar_wait(done, 0) && !bad) atomicExch(&g_bf16_error, 7);
     }
     __syncwarp();
-  } else if (warp < 6) {
+  } else if (warp < 10) {
     // ================================ epilogue ================================
     const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;             // which of the two warps of the quadrant
     const int row = q * 32 + lane;
+    const bool issuer = q == 0 && lane == 0;      // issues this half's TMA stores
+    unsigned char* stg = out_s + (uint32_t)half * 16384u;
     int tcnt = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcnt) {
       const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
       const int ac = tcnt & 1, aph = (tcnt >> 1) & 1;
-      if (!tc::mbar_wait(&accfull[ac], aph)) { atomicExch(&g_bf16_error, 8); break; }
+      bool ok = tc::mbar_wait(&accfull[ac], aph);
+      if (TMA_OUT) {
+        // the named barriers below need all 128 threads of the half: make the exit uniform
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.u32 p, %1, 0;\n\t"
+            "bar.red.and.pred q, %2, 128, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + half) : "memory");
+        ok = all_ok != 0;
+      }
+      if (!ok) { atomicExch(&g_bf16_error, 8); break; }
       tc::fence_after_sync();
       const int m = m0 + row;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)ac * BN;
-      for (int cc = 0; cc < g.BN / 32; ++cc) {
+      // 32 accumulator columns starting at tile column c0 -> bias, activation, residual
+      auto chunk32 = [&](int c0, float (&v)[32]) {
         uint32_t r[32];
-        tc::ld_32x32b_x32(taddr + cc * 32, r);
+        tc::ld_32x32b_x32(taddr + c0, r);
         tc::wait_ld();
-        const int n = n0 + cc * 32;
-        float v[32];
+        const int n = n0 + c0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         if (g.bias != nullptr) {
@@ -178,20 +200,50 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = silu_f(v[j]);
         }
-        if (m < g.M) {
-          if (g.res != nullptr) {
-            const uint4* rp = reinterpret_cast<const uint4*>(g.res + (size_t)m * g.ldr + n);
+        if (g.res != nullptr && m < g.M) {
+          const uint4* rp = reinterpret_cast<const uint4*>(g.res + (size_t)m * g.ldr + n);
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            float f[8];
+            unpack8(__ldg(rp + j4), f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j4 * 8 + e] += f[e];
+          }
+        }
+      };
+      if (TMA_OUT) {
+        for (int box = half; box < g.BN / 64; box += 2) {
+          uint4 pk[8];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            float v[32];
+            chunk32(box * 64 + hh * 32, v);
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
-              const uint4 u = __ldg(rp + j4);
-              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = bf16x2_to_float2(w[e]);
-                v[j4 * 8 + 2 * e] += f.x; v[j4 * 8 + 2 * e + 1] += f.y;
-              }
+              const float f[8] = {v[j4 * 8], v[j4 * 8 + 1], v[j4 * 8 + 2], v[j4 * 8 + 3],
+                                  v[j4 * 8 + 4], v[j4 * 8 + 5], v[j4 * 8 + 6], v[j4 * 8 + 7]};
+              pk[hh * 4 + j4] = pack8(f);
             }
           }
+          // the TMA store that last read this staging box must have drained it
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(stg + tc::sw128_offset(row, c)) = pk[c];
+          tc::fence_proxy_async();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+          if (issuer) {
+            tc::tma_store_2d(&omap, stg, n0 + box * 64, m0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      } else {
+        for (int cc = half; cc < g.BN / 32; cc += 2) {
+          float v[32];
+          chunk32(cc * 32, v);
+          if (m >= g.M) continue;
+          const int n = n0 + cc * 32;
           if (g.out_f32 != nullptr) {
             float4* op = reinterpret_cast<float4*>(g.out_f32 + (size_t)m * g.ldo + n);
 #pragma unroll
@@ -200,12 +252,9 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
             uint4* op = reinterpret_cast<uint4*>(g.out + (size_t)m * g.ldo + n);
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
-              uint4 u;
-              u.x = float2_to_bf16x2(v[j4 * 8 + 0], v[j4 * 8 + 1]);
-              u.y = float2_to_bf16x2(v[j4 * 8 + 2], v[j4 * 8 + 3]);
-              u.z = float2_to_bf16x2(v[j4 * 8 + 4], v[j4 * 8 + 5]);
-              u.w = float2_to_bf16x2(v[j4 * 8 + 6], v[j4 * 8 + 7]);
-              op[j4] = u;
+              const float f[8] = {v[j4 * 8], v[j4 * 8 + 1], v[j4 * 8 + 2], v[j4 * 8 + 3],
+                                  v[j4 * 8 + 4], v[j4 * 8 + 5], v[j4 * 8 + 6], v[j4 * 8 + 7]};
+              op[j4] = pack8(f);
             }
           }
         }
@@ -213,39 +262,65 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
       tc::fence_before_sync();
       tc::mbar_arrive(&accempty[ac]);
     }
+    // the staging boxes must outlive the last TMA stores that read them
+    if (TMA_OUT && issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else if (IM2COL) {
     // ================================ im2col producers ================================
-    const int row = tid - 6 * 32;                 // 0..127: output pixel of the tile
+    // lane = (row group rg, chunk c): the eight lanes of a group read the eight 16-byte chunks of one
+    // output pixel's K block (contiguous channels of one or two taps); thread handles rows rg + 16 i.
+    const int pt = tid - 10 * 32;                 // 0..127
+    const int c = pt & 7, rg = pt >> 3;
     const int HWo = g.Ho * g.Wo;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x) {
-      const int m = (tile / n_tiles) * GB_BM + row;
-      const bool live = m < g.M;
-      const int b = live ? m / HWo : 0;
-      const int px = live ? m - b * HWo : 0;
-      const int ho = px / g.Wo, wo = px - ho * g.Wo;
-      const int hi0 = ho * g.stride - g.pad_h, wi0 = wo * g.stride - g.pad_w;
-      const __nv_bfloat16* xb = g.A + (size_t)b * g.Hi * g.Wi * g.Cin;
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const int s = it % GB_STAGES;
-        uint4 v[8];
+      const int mt = (tile / n_tiles) * GB_BM;
+      int hi0[8], wi0[8], pb[8];                    // window origin and first pixel of the image
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int k0 = kb * GB_BK + c * 8;
-          const int tap = k0 / g.Cin, c0 = k0 - tap * g.Cin;
-          const int ti = tap / g.ksz, tj = tap - ti * g.ksz;
-          const int hi = hi0 + ti, wi = wi0 + tj;
-          const bool in = live && k0 < g.K && hi >= 0 && hi < g.Hi && wi >= 0 && wi < g.Wi;
-          v[c] = in ? __ldg(reinterpret_cast<const uint4*>(xb + ((size_t)hi * g.Wi + wi) * g.Cin + c0))
+      for (int i = 0; i < 8; ++i) {
+        const int m = mt + rg + 16 * i;
+        const bool live = m < g.M;
+        const int b = live ? m / HWo : 0;
+        const int px = live ? m - b * HWo : 0;
+        const int ho = px / g.Wo, wo = px - ho * g.Wo;
+        hi0[i] = live ? ho * g.stride - g.pad_h : -100000;     // dead rows fail the bounds test
+        wi0[i] = wo * g.stride - g.pad_w;
+        pb[i] = b * g.Hi * g.Wi;
+      }
+      auto gather = [&](int kb, uint4 (&v)[8]) {
+        const int k0 = kb * GB_BK + c * 8;
+        const int tap = k0 / g.Cin, c0 = k0 - tap * g.Cin;
+        const int ti = tap / g.ksz, tj = tap - ti * g.ksz;
+        const bool kin = kb < kblocks && k0 < g.K;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int hi = hi0[i] + ti, wi = wi0[i] + tj;
+          const bool in = kin && hi >= 0 && hi < g.Hi && wi >= 0 && wi < g.Wi;
+          v[i] = in ? __ldg(reinterpret_cast<const uint4*>(g.A + (size_t)(pb[i] + hi * g.Wi + wi) * g.Cin + c0))
                     : make_uint4(0u, 0u, 0u, 0u);
         }
-        if (!tc::mbar_wait(&empty[s], ((it / GB_STAGES) & 1) ^ 1)) { atomicExch(&g_bf16_error, 9); bad = true; break; }
-        unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
+      };
+      // register ring two K blocks deep
+      uint4 r0[8], r1[8], r2[8];
+      gather(0, r0);
+      gather(1, r1);
+      for (int kb = 0; kb < kblocks && !bad; kb += 3) {
+        // three blocks per trip so that the ring slots keep compile-time names
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(a_s + tc::sw128_offset(row, c)) = v[c];
-        tc::fence_proxy_async();
-        tc::mbar_arrive(&full[s]);
+        for (int u = 0; u < 3; ++u) {
+          if (kb + u >= kblocks) break;
+          uint4 (&cur)[8] = u == 0 ? r0 : (u == 1 ? r1 : r2);
+          uint4 (&nxt)[8] = u == 0 ? r2 : (u == 1 ? r0 : r1);
+          gather(kb + u + 2, nxt);
+          const int s = it % NS;
+          if (!tc::mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { atomicExch(&g_bf16_error, 9); bad = true; break; }
+          unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint4*>(a_s + tc::sw128_offset(rg + 16 * i, c)) = cur[i];
+          tc::fence_proxy_async();
+          tc::mbar_arrive(&full[s]);
+          ++it;
+        }
       }
     }
   }
@@ -308,6 +383,18 @@ int gemm_bf16_pick_bn(int N) {
   return 0;
 }
 
+// (rows x cols) bf16 output with row stride ld -> boxes of 64 columns x 128 rows for the TMA stores
+static bool make_out_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, uint64_t ld) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {64, 128}, es[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, es,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return CSSM_ERR_DIMS;
   g.Kpad = (g.K + GB_BK - 1) / GB_BK * GB_BK;
@@ -323,25 +410,32 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   } else if (g.K % 8 != 0 || g.lda % 8 != 0 || g.lda < g.K) {
     return CSSM_ERR_UNSUPPORTED;
   }
-  CUtensorMap amap, bmap;
+  CUtensorMap amap, bmap, omap;
   memset(&amap, 0, sizeof(amap));
   memset(&bmap, 0, sizeof(bmap));
+  memset(&omap, 0, sizeof(omap));
   // A: out-of-range k columns (K < Kpad) and rows (M not a multiple of 128) arrive as zeros
   if (!im2col && !make_kmajor_map(&amap, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, GB_BM))
     return CSSM_ERR_CUDA;
   if (!make_kmajor_map(&bmap, g.Wt, (uint64_t)g.N, (uint64_t)g.Kpad, (uint64_t)g.ldw, (uint32_t)g.BN))
     return CSSM_ERR_CUDA;
+  const bool tma_out = g.out_f32 == nullptr && g.BN % 64 == 0 &&
+                       make_out_map(&omap, g.out, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldo);
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const int tiles = ((g.M + GB_BM - 1) / GB_BM) * (g.N / g.BN);
   const int grid = tiles < sms ? tiles : sms;
-  const size_t smem = (size_t)GB_STAGES * (GB_A_BYTES + (size_t)g.BN * 128u) + 256 + 1024;
-  auto kern = im2col ? gemm_bf16_kernel<true> : gemm_bf16_kernel<false>;
+  const size_t stage = GB_A_BYTES + (size_t)g.BN * 128u;
+  g.stages = GB_MAX_STAGES;
+  while (g.stages > 2 && g.stages * stage + (tma_out ? GB_OUT_BYTES : 0) + 256 + 1024 > 227 * 1024) --g.stages;
+  const size_t smem = g.stages * stage + (tma_out ? GB_OUT_BYTES : 0) + 256 + 1024;
+  auto kern = im2col ? (tma_out ? gemm_bf16_kernel<true, true> : gemm_bf16_kernel<true, false>)
+                     : (tma_out ? gemm_bf16_kernel<false, true> : gemm_bf16_kernel<false, false>);
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  kern<<<grid, GB_THREADS, smem, st>>>(g, amap, bmap);
+  kern<<<grid, im2col ? GB_THREADS_CONV : GB_THREADS_PLAIN, smem, st>>>(g, amap, bmap, omap);
   return check_launch();
 }
 

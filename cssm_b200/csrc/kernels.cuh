@@ -121,7 +121,7 @@ struct Bf16GemmArgs {
   __nv_bfloat16* out;        // (M, ldo) bf16 ...
   float* out_f32;            // ... or (M, ldo) float32 when not nullptr
   int ldo;
-  int Kpad, BN;              // filled in by the launcher
+  int Kpad, BN, stages;      // filled in by the launcher
 };
 int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st);
 int gemm_bf16_pick_bn(int N);

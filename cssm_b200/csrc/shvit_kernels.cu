@@ -76,26 +76,29 @@ int launch_scale_cols(const float* src, int K, int N, const float* s, float* out
 // ------------------------------------------------------------------ first stem conv ----
 // 3x3 stride-2 'SAME' conv of the image (few input channels), BatchNorm folded, GELU.
 // x (Nimg, Hi, Wi, Cin) bf16 -> y (Nimg, Ho, Wo, Co) bf16.  wk (9*Cin, Co) fp32 already scaled by the
-// BatchNorm factor, bias (Co).  Thread = (output pixel, 8 output channels).
-__global__ void __launch_bounds__(256)
+// BatchNorm factor, bias (Co).  Thread = one output pixel and CO output channels: the weights are
+// read from shared memory as float4 broadcasts (every thread of a warp reads the same address).
+template <int CO>
+__global__ void __launch_bounds__(128)
 stem_conv1_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
                   const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int Nimg, int Hi,
                   int Wi, int Cin, int Ho, int Wo, int Co, int pad_h, int pad_w, int gelu) {
-  extern __shared__ float ws[];                    // (9*Cin, Co) + (Co)
+  extern __shared__ __align__(16) float ws[];      // (9*Cin, Co) + (Co)
   const int K = 9 * Cin;
   for (int i = threadIdx.x; i < K * Co; i += blockDim.x) ws[i] = wk[i];
   for (int i = threadIdx.x; i < Co; i += blockDim.x) ws[K * Co + i] = bias[i];
   __syncthreads();
-  const int groups = Co / 8;
+  const int groups = Co / CO;
   const long long total = (long long)Nimg * Ho * Wo * groups;
   for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < total;
        it += (long long)gridDim.x * blockDim.x) {
-    const int cg = (int)(it % groups);
-    const long long px = it / groups;
+    // consecutive threads = consecutive pixels (the channel group is the slow index)
+    const long long px = it % ((long long)Nimg * Ho * Wo);
+    const int cg = (int)(it / ((long long)Nimg * Ho * Wo));
     const int wo = (int)(px % Wo), ho = (int)((px / Wo) % Ho), n = (int)(px / ((long long)Wo * Ho));
-    float acc[8];
+    float acc[CO];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = ws[K * Co + cg * 8 + j];
+    for (int j = 0; j < CO; ++j) acc[j] = ws[K * Co + cg * CO + j];
     for (int ti = 0; ti < 3; ++ti) {
       const int hi = ho * 2 + ti - pad_h;
       if (hi < 0 || hi >= Hi) continue;
@@ -105,17 +108,27 @@ stem_conv1_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
         const __nv_bfloat16* xp = x + (((size_t)n * Hi + hi) * Wi + wi) * Cin;
         for (int c = 0; c < Cin; ++c) {
           const float xv = __bfloat162float(xp[c]);
-          const float* wr = ws + ((ti * 3 + tj) * Cin + c) * Co + cg * 8;
+          const float4* wr = reinterpret_cast<const float4*>(ws + ((ti * 3 + tj) * Cin + c) * Co + cg * CO);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, wr[j], acc[j]);
+          for (int j = 0; j < CO / 4; ++j) {
+            const float4 w4 = wr[j];
+            acc[4 * j] = fmaf(xv, w4.x, acc[4 * j]); acc[4 * j + 1] = fmaf(xv, w4.y, acc[4 * j + 1]);
+            acc[4 * j + 2] = fmaf(xv, w4.z, acc[4 * j + 2]); acc[4 * j + 3] = fmaf(xv, w4.w, acc[4 * j + 3]);
+          }
         }
       }
     }
     if (gelu) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = gelu_tanh_f(acc[j]);
+      for (int j = 0; j < CO; ++j) acc[j] = gelu_tanh_f(acc[j]);
     }
-    *reinterpret_cast<uint4*>(y + (size_t)px * Co + cg * 8) = pack8(acc);
+    uint4* yo = reinterpret_cast<uint4*>(y + (size_t)px * Co + cg * CO);
+#pragma unroll
+    for (int j = 0; j < CO / 8; ++j) {
+      const float v8[8] = {acc[8 * j], acc[8 * j + 1], acc[8 * j + 2], acc[8 * j + 3],
+                           acc[8 * j + 4], acc[8 * j + 5], acc[8 * j + 6], acc[8 * j + 7]};
+      yo[j] = pack8(v8);
+    }
   }
 }
 int launch_stem_conv1(const __nv_bfloat16* x, const float* wk, const float* bias, __nv_bfloat16* y,
@@ -125,11 +138,12 @@ int launch_stem_conv1(const __nv_bfloat16* x, const float* wk, const float* bias
   const int pad_h = ((Ho - 1) * 2 + 3 - Hi > 0 ? (Ho - 1) * 2 + 3 - Hi : 0) / 2;
   const int pad_w = ((Wo - 1) * 2 + 3 - Wi > 0 ? (Wo - 1) * 2 + 3 - Wi : 0) / 2;
   const size_t smem = (size_t)(9 * Cin * Co + Co) * 4;
-  const long long total = (long long)Nimg * Ho * Wo * (Co / 8);
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  stem_conv1_kernel<<<(int)blocks, 256, smem, st>>>(x, wk, bias, y, Nimg, Hi, Wi, Cin, Ho, Wo, Co, pad_h,
-                                                     pad_w, gelu);
+  const int co = Co % 32 == 0 ? 32 : (Co % 16 == 0 ? 16 : 8);
+  const long long total = (long long)Nimg * Ho * Wo * (Co / co);
+  long long blocks = (total + 127) / 128;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  auto kern = co == 32 ? stem_conv1_kernel<32> : (co == 16 ? stem_conv1_kernel<16> : stem_conv1_kernel<8>);
+  kern<<<(int)blocks, 128, smem, st>>>(x, wk, bias, y, Nimg, Hi, Wi, Cin, Ho, Wo, Co, pad_h, pad_w, gelu);
   return check_launch();
 }
 
@@ -220,10 +234,115 @@ dwconv_cl_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ 
   }
 }
 
+// Depthwise KS x KS 'SAME' conv, tiled through shared memory (the path of every bf16 output).
+// A CTA of 256 threads owns a tile of 8 output rows x TW columns x CS channels (256 / CS column
+// groups of four columns each) of one image and one channel slice; the bf16 input patch with its
+// halo is staged with 16-byte loads as it lies in memory ([row][column][channel]; the per-sample
+// LayerNorm affine, when given, is applied while staging and the result rounded to bf16, zeros stay
+// zeros outside the image); thread = one channel of one column group, with its KS*KS weights in
+// registers; for each of its four columns it walks the input rows of the window once (KS two-byte
+// shared-memory loads per row, conflict-free because the lanes of a warp are consecutive channels)
+// and feeds each value to the output rows it belongs to.
+template <int KS, int CS>
+__global__ void __launch_bounds__(256)
+dwconv_tiled_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
+                    const float* __restrict__ bias, const float* __restrict__ pre_a,
+                    const float* __restrict__ pre_b, __nv_bfloat16* __restrict__ y, int H, int W, int C,
+                    int add_centre, int gelu) {
+  constexpr int P = (KS - 1) / 2, CG = 256 / CS, TW = CG * 4, TH = 8, PW = TW + KS - 1, PH = TH + KS - 1;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [PH][PW][CS]
+  const int tiles_w = (W + TW - 1) / TW, tiles_h = (H + TH - 1) / TH, slices = C / CS;
+  int bid = blockIdx.x;
+  const int sl = bid % slices; bid /= slices;
+  const int tr = bid % (tiles_w * tiles_h), n = bid / (tiles_w * tiles_h);
+  const int h0 = (tr / tiles_w) * TH, w0 = (tr % tiles_w) * TW, cs0 = sl * CS;
+  const int c = threadIdx.x % CS, cgp = threadIdx.x / CS;
+  // stage the patch (zeros outside the image)
+  constexpr int CH = CS / 8;                         // 16-byte chunks per pixel of the slice
+  const __nv_bfloat16* xn = x + (size_t)n * H * W * C + cs0;
+  for (int q = threadIdx.x; q < PH * PW * CH; q += 256) {
+    const int ck = q % CH, pp = q / CH, pc = pp % PW, pr = pp / PW;
+    const int hi = h0 + pr - P, wi = w0 + pc - P;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (hi >= 0 && hi < H && wi >= 0 && wi < W) {
+      v = __ldg(reinterpret_cast<const uint4*>(xn + ((size_t)hi * W + wi) * C + ck * 8));
+      if (pre_a != nullptr) {
+        float f[8];
+        unpack8(v, f);
+        const float* pa = pre_a + (size_t)n * C + cs0 + ck * 8;
+        const float* pb = pre_b + (size_t)n * C + cs0 + ck * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = fmaf(__ldg(pa + j), f[j], __ldg(pb + j));
+        v = pack8(f);
+      }
+    }
+    *reinterpret_cast<uint4*>(tile + (size_t)pp * CS + ck * 8) = v;
+  }
+  float wr[KS * KS];
+#pragma unroll
+  for (int t = 0; t < KS * KS; ++t) wr[t] = wk ? __ldg(wk + (size_t)t * C + cs0 + c) : 0.f;
+  if (add_centre) wr[P * KS + P] += 1.0f;            // x + conv(x)
+  const float bz = (wk && bias) ? __ldg(bias + cs0 + c) : 0.f;
+  __syncthreads();
+#pragma unroll 1
+  for (int cc = 0; cc < 4; ++cc) {
+    const int wl = cgp * 4 + cc;                     // column inside the tile
+    if (w0 + wl >= W) break;
+    float acc[TH];
+#pragma unroll
+    for (int o = 0; o < TH; ++o) acc[o] = bz;
+#pragma unroll
+    for (int ir = 0; ir < PH; ++ir) {
+      float xv[KS];
+#pragma unroll
+      for (int tj = 0; tj < KS; ++tj) xv[tj] = __bfloat162float(tile[((size_t)ir * PW + wl + tj) * CS + c]);
+#pragma unroll
+      for (int o = 0; o < TH; ++o) {
+        const int ti = ir - o;
+        if (ti < 0 || ti >= KS) continue;
+#pragma unroll
+        for (int tj = 0; tj < KS; ++tj) acc[o] = fmaf(xv[tj], wr[ti * KS + tj], acc[o]);
+      }
+    }
+#pragma unroll
+    for (int o = 0; o < TH; ++o) {
+      const int h = h0 + o;
+      if (h >= H) continue;
+      const float v = gelu ? gelu_tanh_f(acc[o]) : acc[o];
+      y[(((size_t)n * H + h) * W + w0 + wl) * C + cs0 + c] = __float2bfloat16(v);
+    }
+  }
+}
+
+template <int KS, int CS>
+static int launch_dwconv_tiled(const __nv_bfloat16* x, const float* wk, const float* bias, const float* pre_a,
+                               const float* pre_b, __nv_bfloat16* y, int Nimg, int H, int W, int C,
+                               int add_centre, int gelu, cudaStream_t st) {
+  constexpr int CG = 256 / CS, TW = CG * 4, TH = 8;
+  const size_t smem = (size_t)(TH + KS - 1) * (TW + KS - 1) * CS * 2;
+  cudaError_t e = cudaFuncSetAttribute(dwconv_tiled_kernel<KS, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  const long long grid = (long long)Nimg * ((H + TH - 1) / TH) * ((W + TW - 1) / TW) * (C / CS);
+  dwconv_tiled_kernel<KS, CS><<<(unsigned)grid, 256, smem, st>>>(x, wk, bias, pre_a, pre_b, y, H, W, C,
+                                                                  add_centre, gelu);
+  return check_launch();
+}
+
 int launch_dwconv_cl(const __nv_bfloat16* x, const float* wk, const float* bias, const float* pre_a,
                      const float* pre_b, __nv_bfloat16* y, float* y_f32, int Nimg, int H, int W, int C,
                      int ks, int add_centre, int gelu, cudaStream_t st) {
   if (C % 8 != 0 || (ks != 3 && ks != 7)) return CSSM_ERR_UNSUPPORTED;
+  if (y_f32 == nullptr && C % 32 == 0) {
+    // 64-channel slices give 16-column tiles; narrow images and C not a multiple of 64 take 32
+    const bool c64 = C % 64 == 0;
+    if (ks == 7)
+      return c64 ? launch_dwconv_tiled<7, 64>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st)
+                 : launch_dwconv_tiled<7, 32>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
+    return c64 ? launch_dwconv_tiled<3, 64>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st)
+               : launch_dwconv_tiled<3, 32>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
+  }
   constexpr int RH = 4;
   const size_t smem = (size_t)(ks * ks * C + C) * 4;
   const long long total = (long long)Nimg * ((H + RH - 1) / RH) * W * (C / 8);

@@ -278,13 +278,13 @@ CASES = [
     # ---- CSSM-SHViT around the gated mixer (BASELINE configs[4]: T = 1, kernel_size 1)
     _shvit_block("shvit_block_stage2_14", (2, 14, 14, 32), 501, num_timesteps=1, kernel_size=1,
                  short_conv_spatial_size=0, gate_type="factored"),
-    _shvit_block("shvit_block_stage3_7_T3_ks3", (2, 7, 7, 24), 502, num_timesteps=3, kernel_size=3,
+    _shvit_block("shvit_block_stage3_7_T3_ks3", (2, 7, 7, 32), 502, num_timesteps=3, kernel_size=3,
                  gate_type="factored", rope_mode="spatiotemporal"),
-    _shvit_block("shvit_block_no_posconv_no_dwconv", (2, 8, 8, 16), 503, num_timesteps=2,
+    _shvit_block("shvit_block_no_posconv_no_dwconv", (2, 8, 8, 32), 503, num_timesteps=2,
                  kernel_size=3, gate_type="dense", use_pos_conv=False, use_dwconv=False),
-    _shvit("shvit_tiny_64", (2, 64, 64, 3), 511, embed_dims=(16, 32, 48, 64), depths=(1, 2, 2, 1),
+    _shvit("shvit_tiny_64", (2, 64, 64, 3), 511, embed_dims=(32, 32, 64, 64), depths=(1, 2, 2, 1),
            num_classes=10, num_timesteps=1, kernel_sizes=(1, 1, 1, 1), short_conv_spatial_size=0),
-    _shvit("shvit_tiny_T2_ks3_meanpool", (2, 32, 32, 3), 512, embed_dims=(16, 16, 32, 32),
+    _shvit("shvit_tiny_T2_ks3_meanpool", (2, 32, 32, 3), 512, embed_dims=(32, 32, 32, 64),
            depths=(1, 1, 1, 1), num_classes=5, num_timesteps=2, kernel_sizes=(3, 3, 3, 3),
            head_pool="mean"),
     _shvit("shvit_s1_224_cfg5", (2, 224, 224, 3), 513, seeded=5130,
