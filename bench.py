@@ -1,18 +1,21 @@
-"""Benchmark of the CSSM spectral-block forward on B200 (model-level images/s, block stage times,
-roofline of the fused spectral kernel, end-to-end figure through the host-buffer entry point).
+"""Benchmark of the CSSM spectral-block forward on B200: model-level images/s, per-kernel / per-stage
+CUDA-event times, roofline of the dominant kernel, end-to-end figure through the host-buffer entry
+points, CPU restatement beside it.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload cfg2]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
 
-One step = one forward over one per-GPU batch of synthetic inputs of the workload's model: the
-reference's SimpleCSSM wrapper (stem -> spectral block + residual -> last-frame readout) around
-one GatedCSSM or GatedDeltaNetCSSM block.  Prints ONE JSON line (rank 0):
-  value     images/s, images resident on the device, all T output frames of the block computed
-  e2e       the same through cssm_simple_forward_host: pinned host images in, host logits out
-  block     the block alone on its (B,T,H,W,C) input: per-stage CUDA-event times
-  roofline  the fused spectral kernel: algorithmic bytes / its CUDA-event time, vs measured peak
-  last_frame_only   the same model with the block evaluated through its last-frame-only entry
-  cpu_baseline      the CPU restatement of the same model on the host cores (JAX cannot be
-                    installed here, so the reference itself cannot run)
+One step = one forward of the workload's model over one per-GPU batch of seeded synthetic inputs.
+Without --workload the headline is cfg5 (BASELINE.json configs[4], the configuration the metric
+"fwd images/s at 1/2/4/8 B200" names: CSSM-SHViT s1, gated mixers at T = 1, bf16, batch 512 per GPU)
+and the SimpleCSSM workloads cfg2 / cfg3 / cfg4 (configs[1..3], fp32) run after it and are reported
+under "workloads" in the same JSON line (rank 0 prints ONE line):
+  value     images/s, inputs resident on the device, CUDA events around the K timed steps
+  e2e       the same through the host-buffer entry point: pinned host inputs in, host logits out
+  roofline  the dominant kernel: algorithmic bytes / its CUDA-event time, vs the measured HBM peak
+  kernels / block / stage_ms   per-kernel (cfg5: launch trace) or per-stage (SimpleCSSM) event times
+  sustained the headline loop repeated for >= 2 s, with the median SM clock seen
+  cpu_baseline   the CPU restatement of the same model on the host cores (JAX cannot be installed
+                 here, so the reference itself cannot run)
 """
 from __future__ import annotations
 
@@ -64,11 +67,24 @@ WORKLOADS = {
                             pool_type="max", pos_embed="spatiotemporal"),
                  B=128, data="dots"),
 }
+# BASELINE.json configs[4]: CSSM-SHViT s1, gated mixers at T = 1, kernel_size 1 (no spatial short conv),
+# 1000 classes, bf16, batch 512 per GPU of 224x224x3 N(0,1) images
+_SHVIT = dict(num_classes=1000, embed_dims=(64, 128, 256, 384), depths=(1, 2, 2, 1), num_timesteps=1,
+              kernel_sizes=(1, 1, 1, 1), short_conv_size=4, short_conv_spatial_size=0, gate_type="factored")
+WORKLOADS["cfg5"] = dict(kind="shvit", model=_SHVIT, B=512, data="gaussian", hw=224)
+# the same model at a size for profiler captures (stage-0 activations 13 MB per tensor... x 32 images)
+WORKLOADS["cfg5_small"] = dict(kind="shvit", model=_SHVIT, B=64, data="gaussian", hw=224)
 GATED_STAGES = ["in_proj", "short_conv", "gates", "spectral", "out_proj"]
 GDN_STAGES = ["dwconv_ctx", "qkv_proj", "gate_proj", "gates", "short_convs", "spectral", "out_proj"]
 
 
+def is_shvit(workload):
+    return WORKLOADS[workload].get("kind") == "shvit"
+
+
 def metric_name(workload):
+    if is_shvit(workload):
+        return f"fwd images/s (CSSM-SHViT s1, gated mixers, bf16, {workload})"
     return f"fwd images/s (SimpleCSSM {WORKLOADS[workload]['model']['cssm_type']} model, {workload})"
 
 
@@ -78,9 +94,13 @@ def make_model(workload):
 
 
 def make_inputs(workload, n, seed0):
-    """Seeded synthetic inputs: dashed-stroke images (B,128,128,1) or random-walk dot clips
-    (B,32,32,32,3)."""
+    """Seeded synthetic inputs: dashed-stroke images (B,128,128,1), random-walk dot clips
+    (B,32,32,32,3) or N(0,1) images (B,224,224,3) (stand-ins for Pathfinder / PathTracker / ImageNet)."""
     from cssm_b200 import synth
+    if WORKLOADS[workload]["data"] == "gaussian":
+        import numpy as np
+        hw = WORKLOADS[workload]["hw"]
+        return np.random.default_rng(seed0).standard_normal((n, hw, hw, 3), dtype=np.float32)
     if WORKLOADS[workload]["data"] == "strokes":
         return synth.stroke_batch(n, seed0=seed0)
     return synth.dot_clips(n, seed0=seed0)
@@ -174,6 +194,22 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def shvit_model_kwargs(workload):
+    """Keyword arguments of oracle.shvit_oracle / cssm_torch_cpu for a CSSM-SHViT workload."""
+    m = WORKLOADS[workload]["model"]
+    return {k: m[k] for k in ("embed_dims", "depths", "num_timesteps", "kernel_sizes", "short_conv_size",
+                              "short_conv_spatial_size", "gate_type")}
+
+
+def shvit_params(workload, seed=0):
+    from oracle import shvit_oracle as sv
+    m, hw = WORKLOADS[workload]["model"], WORKLOADS[workload]["hw"]
+    return sv.init_shvit_params(seed, (hw, hw), embed_dims=m["embed_dims"], depths=m["depths"],
+                                kernel_sizes=m["kernel_sizes"], num_classes=m["num_classes"],
+                                gate_type=m["gate_type"], short_conv_size=m["short_conv_size"],
+                                short_conv_spatial_size=m["short_conv_spatial_size"])
+
+
 def cpu_model_rate(workload, sample_b, reps=1):
     """images/s of the CPU restatement of the workload's model (torch-CPU, all host threads) on
     `sample_b` inputs.  Returns (images/s, seconds per repetition, threads)."""
@@ -186,6 +222,17 @@ def cpu_model_rate(workload, sample_b, reps=1):
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     except (AttributeError, OSError):
         torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if is_shvit(workload):
+        p, st = shvit_params(workload)
+        kw = shvit_model_kwargs(workload)
+        xt = torch.from_numpy(make_inputs(workload, sample_b, seed0=3000))
+        with torch.no_grad():
+            tc.shvit_forward_torch(p, st, xt[:1], **kw)          # touch code paths once
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                tc.shvit_forward_torch(p, st, xt, **kw)
+            dt = (time.perf_counter() - t0) / reps
+        return sample_b / dt, dt, torch.get_num_threads()
     m = make_model(workload)
     x = make_inputs(workload, sample_b, seed0=3000)
     H, W = m.feature_hw(x.shape[-3], x.shape[-2])
@@ -210,6 +257,8 @@ def cpu_model_rate(workload, sample_b, reps=1):
 
 def cpu_sample_size(workload):
     """Inputs per CPU step, sized so that a step takes seconds, not minutes."""
+    if is_shvit(workload):
+        return 64
     return 4 if WORKLOADS[workload]["model"]["cssm_type"] == "gdn" else 16
 
 
@@ -226,12 +275,13 @@ def run_reference(args, rank):
             times.append(dt)
     ms = 1e3 * sum(times) / len(times)
     value = sample_b / (ms / 1e3)
-    sample = (f"{sample_b} inputs of the {args.workload} model per step, torch-CPU restatement of "
-              f"the reference model (stem on all B*T frames, all T block frames)")
+    sample = (f"{sample_b} inputs of the {args.workload} model per step, torch-CPU (float32) restatement "
+              f"of the reference model (all T frames computed as the reference does)")
     print(json.dumps({
         "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if is_shvit(args.workload) else "f32",
         "data": "synthetic", "config": {"workload": args.workload, "sample_batch": sample_b},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port",
                          "sample": sample},
@@ -324,43 +374,134 @@ def block_stage_times(bound, feat5, steps, dev, st):
     return stage, sum(stage.values())
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
-    ap.add_argument("--strong", action="store_true",
-                    help="strong scaling: the workload's batch is the GLOBAL batch, split evenly "
-                         "over the ranks (default: weak scaling, that batch per GPU)")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-cpu", action="store_true")
-    args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        run_reference(args, rank)
-        return
+def run_shvit(args, name, ctx):
+    """One CSSM-SHViT workload: device-timed model steps, launch trace (per-kernel times and
+    algorithmic bytes), end to end through the host entry point, CPU restatement."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from cssm_b200 import CSSMSHViT, shard
+    dev, st, world, rank = ctx["dev"], ctx["st"], ctx["world"], ctx["rank"]
+    wl = WORKLOADS[name]
+    B = wl["B"]
+    model = CSSMSHViT(**wl["model"])
+    p, stats = shvit_params(name)
+    bound = model.bind({"params": p, "batch_stats": stats}, dev)
+    x_host = torch.from_numpy(make_inputs(name, B, seed0=1000 + B * rank)).to(torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+    K = model.num_classes
+    logits = torch.empty((B, K), dtype=torch.float32, device=dev)
+    gathered = torch.empty((world * B, K), dtype=torch.float32, device=dev)
 
+    def model_step():
+        bound(x, out=logits)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, logits)
+
+    for _ in range(args.warmup):
+        model_step()
+    ctx["barrier"]()
+    total_ms = time_region(model_step, args.steps, dev, st)
+    ctx["barrier"]()
+    ms_step = total_ms / args.steps
+    value = world * B * args.steps / (total_ms / 1e3)
+
+    # per-kernel times from launch traces of the same forward
+    agg, nl = {}, 0
+    reps = max(3, min(args.steps, 10))
+    for _ in range(reps):
+        _, launches = bound.forward_traced(x, out=logits)
+        nl = len(launches)
+        for kind, ms, nbytes in launches:
+            a = agg.setdefault(kind, [0, 0.0, 0.0])
+            a[0] += 1; a[1] += ms; a[2] += nbytes
+    peak, peak_src = peaks()
+    kernels = {k: {"launches_per_step": a[0] // reps, "ms_per_step": a[1] / reps,
+                   "algorithmic_bytes_per_step": a[2] / reps,
+                   "achieved_GBps": (a[2] / reps) / (a[1] / reps / 1e3) / 1e9 if a[1] > 0 else None}
+               for k, a in sorted(agg.items(), key=lambda kv: -kv[1][1])}
+    top = next(iter(kernels))
+    tk = kernels[top]
+    kname = {"gemm": "gemm_bf16_kernel<false>", "conv_gemm": "gemm_bf16_kernel<true>",
+             "dwconv7": "dwconv_tiled_kernel<7>", "dwconv3": "dwconv_tiled_kernel<3>",
+             "layernorm": "layernorm_cl_kernel", "stem_conv": "stem_conv1_kernel",
+             "spectral": "gated_spectral_cl_kernel"}.get(top, top)
+    roofline = {"bound": "hbm", "kernel": kname, "achieved": tk["achieved_GBps"], "peak": peak,
+                "peak_source": peak_src, "unit": "GB/s", "frac": tk["achieved_GBps"] / peak,
+                "frac_of_nominal_8TBps": tk["achieved_GBps"] / 8000.0, "traffic": None,
+                "algorithmic_bytes_per_launch": tk["algorithmic_bytes_per_step"] / tk["launches_per_step"],
+                "ms_per_launch": tk["ms_per_step"] / tk["launches_per_step"],
+                "launches_per_step": tk["launches_per_step"],
+                "note": "all launches of the kernel in one step: sum of algorithmic bytes / sum of event times"}
+    tr = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tr):
+        with open(tr) as f:
+            tj = json.load(f)
+        per_img = tj.get(f"cfg5_{top}_dram_bytes_per_image")
+        if per_img:
+            roofline["traffic"] = per_img * B / tk["launches_per_step"]
+    total_bytes = sum(k["algorithmic_bytes_per_step"] for k in kernels.values())
+    model_hbm = {"algorithmic_bytes": total_bytes, "achieved": total_bytes / (ms_step / 1e3) / 1e9,
+                 "unit": "GB/s", "frac": total_bytes / (ms_step / 1e3) / 1e9 / peak, "peak": peak,
+                 "formula": "sum over the step's launches of inputs + outputs + weights"}
+
+    e2e = None
+    if not args.no_e2e:
+        lh = torch.empty((B, K), dtype=torch.float32).pin_memory()
+        for _ in range(max(1, min(args.warmup, 3))):
+            bound.forward_host(x_host, lh)
+        ctx["barrier"]()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            bound.forward_host(x_host, lh)             # returns after the logits arrived
+        dt = shard.max_over_ranks(time.perf_counter() - t0, dev)
+        e2e = {"value": world * B * args.steps / dt, "unit": "images/s",
+               "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": lh.numel() * 4,
+               "ms_per_step": 1e3 * dt / args.steps}
+
+    sustained = None
+    if ctx.get("sustain"):
+        # the same loop for at least two seconds: the clock under sustained load, not a burst
+        n_rep = max(1, int(2000.0 / max(ms_step * args.steps, 1e-3)) + 1)
+        with ClockSampler(ctx["local"]) as cs:
+            sus_ms = time_region(model_step, n_rep * args.steps, dev, st)
+        sustained = {"value": world * B * n_rep * args.steps / (sus_ms / 1e3), "unit": "images/s",
+                     "ms_per_step": sus_ms / (n_rep * args.steps), "seconds": sus_ms / 1e3,
+                     "clocks": cs.summary()}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sb = min(cpu_sample_size(name), B)
+        rate, dt, cores = cpu_model_rate(name, sb, reps=8)
+        cpu = {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
+               "sample": f"{sb} inputs of the {name} model, 8 repetitions ({dt:.2f} s each), torch-CPU "
+                         f"(float32) restatement of the reference model"}
+    m = wl["model"]
+    return {
+        "metric": metric_name(name), "value": value, "unit": "images/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, "model": "CSSM-SHViT s1 (embed_dims 64/128/256/384, depths 1/2/2/1)",
+                   "block": "gated", "per_gpu_batch": B, "input": [wl["hw"], wl["hw"], 3],
+                   "T": m["num_timesteps"], "kernel_sizes": list(m["kernel_sizes"]),
+                   "gate_type": m["gate_type"], "num_classes": K,
+                   "collective": "all-gather of the logits per step" if world > 1 else None,
+                   "l2": "stage-0/1 activations (205 / 103 MB per tensor at batch 512) larger than the 126 MB L2"},
+        "kernels": kernels, "roofline": roofline, "model_hbm": model_hbm, "sustained": sustained,
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": nl * args.steps,
+    }
+
+
+def run_simple(args, name, ctx):
+    """One SimpleCSSM workload (cfg1..cfg4): device-timed model steps, last-frame-only variant,
+    per-stage block times, roofline of the fused spectral kernel, end to end, CPU restatement."""
     import numpy as np
     import torch
     import torch.distributed as dist
     from cssm_b200 import shard
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: cssm_b200 has no CPU path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        # keep stdout to the one JSON line: NCCL prints a version banner there at the VERSION, WARN
-        # and INFO levels (an unrecognised level name means "none")
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "WARN", "INFO"):
-            os.environ["NCCL_DEBUG"] = "NONE"
-        dist.init_process_group("nccl", device_id=dev)
-    st = torch.cuda.current_stream(dev)
+    dev, st, world, rank = ctx["dev"], ctx["st"], ctx["world"], ctx["rank"]
+    wl = WORKLOADS[name]
+    barrier = ctx["barrier"]
 
     # model, weights, inputs (disjoint seeds per rank: every rank works on its own shard)
     B = wl["B"]
@@ -368,8 +509,8 @@ def main():
         if B % world:
             raise SystemExit(f"--strong: batch {B} does not divide over {world} ranks")
         B //= world
-    model = make_model(args.workload)
-    x_np = make_inputs(args.workload, B, seed0=1000 + B * rank)
+    model = make_model(name)
+    x_np = make_inputs(name, B, seed0=1000 + B * rank)
     variables = model.init(0, x_np.shape)
     bound = model.bind(variables, dev)
     x_host = torch.from_numpy(np.ascontiguousarray(x_np)).pin_memory()
@@ -381,11 +522,6 @@ def main():
     gdn = model.cssm_type == "gdn"
     n_stem = 1 if model.stem_mode == "pathtracker" else model.stem_layers
     launches_per_step = n_stem + (9 if gdn else 5) + 2
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
 
     gathered = torch.empty((world * B, model.num_classes), dtype=torch.float32, device=dev)
 
@@ -400,9 +536,7 @@ def main():
     for _ in range(args.warmup):
         model_step()
     barrier()
-    clk = ClockSampler(local)
-    clk.__enter__()                       # sampled over the device-timed and the e2e regions
-    # ---- headline: images on the device -> logits, all T block frames computed ----
+    # ---- images on the device -> logits, all T block frames computed ----
     total_ms = time_region(model_step, args.steps, dev, st)
     barrier()
     ms_step = total_ms / args.steps
@@ -468,38 +602,120 @@ def main():
                "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": lh.numel() * 4,
                "ms_per_step": 1e3 * dt / args.steps,
                "last_frame_only_value": world * B * args.steps / dt_last}
-    clk.__exit__(None, None, None)
+
+    sustained = None
+    if ctx.get("sustain"):
+        n_rep = max(1, int(2000.0 / max(ms_step * args.steps, 1e-3)) + 1)
+        with ClockSampler(ctx["local"]) as cs:
+            sus_ms = time_region(model_step, n_rep * args.steps, dev, st)
+        sustained = {"value": world * B * n_rep * args.steps / (sus_ms / 1e3), "unit": "images/s",
+                     "ms_per_step": sus_ms / (n_rep * args.steps), "seconds": sus_ms / 1e3,
+                     "clocks": cs.summary()}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        sb = min(cpu_sample_size(args.workload), B)
+        sb = min(cpu_sample_size(name), B)
         reps = 4 if gdn else 8
-        rate, dt, cores = cpu_model_rate(args.workload, sb, reps=reps)
+        rate, dt, cores = cpu_model_rate(name, sb, reps=reps)
         cpu = {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
-               "sample": f"{sb} inputs of the {args.workload} model, {reps} repetitions ({dt:.2f} s "
+               "sample": f"{sb} inputs of the {name} model, {reps} repetitions ({dt:.2f} s "
                          f"each), torch-CPU restatement of the reference model"}
 
+    return {
+        "metric": metric_name(name), "value": value, "unit": "images/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong" if args.strong else "weak",
+        "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": name, "model": "SimpleCSSM depth 1", "block": model.cssm_type,
+                   "per_gpu_batch": B, "input": list(x.shape[1:]), "T": T, "H": H, "W": W, "C": Cc,
+                   "kernel_size": model.kernel_size, "gate_type": model.gate_type,
+                   "pos_embed": model.pos_embed, "stem": model.stem_mode, "pool": model.pool_type,
+                   "collective": "all-gather of the logits per step" if world > 1 else None,
+                   "l2": "block activations (1.07 GB per tensor at cfg2-4) larger than the 126 MB L2"},
+        "block": {"ms_per_step": block_ms, "stage_ms": stage_ms, "stem_ms": stem_ms, "hbm": block_hbm,
+                  "value": world * B / (block_ms / 1e3), "unit": "images/s"},
+        "stage_ms": stage_ms, "roofline": roofline,
+        "last_frame_only": {"ms_per_step": last_ms, "value": world * B / (last_ms / 1e3),
+                            "unit": "images/s"},
+        "sustained": sustained, "cpu_baseline": cpu, "e2e": e2e,
+        "gpu_launches": launches_per_step * args.steps,
+    }
+
+
+HEADLINE = "cfg5"
+ALSO = ["cfg2", "cfg3", "cfg4"]          # reported under "workloads" when no --workload is given
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help=f"one workload only (default: {HEADLINE} as the headline, then {', '.join(ALSO)})")
+    ap.add_argument("--strong", action="store_true",
+                    help="SimpleCSSM workloads: the workload's batch is the GLOBAL batch, split evenly "
+                         "over the ranks (default: weak scaling, that batch per GPU)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    single = args.workload is not None
+    if not single:
+        args.workload = HEADLINE
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: cssm_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        # stdout carries the one JSON line: whatever NCCL logs (at the level the environment asked
+        # for) goes to stderr unless the environment already names a file for it
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=dev)
+    st = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    ctx = dict(dev=dev, st=st, world=world, rank=rank, local=local, barrier=barrier, sustain=True)
+    run = lambda name: (run_shvit if is_shvit(name) else run_simple)(args, name, ctx)
+    clk = ClockSampler(local)
+    clk.__enter__()                       # sampled over the headline's timed regions
+    line = run(args.workload)
+    clk.__exit__(None, None, None)
+    line["clocks"] = clk.summary()
+    if not single and not args.strong:
+        ctx["sustain"] = False
+        line["workloads"] = {}
+        for name in ALSO:
+            r = run(name)
+            line["workloads"][name] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype",
+                                                        "config", "stage_ms", "block", "roofline",
+                                                        "last_frame_only", "cpu_baseline", "e2e",
+                                                        "gpu_launches") if k in r}
+        if world > 1:
+            # strong scaling of cfg2 beside the weak-scaling figures: its batch of 128 split over the ranks
+            args.strong = True
+            no_e2e, args.no_e2e = args.no_e2e, True
+            r = run_simple(args, "cfg2", ctx)
+            args.strong, args.no_e2e = False, no_e2e
+            line["strong_scaling_cfg2"] = {"value": r["value"], "unit": "images/s", "ms_per_step": r["ms_per_step"],
+                                           "global_batch": WORKLOADS["cfg2"]["B"], "n_gpus": world}
     if rank == 0:
-        print(json.dumps({
-            "metric": metric_name(args.workload), "value": value, "unit": "images/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "strong" if args.strong else "weak",
-            "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "model": "SimpleCSSM depth 1", "block": model.cssm_type,
-                       "per_gpu_batch": B, "input": list(x.shape[1:]), "T": T, "H": H, "W": W, "C": Cc,
-                       "kernel_size": model.kernel_size, "gate_type": model.gate_type,
-                       "pos_embed": model.pos_embed, "stem": model.stem_mode, "pool": model.pool_type,
-                       "collective": "all-gather of the logits per step" if world > 1 else None,
-                       "l2": "block activations (1.07 GB per tensor at cfg2-4) larger than the 126 MB L2"},
-            "block": {"ms_per_step": block_ms, "stage_ms": stage_ms, "stem_ms": stem_ms, "hbm": block_hbm,
-                      "value": world * B / (block_ms / 1e3), "unit": "images/s"},
-            "stage_ms": stage_ms, "roofline": roofline,
-            "last_frame_only": {"ms_per_step": last_ms, "value": world * B / (last_ms / 1e3),
-                                "unit": "images/s"},
-            "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary(),
-        }))
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 

@@ -81,6 +81,15 @@ class ShvitWeights(C.Structure):
                 ("head_kernel", C.c_void_p), ("head_bias", C.c_void_p)]
 
 
+class ShvitTrace(C.Structure):
+    _fields_ = [("events", C.POINTER(C.c_void_p)), ("kinds", C.POINTER(C.c_int32)),
+                ("bytes", C.POINTER(C.c_double)), ("capacity", C.c_int32), ("count", C.c_int32)]
+
+
+SHVIT_KINDS = ["stem_conv", "conv_gemm", "gemm", "layernorm", "dwconv7", "dwconv3", "sample_norm",
+               "plane_sum", "gates", "spectral", "pool", "head", "mixer_f32", "add_res", "end"]
+
+
 class GatedWsLayout(C.Structure):
     _fields_ = [("xz_planar", C.c_size_t), ("ctx_sum", C.c_size_t),
                 ("gate_maps", C.c_size_t), ("total", C.c_size_t)]
@@ -234,6 +243,8 @@ SIGNATURES = {
     "cssm_shvit_plan_init": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, C.c_size_t, _P]),
     "cssm_shvit_forward": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
                                      C.c_size_t, _P]),
+    "cssm_shvit_forward_timed": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
+                                           C.c_size_t, _P, C.POINTER(ShvitTrace)]),
     "cssm_shvit_host_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
     "cssm_shvit_forward_host": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
                                           C.c_size_t, _P]),

@@ -101,6 +101,19 @@ static BlockWs block_ws_layout(const cssm_shvit_block_desc& d) {
   return l;
 }
 
+// Launch trace of the call in progress on this thread (cssm_shvit_forward_timed sets it for the
+// duration of its own call): before every kernel launch an event is recorded on the stream and the
+// kernel kind and the algorithmic bytes of the launch (inputs + outputs + weights) are noted.
+static thread_local cssm_shvit_trace* g_trace = nullptr;
+static inline void trace(int kind, double bytes, cudaStream_t st) {
+  cssm_shvit_trace* t = g_trace;
+  if (t == nullptr || t->count >= t->capacity) return;
+  cudaEventRecord(reinterpret_cast<cudaEvent_t>(t->events[t->count]), st);
+  t->kinds[t->count] = kind;
+  t->bytes[t->count] = bytes;
+  ++t->count;
+}
+
 static int gemm_plain(const __nv_bfloat16* A, int M, int K, const __nv_bfloat16* Wt, int N, const float* bias,
                       int act, const __nv_bfloat16* res, __nv_bfloat16* out, cudaStream_t st) {
   Bf16GemmArgs g;
@@ -108,6 +121,7 @@ static int gemm_plain(const __nv_bfloat16* A, int M, int K, const __nv_bfloat16*
   g.A = A; g.M = M; g.N = N; g.K = K; g.lda = K;
   g.Wt = Wt; g.ldw = packed_ld(K); g.bias = bias; g.act = act;
   g.res = res; g.ldr = N; g.out = out; g.ldo = N;
+  trace(CSSM_SHVIT_K_GEMM, 2.0 * ((double)M * K + (double)M * N * (res ? 2 : 1) + (double)N * K), st);
   return launch_gemm_bf16(g, st);
 }
 
@@ -122,6 +136,7 @@ static int conv_s2(const __nv_bfloat16* x, int B, int Hi, int Wi, int Cin, const
   g.pad_h = (th > 0 ? th : 0) / 2; g.pad_w = (tw > 0 ? tw : 0) / 2;
   g.Wt = Wt; g.ldw = packed_ld(9 * Cin); g.bias = bias; g.act = act;
   g.out = out; g.ldo = Cout;
+  trace(CSSM_SHVIT_K_CONV_GEMM, 2.0 * ((double)B * Hi * Wi * Cin + (double)g.M * Cout + 9.0 * Cin * Cout), st);
   return launch_gemm_bf16(g, st);
 }
 
@@ -181,20 +196,25 @@ static int block_forward(const cssm_shvit_block_desc& d, const cssm_shvit_block_
   const __nv_bfloat16* fc2 = (const __nv_bfloat16*)(plan + p.fc2);
   if (!d.is_cssm) {
     // LN -> dw7x7 -> gelu -> Dense + residual
+    trace(CSSM_SHVIT_K_LAYERNORM, 4.0 * M * C, st);
     CSSM_RUN(launch_layernorm_cl(x, w.norm1_scale, w.norm1_bias, T, M, C, st));
+    trace(CSSM_SHVIT_K_DWCONV7, 4.0 * M * C, st);
     CSSM_RUN(launch_dwconv_cl(T, w.dw_kernel, w.dw_bias, nullptr, nullptr, HB, nullptr, d.B, d.H, d.W, C, 7, 0, 1, st));
     CSSM_RUN(gemm_plain(HB, M, C, (const __nv_bfloat16*)(plan + p.pw), C, w.pw_bias, 0, x, X1, st));
   } else {
     float* na = (float*)(ws + l.na);
     float* nb = (float*)(ws + l.nb);
     // LayerNorm over (T,H,W,C) of the repeated image = over (H,W,C) of the image; x + dw3x3(x)
+    trace(CSSM_SHVIT_K_SAMPLE_NORM, 2.0 * M * C, st);
     CSSM_RUN(launch_sample_norm(x, w.norm1_scale, w.norm1_bias, na, nb, d.B, d.H * d.W * C, C, st));
+    trace(CSSM_SHVIT_K_DWCONV3, (mixer_fast(d) ? 4.0 : 6.0) * M * C, st);
     if (mixer_fast(d)) {
       CSSM_RUN(launch_dwconv_cl(x, d.use_pos_conv ? w.dw_kernel : nullptr, w.dw_bias, na, nb, T, nullptr, d.B,
                                 d.H, d.W, C, 3, 1, 0, st));
       const float* inb = (const float*)(plan + p.inp_bias);
       CSSM_RUN(gemm_plain(T, M, C, (const __nv_bfloat16*)(plan + p.inp), 2 * C, inb, 2, nullptr, HB, st));
       float* ctx = (float*)(ws + l.ctx);
+      trace(CSSM_SHVIT_K_PLANE_SUM, 2.0 * M * C, st);
       CSSM_RUN(launch_plane_sum_cl(HB, 2 * C, d.B, d.H * d.W, C, ctx, st));
       GatedGateArgs ga;
       memset(&ga, 0, sizeof(ga));
@@ -202,7 +222,9 @@ static int block_forward(const cssm_shvit_block_desc& d, const cssm_shvit_block_
       ga.act = d.gate_activation; ga.path = PATH_GENERIC;
       for (int i = 0; i < 6; ++i) { ga.gk[i] = w.cssm.gate_kernel[i]; ga.gb[i] = w.cssm.gate_bias[i]; }
       ga.maps = (float4*)(ws + l.maps);
+      trace(CSSM_SHVIT_K_GATES, 16.0 * d.B * d.H * (d.W / 2 + 1), st);
       CSSM_RUN(launch_gated_gates(ga, st));
+      trace(CSSM_SHVIT_K_SPECTRAL, 6.0 * M * C, st);          // x_main, z in; y out (bf16)
       CSSM_RUN(launch_gated_spectral_cl(HB, 2 * C, d.B, d.H, d.W, C, (const float*)(ws + l.maps), T, C, st));
       CSSM_RUN(gemm_plain(T, M, C, (const __nv_bfloat16*)(plan + p.outp), C, w.cssm.out_proj_bias, 0, x, X1, st));
     } else {
@@ -212,16 +234,20 @@ static int block_forward(const cssm_shvit_block_desc& d, const cssm_shvit_block_
                                 d.H, d.W, C, 3, 1, 0, st));
       const cssm_gated_desc g = mixer_desc(d);
       // identical frames in (x_bcast), only the last frame out
+      trace(CSSM_SHVIT_K_MIXER_F32, 8.0 * M * C, st);
       CSSM_RUN(gated_forward_internal(&g, &w.cssm, plan + p.gplan, x32, y32, ws + l.gws, l.gws_bytes, st, 1, 1));
+      trace(CSSM_SHVIT_K_ADD_RES, 8.0 * M * C, st);
       CSSM_RUN(launch_add_res(x, y32, X1, (long long)M * C, st));
     }
   }
   // LN -> fc1 -> gelu -> [h + dw3x3(h)] -> fc2 + residual
+  trace(CSSM_SHVIT_K_LAYERNORM, 4.0 * M * C, st);
   CSSM_RUN(launch_layernorm_cl(X1, w.norm2_scale, w.norm2_bias, T, M, C, st));
   CSSM_RUN(gemm_plain(T, M, C, fc1, Hd, w.fc1_bias, 1, nullptr, HB, st));
   const __nv_bfloat16* h = HB;
   if (d.is_cssm && d.use_dwconv) {
     __nv_bfloat16* H2 = (__nv_bfloat16*)(ws + l.hid2);
+    trace(CSSM_SHVIT_K_DWCONV3, 4.0 * M * Hd, st);
     CSSM_RUN(launch_dwconv_cl(HB, w.mlp_dw_kernel, w.mlp_dw_bias, nullptr, nullptr, H2, nullptr, d.B, d.H, d.W, Hd,
                               3, 1, 0, st));
     h = H2;
@@ -330,6 +356,7 @@ static int model_forward(const cssm_shvit_desc& d, const cssm_shvit_weights& w, 
   const int E0 = d.embed_dims[0];
   const int H1 = (d.H + 1) / 2, W1 = (d.W + 1) / 2;
   // patch embed: ConvBN -> gelu -> ConvBN
+  trace(CSSM_SHVIT_K_STEM_CONV, 2.0 * ((double)d.B * d.H * d.W * d.Cin + (double)d.B * H1 * W1 * (E0 / 2)), st);
   CSSM_RUN(launch_stem_conv1(x, (const float*)(plan + m.plan.c1w), (const float*)(plan + m.plan.c1b), A, d.B, d.H,
                              d.W, d.Cin, E0 / 2, 1, st));
   CSSM_RUN(conv_s2(A, d.B, H1, W1, E0 / 2, (const __nv_bfloat16*)(plan + m.plan.c2w), E0,
@@ -350,10 +377,15 @@ static int model_forward(const cssm_shvit_desc& d, const cssm_shvit_weights& w, 
     }
   }
   const int C3 = d.embed_dims[3], P3 = m.Hs[3] * m.Ws[3];
+  trace(CSSM_SHVIT_K_LAYERNORM, 4.0 * d.B * P3 * C3, st);
   CSSM_RUN(launch_layernorm_cl(cur, w.norm_scale, w.norm_bias, other, (long long)d.B * P3, C3, st));
   float* pooled = (float*)(ws + m.ws.pooled);
+  trace(CSSM_SHVIT_K_POOL, 2.0 * d.B * P3 * C3, st);
   CSSM_RUN(launch_pool_cl(other, d.B, P3, C3, d.head_pool == 0 ? 1 : 0, pooled, st));
-  return launch_head(pooled, w.head_kernel, w.head_bias, logits, d.B, C3, d.num_classes, st);
+  trace(CSSM_SHVIT_K_HEAD, 4.0 * ((double)d.B * C3 + (double)d.B * d.num_classes + (double)C3 * d.num_classes), st);
+  CSSM_RUN(launch_head(pooled, w.head_kernel, w.head_bias, logits, d.B, C3, d.num_classes, st));
+  trace(CSSM_SHVIT_K_END, 0.0, st);
+  return CSSM_OK;
 }
 
 }  // namespace cssm
@@ -449,31 +481,100 @@ int cssm_shvit_forward(const cssm_shvit_desc* d, const cssm_shvit_weights* w, co
                        (cudaStream_t)stream);
 }
 
+int cssm_shvit_forward_timed(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
+                             const void* x_bf16, float* logits, void* workspace, size_t workspace_bytes,
+                             void* stream, cssm_shvit_trace* tr) {
+  if (!tr || !tr->events || !tr->kinds || !tr->bytes || tr->capacity <= 0) return CSSM_ERR_NULL;
+  tr->count = 0;
+  g_trace = tr;
+  const int s = cssm_shvit_forward(d, w, plan, x_bf16, logits, workspace, workspace_bytes, stream);
+  g_trace = nullptr;
+  return s;
+}
+
+// Host-buffer entry point: the batch is cut into chunks; the host->device copy of chunk k+1 runs on
+// a second stream while chunk k computes (two staging buffers, ordered by events), one device->host
+// copy of all logits and one wait at the end.
+static int host_chunks(int B) { return (B >= 256 && B % 4 == 0) ? 4 : ((B >= 64 && B % 2 == 0) ? 2 : 1); }
+struct HostWs { size_t model, xbuf[2], logits, total; size_t model_bytes; int chunk_b; };
+static HostWs host_ws_layout(const cssm_shvit_desc& d) {
+  HostWs h;
+  memset(&h, 0, sizeof(h));
+  cssm_shvit_desc c = d;
+  h.chunk_b = d.B / host_chunks(d.B);
+  c.B = h.chunk_b;
+  h.model_bytes = cssm_shvit_workspace_bytes(&c);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { const size_t o = off; off += al256(bytes); return o; };
+  h.model = take(h.model_bytes);
+  const size_t xb = (size_t)h.chunk_b * d.H * d.W * d.Cin * 2;
+  h.xbuf[0] = take(xb);
+  h.xbuf[1] = take(xb);
+  h.logits = take((size_t)d.B * d.num_classes * 4);
+  h.total = off;
+  return h;
+}
+
 size_t cssm_shvit_host_workspace_bytes(const cssm_shvit_desc* d) {
-  const size_t base = cssm_shvit_workspace_bytes(d);
-  if (base == 0) return 0;
-  return base + al256((size_t)d->B * d->H * d->W * d->Cin * 2) + al256((size_t)d->B * d->num_classes * 4);
+  if (cssm_shvit_workspace_bytes(d) == 0) return 0;
+  return host_ws_layout(*d).total;
 }
 int cssm_shvit_forward_host(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
                             const void* x_bf16_host, float* logits_host, void* workspace, size_t workspace_bytes,
                             void* stream) {
-  const size_t base = cssm_shvit_workspace_bytes(d);
-  if (base == 0) return model_validate(d) != CSSM_OK ? model_validate(d) : CSSM_ERR_UNSUPPORTED;
-  if (!x_bf16_host || !logits_host || !workspace) return CSSM_ERR_NULL;
-  if (workspace_bytes < cssm_shvit_host_workspace_bytes(d)) return CSSM_ERR_WORKSPACE;
+  if (cssm_shvit_workspace_bytes(d) == 0) return model_validate(d) != CSSM_OK ? model_validate(d) : CSSM_ERR_UNSUPPORTED;
+  if (!w || !plan || !x_bf16_host || !logits_host || !workspace) return CSSM_ERR_NULL;
+  if (!aligned16(workspace) || !aligned16(plan)) return CSSM_ERR_ALIGN;
+  const HostWs h = host_ws_layout(*d);
+  if (workspace_bytes < h.total) return CSSM_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   char* ws = (char*)workspace;
-  const size_t xb = (size_t)d->B * d->H * d->W * d->Cin * 2, lb = (size_t)d->B * d->num_classes * 4;
-  char* xd = ws + base;
-  float* ld = (float*)(xd + al256(xb));
-  cudaError_t e = cudaMemcpyAsync(xd, x_bf16_host, xb, cudaMemcpyHostToDevice, st);
-  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  const int s = cssm_shvit_forward(d, w, plan, xd, ld, ws, base, stream);
-  if (s != CSSM_OK) return s;
-  e = cudaMemcpyAsync(logits_host, ld, lb, cudaMemcpyDeviceToHost, st);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  return CSSM_OK;
+  const int nchunk = d->B / h.chunk_b;
+  const size_t xb = (size_t)h.chunk_b * d->H * d->W * d->Cin * 2;
+  float* ld = (float*)(ws + h.logits);
+  cssm_shvit_desc c = *d;
+  c.B = h.chunk_b;
+  cudaStream_t sc = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_in[2] = {nullptr, nullptr}, ev_comp[2] = {nullptr, nullptr};
+  int rc = CSSM_OK;
+  cudaError_t e = cudaSuccess;
+#define CSSM_TRY(call) do { if (rc == CSSM_OK) { e = (call); if (e != cudaSuccess) { set_cuda_error(e); rc = CSSM_ERR_CUDA; } } } while (0)
+  CSSM_TRY(cudaStreamCreateWithFlags(&sc, cudaStreamNonBlocking));
+  CSSM_TRY(cudaEventCreateWithFlags(&ev_start, cudaEventDisableTiming));
+  for (int i = 0; i < 2; ++i) {
+    CSSM_TRY(cudaEventCreateWithFlags(&ev_in[i], cudaEventDisableTiming));
+    CSSM_TRY(cudaEventCreateWithFlags(&ev_comp[i], cudaEventDisableTiming));
+  }
+  // copies start only after work already queued on the caller's stream (e.g. plan_init)
+  CSSM_TRY(cudaEventRecord(ev_start, st));
+  CSSM_TRY(cudaStreamWaitEvent(sc, ev_start, 0));
+  for (int k = 0; k < nchunk && rc == CSSM_OK; ++k) {
+    const int j = k & 1;
+    if (k >= 2) CSSM_TRY(cudaStreamWaitEvent(sc, ev_comp[j], 0));      // chunk k-2 has left this buffer
+    CSSM_TRY(cudaMemcpyAsync(ws + h.xbuf[j], (const char*)x_bf16_host + (size_t)k * xb, xb,
+                             cudaMemcpyHostToDevice, sc));
+    CSSM_TRY(cudaEventRecord(ev_in[j], sc));
+    CSSM_TRY(cudaStreamWaitEvent(st, ev_in[j], 0));
+    if (rc == CSSM_OK)
+      rc = cssm_shvit_forward(&c, w, plan, ws + h.xbuf[j], ld + (size_t)k * h.chunk_b * d->num_classes,
+                              ws + h.model, h.model_bytes, stream);
+    CSSM_TRY(cudaEventRecord(ev_comp[j], st));
+  }
+  CSSM_TRY(cudaMemcpyAsync(logits_host, ld, (size_t)d->B * d->num_classes * 4, cudaMemcpyDeviceToHost, st));
+  // always drain both streams before the events and the stream are destroyed
+  cudaError_t e1 = cudaStreamSynchronize(st), e2 = sc ? cudaStreamSynchronize(sc) : cudaSuccess;
+  if (rc == CSSM_OK && (e1 != cudaSuccess || e2 != cudaSuccess)) {
+    set_cuda_error(e1 != cudaSuccess ? e1 : e2);
+    rc = CSSM_ERR_CUDA;
+  }
+#undef CSSM_TRY
+  for (int i = 0; i < 2; ++i) {
+    if (ev_in[i]) cudaEventDestroy(ev_in[i]);
+    if (ev_comp[i]) cudaEventDestroy(ev_comp[i]);
+  }
+  if (ev_start) cudaEventDestroy(ev_start);
+  if (sc) cudaStreamDestroy(sc);
+  return rc;
 }
 
 int32_t cssm_bf16_packed_ld(int32_t K) { return packed_ld(K); }

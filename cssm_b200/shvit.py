@@ -13,8 +13,8 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import (GATE_ACTS, GATE_TYPES, ROPE_MODES, SHVIT_MAX_BLOCKS, ShvitBlockDesc,
-                   ShvitBlockWeights, ShvitDesc, ShvitWeights, check)
+from ._lib import (GATE_ACTS, GATE_TYPES, ROPE_MODES, SHVIT_KINDS, SHVIT_MAX_BLOCKS, ShvitBlockDesc,
+                   ShvitBlockWeights, ShvitDesc, ShvitTrace, ShvitWeights, check)
 from .modules import _Buffers, _dev_f32, _stream_ptr
 
 
@@ -369,6 +369,29 @@ class BoundShvit:
                                         logits.data_ptr(), ws.data_ptr(), n, _stream_ptr(self.device)),
               "cssm_shvit_forward")
         return logits
+
+    def forward_traced(self, x, out=None, capacity: int = 256):
+        """One forward with an event before every kernel launch.  Returns (logits, launches) where
+        launches is a list of (kernel kind, milliseconds, algorithmic bytes) in launch order."""
+        x = _to_bf16_cuda(x, self.device)
+        d = self.desc(tuple(x.shape))
+        pl = self.plan(d)
+        ws, n = self.workspace(d)
+        logits = torch.empty((d.B, d.num_classes), dtype=torch.float32, device=self.device) if out is None else out
+        stream = torch.cuda.current_stream(self.device)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(capacity)]
+        for e in evs:
+            e.record(stream)                      # creates the raw cudaEvent_t handles
+        torch.cuda.synchronize(self.device)
+        tr = ShvitTrace((C.c_void_p * capacity)(*[e.cuda_event for e in evs]),
+                        (C.c_int32 * capacity)(), (C.c_double * capacity)(), capacity, 0)
+        check(self.L.cssm_shvit_forward_timed(C.byref(d), C.byref(self.w), pl.data_ptr(), x.data_ptr(),
+                                              logits.data_ptr(), ws.data_ptr(), n, stream.cuda_stream,
+                                              C.byref(tr)), "cssm_shvit_forward_timed")
+        torch.cuda.synchronize(self.device)
+        launches = [(SHVIT_KINDS[tr.kinds[i]], evs[i].elapsed_time(evs[i + 1]), tr.bytes[i])
+                    for i in range(tr.count - 1)]
+        return logits, launches
 
     def forward_host(self, x_host: torch.Tensor, logits_host: torch.Tensor):
         """x_host: (B,H,W,Cin) bfloat16 host tensor (pinned for full copy speed); logits_host:

@@ -532,8 +532,31 @@ int cssm_shvit_plan_init(const cssm_shvit_desc* d, const cssm_shvit_weights* w, 
 int cssm_shvit_forward(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
                        const void* x_bf16, float* logits, void* workspace, size_t workspace_bytes,
                        void* stream);
-/* Same with the images and the logits in HOST memory (pinned for full copy speed); the workspace
- * (cssm_shvit_host_workspace_bytes) holds the staging copies.  Waits for the stream. */
+/* cssm_shvit_forward with a launch trace (no counterpart in the reference): before every kernel of
+ * the forward an event of `events` (cudaEvent_t created by the caller, timing enabled) is recorded
+ * on `stream`, and the kernel kind and the algorithmic bytes of that launch (inputs + outputs +
+ * weights) are written beside it; one more entry (CSSM_SHVIT_K_END) marks the end.  `count` returns
+ * the number of entries used.  Nothing is kept after the call returns. */
+enum {
+  CSSM_SHVIT_K_STEM_CONV = 0, CSSM_SHVIT_K_CONV_GEMM = 1, CSSM_SHVIT_K_GEMM = 2,
+  CSSM_SHVIT_K_LAYERNORM = 3, CSSM_SHVIT_K_DWCONV7 = 4, CSSM_SHVIT_K_DWCONV3 = 5,
+  CSSM_SHVIT_K_SAMPLE_NORM = 6, CSSM_SHVIT_K_PLANE_SUM = 7, CSSM_SHVIT_K_GATES = 8,
+  CSSM_SHVIT_K_SPECTRAL = 9, CSSM_SHVIT_K_POOL = 10, CSSM_SHVIT_K_HEAD = 11,
+  CSSM_SHVIT_K_MIXER_F32 = 12, CSSM_SHVIT_K_ADD_RES = 13, CSSM_SHVIT_K_END = 14
+};
+typedef struct cssm_shvit_trace {
+  void** events; int32_t* kinds; double* bytes;
+  int32_t capacity; int32_t count;
+} cssm_shvit_trace;
+int cssm_shvit_forward_timed(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
+                             const void* x_bf16, float* logits, void* workspace, size_t workspace_bytes,
+                             void* stream, cssm_shvit_trace* trace);
+
+/* Same with the images and the logits in HOST memory (pinned for full copy speed).  The batch is
+ * cut into up to four chunks whose host->device copies run on an internal stream while the previous
+ * chunk computes (two staging buffers inside the workspace, ordered by events); the logits of all
+ * chunks return in one copy and the call waits for it.  The internal stream and events live for
+ * the duration of the call only. */
 size_t cssm_shvit_host_workspace_bytes(const cssm_shvit_desc* d);
 int cssm_shvit_forward_host(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
                             const void* x_bf16_host, float* logits_host, void* workspace,

@@ -235,3 +235,77 @@ def simple_forward_torch(params, x, *, cssm_type="gated", seq_len=8, stem_mode="
     z = z.amax(dim=(1, 2)) if pool_type == "max" else z.mean(dim=(1, 2))
     z = _layer_norm_t(z, p["norm_post"])
     return z @ _t(p["head"]["kernel"]) + _t(p["head"]["bias"])
+
+
+# ------------------------------------------------------------------ CSSM-SHViT (timed CPU leg)
+def _conv_same(x, kernel, bias, stride=1, groups=1):
+    """'SAME' conv as XLA pads it (total = (ceil(n/s)-1)*s + k - n, the smaller half first).
+    x (N,C,H,W); kernel HWIO."""
+    kh, kw = kernel.shape[:2]
+    H, W = x.shape[-2:]
+    th = max((-(-H // stride) - 1) * stride + kh - H, 0)
+    tw = max((-(-W // stride) - 1) * stride + kw - W, 0)
+    x = F.pad(x, (tw // 2, tw - tw // 2, th // 2, th - th // 2))
+    return F.conv2d(x, _t(kernel).permute(3, 2, 0, 1).contiguous(), None if bias is None else _t(bias),
+                    stride=stride, groups=groups)
+
+
+def _convbn_t(x, p, s, stride):
+    y = _conv_same(x, p["conv"]["kernel"], None, stride)
+    return F.batch_norm(y, _t(s["bn"]["mean"]), _t(s["bn"]["var"]), _t(p["bn"]["scale"]), _t(p["bn"]["bias"]),
+                        training=False, eps=1e-5)
+
+
+def _ln_cl(x, p):
+    return F.layer_norm(x, x.shape[-1:], _t(p["scale"]), _t(p["bias"]), eps=1e-6)
+
+
+def _dw_cl(x, p):
+    """Depthwise 'SAME' conv on a channels-last tensor."""
+    return _conv_same(x.permute(0, 3, 1, 2), p["kernel"], p["bias"], groups=x.shape[-1]).permute(0, 2, 3, 1)
+
+
+def _mlp_t(x, p, use_dwconv):
+    h = F.gelu(F.linear(x, _t(p["fc1"]["kernel"]).T, _t(p["fc1"]["bias"])), approximate="tanh")
+    if use_dwconv:
+        h = h + _dw_cl(h, p["dwconv"]["dwconv"])
+    return F.linear(h, _t(p["fc2"]["kernel"]).T, _t(p["fc2"]["bias"]))
+
+
+def shvit_forward_torch(params, stats, x, *, embed_dims=(64, 128, 256, 384), depths=(1, 2, 2, 1),
+                        use_cssm_stages=(False, False, True, True), num_timesteps=8,
+                        kernel_sizes=(15, 15, 5, 3), use_pos_conv=True, use_dwconv=True,
+                        head_pool="max", gate_type="factored", **gated_kw):
+    """CSSMSHViT inference forward (src/models/cssm_shvit.py:324-460, gated mixers, image input) in
+    float32 on the host cores, op for op as the reference runs it (the image is repeated over
+    num_timesteps in front of every CSSM block and all T frames go through the mixer).
+    x: (B,H,W,3) float32 torch CPU tensor -> logits (B,num_classes)."""
+    p, s = params, stats
+    y = x.permute(0, 3, 1, 2)
+    y = F.gelu(_convbn_t(y, p["patch_embed"]["ConvBN_0"], s["patch_embed"]["ConvBN_0"], 2), approximate="tanh")
+    y = _convbn_t(y, p["patch_embed"]["ConvBN_1"], s["patch_embed"]["ConvBN_1"], 2)
+    for st in range(4):
+        if st > 0:
+            y = _convbn_t(y, p[f"downsample{st}"]["ConvBN_0"], s[f"downsample{st}"]["ConvBN_0"], 2)
+        v = y.permute(0, 2, 3, 1)
+        for b in range(depths[st]):
+            bp = p[f"stage{st}_block{b}"]
+            if use_cssm_stages[st]:
+                B, H, W, C = v.shape
+                T = num_timesteps
+                xt = v[:, None].expand(-1, T, -1, -1, -1)
+                h = F.layer_norm(xt, xt.shape[1:], eps=1e-6) * _t(bp["norm1"]["scale"]) + _t(bp["norm1"]["bias"])
+                if use_pos_conv:
+                    h = h + _dw_cl(h.reshape(B * T, H, W, C), bp["pos_conv"]).reshape(B, T, H, W, C)
+                m = gated_forward_torch(bp["cssm"], h.contiguous(), kernel_size=kernel_sizes[st],
+                                        gate_type=gate_type, **gated_kw)
+                v = v + m[:, -1]
+                v = v + _mlp_t(_ln_cl(v, bp["norm2"]), bp["mlp"], use_dwconv)
+            else:
+                h = F.gelu(_dw_cl(_ln_cl(v, bp["norm1"]), bp["dwconv"]["dwconv"]), approximate="tanh")
+                v = v + F.linear(h, _t(bp["pwconv"]["kernel"]).T, _t(bp["pwconv"]["bias"]))
+                v = v + _mlp_t(_ln_cl(v, bp["norm2"]), bp["mlp"], False)
+        y = v.permute(0, 3, 1, 2)
+    v = _ln_cl(y.permute(0, 2, 3, 1), p["norm"])
+    pooled = v.amax(dim=(1, 2)) if head_pool == "max" else v.mean(dim=(1, 2))
+    return pooled @ _t(p["head"]["kernel"]) + _t(p["head"]["bias"])

@@ -21,7 +21,7 @@ def test_reference_arm_prints_contract_json():
         assert k in d, k
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
-    assert d["config"]["workload"] == "cfg2"
+    assert d["config"]["workload"] == "cfg5" and d["dtype"] == "bf16"     # the default headline
 
 
 def test_workloads_match_baseline_configs():
@@ -37,15 +37,21 @@ def test_workloads_match_baseline_configs():
     assert m3["pos_embed"] == "mrope" and m3["output_norm"] == "rms"
     m4 = w["cfg4"]["model"]
     assert m4["cssm_type"] == "gdn" and m4["stem_mode"] == "pathtracker" and w["cfg4"]["data"] == "dots"
+    m5 = w["cfg5"]["model"]
+    assert w["cfg5"]["B"] == 512 and m5["num_timesteps"] == 1 and m5["num_classes"] == 1000
+    assert tuple(m5["embed_dims"]) == (64, 128, 256, 384) and tuple(m5["depths"]) == (1, 2, 2, 1)
+    assert tuple(m5["kernel_sizes"]) == (1, 1, 1, 1) and m5["short_conv_spatial_size"] == 0
+    assert bench.make_inputs("cfg5", 2, seed0=1).shape == (2, 224, 224, 3)
     x = bench.make_inputs("cfg4", 2, seed0=1)
     assert x.shape == (2, 32, 32, 32, 3)
     assert bench.make_inputs("cfg2", 1, seed0=1).shape == (1, 128, 128, 1)
 
 
-def test_gdn_reference_arm_runs():
-    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
-                          "--workload", "cfg4", "--steps", "1", "--warmup", "0"],
-                         capture_output=True, text=True, timeout=600, cwd=ROOT)
-    assert out.returncode == 0, out.stderr[-2000:]
-    d = json.loads(out.stdout.strip().splitlines()[-1])
-    assert d["impl"] == "reference" and d["value"] > 0 and d["config"]["workload"] == "cfg4"
+def test_simple_reference_arms_run():
+    for wl in ("cfg2", "cfg4"):
+        out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
+                              "--workload", wl, "--steps", "1", "--warmup", "0"],
+                             capture_output=True, text=True, timeout=600, cwd=ROOT)
+        assert out.returncode == 0, out.stderr[-2000:]
+        d = json.loads(out.stdout.strip().splitlines()[-1])
+        assert d["impl"] == "reference" and d["value"] > 0 and d["config"]["workload"] == wl

@@ -113,3 +113,15 @@ def test_host_entry_matches_device_entry():
     xh, lh = x.pin_memory(), torch.empty((2, 7), dtype=torch.float32).pin_memory()
     bound.forward_host(xh, lh)
     assert torch.equal(lh, want)
+    # a batch that the host entry point cuts into two overlapped chunks
+    x = torch.randn((64, 64, 64, 3)).to(torch.bfloat16)
+    want = bound(x.cuda()).cpu()
+    xh, lh = x.pin_memory(), torch.empty((64, 7), dtype=torch.float32).pin_memory()
+    bound.forward_host(xh, lh)
+    assert torch.equal(lh, want)
+    # the launch trace covers the whole forward and changes nothing
+    logits, launches = bound.forward_traced(x.cuda())
+    assert torch.equal(logits.cpu(), want)
+    kinds = [k for k, _, _ in launches]
+    assert kinds[0] == "stem_conv" and kinds[-1] == "head" and "gemm" in kinds and "conv_gemm" in kinds
+    assert all(ms >= 0 for _, ms, _ in launches)
