@@ -7,7 +7,7 @@ points, CPU restatement beside it.
 One step = one forward of the workload's model over one per-GPU batch of seeded synthetic inputs.
 Without --workload the headline is cfg5 (BASELINE.json configs[4], the configuration the metric
 "fwd images/s at 1/2/4/8 B200" names: CSSM-SHViT s1, gated mixers at T = 1, bf16, batch 512 per GPU)
-and the SimpleCSSM workloads cfg2 / cfg3 / cfg4 (configs[1..3], fp32) run after it and are reported
+and the SimpleCSSM workloads cfg1 .. cfg4 (configs[0..3], fp32) run after it and are reported
 under "workloads" in the same JSON line (rank 0 prints ONE line):
   value     images/s, inputs resident on the device, CUDA events around the K timed steps
   e2e       the same through the host-buffer entry point: pinned host inputs in, host logits out
@@ -644,7 +644,7 @@ def run_simple(args, name, ctx):
 
 
 HEADLINE = "cfg5"
-ALSO = ["cfg2", "cfg3", "cfg4"]          # reported under "workloads" when no --workload is given
+ALSO = ["cfg1", "cfg2", "cfg3", "cfg4"]          # reported under "workloads" when no --workload is given
 
 
 def main():

@@ -183,7 +183,7 @@ SIGNATURES = {
                                           _P, C.c_size_t, _P]),
     "cssm_gated_bf16_workspace_bytes": (C.c_size_t, [C.POINTER(GatedDesc)]),
     "cssm_gated_forward_bf16": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P, _P,
-                                          _P, C.c_size_t, _P]),
+                                          C.c_int32, _P, C.c_size_t, _P]),
     "cssm_gated_host_workspace_bytes": (C.c_size_t, [C.POINTER(GatedDesc), C.c_int32]),
     "cssm_gated_forward_host": (C.c_int, [C.POINTER(GatedDesc), C.POINTER(GatedWeights), _P, _P,
                                           _P, C.c_int32, _P, C.c_size_t, _P]),

@@ -352,12 +352,13 @@ size_t cssm_gated_bf16_workspace_bytes(const cssm_gated_desc* d) {
 }
 
 int cssm_gated_forward_bf16(const cssm_gated_desc* d, const cssm_gated_weights* w, const void* plan,
-                            const void* x_bf16, void* y_bf16, void* workspace,
+                            const void* x_bf16, void* y, int32_t y_is_bf16, void* workspace,
                             size_t workspace_bytes, void* stream) {
+  void* y_bf16 = y;
   const size_t base = cssm_gated_workspace_bytes(d);
   if (base == 0) return validate(d) != CSSM_OK ? validate(d) : CSSM_ERR_DIMS;
-  if (!x_bf16 || !y_bf16 || !workspace) return CSSM_ERR_NULL;
-  if (!aligned16(x_bf16) || !aligned16(y_bf16) || !aligned16(workspace)) return CSSM_ERR_ALIGN;
+  if (!x_bf16 || !y || !workspace) return CSSM_ERR_NULL;
+  if (!aligned16(x_bf16) || !aligned16(y) || !aligned16(workspace)) return CSSM_ERR_ALIGN;
   if (workspace_bytes < cssm_gated_bf16_workspace_bytes(d)) return CSSM_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t n = (size_t)d->B * d->T * d->H * d->W * d->C;
@@ -369,8 +370,9 @@ int cssm_gated_forward_bf16(const cssm_gated_desc* d, const cssm_gated_weights* 
   bf16_to_f32_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x_bf16, xf, n);
   int s = check_launch();
   if (s != CSSM_OK) return s;
-  s = gated_forward_internal(d, w, plan, xf, yf, workspace, base, stream, 0, 0);
-  if (s != CSSM_OK) return s;
+  // float32 result (what Flax's promotion gives the reference) straight into y, or rounded to bf16
+  s = gated_forward_internal(d, w, plan, xf, y_is_bf16 ? yf : (float*)y, workspace, base, stream, 0, 0);
+  if (s != CSSM_OK || !y_is_bf16) return s;
   f32_to_bf16_kernel<<<grid, 256, 0, st>>>(yf, (__nv_bfloat16*)y_bf16, n);
   return check_launch();
 }

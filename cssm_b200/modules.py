@@ -222,12 +222,13 @@ class BoundGated:
         return self.mod._desc(shape)
 
     def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                 last_frame_only: bool = False) -> torch.Tensor:
+                 last_frame_only: bool = False, bf16_output: bool = False) -> torch.Tensor:
         """y = block(x).  With last_frame_only=True returns block(x)[:, -1] of shape (B,H,W,C)
         without computing the earlier output frames (for callers that read only the final
         frame, as SimpleCSSM with frame_readout='last' and CSSMSHViTBlock do).  A bfloat16 x
-        (the SHViT mixers run in a bf16 model) is widened to fp32, as Flax promotion does with
-        the block's fp32 parameters, and the result comes back in bfloat16."""
+        (the SHViT mixers run in a bf16 model) is widened to fp32 and the result is float32, as
+        Flax promotion gives with the block's fp32 parameters; bf16_output=True rounds it to
+        bfloat16 instead."""
         _require_cuda(x, allow_bf16=True)
         x = x.contiguous()
         d = self.desc(tuple(x.shape))
@@ -237,10 +238,12 @@ class BoundGated:
                 raise NotImplementedError("GatedCSSM: last_frame_only with bfloat16 activations")
             n = self.L.cssm_gated_bf16_workspace_bytes(C.byref(d))
             ws = self.buf.get("ws", n)
-            y = torch.empty_like(x) if out is None else out
+            odt = torch.bfloat16 if bf16_output else torch.float32
+            y = torch.empty(x.shape, dtype=odt, device=x.device) if out is None else out
             check(self.L.cssm_gated_forward_bf16(C.byref(d), C.byref(self.w), pl.data_ptr(),
-                                                 x.data_ptr(), y.data_ptr(), ws.data_ptr(), n,
-                                                 _stream_ptr(self.device)), "cssm_gated_forward_bf16")
+                                                 x.data_ptr(), y.data_ptr(), 1 if bf16_output else 0,
+                                                 ws.data_ptr(), n, _stream_ptr(self.device)),
+                  "cssm_gated_forward_bf16")
             return y
         n = self.L.cssm_gated_workspace_bytes(C.byref(d))
         ws = self.buf.get("ws", n)

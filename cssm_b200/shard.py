@@ -5,6 +5,7 @@ evaluation does with its leading device axis (main.py:522-561, src/training/dist
 241-301).  Works with the `nccl` backend on GPUs and the `gloo` backend on CPU."""
 from __future__ import annotations
 
+import datetime
 from typing import List, Tuple
 
 import torch
@@ -50,3 +51,45 @@ def max_over_ranks(value: float, device) -> float:
     t = torch.tensor([float(value)], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+class PeerTimeout(RuntimeError):
+    """Raised by check_peers: `missing` lists the ranks that did not report in time."""
+
+    def __init__(self, missing):
+        super().__init__(f"ranks {missing} did not report before the collective")
+        self.missing = list(missing)
+
+
+def check_peers(store, rank: int, world: int, step: int, timeout_s: float = 30.0) -> None:
+    """Host-side roll call before a collective: every rank posts a key for `step` in the c10d
+    store and waits, with a time limit, for the keys of all ranks.  A rank that died or raised
+    before the collective never posts, so the others learn of it here, on the host, instead of
+    hanging inside the all-gather (the reference probes NCCL the same way before its first pmap
+    step and falls back to one device: main.py:1257-1288).  Raises PeerTimeout."""
+    store.set(f"cssm_step{step}_rank{rank}", "1")
+    deadline = datetime.timedelta(seconds=float(timeout_s))
+    keys = [f"cssm_step{step}_rank{r}" for r in range(world)]
+    try:
+        store.wait(keys, deadline)
+    except Exception:
+        missing = []
+        for r, k in enumerate(keys):
+            try:
+                store.wait([k], datetime.timedelta(milliseconds=50))
+            except Exception:
+                missing.append(r)
+        raise PeerTimeout(missing or list(range(world))) from None
+
+
+def gather_outputs_checked(local: torch.Tensor, n_total: int, store, step: int,
+                           timeout_s: float = 30.0):
+    """gather_outputs behind a roll call.  Returns (outputs, None) when every rank reported, else
+    (this rank's own shard, PeerTimeout): the caller keeps its local results and decides."""
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return local, None
+    try:
+        check_peers(store, dist.get_rank(), dist.get_world_size(), step, timeout_s)
+    except PeerTimeout as e:
+        return local, e
+    return gather_outputs(local, n_total), None

@@ -1,5 +1,8 @@
 """world_size-2 (and 3) CPU tests of the multi-GPU host logic over the gloo backend:
-shard bounds, ragged all-gather in rank order, max-over-ranks timing."""
+shard bounds, ragged all-gather in rank order, max-over-ranks timing, and a rank that raises
+before the collective (the others learn of it on the host within a time limit and keep their own
+shard instead of hanging in the all-gather)."""
+import datetime
 import os
 import socket
 
@@ -63,3 +66,45 @@ def test_gather_rank_order_over_gloo(world, n):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert res == {r: True for r in range(world)}
+
+
+def _failing_worker(rank, world, port, store_port, n, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    store = dist.TCPStore("127.0.0.1", store_port, world, is_master=(rank == 0),
+                          timeout=datetime.timedelta(seconds=60))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        full = torch.arange(n * 2, dtype=torch.float32).reshape(n, 2)
+        lo, hi = shard.shard_bounds(n, rank, world)
+        local = full[lo:hi] + 0.5
+        # step 0: everybody is there
+        got, err = shard.gather_outputs_checked(local, n, store, step=0, timeout_s=30.0)
+        ok0 = err is None and torch.equal(got, full + 0.5)
+        # step 1: the last rank fails before the collective (between steps, nothing in flight)
+        if rank == world - 1:
+            q.put((rank, ok0, "raised"))
+            raise RuntimeError("injected failure before the collective")
+        got, err = shard.gather_outputs_checked(local, n, store, step=1, timeout_s=2.0)
+        ok1 = isinstance(err, shard.PeerTimeout) and err.missing == [world - 1] and torch.equal(got, local)
+        q.put((rank, ok0 and ok1, "reported"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_rank_that_raises_before_the_gather_is_reported(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port, store_port = _free_port(), _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, store_port, 9, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        r, ok, what = q.get(timeout=120)
+        res[r] = (ok, what)
+    for p in procs:
+        p.join(timeout=60)
+    assert res[world - 1] == (True, "raised") and procs[world - 1].exitcode != 0
+    for r in range(world - 1):
+        assert res[r] == (True, "reported") and procs[r].exitcode == 0

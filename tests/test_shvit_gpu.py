@@ -125,3 +125,20 @@ def test_host_entry_matches_device_entry():
     kinds = [k for k, _, _ in launches]
     assert kinds[0] == "stem_conv" and kinds[-1] == "head" and "gemm" in kinds and "conv_gemm" in kinds
     assert all(ms >= 0 for _, ms, _ in launches)
+
+
+def test_cfg5_full_batch_picked_samples():
+    """BASELINE configs[4] at its full size (cssm_shvit_s1, T = 1, kernel_size 1, batch 512 of
+    224x224x3 bf16 N(0,1) images, 1000 classes): logits of samples picked out of the batch against the
+    fp64 oracle run on those samples alone (samples are independent), 2e-2."""
+    import bench
+    p, s = bench.shvit_params("cfg5")
+    model = CSSMSHViT(**bench.WORKLOADS["cfg5"]["model"])
+    bound = model.bind({"params": p, "batch_stats": s})
+    x = torch.from_numpy(bench.make_inputs("cfg5", 512, seed0=77)).to(torch.bfloat16)
+    y = bound(x.cuda()).cpu().numpy()
+    assert np.isfinite(y).all() and y.shape == (512, 1000)
+    pick = [0, 255, 511]
+    ref = sv.shvit_forward(p, s, x[pick].float().numpy().astype(np.float64), **bench.shvit_model_kwargs("cfg5"))
+    for i, b in enumerate(pick):
+        assert orc.rel_l2(y[b], ref[i]) <= 2e-2, (b, orc.rel_l2(y[b], ref[i]))
