@@ -76,10 +76,10 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, const __grid_constant__ CUtensor
                                  : (2 * N <= 256) ? 256 : 512;
 
   if (tid == 0) {
-    tc::mbar_init(&full[0], NPROD); tc::mbar_init(&full[1], NPROD);
+    tc::mbar_init(&full[0], NPROD / 32); tc::mbar_init(&full[1], NPROD / 32);      // one lane per producer warp
     tc::mbar_init(&empty[0], 1); tc::mbar_init(&empty[1], 1);
     tc::mbar_init(&accfull[0], 1); tc::mbar_init(&accfull[1], 1);
-    tc::mbar_init(&accempty[0], 256); tc::mbar_init(&accempty[1], 256);
+    tc::mbar_init(&accempty[0], 8); tc::mbar_init(&accempty[1], 8);                  // one lane per epilogue warp
     tc::mbar_init(done, 1);
     tc::fence_mbar_init();
   }
@@ -157,7 +157,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, const __grid_constant__ CUtensor
           }
         }
       }
-      if (!tc::mbar_wait(&empty[s], ((it / NSTAGE) & 1) ^ 1)) { atomicExch(&g_tc_error, 1); break; }
+      // warp-uniform exit: the lanes of a warp meet again at the __syncwarp before the arrive
+      if (__any_sync(0xffffffffu, !tc::mbar_wait(&empty[s], ((it / NSTAGE) & 1) ^ 1))) { atomicExch(&g_tc_error, 1); break; }
       unsigned char* a_hi = smem + L::A_OFF + (uint32_t)s * 2u * TC_A_HALF;
       unsigned char* a_lo = a_hi + TC_A_HALF;
       if (!A_PLANAR) {
@@ -239,7 +240,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, const __grid_constant__ CUtensor
         }
       }
       tc::fence_proxy_async();
-      tc::mbar_arrive(&full[s]);
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&full[s]);
     }
   } else if (warp == TC_MMA_WARP) {
     // ================================ MMA issuer ================================
@@ -298,6 +300,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, const __grid_constant__ CUtensor
             "selp.u32 %0, 1, 0, q;\n\t}"
             : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + half) : "memory");
         ok = all_ok != 0;
+      } else {
+        ok = !__any_sync(0xffffffffu, !ok);
       }
       if (!ok) { atomicExch(&g_tc_error, 4); break; }
       tc::fence_after_sync();
@@ -401,7 +405,8 @@ gemm_tc_kernel(const GemmArgs g, int num_tiles, const __grid_constant__ CUtensor
         }
       }
       tc::fence_before_sync();
-      tc::mbar_arrive(&accempty[s]);
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&accempty[s]);
     }
     // shared memory must outlive the last TMA stores that read it
     if (STG) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");

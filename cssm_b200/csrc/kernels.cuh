@@ -118,8 +118,8 @@ struct Bf16GemmArgs {
   int act;                   // 0 none, 1 gelu (tanh form), 2 silu
   const __nv_bfloat16* res;  // (M, ldr) added after the activation, or nullptr
   int ldr;
-  __nv_bfloat16* out;        // (M, ldo) bf16 ...
-  float* out_f32;            // ... or (M, ldo) float32 when not nullptr
+  __nv_bfloat16* out;        // (M, ldo) bf16
+  float* out_f32;            // reserved (must be nullptr)
   int ldo;
   int Kpad, BN, stages;      // filled in by the launcher
 };
