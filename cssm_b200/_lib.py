@@ -251,6 +251,8 @@ SIGNATURES = {
     "cssm_bf16_packed_ld": (C.c_int32, [C.c_int32]),
     "cssm_bf16_pack_weight": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P]),
     "cssm_bf16_gemm": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _P, C.c_int32, _P, _P, _P]),
+    "cssm_bf16_conv3x3s2_packed_ld": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32]),
+    "cssm_bf16_pack_conv3x3s2_weight": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),
     "cssm_bf16_conv3x3s2": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, _P,
                                       C.c_int32, _P, _P]),
     "cssm_static_scratch_bytes": (C.c_size_t, []),

@@ -134,7 +134,7 @@ static int conv_s2(const __nv_bfloat16* x, int B, int Hi, int Wi, int Cin, const
   g.A = x; g.M = B * Ho * Wo; g.N = Cout; g.K = 9 * Cin;
   g.ksz = 3; g.stride = 2; g.Hi = Hi; g.Wi = Wi; g.Cin = Cin; g.Ho = Ho; g.Wo = Wo;
   g.pad_h = (th > 0 ? th : 0) / 2; g.pad_w = (tw > 0 ? tw : 0) / 2;
-  g.Wt = Wt; g.ldw = packed_ld(9 * Cin); g.bias = bias; g.act = act;
+  g.Wt = Wt; g.ldw = packed_ld(conv3x3s2_packed_k(Cin, Wi, Cout)); g.bias = bias; g.act = act;
   g.out = out; g.ldo = Cout;
   trace(CSSM_SHVIT_K_CONV_GEMM, 2.0 * ((double)B * Hi * Wi * Cin + (double)g.M * Cout + 9.0 * Cin * Cout), st);
   return launch_gemm_bf16(g, st);
@@ -305,16 +305,18 @@ static ModelWalk model_walk(const cssm_shvit_desc& d) {
   const int E0 = d.embed_dims[0];
   m.plan.c1w = take((size_t)9 * d.Cin * (E0 / 2) * 4);
   m.plan.c1b = take((size_t)(E0 / 2) * 4);
-  m.plan.c2w = take((size_t)E0 * packed_ld(9 * (E0 / 2)) * 2);
+  m.plan.c2w = take((size_t)E0 * packed_ld(conv3x3s2_packed_k(E0 / 2, (d.W + 1) / 2, E0)) * 2);
   m.plan.c2b = take((size_t)E0 * 4);
   int H = (((d.H + 1) / 2) + 1) / 2, W = (((d.W + 1) / 2) + 1) / 2;
+  int Wprev = W;                                       // width of the input of the next downsample conv
   size_t act_max = (size_t)d.B * ((d.H + 1) / 2) * ((d.W + 1) / 2) * (E0 / 2);
   size_t blk_ws = 0;
   for (int s = 0; s < 4; ++s) {
     if (s > 0) {
-      m.plan.dsw[s - 1] = take((size_t)d.embed_dims[s] * packed_ld(9 * d.embed_dims[s - 1]) * 2);
+      m.plan.dsw[s - 1] = take((size_t)d.embed_dims[s] * packed_ld(conv3x3s2_packed_k(d.embed_dims[s - 1], Wprev, d.embed_dims[s])) * 2);
       m.plan.dsb[s - 1] = take((size_t)d.embed_dims[s] * 4);
       H = (H + 1) / 2; W = (W + 1) / 2;
+      Wprev = W;
     }
     m.Hs[s] = H; m.Ws[s] = W;
     const size_t act = (size_t)d.B * H * W * d.embed_dims[s];
@@ -457,12 +459,12 @@ int cssm_shvit_plan_init(const cssm_shvit_desc* d, const cssm_shvit_weights* w, 
   CSSM_RUN(fold(w->patch[0], E0 / 2, (float*)(pl + m.plan.c1b)));
   CSSM_RUN(launch_scale_cols(w->patch[0].kernel, 9 * d->Cin, E0 / 2, sc, (float*)(pl + m.plan.c1w), st));
   CSSM_RUN(fold(w->patch[1], E0, (float*)(pl + m.plan.c2b)));
-  CSSM_RUN(launch_pack_wt(w->patch[1].kernel, 9 * (E0 / 2), E0, sc, (__nv_bfloat16*)(pl + m.plan.c2w),
-                          packed_ld(9 * (E0 / 2)), st));
+  CSSM_RUN(launch_pack_conv3x3(w->patch[1].kernel, E0 / 2, E0, (d->W + 1) / 2, sc,
+                               (__nv_bfloat16*)(pl + m.plan.c2w), st));
   for (int i = 1; i < 4; ++i) {
     CSSM_RUN(fold(w->down[i - 1], d->embed_dims[i], (float*)(pl + m.plan.dsb[i - 1])));
-    CSSM_RUN(launch_pack_wt(w->down[i - 1].kernel, 9 * d->embed_dims[i - 1], d->embed_dims[i], sc,
-                            (__nv_bfloat16*)(pl + m.plan.dsw[i - 1]), packed_ld(9 * d->embed_dims[i - 1]), st));
+    CSSM_RUN(launch_pack_conv3x3(w->down[i - 1].kernel, d->embed_dims[i - 1], d->embed_dims[i], m.Ws[i - 1], sc,
+                                 (__nv_bfloat16*)(pl + m.plan.dsw[i - 1]), st));
   }
   for (int b = 0; b < m.nblocks; ++b)
     CSSM_RUN(block_plan_init(m.bd[b], w->blocks[b], pl + m.plan.blocks[b], st));
@@ -589,6 +591,13 @@ int cssm_bf16_gemm(const void* A, int32_t M, int32_t K, const void* wt, int32_t 
   if (!A || !wt || !out) return CSSM_ERR_NULL;
   return gemm_plain((const __nv_bfloat16*)A, M, K, (const __nv_bfloat16*)wt, N, bias, act,
                     (const __nv_bfloat16*)res, (__nv_bfloat16*)out, (cudaStream_t)stream);
+}
+int32_t cssm_bf16_conv3x3s2_packed_ld(int32_t Cin, int32_t Wi, int32_t Cout) { return packed_ld(conv3x3s2_packed_k(Cin, Wi, Cout)); }
+int cssm_bf16_pack_conv3x3s2_weight(const float* kernel, int32_t Cin, int32_t Cout, int32_t Wi,
+                                    const float* col_scale, void* wt, void* stream) {
+  if (!kernel || !wt) return CSSM_ERR_NULL;
+  if (Cin <= 0 || Cout <= 0 || Wi <= 0) return CSSM_ERR_DIMS;
+  return launch_pack_conv3x3(kernel, Cin, Cout, Wi, col_scale, (__nv_bfloat16*)wt, (cudaStream_t)stream);
 }
 int cssm_bf16_conv3x3s2(const void* x, int32_t B, int32_t Hi, int32_t Wi, int32_t Cin, const void* wt,
                         int32_t Cout, const float* bias, int32_t act, void* out, void* stream) {

@@ -75,7 +75,8 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m_tiles = (g.M + GB_BM - 1) / GB_BM, n_tiles = g.N / g.BN;
+  const int n_tiles = g.N / g.BN;
+  const int m_tiles = g.conv_tma ? g.tiles_w * g.tiles_h * ((g.Bimg + g.Bbox - 1) / g.Bbox) : (g.M + GB_BM - 1) / GB_BM;
   const int num_tiles = m_tiles * n_tiles;
   const int kblocks = g.Kpad / GB_BK;
   uint32_t tmem_cols = 32;
@@ -106,14 +107,30 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
     if (lane == 0) {
       int it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
+        const int mt = tile / n_tiles;
+        const int m0 = mt * GB_BM, n0 = (tile % n_tiles) * g.BN;
+        // conv through TMA: the tile's patch origin (input coordinates of window position (0,0))
+        int cw0 = 0, ch0 = 0, cb0 = 0;
+        if (g.conv_tma) {
+          const int tw = mt % g.tiles_w, th = (mt / g.tiles_w) % g.tiles_h;
+          cb0 = (mt / (g.tiles_w * g.tiles_h)) * g.Bbox;
+          cw0 = tw * g.Wbox * (g.conv_tma == 2 ? 1 : g.stride) - (g.conv_tma == 2 ? 0 : g.pad_w);
+          ch0 = th * g.Hbox * g.stride - g.pad_h;
+        }
+        const uint32_t a_bytes = g.conv_tma ? (uint32_t)(g.Wbox * g.Hbox * g.Bbox) * 128u : GB_A_BYTES;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % NS;
           if (!tc::mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { atomicExch(&g_bf16_error, 5); bad = true; break; }
           unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
           unsigned char* b_s = a_s + GB_A_BYTES;
-          tc::mbar_expect_tx(&full[s], (IM2COL ? 0u : GB_A_BYTES) + BN * 128u);
-          if (!IM2COL) tc::tma_load_2d(a_s, &amap, kb * GB_BK, m0, &full[s]);
+          tc::mbar_expect_tx(&full[s], (IM2COL ? 0u : a_bytes) + BN * 128u);
+          if (g.conv_tma) {
+            const int pos = kb / g.kb_per_tap, cb = kb - pos * g.kb_per_tap;
+            const int pr = pos / g.pos_w, pc = pos - pr * g.pos_w;
+            tc::tma_load_4d(a_s, &amap, cb * GB_BK, cw0 + pc, ch0 + pr, cb0, &full[s]);
+          } else if (!IM2COL) {
+            tc::tma_load_2d(a_s, &amap, kb * GB_BK, m0, &full[s]);
+          }
           tc::tma_load_2d(b_s, &bmap, kb * GB_BK, n0, &full[s]);
         }
       }
@@ -254,7 +271,14 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
           tc::fence_proxy_async();
           asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
           if (issuer) {
-            tc::tma_store_2d(&omap, stg, n0 + box * 64, m0);
+            if (g.conv_tma) {
+              const int mt = tile / n_tiles;
+              const int tw = mt % g.tiles_w, th = (mt / g.tiles_w) % g.tiles_h;
+              tc::tma_store_4d(&omap, stg, n0 + box * 64, tw * g.Wbox, th * g.Hbox,
+                               (mt / (g.tiles_w * g.tiles_h)) * g.Bbox);
+            } else {
+              tc::tma_store_2d(&omap, stg, n0 + box * 64, m0);
+            }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         } else if (m < g.M) {
@@ -418,18 +442,44 @@ static bool make_out_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t c
              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 4-D bf16 tensor (d0 innermost) with byte strides st[0..2] of dims 1..3, boxes and traversal strides
+static bool make_map_4d(CUtensorMap* map, const void* base, const uint64_t (&dims)[4], const uint64_t (&st)[3],
+                        const uint32_t (&box)[4], const uint32_t (&es)[4]) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  const cuuint64_t s[3] = {st[0], st[1], st[2]};
+  const cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+  const cuuint32_t e[4] = {es[0], es[1], es[2], es[3]};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), d, s, b, e,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int conv3x3s2_weight_layout(int Cin, int Wi, int Cout) { return (Cin == 32 && Wi % 2 == 0 && Cout % 64 == 0) ? 1 : 0; }
+int conv3x3s2_packed_k(int Cin, int Wi, int Cout) { return conv3x3s2_weight_layout(Cin, Wi, Cout) ? 384 : 9 * Cin; }
+
 int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return CSSM_ERR_DIMS;
-  g.Kpad = (g.K + GB_BK - 1) / GB_BK * GB_BK;
+  const bool conv = g.ksz > 0;
+  const int wide = conv ? conv3x3s2_weight_layout(g.Cin, g.Wi, g.N) : 0;
+  // 3x3 stride-2 convs with 64-channel K blocks go through strided TMA boxes (no gather warps)
+  g.conv_tma = 0;
+  if (conv && g.ksz == 3 && g.stride == 2 && g.N % 64 == 0 && g.res == nullptr && (wide || g.Cin % 64 == 0))
+    g.conv_tma = wide ? 2 : 1;
+  const int Kw = conv ? conv3x3s2_packed_k(g.Cin, g.Wi, g.N) : g.K;      // K as the packed weights lay it out
+  g.Kpad = (Kw + GB_BK - 1) / GB_BK * GB_BK;
   g.BN = gemm_bf16_pick_bn(g.N);
   if (g.BN == 0 || g.ldw < g.Kpad || (g.ldw % 8) != 0) return CSSM_ERR_UNSUPPORTED;
   if (g.ldo % 8 != 0 || (g.res != nullptr && g.ldr % 8 != 0)) return CSSM_ERR_UNSUPPORTED;
   if (!aligned16(g.A) || !aligned16(g.Wt) || (g.out && !aligned16(g.out)) ||
       (g.out_f32 && !aligned16(g.out_f32)) || (g.res && !aligned16(g.res)))
     return CSSM_ERR_ALIGN;
-  const bool im2col = g.ksz > 0;
-  if (im2col) {
+  if (g.out_f32 != nullptr || g.out == nullptr) return CSSM_ERR_UNSUPPORTED;
+  const bool im2col = conv && !g.conv_tma;
+  if (conv) {
     if (g.Cin % 8 != 0 || g.K != g.ksz * g.ksz * g.Cin) return CSSM_ERR_UNSUPPORTED;
+    if (wide && !g.conv_tma) return CSSM_ERR_UNSUPPORTED;          // the wide weight layout has no gather path
   } else if (g.K % 8 != 0 || g.lda % 8 != 0 || g.lda < g.K) {
     return CSSM_ERR_UNSUPPORTED;
   }
@@ -437,19 +487,59 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   memset(&amap, 0, sizeof(amap));
   memset(&bmap, 0, sizeof(bmap));
   memset(&omap, 0, sizeof(omap));
-  // A: out-of-range k columns (K < Kpad) and rows (M not a multiple of 128) arrive as zeros
-  if (!im2col && !make_kmajor_map(&amap, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, GB_BM))
-    return CSSM_ERR_CUDA;
+  bool tma_out = g.BN % 64 == 0;
+  int m_tiles = (g.M + GB_BM - 1) / GB_BM;
+  if (g.conv_tma) {
+    // M tile = Bbox images x Hbox output rows x Wbox output columns, at most 128 pixels
+    g.Bimg = g.M / (g.Ho * g.Wo);
+    g.tiles_w = (g.Wo + 127) / 128;
+    g.Wbox = (g.Wo + g.tiles_w - 1) / g.tiles_w;
+    const int hmax = 128 / g.Wbox > 0 ? 128 / g.Wbox : 1;
+    g.tiles_h = (g.Ho + hmax - 1) / hmax;
+    g.Hbox = (g.Ho + g.tiles_h - 1) / g.tiles_h;
+    g.Bbox = (g.tiles_w == 1 && g.tiles_h == 1) ? 128 / (g.Wbox * g.Hbox) : 1;
+    if (g.Bbox > g.Bimg) g.Bbox = g.Bimg;
+    if (g.Bbox < 1) g.Bbox = 1;
+    m_tiles = g.tiles_w * g.tiles_h * ((g.Bimg + g.Bbox - 1) / g.Bbox);
+    const uint64_t C = (uint64_t)g.Cin;
+    bool ok;
+    if (g.conv_tma == 2) {
+      // pairs of adjacent input pixels as 64-channel "wide pixels": window columns {0,1} and {2,(3)}
+      const uint64_t W2 = (uint64_t)g.Wi / 2;
+      const uint64_t dims[4] = {64, W2, (uint64_t)g.Hi, (uint64_t)g.Bimg};
+      const uint64_t stb[3] = {128, W2 * 128, (uint64_t)g.Hi * W2 * 128};
+      const uint32_t box[4] = {64, (uint32_t)g.Wbox, (uint32_t)g.Hbox * 2, (uint32_t)g.Bbox};
+      const uint32_t es[4] = {1, 1, 2, 1};
+      ok = make_map_4d(&amap, g.A, dims, stb, box, es);
+      g.kb_per_tap = 1; g.pos_w = 2;
+    } else {
+      const uint64_t dims[4] = {C, (uint64_t)g.Wi, (uint64_t)g.Hi, (uint64_t)g.Bimg};
+      const uint64_t stb[3] = {C * 2, (uint64_t)g.Wi * C * 2, (uint64_t)g.Hi * g.Wi * C * 2};
+      const uint32_t box[4] = {64, (uint32_t)g.Wbox * 2, (uint32_t)g.Hbox * 2, (uint32_t)g.Bbox};
+      const uint32_t es[4] = {1, 2, 2, 1};
+      ok = make_map_4d(&amap, g.A, dims, stb, box, es);
+      g.kb_per_tap = g.Cin / 64; g.pos_w = 3;
+    }
+    const uint64_t N = (uint64_t)g.N;
+    const uint64_t odims[4] = {N, (uint64_t)g.Wo, (uint64_t)g.Ho, (uint64_t)g.Bimg};
+    const uint64_t ost[3] = {(uint64_t)g.ldo * 2, (uint64_t)g.Wo * g.ldo * 2, (uint64_t)g.Ho * g.Wo * g.ldo * 2};
+    const uint32_t obox[4] = {64, (uint32_t)g.Wbox, (uint32_t)g.Hbox, (uint32_t)g.Bbox};
+    const uint32_t oes[4] = {1, 1, 1, 1};
+    ok = ok && make_map_4d(&omap, g.out, odims, ost, obox, oes);
+    if (!ok) return CSSM_ERR_CUDA;
+  } else {
+    // A: out-of-range k columns (K < Kpad) and rows (M not a multiple of 128) arrive as zeros
+    if (!im2col && !make_kmajor_map(&amap, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, GB_BM))
+      return CSSM_ERR_CUDA;
+    tma_out = tma_out && make_out_map(&omap, g.out, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldo);
+  }
   if (!make_kmajor_map(&bmap, g.Wt, (uint64_t)g.N, (uint64_t)g.Kpad, (uint64_t)g.ldw, (uint32_t)g.BN))
     return CSSM_ERR_CUDA;
-  if (g.out_f32 != nullptr || g.out == nullptr) return CSSM_ERR_UNSUPPORTED;
-  const bool tma_out = g.BN % 64 == 0 &&
-                       make_out_map(&omap, g.out, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldo);
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  const int tiles = ((g.M + GB_BM - 1) / GB_BM) * (g.N / g.BN);
+  const int tiles = m_tiles * (g.N / g.BN);
   const int grid = tiles < sms ? tiles : sms;
   const size_t stage = GB_A_BYTES + (size_t)g.BN * 128u;
   g.stages = GB_MAX_STAGES;

@@ -122,14 +122,27 @@ struct Bf16GemmArgs {
   float* out_f32;            // reserved (must be nullptr)
   int ldo;
   int Kpad, BN, stages;      // filled in by the launcher
+  // conv mode through TMA (filled in by the launcher): an M tile is a patch of Bbox images x Hbox
+  // output rows x Wbox output columns (at most 128 pixels); K block kb is `kb_ch` channels from
+  // channel (kb % kb_per_tap) * kb_ch of window position kb / kb_per_tap (row = pos / pos_w,
+  // column = pos % pos_w, in units of w_unit input pixels).
+  int conv_tma, Wbox, Hbox, Bbox, tiles_w, tiles_h, kb_per_tap, pos_w, Bimg;
 };
 int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st);
+// Weight layout of the 3x3 stride-2 conv for an input of Cin channels and width Wi: 0 = the HWIO
+// kernel flattened to (9*Cin, Cout) (K = (row, column, channel)); 1 = the wide-pixel layout for
+// Cin = 32, even Wi and Cout a multiple of 64: per kernel row two K blocks of 64 = [column 0 | column 1] and
+// [column 2 | zeros], so that every K block is one 128-byte pair of adjacent input pixels.
+int conv3x3s2_weight_layout(int Cin, int Wi, int Cout);
+int conv3x3s2_packed_k(int Cin, int Wi, int Cout);
 int gemm_bf16_pick_bn(int N);
 int read_bf16_error(int* out, int clear);
 
 // ---- bf16 model kernels (csrc/shvit_kernels.cu, csrc/spectral_cl.cu) ----
 int launch_pack_wt(const float* src, int K, int N, const float* colscale, __nv_bfloat16* dst, int ldw,
                    cudaStream_t st);
+int launch_pack_conv3x3(const float* src, int Cin, int N, int Wi, const float* colscale, __nv_bfloat16* dst,
+                        cudaStream_t st);
 int launch_bn_fold(const float* scale, const float* bias, const float* mean, const float* var, int C,
                    float* oscale, float* obias, cudaStream_t st);
 int launch_affine_vec(const float* a, const float* s, const float* b, int C, float* out, cudaStream_t st);

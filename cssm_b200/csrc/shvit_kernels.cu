@@ -28,6 +28,34 @@ int launch_pack_wt(const float* src, int K, int N, const float* colscale, __nv_b
   return check_launch();
 }
 
+// 3x3 conv kernel with 32 input channels in the wide-pixel layout: src HWIO (3,3,32,N) fp32 ->
+// dst (N, 384) bf16 with k = row*128 + p*64 + j: j < 32 is column 2p, channel j; j >= 32 is column
+// 2p+1, channel j-32 (zero for the non-existent column 3).
+__global__ void pack_conv_wide_kernel(const float* __restrict__ src, int N, const float* __restrict__ colscale,
+                                      __nv_bfloat16* __restrict__ dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N * 384) return;
+  const int n = i / 384, k = i - n * 384;
+  const int ti = k >> 7, p = (k >> 6) & 1, j = k & 63;
+  const int tj = 2 * p + (j >> 5), c = j & 31;
+  float v = 0.f;
+  if (tj < 3) {
+    v = src[(size_t)((ti * 3 + tj) * 32 + c) * N + n];
+    if (colscale) v *= colscale[n];
+  }
+  dst[i] = __float2bfloat16(v);
+}
+// Packs an HWIO 3x3 kernel for the stride-2 conv of an input of width Wi (see conv3x3s2_weight_layout).
+int launch_pack_conv3x3(const float* src, int Cin, int N, int Wi, const float* colscale, __nv_bfloat16* dst,
+                        cudaStream_t st) {
+  if (conv3x3s2_weight_layout(Cin, Wi, N)) {
+    pack_conv_wide_kernel<<<(N * 384 + 255) / 256, 256, 0, st>>>(src, N, colscale, dst);
+    return check_launch();
+  }
+  const int K = 9 * Cin;
+  return launch_pack_wt(src, K, N, colscale, dst, (K + 63) / 64 * 64, st);
+}
+
 // BatchNorm (running statistics, eps 1e-5) after a bias-free conv as a per-channel scale and bias
 __global__ void bn_fold_kernel(const float* scale, const float* bias, const float* mean, const float* var,
                                int C, float* oscale, float* obias) {

@@ -56,6 +56,19 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* map, int
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1),
         "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* map, int c0, int c1, int c2,
+                                            int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const void* map, const void* smem_src, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1),
+                 "r"(c2), "r"(c3) : "memory");
+}
 // TMA tensor stores shared -> global (bulk_group completion).  `map` is a CUtensorMap passed
 // to the kernel as a __grid_constant__ parameter; coordinates are innermost first.
 __device__ __forceinline__ void tma_store_2d(const void* map, const void* smem_src, int c0, int c1) {

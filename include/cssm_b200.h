@@ -575,8 +575,12 @@ int cssm_bf16_pack_weight(const float* kernel, int32_t K, int32_t N, const float
 int cssm_bf16_gemm(const void* A, int32_t M, int32_t K, const void* wt, int32_t N, const float* bias,
                    int32_t act, const void* res, void* out, void* stream);
 /* 3x3 stride-2 'SAME' convolution (nn.Conv inside ConvBN, shvit.py:45-54) as an implicit GEMM:
- * x (B,Hi,Wi,Cin) bf16 -> out (B,ceil(Hi/2),ceil(Wi/2),Cout) bf16; `wt` = the HWIO kernel viewed as
- * (9*Cin, Cout) and packed by cssm_bf16_pack_weight (col_scale = the BatchNorm factor). */
+ * x (B,Hi,Wi,Cin) bf16 -> out (B,ceil(Hi/2),ceil(Wi/2),Cout) bf16; `wt` = the HWIO kernel (3,3,Cin,Cout)
+ * packed by cssm_bf16_pack_conv3x3s2_weight into (Cout, cssm_bf16_conv3x3s2_packed_ld(Cin, Wi, Cout)) bf16
+ * (col_scale = the BatchNorm factor; the layout depends on Cin, Cout and the parity of the input width). */
+int32_t cssm_bf16_conv3x3s2_packed_ld(int32_t Cin, int32_t Wi, int32_t Cout);
+int cssm_bf16_pack_conv3x3s2_weight(const float* kernel, int32_t Cin, int32_t Cout, int32_t Wi,
+                                    const float* col_scale, void* wt, void* stream);
 int cssm_bf16_conv3x3s2(const void* x, int32_t B, int32_t Hi, int32_t Wi, int32_t Cin, const void* wt,
                         int32_t Cout, const float* bias, int32_t act, void* out, void* stream);
 

@@ -58,7 +58,9 @@ def test_bf16_gemm(M, K, N, act, res):
 
 @pytest.mark.parametrize("B,Hi,Wi,Cin,Cout", [(2, 16, 16, 32, 64), (3, 14, 14, 128, 256),
                                               (2, 7, 9, 64, 128), (1, 56, 56, 64, 128),
-                                              (2, 112, 112, 32, 64)])
+                                              (2, 112, 112, 32, 64), (5, 14, 14, 256, 384),
+                                              (2, 9, 7, 32, 64), (3, 28, 28, 128, 256), (2, 12, 20, 16, 32),
+                                              (1, 300, 260, 64, 64)])
 def test_bf16_conv3x3s2(B, Hi, Wi, Cin, Cout):
     L = lib()
     g = torch.Generator(device="cuda").manual_seed(Hi * Cin)
@@ -66,7 +68,9 @@ def test_bf16_conv3x3s2(B, Hi, Wi, Cin, Cout):
     W = torch.randn((3, 3, Cin, Cout), device="cuda", generator=g) / (9 * Cin) ** 0.5
     scale = 1.0 + 0.2 * torch.randn((Cout,), device="cuda", generator=g)
     b = torch.randn((Cout,), device="cuda", generator=g)
-    wt = _pack(L, W, 9 * Cin, Cout, scale)
+    wt = torch.empty((Cout, L.cssm_bf16_conv3x3s2_packed_ld(Cin, Wi, Cout)), dtype=torch.bfloat16, device="cuda")
+    check(L.cssm_bf16_pack_conv3x3s2_weight(W.data_ptr(), Cin, Cout, Wi, scale.data_ptr(), wt.data_ptr(), _st()),
+          "pack_conv")
     Ho, Wo = (Hi + 1) // 2, (Wi + 1) // 2
     out = torch.empty((B, Ho, Wo, Cout), dtype=torch.bfloat16, device="cuda")
     check(L.cssm_bf16_conv3x3s2(x.data_ptr(), B, Hi, Wi, Cin, wt.data_ptr(), Cout, b.data_ptr(), 0,
