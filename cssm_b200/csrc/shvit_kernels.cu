@@ -442,9 +442,58 @@ layernorm_cl_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * __ldg(scale + ck * 8 + j) + __ldg(bias + ck * 8 + j);
   *reinterpret_cast<uint4*>(y + px * C + ck * 8) = pack8(o);
 }
+// The same for C / 8 a power of two of at most 32 lanes: the lanes of a pixel are a segment of one
+// warp, so the two reductions are shuffles and the kernel needs no barrier.
+template <int G>
+__global__ void __launch_bounds__(256)
+layernorm_cl_shfl_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                         const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, long long npix) {
+  constexpr int C = G * 8;
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long px = gid / G;
+  const int ck = (int)(gid % G);
+  const bool on = px < npix;
+  float v[8];
+  if (on) unpack8(__ldg(reinterpret_cast<const uint4*>(x + px * C + ck * 8)), v);
+  else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s += v[j];
+#pragma unroll
+  for (int o = G / 2; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  const float mean = s * (1.0f / C);
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { const float d = v[j] - mean; q = fmaf(d, d, q); }
+#pragma unroll
+  for (int o = G / 2; o; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+  if (!on) return;
+  const float rstd = rsqrtf(q * (1.0f / C) + 1e-6f);
+  const float4 s0 = __ldg(reinterpret_cast<const float4*>(scale + ck * 8)), s1 = __ldg(reinterpret_cast<const float4*>(scale + ck * 8 + 4));
+  const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + ck * 8)), b1 = __ldg(reinterpret_cast<const float4*>(bias + ck * 8 + 4));
+  const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  const float bi[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  float o8[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o8[j] = fmaf((v[j] - mean) * rstd, sc[j], bi[j]);
+  *reinterpret_cast<uint4*>(y + px * C + ck * 8) = pack8(o8);
+}
+
 int launch_layernorm_cl(const __nv_bfloat16* x, const float* scale, const float* bias, __nv_bfloat16* y,
                         long long npix, int C, cudaStream_t st) {
   if (C % 8 != 0 || C / 8 > 256) return CSSM_ERR_UNSUPPORTED;
+  if ((C == 32 || C == 64 || C == 128 || C == 256) && aligned16(scale) && aligned16(bias)) {
+    const int G = C / 8;
+    const long long blocks = (npix * G + 255) / 256;
+    if (G == 4) layernorm_cl_shfl_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(x, scale, bias, y, npix);
+    else if (G == 8) layernorm_cl_shfl_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(x, scale, bias, y, npix);
+    else if (G == 16) layernorm_cl_shfl_kernel<16><<<(unsigned)blocks, 256, 0, st>>>(x, scale, bias, y, npix);
+    else layernorm_cl_shfl_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(x, scale, bias, y, npix);
+    return check_launch();
+  }
   const int chunks = C / 8, ppb = 256 / chunks;
   const long long blocks = (npix + ppb - 1) / ppb;
   layernorm_cl_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, scale, bias, y, npix, C, ppb);
@@ -566,23 +615,54 @@ int launch_pool_cl(const __nv_bfloat16* x, int Nimg, int P, int C, int use_max, 
   return check_launch();
 }
 
-// logits[n, k] = pooled[n, :] . W[:, k] + b[k], float32 (the reference keeps its head in float32)
-__global__ void head_kernel(const float* __restrict__ pooled, const float* __restrict__ W,
-                            const float* __restrict__ b, float* __restrict__ logits, int C, int K) {
-  extern __shared__ float ps[];
-  const int n = blockIdx.y;
-  for (int i = threadIdx.x; i < C; i += blockDim.x) ps[i] = pooled[(size_t)n * C + i];
+// logits[n, k] = pooled[n, :] . W[:, k] + b[k], float32 (the reference keeps its head in float32).
+// A CTA computes 128 classes for 8 samples, so a weight read feeds eight accumulators.
+__global__ void __launch_bounds__(128)
+head_kernel(const float* __restrict__ pooled, const float* __restrict__ W, const float* __restrict__ b,
+            float* __restrict__ logits, int Nimg, int C, int K) {
+  extern __shared__ __align__(16) float ps[];        // [8][C], C a multiple of 4 for the float4 reads
+  const int n0 = blockIdx.y * 8;
+  for (int i = threadIdx.x; i < 8 * C; i += blockDim.x) {
+    const int j = i / C, c = i - j * C;
+    ps[i] = n0 + j < Nimg ? pooled[(size_t)(n0 + j) * C + c] : 0.f;
+  }
   __syncthreads();
   const int k = blockIdx.x * blockDim.x + threadIdx.x;
   if (k >= K) return;
-  float acc = b[k];
-  for (int c = 0; c < C; ++c) acc = fmaf(ps[c], __ldg(W + (size_t)c * K + k), acc);
-  logits[(size_t)n * K + k] = acc;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = b[k];
+  // eight weight loads in flight per thread; the pooled values are read as float4 (one shared-memory
+  // load per four channels: the loop is bound by the number of shared-memory instructions otherwise)
+  int c = 0;
+  for (; c + 8 <= C; c += 8) {
+    float w[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) w[u] = __ldg(W + (size_t)(c + u) * K + k);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 p0 = *reinterpret_cast<const float4*>(ps + j * C + c);
+      const float4 p1 = *reinterpret_cast<const float4*>(ps + j * C + c + 4);
+      acc[j] = fmaf(p0.x, w[0], acc[j]); acc[j] = fmaf(p0.y, w[1], acc[j]);
+      acc[j] = fmaf(p0.z, w[2], acc[j]); acc[j] = fmaf(p0.w, w[3], acc[j]);
+      acc[j] = fmaf(p1.x, w[4], acc[j]); acc[j] = fmaf(p1.y, w[5], acc[j]);
+      acc[j] = fmaf(p1.z, w[6], acc[j]); acc[j] = fmaf(p1.w, w[7], acc[j]);
+    }
+  }
+  for (; c < C; ++c) {
+    const float w = __ldg(W + (size_t)c * K + k);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = fmaf(ps[j * C + c], w, acc[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (n0 + j < Nimg) logits[(size_t)(n0 + j) * K + k] = acc[j];
 }
 int launch_head(const float* pooled, const float* W, const float* b, float* logits, int Nimg, int C, int K,
                 cudaStream_t st) {
-  dim3 grid((K + 127) / 128, Nimg);
-  head_kernel<<<grid, 128, (size_t)C * 4, st>>>(pooled, W, b, logits, C, K);
+  if (C % 4 != 0) return CSSM_ERR_UNSUPPORTED;
+  dim3 grid((K + 127) / 128, (Nimg + 7) / 8);
+  head_kernel<<<grid, 128, (size_t)8 * C * 4, st>>>(pooled, W, b, logits, Nimg, C, K);
   return check_launch();
 }
 
