@@ -263,21 +263,21 @@ dwconv_cl_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ 
 }
 
 // Depthwise KS x KS 'SAME' conv, tiled through shared memory (the path of every bf16 output).
-// A CTA of 256 threads owns a tile of 8 output rows x TW columns x CS channels (256 / CS column
-// groups of four columns each) of one image and one channel slice; the bf16 input patch with its
-// halo is staged with 16-byte loads as it lies in memory ([row][column][channel]; the per-sample
-// LayerNorm affine, when given, is applied while staging and the result rounded to bf16, zeros stay
-// zeros outside the image); thread = one channel of one column group, with its KS*KS weights in
-// registers; for each of its four columns it walks the input rows of the window once (KS two-byte
-// shared-memory loads per row, conflict-free because the lanes of a warp are consecutive channels)
-// and feeds each value to the output rows it belongs to.
-template <int KS, int CS>
-__global__ void __launch_bounds__(256)
+// A CTA of 128 threads owns a tile of 8 output rows x 16 columns x 64 channels of one image and one
+// channel slice; the bf16 input patch with its halo is staged with 16-byte loads as it lies in
+// memory ([row][column][channel]; the per-sample LayerNorm affine, when given, is applied while
+// staging and the result rounded to bf16, zeros stay zeros outside the image).  Thread = one PAIR of
+// channels of one column group (a warp = the 32 channel pairs of the slice), its KS*KS weight pairs in
+// registers; for each of its four columns it walks the input rows of the window once: KS four-byte
+// shared-memory loads per row (conflict-free: the lanes of a warp are consecutive pairs), each value
+// pair feeds the output rows it belongs to with packed f32x2 FMAs (two channels per instruction).
+template <int KS>
+__global__ void __launch_bounds__(128)
 dwconv_tiled_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
                     const float* __restrict__ bias, const float* __restrict__ pre_a,
                     const float* __restrict__ pre_b, __nv_bfloat16* __restrict__ y, int H, int W, int C,
                     int add_centre, int gelu) {
-  constexpr int P = (KS - 1) / 2, CG = 256 / CS, TW = CG * 4, TH = 8, PW = TW + KS - 1, PH = TH + KS - 1;
+  constexpr int CS = 64, P = (KS - 1) / 2, CG = 4, NC = 4, TW = CG * NC, TH = 8, PW = TW + KS - 1, PH = TH + KS - 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [PH][PW][CS]
   const int tiles_w = (W + TW - 1) / TW, tiles_h = (H + TH - 1) / TH, slices = C / CS;
@@ -285,76 +285,99 @@ dwconv_tiled_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   const int sl = bid % slices; bid /= slices;
   const int tr = bid % (tiles_w * tiles_h), n = bid / (tiles_w * tiles_h);
   const int h0 = (tr / tiles_w) * TH, w0 = (tr % tiles_w) * TW, cs0 = sl * CS;
-  const int c = threadIdx.x % CS, cgp = threadIdx.x / CS;
-  // stage the patch (zeros outside the image)
+  const int cp = threadIdx.x & 31, cgp = threadIdx.x >> 5;                 // channel pair, column group
+  // stage the patch (zeros outside the image): asynchronous 16-byte copies, all in flight at once
+  // (with the LayerNorm affine the values pass through registers instead)
   constexpr int CH = CS / 8;                         // 16-byte chunks per pixel of the slice
   const __nv_bfloat16* xn = x + (size_t)n * H * W * C + cs0;
-  for (int q = threadIdx.x; q < PH * PW * CH; q += 256) {
-    const int ck = q % CH, pp = q / CH, pc = pp % PW, pr = pp / PW;
-    const int hi = h0 + pr - P, wi = w0 + pc - P;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (hi >= 0 && hi < H && wi >= 0 && wi < W) {
-      v = __ldg(reinterpret_cast<const uint4*>(xn + ((size_t)hi * W + wi) * C + ck * 8));
-      if (pre_a != nullptr) {
-        float f[8];
-        unpack8(v, f);
-        const float* pa = pre_a + (size_t)n * C + cs0 + ck * 8;
-        const float* pb = pre_b + (size_t)n * C + cs0 + ck * 8;
+  for (int pr = 0; pr < PH; ++pr) {
+    const int hi = h0 + pr - P;
+    const bool hin = hi >= 0 && hi < H;
+    for (int q = threadIdx.x; q < PW * CH; q += 128) {
+      const int ck = q & (CH - 1), pc = q / CH;
+      const int wi = w0 + pc - P;
+      const bool in = hin && wi >= 0 && wi < W;
+      __nv_bfloat16* dst = tile + ((size_t)pr * PW + pc) * CS + ck * 8;
+      const __nv_bfloat16* src = xn + ((size_t)(in ? hi : 0) * W + (in ? wi : 0)) * C + ck * 8;
+      if (pre_a == nullptr) {
+        // src-size 0 writes zeros
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(in ? 16 : 0) : "memory");
+      } else {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (in) {
+          float f[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(src)), f);
+          const float* pa = pre_a + (size_t)n * C + cs0 + ck * 8;
+          const float* pb = pre_b + (size_t)n * C + cs0 + ck * 8;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = fmaf(__ldg(pa + j), f[j], __ldg(pb + j));
-        v = pack8(f);
+          for (int j = 0; j < 8; ++j) f[j] = fmaf(__ldg(pa + j), f[j], __ldg(pb + j));
+          v = pack8(f);
+        }
+        *reinterpret_cast<uint4*>(dst) = v;
       }
     }
-    *reinterpret_cast<uint4*>(tile + (size_t)pp * CS + ck * 8) = v;
   }
-  float wr[KS * KS];
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  unsigned long long wr[KS * KS];
 #pragma unroll
-  for (int t = 0; t < KS * KS; ++t) wr[t] = wk ? __ldg(wk + (size_t)t * C + cs0 + c) : 0.f;
-  if (add_centre) wr[P * KS + P] += 1.0f;            // x + conv(x)
-  const float bz = (wk && bias) ? __ldg(bias + cs0 + c) : 0.f;
+  for (int t = 0; t < KS * KS; ++t) {
+    const float2 w2 = wk ? __ldg(reinterpret_cast<const float2*>(wk + (size_t)t * C + cs0) + cp) : make_float2(0.f, 0.f);
+    wr[t] = pk2(w2.x + ((add_centre && t == P * KS + P) ? 1.0f : 0.f),
+                w2.y + ((add_centre && t == P * KS + P) ? 1.0f : 0.f));     // x + conv(x)
+  }
+  const float2 b2 = (wk && bias) ? __ldg(reinterpret_cast<const float2*>(bias + cs0) + cp) : make_float2(0.f, 0.f);
+  const unsigned long long bz = pk2(b2.x, b2.y);
+  const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(tile);        // [PH][PW][32 pairs]
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 #pragma unroll 1
-  for (int cc = 0; cc < 4; ++cc) {
-    const int wl = cgp * 4 + cc;                     // column inside the tile
+  for (int cc = 0; cc < NC; ++cc) {
+    const int wl = cgp * NC + cc;                    // column inside the tile
     if (w0 + wl >= W) break;
-    float acc[TH];
+    unsigned long long acc[TH];
 #pragma unroll
     for (int o = 0; o < TH; ++o) acc[o] = bz;
 #pragma unroll
     for (int ir = 0; ir < PH; ++ir) {
-      float xv[KS];
+      unsigned long long xv[KS];
 #pragma unroll
-      for (int tj = 0; tj < KS; ++tj) xv[tj] = __bfloat162float(tile[((size_t)ir * PW + wl + tj) * CS + c]);
+      for (int tj = 0; tj < KS; ++tj) {
+        const uint32_t u = tile32[((size_t)ir * PW + wl + tj) * 32 + cp];
+        xv[tj] = pk2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+      }
 #pragma unroll
       for (int o = 0; o < TH; ++o) {
         const int ti = ir - o;
         if (ti < 0 || ti >= KS) continue;
 #pragma unroll
-        for (int tj = 0; tj < KS; ++tj) acc[o] = fmaf(xv[tj], wr[ti * KS + tj], acc[o]);
+        for (int tj = 0; tj < KS; ++tj) acc[o] = fma2(xv[tj], wr[ti * KS + tj], acc[o]);
       }
     }
 #pragma unroll
     for (int o = 0; o < TH; ++o) {
       const int h = h0 + o;
       if (h >= H) continue;
-      const float v = gelu ? gelu_tanh_f(acc[o]) : acc[o];
-      y[(((size_t)n * H + h) * W + w0 + wl) * C + cs0 + c] = __float2bfloat16(v);
+      float va, vb;
+      upk2(acc[o], va, vb);
+      if (gelu) gelu_tanh_x2(va, vb);
+      *reinterpret_cast<uint32_t*>(y + (((size_t)n * H + h) * W + w0 + wl) * C + cs0 + 2 * cp) = float2_to_bf16x2(va, vb);
     }
   }
 }
 
-template <int KS, int CS>
+template <int KS>
 static int launch_dwconv_tiled(const __nv_bfloat16* x, const float* wk, const float* bias, const float* pre_a,
                                const float* pre_b, __nv_bfloat16* y, int Nimg, int H, int W, int C,
                                int add_centre, int gelu, cudaStream_t st) {
-  constexpr int CG = 256 / CS, TW = CG * 4, TH = 8;
-  const size_t smem = (size_t)(TH + KS - 1) * (TW + KS - 1) * CS * 2;
-  cudaError_t e = cudaFuncSetAttribute(dwconv_tiled_kernel<KS, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  constexpr int TW = 16, TH = 8;
+  const size_t smem = (size_t)(TH + KS - 1) * (TW + KS - 1) * 64 * 2;
+  cudaError_t e = cudaFuncSetAttribute(dwconv_tiled_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  const long long grid = (long long)Nimg * ((H + TH - 1) / TH) * ((W + TW - 1) / TW) * (C / CS);
-  dwconv_tiled_kernel<KS, CS><<<(unsigned)grid, 256, smem, st>>>(x, wk, bias, pre_a, pre_b, y, H, W, C,
-                                                                  add_centre, gelu);
+  const long long grid = (long long)Nimg * ((H + TH - 1) / TH) * ((W + TW - 1) / TW) * (C / 64);
+  dwconv_tiled_kernel<KS><<<(unsigned)grid, 128, smem, st>>>(x, wk, bias, pre_a, pre_b, y, H, W, C,
+                                                              add_centre, gelu);
   return check_launch();
 }
 
@@ -362,14 +385,9 @@ int launch_dwconv_cl(const __nv_bfloat16* x, const float* wk, const float* bias,
                      const float* pre_b, __nv_bfloat16* y, float* y_f32, int Nimg, int H, int W, int C,
                      int ks, int add_centre, int gelu, cudaStream_t st) {
   if (C % 8 != 0 || (ks != 3 && ks != 7)) return CSSM_ERR_UNSUPPORTED;
-  if (y_f32 == nullptr && C % 32 == 0) {
-    // 64-channel slices give 16-column tiles; narrow images and C not a multiple of 64 take 32
-    const bool c64 = C % 64 == 0;
-    if (ks == 7)
-      return c64 ? launch_dwconv_tiled<7, 64>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st)
-                 : launch_dwconv_tiled<7, 32>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
-    return c64 ? launch_dwconv_tiled<3, 64>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st)
-               : launch_dwconv_tiled<3, 32>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
+  if (y_f32 == nullptr && C % 64 == 0 && (wk == nullptr || (aligned16(wk) && (bias == nullptr || aligned16(bias))))) {
+    if (ks == 7) return launch_dwconv_tiled<7>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
+    return launch_dwconv_tiled<3>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
   }
   constexpr int RH = 4;
   const size_t smem = (size_t)(ks * ks * C + C) * 4;
