@@ -10,7 +10,8 @@ LIB_PATH = os.path.join(HERE, "libcssm_b200.so")
 
 ROPE_MODES = {"none": 0, "spatiotemporal": 1, "temporal": 2, "spatial_only": 3, "mrope": 4}
 GATE_TYPES = {"dense": 0, "factored": 1}
-DELTANET_GATE_TYPES = {"dense": 0, "factored": 1, "channel": 2}   # CSSM_GATE_CHANNEL: DeltaNet only
+DELTANET_GATE_TYPES = {"dense": 0, "factored": 1, "channel": 2}
+GDN_GATE_TYPES = {"dense": 0, "factored": 1, "channel": 2, "scalar": 3}
 GATE_ACTS = {"softplus": 0, "sigmoid": 1, "exp": 2}
 
 

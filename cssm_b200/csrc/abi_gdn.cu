@@ -10,7 +10,7 @@ static SpectralPath gdn_path(const cssm_gdn_desc& d) {
   return (p != PATH_GENERIC && d.delta_key_dim == 4) ? p : PATH_GENERIC;
 }
 
-struct GdnPlan { size_t what, rope_t, rope_h, rope_w, rope_nz, tcode, total; };
+struct GdnPlan { size_t what, rope_t, rope_h, rope_w, rope_nz, tcode, gw, gb, total; };
 static GdnPlan gdn_plan_layout(const cssm_gdn_desc& d) {
   GdnPlan p;
   const size_t Wf = d.W / 2 + 1, n2 = d.C / 2, nh = d.C / d.delta_key_dim;
@@ -21,11 +21,29 @@ static GdnPlan gdn_plan_layout(const cssm_gdn_desc& d) {
   p.rope_w = off; off += round_up((size_t)d.W * n2 * sizeof(float2), 256);
   p.rope_nz = off; off += round_up(n2 * sizeof(float), 256);
   p.tcode = off;  off += round_up((size_t)d.T * d.C * sizeof(float), 256);
+  // channel gates: the B_k, B_v 1x1-conv kernels packed side by side as one (C, 2C) matrix
+  const bool chsp = d.gate_type == CSSM_GATE_CHANNEL && d.use_input_gates;
+  p.gw = off;     off += chsp ? round_up((size_t)d.C * 2 * d.C * sizeof(float), 256) : 0;
+  p.gb = off;     off += chsp ? round_up((size_t)2 * d.C * sizeof(float), 256) : 0;
   p.total = off;
   return p;
 }
 
-struct GdnWs { size_t xdw, qkv, gate, ctx_part, ab, bkv, state, total; };
+// k, v planes times their spatial gate planes: for every frame the 2C planes C..3C of the
+// (frames, 3C, HW) q/k/v buffer are multiplied by the 2C planes of the (frames, 2C, HW) gate buffer
+__global__ void __launch_bounds__(256) gdn_kv_gate_kernel(float* __restrict__ qkv, const float* __restrict__ gsp,
+                                                          size_t per_frame4, size_t total4) {
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total4) return;
+  const size_t fr = i / per_frame4, r = i - fr * per_frame4;
+  float4* d = reinterpret_cast<float4*>(qkv) + fr * (per_frame4 + per_frame4 / 2) + per_frame4 / 2 + r;
+  const float4 gv = __ldg(reinterpret_cast<const float4*>(gsp) + i);
+  float4 v = *d;
+  v.x *= gv.x; v.y *= gv.y; v.z *= gv.z; v.w *= gv.w;
+  *d = v;
+}
+
+struct GdnWs { size_t xdw, qkv, gate, ctx_part, ab, bkv, gsp, state, total; };
 static GdnWs gdn_ws_layout(const cssm_gdn_desc& d) {
   GdnWs l;
   const size_t BT = (size_t)d.B * d.T, HW = (size_t)d.H * d.W, NB = (size_t)d.H * (d.W / 2 + 1);
@@ -35,8 +53,11 @@ static GdnWs gdn_ws_layout(const cssm_gdn_desc& d) {
   l.qkv = off;      off += round_up(BT * 3 * d.C * HW * sizeof(float), 256);
   l.gate = off;     off += round_up(BT * d.C * HW * sizeof(float), 256);
   l.ctx_part = off; off += round_up(BT * d.H * d.C * sizeof(float), 256);
-  l.ab = off;       off += round_up(BT * NB * sizeof(float2), 256);
+  // channel gates: one {alpha, beta} map per (frame, head); the spatial input gates are planes
+  const bool chan = d.gate_type == CSSM_GATE_CHANNEL;
+  l.ab = off;       off += round_up(BT * (chan ? nh : 1) * NB * sizeof(float2), 256);
   l.bkv = off;      off += round_up(BT * HW * sizeof(float2), 256);
+  l.gsp = off;      off += (chan && d.use_input_gates) ? round_up(BT * 2 * d.C * HW * sizeof(float), 256) : 0;
   l.state = off;    off += round_up((size_t)d.B * nh * dk * dk * NB * sizeof(cf), 256);
   l.total = off;
   return l;
@@ -50,8 +71,7 @@ static int gdn_validate(const cssm_gdn_desc* d) {
   if (d->C % d->delta_key_dim != 0) return CSSM_ERR_DIMS;          // cssm.py:4690
   if (d->delta_key_dim > 4 || d->C % 4 != 0) return CSSM_ERR_UNSUPPORTED;
   if (d->rope_mode < CSSM_ROPE_NONE || d->rope_mode > CSSM_ROPE_MROPE) return CSSM_ERR_UNSUPPORTED;
-  if (d->gate_type != CSSM_GATE_DENSE && d->gate_type != CSSM_GATE_FACTORED)
-    return CSSM_ERR_UNSUPPORTED;
+  if (d->gate_type < CSSM_GATE_DENSE || d->gate_type > CSSM_GATE_SCALAR) return CSSM_ERR_UNSUPPORTED;
   if (d->short_conv_size < 0 || d->short_conv_size > 8) return CSSM_ERR_UNSUPPORTED;
   if (d->output_norm != 0 && d->output_norm != 1) return CSSM_ERR_UNSUPPORTED;
   if (d->output_gate_act != 0 && d->output_gate_act != 1) return CSSM_ERR_UNSUPPORTED;
@@ -111,6 +131,18 @@ int cssm_gdn_plan_init(const cssm_gdn_desc* d, const cssm_gdn_weights* w, void* 
                          (float2*)(base + p.rope_w), (float*)(base + p.rope_nz), d->T, d->H, d->W,
                          d->C, d->rope_mode, d->rope_base, st);
   if (s != CSSM_OK) return s;
+  if (d->gate_type == CSSM_GATE_CHANNEL && d->use_input_gates) {
+    // gate_kernel[2], [3] = B_k, B_v 1x1-conv kernels (1,1,C,C) -> one (C, 2C) matrix
+    const size_t cb = (size_t)d->C * sizeof(float);
+    for (int i = 0; i < 2; ++i) {
+      if (!w->gate_kernel[2 + i] || !w->gate_bias[2 + i]) return CSSM_ERR_NULL;
+      cudaError_t e = cudaMemcpy2DAsync(base + p.gw + i * cb, 2 * cb, w->gate_kernel[2 + i], cb, cb,
+                                        (size_t)d->C, cudaMemcpyDeviceToDevice, st);
+      if (e == cudaSuccess)
+        e = cudaMemcpyAsync(base + p.gb + i * cb, w->gate_bias[2 + i], cb, cudaMemcpyDeviceToDevice, st);
+      if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+    }
+  }
   return launch_tcode((float*)(base + p.tcode), d->T, d->C, d->rope_base, st);
 }
 
@@ -159,6 +191,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
     // preconditions asserted by the reference (cssm.py:4354-4370)
     if (d && (d->short_conv_size != 0 || d->use_input_gates != 0 || d->rope_mode != CSSM_ROPE_NONE))
       return CSSM_ERR_UNSUPPORTED;
+    if (d && d->gate_type >= CSSM_GATE_CHANNEL) return CSSM_ERR_UNSUPPORTED;   // dense and factored maps only
   }
   int s = gdn_validate(d);
   if (s != CSSM_OK) return s;
@@ -171,6 +204,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   if (d->short_conv_size > 0)
     for (int i = 0; i < 3; ++i)
       if (!w->conv_t_kernel[i] || !w->conv_t_bias[i]) return CSSM_ERR_NULL;
+  const bool chan = d->gate_type == CSSM_GATE_CHANNEL;
   const int ngate = d->use_input_gates ? 4 : 2;
   const int nptr = d->gate_type == CSSM_GATE_FACTORED ? 2 * ngate : ngate;
   for (int i = 0; i < nptr; ++i)
@@ -247,6 +281,7 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
   ga.BT = d->B * d->T; ga.T = d->T; ga.C = C; ga.H = d->H; ga.W = d->W;
   ga.ctx_per_clip = static_image;
   ga.gate_type = d->gate_type; ga.use_input_gates = d->use_input_gates; ga.path = gdn_path(*d);
+  ga.nh = C / d->delta_key_dim;
   for (int i = 0; i < nptr; ++i) { ga.gk[i] = w->gate_kernel[i]; ga.gb[i] = w->gate_bias[i]; }
   ga.ab = (float2*)(ws + l.ab); ga.bkv = (float2*)(ws + l.bkv);
   if ((s = launch_gdn_gates(ga, st)) != CSSM_OK) return s;
@@ -261,13 +296,13 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
     memset(&ta, 0, sizeof(ta));
     ta.buf = qkv; ta.B = d->B; ta.T = Tdata; ta.C = C; ta.HW = HW; ta.kt = d->short_conv_size;
     for (int i = 0; i < 3; ++i) { ta.wt[i] = w->conv_t_kernel[i]; ta.bt[i] = w->conv_t_bias[i]; }
-    ta.bkv = d->use_input_gates ? (const float2*)(ws + l.bkv) : nullptr;
+    ta.bkv = (d->use_input_gates && !chan) ? (const float2*)(ws + l.bkv) : nullptr;
     s = launch_qkv_temporal_conv(ta, st);
     if (s == CSSM_OK) tconv_done = true;
     else if (s != CSSM_ERR_UNSUPPORTED) return s;
   }
   for (int i = 0; i < 3 && !tconv_done; ++i) {
-    const bool has_post = d->use_input_gates && i > 0;
+    const bool has_post = d->use_input_gates && !chan && i > 0;
     if (d->short_conv_size == 0 && !has_post) continue;
     StencilArgs sa;
     memset(&sa, 0, sizeof(sa));
@@ -280,11 +315,30 @@ int cssm::gdn_forward_internal(const cssm_gdn_desc* d, const cssm_gdn_weights* w
     if ((s = launch_plane_stencil(sa, st)) != CSSM_OK) return s;
   }
 
+  if (chan && d->use_input_gates) {
+    // spatial gates sigmoid(Conv1x1(rotated x)) -> planes (BT, 2C, H, W): B_k, B_v; k *= B_k, v *= B_v
+    float* gsp = (float*)(ws + l.gsp);
+    memset(&g, 0, sizeof(g));
+    g.M = BT * HW; g.N = 2 * C; g.K = C; g.HW = HW;
+    g.A = x; g.rope_t = rt; g.rope_h = rh; g.rope_w = rw; g.rope_nz = rnz;
+    if (x_bcast) { g.a_fdiv = d->T; g.a_fmul = 1; g.a_fadd = 0; }
+    g.Wk = (const float*)(pl + p.gw); g.bias = (const float*)(pl + p.gb);      // packed by plan_init
+    g.out = gsp; g.o_planes = 2 * C; g.o_plane0 = 0;
+    g.T = Tdata; g.H = d->H; g.W = d->W;
+    g.out_act = 2; g.act_n0 = 0;
+    if ((s = launch_gemm<false, true>(g, st)) != CSSM_OK) return s;
+    if (((size_t)C * HW) % 8 != 0) return CSSM_ERR_UNSUPPORTED;
+    const size_t per_frame4 = (size_t)2 * C * HW / 4, total4 = per_frame4 * BT;
+    gdn_kv_gate_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, st>>>(qkv, gsp, per_frame4, total4);
+    if ((s = check_launch()) != CSSM_OK) return s;
+  }
+
   // 6. fused spectral recurrence; the output planes overwrite the v planes
   mark(5, st);
   GdnSpectralArgs sp;
   memset(&sp, 0, sizeof(sp));
   sp.qkv = qkv; sp.what = (const cf*)(pl + p.what); sp.ab = ga.ab; sp.state = (cf*)(ws + l.state);
+  sp.ab_heads = chan ? C / d->delta_key_dim : 1;
   sp.B = d->B; sp.T = d->T; sp.C = C; sp.H = d->H; sp.W = d->W; sp.dk = d->delta_key_dim;
   sp.use_l2 = d->use_spectral_l2_norm;
   sp.last_only = last_only;

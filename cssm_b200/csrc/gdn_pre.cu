@@ -257,6 +257,25 @@ __global__ void __launch_bounds__(256) gdn_gates_kernel(const GdnGateArgs g) {
         g.bkv[(size_t)fr * HW + px] = make_float2(sigmoid_f(vec[off[4] + h] + vec[off[5] + w]),
                                                   sigmoid_f(vec[off[6] + h] + vec[off[7] + w]));
       }
+  } else if (g.gate_type == CSSM_GATE_SCALAR || g.gate_type == CSSM_GATE_CHANNEL) {
+    // scalar: one value per frame and gate, Dense(1)(ctx) (cssm.py:4825-4833).  channel: alpha, beta
+    // per head, Dense(n_h)(ctx) (cssm.py:4808-4810); its spatial gates are a 1x1 conv of the block
+    // input and are applied elsewhere.  The maps are constant over the bins.
+    const bool chan = g.gate_type == CSSM_GATE_CHANNEL;
+    const int nout = chan ? g.nh : 1, nvec = chan ? 2 : ngate;
+    for (int o = tid; o < nvec * nout; o += blockDim.x) {
+      const int gi = o / nout, col = o - gi * nout;
+      float acc = g.gb[gi][col];
+      for (int c = 0; c < g.C; ++c) acc = fmaf(ctx[c], g.gk[gi][(size_t)c * nout + col], acc);
+      vec[o] = sigmoid_f(acc);
+    }
+    __syncthreads();
+    for (int i = tid; i < nout * NB; i += blockDim.x) {
+      const int hh = i / NB;
+      g.ab[((size_t)fr * nout + hh) * NB + (i - hh * NB)] = make_float2(0.1f + 0.89f * vec[hh], vec[nout + hh]);
+    }
+    if (!chan && g.use_input_gates)
+      for (int px = tid; px < HW; px += blockDim.x) g.bkv[(size_t)fr * HW + px] = make_float2(vec[2], vec[3]);
   } else {
     for (int bin = tid; bin < NB; bin += blockDim.x) {
       const int kh = bin / Wf, kw = bin % Wf;
@@ -281,7 +300,7 @@ __global__ void __launch_bounds__(256) gdn_gates_kernel(const GdnGateArgs g) {
 }
 
 int launch_gdn_gates(const GdnGateArgs& g, cudaStream_t st) {
-  const size_t smem = (size_t)(g.C + 4 * g.H + 2 * (g.W / 2 + 1) + 2 * g.W) * sizeof(float);
+  const size_t smem = (size_t)(g.C + 4 * g.H + 2 * (g.W / 2 + 1) + 2 * g.W + 2 * g.nh + 8) * sizeof(float);
   gdn_gates_kernel<<<g.BT, 256, smem, st>>>(g);
   return check_launch();
 }

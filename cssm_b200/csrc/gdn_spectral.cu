@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpec
       const float kn = rsqrtf(ks + 1e-6f);
       for (int i = 0; i < dk; ++i) SK[(size_t)i * NB + o] = mk(kv[i].x * kn, kv[i].y * kn);
     }
-    const float2* ab = a.ab + (a.static_image ? (size_t)b * a.T : frame) * NB;
+    const float2* ab = a.ab + ((a.static_image ? (size_t)b * a.T : frame) * a.ab_heads + (a.ab_heads > 1 ? hd : 0)) * NB;
     for (int v = 0; v < dk; ++v) {
       float* vplane = base + (size_t)(2 * a.C + hd * dk + v) * HW;
       gen_fwd_plane(vplane, xs, Rb, Fb, twW, twH, H, W);
@@ -101,10 +101,10 @@ __global__ void __launch_bounds__(GG_THREADS) gdn_spectral_generic(const GdnSpec
         if (a.static_image) {
           cf ov;
           switch (dk) {
-            case 1: ov = gdn_bin_static<1>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
-            case 2: ov = gdn_bin_static<2>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
-            case 3: ov = gdn_bin_static<3>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
-            default: ov = gdn_bin_static<4>(kk, qq, Fb[o], wh[o], ab + o, NB, a.T); break;
+            case 1: ov = gdn_bin_static<1>(kk, qq, Fb[o], wh[o], ab + o, (size_t)a.ab_heads * NB, a.T); break;
+            case 2: ov = gdn_bin_static<2>(kk, qq, Fb[o], wh[o], ab + o, (size_t)a.ab_heads * NB, a.T); break;
+            case 3: ov = gdn_bin_static<3>(kk, qq, Fb[o], wh[o], ab + o, (size_t)a.ab_heads * NB, a.T); break;
+            default: ov = gdn_bin_static<4>(kk, qq, Fb[o], wh[o], ab + o, (size_t)a.ab_heads * NB, a.T); break;
           }
           Fb[o] = mk(ov.x * invHW, ov.y * invHW);
           continue;

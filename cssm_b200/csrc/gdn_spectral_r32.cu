@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
         for (int w = 0; w < 9; ++w) s += red[w][p];
         nrm[p] = a.use_l2 ? rsqrtf(s + 1e-6f) : 1.f;
       }
-      const float2* abp = a.ab + (STATIC ? (size_t)b * a.T : frame) * NB + (kw << 2) + q;
+      const float2* abp = a.ab + ((STATIC ? (size_t)b * a.T : frame) * a.ab_heads + (a.ab_heads > 1 ? hd : 0)) * NB + (kw << 2) + q;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         cf kk[4], qq[4];
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(G32_THREADS, 1) gdn_spectral_r32(const GdnSpec
         for (int i = 0; i < 4; ++i) kk[i] = mk(kk[i].x * kn, kk[i].y * kn);
         cf o = mk(0.f, 0.f);
         if (STATIC) {
-          if (col_on) o = gdn_bin_static<4>(kk, qq, v[r], wh[r], abp + r * (17 * 4), NB, a.T);
+          if (col_on) o = gdn_bin_static<4>(kk, qq, v[r], wh[r], abp + r * (17 * 4), (size_t)a.ab_heads * NB, a.T);
         } else if (col_on) {
           const float2 g = abp[r * (17 * 4)];
           const cf aw = mk(g.x * wh[r].x, g.x * wh[r].y);

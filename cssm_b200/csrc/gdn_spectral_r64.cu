@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
       }
     }
     // gates: of this frame, or (static path) of step 0 of this batch element's T steps
-    const float2* abp = a.ab + (STATIC ? (size_t)b * a.T : frame) * NB + (c.grp << 3) + c.a;
+    const float2* abp = a.ab + ((STATIC ? (size_t)b * a.T : frame) * a.ab_heads + (a.ab_heads > 1 ? hd : 0)) * NB + (c.grp << 3) + c.a;
     // ---- v rows: transform, state update, readout, inverse transform over the v plane ----
 #pragma unroll 1
     for (int vr = 0; vr < DK; ++vr) {
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(R64_NT, 1) gdn_spectral_r64(const GdnSpectralA
           }
           if (STATIC) {
             cf o = mk(0.f, 0.f);
-            if (c.col_on) o = gdn_bin_static<4>(kk, qq, v[q], wh[q], abp + q * (33 * 8), NB, a.T);
+            if (c.col_on) o = gdn_bin_static<4>(kk, qq, v[q], wh[q], abp + q * (33 * 8), (size_t)a.ab_heads * NB, a.T);
             v[q] = mk(o.x * invHW, o.y * invHW);
             continue;
           }

@@ -83,15 +83,17 @@ struct GdnGateArgs {
   int BT, T, C, H, W, gate_type, use_input_gates, path;
   int ctx_per_clip;                      // 1: ctx_part holds one frame per clip (frame fr reads fr / T)
   const float* gk[8]; const float* gb[8];
-  float2* ab;                            // (BT, H*Wf) {alpha, beta} in spectral bin order
-  float2* bkv;                           // (BT, H*W)  {B_k, B_v}
+  int nh;                                // heads (channel gates: one {alpha, beta} map per head)
+  float2* ab;                            // (BT, H*Wf) {alpha, beta} in spectral bin order; channel gates: (BT, nh, H*Wf)
+  float2* bkv;                           // (BT, H*W)  {B_k, B_v} (not written for channel gates)
 };
 int launch_gdn_gates(const GdnGateArgs& g, cudaStream_t st);
 
 struct GdnSpectralArgs {
   float* qkv;                // planar (BT, 3C, H, W): q planes, k planes, v planes (o overwrites v)
   const cf* what;            // (n_h, H*Wf) in spectral bin order
-  const float2* ab;          // (BT, H*Wf)
+  const float2* ab;          // (BT, ab_heads, H*Wf)
+  int ab_heads;              // 1: one gate map per frame; C/dk: one per (frame, head)
   cf* state;                 // (B*n_h, dk, dk, H*Wf) scratch for the matrix state
   int B, T, C, H, W, dk, use_l2;
   int static_image;          // != 0: static-image fast path: qkv holds ONE frame per batch element

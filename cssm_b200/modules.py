@@ -371,6 +371,12 @@ class GatedDeltaNetCSSM:
             if self.gate_type == "factored":
                 s[f"{n}_h"] = {"kernel": (Cc, H), "bias": (H,)}
                 s[f"{n}_w"] = {"kernel": (Cc, wd), "bias": (wd,)}
+            elif self.gate_type == "channel":
+                # per-head scalars for alpha, beta; per-pixel 1x1 convs for B_k, B_v (cssm.py:4800-4810)
+                s[n] = ({"kernel": (1, 1, Cc, Cc), "bias": (Cc,)} if n.startswith("B_")
+                        else {"kernel": (Cc, nh), "bias": (nh,)})
+            elif self.gate_type == "scalar":
+                s[n] = {"kernel": (Cc, 1), "bias": (1,)}
             else:
                 s[n] = {"kernel": (Cc, H * wd), "bias": (H * wd,)}
         return s
@@ -382,7 +388,7 @@ class GatedDeltaNetCSSM:
         for k, v in self.param_shapes(H, W).items():
             if isinstance(v, dict):
                 kern = v["kernel"]
-                fan_in = kern[0] * kern[1] if len(kern) == 4 else kern[0]
+                fan_in = kern[0] * kern[1] if k == "qkv_dw" else (kern[2] if len(kern) == 4 else kern[0])
                 b = bias_scale * rng.standard_normal(v["bias"])
                 if k == "gate_proj":
                     b = b + self.gate_proj_bias_init
@@ -397,8 +403,8 @@ class GatedDeltaNetCSSM:
 
     def _check_fields(self):
         bad = []
-        if self.gate_type not in GATE_TYPES:
-            bad.append(f"gate_type={self.gate_type!r} (have 'factored', 'dense')")
+        if self.gate_type not in _lib.GDN_GATE_TYPES:
+            bad.append(f"gate_type={self.gate_type!r} (have 'factored', 'dense', 'channel', 'scalar')")
         if not (self.use_log and self.use_goom) and (self.use_complex32 or self.use_complex16):
             bad.append("bf16/fp8 split-precision scans")
         if self.position_independent_gates:
@@ -420,6 +426,8 @@ class GatedDeltaNetCSSM:
                 raise AssertionError("static_image_fast_path requires num_timesteps > 0")
             if self.output_norm == "layer":
                 bad.append("output_norm='layer'")
+            if self.gate_type in ("channel", "scalar"):
+                bad.append(f"static_image_fast_path with gate_type={self.gate_type!r}")
         if self.output_gate_act not in ("silu", "sigmoid"):
             bad.append(f"output_gate_act={self.output_gate_act!r}")
         if self.delta_key_dim > 4:
@@ -435,7 +443,7 @@ class GatedDeltaNetCSSM:
             raise AssertionError(f"channels={Cc} must be divisible by delta_key_dim={self.delta_key_dim}")
         return GdnDesc(B, T, H, W, Cc, self.delta_key_dim, self.kernel_size,
                        ROPE_MODES[self.rope_mode], float(self.rope_base), float(self.spectral_rho),
-                       GATE_TYPES[self.gate_type], self.short_conv_size,
+                       _lib.GDN_GATE_TYPES[self.gate_type], self.short_conv_size,
                        1 if self.output_norm == "rms" else 0, int(self.use_input_gates),
                        0 if self.output_gate_act == "silu" else 1, int(self.use_spectral_l2_norm),
                        self.qkv_conv_size, int(self.no_spectral_clamp))

@@ -40,9 +40,11 @@ typedef enum cssm_rope_mode {      /* apply_rope modes, cssm.py:94-262 */
   CSSM_ROPE_MROPE = 4
 } cssm_rope_mode;
 
-/* CSSM_GATE_CHANNEL (per-channel decay scalars, 1x1-conv spatial I/O gates) exists for the
-   DeltaNet block only; the other blocks reject it. */
-typedef enum cssm_gate_type { CSSM_GATE_DENSE = 0, CSSM_GATE_FACTORED = 1, CSSM_GATE_CHANNEL = 2 } cssm_gate_type;
+/* CSSM_GATE_CHANNEL (per-channel / per-head decay scalars, 1x1-conv spatial input gates) exists for
+   the DeltaNet and GDN blocks, CSSM_GATE_SCALAR (one scalar per frame and gate) for the GDN block;
+   the other blocks reject them. */
+typedef enum cssm_gate_type { CSSM_GATE_DENSE = 0, CSSM_GATE_FACTORED = 1, CSSM_GATE_CHANNEL = 2,
+                              CSSM_GATE_SCALAR = 3 } cssm_gate_type;
 
 typedef enum cssm_gate_act {       /* GatedCSSM._compute_gate, cssm.py:432-441 */
   CSSM_ACT_SOFTPLUS = 0,

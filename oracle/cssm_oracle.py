@@ -770,6 +770,14 @@ def init_gdn_params(seed, C, H, W, *, delta_key_dim=4, kernel_size=11, gate_type
         if gate_type == "factored":
             p[f"{n}_h"] = _dense_p(rng, C, H, bias_scale)
             p[f"{n}_w"] = _dense_p(rng, C, wd, bias_scale)
+        elif gate_type == "channel":
+            if n.startswith("B_"):
+                d = _dense_p(rng, C, C, bias_scale)
+                p[n] = {"kernel": d["kernel"].reshape(1, 1, C, C), "bias": d["bias"]}
+            else:
+                p[n] = _dense_p(rng, C, nh, bias_scale)
+        elif gate_type == "scalar":
+            p[n] = _dense_p(rng, C, 1, bias_scale)
         else:
             p[n] = _dense_p(rng, C, H * wd, bias_scale)
     return p

@@ -46,6 +46,15 @@ CASES = [
     (1, 2, 64, 64, 8, 2, 11, "factored", "none", 0, 1),      # 64x64 with d_k=2: generic kernel
     (1, 2, 7, 7, 8, 4, 11, "factored", "temporal", 4, 3),    # kernel larger than the plane
     (1, 2, 64, 64, 64, 4, 11, "factored", "mrope", 4, 5),    # C = 64: tensor-core projections
+    # per-head alpha/beta, 1x1-conv spatial gates ('channel', the reference default) and one
+    # scalar per frame ('scalar'), on the generic, 32x32 and 64x64 recurrence kernels
+    (2, 3, 8, 8, 8, 4, 5, "channel", "mrope", 4, 3),
+    (1, 3, 32, 32, 16, 4, 11, "channel", "spatiotemporal", 4, 1),
+    (1, 3, 64, 64, 8, 4, 11, "channel", "mrope", 4, 5),
+    (1, 2, 64, 64, 64, 4, 11, "channel", "none", 0, 1),
+    (2, 3, 6, 10, 12, 3, 3, "scalar", "temporal", 2, 1),
+    (1, 3, 32, 32, 8, 4, 11, "scalar", "mrope", 4, 3),
+    (1, 2, 64, 64, 8, 4, 11, "scalar", "none", 4, 1),
 ]
 
 
@@ -53,6 +62,11 @@ CASES = [
 def test_block_parity(case):
     y, ref = _run(*case)
     assert np.isfinite(y).all()
+    assert orc.rel_l2(y, ref) <= TOL
+
+
+def test_channel_gates_without_input_gates():
+    y, ref = _run(1, 3, 32, 32, 8, 4, 5, "channel", "none", 4, 1, ig=False)
     assert orc.rel_l2(y, ref) <= TOL
 
 
@@ -85,7 +99,8 @@ def test_deterministic():
     assert torch.equal(y1, y2)
 
 
-@pytest.mark.parametrize("case", [CASES[0], CASES[1], CASES[4], CASES[5], CASES[7], CASES[9]],
+@pytest.mark.parametrize("case", [CASES[0], CASES[1], CASES[4], CASES[5], CASES[7], CASES[9], CASES[11],
+                                  CASES[12], CASES[15]],
                          ids=lambda c: "x".join(map(str, c)))
 def test_last_frame_only_matches_full_forward(case):
     """cssm_gdn_forward_last equals the last frame of the full forward (generic, 32x32 and 64x64
