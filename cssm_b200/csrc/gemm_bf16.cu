@@ -8,13 +8,14 @@
 //              64 k, plain mode) and the weight tile (BN rows x 64 k) of every K block into a
 //              4-stage ring of 128-byte-swizzled K-major operand tiles;
 //   warp 1     MMA issuer: one lane issues 4 tcgen05.mma.kind::f16 (M128 x BN x K16) per K block
-//              into one of two TMEM accumulators; tcgen05.commit frees the stage / publishes the
-//              accumulator;
+//              into one of four TMEM accumulators (BN <= 128; two for wider single tiles);
+//              tcgen05.commit frees the stage / publishes the accumulator;
 //   warps 2-9  epilogue, two warps per TMEM lane quadrant: tcgen05.ld (lane = output row), bias,
-//              GELU / SiLU, residual; each half (one warp per quadrant) stages boxes of 128 rows x 64
-//              bf16 columns in the 128-byte swizzle and writes them with one TMA tensor store
-//              (N a multiple of 64; otherwise direct 16-byte stores); overlaps the next tile's
-//              main loop through the second accumulator;
+//              GELU / SiLU, residual; each half (one warp per quadrant) owns every other tile and two
+//              of the accumulators, stages boxes of 128 rows x 64 bf16 columns in the 128-byte
+//              swizzle in a ring of three or four slots and writes them with TMA tensor stores; the
+//              residual box is fetched by TMA into the slot it will be staged in, two boxes ahead,
+//              and added in place (N a multiple of 64; otherwise direct 16-byte loads and stores);
 //   warps 10-13 im2col producers (conv mode only): eight consecutive lanes fetch the eight 16-byte
 //              channel chunks of one output pixel's K block from the channels-last input (zero
 //              outside the image), four pixels per warp instruction, and write them in the same
@@ -33,7 +34,6 @@ namespace cssm {
 __device__ int g_bf16_error = 0;
 
 constexpr int GB_THREADS_PLAIN = 320, GB_THREADS_CONV = 448;
-constexpr uint32_t GB_OUT_BYTES = 4u * 16384u;           // two 128 x 64 bf16 staging boxes per epilogue half
 constexpr int GB_BM = 128, GB_BK = 64, GB_MAX_STAGES = 4;
 constexpr uint32_t GB_A_BYTES = GB_BM * 128u;            // one A stage: 128 rows x 128 bytes
 
@@ -58,21 +58,24 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64
 template <bool IM2COL, bool TMA_OUT>
 __global__ void __launch_bounds__(IM2COL ? GB_THREADS_CONV : GB_THREADS_PLAIN, 1)
 gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
-                 const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap omap) {
+                 const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap omap,
+                 const __grid_constant__ CUtensorMap rmap) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = tc::smem_u32(smem);
   const uint32_t BN = (uint32_t)g.BN;
   const uint32_t stage_bytes = GB_A_BYTES + BN * 128u;
   const int NS = g.stages;                                  // ring depth (3 when BN = 256 and TMA_OUT)
-  unsigned char* out_s = smem + (uint32_t)NS * stage_bytes; // TMA_OUT: 4 x 16 KB staging boxes
-  uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + (TMA_OUT ? GB_OUT_BYTES : 0u));
+  unsigned char* out_s = smem + (uint32_t)NS * stage_bytes; // TMA_OUT: 2 x ostg staging boxes of 16 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + (TMA_OUT ? (uint32_t)(2 * g.ostg) * 16384u : 0u));
   uint64_t* full = bars;                        // [4] operands landed
   uint64_t* empty = bars + GB_MAX_STAGES;       // [4] stage consumed
-  uint64_t* accfull = bars + 2 * GB_MAX_STAGES; // [2]
-  uint64_t* accempty = accfull + 2;         // [2]
-  uint64_t* done = accempty + 2;
+  uint64_t* accfull = bars + 2 * GB_MAX_STAGES; // [4] accumulator complete
+  uint64_t* accempty = accfull + 4;             // [4] accumulator drained
+  uint64_t* resfull = accempty + 4;             // [2][4] residual box landed in its staging slot
+  uint64_t* done = resfull + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+  const int NACC = g.nacc;                                  // TMEM accumulators: 4 of BN <= 128 columns, else 2
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = g.N / g.BN;
@@ -80,15 +83,19 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
   const int num_tiles = m_tiles * n_tiles;
   const int kblocks = g.Kpad / GB_BK;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < 2 * BN) tmem_cols <<= 1;
+  while (tmem_cols < (uint32_t)NACC * BN) tmem_cols <<= 1;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       tc::mbar_init(&full[s], IM2COL ? 1 + 4 : 1);      // TMA lane + one lane per producer warp
       tc::mbar_init(&empty[s], 1);
     }
-    tc::mbar_init(&accfull[0], 1); tc::mbar_init(&accfull[1], 1);
-    tc::mbar_init(&accempty[0], 4); tc::mbar_init(&accempty[1], 4);   // one lane per warp of the owning half
+    for (int a = 0; a < 4; ++a) {
+      tc::mbar_init(&accfull[a], 1);
+      // one lane per warp of the half that drains the accumulator
+      tc::mbar_init(&accempty[a], 4);
+    }
+    for (int a = 0; a < 8; ++a) tc::mbar_init(&resfull[a], 1);
     tc::mbar_init(done, 1);
     tc::fence_mbar_init();
   }
@@ -142,7 +149,7 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
       const uint32_t idesc = make_idesc_bf16(GB_BM, BN);
       int it = 0, tcnt = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x, ++tcnt) {
-        const int ac = tcnt & 1, aph = (tcnt >> 1) & 1;
+        const int ac = tcnt % NACC, aph = (tcnt / NACC) & 1;
         if (!tc::mbar_wait(&accempty[ac], aph ^ 1)) { atomicExch(&g_bf16_error, 6); bad = true; break; }
         tc::fence_after_sync();
         const uint32_t d = tmem_base + (uint32_t)ac * BN;
@@ -170,101 +177,150 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
   } else if (warp < 10) {
     // ================================ epilogue ================================
     // Two halves of four warps (one per TMEM lane quadrant).  Half h owns the tiles of its CTA with
-    // tile count parity h and their accumulator h, so the epilogues of two consecutive tiles overlap;
-    // the residual rows of a 64-column box are fetched before the wait on the accumulator.
+    // tile count parity h; accumulator = tile count mod NACC, so a half drains one accumulator while
+    // the MMA warp fills its other one.
     const int q = warp & 3;                       // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;
     const int row = q * 32 + lane;
-    const bool issuer = q == 0 && lane == 0;      // issues this half's TMA stores
-    unsigned char* stg2 = out_s + (uint32_t)half * 32768u;   // this half's two staging boxes
-    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)half * BN;
-    int tcnt = 0, nbox = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcnt) {
-      if ((tcnt & 1) != half) continue;
-      const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
-      const int aph = (tcnt >> 1) & 1;
-      const int m = m0 + row;
-      const bool has_res = g.res != nullptr && m < g.M;
-      const uint4* rrow = reinterpret_cast<const uint4*>(g.res + (has_res ? (size_t)m * g.ldr + n0 : 0));
-      uint4 rs[8];                                // residual of the next 64 columns
-      auto fetch_res = [&](int c0) {
+    const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+    // bias, activation on 32 accumulator columns starting at tile column c0
+    auto act32 = [&](const uint32_t (&r)[32], int n, float (&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) rs[j] = has_res ? __ldg(rrow + (c0 >> 3) + j) : make_uint4(0u, 0u, 0u, 0u);
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      if (g.bias != nullptr) {
+        const float4* bp = reinterpret_cast<const float4*>(g.bias + n);
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 b4 = __ldg(bp + (j >> 2));
+          v[j] += b4.x; v[j + 1] += b4.y; v[j + 2] += b4.z; v[j + 3] += b4.w;
+        }
+      }
+      if (g.act == 1) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) gelu_tanh_x2(v[j], v[j + 1]);
+      } else if (g.act == 2) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) silu_tanh_x2(v[j], v[j + 1]);
+      }
+    };
+    if constexpr (TMA_OUT) {
+      // Output boxes of 128 rows x 64 bf16 columns are staged in the 128-byte swizzle in a ring of D
+      // slots per half and written by TMA tensor stores.  A residual is fetched by TMA into the
+      // very slot its box will be staged in, D - 2 boxes ahead (the wait before a slot is reused
+      // leaves only the most recent store pending), and is added in place.
+      // (Both halves draining every tile of a two-accumulator configuration, each every other box,
+      // measured slower than whole tiles in turn: 232 against 197 us for M = 1.6 M, K = 64, N = 256.)
+      const bool issuer = q == 0 && lane == 0;    // issues this half's TMA loads and stores
+      const int D = g.ostg, nb = g.BN / 64;
+      constexpr int b0 = 0, bstep = 1, tstep = 2;
+      const int t0 = half;
+      unsigned char* stgh = out_s + (uint32_t)(half * D) * 16384u;
+      uint64_t* resf = resfull + half * 4;
+      const bool rtma = g.res != nullptr && D >= 3;
+      const bool rreg = g.res != nullptr && !rtma;      // two slots only: residual rows by plain loads
+      int pf_t = t0, pf_box = b0, pf_q = 0;       // issuer: the next box whose residual is to be fetched
+      auto pf_issue = [&]() {
+        const int tile = blockIdx.x + pf_t * (int)gridDim.x;
+        if (tile >= num_tiles) return;
+        const int slot = pf_q % D;
+        tc::mbar_expect_tx(&resf[slot], 16384u);
+        tc::tma_load_2d(stgh + (uint32_t)slot * 16384u, &rmap, (tile % n_tiles) * g.BN + pf_box * 64,
+                        (tile / n_tiles) * GB_BM, &resf[slot]);
+        ++pf_q;
+        pf_box += bstep;
+        if (pf_box >= nb) { pf_box = b0; pf_t += tstep; }
       };
-      if (g.res != nullptr) fetch_res(0);
-      bool ok = tc::mbar_wait(&accfull[half], aph);
-      if (TMA_OUT) {
-        // the named barriers below need all 128 threads of the half: make the exit uniform
-        uint32_t all_ok;
+      if (rtma && issuer)
+        for (int k = 0; k < D - 2; ++k) pf_issue();
+      // all 128 threads of the half agree on `ok` (and meet, as a barrier)
+      auto all_ok = [&](bool ok) {
+        uint32_t r;
         asm volatile(
             "{\n\t.reg .pred p, q;\n\t"
             "setp.ne.u32 p, %1, 0;\n\t"
             "bar.red.and.pred q, %2, 128, p;\n\t"
             "selp.u32 %0, 1, 0, q;\n\t}"
-            : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + half) : "memory");
-        ok = all_ok != 0;
-      } else {
-        ok = !__any_sync(0xffffffffu, !ok);
-      }
-      if (!ok) { atomicExch(&g_bf16_error, 8); break; }
-      tc::fence_after_sync();
-      // 32 raw accumulator columns of tile column c0 (already loaded into r) -> bias, activation,
-      // residual (rs[4 hh ..]) -> four packed 16-byte chunks
-      auto finish32 = [&](const uint32_t (&r)[32], int c0, int hh, uint4* pk4) {
-        float v[32];
-        const int n = n0 + c0;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (g.bias != nullptr) {
-          const float4* bp = reinterpret_cast<const float4*>(g.bias + n);
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const float4 b4 = __ldg(bp + (j >> 2));
-            v[j] += b4.x; v[j + 1] += b4.y; v[j + 2] += b4.z; v[j + 3] += b4.w;
-          }
-        }
-        if (g.act == 1) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) gelu_tanh_x2(v[j], v[j + 1]);
-        } else if (g.act == 2) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) silu_tanh_x2(v[j], v[j + 1]);
-        }
-        if (g.res != nullptr) {
-#pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) {
-            float f[8];
-            unpack8(hh ? rs[4 + j4] : rs[j4], f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[j4 * 8 + e] += f[e];
-          }
-        }
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float f[8] = {v[j4 * 8], v[j4 * 8 + 1], v[j4 * 8 + 2], v[j4 * 8 + 3],
-                              v[j4 * 8 + 4], v[j4 * 8 + 5], v[j4 * 8 + 6], v[j4 * 8 + 7]};
-          pk4[j4] = pack8(f);
-        }
+            : "=r"(r) : "r"((uint32_t)ok), "r"(1 + half) : "memory");
+        return r != 0;
       };
-      // (keeping the TMEM load of the next 32 columns in flight during this arithmetic measured
-      // slower: 168 registers against 146)
-      uint32_t ra[32];
-      const int nbox_tile = g.BN / 64;
-      for (int box = 0; box < nbox_tile; ++box) {
-        uint4 pk[8];
-        tc::ld_32x32b_x32(taddr + box * 64, ra);
-        tc::wait_ld();
-        finish32(ra, box * 64, 0, pk);
-        tc::ld_32x32b_x32(taddr + box * 64 + 32, ra);
-        tc::wait_ld();
-        finish32(ra, box * 64 + 32, 1, pk + 4);
-        if (g.res != nullptr && box + 1 < g.BN / 64) fetch_res((box + 1) * 64);
-        if (TMA_OUT) {
-          // two staging boxes in turn: the TMA store issued two boxes ago must have drained this one
-          unsigned char* stg = stg2 + (uint32_t)(nbox & 1) * 16384u;
-          ++nbox;
-          if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+      int bq = 0;                                 // boxes staged by this half so far
+      bool live = true;
+      for (int tcnt = t0; live; tcnt += tstep) {
+        const int tile = blockIdx.x + tcnt * (int)gridDim.x;
+        if (tile >= num_tiles) break;
+        const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
+        const int ac = tcnt % NACC, aph = (tcnt / NACC) & 1;
+        const bool has_res = rreg && m0 + row < g.M;
+        const uint4* rrow = reinterpret_cast<const uint4*>(g.res + (has_res ? (size_t)(m0 + row) * g.ldr + n0 : 0));
+        uint4 rs[8];                              // rreg: residual of the next 64 columns
+        auto fetch_res = [&](int c0) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) rs[j] = has_res ? __ldg(rrow + (c0 >> 3) + j) : make_uint4(0u, 0u, 0u, 0u);
+        };
+        if (rreg) fetch_res(0);
+        if (!all_ok(tc::mbar_wait(&accfull[ac], aph))) { atomicExch(&g_bf16_error, 8); break; }
+        tc::fence_after_sync();
+        const uint32_t taddr = tlane + (uint32_t)ac * BN;
+        uint32_t ra[32];
+        for (int box = b0; box < nb; box += bstep, ++bq) {
+          const int slot = bq % D;
+          unsigned char* stg = stgh + (uint32_t)slot * 16384u;
+          // accumulator -> bias, activation: nothing here depends on the staging slot, so it runs
+          // while the earlier stores drain (keeping the TMEM load of the next 32 columns in flight
+          // during the arithmetic measured slower)
+          float v[64];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            float vh[32];
+            tc::ld_32x32b_x32(taddr + box * 64 + hh * 32, ra);
+            tc::wait_ld();
+            act32(ra, n0 + box * 64 + hh * 32, vh);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[hh * 32 + j] = vh[j];
+          }
+          uint4 pk[8];
+          auto pack64 = [&]() {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const float f[8] = {v[c * 8], v[c * 8 + 1], v[c * 8 + 2], v[c * 8 + 3],
+                                  v[c * 8 + 4], v[c * 8 + 5], v[c * 8 + 6], v[c * 8 + 7]};
+              pk[c] = pack8(f);
+            }
+          };
+          if (!rtma) {
+            if (rreg) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                float f[8];
+                unpack8(rs[c], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[c * 8 + e] += f[e];
+              }
+            }
+            pack64();
+          }
+          if (issuer) {
+            // the store that last read the slot about to be refilled has drained: with a residual
+            // that slot is the one of two boxes back, else this box's own (D boxes back)
+            if (rtma || D < 3) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else if (D == 3) asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+            if (rtma) pf_issue();
+          }
+          if (rtma) {
+            if (!all_ok(tc::mbar_wait(&resf[slot], (bq / D) & 1))) { atomicExch(&g_bf16_error, 8); live = false; break; }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float f[8];
+              unpack8(*reinterpret_cast<const uint4*>(stg + tc::sw128_offset(row, c)), f);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[c * 8 + e] += f[e];
+            }
+            pack64();
+          } else {
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+          }
+          if (rreg && box + 1 < nb) fetch_res((box + 1) * 64);
 #pragma unroll
           for (int c = 0; c < 8; ++c)
             *reinterpret_cast<uint4*>(stg + tc::sw128_offset(row, c)) = pk[c];
@@ -281,35 +337,64 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
-        } else if (m < g.M) {
-          uint4* op = reinterpret_cast<uint4*>(g.out + (size_t)m * g.ldo + n0 + box * 64);
-#pragma unroll
-          for (int c = 0; c < 8; ++c) op[c] = pk[c];
         }
+        if (!live) break;
+        tc::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&accempty[ac]);
       }
-      // a last group of 32 columns (N = 32 or 96 ...): direct stores
-      if (g.BN % 64 != 0) {
-        const int c0 = g.BN - 32;
-        if (has_res) {
+      // the staging slots must outlive the last TMA stores that read them
+      if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else {
+      // direct 16-byte stores (N not a multiple of 64, or no tensor map): residual rows by plain loads
+      for (int i = 0;; ++i) {
+        const int tcnt = 2 * i + half;
+        const int tile = blockIdx.x + tcnt * (int)gridDim.x;
+        if (tile >= num_tiles) break;
+        const int m0 = (tile / n_tiles) * GB_BM, n0 = (tile % n_tiles) * g.BN;
+        const int ac = tcnt % NACC, aph = (tcnt / NACC) & 1;
+        const int m = m0 + row;
+        const bool has_res = g.res != nullptr && m < g.M;
+        const uint4* rrow = reinterpret_cast<const uint4*>(g.res + (has_res ? (size_t)m * g.ldr + n0 : 0));
+        uint4 rs[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) rs[j] = __ldg(rrow + (c0 >> 3) + j);
-        }
-        uint4 pk[4];
-        tc::ld_32x32b_x32(taddr + c0, ra);
-        tc::wait_ld();
-        finish32(ra, c0, 0, pk);
-        if (m < g.M) {
-          uint4* op = reinterpret_cast<uint4*>(g.out + (size_t)m * g.ldo + n0 + c0);
+        for (int j = 0; j < 4; ++j) rs[j] = has_res ? __ldg(rrow + j) : make_uint4(0u, 0u, 0u, 0u);
+        if (__any_sync(0xffffffffu, !tc::mbar_wait(&accfull[ac], aph))) { atomicExch(&g_bf16_error, 8); break; }
+        tc::fence_after_sync();
+        const uint32_t taddr = tlane + (uint32_t)ac * BN;
+        uint32_t ra[32];
+        for (int c0 = 0; c0 < g.BN; c0 += 32) {
+          float v[32];
+          tc::ld_32x32b_x32(taddr + c0, ra);
+          tc::wait_ld();
+          act32(ra, n0 + c0, v);
 #pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) op[j4] = pk[j4];
+          for (int j4 = 0; j4 < 4; ++j4) {
+            float f[8];
+            unpack8(rs[j4], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j4 * 8 + e] += f[e];
+          }
+          if (c0 + 32 < g.BN) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              rs[j] = has_res ? __ldg(rrow + ((c0 + 32) >> 3) + j) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          if (m < g.M) {
+            uint4* op = reinterpret_cast<uint4*>(g.out + (size_t)m * g.ldo + n0 + c0);
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+              const float f[8] = {v[j4 * 8], v[j4 * 8 + 1], v[j4 * 8 + 2], v[j4 * 8 + 3],
+                                  v[j4 * 8 + 4], v[j4 * 8 + 5], v[j4 * 8 + 6], v[j4 * 8 + 7]};
+              op[j4] = pack8(f);
+            }
+          }
         }
+        tc::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&accempty[ac]);
       }
-      tc::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&accempty[half]);
     }
-    // the staging boxes must outlive the last TMA stores that read them
-    if (TMA_OUT && issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else if (IM2COL) {
     // ================================ im2col producers ================================
     // lane = (row group rg, chunk c): the eight lanes of a group read the eight 16-byte chunks of one
@@ -421,12 +506,13 @@ int read_bf16_error(int* out, int clear) {
   return CSSM_OK;
 }
 
+// Tile width: 256 columns (two TMEM accumulators), 128 or 64 (four), all with the TMA-store epilogue;
+// other multiples of 32 up to 256 as one tile with direct stores.
 int gemm_bf16_pick_bn(int N) {
-  if (N <= 256) return (N % 32 == 0) ? N : 0;
   if (N % 256 == 0) return 256;
-  if (N % 192 == 0) return 192;
   if (N % 128 == 0) return 128;
   if (N % 64 == 0) return 64;
+  if (N <= 256 && N % 32 == 0) return N;
   return 0;
 }
 
@@ -470,6 +556,9 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   const int Kw = conv ? conv3x3s2_packed_k(g.Cin, g.Wi, g.N) : g.K;      // K as the packed weights lay it out
   g.Kpad = (Kw + GB_BK - 1) / GB_BK * GB_BK;
   g.BN = gemm_bf16_pick_bn(g.N);
+  // a residual with a short K loop gains more from the TMA residual prefetch (three staging slots,
+  // BN <= 128) than it loses in operand traffic: 37 against 47 us for M = 100 K, K = 256, N = 256
+  if (g.BN == 256 && g.res != nullptr && g.K < 512) g.BN = 128;
   if (g.BN == 0 || g.ldw < g.Kpad || (g.ldw % 8) != 0) return CSSM_ERR_UNSUPPORTED;
   if (g.ldo % 8 != 0 || (g.res != nullptr && g.ldr % 8 != 0)) return CSSM_ERR_UNSUPPORTED;
   if (!aligned16(g.A) || !aligned16(g.Wt) || (g.out && !aligned16(g.out)) ||
@@ -483,10 +572,11 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   } else if (g.K % 8 != 0 || g.lda % 8 != 0 || g.lda < g.K) {
     return CSSM_ERR_UNSUPPORTED;
   }
-  CUtensorMap amap, bmap, omap;
+  CUtensorMap amap, bmap, omap, rmap;
   memset(&amap, 0, sizeof(amap));
   memset(&bmap, 0, sizeof(bmap));
   memset(&omap, 0, sizeof(omap));
+  memset(&rmap, 0, sizeof(rmap));
   bool tma_out = g.BN % 64 == 0;
   int m_tiles = (g.M + GB_BM - 1) / GB_BM;
   if (g.conv_tma) {
@@ -532,6 +622,8 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
     if (!im2col && !make_kmajor_map(&amap, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, GB_BM))
       return CSSM_ERR_CUDA;
     tma_out = tma_out && make_out_map(&omap, g.out, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldo);
+    if (tma_out && g.res != nullptr)
+      tma_out = make_out_map(&rmap, const_cast<__nv_bfloat16*>(g.res), (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldr);
   }
   if (!make_kmajor_map(&bmap, g.Wt, (uint64_t)g.N, (uint64_t)g.Kpad, (uint64_t)g.ldw, (uint32_t)g.BN))
     return CSSM_ERR_CUDA;
@@ -542,14 +634,26 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   const int tiles = m_tiles * (g.N / g.BN);
   const int grid = tiles < sms ? tiles : sms;
   const size_t stage = GB_A_BYTES + (size_t)g.BN * 128u;
+  const size_t budget = 227 * 1024, fixed = 256 + 1024;
+  g.nacc = g.BN <= 128 ? 4 : 2;
   g.stages = GB_MAX_STAGES;
-  while (g.stages > 2 && g.stages * stage + (tma_out ? GB_OUT_BYTES : 0) + 256 + 1024 > 227 * 1024) --g.stages;
-  const size_t smem = g.stages * stage + (tma_out ? GB_OUT_BYTES : 0) + 256 + 1024;
+  g.ostg = 0;
+  if (tma_out) {
+    // staging slots per epilogue half: as many as fit beside the operand ring, two to four; the
+    // residual prefetch by TMA wants three (BN = 256 has room for two: residual rows by plain loads)
+    if (g.BN == 256) g.stages = 3;
+    g.ostg = (int)((budget - fixed - g.stages * stage) / (2 * 16384));
+    if (g.ostg > 4) g.ostg = 4;
+    if (g.ostg < 2) return CSSM_ERR_UNSUPPORTED;
+  } else {
+    while (g.stages > 2 && g.stages * stage + fixed > budget) --g.stages;
+  }
+  const size_t smem = g.stages * stage + (size_t)g.ostg * 2 * 16384 + fixed;
   auto kern = im2col ? (tma_out ? gemm_bf16_kernel<true, true> : gemm_bf16_kernel<true, false>)
                      : (tma_out ? gemm_bf16_kernel<false, true> : gemm_bf16_kernel<false, false>);
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-  kern<<<grid, im2col ? GB_THREADS_CONV : GB_THREADS_PLAIN, smem, st>>>(g, amap, bmap, omap);
+  kern<<<grid, im2col ? GB_THREADS_CONV : GB_THREADS_PLAIN, smem, st>>>(g, amap, bmap, omap, rmap);
   return check_launch();
 }
 
