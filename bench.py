@@ -448,16 +448,35 @@ def run_shvit(args, name, ctx):
     e2e = None
     if not args.no_e2e:
         lh = torch.empty((B, K), dtype=torch.float32).pin_memory()
+        # (a) one self-contained call per step: copies in chunks overlapped with compute inside the call
         for _ in range(max(1, min(args.warmup, 3))):
             bound.forward_host(x_host, lh)
         ctx["barrier"]()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             bound.forward_host(x_host, lh)             # returns after the logits arrived
+        dt1 = shard.max_over_ranks(time.perf_counter() - t0, dev)
+        # (b) the streaming loop: every call copies the NEXT step's images (a second pinned buffer)
+        # while it computes its own, and returns after its logits arrived; one copy in and one
+        # copy out per step inside the timed region
+        x_host2 = x_host.clone().pin_memory()
+        bufs = [x_host, x_host2]
+        for i in range(max(2, min(args.warmup, 3))):
+            bound.forward_host_pipelined(bufs[i & 1], bufs[(i + 1) & 1], lh)
+        i0 = max(2, min(args.warmup, 3))
+        ctx["barrier"]()
+        t0 = time.perf_counter()
+        for i in range(i0, i0 + args.steps):
+            bound.forward_host_pipelined(bufs[i & 1], bufs[(i + 1) & 1], lh)
         dt = shard.max_over_ranks(time.perf_counter() - t0, dev)
+        bound.close()
         e2e = {"value": world * B * args.steps / dt, "unit": "images/s",
                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": lh.numel() * 4,
-               "ms_per_step": 1e3 * dt / args.steps}
+               "ms_per_step": 1e3 * dt / args.steps,
+               "mode": "streaming loop: the host->device copy of step i+1 runs on a copy stream while "
+                       "step i computes; every call returns after its own logits reached the host",
+               "single_call_value": world * B * args.steps / dt1,
+               "single_call_ms_per_step": 1e3 * dt1 / args.steps}
 
     sustained = None
     if ctx.get("sustain"):

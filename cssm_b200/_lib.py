@@ -249,6 +249,11 @@ SIGNATURES = {
     "cssm_shvit_host_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
     "cssm_shvit_forward_host": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
                                           C.c_size_t, _P]),
+    "cssm_shvit_host_pipe_create": (C.c_int, [C.POINTER(_P)]),
+    "cssm_shvit_host_pipe_destroy": (C.c_int, [_P]),
+    "cssm_shvit_host_pipe_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
+    "cssm_shvit_forward_host_pipelined": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
+                                                    _P, _P, C.c_size_t, _P]),
     "cssm_bf16_packed_ld": (C.c_int32, [C.c_int32]),
     "cssm_bf16_pack_weight": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P]),
     "cssm_bf16_gemm": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _P, C.c_int32, _P, _P, _P]),

@@ -1,6 +1,7 @@
 // C ABI of the bf16 CSSM-SHViT forward: plan (packed bf16 weights, folded BatchNorm), the two block
 // kinds, the whole model on device buffers and on host buffers, and the bf16 GEMM / conv on their own.
 #include <string.h>
+#include <new>
 #include "kernels.cuh"
 
 namespace cssm {
@@ -576,6 +577,116 @@ int cssm_shvit_forward_host(const cssm_shvit_desc* d, const cssm_shvit_weights* 
   }
   if (ev_start) cudaEventDestroy(ev_start);
   if (sc) cudaStreamDestroy(sc);
+  return rc;
+}
+
+// ---- streaming host entry point: the next batch's images are copied while this one computes ----
+struct PipeWs { size_t model, xbuf[2], logits, total; size_t model_bytes, xbytes; };
+static PipeWs pipe_ws_layout(const cssm_shvit_desc& d) {
+  PipeWs h;
+  memset(&h, 0, sizeof(h));
+  h.model_bytes = cssm_shvit_workspace_bytes(&d);
+  h.xbytes = (size_t)d.B * d.H * d.W * d.Cin * 2;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { const size_t o = off; off += al256(bytes); return o; };
+  h.model = take(h.model_bytes);
+  h.xbuf[0] = take(h.xbytes);
+  h.xbuf[1] = take(h.xbytes);
+  h.logits = take((size_t)d.B * d.num_classes * 4);
+  h.total = off;
+  return h;
+}
+
+}  // extern "C"
+struct cssm_shvit_host_pipe {
+  cudaStream_t copy;
+  cudaEvent_t copied[2];       // the copy into input buffer j has finished
+  cudaEvent_t computed;        // the last forward has finished reading its input buffer
+  const void* src;             // host address whose images sit (or are arriving) in buffer `buf`
+  const void* ws;              // ... of this workspace
+  int buf;
+};
+extern "C" {
+
+int cssm_shvit_host_pipe_create(cssm_shvit_host_pipe** pipe) {
+  if (!pipe) return CSSM_ERR_NULL;
+  *pipe = nullptr;
+  cssm_shvit_host_pipe* p = new (std::nothrow) cssm_shvit_host_pipe();
+  if (!p) return CSSM_ERR_CUDA;
+  memset(p, 0, sizeof(*p));
+  cudaError_t e = cudaStreamCreateWithFlags(&p->copy, cudaStreamNonBlocking);
+  for (int i = 0; i < 2 && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&p->copied[i], cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->computed, cudaEventDisableTiming);
+  if (e != cudaSuccess) {
+    set_cuda_error(e);
+    cssm_shvit_host_pipe_destroy(p);
+    return CSSM_ERR_CUDA;
+  }
+  *pipe = p;
+  return CSSM_OK;
+}
+
+int cssm_shvit_host_pipe_destroy(cssm_shvit_host_pipe* p) {
+  if (!p) return CSSM_OK;
+  if (p->copy) cudaStreamSynchronize(p->copy);        // a prefetch may still be reading the host buffer
+  for (int i = 0; i < 2; ++i)
+    if (p->copied[i]) cudaEventDestroy(p->copied[i]);
+  if (p->computed) cudaEventDestroy(p->computed);
+  if (p->copy) cudaStreamDestroy(p->copy);
+  delete p;
+  return CSSM_OK;
+}
+
+size_t cssm_shvit_host_pipe_workspace_bytes(const cssm_shvit_desc* d) {
+  if (cssm_shvit_workspace_bytes(d) == 0) return 0;
+  return pipe_ws_layout(*d).total;
+}
+
+int cssm_shvit_forward_host_pipelined(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
+                                      cssm_shvit_host_pipe* p, const void* x_bf16_host,
+                                      const void* x_next_bf16_host, float* logits_host, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  if (cssm_shvit_workspace_bytes(d) == 0) return model_validate(d) != CSSM_OK ? model_validate(d) : CSSM_ERR_UNSUPPORTED;
+  if (!w || !plan || !p || !x_bf16_host || !logits_host || !workspace) return CSSM_ERR_NULL;
+  if (!aligned16(workspace) || !aligned16(plan)) return CSSM_ERR_ALIGN;
+  const PipeWs h = pipe_ws_layout(*d);
+  if (workspace_bytes < h.total) return CSSM_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  int rc = CSSM_OK;
+  cudaError_t e = cudaSuccess;
+#define CSSM_TRY(call) do { if (rc == CSSM_OK) { e = (call); if (e != cudaSuccess) { set_cuda_error(e); rc = CSSM_ERR_CUDA; } } } while (0)
+  int j;
+  if (p->src == x_bf16_host && p->ws == workspace) {
+    j = p->buf;                                        // prefetched by the previous call
+  } else {
+    j = 0;
+    // after whatever the caller queued on its stream, and after any copy still running on the pipe
+    CSSM_TRY(cudaEventRecord(p->computed, st));
+    CSSM_TRY(cudaStreamWaitEvent(p->copy, p->computed, 0));
+    CSSM_TRY(cudaMemcpyAsync(ws + h.xbuf[0], x_bf16_host, h.xbytes, cudaMemcpyHostToDevice, p->copy));
+    CSSM_TRY(cudaEventRecord(p->copied[0], p->copy));
+  }
+  p->src = nullptr;
+  if (x_next_bf16_host != nullptr && rc == CSSM_OK) {
+    // buffer 1 - j was last read by the previous call's forward, which that call waited for
+    CSSM_TRY(cudaMemcpyAsync(ws + h.xbuf[1 - j], x_next_bf16_host, h.xbytes, cudaMemcpyHostToDevice, p->copy));
+    CSSM_TRY(cudaEventRecord(p->copied[1 - j], p->copy));
+    if (rc == CSSM_OK) { p->src = x_next_bf16_host; p->ws = workspace; p->buf = 1 - j; }
+  }
+  CSSM_TRY(cudaStreamWaitEvent(st, p->copied[j], 0));
+  float* ld = (float*)(ws + h.logits);
+  if (rc == CSSM_OK)
+    rc = cssm_shvit_forward(d, w, plan, ws + h.xbuf[j], ld, ws + h.model, h.model_bytes, stream);
+  CSSM_TRY(cudaMemcpyAsync(logits_host, ld, (size_t)d->B * d->num_classes * 4, cudaMemcpyDeviceToHost, st));
+  const cudaError_t e1 = cudaStreamSynchronize(st);
+  if (rc == CSSM_OK && e1 != cudaSuccess) { set_cuda_error(e1); rc = CSSM_ERR_CUDA; }
+  if (rc != CSSM_OK) {
+    // leave no copy running into a workspace the caller may now free
+    cudaStreamSynchronize(p->copy);
+    p->src = nullptr;
+  }
+#undef CSSM_TRY
   return rc;
 }
 

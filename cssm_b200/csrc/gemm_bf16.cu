@@ -55,7 +55,8 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-template <bool IM2COL, bool TMA_OUT>
+// RTMA (with TMA_OUT): the residual boxes come by TMA into the staging slots.
+template <bool IM2COL, bool TMA_OUT, bool RTMA>
 __global__ void __launch_bounds__(IM2COL ? GB_THREADS_CONV : GB_THREADS_PLAIN, 1)
 gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
                  const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap omap,
@@ -216,8 +217,8 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
       const int t0 = half;
       unsigned char* stgh = out_s + (uint32_t)(half * D) * 16384u;
       uint64_t* resf = resfull + half * 4;
-      const bool rtma = g.res != nullptr && D >= 3;
-      const bool rreg = g.res != nullptr && !rtma;      // two slots only: residual rows by plain loads
+      constexpr bool rtma = RTMA;
+      const bool rreg = !RTMA && g.res != nullptr;      // residual rows by plain loads
       int pf_t = t0, pf_box = b0, pf_q = 0;       // issuer: the next box whose residual is to be fetched
       auto pf_issue = [&]() {
         const int tile = blockIdx.x + pf_t * (int)gridDim.x;
@@ -265,39 +266,35 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
         for (int box = b0; box < nb; box += bstep, ++bq) {
           const int slot = bq % D;
           unsigned char* stg = stgh + (uint32_t)slot * 16384u;
-          // accumulator -> bias, activation: nothing here depends on the staging slot, so it runs
-          // while the earlier stores drain (keeping the TMEM load of the next 32 columns in flight
-          // during the arithmetic measured slower)
-          float v[64];
+          // residual by TMA: its box landed in this slot two boxes ago (a wait that expires is
+          // recorded and the data is wrong, but every thread still meets the barriers below)
+          if (rtma && !tc::mbar_wait(&resf[slot], (bq / D) & 1)) atomicExch(&g_bf16_error, 8);
+          // accumulator -> bias, activation, residual -> eight packed 16-byte chunks.  Nothing here
+          // writes the slot, so it runs while the earlier stores drain.  (Keeping the TMEM load of the
+          // next 32 columns in flight during the arithmetic measured slower.)
+          uint4 pk[8];
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
-            float vh[32];
+            float v[32];
             tc::ld_32x32b_x32(taddr + box * 64 + hh * 32, ra);
             tc::wait_ld();
-            act32(ra, n0 + box * 64 + hh * 32, vh);
+            act32(ra, n0 + box * 64 + hh * 32, v);
+            if (rtma || rreg) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[hh * 32 + j] = vh[j];
-          }
-          uint4 pk[8];
-          auto pack64 = [&]() {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const float f[8] = {v[c * 8], v[c * 8 + 1], v[c * 8 + 2], v[c * 8 + 3],
-                                  v[c * 8 + 4], v[c * 8 + 5], v[c * 8 + 6], v[c * 8 + 7]};
-              pk[c] = pack8(f);
-            }
-          };
-          if (!rtma) {
-            if (rreg) {
-#pragma unroll
-              for (int c = 0; c < 8; ++c) {
+              for (int j4 = 0; j4 < 4; ++j4) {
                 float f[8];
-                unpack8(rs[c], f);
+                unpack8(rtma ? *reinterpret_cast<const uint4*>(stg + tc::sw128_offset(row, hh * 4 + j4))
+                             : rs[hh * 4 + j4], f);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[c * 8 + e] += f[e];
+                for (int e = 0; e < 8; ++e) v[j4 * 8 + e] += f[e];
               }
             }
-            pack64();
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+              const float f[8] = {v[j4 * 8], v[j4 * 8 + 1], v[j4 * 8 + 2], v[j4 * 8 + 3],
+                                  v[j4 * 8 + 4], v[j4 * 8 + 5], v[j4 * 8 + 6], v[j4 * 8 + 7]};
+              pk[hh * 4 + j4] = pack8(f);
+            }
           }
           if (issuer) {
             // the store that last read the slot about to be refilled has drained: with a residual
@@ -307,19 +304,9 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
             else asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
             if (rtma) pf_issue();
           }
-          if (rtma) {
-            if (!all_ok(tc::mbar_wait(&resf[slot], (bq / D) & 1))) { atomicExch(&g_bf16_error, 8); live = false; break; }
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              float f[8];
-              unpack8(*reinterpret_cast<const uint4*>(stg + tc::sw128_offset(row, c)), f);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[c * 8 + e] += f[e];
-            }
-            pack64();
-          } else {
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-          }
+          // without the TMA residual the slot's last reader is only known to the issuer; with it
+          // every thread rewrites just its own row of the box it has read
+          if (!rtma) asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
           if (rreg && box + 1 < nb) fetch_res((box + 1) * 64);
 #pragma unroll
           for (int c = 0; c < 8; ++c)
@@ -506,10 +493,11 @@ int read_bf16_error(int* out, int clear) {
   return CSSM_OK;
 }
 
-// Tile width: 256 columns (two TMEM accumulators), 128 or 64 (four), all with the TMA-store epilogue;
+// Tile width: 256, 192, 128 or 64 columns with the TMA-store epilogue;
 // other multiples of 32 up to 256 as one tile with direct stores.
 int gemm_bf16_pick_bn(int N) {
   if (N % 256 == 0) return 256;
+  if (N % 192 == 0) return 192;
   if (N % 128 == 0) return 128;
   if (N % 64 == 0) return 64;
   if (N <= 256 && N % 32 == 0) return N;
@@ -622,7 +610,7 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
     if (!im2col && !make_kmajor_map(&amap, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, GB_BM))
       return CSSM_ERR_CUDA;
     tma_out = tma_out && make_out_map(&omap, g.out, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldo);
-    if (tma_out && g.res != nullptr)
+    if (tma_out && g.res != nullptr && g.BN <= 128)
       tma_out = make_out_map(&rmap, const_cast<__nv_bfloat16*>(g.res), (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldr);
   }
   if (!make_kmajor_map(&bmap, g.Wt, (uint64_t)g.N, (uint64_t)g.Kpad, (uint64_t)g.ldw, (uint32_t)g.BN))
@@ -635,22 +623,25 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   const int grid = tiles < sms ? tiles : sms;
   const size_t stage = GB_A_BYTES + (size_t)g.BN * 128u;
   const size_t budget = 227 * 1024, fixed = 256 + 1024;
-  g.nacc = g.BN <= 128 ? 4 : 2;
+  // Residual by TMA (plain GEMMs with tiles of at most 128 columns): four accumulators and three or
+  // four staging slots per epilogue half.  Everything else: two accumulators, two slots, residual
+  // rows (if any) by plain loads -- the configuration that measured best without a residual.
+  const bool rtma = tma_out && g.res != nullptr && !conv && g.BN <= 128;
+  g.nacc = rtma ? 4 : 2;
   g.stages = GB_MAX_STAGES;
   g.ostg = 0;
   if (tma_out) {
-    // staging slots per epilogue half: as many as fit beside the operand ring, two to four; the
-    // residual prefetch by TMA wants three (BN = 256 has room for two: residual rows by plain loads)
-    if (g.BN == 256) g.stages = 3;
-    g.ostg = (int)((budget - fixed - g.stages * stage) / (2 * 16384));
+    while (g.stages > 2 && g.stages * stage + 4 * 16384 + fixed > budget) --g.stages;
+    g.ostg = rtma ? (int)((budget - fixed - g.stages * stage) / (2 * 16384)) : 2;
     if (g.ostg > 4) g.ostg = 4;
-    if (g.ostg < 2) return CSSM_ERR_UNSUPPORTED;
+    if (g.ostg < (rtma ? 3 : 2)) return CSSM_ERR_UNSUPPORTED;
   } else {
     while (g.stages > 2 && g.stages * stage + fixed > budget) --g.stages;
   }
   const size_t smem = g.stages * stage + (size_t)g.ostg * 2 * 16384 + fixed;
-  auto kern = im2col ? (tma_out ? gemm_bf16_kernel<true, true> : gemm_bf16_kernel<true, false>)
-                     : (tma_out ? gemm_bf16_kernel<false, true> : gemm_bf16_kernel<false, false>);
+  auto kern = im2col ? (tma_out ? gemm_bf16_kernel<true, true, false> : gemm_bf16_kernel<true, false, false>)
+                     : (tma_out ? (rtma ? gemm_bf16_kernel<false, true, true> : gemm_bf16_kernel<false, true, false>)
+                                : gemm_bf16_kernel<false, false, false>);
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   kern<<<grid, im2col ? GB_THREADS_CONV : GB_THREADS_PLAIN, smem, st>>>(g, amap, bmap, omap, rmap);

@@ -159,12 +159,102 @@ stem_conv1_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
     }
   }
 }
+// The same conv for the shape the model has (3 input channels, 32 output channels, even image sides:
+// XLA's 'SAME' rule then pads one row below and one column to the right only).  Thread = TWO adjacent
+// output pixels: their 3 x 5 x 3 input window is loaded once with 8-byte loads, every weight vector
+// read from shared memory (float4 broadcasts) feeds both pixels, the 32 output channels of a pixel are
+// 16 packed f32x2 accumulators (half the FMA issue slots of scalar code), GELU on pairs, and the
+// thread writes 128 contiguous bytes.
+__global__ void __launch_bounds__(128)
+stem_conv1_pair_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
+                       const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int Nimg, int Hi,
+                       int Wi, int Ho, int Wo, int gelu) {
+  constexpr int CI = 3, CO = 32, K = 9 * CI;
+  __shared__ __align__(16) float ws[K * CO + CO];
+  for (int i = threadIdx.x; i < K * CO; i += blockDim.x) ws[i] = wk[i];
+  for (int i = threadIdx.x; i < CO; i += blockDim.x) ws[K * CO + i] = bias[i];
+  __syncthreads();
+  const int Wp = Wo / 2;
+  const long long total = (long long)Nimg * Ho * Wp;
+  for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < total;
+       it += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(it % Wp), ho = (int)((it / Wp) % Ho), n = (int)(it / ((long long)Wp * Ho));
+    // window: rows 2 ho .. 2 ho + 2, columns 4 p .. 4 p + 4 (row Hi / column Wi = zero padding)
+    float in[3][5 * CI];
+#pragma unroll
+    for (int ti = 0; ti < 3; ++ti) {
+      const int hi = 2 * ho + ti;
+      const bool rin = hi < Hi;
+      const uint2* rp = reinterpret_cast<const uint2*>(x + (((size_t)n * Hi + (rin ? hi : 0)) * Wi + 4 * p) * CI);
+      const bool c4 = 4 * p + 4 < Wi;
+      uint2 u[4];
+#pragma unroll
+      for (int q = 0; q < 3; ++q) u[q] = rin ? __ldg(rp + q) : make_uint2(0u, 0u);
+      u[3] = (rin && c4) ? __ldg(rp + 3) : make_uint2(0u, 0u);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = bf16x2_to_float2(u[q].x), b = bf16x2_to_float2(u[q].y);
+        if (4 * q < 5 * CI) in[ti][4 * q] = a.x;
+        if (4 * q + 1 < 5 * CI) in[ti][4 * q + 1] = a.y;
+        if (4 * q + 2 < 5 * CI) in[ti][4 * q + 2] = b.x;
+        if (4 * q + 3 < 5 * CI) in[ti][4 * q + 3] = b.y;
+      }
+    }
+    unsigned long long accA[CO / 2], accB[CO / 2];
+#pragma unroll
+    for (int j = 0; j < CO / 2; ++j) {
+      const float2 b2 = *reinterpret_cast<const float2*>(ws + K * CO + 2 * j);
+      accA[j] = accB[j] = pk2(b2.x, b2.y);
+    }
+#pragma unroll
+    for (int ti = 0; ti < 3; ++ti)
+#pragma unroll
+      for (int tj = 0; tj < 3; ++tj)
+#pragma unroll
+        for (int c = 0; c < CI; ++c) {
+          const float xa = in[ti][tj * CI + c], xb = in[ti][(tj + 2) * CI + c];
+          const unsigned long long pa = pk2(xa, xa), pb = pk2(xb, xb);
+          const float4* wr = reinterpret_cast<const float4*>(ws + ((ti * 3 + tj) * CI + c) * CO);
+#pragma unroll
+          for (int j = 0; j < CO / 4; ++j) {
+            const float4 w4 = wr[j];
+            const unsigned long long w01 = pk2(w4.x, w4.y), w23 = pk2(w4.z, w4.w);
+            accA[2 * j] = fma2(pa, w01, accA[2 * j]); accA[2 * j + 1] = fma2(pa, w23, accA[2 * j + 1]);
+            accB[2 * j] = fma2(pb, w01, accB[2 * j]); accB[2 * j + 1] = fma2(pb, w23, accB[2 * j + 1]);
+          }
+        }
+    uint4* yo = reinterpret_cast<uint4*>(y + ((((size_t)n * Ho + ho) * Wo) + 2 * p) * CO);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+      for (int j = 0; j < CO / 8; ++j) {
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float a, b;
+          upk2(half ? accB[4 * j + e] : accA[4 * j + e], a, b);
+          if (gelu) gelu_tanh_x2(a, b);
+          o[e] = float2_to_bf16x2(a, b);
+        }
+        yo[half * (CO / 8) + j] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
 int launch_stem_conv1(const __nv_bfloat16* x, const float* wk, const float* bias, __nv_bfloat16* y,
                       int Nimg, int Hi, int Wi, int Cin, int Co, int gelu, cudaStream_t st) {
   if (Co % 8 != 0 || Cin > 16) return CSSM_ERR_UNSUPPORTED;
   const int Ho = (Hi + 1) / 2, Wo = (Wi + 1) / 2;
   const int pad_h = ((Ho - 1) * 2 + 3 - Hi > 0 ? (Ho - 1) * 2 + 3 - Hi : 0) / 2;
   const int pad_w = ((Wo - 1) * 2 + 3 - Wi > 0 ? (Wo - 1) * 2 + 3 - Wi : 0) / 2;
+  if (Cin == 3 && Co == 32 && Hi % 2 == 0 && Wi % 4 == 0 && aligned16(x) && aligned16(y)) {
+    const long long pairs = (long long)Nimg * Ho * (Wo / 2);
+    long long blocks = (pairs + 127) / 128;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    stem_conv1_pair_kernel<<<(int)blocks, 128, 0, st>>>(x, wk, bias, y, Nimg, Hi, Wi, Ho, Wo, gelu);
+    return check_launch();
+  }
   const size_t smem = (size_t)(9 * Cin * Co + Co) * 4;
   const int co = Co % 32 == 0 ? 32 : (Co % 16 == 0 ? 16 : 8);
   const long long total = (long long)Nimg * Ho * Wo * (Co / co);

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass, field
-from typing import Any, Dict, Sequence
+from typing import Any, Dict, Optional, Sequence
 
 import numpy as np
 import torch
@@ -337,6 +337,7 @@ class BoundShvit:
         self.w = w
         self.buf = _Buffers(device)
         self._plans: Dict[Any, torch.Tensor] = {}
+        self._pipe = None
 
     def desc(self, shape):
         return self.mod.desc(shape)
@@ -403,3 +404,37 @@ class BoundShvit:
                                              logits_host.data_ptr(), ws.data_ptr(), n,
                                              _stream_ptr(self.device)), "cssm_shvit_forward_host")
         return logits_host
+
+    def forward_host_pipelined(self, x_host: torch.Tensor, x_next_host: Optional[torch.Tensor],
+                               logits_host: torch.Tensor):
+        """Streaming form of forward_host for a loop over batches: computes the logits of x_host and,
+        meanwhile, copies x_next_host (the batch the next call will be given; may be None) to the
+        device.  x_next_host must stay unchanged until that next call.  Returns after the logits of
+        x_host have arrived."""
+        d = self.desc(tuple(x_host.shape))
+        if x_next_host is not None and tuple(x_next_host.shape) != tuple(x_host.shape):
+            raise ValueError("x_next_host must have the shape of x_host")
+        pl = self.plan(d)
+        n = self.L.cssm_shvit_host_pipe_workspace_bytes(C.byref(d))
+        ws = self.buf.get("ws_pipe", n)
+        if self._pipe is None:
+            h = C.c_void_p()
+            check(self.L.cssm_shvit_host_pipe_create(C.byref(h)), "cssm_shvit_host_pipe_create")
+            self._pipe = h
+        check(self.L.cssm_shvit_forward_host_pipelined(
+            C.byref(d), C.byref(self.w), pl.data_ptr(), self._pipe, x_host.data_ptr(),
+            x_next_host.data_ptr() if x_next_host is not None else None, logits_host.data_ptr(),
+            ws.data_ptr(), n, _stream_ptr(self.device)), "cssm_shvit_forward_host_pipelined")
+        return logits_host
+
+    def close(self):
+        """Waits for a prefetch still in flight and frees the pipe of forward_host_pipelined."""
+        if self._pipe is not None:
+            self.L.cssm_shvit_host_pipe_destroy(self._pipe)
+            self._pipe = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

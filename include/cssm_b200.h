@@ -566,6 +566,28 @@ int cssm_shvit_forward_host(const cssm_shvit_desc* d, const cssm_shvit_weights* 
                             const void* x_bf16_host, float* logits_host, void* workspace,
                             size_t workspace_bytes, void* stream);
 
+/* Streaming form of the host entry point, for a loop that feeds batch after batch (the reference's
+ * evaluation loop, main.py:522-561, prefetches its next batch the same way): while batch i computes,
+ * the images of batch i+1 are copied to the device on the pipe's own stream.
+ *   cssm_shvit_host_pipe_create / _destroy: a caller-owned handle holding one copy stream, two
+ *     events and the address of the prefetched batch; it owns no device memory.
+ *   cssm_shvit_forward_host_pipelined(..., x_bf16_host, x_next_bf16_host, ...): computes the logits of
+ *     x_bf16_host for the whole batch at once and returns after they have arrived on the host.  If the
+ *     previous call on this pipe named the same address as its x_next, the images are already on the
+ *     device (or still arriving: the compute stream waits for the copy's event); otherwise they are
+ *     copied first.  x_next_bf16_host (may be NULL) starts copying into the other input buffer before
+ *     the call computes; the caller must leave that host buffer unchanged until the next call on this
+ *     pipe or its destruction.  Workspace: cssm_shvit_host_pipe_workspace_bytes (the model workspace,
+ *     two whole-batch input buffers, the logits). */
+typedef struct cssm_shvit_host_pipe cssm_shvit_host_pipe;
+int cssm_shvit_host_pipe_create(cssm_shvit_host_pipe** pipe);
+int cssm_shvit_host_pipe_destroy(cssm_shvit_host_pipe* pipe);
+size_t cssm_shvit_host_pipe_workspace_bytes(const cssm_shvit_desc* d);
+int cssm_shvit_forward_host_pipelined(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
+                                      cssm_shvit_host_pipe* pipe, const void* x_bf16_host,
+                                      const void* x_next_bf16_host, float* logits_host, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
 /* The bf16 tensor-core GEMM of the model's Dense layers on its own (nn.Dense with dtype bfloat16:
  * shvit.py:165-180; cssm.py:481, 584 inside a bf16 model):
  *   out (M,N) bf16 = act(A (M,K) bf16 @ kernel (K,N) + bias) [+ res (M,N) bf16]

@@ -131,6 +131,33 @@ def test_host_entry_matches_device_entry():
     assert all(ms >= 0 for _, ms, _ in launches)
 
 
+def test_streaming_host_entry_prefetches_the_next_batch():
+    """forward_host_pipelined: a batch that the previous call prefetched, a batch that nobody
+    prefetched, and a prefetch that is never used all give the device entry point's logits."""
+    p, s = sv.init_shvit_params(9, (64, 64), embed_dims=(32, 32, 64, 64), depths=(1, 1, 1, 1), num_classes=7,
+                                kernel_sizes=(3, 3, 3, 3))
+    model = CSSMSHViT(embed_dims=(32, 32, 64, 64), depths=(1, 1, 1, 1), num_classes=7, num_timesteps=2,
+                      kernel_sizes=(3, 3, 3, 3))
+    bound = model.bind({"params": p, "batch_stats": s})
+    xs = [torch.randn((16, 64, 64, 3)).to(torch.bfloat16).pin_memory() for _ in range(4)]
+    want = [bound(x.cuda()).cpu() for x in xs]
+    lh = torch.empty((16, 7), dtype=torch.float32).pin_memory()
+    bound.forward_host_pipelined(xs[0], xs[1], lh)          # cold: copies xs[0] itself, prefetches xs[1]
+    assert torch.equal(lh, want[0])
+    bound.forward_host_pipelined(xs[1], xs[2], lh)          # prefetched
+    assert torch.equal(lh, want[1])
+    bound.forward_host_pipelined(xs[3], None, lh)           # the prefetch of xs[2] is dropped
+    assert torch.equal(lh, want[3])
+    bound.forward_host_pipelined(xs[2], xs[2], lh)          # nothing prefetched; next = the same buffer
+    assert torch.equal(lh, want[2])
+    bound.forward_host_pipelined(xs[2], None, lh)
+    assert torch.equal(lh, want[2])
+    bound.close()
+    bound.forward_host_pipelined(xs[0], None, lh)           # a new pipe after close()
+    assert torch.equal(lh, want[0])
+    bound.close()
+
+
 def test_cfg5_full_batch_picked_samples():
     """BASELINE configs[4] at its full size (cssm_shvit_s1, T = 1, kernel_size 1, batch 512 of
     224x224x3 bf16 N(0,1) images, 1000 classes): logits of samples picked out of the batch against the
