@@ -73,7 +73,7 @@ _SHVIT = dict(num_classes=1000, embed_dims=(64, 128, 256, 384), depths=(1, 2, 2,
               kernel_sizes=(1, 1, 1, 1), short_conv_size=4, short_conv_spatial_size=0, gate_type="factored")
 WORKLOADS["cfg5"] = dict(kind="shvit", model=_SHVIT, B=512, data="gaussian", hw=224)
 # the same model at a size for profiler captures (stage-0 activations 13 MB per tensor... x 32 images)
-WORKLOADS["cfg5_small"] = dict(kind="shvit", model=_SHVIT, B=64, data="gaussian", hw=224)
+WORKLOADS["cfg5_small"] = dict(kind="shvit", model=_SHVIT, B=128, data="gaussian", hw=224)
 GATED_STAGES = ["in_proj", "short_conv", "gates", "spectral", "out_proj"]
 GDN_STAGES = ["dwconv_ctx", "qkv_proj", "gate_proj", "gates", "short_convs", "spectral", "out_proj"]
 

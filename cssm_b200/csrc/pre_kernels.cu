@@ -557,66 +557,76 @@ __global__ void __launch_bounds__(256) gated_gates_kernel(const GatedGateArgs g)
 }
 
 // Factored gates of many frames with small planes (the CSSM-SHViT stages: hundreds of frames of
-// 14x14 / 7x7): a CTA keeps the six gate matrices (C x H and C x Wf each, at most ~100 KB) in shared
-// memory and walks over its frames; per frame each warp computes a few of the 3 (H + Wf) gate vector
-// entries (lanes split the channels, shuffle reduction), then the bins are written.
+// 14x14 / 7x7).  A CTA takes GB_FR frames.  It first copies the six gate matrices (C x H and C x Wf
+// each, at most ~100 KB) to shared memory with every thread's 16-byte loads all in flight at once (a
+// walk through them with a few loads per thread in flight is a chain of cold misses: 31 us); then a
+// thread computes whole gate-vector entries (one dot product over the C channels) and the bins are
+// written.
+constexpr int GB_FR = 4;
 __global__ void __launch_bounds__(256) gated_gates_batched_kernel(const GatedGateArgs g) {
-  extern __shared__ float sh[];
+  extern __shared__ __align__(16) float sh[];
   const int Wf = g.W / 2 + 1, NB = g.H * Wf, per = g.H + Wf;
-  float* wsm = sh;                         // [3][C][per]: row c holds the H then the Wf weights of channel c
-  float* bsm = wsm + 3 * g.C * per;        // [3][per]
-  float* ctx = bsm + 3 * per;              // [C]
-  float* vec = ctx + g.C;                  // [3][per]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // the six source matrices are contiguous: flat coalesced reads, four loads in flight per thread
-  for (int m6 = 0; m6 < 6; ++m6) {
-    const int gi = m6 >> 1, ncol = (m6 & 1) ? Wf : g.H, coff = (m6 & 1) ? g.H : 0;
-    const float* src = g.gk[m6];
-    float* dst = wsm + (size_t)gi * g.C * per + coff;
-    const int n = g.C * ncol;
-    for (int i0 = tid; i0 < n; i0 += 4 * 256) {
-      float v[4];
+  const int nH = g.C * g.H, nW = g.C * Wf;           // floats per matrix (multiples of 4: C % 4 == 0)
+  float* wsm = sh;                         // six matrices as they lie in memory: [gate][H part | Wf part]
+  float* ctx = wsm + 3 * (nH + nW);        // [GB_FR][C]
+  float* vec = ctx + GB_FR * g.C;          // [GB_FR][3][per]: the H then the Wf entries of each gate
+  const int tid = threadIdx.x;
+  const int f0 = blockIdx.x * GB_FR;
+  const int nf = g.BT - f0 < GB_FR ? g.BT - f0 : GB_FR;
+  const float inv = 1.0f / (float)(g.H * g.W);
+  {
+    const int q4H = nH / 4, q4W = nW / 4, tot4 = 3 * (q4H + q4W);
+    for (int i0 = tid; i0 < tot4; i0 += 16 * 256) {
+      float4 v[16];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = i0 + u * 256 < n ? __ldg(src + i0 + u * 256) : 0.f;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 16; ++u) {
         const int i = i0 + u * 256;
-        if (i < n) { const int c = i / ncol; dst[(size_t)c * per + (i - c * ncol)] = v[u]; }
+        if (i < tot4) {
+          const int gi = i / (q4H + q4W), r = i - gi * (q4H + q4W);
+          v[u] = r < q4H ? __ldg(reinterpret_cast<const float4*>(g.gk[2 * gi]) + r)
+                         : __ldg(reinterpret_cast<const float4*>(g.gk[2 * gi + 1]) + (r - q4H));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int i = i0 + u * 256;
+        if (i < tot4) reinterpret_cast<float4*>(wsm)[i] = v[u];
       }
     }
   }
-  for (int i = tid; i < 3 * per; i += blockDim.x) {
-    const int gi = i / per, col = i - gi * per;
-    bsm[i] = col < g.H ? g.gb[2 * gi][col] : g.gb[2 * gi + 1][col - g.H];
+  for (int i = tid; i < nf * g.C; i += blockDim.x) ctx[i] = g.ctx_sum[(size_t)f0 * g.C + i] * inv;
+  __syncthreads();
+  for (int idx = tid; idx < nf * 3 * per; idx += blockDim.x) {
+    const int f = idx / (3 * per), o = idx - f * 3 * per;
+    const int gi = o / per, col = o - gi * per;
+    const bool wpart = col >= g.H;
+    const int cc = wpart ? col - g.H : col, ncol = wpart ? Wf : g.H;
+    const float* src = wsm + gi * (nH + nW) + (wpart ? nH : 0) + cc;
+    const float* cx = ctx + f * g.C;
+    float acc[4] = {g.gb[2 * gi + (wpart ? 1 : 0)][cc], 0.f, 0.f, 0.f};
+    int c = 0;
+    for (; c + 4 <= g.C; c += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = fmaf(cx[c + u], src[(c + u) * ncol], acc[u]);
+    }
+    for (; c < g.C; ++c) acc[0] = fmaf(cx[c], src[c * ncol], acc[0]);
+    vec[idx] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
   }
-  const float inv = 1.0f / (float)(g.H * g.W);
-  for (int bt = blockIdx.x; bt < g.BT; bt += gridDim.x) {
-    __syncthreads();                       // weights staged / previous frame's vec consumed
-    for (int i = tid; i < g.C; i += blockDim.x) ctx[i] = g.ctx_sum[(size_t)bt * g.C + i] * inv;
-    __syncthreads();
-    for (int o = warp; o < 3 * per; o += 8) {
-      const int gi = o / per, col = o - gi * per;
-      const float* wc = wsm + (size_t)gi * g.C * per + col;
-      float acc = 0.f;
-      for (int c = lane; c < g.C; c += 32) acc = fmaf(ctx[c], wc[(size_t)c * per], acc);
+  __syncthreads();
+  for (int idx = tid; idx < nf * NB; idx += blockDim.x) {
+    const int f = idx / NB, bin = idx - f * NB;
+    const int kh = bin / Wf, kw = bin - kh * Wf;
+    const float* v = vec + f * 3 * per;
+    float r[3];
 #pragma unroll
-      for (int sft = 16; sft; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
-      if (lane == 0) vec[o] = acc + bsm[o];
-    }
-    __syncthreads();
-    for (int bin = tid; bin < NB; bin += blockDim.x) {
-      const int kh = bin / Wf, kw = bin - kh * Wf;
-      float r[3];
-#pragma unroll
-      for (int gi = 0; gi < 3; ++gi) r[gi] = vec[gi * per + kh] * vec[gi * per + g.H + kw];
-      const float D = gate_act(r[0], g.act);
-      float4 o;
-      o.x = expf(-D);
-      o.y = (D + 1e-8f) * r[1];
-      o.z = r[2] * inv;
-      o.w = 1e-7f * (D + 1e-8f);
-      g.maps[(size_t)bt * NB + bin_index(g.path, kh, kw, g.H, Wf)] = o;
-    }
+    for (int gi = 0; gi < 3; ++gi) r[gi] = v[gi * per + kh] * v[gi * per + g.H + kw];
+    const float D = gate_act(r[0], g.act);
+    float4 o;
+    o.x = expf(-D);
+    o.y = (D + 1e-8f) * r[1];
+    o.z = r[2] * inv;
+    o.w = 1e-7f * (D + 1e-8f);
+    g.maps[(size_t)(f0 + f) * NB + bin_index(g.path, kh, kw, g.H, Wf)] = o;
   }
 }
 
@@ -624,13 +634,14 @@ int launch_gated_gates(const GatedGateArgs& g, cudaStream_t st) {
   const int Wf = g.W / 2 + 1;
   {
     const size_t per = (size_t)g.H + Wf;
-    const size_t bsm = (3 * g.C * per + 6 * per + g.C) * sizeof(float);
-    if (g.gate_type == CSSM_GATE_FACTORED && g.BT >= 64 && g.H * Wf <= 256 && bsm <= 160 * 1024) {
+    const size_t bsm = ((size_t)3 * g.C * per + (size_t)GB_FR * (g.C + 3 * per)) * sizeof(float);
+    bool al = g.C % 4 == 0;
+    for (int i = 0; i < 6; ++i) al = al && aligned16(g.gk[i]);
+    if (g.gate_type == CSSM_GATE_FACTORED && g.BT >= 64 && g.H * Wf <= 256 && bsm <= 160 * 1024 && al) {
       cudaError_t e = cudaFuncSetAttribute(gated_gates_batched_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)bsm);
       if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
-      const int grid = g.BT < 148 ? g.BT : 148;
-      gated_gates_batched_kernel<<<grid, 256, bsm, st>>>(g);
+      gated_gates_batched_kernel<<<(g.BT + GB_FR - 1) / GB_FR, 256, bsm, st>>>(g);
       return check_launch();
     }
   }

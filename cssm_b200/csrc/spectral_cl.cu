@@ -2,19 +2,24 @@
 // (14 x 14 and 7 x 7) at T = 1, on bf16 channels-last activations:
 //   y[n, p, c] = irfft2( C * floor((Delta + 1e-8) * B * rfft2(x[n, :, c])) )[p] * z[n, p, c]
 // (at T = 1 the state is h_1 = U_1, so the kernel spectrum K_hat does not enter; z arrives already
-// through SiLU).  One THREAD per (sample, channel) plane, 64 channels of one sample per CTA: the
+// through SiLU).  TWO threads per (sample, channel) plane, 64 channels of one sample per CTA: in the
+// row passes a thread owns half of the rows, in the column pass half of the spectrum columns.  The
 // DFT twiddles are compile-time constants shared by every thread, so the transforms are straight
-// FMA chains without shuffles or exchanges; the 14-point complex DFTs of the column passes are
-// split into two 7-point DFTs.  The half spectrum of the plane (N x (N/2+1) complex) lives in
-// shared memory as [bin][thread] (conflict-free); the input tile, the z tile and the output tile
-// share one [pixel][64] bf16 buffer that is filled and drained with 16-byte accesses, so HBM sees
-// x, z and y once each as full 128-byte rows.
+// FMA chains without shuffles; the 14-point complex DFTs of the column passes are split into two
+// 7-point DFTs.  The half spectrum of the plane (N x (N/2+1) complex) waits in shared memory between
+// the passes as fp16 pairs [bin][plane] (conflict-free; the row pass scales by 1/N so that the
+// values stay in range, fp16's 11 significant bits are finer than the bf16 output): 55 KB per CTA
+// instead of 84 KB with fp32, four CTAs = 16 warps per SM instead of 4 warps.  The input tile, the z
+// tile and the output tile share one [pixel][64] bf16 buffer that is filled and drained with
+// 16-byte accesses, so HBM sees x, z and y once each as full 128-byte rows.
+#include <cuda_fp16.h>
 #include "kernels.cuh"
 #include "bf16_ops.cuh"
 
 namespace cssm {
 
-constexpr int SCL_TPB = 64;
+constexpr int SCL_PL = 64;             // planes (channels of one sample) per CTA
+constexpr int SCL_TPB = 2 * SCL_PL;    // two threads per plane
 
 template <int N> struct Tw;
 template <> struct Tw<7> {
@@ -92,30 +97,34 @@ __global__ void __launch_bounds__(SCL_TPB)
 gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
                          const float4* __restrict__ gates, __nv_bfloat16* __restrict__ y, int ldy) {
   constexpr int Wf = N / 2 + 1, P = N * N, NB = N * Wf;
+  constexpr int RH = (N + 1) / 2, KH = Wf / 2;       // rows / spectrum columns of the first thread of a plane
+  constexpr float INV_N = 1.0f / (float)N;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* R = reinterpret_cast<float*>(smem_raw);                          // [NB*2][64]
-  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(R + NB * 2 * SCL_TPB);   // [P][64]
-  float4* gs = reinterpret_cast<float4*>(tile + P * SCL_TPB);             // [NB]
-  const int tid = threadIdx.x;
-  const int slices = C / SCL_TPB;
-  const int n = blockIdx.x / slices, c0 = (blockIdx.x % slices) * SCL_TPB;
+  __half2* R = reinterpret_cast<__half2*>(smem_raw);                      // [NB][64] (re, im)
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(R + NB * SCL_PL);   // [P][64]
+  float4* gs = reinterpret_cast<float4*>(tile + P * SCL_PL);              // [NB]
+  const int tid = threadIdx.x, pl = tid & (SCL_PL - 1), hf = tid / SCL_PL;
+  const int slices = C / SCL_PL;
+  const int n = blockIdx.x / slices, c0 = (blockIdx.x % slices) * SCL_PL;
   const __nv_bfloat16* xin = xz + (size_t)n * P * ld + c0;
+  const int h_lo = hf ? RH : 0, h_hi = hf ? N : RH;
+  const int k_lo = hf ? KH : 0, k_hi = hf ? Wf : KH;
 
   // ---- stage x tile and the sample's gate map ----
   for (int q = tid; q < P * 8; q += SCL_TPB) {
     const int p = q >> 3, j = q & 7;
-    *reinterpret_cast<uint4*>(tile + p * SCL_TPB + j * 8) =
+    *reinterpret_cast<uint4*>(tile + p * SCL_PL + j * 8) =
         __ldg(reinterpret_cast<const uint4*>(xin + (size_t)p * ld + j * 8));
   }
   for (int i = tid; i < NB; i += SCL_TPB) gs[i] = __ldg(gates + (size_t)n * NB + i);
   __syncthreads();
 
-  // ---- forward rows: real N-point DFT -> Wf bins ----
+  // ---- forward rows: real N-point DFT -> Wf bins, scaled by 1/N ----
 #pragma unroll 1
-  for (int h = 0; h < N; ++h) {
+  for (int h = h_lo; h < h_hi; ++h) {
     float xv[N];
 #pragma unroll
-    for (int w = 0; w < N; ++w) xv[w] = __bfloat162float(tile[(h * N + w) * SCL_TPB + tid]);
+    for (int w = 0; w < N; ++w) xv[w] = __bfloat162float(tile[(h * N + w) * SCL_PL + pl]) * INV_N;
 #pragma unroll
     for (int k = 0; k < Wf; ++k) {
       float ar = xv[0], ai = 0.f;
@@ -124,52 +133,49 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
         ar = fmaf(xv[w], Tw<N>::c((w * k) % N), ar);
         ai = fmaf(xv[w], -Tw<N>::s((w * k) % N), ai);
       }
-      R[((h * Wf + k) * 2 + 0) * SCL_TPB + tid] = ar;
-      R[((h * Wf + k) * 2 + 1) * SCL_TPB + tid] = ai;
+      R[(h * Wf + k) * SCL_PL + pl] = __floats2half2_rn(ar, ai);
     }
   }
-  __syncthreads();                      // all threads are done with the x tile
+  __syncthreads();                      // x tile consumed; row spectra of both halves visible
   // ---- z tile (already through SiLU) into the same buffer ----
   for (int q = tid; q < P * 8; q += SCL_TPB) {
     const int p = q >> 3, j = q & 7;
-    *reinterpret_cast<uint4*>(tile + p * SCL_TPB + j * 8) =
+    *reinterpret_cast<uint4*>(tile + p * SCL_PL + j * 8) =
         __ldg(reinterpret_cast<const uint4*>(xin + C + (size_t)p * ld + j * 8));
   }
 
   // ---- columns: forward DFT, gates (T = 1: h = U), inverse DFT ----
 #pragma unroll 1
-  for (int k = 0; k < Wf; ++k) {
+  for (int k = k_lo; k < k_hi; ++k) {
     float vr[N], vi[N];
 #pragma unroll
     for (int h = 0; h < N; ++h) {
-      vr[h] = R[((h * Wf + k) * 2 + 0) * SCL_TPB + tid];
-      vi[h] = R[((h * Wf + k) * 2 + 1) * SCL_TPB + tid];
+      const float2 v = __half22float2(R[(h * Wf + k) * SCL_PL + pl]);
+      vr[h] = v.x; vi[h] = v.y;
     }
     dftc<N, -1>(vr, vi);
 #pragma unroll
     for (int kh = 0; kh < N; ++kh) {
       const float4 g = gs[kh * Wf + k];          // {exp(-D), (D+1e-8)B, C/(HW), 1e-7(D+1e-8)}
-      float ur = g.y * vr[kh], ui = g.y * vi[kh];
+      const float gy = g.y * (float)N;           // undoes the row pass's 1/N
+      float ur = gy * vr[kh], ui = gy * vi[kh];
       if (ur * ur + ui * ui < g.w * g.w) { ur = g.w; ui = 0.f; }
       vr[kh] = g.z * ur; vi[kh] = g.z * ui;
     }
     dftc<N, 1>(vr, vi);
 #pragma unroll
-    for (int h = 0; h < N; ++h) {
-      R[((h * Wf + k) * 2 + 0) * SCL_TPB + tid] = vr[h];
-      R[((h * Wf + k) * 2 + 1) * SCL_TPB + tid] = vi[h];
-    }
+    for (int h = 0; h < N; ++h) R[(h * Wf + k) * SCL_PL + pl] = __floats2half2_rn(vr[h], vi[h]);
   }
-  __syncthreads();                      // z tile complete (R is thread-private)
+  __syncthreads();                      // z tile complete; columns of both halves visible
 
   // ---- inverse rows (C2R: imaginary parts of the DC and Nyquist bins are ignored), * z ----
 #pragma unroll 1
-  for (int h = 0; h < N; ++h) {
+  for (int h = h_lo; h < h_hi; ++h) {
     float cr[Wf], ci[Wf];
 #pragma unroll
     for (int k = 0; k < Wf; ++k) {
-      cr[k] = R[((h * Wf + k) * 2 + 0) * SCL_TPB + tid];
-      ci[k] = R[((h * Wf + k) * 2 + 1) * SCL_TPB + tid];
+      const float2 v = __half22float2(R[(h * Wf + k) * SCL_PL + pl]);
+      cr[k] = v.x; ci[k] = v.y;
     }
     constexpr int KM = (N - 1) / 2;               // bins with a conjugate partner
 #pragma unroll
@@ -183,7 +189,7 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
         s2 = fmaf(-ci[k], Tw<N>::s((w * k) % N), s2);
       }
       acc = fmaf(2.f, s2, acc);
-      const int idx = (h * N + w) * SCL_TPB + tid;
+      const int idx = (h * N + w) * SCL_PL + pl;
       tile[idx] = __float2bfloat16(acc * __bfloat162float(tile[idx]));
     }
   }
@@ -192,12 +198,12 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
   for (int q = tid; q < P * 8; q += SCL_TPB) {
     const int p = q >> 3, j = q & 7;
     *reinterpret_cast<uint4*>(yo + (size_t)p * ldy + j * 8) =
-        *reinterpret_cast<const uint4*>(tile + p * SCL_TPB + j * 8);
+        *reinterpret_cast<const uint4*>(tile + p * SCL_PL + j * 8);
   }
 }
 
 bool spectral_cl_supported(int H, int W, int C, int T) {
-  return T == 1 && H == W && (H == 14 || H == 7) && C % SCL_TPB == 0;
+  return T == 1 && H == W && (H == 14 || H == 7) && C % SCL_PL == 0;
 }
 
 // xz: (Nimg, H*W, ld) bf16 with x_main in columns [0, C) and silu(z) in [C, 2C); gates: the
@@ -206,8 +212,8 @@ int launch_gated_spectral_cl(const __nv_bfloat16* xz, int ld, int Nimg, int H, i
                              const float* gates, __nv_bfloat16* y, int ldy, cudaStream_t st) {
   if (!spectral_cl_supported(H, W, C, 1) || ld % 8 != 0 || ldy % 8 != 0) return CSSM_ERR_UNSUPPORTED;
   const int Wf = W / 2 + 1, NB = H * Wf, P = H * W;
-  const size_t smem = (size_t)NB * 2 * SCL_TPB * 4 + (size_t)P * SCL_TPB * 2 + (size_t)NB * 16;
-  const int grid = Nimg * (C / SCL_TPB);
+  const size_t smem = (size_t)NB * SCL_PL * 4 + (size_t)P * SCL_PL * 2 + (size_t)NB * 16;
+  const int grid = Nimg * (C / SCL_PL);
   cudaError_t e;
   if (H == 14) {
     e = cudaFuncSetAttribute(gated_spectral_cl_kernel<14>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
