@@ -407,14 +407,19 @@ def run_shvit(args, name, ctx):
     value = world * B * args.steps / (total_ms / 1e3)
 
     # per-kernel times from launch traces of the same forward
-    agg, nl = {}, 0
+    agg, nl, per_launch = {}, 0, None
     reps = max(3, min(args.steps, 10))
     for _ in range(reps):
         _, launches = bound.forward_traced(x, out=logits)
         nl = len(launches)
-        for kind, ms, nbytes in launches:
+        if per_launch is None:
+            per_launch = [[kind, 0.0, nbytes] for kind, _, nbytes in launches]
+        for i, (kind, ms, nbytes) in enumerate(launches):
             a = agg.setdefault(kind, [0, 0.0, 0.0])
             a[0] += 1; a[1] += ms; a[2] += nbytes
+            per_launch[i][1] += ms / reps
+    # every launch of one step in order: [kind, microseconds, algorithmic megabytes]
+    launch_list = [[k, round(ms * 1e3, 1), round(nb / 1e6, 1)] for k, ms, nb in per_launch]
     peak, peak_src = peaks()
     kernels = {k: {"launches_per_step": a[0] // reps, "ms_per_step": a[1] / reps,
                    "algorithmic_bytes_per_step": a[2] / reps,
@@ -506,8 +511,8 @@ def run_shvit(args, name, ctx):
                    "gate_type": m["gate_type"], "num_classes": K,
                    "collective": "all-gather of the logits per step" if world > 1 else None,
                    "l2": "stage-0/1 activations (205 / 103 MB per tensor at batch 512) larger than the 126 MB L2"},
-        "kernels": kernels, "roofline": roofline, "model_hbm": model_hbm, "sustained": sustained,
-        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": nl * args.steps,
+        "kernels": kernels, "launches": launch_list, "roofline": roofline, "model_hbm": model_hbm,
+        "sustained": sustained, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": nl * args.steps,
     }
 
 
@@ -679,6 +684,7 @@ def main():
                          "over the ranks (default: weak scaling, that batch per GPU)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-sustain", action="store_true", help="skip the >= 2 s sustained loop (profiler runs)")
     args = ap.parse_args()
     single = args.workload is not None
     if not single:
@@ -709,7 +715,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    ctx = dict(dev=dev, st=st, world=world, rank=rank, local=local, barrier=barrier, sustain=True)
+    ctx = dict(dev=dev, st=st, world=world, rank=rank, local=local, barrier=barrier, sustain=not args.no_sustain)
     run = lambda name: (run_shvit if is_shvit(name) else run_simple)(args, name, ctx)
     clk = ClockSampler(local)
     clk.__enter__()                       # sampled over the headline's timed regions
