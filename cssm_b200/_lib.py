@@ -232,6 +232,9 @@ SIGNATURES = {
     "cssm_simple_host_workspace_bytes": (C.c_size_t, [C.POINTER(SimpleDesc), _P]),
     "cssm_simple_forward_host": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P,
                                            _P, _P, _P, _P, C.c_size_t, C.c_int32, _P]),
+    "cssm_simple_host_pipe_workspace_bytes": (C.c_size_t, [C.POINTER(SimpleDesc), _P]),
+    "cssm_simple_forward_host_pipelined": (C.c_int, [C.POINTER(SimpleDesc), C.POINTER(SimpleWeights), _P, _P,
+                                                     _P, _P, _P, _P, _P, _P, C.c_size_t, C.c_int32, _P]),
     "cssm_device_error": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "cssm_shvit_block_plan_bytes": (C.c_size_t, [C.POINTER(ShvitBlockDesc)]),
     "cssm_shvit_block_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitBlockDesc)]),
@@ -249,8 +252,8 @@ SIGNATURES = {
     "cssm_shvit_host_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
     "cssm_shvit_forward_host": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
                                           C.c_size_t, _P]),
-    "cssm_shvit_host_pipe_create": (C.c_int, [C.POINTER(_P)]),
-    "cssm_shvit_host_pipe_destroy": (C.c_int, [_P]),
+    "cssm_host_pipe_create": (C.c_int, [C.POINTER(_P)]),
+    "cssm_host_pipe_destroy": (C.c_int, [_P]),
     "cssm_shvit_host_pipe_workspace_bytes": (C.c_size_t, [C.POINTER(ShvitDesc)]),
     "cssm_shvit_forward_host_pipelined": (C.c_int, [C.POINTER(ShvitDesc), C.POINTER(ShvitWeights), _P, _P, _P, _P,
                                                     _P, _P, C.c_size_t, _P]),

@@ -205,7 +205,8 @@ static size_t deltanet_smem_bytes(int H, int W) {
 }
 
 static int deltanet_path(const cssm_deltanet_desc& d) {
-  return spectral_path(d.H, d.W) == PATH_R64 ? PATH_R64 : PATH_GENERIC;
+  const SpectralPath p = spectral_path(d.H, d.W);
+  return (p == PATH_R64 || p == PATH_R32) ? p : PATH_GENERIC;
 }
 
 static int deltanet_validate(const cssm_deltanet_desc* d) {
@@ -408,6 +409,8 @@ int cssm_deltanet_forward(const cssm_deltanet_desc* d, const cssm_deltanet_weigh
   sp.chan = chan ? (const float2*)(ws + l.chan) : nullptr;
   if (deltanet_path(*d) == PATH_R64) {
     if ((s = launch_deltanet_spectral_r64(sp, st)) != CSSM_OK) return s;
+  } else if (deltanet_path(*d) == PATH_R32) {
+    if ((s = launch_deltanet_spectral_r32(sp, st)) != CSSM_OK) return s;
   } else {
     const size_t smem = deltanet_smem_bytes(d->H, d->W);
     cudaError_t e = cudaFuncSetAttribute(deltanet_spectral_kernel,

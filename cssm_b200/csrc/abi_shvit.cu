@@ -598,20 +598,12 @@ static PipeWs pipe_ws_layout(const cssm_shvit_desc& d) {
 }
 
 }  // extern "C"
-struct cssm_shvit_host_pipe {
-  cudaStream_t copy;
-  cudaEvent_t copied[2];       // the copy into input buffer j has finished
-  cudaEvent_t computed;        // the last forward has finished reading its input buffer
-  const void* src;             // host address whose images sit (or are arriving) in buffer `buf`
-  const void* ws;              // ... of this workspace
-  int buf;
-};
 extern "C" {
 
-int cssm_shvit_host_pipe_create(cssm_shvit_host_pipe** pipe) {
+int cssm_host_pipe_create(cssm_host_pipe** pipe) {
   if (!pipe) return CSSM_ERR_NULL;
   *pipe = nullptr;
-  cssm_shvit_host_pipe* p = new (std::nothrow) cssm_shvit_host_pipe();
+  cssm_host_pipe* p = new (std::nothrow) cssm_host_pipe();
   if (!p) return CSSM_ERR_CUDA;
   memset(p, 0, sizeof(*p));
   cudaError_t e = cudaStreamCreateWithFlags(&p->copy, cudaStreamNonBlocking);
@@ -619,14 +611,14 @@ int cssm_shvit_host_pipe_create(cssm_shvit_host_pipe** pipe) {
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->computed, cudaEventDisableTiming);
   if (e != cudaSuccess) {
     set_cuda_error(e);
-    cssm_shvit_host_pipe_destroy(p);
+    cssm_host_pipe_destroy(p);
     return CSSM_ERR_CUDA;
   }
   *pipe = p;
   return CSSM_OK;
 }
 
-int cssm_shvit_host_pipe_destroy(cssm_shvit_host_pipe* p) {
+int cssm_host_pipe_destroy(cssm_host_pipe* p) {
   if (!p) return CSSM_OK;
   if (p->copy) cudaStreamSynchronize(p->copy);        // a prefetch may still be reading the host buffer
   for (int i = 0; i < 2; ++i)
@@ -643,7 +635,7 @@ size_t cssm_shvit_host_pipe_workspace_bytes(const cssm_shvit_desc* d) {
 }
 
 int cssm_shvit_forward_host_pipelined(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
-                                      cssm_shvit_host_pipe* p, const void* x_bf16_host,
+                                      cssm_host_pipe* p, const void* x_bf16_host,
                                       const void* x_next_bf16_host, float* logits_host, void* workspace,
                                       size_t workspace_bytes, void* stream) {
   if (cssm_shvit_workspace_bytes(d) == 0) return model_validate(d) != CSSM_OK ? model_validate(d) : CSSM_ERR_UNSUPPORTED;
@@ -653,40 +645,20 @@ int cssm_shvit_forward_host_pipelined(const cssm_shvit_desc* d, const cssm_shvit
   if (workspace_bytes < h.total) return CSSM_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   char* ws = (char*)workspace;
-  int rc = CSSM_OK;
-  cudaError_t e = cudaSuccess;
-#define CSSM_TRY(call) do { if (rc == CSSM_OK) { e = (call); if (e != cudaSuccess) { set_cuda_error(e); rc = CSSM_ERR_CUDA; } } } while (0)
-  int j;
-  if (p->src == x_bf16_host && p->ws == workspace) {
-    j = p->buf;                                        // prefetched by the previous call
-  } else {
-    j = 0;
-    // after whatever the caller queued on its stream, and after any copy still running on the pipe
-    CSSM_TRY(cudaEventRecord(p->computed, st));
-    CSSM_TRY(cudaStreamWaitEvent(p->copy, p->computed, 0));
-    CSSM_TRY(cudaMemcpyAsync(ws + h.xbuf[0], x_bf16_host, h.xbytes, cudaMemcpyHostToDevice, p->copy));
-    CSSM_TRY(cudaEventRecord(p->copied[0], p->copy));
-  }
-  p->src = nullptr;
-  if (x_next_bf16_host != nullptr && rc == CSSM_OK) {
-    // buffer 1 - j was last read by the previous call's forward, which that call waited for
-    CSSM_TRY(cudaMemcpyAsync(ws + h.xbuf[1 - j], x_next_bf16_host, h.xbytes, cudaMemcpyHostToDevice, p->copy));
-    CSSM_TRY(cudaEventRecord(p->copied[1 - j], p->copy));
-    if (rc == CSSM_OK) { p->src = x_next_bf16_host; p->ws = workspace; p->buf = 1 - j; }
-  }
-  CSSM_TRY(cudaStreamWaitEvent(st, p->copied[j], 0));
+  int j = 0;
+  int rc = host_pipe_stage(p, workspace, ws + h.xbuf[0], ws + h.xbuf[1], h.xbytes, x_bf16_host,
+                           x_next_bf16_host, st, &j);
   float* ld = (float*)(ws + h.logits);
   if (rc == CSSM_OK)
     rc = cssm_shvit_forward(d, w, plan, ws + h.xbuf[j], ld, ws + h.model, h.model_bytes, stream);
-  CSSM_TRY(cudaMemcpyAsync(logits_host, ld, (size_t)d->B * d->num_classes * 4, cudaMemcpyDeviceToHost, st));
+  if (rc == CSSM_OK) {
+    const cudaError_t e = cudaMemcpyAsync(logits_host, ld, (size_t)d->B * d->num_classes * 4,
+                                          cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) { set_cuda_error(e); rc = CSSM_ERR_CUDA; }
+  }
   const cudaError_t e1 = cudaStreamSynchronize(st);
   if (rc == CSSM_OK && e1 != cudaSuccess) { set_cuda_error(e1); rc = CSSM_ERR_CUDA; }
-  if (rc != CSSM_OK) {
-    // leave no copy running into a workspace the caller may now free
-    cudaStreamSynchronize(p->copy);
-    p->src = nullptr;
-  }
-#undef CSSM_TRY
+  if (rc != CSSM_OK) host_pipe_abort(p);
   return rc;
 }
 

@@ -92,3 +92,53 @@ __host__ __device__ inline int bin_index(int path, int kh, int kw, int H, int Wf
 }
 
 }  // namespace cssm
+
+// Caller-owned state of the streaming host entry points (cssm_host_pipe_create / _destroy; the type
+// is opaque in the public header): one copy stream, its events, and which host buffer was prefetched
+// into which of the two input buffers of which workspace.
+struct cssm_host_pipe {
+  cudaStream_t copy;
+  cudaEvent_t copied[2];       // the copy into input buffer j has finished
+  cudaEvent_t computed;        // orders a cold copy behind the work already queued on the caller's stream
+  const void* src;             // host address whose batch sits (or is arriving) in buffer `buf`
+  const void* ws;              // ... of this workspace
+  int buf;
+};
+
+namespace cssm {
+// First half of a streaming host call: makes `stream` wait for the batch x_host in input buffer
+// *j of the workspace (already prefetched by the previous call on this pipe, or copied now), and
+// starts the copy of x_next_host (may be null) into the other buffer on the pipe's stream.
+inline int host_pipe_stage(cssm_host_pipe* p, void* workspace, char* xbuf0, char* xbuf1, size_t xbytes,
+                           const void* x_host, const void* x_next_host, cudaStream_t st, int* j_out) {
+  cudaError_t e = cudaSuccess;
+  char* xb[2] = {xbuf0, xbuf1};
+  int j;
+  if (p->src == x_host && p->ws == workspace) {
+    j = p->buf;                                        // prefetched by the previous call
+  } else {
+    j = 0;
+    // after whatever the caller queued on its stream, and after any copy still running on the pipe
+    e = cudaEventRecord(p->computed, st);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(p->copy, p->computed, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(xb[0], x_host, xbytes, cudaMemcpyHostToDevice, p->copy);
+    if (e == cudaSuccess) e = cudaEventRecord(p->copied[0], p->copy);
+  }
+  p->src = nullptr;
+  if (x_next_host != nullptr && e == cudaSuccess) {
+    // buffer 1 - j was last read by the previous call's forward, which that call waited for
+    e = cudaMemcpyAsync(xb[1 - j], x_next_host, xbytes, cudaMemcpyHostToDevice, p->copy);
+    if (e == cudaSuccess) e = cudaEventRecord(p->copied[1 - j], p->copy);
+    if (e == cudaSuccess) { p->src = x_next_host; p->ws = workspace; p->buf = 1 - j; }
+  }
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(st, p->copied[j], 0);
+  *j_out = j;
+  if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+  return CSSM_OK;
+}
+// Error path of a streaming host call: leave no copy running into a workspace the caller may free.
+inline void host_pipe_abort(cssm_host_pipe* p) {
+  cudaStreamSynchronize(p->copy);
+  p->src = nullptr;
+}
+}  // namespace cssm

@@ -27,18 +27,19 @@ constexpr int R64_SMEM_BYTES = (R64_EX_CF + R64_ZR_CF + R64_GB_CF) * 8 + 3 * R64
 
 __device__ int g_spec_error = 0;
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
-                              int last_only, int nogate, cudaStream_t st);
+                              int last_only, int nogate, cudaStream_t st, const float* dchan);
 
 // LAST: only the last step's output plane is produced (compile-time, so that the all-frames
 // kernel carries none of the branches).
 // MODE 0: gated block (gate maps, output times the silu(z) plane).  MODE 1: the ungated recurrence
 // S_t = K_hat S_{t-1} + X_hat_t of NoGateCSSM (no gate maps, no z plane).  MODE 2: gate maps but no
-// z plane (the single-state AdditiveCSSM).
+// z plane (the single-state AdditiveCSSM).  MODE 3: MODE 2 with a per-(frame, channel) decay dchan[frame, c]
+// on top of the maps (the additive block's per-channel gates).
 template <bool LAST, int MODE>
 __global__ void __launch_bounds__(R64_THREADS, 2)
 gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
                    const float4* __restrict__ gates, int T, int C,
-                   const __grid_constant__ CUtensorMap pmap) {
+                   const __grid_constant__ CUtensorMap pmap, const float* __restrict__ dchan) {
   constexpr int last_only = LAST ? 1 : 0;
   constexpr int PRS = 68;                                     // floats per staged row
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -120,10 +121,13 @@ gated_spectral_r64(float* __restrict__ xz, const cf* __restrict__ khat,
       float4 g[8];
       cf kh[8];
       const float4* gp = gates + frame * (64 * 33) + (c.grp << 3) + c.a;
+      // MODE 3: the decay of this (frame, channel) multiplies the map's decay entry
+      const float dc = MODE == 3 ? __ldg(dchan + frame * C + ch) : 1.f;
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         // {exp(-D), (D+1e-8)B, C/(HW), 1e-7(D+1e-8)}
         if (MODE != 1) g[q] = c.col_on ? __ldg(gp + q * (33 * 8)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE == 3) g[q].x *= dc;
         kh[q] = c.col_on ? khp[q * (33 * 8)] : mk(0.f, 0.f);
       }
       cf v[8];
@@ -201,7 +205,7 @@ constexpr int GEN_THREADS = 256;
 __global__ void __launch_bounds__(GEN_THREADS)
 gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
                        const float4* __restrict__ gates, int T, int C, int H, int W, int last_only,
-                       int nog) {
+                       int nog, const float* __restrict__ dchan) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Wf = W / 2 + 1, HW = H * W, NB = H * Wf;
   float* xs = reinterpret_cast<float*>(smem_raw);              // [H][W]
@@ -256,7 +260,8 @@ gated_spectral_generic(float* __restrict__ xz, const cf* __restrict__ khat,
         idx += kh; if (idx >= H) idx -= H;
       }
       // ungated mode: A = K_hat, U = X_hat, output scale 1/(H*W), no floor
-      const float4 g = nog == 1 ? make_float4(1.f, 1.f, 1.0f / (float)HW, 0.f) : gp[o];
+      float4 g = nog == 1 ? make_float4(1.f, 1.f, 1.0f / (float)HW, 0.f) : gp[o];
+      if (nog == 3) g.x *= __ldg(dchan + frame * C + c);
       const cf k = khc[o];
       cf A = mk(k.x * g.x, k.y * g.x);
       cf U = mk(g.y * ax, g.y * ay);
@@ -312,7 +317,7 @@ constexpr int SMALL_WARPS = 8, SMALL_MAX_HW = 256;
 __global__ void __launch_bounds__(SMALL_WARPS * 32)
 gated_spectral_small(float* __restrict__ xz, const cf* __restrict__ khat,
                      const float4* __restrict__ gates, int nplanes, int T, int C, int H, int W,
-                     int last_only, int nog) {
+                     int last_only, int nog, const float* __restrict__ dchan) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Wf = W / 2 + 1, HW = H * W, NB = H * Wf;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -368,7 +373,8 @@ gated_spectral_small(float* __restrict__ xz, const cf* __restrict__ khat,
           ax += r.x * e.x - r.y * e.y; ay += r.x * e.y + r.y * e.x;
           idx += kh; if (idx >= H) idx -= H;
         }
-        const float4 g = nog == 1 ? make_float4(1.f, 1.f, invHW, 0.f) : __ldg(gp + o);
+        float4 g = nog == 1 ? make_float4(1.f, 1.f, invHW, 0.f) : __ldg(gp + o);
+        if (nog == 3) g.x *= __ldg(dchan + frame * C + c);
         const cf k = khc[o];
         const cf A = mk(k.x * g.x, k.y * g.x);
         cf U = mk(g.y * ax, g.y * ay);
@@ -430,11 +436,12 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
 }
 
 int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const float* gates,
-                    float* xz, int last_only, int nogate, cudaStream_t st) {
+                    float* xz, int last_only, int nogate, cudaStream_t st, const float* dchan) {
+  if ((nogate == 3) != (dchan != nullptr)) return CSSM_ERR_NULL;
   struct { int B, T, H, W, C; } d = {B, T, H, W, C};
   const SpectralPath path = spectral_path(d.H, d.W);
   const int grid = d.B * d.C;
-  if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, last_only, nogate, st);
+  if (path == PATH_R32) return launch_gated_spectral_r32(xz, khat, gates, d.B, d.T, d.C, last_only, nogate, st, dchan);
   if (path == PATH_R64) {
     const size_t smem = R64_SMEM_BYTES;
     // tensor map over the planar buffer as rows of 64 floats; box 68 x 64 (see the kernel)
@@ -463,11 +470,12 @@ int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const flo
     auto kern = last_only ? gated_spectral_r64<true, 0> : gated_spectral_r64<false, 0>;
     if (nogate == 1) kern = last_only ? gated_spectral_r64<true, 1> : gated_spectral_r64<false, 1>;
     else if (nogate == 2) kern = last_only ? gated_spectral_r64<true, 2> : gated_spectral_r64<false, 2>;
+    else if (nogate == 3) kern = last_only ? gated_spectral_r64<true, 3> : gated_spectral_r64<false, 3>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     kern<<<grid, R64_THREADS, smem, st>>>(xz, khat, reinterpret_cast<const float4*>(gates), d.T,
-                                          d.C, pmap);
+                                          d.C, pmap, dchan);
   } else if (d.H * d.W <= SMALL_MAX_HW) {
     const size_t smem = small_smem_bytes(d.H, d.W);
     cudaError_t e = cudaFuncSetAttribute(gated_spectral_small,
@@ -476,7 +484,7 @@ int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const flo
     const int need = (grid + SMALL_WARPS - 1) / SMALL_WARPS;
     const int ctas = need < 148 * 6 ? need : 148 * 6;
     gated_spectral_small<<<ctas, SMALL_WARPS * 32, smem, st>>>(
-        xz, khat, reinterpret_cast<const float4*>(gates), grid, d.T, d.C, d.H, d.W, last_only, nogate);
+        xz, khat, reinterpret_cast<const float4*>(gates), grid, d.T, d.C, d.H, d.W, last_only, nogate, dchan);
   } else {
     const size_t smem = generic_smem_bytes(d.H, d.W);
     if (smem > 200 * 1024) return CSSM_ERR_UNSUPPORTED;
@@ -484,7 +492,7 @@ int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const flo
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
     gated_spectral_generic<<<grid, GEN_THREADS, smem, st>>>(
-        xz, khat, reinterpret_cast<const float4*>(gates), d.T, d.C, d.H, d.W, last_only, nogate);
+        xz, khat, reinterpret_cast<const float4*>(gates), d.T, d.C, d.H, d.W, last_only, nogate, dchan);
   }
   return check_launch();
 }

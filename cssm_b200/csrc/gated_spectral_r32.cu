@@ -19,11 +19,11 @@ constexpr int R32_SMEM_BYTES = (R32_EX_CF + R32_ZR_CF + R32_GB_CF) * 8;
 
 // LAST: only the last step's output planes are produced (compile-time switch).
 // MODE 0: gate maps and z planes; 1: ungated recurrence S_t = K_hat S_{t-1} + X_hat_t (neither);
-// 2: gate maps, no z planes.
+// 2: gate maps, no z planes; 3: as 2 with a per-(frame, channel) decay dchan[frame, c] on top of the maps.
 template <bool LAST, int MODE>
 __global__ void __launch_bounds__(R32_THREADS, 2)
 gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
-                   const float4* __restrict__ gates, int T, int C) {
+                   const float4* __restrict__ gates, int T, int C, const float* __restrict__ dchan) {
   constexpr int last_only = LAST ? 1 : 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cf* EX = reinterpret_cast<cf*>(smem_raw);
@@ -83,9 +83,11 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
       float4 g[8];
       cf kh[8];
       const float4* gp = gates + frame * NB + (kw << 2) + q;
+      const float dc = MODE == 3 ? __ldg(dchan + frame * C + c0 + cpl) : 1.f;   // per-(frame, channel) decay
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         if (MODE != 1) g[r] = col_on ? __ldg(gp + r * (17 * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE == 3) g[r].x *= dc;
         kh[r] = col_on ? khp[r * (17 * 4)] : mk(0.f, 0.f);
       }
       cf v[8];
@@ -162,15 +164,16 @@ gated_spectral_r32(float* __restrict__ xz, const cf* __restrict__ khat,
 }
 
 int launch_gated_spectral_r32(float* xz, const cf* khat, const float* gates, int B, int T, int C,
-                              int last_only, int nogate, cudaStream_t st) {
+                              int last_only, int nogate, cudaStream_t st, const float* dchan) {
   auto kern = last_only ? gated_spectral_r32<true, 0> : gated_spectral_r32<false, 0>;
   if (nogate == 1) kern = last_only ? gated_spectral_r32<true, 1> : gated_spectral_r32<false, 1>;
   if (nogate == 2) kern = last_only ? gated_spectral_r32<true, 2> : gated_spectral_r32<false, 2>;
+  if (nogate == 3) kern = last_only ? gated_spectral_r32<true, 3> : gated_spectral_r32<false, 3>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        R32_SMEM_BYTES);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   kern<<<B * (C / 4), R32_THREADS, R32_SMEM_BYTES, st>>>(
-      xz, khat, reinterpret_cast<const float4*>(gates), T, C);
+      xz, khat, reinterpret_cast<const float4*>(gates), T, C, dchan);
   return check_launch();
 }
 

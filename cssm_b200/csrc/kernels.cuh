@@ -48,7 +48,7 @@ int launch_gated_spectral(const cssm_gated_desc& d, const cf* khat, const float*
 // read and the z planes of the (B*T, 2C, H, W) buffer are neither read nor written.
 // nogate == 2: gate maps as in the gated block, but no z planes (single-state AdditiveCSSM)
 int launch_spectral(int B, int T, int H, int W, int C, const cf* khat, const float* gates,
-                    float* xz, int last_only, int nogate, cudaStream_t st);
+                    float* xz, int last_only, int nogate, cudaStream_t st, const float* dchan = nullptr);
 size_t generic_smem_bytes(int H, int W);
 int read_spec_error(int* out, int clear);
 
@@ -65,6 +65,7 @@ struct DnSpectralArgs {
   int goom_floor;
 };
 int launch_deltanet_spectral_r64(const DnSpectralArgs& a, cudaStream_t st);
+int launch_deltanet_spectral_r32(const DnSpectralArgs& a, cudaStream_t st);
 
 // ---- GDN block ----
 struct GdnDwArgs {

@@ -755,4 +755,43 @@ int cssm_simple_forward_host(const cssm_simple_desc* d, const cssm_simple_weight
   return CSSM_OK;
 }
 
+size_t cssm_simple_host_pipe_workspace_bytes(const cssm_simple_desc* d, const void* block_desc) {
+  const size_t base = cssm_simple_workspace_bytes(d, block_desc);
+  if (base == 0) return 0;
+  const size_t nx = (size_t)(d->image_input ? d->B : d->B * d->T) * d->Hin * d->Win * d->Cin * sizeof(float);
+  return base + 2 * round_up(nx, 256) + round_up((size_t)d->B * d->num_classes * sizeof(float), 256);
+}
+
+int cssm_simple_forward_host_pipelined(const cssm_simple_desc* d, const cssm_simple_weights* w,
+                                       const void* block_desc, const void* block_weights,
+                                       const void* block_plan, cssm_host_pipe* pipe, const float* x_host,
+                                       const float* x_next_host, float* logits_host, void* workspace,
+                                       size_t workspace_bytes, int32_t flags, void* stream) {
+  const size_t base = cssm_simple_workspace_bytes(d, block_desc);
+  if (base == 0) return simple_validate(d) != CSSM_OK ? simple_validate(d) : CSSM_ERR_DIMS;
+  if (!pipe || !x_host || !logits_host || !workspace) return CSSM_ERR_NULL;
+  if (!aligned16(workspace)) return CSSM_ERR_ALIGN;
+  if (workspace_bytes < cssm_simple_host_pipe_workspace_bytes(d, block_desc)) return CSSM_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t nx = (size_t)(d->image_input ? d->B : d->B * d->T) * d->Hin * d->Win * d->Cin * sizeof(float);
+  const size_t nl = (size_t)d->B * d->num_classes * sizeof(float);
+  char* ws = (char*)workspace;
+  char* xb0 = ws + base;
+  char* xb1 = xb0 + round_up(nx, 256);
+  float* ld = (float*)(xb1 + round_up(nx, 256));
+  int j = 0;
+  int rc = host_pipe_stage(pipe, workspace, xb0, xb1, nx, x_host, x_next_host, st, &j);
+  if (rc == CSSM_OK)
+    rc = cssm_simple_forward(d, w, block_desc, block_weights, block_plan, (const float*)(j ? xb1 : xb0), ld,
+                             workspace, base, flags, stream);
+  if (rc == CSSM_OK) {
+    const cudaError_t e = cudaMemcpyAsync(logits_host, ld, nl, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) { set_cuda_error(e); rc = CSSM_ERR_CUDA; }
+  }
+  const cudaError_t e1 = cudaStreamSynchronize(st);
+  if (rc == CSSM_OK && e1 != cudaSuccess) { set_cuda_error(e1); rc = CSSM_ERR_CUDA; }
+  if (rc != CSSM_OK) host_pipe_abort(pipe);
+  return rc;
+}
+
 }  // extern "C"

@@ -664,7 +664,8 @@ class AdditiveCSSM:
     """Single-state path of the reference's AdditiveCSSM (src/models/cssm.py:2961-3359,
     3580-3626): x_proj -> rfft2 -> h_t = (d_X K_hat) h_{t-1} + B_X X_hat_t -> C_gate h_t ->
     irfft2 -> output_proj.  Field names and defaults are the reference's; only
-    single_state=True with gate_type 'dense' or 'factored' has a CUDA path, everything else
+    single_state=True with gate_type 'dense', 'factored' or 'channel' (d_X per channel, B_X and
+    C_gate per-pixel 1x1-conv maps applied in the spatial domain) has a CUDA path, everything else
     raises NotImplementedError (no fallback)."""
     channels: int
     kernel_size: int = 11
@@ -694,9 +695,9 @@ class AdditiveCSSM:
         if not self.single_state:
             raise NotImplementedError("AdditiveCSSM: only single_state=True has a CUDA path "
                                       "(the 2- and 3-state triangular scans are not built)")
-        if self.gate_type not in ("dense", "factored"):
+        if self.gate_type not in ("dense", "factored", "channel"):
             raise NotImplementedError(f"AdditiveCSSM: gate_type {self.gate_type!r} not built "
-                                      "(supported: 'dense', 'factored')")
+                                      "(supported: 'dense', 'factored', 'channel')")
         if self.rope_mode not in ROPE_MODES:
             raise NotImplementedError(f"AdditiveCSSM: rope_mode {self.rope_mode!r} not built")
         if self.position_independent_gates or self.learned_init:
@@ -721,6 +722,9 @@ class AdditiveCSSM:
             if self.gate_type == "factored":
                 p[f"{n}_h"] = {"kernel": (Cc, H), "bias": (H,)}
                 p[f"{n}_w"] = {"kernel": (Cc, Wf), "bias": (Wf,)}
+            elif self.gate_type == "channel":
+                # d_X: Dense(C); B_X, C_gate: 1x1 convs (cssm.py:3168-3178)
+                p[n] = {"kernel": (Cc, Cc) if n == "d_X" else (1, 1, Cc, Cc), "bias": (Cc,)}
             else:
                 p[n] = {"kernel": (Cc, H * Wf), "bias": (H * Wf,)}
         return p
@@ -736,7 +740,8 @@ class AdditiveCSSM:
                 return {k: fill(v, k) for k, v in shape_tree.items()}
             if name == "bias":
                 return (bias_scale * rng.standard_normal(shape_tree)).astype(np.float32)
-            fan_in = shape_tree[0] if len(shape_tree) == 2 else 2 * self.kernel_size * self.channels / 2
+            fan_in = (shape_tree[0] if len(shape_tree) == 2 else
+                      shape_tree[2] if len(shape_tree) == 4 else 2 * self.kernel_size * self.channels / 2)
             return (rng.standard_normal(shape_tree) / np.sqrt(fan_in)).astype(np.float32)
         return {"params": fill(self.param_shapes(H, W))}
 
@@ -795,13 +800,13 @@ class BoundAdditive:
             raise ValueError(f"x has {Cc} channels, module has {m.channels}")
         Wf = W // 2 + 1
         gshape = tuple(self.t["gk0"].shape)
-        want = (Cc, H) if m.gate_type == "factored" else (Cc, H * Wf)
+        want = {"factored": (Cc, H), "channel": (Cc, Cc)}.get(m.gate_type, (Cc, H * Wf))
         if gshape != want:
             raise ValueError(f"AdditiveCSSM: gate weights {gshape} were made for another plane size "
                              f"(this input needs {want})")
         return _lib.AdditiveDesc(B, T, H, W, Cc, m.kernel_size, ROPE_MODES[m.rope_mode],
-                                 float(m.rope_base), float(m.spectral_rho), GATE_TYPES[m.gate_type],
-                                 1, m._floor())
+                                 float(m.rope_base), float(m.spectral_rho),
+                                 _lib.DELTANET_GATE_TYPES[m.gate_type], 1, m._floor())
 
     def plan(self, d) -> torch.Tensor:
         """The weight-only plan (kernel spectrum, RoPE tables, temporal code) for descriptor d."""

@@ -419,7 +419,7 @@ class BoundShvit:
         ws = self.buf.get("ws_pipe", n)
         if self._pipe is None:
             h = C.c_void_p()
-            check(self.L.cssm_shvit_host_pipe_create(C.byref(h)), "cssm_shvit_host_pipe_create")
+            check(self.L.cssm_host_pipe_create(C.byref(h)), "cssm_host_pipe_create")
             self._pipe = h
         check(self.L.cssm_shvit_forward_host_pipelined(
             C.byref(d), C.byref(self.w), pl.data_ptr(), self._pipe, x_host.data_ptr(),
@@ -430,7 +430,7 @@ class BoundShvit:
     def close(self):
         """Waits for a prefetch still in flight and frees the pipe of forward_host_pipelined."""
         if self._pipe is not None:
-            self.L.cssm_shvit_host_pipe_destroy(self._pipe)
+            self.L.cssm_host_pipe_destroy(self._pipe)
             self._pipe = None
 
     def __del__(self):

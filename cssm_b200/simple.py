@@ -310,3 +310,44 @@ class BoundSimple:
                                               SIMPLE_LAST_FRAME_ONLY if last_frame_only else 0,
                                               _stream_ptr(self.device)), "cssm_simple_forward_host")
         return logits_host
+
+    def forward_host_pipelined(self, x_host: torch.Tensor, x_next_host: Optional[torch.Tensor],
+                               logits_host: torch.Tensor, last_frame_only: bool = False) -> torch.Tensor:
+        """Streaming form of forward_host for a loop over batches: computes the logits of x_host and,
+        meanwhile, copies x_next_host (the batch the next call will be given; may be None) to the
+        device.  x_next_host must stay unchanged until that next call.  Returns after the logits of
+        x_host have arrived."""
+        for t in (x_host, x_next_host):
+            if t is not None and (t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous()):
+                raise TypeError("host batches must be contiguous float32 host tensors")
+        if x_next_host is not None and tuple(x_next_host.shape) != tuple(x_host.shape):
+            raise ValueError("x_next_host must have the shape of x_host")
+        d = self.desc(tuple(x_host.shape))
+        bd = self.block_desc(d)
+        pl = self.block.plan(bd)
+        n = self.L.cssm_simple_host_pipe_workspace_bytes(C.byref(d), C.byref(bd))
+        if n == 0:
+            raise NotImplementedError("SimpleCSSM: unsupported shape / field combination")
+        ws = self.buf.get("pws", n)
+        if getattr(self, "_pipe", None) is None:
+            h = C.c_void_p()
+            check(self.L.cssm_host_pipe_create(C.byref(h)), "cssm_host_pipe_create")
+            self._pipe = h
+        check(self.L.cssm_simple_forward_host_pipelined(
+            C.byref(d), C.byref(self.w), C.byref(bd), C.byref(self.block.w), pl.data_ptr(), self._pipe,
+            x_host.data_ptr(), x_next_host.data_ptr() if x_next_host is not None else None,
+            logits_host.data_ptr(), ws.data_ptr(), n, SIMPLE_LAST_FRAME_ONLY if last_frame_only else 0,
+            _stream_ptr(self.device)), "cssm_simple_forward_host_pipelined")
+        return logits_host
+
+    def close(self):
+        """Waits for a prefetch still in flight and frees the pipe of forward_host_pipelined."""
+        if getattr(self, "_pipe", None) is not None:
+            self.L.cssm_host_pipe_destroy(self._pipe)
+            self._pipe = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -296,7 +296,7 @@ int cssm_nogate_forward(const cssm_nogate_desc* d, const cssm_nogate_weights* w,
  * scan_mode of that path (associative / ssd / quadratic / pallas, cssm.py:3294-3359): they
  * evaluate the same recurrence.  goom_floor = 1 keeps the 1e-7 magnitude floors of the
  * log-space scan (to_goom, src/models/goom.py:161-173) on K_hat and on B_X * X_hat; 0 is the
- * plain complex recurrence of the other scan modes.  Gates of type conv / channel /
+ * plain complex recurrence of the other scan modes.  Gates of type conv /
  * dense_decay / dense_io / spectral_conv / low_rank / scalar, learned_init,
  * position_independent_gates and the 2- and 3-state paths are rejected. */
 typedef struct cssm_additive_desc {
@@ -305,7 +305,7 @@ typedef struct cssm_additive_desc {
   int32_t rope_mode;        /* CSSM_ROPE_* */
   float   rope_base;        /* 10000 */
   float   spectral_rho;     /* 0.999 */
-  int32_t gate_type;        /* CSSM_GATE_DENSE or CSSM_GATE_FACTORED */
+  int32_t gate_type;        /* CSSM_GATE_DENSE, CSSM_GATE_FACTORED or CSSM_GATE_CHANNEL */
   int32_t single_state;     /* must be 1 */
   int32_t goom_floor;       /* 1: scan_mode 'associative' with use_goom; 0: linear scan modes */
 } cssm_additive_desc;
@@ -315,7 +315,10 @@ typedef struct cssm_additive_weights {
   const float* x_proj_kernel;       /* (C, C)                                                 */
   const float* x_proj_bias;         /* (C)                                                    */
   /* dense: [0..2] = d_X, B_X, C_gate, kernels (C, H*Wf), biases (H*Wf).
-     factored: [0..5] = d_X_h, d_X_w, B_X_h, B_X_w, C_gate_h, C_gate_w, kernels (C,H) / (C,Wf) */
+     factored: [0..5] = d_X_h, d_X_w, B_X_h, B_X_w, C_gate_h, C_gate_w, kernels (C,H) / (C,Wf).
+     channel (cssm.py:3168-3178): [0] = d_X Dense kernel (C,C); [1], [2] = the 1x1 conv kernels
+     (1,1,C,C) of the per-pixel maps B_X (times x_proj before the transform) and C_gate (times the
+     output after the inverse transform); biases (C) */
   const float* gate_kernel[6];
   const float* gate_bias[6];
   const float* output_proj_kernel;  /* (C, C)                                                 */
@@ -569,7 +572,7 @@ int cssm_shvit_forward_host(const cssm_shvit_desc* d, const cssm_shvit_weights* 
 /* Streaming form of the host entry point, for a loop that feeds batch after batch (the reference's
  * evaluation loop, main.py:522-561, prefetches its next batch the same way): while batch i computes,
  * the images of batch i+1 are copied to the device on the pipe's own stream.
- *   cssm_shvit_host_pipe_create / _destroy: a caller-owned handle holding one copy stream, two
+ *   cssm_host_pipe_create / _destroy: a caller-owned handle holding one copy stream, two
  *     events and the address of the prefetched batch; it owns no device memory.
  *   cssm_shvit_forward_host_pipelined(..., x_bf16_host, x_next_bf16_host, ...): computes the logits of
  *     x_bf16_host for the whole batch at once and returns after they have arrived on the host.  If the
@@ -579,14 +582,23 @@ int cssm_shvit_forward_host(const cssm_shvit_desc* d, const cssm_shvit_weights* 
  *     the call computes; the caller must leave that host buffer unchanged until the next call on this
  *     pipe or its destruction.  Workspace: cssm_shvit_host_pipe_workspace_bytes (the model workspace,
  *     two whole-batch input buffers, the logits). */
-typedef struct cssm_shvit_host_pipe cssm_shvit_host_pipe;
-int cssm_shvit_host_pipe_create(cssm_shvit_host_pipe** pipe);
-int cssm_shvit_host_pipe_destroy(cssm_shvit_host_pipe* pipe);
+typedef struct cssm_host_pipe cssm_host_pipe;
+int cssm_host_pipe_create(cssm_host_pipe** pipe);
+int cssm_host_pipe_destroy(cssm_host_pipe* pipe);
 size_t cssm_shvit_host_pipe_workspace_bytes(const cssm_shvit_desc* d);
 int cssm_shvit_forward_host_pipelined(const cssm_shvit_desc* d, const cssm_shvit_weights* w, const void* plan,
-                                      cssm_shvit_host_pipe* pipe, const void* x_bf16_host,
+                                      cssm_host_pipe* pipe, const void* x_bf16_host,
                                       const void* x_next_bf16_host, float* logits_host, void* workspace,
                                       size_t workspace_bytes, void* stream);
+
+/* The streaming form for the SimpleCSSM models (float32 images or clips): same pipe handle, same
+ * contract as cssm_shvit_forward_host_pipelined, arguments of cssm_simple_forward_host. */
+size_t cssm_simple_host_pipe_workspace_bytes(const cssm_simple_desc* d, const void* block_desc);
+int cssm_simple_forward_host_pipelined(const cssm_simple_desc* d, const cssm_simple_weights* w,
+                                       const void* block_desc, const void* block_weights,
+                                       const void* block_plan, cssm_host_pipe* pipe, const float* x_host,
+                                       const float* x_next_host, float* logits_host, void* workspace,
+                                       size_t workspace_bytes, int32_t flags, void* stream);
 
 /* The bf16 tensor-core GEMM of the model's Dense layers on its own (nn.Dense with dtype bfloat16:
  * shvit.py:165-180; cssm.py:481, 584 inside a bf16 model):

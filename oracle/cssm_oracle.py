@@ -408,7 +408,10 @@ def additive1_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=
                       spectral_rho=0.999, gate_type="dense", scan_mode="associative",
                       dtype=np.float64, scan="direct"):
     """AdditiveCSSM.__call__ with single_state=True (cssm.py:3061-3359, 3580-3626), gate_type
-    'dense' or 'factored', position_independent_gates=False, learned_init=False, use_goom=True.
+    'dense', 'factored' or 'channel', position_independent_gates=False, learned_init=False,
+    use_goom=True.  With 'channel' (cssm.py:3168-3178, 3241-3244, 3615-3618) d_X is a per-channel
+    scalar Dense(C)(ctx), B_X and C_gate are per-pixel maps sigmoid(Conv1x1(C)(rotated x)) applied
+    in the spatial domain: x_proj * B_X before the transform, C_gate after the inverse transform.
 
     x_proj = Dense(C)(rope(x)); ctx = mean_{H,W}(rope(x)) + temporal code (cssm.py:3127-3131);
     d_X = 0.1 + 0.89 sigmoid(.) (bounded), B_X = C_gate = sigmoid(.), each (B,T,1,H,Wf)
@@ -426,7 +429,15 @@ def additive1_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=
     x_proj = dense(x, params["x_proj"])
     ctx = x.mean(axis=(2, 3)) + temporal_ctx_code(T, C, rope_base)[None]
 
-    def gate(name, bounded=False):
+    chan = gate_type == "channel"
+
+    def gate(name, bounded=False, spatial=False):
+        if chan:
+            if spatial:
+                kern = np.asarray(params[name]["kernel"], dtype).reshape(C, C)
+                return sigmoid(x @ kern + np.asarray(params[name]["bias"], dtype))     # (B,T,H,W,C)
+            raw = sigmoid(dense(ctx, params[name])).reshape(B, T, C, 1, 1)
+            return 0.1 + 0.89 * raw if bounded else raw
         if gate_type == "factored":
             row = dense(ctx, params[f"{name}_h"])
             col = dense(ctx, params[f"{name}_w"])
@@ -436,10 +447,14 @@ def additive1_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=
         raw = raw.reshape(B, T, 1, H, Wf)
         return 0.1 + 0.89 * raw if bounded else raw
 
-    d_X, B_X, C_gate = gate("d_X", True), gate("B_X"), gate("C_gate")
+    d_X, B_X, C_gate = gate("d_X", True), gate("B_X", spatial=True), gate("C_gate", spatial=True)
     K_hat = spectral_kernel(params["kernel"], H, W, spectral_rho).astype(cdt)
     A = d_X.astype(cdt) * K_hat[None, None]
-    U = np.fft.rfft2(x_proj.transpose(0, 1, 4, 2, 3), axes=(3, 4)).astype(cdt) * B_X
+    if chan:
+        U = np.fft.rfft2((x_proj * B_X).transpose(0, 1, 4, 2, 3), axes=(3, 4)).astype(cdt)
+        A = np.broadcast_to(A, U.shape)
+    else:
+        U = np.fft.rfft2(x_proj.transpose(0, 1, 4, 2, 3), axes=(3, 4)).astype(cdt) * B_X
     if scan == "goom":
         assert scan_mode == "associative"
         V = goom_scalar_scan(A, U).astype(cdt)
@@ -452,7 +467,10 @@ def additive1_forward(params, x, *, kernel_size=11, rope_mode="none", rope_base=
             h = A[:, t] * h + U[:, t]
             hs.append(h)
         V = np.stack(hs, axis=1)
-    out = np.fft.irfft2(V * C_gate, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2).astype(dtype)
+    if chan:
+        out = np.fft.irfft2(V, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2).astype(dtype) * C_gate
+    else:
+        out = np.fft.irfft2(V * C_gate, s=(H, W), axes=(3, 4)).transpose(0, 1, 3, 4, 2).astype(dtype)
     return dense(out, params["output_proj"])
 
 
@@ -470,6 +488,9 @@ def init_additive1_params(seed, C, H, W, *, kernel_size=11, gate_type="dense", b
         if gate_type == "factored":
             p[f"{n}_h"] = _dense_p(rng, C, H, bias_scale)
             p[f"{n}_w"] = _dense_p(rng, C, Wf, bias_scale)
+        elif gate_type == "channel":
+            d = _dense_p(rng, C, C, bias_scale)
+            p[n] = d if n == "d_X" else {"kernel": d["kernel"].reshape(1, 1, C, C), "bias": d["bias"]}
         else:
             p[n] = _dense_p(rng, C, H * Wf, bias_scale)
     return p

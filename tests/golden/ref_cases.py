@@ -248,6 +248,11 @@ CASES = [
               scan_mode="ssd"),
     _additive("additive1_quadratic", (1, 8, 8, 8, 8), 314, kernel_size=5, gate_type="dense",
               scan_mode="quadratic"),
+    _additive("additive1_channel", (2, 4, 8, 10, 8), 315, kernel_size=5, gate_type="channel",
+              rope_mode="mrope"),
+    _additive("additive1_channel_32", (1, 3, 32, 32, 8), 316, kernel_size=11, gate_type="channel"),
+    _additive("additive1_channel_64", (1, 2, 64, 64, 4), 317, kernel_size=11, gate_type="channel",
+              rope_mode="spatiotemporal"),
     _deltanet("deltanet_channel", (2, 4, 8, 8, 8), 321, kernel_size=5, gate_type="channel",
               rope_mode="mrope"),
     _deltanet("deltanet_dense", (2, 4, 8, 8, 8), 322, kernel_size=5, gate_type="dense"),

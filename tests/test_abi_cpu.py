@@ -144,7 +144,8 @@ def test_additive_descriptor_validation_without_gpu():
     d = desc()
     assert L.cssm_additive_plan_bytes(C.byref(d)) >= 8 * 8 * 5 * 8
     assert L.cssm_additive_workspace_bytes(C.byref(d)) >= 2 * 3 * 2 * 8 * 8 * 8 * 4
-    for bad in (desc(single_state=0), desc(gate_type=2), desc(C=6), desc(B=0), desc(goom_floor=2),
+    assert L.cssm_additive_plan_bytes(C.byref(desc(gate_type=2))) > L.cssm_additive_plan_bytes(C.byref(d))
+    for bad in (desc(single_state=0), desc(gate_type=3), desc(C=6), desc(B=0), desc(goom_floor=2),
                 desc(rope_mode=9)):
         assert L.cssm_additive_plan_bytes(C.byref(bad)) == 0
         assert L.cssm_additive_workspace_bytes(C.byref(bad)) == 0
@@ -159,7 +160,9 @@ def test_additive_module_rejects_unbuilt_variants():
     with pytest.raises(NotImplementedError):
         AdditiveCSSM(channels=8).init(0, (1, 2, 8, 8, 8))                      # 3-state default
     with pytest.raises(NotImplementedError):
-        AdditiveCSSM(channels=8, single_state=True, gate_type="channel").init(0, (1, 2, 8, 8, 8))
+        AdditiveCSSM(channels=8, single_state=True, gate_type="low_rank").init(0, (1, 2, 8, 8, 8))
+    pc = AdditiveCSSM(channels=8, single_state=True, gate_type="channel").init(0, (1, 2, 8, 8, 8))["params"]
+    assert pc["d_X"]["kernel"].shape == (8, 8) and pc["B_X"]["kernel"].shape == (1, 1, 8, 8)
     with pytest.raises(NotImplementedError):
         AdditiveCSSM(channels=8, single_state=True, learned_init=True).init(0, (1, 2, 8, 8, 8))
     m = AdditiveCSSM(channels=8, single_state=True, gate_type="factored", kernel_size=5)

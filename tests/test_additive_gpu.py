@@ -36,6 +36,12 @@ def _run(case, gate_type, rope, scan_mode="associative", seed=0):
     ((2, 3, 14, 10, 12, 3), "factored", "spatial_only"),      # small-plane kernel, ragged plane
     ((2, 3, 20, 18, 8, 7), "dense", "temporal"),              # generic kernel
     ((1, 1, 7, 7, 4, 11), "dense", "none"),                   # T = 1, kernel larger than the plane
+    # per-channel decay, per-pixel 1x1-conv input / output gates ('channel') on all four kernels
+    ((2, 4, 64, 64, 64, 11), "channel", "spatiotemporal"),
+    ((1, 3, 64, 64, 8, 5), "channel", "none"),
+    ((2, 5, 32, 32, 8, 11), "channel", "mrope"),
+    ((2, 3, 14, 10, 12, 3), "channel", "temporal"),
+    ((2, 3, 20, 18, 8, 7), "channel", "none"),
 ], ids=lambda c: "x".join(map(str, c)) if isinstance(c, tuple) else str(c))
 def test_block_parity(case, gate_type, rope):
     assert _run(case, gate_type, rope) <= TOL

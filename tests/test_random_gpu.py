@@ -120,7 +120,7 @@ def _scalar_case(seed):
     rope = pick("none", "spatiotemporal", "mrope", "temporal", "spatial_only")
     gate = pick("factored", "dense")
     mode = pick("associative", "associative", "ssd", "quadratic", "pallas")
-    if kind == "deltanet" and pick(0, 1):
+    if pick(0, 1):
         gate = "channel"
     x = rng.standard_normal((B, T, H, W, C)).astype(np.float32)
     kw = dict(kernel_size=ks, gate_type=gate, rope_mode=rope, scan_mode=mode)

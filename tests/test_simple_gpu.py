@@ -146,3 +146,25 @@ def test_golden_fixture_on_gpu():
                    gate_type="factored", seq_len=3, stem_layers=1, pool_type="max")
     logits = m.apply({"params": p}, torch.from_numpy(g["x"]).cuda()).cpu().numpy()
     assert orc.rel_l2(logits, g["y"]) <= TOL
+
+
+def test_streaming_host_entry_prefetches_the_next_batch():
+    """forward_host_pipelined: prefetched, cold and dropped-prefetch batches all give the device
+    entry point's logits, for image and clip inputs."""
+    for shape, extra in (((4, 32, 32, 1), dict(seq_len=3)), ((2, 4, 16, 16, 3), dict(stem_mode="pathtracker"))):
+        m = _model("gated", 8, 5, "spatiotemporal", extra.pop("stem_mode", "default"), 1, "max", "pre", **extra)
+        rng = np.random.default_rng(3)
+        xs = [torch.from_numpy(rng.random(shape).astype(np.float32)).pin_memory() for _ in range(3)]
+        v = m.init(0, shape)
+        bound = m.bind(v)
+        want = [bound(x.cuda()).cpu() for x in xs]
+        lh = torch.empty_like(want[0]).pin_memory()
+        bound.forward_host_pipelined(xs[0], xs[1], lh)      # cold, prefetches xs[1]
+        assert torch.equal(lh, want[0])
+        bound.forward_host_pipelined(xs[1], xs[2], lh)      # prefetched
+        assert torch.equal(lh, want[1])
+        bound.forward_host_pipelined(xs[0], None, lh)       # the prefetch of xs[2] is dropped
+        assert torch.equal(lh, want[0])
+        bound.forward_host_pipelined(xs[2], xs[2], lh, last_frame_only=True)
+        assert orc.rel_l2(lh.numpy(), want[2].numpy()) <= 1e-5
+        bound.close()
