@@ -289,6 +289,23 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def device_error(clear: bool = True) -> int:
+    """The device error word: non-zero when a bounded wait inside a kernel expired since the last
+    clearing read (bits 0-7 fp32 GEMM, 8-15 fused spectral kernel, 16-23 bf16 GEMM).  Reading it
+    waits for the device, so the mirrors call it only where they wait anyway (host entry points)."""
+    L = lib()
+    word = C.c_int(0)
+    check(L.cssm_device_error(C.byref(word), 1 if clear else 0), "cssm_device_error")
+    return int(word.value)
+
+
+def raise_on_device_error(what: str) -> None:
+    word = device_error(clear=True)
+    if word:
+        raise CssmError(f"{what}: a bounded device-side wait expired (error word 0x{word:x}); "
+                        "the results of the call are not valid")
+
+
 def check(status: int, what: str) -> None:
     if status != 0:
         L = lib()

@@ -403,6 +403,7 @@ class BoundShvit:
         check(self.L.cssm_shvit_forward_host(C.byref(d), C.byref(self.w), pl.data_ptr(), x_host.data_ptr(),
                                              logits_host.data_ptr(), ws.data_ptr(), n,
                                              _stream_ptr(self.device)), "cssm_shvit_forward_host")
+        _lib.raise_on_device_error("cssm_shvit_forward_host")
         return logits_host
 
     def forward_host_pipelined(self, x_host: torch.Tensor, x_next_host: Optional[torch.Tensor],
@@ -425,6 +426,7 @@ class BoundShvit:
             C.byref(d), C.byref(self.w), pl.data_ptr(), self._pipe, x_host.data_ptr(),
             x_next_host.data_ptr() if x_next_host is not None else None, logits_host.data_ptr(),
             ws.data_ptr(), n, _stream_ptr(self.device)), "cssm_shvit_forward_host_pipelined")
+        _lib.raise_on_device_error("cssm_shvit_forward_host_pipelined")
         return logits_host
 
     def close(self):

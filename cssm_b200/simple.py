@@ -309,6 +309,7 @@ class BoundSimple:
                                               ws.data_ptr(), n,
                                               SIMPLE_LAST_FRAME_ONLY if last_frame_only else 0,
                                               _stream_ptr(self.device)), "cssm_simple_forward_host")
+        _lib.raise_on_device_error("cssm_simple_forward_host")
         return logits_host
 
     def forward_host_pipelined(self, x_host: torch.Tensor, x_next_host: Optional[torch.Tensor],
@@ -338,6 +339,7 @@ class BoundSimple:
             x_host.data_ptr(), x_next_host.data_ptr() if x_next_host is not None else None,
             logits_host.data_ptr(), ws.data_ptr(), n, SIMPLE_LAST_FRAME_ONLY if last_frame_only else 0,
             _stream_ptr(self.device)), "cssm_simple_forward_host_pipelined")
+        _lib.raise_on_device_error("cssm_simple_forward_host_pipelined")
         return logits_host
 
     def close(self):
