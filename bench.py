@@ -430,7 +430,7 @@ def run_shvit(args, name, ctx):
     kname = {"gemm": "gemm_bf16_kernel<false>", "conv_gemm": "gemm_bf16_kernel<true>",
              "dwconv7": "dwconv_tiled_kernel<7>", "dwconv3": "dwconv_tiled_kernel<3>",
              "layernorm": "layernorm_cl_kernel", "stem_conv": "stem_conv1_kernel",
-             "spectral": "gated_spectral_cl_kernel"}.get(top, top)
+             "spectral": "gated_spectral_cl_kernel", "mlp": "mlp_fused_kernel"}.get(top, top)
     roofline = {"bound": "hbm", "kernel": kname, "achieved": tk["achieved_GBps"], "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": tk["achieved_GBps"] / peak,
                 "frac_of_nominal_8TBps": tk["achieved_GBps"] / 8000.0, "traffic": None,

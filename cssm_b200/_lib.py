@@ -88,7 +88,7 @@ class ShvitTrace(C.Structure):
 
 
 SHVIT_KINDS = ["stem_conv", "conv_gemm", "gemm", "layernorm", "dwconv7", "dwconv3", "sample_norm",
-               "plane_sum", "gates", "spectral", "pool", "head", "mixer_f32", "add_res", "end"]
+               "plane_sum", "gates", "spectral", "pool", "head", "mixer_f32", "add_res", "mlp", "end"]
 
 
 class GatedWsLayout(C.Structure):
@@ -260,6 +260,7 @@ SIGNATURES = {
     "cssm_bf16_packed_ld": (C.c_int32, [C.c_int32]),
     "cssm_bf16_pack_weight": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P]),
     "cssm_bf16_gemm": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _P, C.c_int32, _P, _P, _P]),
+    "cssm_bf16_mlp": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P]),
     "cssm_bf16_conv3x3s2_packed_ld": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32]),
     "cssm_bf16_pack_conv3x3s2_weight": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),
     "cssm_bf16_conv3x3s2": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, _P,
@@ -291,7 +292,7 @@ def lib() -> C.CDLL:
 
 def device_error(clear: bool = True) -> int:
     """The device error word: non-zero when a bounded wait inside a kernel expired since the last
-    clearing read (bits 0-7 fp32 GEMM, 8-15 fused spectral kernel, 16-23 bf16 GEMM).  Reading it
+    clearing read (bits 0-7 fp32 GEMM, 8-15 fused spectral kernel, 16-23 bf16 GEMM, 24-31 fused MLP).  Reading it
     waits for the device, so the mirrors call it only where they wait anyway (host entry points)."""
     L = lib()
     word = C.c_int(0)

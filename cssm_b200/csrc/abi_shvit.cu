@@ -244,6 +244,11 @@ static int block_forward(const cssm_shvit_block_desc& d, const cssm_shvit_block_
   // LN -> fc1 -> gelu -> [h + dw3x3(h)] -> fc2 + residual
   trace(CSSM_SHVIT_K_LAYERNORM, 4.0 * M * C, st);
   CSSM_RUN(launch_layernorm_cl(X1, w.norm2_scale, w.norm2_bias, T, M, C, st));
+  if (!(d.is_cssm && d.use_dwconv) && mlp_fused_supported(C, Hd)) {
+    // fc1 + GELU + fc2 + residual in one kernel: the hidden tensor stays on chip
+    trace(CSSM_SHVIT_K_MLP, 2.0 * (3.0 * M * C + 2.0 * C * Hd), st);
+    return launch_mlp_fused(T, M, fc1, packed_ld(C), w.fc1_bias, fc2, packed_ld(Hd), w.fc2_bias, X1, y, st);
+  }
   CSSM_RUN(gemm_plain(T, M, C, fc1, Hd, w.fc1_bias, 1, nullptr, HB, st));
   const __nv_bfloat16* h = HB;
   if (d.is_cssm && d.use_dwconv) {
@@ -674,6 +679,14 @@ int cssm_bf16_gemm(const void* A, int32_t M, int32_t K, const void* wt, int32_t 
   if (!A || !wt || !out) return CSSM_ERR_NULL;
   return gemm_plain((const __nv_bfloat16*)A, M, K, (const __nv_bfloat16*)wt, N, bias, act,
                     (const __nv_bfloat16*)res, (__nv_bfloat16*)out, (cudaStream_t)stream);
+}
+int cssm_bf16_mlp(const void* a, int32_t M, int32_t C, int32_t Hd, const void* w1t, const float* b1,
+                  const void* w2t, const float* b2, const void* res, void* out, void* stream) {
+  if (M <= 0 || C <= 0 || Hd <= 0) return CSSM_ERR_DIMS;
+  if (!mlp_fused_supported(C, Hd)) return CSSM_ERR_UNSUPPORTED;
+  return launch_mlp_fused((const __nv_bfloat16*)a, M, (const __nv_bfloat16*)w1t, packed_ld(C), b1,
+                          (const __nv_bfloat16*)w2t, packed_ld(Hd), b2, (const __nv_bfloat16*)res,
+                          (__nv_bfloat16*)out, (cudaStream_t)stream);
 }
 int32_t cssm_bf16_conv3x3s2_packed_ld(int32_t Cin, int32_t Wi, int32_t Cout) { return packed_ld(conv3x3s2_packed_k(Cin, Wi, Cout)); }
 int cssm_bf16_pack_conv3x3s2_weight(const float* kernel, int32_t Cin, int32_t Cout, int32_t Wi,

@@ -531,10 +531,12 @@ int cssm_device_error(int* out, int clear) {
   if (rc != CSSM_OK) return rc;
   rc = cssm::read_spec_error(&b, clear);
   if (rc != CSSM_OK) return rc;
-  int c = 0;
+  int c = 0, m = 0;
   rc = cssm::read_bf16_error(&c, clear);
-  // low byte: fp32 tensor-core GEMMs, next byte: fused spectral kernels, third: bf16 GEMM
-  *out = a | (b << 8) | (c << 16);
+  if (rc != CSSM_OK) return rc;
+  rc = cssm::read_mlp_error(&m, clear);
+  // low byte: fp32 tensor-core GEMMs, next byte: fused spectral kernels, third: bf16 GEMM, fourth: fused MLP
+  *out = a | (b << 8) | (c << 16) | (m << 24);
   return rc;
 }
 }

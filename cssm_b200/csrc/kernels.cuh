@@ -142,6 +142,13 @@ int conv3x3s2_packed_k(int Cin, int Wi, int Cout);
 int gemm_bf16_pick_bn(int N);
 int read_bf16_error(int* out, int clear);
 
+// fused fc1 + GELU + fc2 + residual of the 64-channel ConvBlock (csrc/mlp_fused.cu)
+bool mlp_fused_supported(int C, int Hd);
+int launch_mlp_fused(const __nv_bfloat16* a, int M, const __nv_bfloat16* w1t, int ld1, const float* b1,
+                     const __nv_bfloat16* w2t, int ld2, const float* b2, const __nv_bfloat16* res,
+                     __nv_bfloat16* out, cudaStream_t st);
+int read_mlp_error(int* out, int clear);
+
 // ---- bf16 model kernels (csrc/shvit_kernels.cu, csrc/spectral_cl.cu) ----
 int launch_pack_wt(const float* src, int K, int N, const float* colscale, __nv_bfloat16* dst, int ldw,
                    cudaStream_t st);

@@ -35,6 +35,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   }
   return false;
 }
+// The same bounded wait without the sleep, for hand-offs on a kernel's critical chain (the sleep's
+// wake-up granularity is far coarser than the few hundred cycles such a hand-off takes).
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 24) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
 // TMA bulk copy (untiled): `bytes` (multiple of 16, both addresses 16-byte aligned) from global
 // to this CTA's shared memory; completion is counted in bytes on the mbarrier.
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {

@@ -549,7 +549,7 @@ enum {
   CSSM_SHVIT_K_LAYERNORM = 3, CSSM_SHVIT_K_DWCONV7 = 4, CSSM_SHVIT_K_DWCONV3 = 5,
   CSSM_SHVIT_K_SAMPLE_NORM = 6, CSSM_SHVIT_K_PLANE_SUM = 7, CSSM_SHVIT_K_GATES = 8,
   CSSM_SHVIT_K_SPECTRAL = 9, CSSM_SHVIT_K_POOL = 10, CSSM_SHVIT_K_HEAD = 11,
-  CSSM_SHVIT_K_MIXER_F32 = 12, CSSM_SHVIT_K_ADD_RES = 13, CSSM_SHVIT_K_END = 14
+  CSSM_SHVIT_K_MIXER_F32 = 12, CSSM_SHVIT_K_ADD_RES = 13, CSSM_SHVIT_K_MLP = 14, CSSM_SHVIT_K_END = 15
 };
 typedef struct cssm_shvit_trace {
   void** events; int32_t* kinds; double* bytes;
@@ -610,6 +610,14 @@ int cssm_bf16_pack_weight(const float* kernel, int32_t K, int32_t N, const float
                           void* wt, void* stream);
 int cssm_bf16_gemm(const void* A, int32_t M, int32_t K, const void* wt, int32_t N, const float* bias,
                    int32_t act, const void* res, void* out, void* stream);
+/* The whole Mlp of a block (shvit.py:165-180: fc1 C -> Hd, gelu, fc2 Hd -> C) plus the block's residual
+ * in one kernel, the hidden tensor staying on the SM:
+ *   out (M,C) bf16 = res (M,C) bf16 + gelu(a (M,C) bf16 @ W1 + b1) @ W2 + b2
+ * w1t / w2t are W1 (C,Hd) / W2 (Hd,C) packed by cssm_bf16_pack_weight.  Built for C = 64, Hd = 256 (the
+ * stage-0 ConvBlock of CSSM-SHViT s1); other sizes return CSSM_ERR_UNSUPPORTED and the caller runs two
+ * cssm_bf16_gemm calls instead, as the model's forward pass does. */
+int cssm_bf16_mlp(const void* a, int32_t M, int32_t C, int32_t Hd, const void* w1t, const float* b1,
+                  const void* w2t, const float* b2, const void* res, void* out, void* stream);
 /* 3x3 stride-2 'SAME' convolution (nn.Conv inside ConvBN, shvit.py:45-54) as an implicit GEMM:
  * x (B,Hi,Wi,Cin) bf16 -> out (B,ceil(Hi/2),ceil(Wi/2),Cout) bf16; `wt` = the HWIO kernel (3,3,Cin,Cout)
  * packed by cssm_bf16_pack_conv3x3s2_weight into (Cout, cssm_bf16_conv3x3s2_packed_ld(Cin, Wi, Cout)) bf16

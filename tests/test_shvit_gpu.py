@@ -9,7 +9,7 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from cssm_b200 import CSSMSHViT, lib
+from cssm_b200 import CSSMSHViT, device_error, lib
 from cssm_b200._lib import check
 from oracle import cssm_oracle as orc
 from oracle import shvit_oracle as sv
@@ -83,6 +83,41 @@ def test_bf16_conv3x3s2(B, Hi, Wi, Cin, Cout):
     assert out.shape == ref.shape
     err = (out.float() - ref).norm() / ref.norm()
     assert err < 6e-3, float(err)
+
+
+@pytest.mark.parametrize("M", [1, 300, 128 * 148 + 64, 128 * 148 * 5 + 17])
+def test_bf16_fused_mlp(M):
+    """fc1 -> gelu -> fc2 -> + residual in one kernel (C = 64, Hd = 256) against float32 torch on the same
+    bf16 operands, with the hidden layer rounded to bf16 as the kernel and the two-GEMM path round it;
+    ragged last tiles, fewer tiles than CTAs, several tiles per CTA."""
+    L = lib()
+    Cd, Hd = 64, 256
+    g = torch.Generator(device="cuda").manual_seed(M)
+    A = torch.randn((M, Cd), device="cuda", generator=g).to(torch.bfloat16)
+    R = torch.randn((M, Cd), device="cuda", generator=g).to(torch.bfloat16)
+    W1 = torch.randn((Cd, Hd), device="cuda", generator=g) / Cd ** 0.5
+    W2 = torch.randn((Hd, Cd), device="cuda", generator=g) / Hd ** 0.5
+    b1 = torch.randn((Hd,), device="cuda", generator=g)
+    b2 = torch.randn((Cd,), device="cuda", generator=g)
+    w1t, w2t = _pack(L, W1, Cd, Hd), _pack(L, W2, Hd, Cd)
+    out = torch.full((M, Cd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    check(L.cssm_bf16_mlp(A.data_ptr(), M, Cd, Hd, w1t.data_ptr(), b1.data_ptr(), w2t.data_ptr(),
+                          b2.data_ptr(), R.data_ptr(), out.data_ptr(), _st()), "mlp")
+    hid = F.gelu(A.float() @ W1.to(torch.bfloat16).float() + b1, approximate="tanh").to(torch.bfloat16)
+    ref = hid.float() @ W2.to(torch.bfloat16).float() + b2 + R.float()
+    torch.cuda.synchronize()
+    assert device_error() == 0
+    err = (out.float() - ref).norm() / ref.norm()
+    assert err < 6e-3, float(err)
+    # the same through the two GEMM calls the model uses for every other size
+    h2 = torch.empty((M, Hd), dtype=torch.bfloat16, device="cuda")
+    o2 = torch.empty((M, Cd), dtype=torch.bfloat16, device="cuda")
+    check(L.cssm_bf16_gemm(A.data_ptr(), M, Cd, w1t.data_ptr(), Hd, b1.data_ptr(), 1, None, h2.data_ptr(), _st()), "fc1")
+    check(L.cssm_bf16_gemm(h2.data_ptr(), M, Hd, w2t.data_ptr(), Cd, b2.data_ptr(), 0, R.data_ptr(), o2.data_ptr(), _st()), "fc2")
+    torch.cuda.synchronize()
+    assert (out.float() - o2.float()).norm() / o2.float().norm() < 6e-3
+    assert L.cssm_bf16_mlp(A.data_ptr(), M, 128, 512, w1t.data_ptr(), b1.data_ptr(), w2t.data_ptr(),
+                           b2.data_ptr(), R.data_ptr(), out.data_ptr(), _st()) != 0
 
 
 _TINY = dict(embed_dims=(32, 64, 64, 128), depths=(1, 1, 2, 1), num_classes=10, num_timesteps=1,
