@@ -637,7 +637,7 @@ int cssm_bf16_conv3x3s2(const void* x, int32_t B, int32_t Hi, int32_t Wi, int32_
  * device since the last clear; low byte = fp32 tensor-core projection kernels (1 producer, 2 MMA
  * issuer, 3 drain, 4 epilogue), next byte = fused spectral kernels (1 input plane, 2 z plane),
  * third byte = bf16 tensor-core GEMM (5 TMA producer, 6 MMA issuer, 7 drain, 8 epilogue, 9 im2col
- * producer).
+ * producer), top byte = fused Mlp kernel (1 TMA producer, 2-6 MMA issuers, 8 drain, 9-13 epilogue).
  * A non-zero value means the outputs of the calls since the last clear are not to be trusted.
  * clear != 0 resets the word after reading it.  The call copies from the device on the legacy
  * default stream (it waits for work on blocking streams). */
