@@ -1,6 +1,7 @@
 // GDN block, kernels ahead of the spectral stage: RoPE + channels-last depthwise conv with
 // per-row context sums, and the gate maps (alpha, beta per frequency bin; B_k, B_v per pixel).
 #include "kernels.cuh"
+#include "bf16_ops.cuh"
 
 namespace cssm {
 
@@ -22,7 +23,7 @@ __device__ __forceinline__ int dw_pos(int col, int c) {
 }
 
 template <int K, int DW_CG>
-__global__ void __launch_bounds__(DW_THREADS, (K <= 5 ? 3 : 2)) rope_dwconv_cl_kernel(const GdnDwArgs a) {
+__global__ void __launch_bounds__(DW_THREADS, (K <= 5 ? 2 : 1)) rope_dwconv_cl_kernel(const GdnDwArgs a) {
   extern __shared__ __align__(16) float sm[];
   constexpr int LO = (K - 1) / 2, NR = DW_ROWS + K - 1;
   const int W = a.W, C = a.C, n2 = C / 2;
@@ -44,34 +45,56 @@ __global__ void __launch_bounds__(DW_THREADS, (K <= 5 ? 3 : 2)) rope_dwconv_cl_k
     sm[r * rpitch + dw_pos<DW_CG>(col, c)] = 0.f;
   }
   // ---- stage rows h0-LO .. h0+DW_ROWS-1+(K-1-LO), DW_CG channels, rotated ----
-  // DW_THREADS is a multiple of the pairs per pixel, so a thread keeps its channel pair: the
-  // t part of the angle is loaded once, the h part once per row, the w part per element.
+  // DW_THREADS is a multiple of the pairs per pixel, so a thread keeps its channel pair and walks
+  // columns wb, wb + WSTEP of every staged row: the t part of the angle is loaded once, the w part
+  // once per column, the h part once per row.  Four rows x two columns are fetched per trip, every
+  // load issued before the first is used.
   constexpr int PP = DW_CG / 2;                         // pairs per pixel in this channel group
+  constexpr int WSTEP = DW_THREADS / PP;
   const int pl = tid % PP, pi = c0 / 2 + pl;
   const bool rope = a.rope_t != nullptr;
   float2 ct = make_float2(1.f, 0.f);
   if (rope) ct = a.rope_t[t * n2 + pi];
-  for (int r = 0; r < NR; ++r) {
-    const int hh = h0 + r - LO;
-    const bool rin = hh >= 0 && hh < a.H;
-    float cth = 1.f, sth = 0.f;
-    if (rope && rin) {
-      const float2 ch = a.rope_h[hh * n2 + pi];
-      cth = ct.x * ch.x - ct.y * ch.y; sth = ct.x * ch.y + ct.y * ch.x;
+  const float* xf = a.x + (size_t)fsrc * a.H * W * C + c0 + 2 * pl;
+  for (int wb = tid / PP; wb < W; wb += 2 * WSTEP) {
+    float2 cw[2];
+    int spos[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int w = wb + k * WSTEP;
+      cw[k] = (rope && w < W) ? __ldg(&a.rope_w[w * n2 + pi]) : make_float2(1.f, 0.f);
+      spos[k] = dw_pos<DW_CG>(min(w, W - 1) + LO, 2 * pl);
     }
-    const float* xr = a.x + (((size_t)fsrc * a.H + (rin ? hh : 0)) * W) * C + c0 + 2 * pl;
-    float* srow = sm + r * rpitch;
-    for (int w = tid / PP; w < W; w += DW_THREADS / PP) {
-      float2 v = make_float2(0.f, 0.f);
-      if (rin) {
-        v = __ldg(reinterpret_cast<const float2*>(xr + (size_t)w * C));
-        if (rope) {
-          const float2 cw = __ldg(&a.rope_w[w * n2 + pi]);
-          const float c2 = cth * cw.x - sth * cw.y, s2 = cth * cw.y + sth * cw.x;
-          v = make_float2(v.x * c2 - v.y * s2, v.x * s2 + v.y * c2);
+#pragma unroll
+    for (int r0 = 0; r0 < NR; r0 += 4) {
+      float2 v[4][2];
+#pragma unroll
+      for (int r4 = 0; r4 < 4; ++r4) {
+        const int hh = h0 + r0 + r4 - LO;
+        const bool rin = r0 + r4 < NR && hh >= 0 && hh < a.H;
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+          v[r4][k] = (rin && wb + k * WSTEP < W)
+                         ? __ldg(reinterpret_cast<const float2*>(xf + ((size_t)hh * W + wb + k * WSTEP) * C))
+                         : make_float2(0.f, 0.f);
+      }
+#pragma unroll
+      for (int r4 = 0; r4 < 4; ++r4) {
+        if (r0 + r4 >= NR) continue;
+        const int hh = h0 + r0 + r4 - LO;
+        float cth = 1.f, sth = 0.f;
+        if (rope && hh >= 0 && hh < a.H) {
+          const float2 ch = __ldg(&a.rope_h[hh * n2 + pi]);
+          cth = ct.x * ch.x - ct.y * ch.y; sth = ct.x * ch.y + ct.y * ch.x;
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (wb + k * WSTEP >= W) continue;
+          const float c2 = cth * cw[k].x - sth * cw[k].y, s2 = cth * cw[k].y + sth * cw[k].x;
+          const float2 o = make_float2(v[r4][k].x * c2 - v[r4][k].y * s2, v[r4][k].x * s2 + v[r4][k].y * c2);
+          *reinterpret_cast<float2*>(sm + (r0 + r4) * rpitch + spos[k]) = o;
         }
       }
-      *reinterpret_cast<float2*>(srow + dw_pos<DW_CG>(w + LO, 2 * pl)) = v;
     }
   }
   __syncthreads();
@@ -86,29 +109,36 @@ __global__ void __launch_bounds__(DW_THREADS, (K <= 5 ? 3 : 2)) rope_dwconv_cl_k
     }
   }
   if (a.out == nullptr) return;
-  // ---- conv: thread = (channel c, group of 4 consecutive w), all DW_ROWS rows ----
-  const int c = tid % DW_CG;
-  float wk[K * K];
+  // ---- conv: thread = (channel pair, two consecutive w), all DW_ROWS rows; packed f32x2 FMAs ----
+  // The staged pairs are read with 8-byte loads as they lie.  With eight pairs per pixel a warp holds
+  // four column pairs; they are taken in the order 0, 2, 1, 3 so that the two of a half-warp are four
+  // columns apart and land in different halves of the swizzled 128-byte lines.
+  unsigned long long wk2[K * K];
 #pragma unroll
-  for (int i = 0; i < K * K; ++i) wk[i] = a.wk[(size_t)i * C + c0 + c];
-  const float bias = a.bias[c0 + c];
-  for (int wg = tid / DW_CG; wg * 4 < W; wg += DW_THREADS / DW_CG) {
-    const int w0 = wg * 4;
-    float acc[DW_ROWS][4];
+  for (int i = 0; i < K * K; ++i) {
+    const float2 w2 = *reinterpret_cast<const float2*>(a.wk + (size_t)i * C + c0 + 2 * pl);
+    wk2[i] = pk2(w2.x, w2.y);
+  }
+  const float2 b2 = *reinterpret_cast<const float2*>(a.bias + c0 + 2 * pl);
+  const unsigned long long bias2 = pk2(b2.x, b2.y);
+  const int q = tid / PP;
+  const int qs = PP == 8 ? ((q & ~3) | ((q & 1) << 1) | ((q >> 1) & 1)) : q;
+  for (int wg = qs; wg * 2 < W; wg += WSTEP) {
+    const int w0 = wg * 2;
+    unsigned long long acc[DW_ROWS][2];
 #pragma unroll
-    for (int r = 0; r < DW_ROWS; ++r)
+    for (int r = 0; r < DW_ROWS; ++r) { acc[r][0] = bias2; acc[r][1] = bias2; }
+    // offsets of the window's padded columns w0 .. w0+K inside a staged row (same for all rows)
+    int off[2 + K - 1];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[r][j] = bias;
-    // offsets of the window's padded columns w0 .. w0+K+2 inside a staged row (same for all rows)
-    int off[4 + K - 1];
-#pragma unroll
-    for (int j = 0; j < 4 + K - 1; ++j) off[j] = dw_pos<DW_CG>(min(w0 + j, WP - 1), c);
+    for (int j = 0; j < 2 + K - 1; ++j) off[j] = dw_pos<DW_CG>(min(w0 + j, WP - 1), 2 * pl);
 #pragma unroll
     for (int ir = 0; ir < NR; ++ir) {
       const float* srow = sm + ir * rpitch;
-      float win[4 + K - 1];
+      unsigned long long win[2 + K - 1];
 #pragma unroll
-      for (int j = 0; j < 4 + K - 1; ++j) win[j] = srow[off[j]];   // pad columns hold zeros
+      for (int j = 0; j < 2 + K - 1; ++j)
+        win[j] = *reinterpret_cast<const unsigned long long*>(srow + off[j]);   // pad columns hold zeros
       // input row ir feeds output row r = ir - di for tap row di
 #pragma unroll
       for (int di = 0; di < K; ++di) {
@@ -116,19 +146,22 @@ __global__ void __launch_bounds__(DW_THREADS, (K <= 5 ? 3 : 2)) rope_dwconv_cl_k
         if (r < 0 || r >= DW_ROWS) continue;
 #pragma unroll
         for (int dj = 0; dj < K; ++dj) {
-          const float wv = wk[di * K + dj];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc[r][j] = fmaf(wv, win[j + dj], acc[r][j]);
+          acc[r][0] = fma2(wk2[di * K + dj], win[dj], acc[r][0]);
+          acc[r][1] = fma2(wk2[di * K + dj], win[dj + 1], acc[r][1]);
         }
       }
     }
-    float* orow = a.out + (((size_t)fr * a.H + h0) * W + w0) * C + c0 + c;
+    float* orow = a.out + (((size_t)fr * a.H + h0) * W + w0) * C + c0 + 2 * pl;
 #pragma unroll
     for (int r = 0; r < DW_ROWS; ++r) {
       if (h0 + r >= a.H) continue;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (w0 + j < W) orow[((size_t)r * W + j) * C] = acc[r][j];
+      for (int j = 0; j < 2; ++j)
+        if (w0 + j < W) {
+          float ox, oy;
+          upk2(acc[r][j], ox, oy);
+          *reinterpret_cast<float2*>(orow + ((size_t)r * W + j) * C) = make_float2(ox, oy);
+        }
     }
   }
 }
