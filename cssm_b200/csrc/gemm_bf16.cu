@@ -65,9 +65,14 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
   unsigned char* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = tc::smem_u32(smem);
   const uint32_t BN = (uint32_t)g.BN;
-  const uint32_t stage_bytes = GB_A_BYTES + BN * 128u;
+  // wres: the whole weight matrix (one N tile, all K blocks) stays in shared memory for the life of
+  // the CTA and the ring carries only the A tiles
+  const bool wres = g.wres != 0;
+  const uint32_t wres_bytes = wres ? (uint32_t)(g.Kpad / GB_BK) * BN * 128u : 0u;
+  const uint32_t stage_bytes = GB_A_BYTES + (wres ? 0u : BN * 128u);
   const int NS = g.stages;                                  // ring depth (3 when BN = 256 and TMA_OUT)
-  unsigned char* out_s = smem + (uint32_t)NS * stage_bytes; // TMA_OUT: 2 x ostg staging boxes of 16 KB
+  unsigned char* ring = smem + wres_bytes;
+  unsigned char* out_s = ring + (uint32_t)NS * stage_bytes; // TMA_OUT: 2 x ostg staging boxes of 16 KB
   uint64_t* bars = reinterpret_cast<uint64_t*>(out_s + (TMA_OUT ? (uint32_t)(2 * g.ostg) * 16384u : 0u));
   uint64_t* full = bars;                        // [4] operands landed
   uint64_t* empty = bars + GB_MAX_STAGES;       // [4] stage consumed
@@ -75,7 +80,8 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
   uint64_t* accempty = accfull + 4;             // [4] accumulator drained
   uint64_t* resfull = accempty + 4;             // [2][4] residual box landed in its staging slot
   uint64_t* done = resfull + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+  uint64_t* wfull = done + 1;                   // resident weights landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wfull + 1);
   const int NACC = g.nacc;                                  // TMEM accumulators: 4 of BN <= 128 columns, else 2
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -98,6 +104,7 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
     }
     for (int a = 0; a < 8; ++a) tc::mbar_init(&resfull[a], 1);
     tc::mbar_init(done, 1);
+    tc::mbar_init(wfull, 1);
     tc::fence_mbar_init();
   }
   if (warp == 1) {
@@ -113,6 +120,10 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
   if (warp == 0) {
     // ================================ TMA producer ================================
     if (lane == 0) {
+      if (wres) {
+        tc::mbar_expect_tx(wfull, wres_bytes);
+        for (int kb = 0; kb < kblocks; ++kb) tc::tma_load_2d(smem + (uint32_t)kb * BN * 128u, &bmap, kb * GB_BK, 0, wfull);
+      }
       int it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x) {
         const int mt = tile / n_tiles;
@@ -129,9 +140,9 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % NS;
           if (!tc::mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { atomicExch(&g_bf16_error, 5); bad = true; break; }
-          unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
+          unsigned char* a_s = ring + (uint32_t)s * stage_bytes;
           unsigned char* b_s = a_s + GB_A_BYTES;
-          tc::mbar_expect_tx(&full[s], (IM2COL ? 0u : a_bytes) + BN * 128u);
+          tc::mbar_expect_tx(&full[s], (IM2COL ? 0u : a_bytes) + (wres ? 0u : BN * 128u));
           if (g.conv_tma) {
             const int pos = kb / g.kb_per_tap, cb = kb - pos * g.kb_per_tap;
             const int pr = pos / g.pos_w, pc = pos - pr * g.pos_w;
@@ -139,7 +150,7 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
           } else if (!IM2COL) {
             tc::tma_load_2d(a_s, &amap, kb * GB_BK, m0, &full[s]);
           }
-          tc::tma_load_2d(b_s, &bmap, kb * GB_BK, n0, &full[s]);
+          if (!wres) tc::tma_load_2d(b_s, &bmap, kb * GB_BK, n0, &full[s]);
         }
       }
     }
@@ -148,6 +159,7 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
     // ================================ MMA issuer ================================
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(GB_BM, BN);
+      if (wres && !tc::mbar_wait(wfull, 0)) { atomicExch(&g_bf16_error, 6); bad = true; }
       int it = 0, tcnt = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !bad; tile += gridDim.x, ++tcnt) {
         const int ac = tcnt % NACC, aph = (tcnt / NACC) & 1;
@@ -158,7 +170,8 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
           const int s = it % NS;
           if (!tc::mbar_wait(&full[s], (it / NS) & 1)) { atomicExch(&g_bf16_error, 6); bad = true; break; }
           tc::fence_after_sync();
-          const uint32_t a_s = sbase + (uint32_t)s * stage_bytes, b_s = a_s + GB_A_BYTES;
+          const uint32_t a_s = sbase + wres_bytes + (uint32_t)s * stage_bytes;
+          const uint32_t b_s = wres ? sbase + (uint32_t)kb * BN * 128u : a_s + GB_A_BYTES;
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             const uint64_t ad = tc::make_desc_sw128(a_s + (uint32_t)ks * 32u);
@@ -431,7 +444,7 @@ gemm_bf16_kernel(const Bf16GemmArgs g, const __grid_constant__ CUtensorMap amap,
           gather(kb + u + 2, nxt);
           const int s = it % NS;
           if (__any_sync(0xffffffffu, !tc::mbar_wait(&empty[s], ((it / NS) & 1) ^ 1))) { atomicExch(&g_bf16_error, 9); bad = true; break; }
-          unsigned char* a_s = smem + (uint32_t)s * stage_bytes;
+          unsigned char* a_s = ring + (uint32_t)s * stage_bytes;
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             *reinterpret_cast<uint4*>(a_s + tc::sw128_offset(rg + 16 * i, c)) = cur[i];
@@ -621,8 +634,12 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const int tiles = m_tiles * (g.N / g.BN);
   const int grid = tiles < sms ? tiles : sms;
-  const size_t stage = GB_A_BYTES + (size_t)g.BN * 128u;
-  const size_t budget = 227 * 1024, fixed = 256 + 1024;
+  // Weights of at most 64 KB that form a single N tile stay resident in shared memory (a weight tile
+  // re-read from L2 for every M tile costs as much operand traffic as the A tile itself).
+  const size_t wres_bytes = (size_t)g.Kpad * g.BN * 2;
+  g.wres = (!im2col && g.N == g.BN && wres_bytes <= 64 * 1024) ? 1 : 0;
+  const size_t stage = GB_A_BYTES + (g.wres ? 0 : (size_t)g.BN * 128u);
+  const size_t budget = 227 * 1024 - (g.wres ? wres_bytes : 0), fixed = 256 + 1024;
   // Residual by TMA (plain GEMMs with tiles of at most 128 columns): four accumulators and three or
   // four staging slots per epilogue half.  Everything else: two accumulators, two slots, residual
   // rows (if any) by plain loads -- the configuration that measured best without a residual.
@@ -638,7 +655,7 @@ int launch_gemm_bf16(Bf16GemmArgs g, cudaStream_t st) {
   } else {
     while (g.stages > 2 && g.stages * stage + fixed > budget) --g.stages;
   }
-  const size_t smem = g.stages * stage + (size_t)g.ostg * 2 * 16384 + fixed;
+  const size_t smem = (g.wres ? wres_bytes : 0) + g.stages * stage + (size_t)g.ostg * 2 * 16384 + fixed;
   auto kern = im2col ? (tma_out ? gemm_bf16_kernel<true, true, false> : gemm_bf16_kernel<true, false, false>)
                      : (tma_out ? (rtma ? gemm_bf16_kernel<false, true, true> : gemm_bf16_kernel<false, true, false>)
                                 : gemm_bf16_kernel<false, false, false>);

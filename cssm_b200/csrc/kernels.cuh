@@ -126,6 +126,7 @@ struct Bf16GemmArgs {
   int ldo;
   int Kpad, BN, stages;      // filled in by the launcher
   int nacc, ostg;            // TMEM accumulators; staging slots per epilogue half (launcher)
+  int wres;                  // 1: the weights stay resident in shared memory (launcher)
   // conv mode through TMA (filled in by the launcher): an M tile is a patch of Bbox images x Hbox
   // output rows x Wbox output columns (at most 128 pixels); K block kb is `kb_ch` channels from
   // channel (kb % kb_per_tap) * kb_ch of window position kb / kb_per_tap (row = pos / pos_w,
