@@ -361,13 +361,16 @@ dwconv_cl_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ 
 // registers; for each of its four columns it walks the input rows of the window once: KS four-byte
 // shared-memory loads per row (conflict-free: the lanes of a warp are consecutive pairs), each value
 // pair feeds the output rows it belongs to with packed f32x2 FMAs (two channels per instruction).
-template <int KS>
-__global__ void __launch_bounds__(128)
+// Tile geometry as template parameters: CG column groups (32 * CG threads), NC columns per group, TH rows;
+// the launcher picks one that divides the plane (8 x 16 tiles on a 28 x 28 plane compute 31 % more
+// outputs than the plane has).
+template <int KS, int CG, int NC, int TH>
+__global__ void __launch_bounds__(32 * CG)
 dwconv_tiled_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
                     const float* __restrict__ bias, const float* __restrict__ pre_a,
                     const float* __restrict__ pre_b, __nv_bfloat16* __restrict__ y, int H, int W, int C,
                     int add_centre, int gelu) {
-  constexpr int CS = 64, P = (KS - 1) / 2, CG = 4, NC = 4, TW = CG * NC, TH = 8, PW = TW + KS - 1, PH = TH + KS - 1;
+  constexpr int CS = 64, P = (KS - 1) / 2, TW = CG * NC, PW = TW + KS - 1, PH = TH + KS - 1, NT = 32 * CG;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [PH][PW][CS]
   const int tiles_w = (W + TW - 1) / TW, tiles_h = (H + TH - 1) / TH, slices = C / CS;
@@ -383,7 +386,7 @@ dwconv_tiled_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   for (int pr = 0; pr < PH; ++pr) {
     const int hi = h0 + pr - P;
     const bool hin = hi >= 0 && hi < H;
-    for (int q = threadIdx.x; q < PW * CH; q += 128) {
+    for (int q = threadIdx.x; q < PW * CH; q += NT) {
       const int ck = q & (CH - 1), pc = q / CH;
       const int wi = w0 + pc - P;
       const bool in = hin && wi >= 0 && wi < W;
@@ -456,18 +459,18 @@ dwconv_tiled_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   }
 }
 
-template <int KS>
+template <int KS, int CG, int NC, int TH>
 static int launch_dwconv_tiled(const __nv_bfloat16* x, const float* wk, const float* bias, const float* pre_a,
                                const float* pre_b, __nv_bfloat16* y, int Nimg, int H, int W, int C,
                                int add_centre, int gelu, cudaStream_t st) {
-  constexpr int TW = 16, TH = 8;
+  constexpr int TW = CG * NC;
   const size_t smem = (size_t)(TH + KS - 1) * (TW + KS - 1) * 64 * 2;
-  cudaError_t e = cudaFuncSetAttribute(dwconv_tiled_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(dwconv_tiled_kernel<KS, CG, NC, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
   const long long grid = (long long)Nimg * ((H + TH - 1) / TH) * ((W + TW - 1) / TW) * (C / 64);
-  dwconv_tiled_kernel<KS><<<(unsigned)grid, 128, smem, st>>>(x, wk, bias, pre_a, pre_b, y, H, W, C,
-                                                              add_centre, gelu);
+  dwconv_tiled_kernel<KS, CG, NC, TH><<<(unsigned)grid, 32 * CG, smem, st>>>(x, wk, bias, pre_a, pre_b, y, H, W, C,
+                                                                            add_centre, gelu);
   return check_launch();
 }
 
@@ -476,8 +479,17 @@ int launch_dwconv_cl(const __nv_bfloat16* x, const float* wk, const float* bias,
                      int ks, int add_centre, int gelu, cudaStream_t st) {
   if (C % 8 != 0 || (ks != 3 && ks != 7)) return CSSM_ERR_UNSUPPORTED;
   if (y_f32 == nullptr && C % 64 == 0 && (wk == nullptr || (aligned16(wk) && (bias == nullptr || aligned16(bias))))) {
-    if (ks == 7) return launch_dwconv_tiled<7>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
-    return launch_dwconv_tiled<3>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st);
+#define CSSM_DW(KS_, CG_, NC_, TH_) \
+  return launch_dwconv_tiled<KS_, CG_, NC_, TH_>(x, wk, bias, pre_a, pre_b, y, Nimg, H, W, C, add_centre, gelu, st)
+    if (ks == 7) {
+      if (W % 28 == 0 && H % 8 != 0 && H % 7 == 0) CSSM_DW(7, 4, 7, 7);      // 28 x 28 planes
+      if (W % 28 == 0) CSSM_DW(7, 4, 7, 8);                                  // 56 x 56 planes
+      CSSM_DW(7, 4, 4, 8);
+    }
+    if (W == 14 && H == 14) CSSM_DW(3, 2, 7, 7);                             // two tiles per plane
+    if (W == 7 && H == 7) CSSM_DW(3, 1, 7, 7);
+    CSSM_DW(3, 4, 4, 8);
+#undef CSSM_DW
   }
   constexpr int RH = 4;
   const size_t smem = (size_t)(ks * ks * C + C) * 4;
