@@ -242,12 +242,138 @@ stem_conv1_pair_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
   }
 }
 
+// The same conv once more for that shape, on the tensor cores: warp-level mma.sync (m16n8k16, bf16 in,
+// f32 accumulate) -- the contraction is K = 27, far too short for a tcgen05 pipeline (a 128 x 32 tile
+// per barrier round trip was measured at 390 us against the 328 us of the packed-FMA kernel above).
+// A warp owns 16 consecutive output pixels of one row x all 32 channels.  K is laid out as three
+// window rows of ten slots (nine taps*channels + one zero-weight pad), so that every A-fragment
+// register is one ALIGNED 32-bit word of the image: window row ti of pixel wo starts at element
+// 6 wo of image row 2 ho + ti, and lane (g, t) needs words t, t + 4, t + 8, t + 12 of the 15-word
+// patch of pixels g and g + 8 -- eight coalesced loads per lane and tile, no shuffles.  The weights
+// (B fragments) and the bias live in registers.  Epilogue: bias, GELU, bf16; the quad's words pass
+// through a per-warp shared-memory patch so that every lane stores 16 contiguous bytes.
+constexpr int SM_WARPS = 8;
+__global__ void __launch_bounds__(SM_WARPS * 32, 3)
+stem_conv1_mma_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wk,
+                      const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int Nimg, int Hi, int Wi,
+                      int Ho, int Wo, int gelu) {
+  __shared__ __align__(16) uint32_t stage[SM_WARPS][16 * 20];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  // B fragments: slot k = 16 s + 2 t + 8 h (+0, +1) of output channel n = 8 nt + g
+  uint32_t bf[4][2][2];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int sk = 0; sk < 2; ++sk)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float wv[2];
+#pragma unroll
+        for (int e2 = 0; e2 < 2; ++e2) {
+          const int k = 16 * sk + 2 * t + 8 * h + e2, ti = k / 10, e = k - ti * 10;
+          wv[e2] = (ti < 3 && e < 9) ? __ldg(wk + (ti * 9 + e) * 32 + nt * 8 + g) : 0.f;
+        }
+        bf[nt][sk][h] = float2_to_bf16x2(wv[0], wv[1]);
+      }
+  float2 bz[4];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) bz[nt] = __ldg(reinterpret_cast<const float2*>(bias + nt * 8 + 2 * t));
+  // the lane's four words of a patch: word w = t + 4 i -> window row w / 5, word w % 5 of it (15 = none)
+  int wti[4], wj[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const int w = t + 4 * i; wti[i] = w / 5; wj[i] = w - wti[i] * 5; }
+  const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
+  const int tpr = Wo / 16;                               // tiles per output row
+  const long long ntiles = (long long)Nimg * Ho * tpr;
+  // a warp walks a contiguous range of tiles (row after row of one image: the image row shared by two
+  // output rows is still in L1), its coordinates advanced without divisions
+  const long long nwarps = (long long)gridDim.x * SM_WARPS, gw = (long long)blockIdx.x * SM_WARPS + warp;
+  const long long per = (ntiles + nwarps - 1) / nwarps;
+  long long tile = gw * per;
+  const long long tend = tile + per < ntiles ? tile + per : ntiles;
+  // word offsets of the lane's eight patch words from the first word of the tile's window
+  int woff[2][4];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) woff[hh][i] = ((wti[i] * Wi + 2 * (g + 8 * hh)) * 3 >> 1) + wj[i];
+  auto fetch = [&](bool live, long long base, int ho, int wt, uint32_t (&a)[2][4]) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const bool v2 = 2 * (wt * 16 + g + 8 * hh) + 2 < Wi;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool ok = live && wti[i] < 3 && 2 * ho + wti[i] < Hi && (wj[i] < 3 || v2);
+        uint32_t u = 0u;
+        if (ok) u = __ldg(xw + base + woff[hh][i]);
+        if (wj[i] == 4) u &= 0xFFFFu;                     // the upper half belongs to the next pixel
+        a[hh][i] = u;
+      }
+    }
+  };
+  // coordinates of `tile`: (image * Ho + ho) = rowi, tile of the row wt; window word base
+  long long rowi = tile < ntiles ? tile / tpr : 0;
+  int wt = (int)(tile < ntiles ? tile - rowi * tpr : 0);
+  int ho = (int)(rowi % Ho);
+  long long b_ = rowi / Ho;
+  auto base_of = [&](long long bb, int h, int w) { return ((bb * Hi + 2 * h) * Wi + 32 * w) * 3 >> 1; };
+  uint32_t cur[2][4], nxt[2][4];
+  fetch(tile < tend, base_of(b_, ho, wt), ho, wt, cur);
+  for (; tile < tend; ++tile) {
+    // coordinates of the next tile
+    int wt2 = wt + 1, ho2 = ho;
+    long long b2 = b_, rowi2 = rowi;
+    if (wt2 == tpr) { wt2 = 0; ++rowi2; if (++ho2 == Ho) { ho2 = 0; ++b2; } }
+    fetch(tile + 1 < tend, base_of(b2, ho2, wt2), ho2, wt2, nxt);
+    float c[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) { c[nt][0] = bz[nt].x; c[nt][1] = bz[nt].y; c[nt][2] = bz[nt].x; c[nt][3] = bz[nt].y; }
+    // A fragment of k-step s: {row g: word t + 8 s, row g + 8: same, row g: word t + 8 s + 4, row g + 8: same}
+#pragma unroll
+    for (int sk = 0; sk < 2; ++sk)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[nt][0]), "+f"(c[nt][1]), "+f"(c[nt][2]), "+f"(c[nt][3])
+            : "r"(cur[0][2 * sk]), "r"(cur[1][2 * sk]), "r"(cur[0][2 * sk + 1]), "r"(cur[1][2 * sk + 1]),
+              "r"(bf[nt][sk][0]), "r"(bf[nt][sk][1]));
+    uint32_t* sp = stage[warp];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      if (gelu) { gelu_tanh_x2(c[nt][0], c[nt][1]); gelu_tanh_x2(c[nt][2], c[nt][3]); }
+      sp[g * 20 + 4 * nt + t] = float2_to_bf16x2(c[nt][0], c[nt][1]);
+      sp[(g + 8) * 20 + 4 * nt + t] = float2_to_bf16x2(c[nt][2], c[nt][3]);
+    }
+    __syncwarp();
+    __nv_bfloat16* yo = y + ((rowi * Wo + wt * 16) * 32);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int p = (lane >> 2) + 8 * hh;
+      *reinterpret_cast<uint4*>(yo + p * 32 + (lane & 3) * 8) = *reinterpret_cast<const uint4*>(sp + p * 20 + (lane & 3) * 4);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cur[hh][i] = nxt[hh][i];
+    wt = wt2; ho = ho2; b_ = b2; rowi = rowi2;
+  }
+}
+
 int launch_stem_conv1(const __nv_bfloat16* x, const float* wk, const float* bias, __nv_bfloat16* y,
                       int Nimg, int Hi, int Wi, int Cin, int Co, int gelu, cudaStream_t st) {
   if (Co % 8 != 0 || Cin > 16) return CSSM_ERR_UNSUPPORTED;
   const int Ho = (Hi + 1) / 2, Wo = (Wi + 1) / 2;
   const int pad_h = ((Ho - 1) * 2 + 3 - Hi > 0 ? (Ho - 1) * 2 + 3 - Hi : 0) / 2;
   const int pad_w = ((Wo - 1) * 2 + 3 - Wi > 0 ? (Wo - 1) * 2 + 3 - Wi : 0) / 2;
+  if (Cin == 3 && Co == 32 && Hi % 2 == 0 && Wi % 32 == 0 && aligned16(x) && aligned16(y) && aligned16(bias)) {
+    const long long tiles = (long long)Nimg * Ho * (Wo / 16);
+    long long blocks = (tiles + SM_WARPS - 1) / SM_WARPS;
+    if (blocks > 148 * 3) blocks = 148 * 3;                // one wave at three resident blocks per SM
+    stem_conv1_mma_kernel<<<(int)blocks, SM_WARPS * 32, 0, st>>>(x, wk, bias, y, Nimg, Hi, Wi, Ho, Wo, gelu);
+    return check_launch();
+  }
   if (Cin == 3 && Co == 32 && Hi % 2 == 0 && Wi % 4 == 0 && aligned16(x) && aligned16(y)) {
     const long long pairs = (long long)Nimg * Ho * (Wo / 2);
     long long blocks = (pairs + 127) / 128;
