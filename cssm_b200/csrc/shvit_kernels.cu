@@ -938,9 +938,70 @@ head_kernel(const float* __restrict__ pooled, const float* __restrict__ W, const
   for (int j = 0; j < 8; ++j)
     if (n0 + j < Nimg) logits[(size_t)(n0 + j) * K + k] = acc[j];
 }
+// The same product with the weights read from L2 once per CTA instead of once per eight samples: a CTA
+// keeps a slice of 64 classes (C x 64 floats) and its share of the pooled rows in shared memory, about
+// one CTA per SM; thread = one class x every fourth sample of the CTA, four samples at a time.
+constexpr int HT_K = 64;
+__global__ void __launch_bounds__(256)
+head_tile_kernel(const float* __restrict__ pooled, const float* __restrict__ W, const float* __restrict__ b,
+                 float* __restrict__ logits, int Nimg, int C, int K, int spc) {
+  extern __shared__ __align__(16) float hs[];
+  float* Ws = hs;                                      // [C][64]
+  float* ps = hs + (size_t)C * HT_K;                   // [spc][C]
+  const int k0 = blockIdx.x * HT_K, n0 = blockIdx.y * spc;
+  const int ns = Nimg - n0 < spc ? Nimg - n0 : spc;
+  for (int i = threadIdx.x; i < C * (HT_K / 4); i += 256) {
+    const int c = i / (HT_K / 4), k4 = (i - c * (HT_K / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k0 + k4 < K) v = __ldg(reinterpret_cast<const float4*>(W + (size_t)c * K + k0 + k4));   // K % 4 == 0
+    *reinterpret_cast<float4*>(Ws + c * HT_K + k4) = v;
+  }
+  for (int i = threadIdx.x; i < ns * (C / 4); i += 256)
+    reinterpret_cast<float4*>(ps)[i] = __ldg(reinterpret_cast<const float4*>(pooled + (size_t)n0 * C) + i);
+  __syncthreads();
+  const int kk = threadIdx.x & (HT_K - 1), sl = threadIdx.x / HT_K;      // class, sample lane 0..3
+  if (k0 + kk >= K) return;
+  const float bias = b[k0 + kk];
+  for (int j0 = sl; j0 < ns; j0 += 16) {
+    float acc[4] = {bias, bias, bias, bias};
+    const float* pj[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) pj[m] = ps + (size_t)(j0 + 4 * m < ns ? j0 + 4 * m : j0) * C;
+    for (int c = 0; c < C; c += 4) {
+      const float w0 = Ws[c * HT_K + kk], w1 = Ws[(c + 1) * HT_K + kk], w2 = Ws[(c + 2) * HT_K + kk],
+                  w3 = Ws[(c + 3) * HT_K + kk];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const float4 p = *reinterpret_cast<const float4*>(pj[m] + c);
+        acc[m] = fmaf(p.x, w0, acc[m]); acc[m] = fmaf(p.y, w1, acc[m]);
+        acc[m] = fmaf(p.z, w2, acc[m]); acc[m] = fmaf(p.w, w3, acc[m]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+      if (j0 + 4 * m < ns) logits[(size_t)(n0 + j0 + 4 * m) * K + k0 + kk] = acc[m];
+  }
+}
 int launch_head(const float* pooled, const float* W, const float* b, float* logits, int Nimg, int C, int K,
                 cudaStream_t st) {
   if (C % 4 != 0) return CSSM_ERR_UNSUPPORTED;
+  if (K % 4 == 0 && Nimg >= 64 && aligned16(W) && aligned16(pooled)) {
+    const int nx = (K + HT_K - 1) / HT_K;
+    int ny = 148 / nx > 0 ? 148 / nx : 1;
+    int spc = (Nimg + ny - 1) / ny;
+    const size_t cap = 200 * 1024;
+    const size_t wbytes = (size_t)C * HT_K * 4;
+    if (wbytes + 4 * (size_t)C * 4 <= cap) {
+      const int spc_max = (int)((cap - wbytes) / ((size_t)C * 4));
+      if (spc > spc_max) spc = spc_max;
+      ny = (Nimg + spc - 1) / spc;
+      const size_t smem = wbytes + (size_t)spc * C * 4;
+      cudaError_t e = cudaFuncSetAttribute(head_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) { set_cuda_error(e); return CSSM_ERR_CUDA; }
+      head_tile_kernel<<<dim3(nx, ny), 256, smem, st>>>(pooled, W, b, logits, Nimg, C, K, spc);
+      return check_launch();
+    }
+  }
   dim3 grid((K + 127) / 128, (Nimg + 7) / 8);
   head_kernel<<<grid, 128, (size_t)8 * C * 4, st>>>(pooled, W, b, logits, Nimg, C, K);
   return check_launch();
