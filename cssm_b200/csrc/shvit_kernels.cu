@@ -509,31 +509,61 @@ dwconv_tiled_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   // (with the LayerNorm affine the values pass through registers instead)
   constexpr int CH = CS / 8;                         // 16-byte chunks per pixel of the slice
   const __nv_bfloat16* xn = x + (size_t)n * H * W * C + cs0;
-  for (int pr = 0; pr < PH; ++pr) {
-    const int hi = h0 + pr - P;
-    const bool hin = hi >= 0 && hi < H;
-    for (int q = threadIdx.x; q < PW * CH; q += NT) {
-      const int ck = q & (CH - 1), pc = q / CH;
-      const int wi = w0 + pc - P;
-      const bool in = hin && wi >= 0 && wi < W;
-      __nv_bfloat16* dst = tile + ((size_t)pr * PW + pc) * CS + ck * 8;
-      const __nv_bfloat16* src = xn + ((size_t)(in ? hi : 0) * W + (in ? wi : 0)) * C + ck * 8;
-      if (pre_a == nullptr) {
+  // the thread's chunk of eight channels is the same for every element it stages (NT is a multiple of
+  // CH): its LayerNorm affine is fetched once, with four 16-byte loads
+  float pav[8], pbv[8];
+  if (pre_a != nullptr) {
+    const int ck0 = threadIdx.x & (CH - 1);
+    const float4* pa4 = reinterpret_cast<const float4*>(pre_a + (size_t)n * C + cs0 + ck0 * 8);
+    const float4* pb4 = reinterpret_cast<const float4*>(pre_b + (size_t)n * C + cs0 + ck0 * 8);
+    const float4 a0 = __ldg(pa4), a1 = __ldg(pa4 + 1), b0 = __ldg(pb4), b1 = __ldg(pb4 + 1);
+    pav[0] = a0.x; pav[1] = a0.y; pav[2] = a0.z; pav[3] = a0.w; pav[4] = a1.x; pav[5] = a1.y; pav[6] = a1.z; pav[7] = a1.w;
+    pbv[0] = b0.x; pbv[1] = b0.y; pbv[2] = b0.z; pbv[3] = b0.w; pbv[4] = b1.x; pbv[5] = b1.y; pbv[6] = b1.z; pbv[7] = b1.w;
+  }
+  if (pre_a == nullptr) {
+    for (int pr = 0; pr < PH; ++pr) {
+      const int hi = h0 + pr - P;
+      const bool hin = hi >= 0 && hi < H;
+      for (int q = threadIdx.x; q < PW * CH; q += NT) {
+        const int ck = q & (CH - 1), pc = q / CH;
+        const int wi = w0 + pc - P;
+        const bool in = hin && wi >= 0 && wi < W;
+        __nv_bfloat16* dst = tile + ((size_t)pr * PW + pc) * CS + ck * 8;
+        const __nv_bfloat16* src = xn + ((size_t)(in ? hi : 0) * W + (in ? wi : 0)) * C + ck * 8;
         // src-size 0 writes zeros
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
                      ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(in ? 16 : 0) : "memory");
-      } else {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (in) {
-          float f[8];
-          unpack8(__ldg(reinterpret_cast<const uint4*>(src)), f);
-          const float* pa = pre_a + (size_t)n * C + cs0 + ck * 8;
-          const float* pb = pre_b + (size_t)n * C + cs0 + ck * 8;
+      }
+    }
+  } else {
+    // through registers, six 16-byte loads in flight per thread
+    constexpr int TOT = PH * PW * CH, SBN = 6;
+    for (int base = threadIdx.x; base < TOT; base += NT * SBN) {
+      uint4 raw[SBN];
+      bool inb[SBN];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = fmaf(__ldg(pa + j), f[j], __ldg(pb + j));
+      for (int u = 0; u < SBN; ++u) {
+        const int i = base + u * NT;
+        const int pr = i / (PW * CH), q = i - pr * (PW * CH);
+        const int ck = q & (CH - 1), pc = q / CH;
+        const int hi = h0 + pr - P, wi = w0 + pc - P;
+        inb[u] = i < TOT && hi >= 0 && hi < H && wi >= 0 && wi < W;
+        raw[u] = inb[u] ? __ldg(reinterpret_cast<const uint4*>(xn + ((size_t)hi * W + wi) * C + ck * 8))
+                        : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < SBN; ++u) {
+        const int i = base + u * NT;
+        if (i >= TOT) continue;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (inb[u]) {
+          float f[8];
+          unpack8(raw[u], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = fmaf(pav[j], f[j], pbv[j]);
           v = pack8(f);
         }
-        *reinterpret_cast<uint4*>(dst) = v;
+        *reinterpret_cast<uint4*>(tile + (size_t)i * 8) = v;        // [pr][pc][ck] is the order of i
       }
     }
   }
