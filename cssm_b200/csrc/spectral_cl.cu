@@ -111,12 +111,16 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
   const int k_lo = hf ? KH : 0, k_hi = hf ? Wf : KH;
 
   // ---- stage x tile and the sample's gate map ----
+  // (asynchronous 16-byte copies: every request of the tile is in flight at once)
   for (int q = tid; q < P * 8; q += SCL_TPB) {
     const int p = q >> 3, j = q & 7;
-    *reinterpret_cast<uint4*>(tile + p * SCL_PL + j * 8) =
-        __ldg(reinterpret_cast<const uint4*>(xin + (size_t)p * ld + j * 8));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(tile + p * SCL_PL + j * 8)),
+                   "l"(xin + (size_t)p * ld + j * 8) : "memory");
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
   for (int i = tid; i < NB; i += SCL_TPB) gs[i] = __ldg(gates + (size_t)n * NB + i);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
   // ---- forward rows: real N-point DFT -> Wf bins, scaled by 1/N ----
@@ -138,11 +142,14 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
   }
   __syncthreads();                      // x tile consumed; row spectra of both halves visible
   // ---- z tile (already through SiLU) into the same buffer ----
+  // (asynchronous copies again: they land while the column pass runs)
   for (int q = tid; q < P * 8; q += SCL_TPB) {
     const int p = q >> 3, j = q & 7;
-    *reinterpret_cast<uint4*>(tile + p * SCL_PL + j * 8) =
-        __ldg(reinterpret_cast<const uint4*>(xin + C + (size_t)p * ld + j * 8));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(tile + p * SCL_PL + j * 8)),
+                   "l"(xin + C + (size_t)p * ld + j * 8) : "memory");
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
 
   // ---- columns: forward DFT, gates (T = 1: h = U), inverse DFT ----
 #pragma unroll 1
@@ -166,6 +173,7 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
 #pragma unroll
     for (int h = 0; h < N; ++h) R[(h * Wf + k) * SCL_PL + pl] = __floats2half2_rn(vr[h], vi[h]);
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();                      // z tile complete; columns of both halves visible
 
   // ---- inverse rows (C2R: imaginary parts of the DC and Nyquist bins are ignored), * z ----
