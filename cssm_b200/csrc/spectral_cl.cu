@@ -129,15 +129,50 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
     float xv[N];
 #pragma unroll
     for (int w = 0; w < N; ++w) xv[w] = __bfloat162float(tile[(h * N + w) * SCL_PL + pl]) * INV_N;
+    if constexpr (N == 14) {
+      // radix 2 x 7: real 7-point DFTs of the even and the odd samples (bins 0..3, the others are their
+      // conjugates), X[k] = E[k mod 7] + W14^k O[k mod 7]: 110 multiply-adds per row instead of 208
+      float er[4], ei[4], od[4], oi[4];
 #pragma unroll
-    for (int k = 0; k < Wf; ++k) {
-      float ar = xv[0], ai = 0.f;
+      for (int par = 0; par < 2; ++par) {
+        float (&yr)[4] = par ? od : er;
+        float (&yi)[4] = par ? oi : ei;
+        yr[0] = xv[par]; yi[0] = 0.f;
 #pragma unroll
-      for (int w = 1; w < N; ++w) {
-        ar = fmaf(xv[w], Tw<N>::c((w * k) % N), ar);
-        ai = fmaf(xv[w], -Tw<N>::s((w * k) % N), ai);
+        for (int n = 1; n < 7; ++n) yr[0] += xv[par + 2 * n];
+#pragma unroll
+        for (int k = 1; k < 4; ++k) {
+          float ar = xv[par], ai = 0.f;
+#pragma unroll
+          for (int n = 1; n < 7; ++n) {
+            ar = fmaf(xv[par + 2 * n], Tw<7>::c((n * k) % 7), ar);
+            ai = fmaf(xv[par + 2 * n], -Tw<7>::s((n * k) % 7), ai);
+          }
+          yr[k] = ar; yi[k] = ai;
+        }
       }
-      R[(h * Wf + k) * SCL_PL + pl] = __floats2half2_rn(ar, ai);
+      R[(h * Wf + 0) * SCL_PL + pl] = __floats2half2_rn(er[0] + od[0], 0.f);
+      R[(h * Wf + 7) * SCL_PL + pl] = __floats2half2_rn(er[0] - od[0], 0.f);
+#pragma unroll
+      for (int k = 1; k < 7; ++k) {
+        const int kk = k <= 3 ? k : 7 - k;
+        const float e_r = er[kk], e_i = k <= 3 ? ei[kk] : -ei[kk];
+        const float o_r = od[kk], o_i = k <= 3 ? oi[kk] : -oi[kk];
+        const float xr = fmaf(o_i, Tw<14>::s(k), fmaf(o_r, Tw<14>::c(k), e_r));
+        const float xi = fmaf(-o_r, Tw<14>::s(k), fmaf(o_i, Tw<14>::c(k), e_i));
+        R[(h * Wf + k) * SCL_PL + pl] = __floats2half2_rn(xr, xi);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < Wf; ++k) {
+        float ar = xv[0], ai = 0.f;
+#pragma unroll
+        for (int w = 1; w < N; ++w) {
+          ar = fmaf(xv[w], Tw<N>::c((w * k) % N), ar);
+          ai = fmaf(xv[w], -Tw<N>::s((w * k) % N), ai);
+        }
+        R[(h * Wf + k) * SCL_PL + pl] = __floats2half2_rn(ar, ai);
+      }
     }
   }
   __syncthreads();                      // x tile consumed; row spectra of both halves visible
@@ -184,6 +219,34 @@ gated_spectral_cl_kernel(const __nv_bfloat16* __restrict__ xz, int ld, int C,
     for (int k = 0; k < Wf; ++k) {
       const float2 v = __half22float2(R[(h * Wf + k) * SCL_PL + pl]);
       cr[k] = v.x; ci[k] = v.y;
+    }
+    if constexpr (N == 14) {
+      // radix 2 x 7 the other way: A[k] = X[k] + conj X[7-k] gives the even samples, B[k] =
+      // (X[k] - conj X[7-k]) e^{2 pi i k / 14} the odd ones, each by a real-output 7-point inverse DFT
+      // from bins 0..3 (the imaginary parts of the DC and Nyquist bins do not enter)
+      float a_r[4], a_i[4], b_r[4], b_i[4];
+      ci[0] = 0.f; ci[7] = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float dr = cr[k] - cr[7 - k], di = ci[k] + ci[7 - k];
+        a_r[k] = cr[k] + cr[7 - k]; a_i[k] = ci[k] - ci[7 - k];
+        b_r[k] = dr * Tw<14>::c(k) - di * Tw<14>::s(k);
+        b_i[k] = dr * Tw<14>::s(k) + di * Tw<14>::c(k);
+      }
+#pragma unroll
+      for (int m = 0; m < 7; ++m) {
+        float se = 0.f, so = 0.f;
+#pragma unroll
+        for (int k = 1; k < 4; ++k) {
+          se = fmaf(a_r[k], Tw<7>::c((m * k) % 7), se); se = fmaf(-a_i[k], Tw<7>::s((m * k) % 7), se);
+          so = fmaf(b_r[k], Tw<7>::c((m * k) % 7), so); so = fmaf(-b_i[k], Tw<7>::s((m * k) % 7), so);
+        }
+        const float ve = fmaf(2.f, se, a_r[0]), vo = fmaf(2.f, so, b_r[0]);
+        const int idx = (h * N + 2 * m) * SCL_PL + pl;
+        tile[idx] = __float2bfloat16(ve * __bfloat162float(tile[idx]));
+        tile[idx + SCL_PL] = __float2bfloat16(vo * __bfloat162float(tile[idx + SCL_PL]));
+      }
+      continue;
     }
     constexpr int KM = (N - 1) / 2;               // bins with a conjugate partner
 #pragma unroll
